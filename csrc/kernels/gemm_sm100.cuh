@@ -1,0 +1,370 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a, shared by the plain GEMM entry point and the
+// fused communication variants (all-gather -> GEMM, GEMM -> reduce-scatter).
+//
+//   C[M,N] = epilogue(alpha * A * B)   with fp32 accumulation in tensor memory
+//
+// Operand layouts (element type bf16):
+//   A_MAJOR = 0: A is stored [M, K] row-major (K contiguous);   A_MAJOR = 1: A is stored [K, M] row-major.
+//   B_MAJOR = 0: B is stored [N, K] row-major (K contiguous);   B_MAJOR = 1: B is stored [K, N] row-major.
+// so (0,0) is x @ W^T of a Linear layer, (0,1) is dY @ W, (1,1) is dY^T @ X.
+//
+// Pipeline per CTA (192 threads, one CTA per SM, grid-stride over output tiles):
+//   warp 0   : TMA producer   (cp.async.bulk.tensor, 128-byte swizzle, mbarrier complete_tx)
+//   warp 1   : MMA issuer     (tcgen05.mma 128 x BLOCK_N x 16, accumulators double-buffered in TMEM)
+//   warps 2-5: epilogue       (tcgen05.ld -> registers -> bias / GELU / residual / accumulate -> global)
+// The epilogue of tile i overlaps the main loop of tile i+1 through the two TMEM accumulator buffers.
+//
+// Hooks: a `TileGate` functor lets a fused variant delay a tile until the data it needs has arrived
+// (all-gather -> GEMM) and a `TileDone` functor lets it publish a finished tile (GEMM -> reduce-scatter).
+#pragma once
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace lt {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  int out_fp32;
+  const __nv_bfloat16* bias;      // [N] or nullptr
+  const __nv_bfloat16* residual;  // [M, N] (pitch ldr) or nullptr
+  long long ldr;
+  int act;         // 0 none, 1 GELU(tanh)
+  int accumulate;  // C += result
+  float alpha;
+  int m_blocks, n_blocks, k_blocks, num_tiles;
+  int group_m;  // raster group height (tiles)
+  int* status;
+};
+
+template <int BLOCK_N>
+struct GemmCfg {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BLOCK_N;
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+};
+
+struct NoGate {
+  __device__ __forceinline__ bool operator()(int, int, int, int*) const { return true; }
+};
+struct NoDone {
+  __device__ __forceinline__ void operator()(int, int) const {}
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.n_blocks;
+  const int group = tile / per_group;
+  const int first_m = group * p.group_m;
+  const int rows = min(p.m_blocks - first_m, p.group_m);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % rows;
+  n_blk = in_group / rows;
+}
+
+// One 32-column slice of one output row.
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32]) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  const bool full = (col0 + 32 <= p.N);
+  const int ncols = full ? 32 : (p.N - col0);
+  if (p.bias) {
+    if (full) {
+      const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u = __ldg(b4 + q);
+        float2 f;
+        f = unpack_bf16x2(u.x); v[q * 8 + 0] += f.x; v[q * 8 + 1] += f.y;
+        f = unpack_bf16x2(u.y); v[q * 8 + 2] += f.x; v[q * 8 + 3] += f.y;
+        f = unpack_bf16x2(u.z); v[q * 8 + 4] += f.x; v[q * 8 + 5] += f.y;
+        f = unpack_bf16x2(u.w); v[q * 8 + 6] += f.x; v[q * 8 + 7] += f.y;
+      }
+    } else {
+      _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(p.bias[col0 + j]);
+    }
+  }
+  if (p.act == 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+  }
+  if (p.residual) {
+    const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
+    if (full && (p.ldr % 8 == 0)) {
+      const uint4* r4 = reinterpret_cast<const uint4*>(rp);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u = r4[q];
+        float2 f;
+        f = unpack_bf16x2(u.x); v[q * 8 + 0] += f.x; v[q * 8 + 1] += f.y;
+        f = unpack_bf16x2(u.y); v[q * 8 + 2] += f.x; v[q * 8 + 3] += f.y;
+        f = unpack_bf16x2(u.z); v[q * 8 + 4] += f.x; v[q * 8 + 5] += f.y;
+        f = unpack_bf16x2(u.w); v[q * 8 + 6] += f.x; v[q * 8 + 7] += f.y;
+      }
+    } else {
+      _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(rp[j]);
+    }
+  }
+  if (p.out_fp32) {
+    float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+    if (full && (p.ldc % 4 == 0)) {
+      float4* c4 = reinterpret_cast<float4*>(cp);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        if (p.accumulate) {
+          float4 old = c4[q];
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        c4[q] = o;
+      }
+    } else {
+      _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) cp[j] = p.accumulate ? cp[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+    if (full && (p.ldc % 8 == 0)) {
+      uint4* c4 = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (p.accumulate) {
+          uint4 old = c4[q];
+          float2 f;
+          f = unpack_bf16x2(old.x); v[q * 8 + 0] += f.x; v[q * 8 + 1] += f.y;
+          f = unpack_bf16x2(old.y); v[q * 8 + 2] += f.x; v[q * 8 + 3] += f.y;
+          f = unpack_bf16x2(old.z); v[q * 8 + 4] += f.x; v[q * 8 + 5] += f.y;
+          f = unpack_bf16x2(old.w); v[q * 8 + 6] += f.x; v[q * 8 + 7] += f.y;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        c4[q] = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j >= ncols) break;
+        float o = v[j];
+        if (p.accumulate) o += __bfloat162float(cp[j]);
+        cp[j] = __float2bfloat16(o);
+      }
+    }
+  }
+}
+
+// The body shared by all GEMM kernels. `gate(m_blk, n_blk, kb, status)` is called by the producer
+// before it loads k-block kb of a tile and returns false if a bounded wait ran out; `done(m_blk, n_blk)`
+// is called by one thread of each epilogue warp after the warp's rows of a tile are in global memory.
+template <int BLOCK_N, int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
+__device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
+                                          TileGate gate, TileDone done) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* issued_parity = reinterpret_cast<volatile int*>(tmem_holder + 2);  // [S]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      issued_parity[s] = -1;
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(tmA);
+    tma_prefetch_desc(tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(p, tile, m_blk, n_blk);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!gate(m_blk, n_blk, kb, p.status)) { *abort_flag = 1; ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, Cfg::kStageBytes);
+          issued_parity[stage] = int(phase);
+          const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          if (A_MAJOR == 0) {
+            tma_load_2d(a_dst, tmA, fb, kb * kBlockK, m_blk * kBlockM);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBlockM / 64; ++i)
+              tma_load_2d(a_dst + i * (64 * kBlockK * 2), tmA, fb, m_blk * kBlockM + i * 64, kb * kBlockK);
+          }
+          if (B_MAJOR == 0) {
+            tma_load_2d(b_dst, tmB, fb, kb * kBlockK, n_blk * BLOCK_N);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BLOCK_N / 64; ++i)
+              tma_load_2d(b_dst + i * (64 * kBlockK * 2), tmB, fb, n_blk * BLOCK_N + i * 64, kb * kBlockK);
+          }
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, 1, A_MAJOR, B_MAJOR);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aphase ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t adesc = (A_MAJOR == 0) ? make_smem_desc_sw128(a_addr + k * (kUmmaK * 2), 16, 1024)
+                                                  : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
+            const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
+                                                  : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const bool got = mbar_wait(tfull_bar(buf), aphase, abort_flag, p.status, kStatusTimeoutTmemFull);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      const int row = m_blk * kBlockM + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * BLOCK_N + c * 32;
+        if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(tempty_bar(buf));
+        done(m_blk, n_blk);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // Give copies that are still in flight a bounded chance to land before shared memory is released.
+    for (int s = 0; s < S; ++s) {
+      const int par = issued_parity[s];
+      if (par < 0) continue;
+      for (int spin = 0; spin < 20000; ++spin) {
+        if (mbar_try_wait(full_bar(s), uint32_t(par))) break;
+        __nanosleep(100);
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// Host: fill tile counts and pick BLOCK_N when the caller did not.
+inline int pick_block_n(int M, int N, int sms) {
+  const int mb = (M + kBlockM - 1) / kBlockM;
+  auto eff = [&](int bn) {
+    const long long tiles = (long long)mb * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double useful = double(M) * double(N);
+    const double done = double(waves) * sms * kBlockM * bn;
+    return useful / done;
+  };
+  const double e256 = eff(256), e128 = eff(128) * 0.93;
+  return (e256 >= e128) ? 256 : 128;
+}
+
+inline void fill_tiles(GemmParams& p, int block_n) {
+  p.m_blocks = (p.M + kBlockM - 1) / kBlockM;
+  p.n_blocks = (p.N + block_n - 1) / block_n;
+  p.k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.group_m = 16;
+}
+
+// Host: tensor maps for the two operands.
+inline int make_operand_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
+                             long long lda, long long ldb, int a_major, int b_major, int block_n) {
+  int r;
+  if (a_major == 0) r = encode_tmap_2d(tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, kBlockK, kBlockM, 1);
+  else              r = encode_tmap_2d(tmA, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, kBlockK, 1);
+  if (r) return 1000 + r;
+  if (b_major == 0) r = encode_tmap_2d(tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBlockK, block_n, 1);
+  else              r = encode_tmap_2d(tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBlockK, 1);
+  if (r) return 2000 + r;
+  return 0;
+}
+
+}  // namespace lt

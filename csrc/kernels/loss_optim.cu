@@ -1,0 +1,370 @@
+// Cross-entropy (vocab-parallel capable, backward fused in place) and the optimizer kernels.
+//
+// Reference counterparts: cross_entropy_loss_forward/backward, one thread per row and a serial loop over
+// the vocabulary (src/backend/gpu_native/nn/nn_kernels.cu:1070-1116); adamw_step_kernel launched once per
+// parameter tensor (src/backend/gpu_native/optim/optimizers.cu:3-124); GradScaler's inf check through
+// Ops::max(Ops::abs(g)) (src/optim/grad_scaler.cpp:29-33); host-side clip_grad_norm_ (src/ops/clip_grad.cpp:8-52).
+//
+// Here: a CTA per row with an online (max, sum-exp) scan; the statistics of a vocabulary shard are
+// exposed so that tensor-parallel ranks can combine them with one tiny collective before the in-place
+// gradient pass; AdamW/Adam/SGD/RMSprop run over flat buffers or over a pointer table in ONE launch,
+// with the gradient unscale and the skip-on-overflow decision read from device memory.
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace lt {
+
+constexpr int kCeThreads = 256;
+
+__device__ __forceinline__ void ce_ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+// stats[row] = {max, sum exp(l - max), target logit if the target falls in [vocab_start, vocab_start+V) else 0}
+__global__ void __launch_bounds__(kCeThreads)
+ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets,
+                int vocab_start, int N, int V, float* __restrict__ stats) {
+  __shared__ float sm[32], ss[32];
+  for (int row = blockIdx.x; row < N; row += gridDim.x) {
+    const __nv_bfloat16* lr = logits + (long long)row * ldl;
+    float m = -INFINITY, s = 0.f;
+    const int v8 = V / 8;
+    for (int i = threadIdx.x; i < v8; i += blockDim.x) {
+      float f[8];
+      ce_ld8(lr + i * 8, f);
+      float cm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) cm = fmaxf(cm, f[j]);
+      const float nm = fmaxf(m, cm);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+      s = s * __expf(m - nm) + acc;
+      m = nm;
+    }
+    for (int i = v8 * 8 + threadIdx.x; i < V; i += blockDim.x) {
+      const float f = __bfloat162float(lr[i]);
+      const float nm = fmaxf(m, f);
+      s = s * __expf(m - nm) + __expf(f - nm);
+      m = nm;
+    }
+    // combine (m, s) across the block
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      const float nm = fmaxf(m, om);
+      s = (m == -INFINITY ? 0.f : s * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+      m = nm;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { sm[warp] = m; ss[warp] = s; }
+    __syncthreads();
+    if (warp == 0) {
+      m = (lane < (blockDim.x >> 5)) ? sm[lane] : -INFINITY;
+      s = (lane < (blockDim.x >> 5)) ? ss[lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const float os = __shfl_xor_sync(0xffffffffu, s, o);
+        const float nm = fmaxf(m, om);
+        s = (m == -INFINITY ? 0.f : s * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+        m = nm;
+      }
+      if (lane == 0) {
+        const long long t = targets[row] - vocab_start;
+        stats[row * 3 + 0] = m;
+        stats[row * 3 + 1] = s;
+        stats[row * 3 + 2] = (t >= 0 && t < V) ? __bfloat162float(lr[t]) : 0.f;
+      }
+    }
+  }
+}
+
+// gstats[row] = {global max, global sum-exp, target logit}.  loss[row] = log(sum) + max - target (0 if ignored);
+// logits are overwritten by dlogits = (softmax - onehot) * grad_scale when write_grad != 0.
+__global__ void __launch_bounds__(kCeThreads)
+ce_finish_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets,
+                 int vocab_start, int N, int V, const float* __restrict__ gstats, float* __restrict__ loss,
+                 float grad_scale, long long ignore_index, int write_grad) {
+  for (int row = blockIdx.x; row < N; row += gridDim.x) {
+    __nv_bfloat16* lr = logits + (long long)row * ldl;
+    const long long tgt = targets[row];
+    const bool ignored = (tgt == ignore_index);
+    const float gm = gstats[row * 3 + 0], gs = gstats[row * 3 + 1], gt = gstats[row * 3 + 2];
+    if (threadIdx.x == 0 && loss) loss[row] = ignored ? 0.f : (__logf(gs) + gm - gt);
+    if (!write_grad) continue;
+    const float inv = ignored ? 0.f : grad_scale / gs;
+    const long long t = tgt - vocab_start;
+    const int v8 = V / 8;
+    for (int i = threadIdx.x; i < v8; i += blockDim.x) {
+      float f[8];
+      ce_ld8(lr + i * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float g = __expf(f[j] - gm) * inv;
+        if (!ignored && (long long)(i * 8 + j) == t) g -= grad_scale;
+        f[j] = g;
+      }
+      uint4 u;
+      u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+      u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+      *reinterpret_cast<uint4*>(lr + i * 8) = u;
+    }
+    for (int i = v8 * 8 + threadIdx.x; i < V; i += blockDim.x) {
+      float g = __expf(__bfloat162float(lr[i]) - gm) * inv;
+      if (!ignored && (long long)i == t) g -= grad_scale;
+      lr[i] = __float2bfloat16(g);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- optimizers
+struct AdamArgs {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;  // bc = 1 - beta^t
+  int adamw;                                  // 1 decoupled weight decay, 0 L2 (Adam)
+};
+
+__device__ __forceinline__ float adam_update(float p, float g, float& m, float& v, const AdamArgs& a) {
+  if (!a.adamw) g += a.wd * p;
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  const float mh = m / a.bc1, vh = v / a.bc2;
+  if (a.adamw) p -= a.lr * a.wd * p;
+  return p - a.lr * mh / (sqrtf(vh) + a.eps);
+}
+
+// dyn (nullable, device): dyn[0] = multiplier applied to every gradient, dyn[1] != 0 -> skip the step.
+template <typename GradT>
+__global__ void adam_flat_kernel(float* __restrict__ master, const GradT* __restrict__ grad, float* __restrict__ m,
+                                 float* __restrict__ v, __nv_bfloat16* __restrict__ param_bf16, long long n,
+                                 AdamArgs a, const float* __restrict__ dyn) {
+  float gmul = 1.f;
+  if (dyn) {
+    if (dyn[1] != 0.f) return;
+    gmul = dyn[0];
+  }
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float g;
+    if (sizeof(GradT) == 2) g = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i]);
+    else g = reinterpret_cast<const float*>(grad)[i];
+    g *= gmul;
+    float mm = m[i], vv = v[i];
+    const float p = adam_update(master[i], g, mm, vv, a);
+    m[i] = mm; v[i] = vv; master[i] = p;
+    if (param_bf16) param_bf16[i] = __float2bfloat16(p);
+  }
+}
+
+// Pointer-table variant: chunk c covers elements [chunk_off[c], +chunk_len) of tensor chunk_tensor[c].
+// Tensor t has fp32 param p[t], grad g[t] (fp32 or bf16 by gdtype[t]), m[t], v[t], optional bf16 copy.
+struct TensorTable {
+  float* const* p;
+  const void* const* g;
+  float* const* m;
+  float* const* v;
+  __nv_bfloat16* const* p16;
+  const long long* numel;
+  const int* g_is_bf16;
+  const int* chunk_tensor;
+  const long long* chunk_off;
+};
+constexpr int kChunk = 65536;
+
+__global__ void adam_table_kernel(TensorTable tb, int n_chunks, AdamArgs a, const float* __restrict__ dyn) {
+  float gmul = 1.f;
+  if (dyn) {
+    if (dyn[1] != 0.f) return;
+    gmul = dyn[0];
+  }
+  for (int c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+    const int t = tb.chunk_tensor[c];
+    const long long off = tb.chunk_off[c];
+    const long long end = min(off + (long long)kChunk, tb.numel[t]);
+    float* p = tb.p[t];
+    float* m = tb.m[t];
+    float* v = tb.v[t];
+    __nv_bfloat16* p16 = tb.p16 ? tb.p16[t] : nullptr;
+    const bool gb = tb.g_is_bf16[t] != 0;
+    for (long long i = off + threadIdx.x; i < end; i += blockDim.x) {
+      float g = gb ? __bfloat162float(static_cast<const __nv_bfloat16*>(tb.g[t])[i]) : static_cast<const float*>(tb.g[t])[i];
+      g *= gmul;
+      float mm = m[i], vv = v[i];
+      const float np = adam_update(p[i], g, mm, vv, a);
+      m[i] = mm; v[i] = vv; p[i] = np;
+      if (p16) p16[i] = __float2bfloat16(np);
+    }
+  }
+}
+
+// SGD with momentum / RMSprop over a flat fp32 buffer.
+__global__ void sgd_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ vel, long long n,
+                                float lr, float momentum, float wd) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float gg = g[i] + wd * p[i];
+    if (vel) {
+      const float nv = momentum * vel[i] + gg;
+      vel[i] = nv;
+      gg = nv;
+    }
+    p[i] -= lr * gg;
+  }
+}
+__global__ void rmsprop_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ sq, long long n,
+                                    float lr, float alpha, float eps, float wd) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gg = g[i] + wd * p[i];
+    const float s = alpha * sq[i] + (1.f - alpha) * gg * gg;
+    sq[i] = s;
+    p[i] -= lr * gg / (sqrtf(s) + eps);
+  }
+}
+
+// out[0] += sum x^2, out[1] += number of non-finite elements.
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
+  float s = 0.f, bad = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float f;
+    if (sizeof(T) == 2) f = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    else f = reinterpret_cast<const float*>(x)[i];
+    if (!isfinite(f)) bad += 1.f; else s += f * f;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    bad += __shfl_xor_sync(0xffffffffu, bad, o);
+  }
+  __shared__ float rs[32], rb[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { rs[warp] = s; rb[warp] = bad; }
+  __syncthreads();
+  if (warp == 0) {
+    s = lane < (blockDim.x >> 5) ? rs[lane] : 0.f;
+    bad = lane < (blockDim.x >> 5) ? rb[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    }
+    if (lane == 0) {
+      atomicAdd(out, s);
+      if (bad != 0.f) atomicAdd(out + 1, bad);
+    }
+  }
+}
+
+// dyn[0] = clip coefficient * inv_scale, dyn[1] = overflow flag, from stats = {sumsq, nonfinite}.
+__global__ void clip_coef_kernel(const float* __restrict__ stats, float* __restrict__ dyn, float max_norm, float inv_scale) {
+  const float norm = sqrtf(stats[0]) * inv_scale;
+  float coef = 1.f;
+  if (max_norm > 0.f && norm > max_norm) coef = max_norm / (norm + 1e-6f);
+  dyn[0] = coef * inv_scale;
+  dyn[1] = stats[1] != 0.f ? 1.f : 0.f;
+  dyn[2] = norm;
+}
+
+inline int flat_grid(long long n) {
+  long long g = (n + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  return int(g > cap ? cap : (g < 1 ? 1 : g));
+}
+
+}  // namespace lt
+
+extern "C" {
+
+int lt_ce_stats(const void* logits, long long ldl, const long long* targets, int vocab_start, int N, int V, float* stats,
+                void* stream) {
+  using namespace lt;
+  if (N == 0) return 0;
+  if (ldl % 8 != 0) return -int(kStatusBadArgument);
+  const int grid = N < sm_count() * 8 ? N : sm_count() * 8;
+  ce_stats_kernel<<<grid, kCeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, stats);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+int lt_ce_finish(void* logits, long long ldl, const long long* targets, int vocab_start, int N, int V, const float* gstats,
+                 float* loss, float grad_scale, long long ignore_index, int write_grad, void* stream) {
+  using namespace lt;
+  if (N == 0) return 0;
+  if (ldl % 8 != 0) return -int(kStatusBadArgument);
+  const int grid = N < sm_count() * 8 ? N : sm_count() * 8;
+  ce_finish_kernel<<<grid, kCeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, gstats, loss, grad_scale, ignore_index, write_grad);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+int lt_adam_flat(float* master, const void* grad, int grad_is_bf16, float* m, float* v, void* param_bf16, long long n,
+                 float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, int adamw,
+                 const float* dyn, void* stream) {
+  using namespace lt;
+  if (n == 0) return 0;
+  AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, adamw};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (grad_is_bf16)
+    adam_flat_kernel<__nv_bfloat16><<<flat_grid(n), 256, 0, st>>>(master, static_cast<const __nv_bfloat16*>(grad), m, v,
+                                                                 static_cast<__nv_bfloat16*>(param_bf16), n, a, dyn);
+  else
+    adam_flat_kernel<float><<<flat_grid(n), 256, 0, st>>>(master, static_cast<const float*>(grad), m, v,
+                                                         static_cast<__nv_bfloat16*>(param_bf16), n, a, dyn);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// All table pointers are device arrays prepared by the caller (n_tensors / n_chunks entries).
+int lt_adam_table(const void* p_ptrs, const void* g_ptrs, const void* m_ptrs, const void* v_ptrs, const void* p16_ptrs,
+                  const long long* numel, const int* g_is_bf16, const int* chunk_tensor, const long long* chunk_off,
+                  int n_chunks, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, int adamw,
+                  const float* dyn, void* stream) {
+  using namespace lt;
+  if (n_chunks == 0) return 0;
+  TensorTable tb{static_cast<float* const*>(p_ptrs), static_cast<const void* const*>(g_ptrs),
+                 static_cast<float* const*>(m_ptrs), static_cast<float* const*>(v_ptrs),
+                 static_cast<__nv_bfloat16* const*>(p16_ptrs), numel, g_is_bf16, chunk_tensor, chunk_off};
+  AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, adamw};
+  const int cap = sm_count() * 8;
+  adam_table_kernel<<<n_chunks < cap ? n_chunks : cap, 256, 0, static_cast<cudaStream_t>(stream)>>>(tb, n_chunks, a, dyn);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+int lt_adam_chunk_elems() { return lt::kChunk; }
+
+int lt_sgd_flat(float* p, const float* g, float* vel, long long n, float lr, float momentum, float wd, void* stream) {
+  using namespace lt;
+  if (n == 0) return 0;
+  sgd_flat_kernel<<<flat_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, g, vel, n, lr, momentum, wd);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+int lt_rmsprop_flat(float* p, const float* g, float* sq, long long n, float lr, float alpha, float eps, float wd, void* stream) {
+  using namespace lt;
+  if (n == 0) return 0;
+  rmsprop_flat_kernel<<<flat_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, g, sq, n, lr, alpha, eps, wd);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+// out: 2 floats, accumulated into (zero them before the first call of a step).
+int lt_sumsq(const void* x, int is_bf16, long long n, float* out, void* stream) {
+  using namespace lt;
+  if (n == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16) sumsq_kernel<__nv_bfloat16><<<flat_grid(n), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out);
+  else sumsq_kernel<float><<<flat_grid(n), 256, 0, st>>>(static_cast<const float*>(x), n, out);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+// dyn: 3 floats {grad multiplier, overflow flag, grad norm}.
+int lt_clip_coef(const float* stats, float* dyn, float max_norm, float inv_scale, void* stream) {
+  lt::clip_coef_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(stats, dyn, max_norm, inv_scale);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,312 @@
+"""ctypes front-end of the sm_100a kernels in liblt_cuda.so.
+
+Every function takes torch CUDA tensors, launches on the current torch stream and returns torch
+tensors.  No autograd here: `litetorch_b200.ops.functional` wraps these into autograd Functions and
+`litetorch_b200.models` calls them directly from hand-written layer backward passes.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_longlong, c_float
+
+import torch
+
+from .._native import cuda_lib
+
+_vp, _i, _ll, _f = c_void_p, c_int, c_longlong, c_float
+
+_SIGS = {
+    "lt_status_fetch": [],
+    "lt_sm_count": [],
+    "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
+    "lt_norm_bwd_ctas": [_i],
+    "lt_norm_fwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "lt_norm_bwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lt_rope": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _i, _vp],
+    "lt_swiglu_fwd": [_vp, _vp, _ll, _i, _vp],
+    "lt_swiglu_bwd": [_vp, _vp, _vp, _ll, _i, _vp],
+    "lt_gelu_fwd": [_vp, _vp, _ll, _vp],
+    "lt_gelu_bwd": [_vp, _vp, _vp, _ll, _vp],
+    "lt_axpby": [_vp, _vp, _vp, _f, _f, _ll, _vp],
+    "lt_embedding_fwd": [_vp, _vp, _vp, _ll, _i, _i, _vp],
+    "lt_embedding_bwd": [_vp, _vp, _vp, _ll, _i, _i, _vp],
+    "lt_cast_f32_to_bf16": [_vp, _vp, _ll, _vp],
+    "lt_cast_bf16_to_f32": [_vp, _vp, _ll, _vp],
+    "lt_ce_stats": [_vp, _ll, _vp, _i, _i, _i, _vp, _vp],
+    "lt_ce_finish": [_vp, _ll, _vp, _i, _i, _i, _vp, _vp, _f, _ll, _i, _vp],
+    "lt_adam_flat": [_vp, _vp, _i, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _i, _vp, _vp],
+    "lt_adam_table": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _i, _vp, _vp],
+    "lt_adam_chunk_elems": [],
+    "lt_sgd_flat": [_vp, _vp, _vp, _ll, _f, _f, _f, _vp],
+    "lt_rmsprop_flat": [_vp, _vp, _vp, _ll, _f, _f, _f, _f, _vp],
+    "lt_sumsq": [_vp, _i, _ll, _vp, _vp],
+    "lt_clip_coef": [_vp, _vp, _f, _f, _vp],
+    "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
+    "lt_flash_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                     _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
+}
+
+_bound = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(name):
+    f = _bound.get(name)
+    if f is None:
+        lib = cuda_lib()
+        f = getattr(lib, name)
+        f.argtypes = _SIGS[name]
+        f.restype = c_int
+        _bound[name] = f
+    return f
+
+
+def has_kernel(name: str) -> bool:
+    try:
+        return hasattr(cuda_lib(), name)
+    except Exception:
+        return False
+
+
+def _check(rc, name):
+    if rc != 0:
+        raise KernelError("%s failed with code %d" % (name, rc))
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def status_fetch() -> int:
+    """Read-and-clear the device status word (synchronises). 0 = no bounded wait ran out."""
+    return _fn("lt_status_fetch")()
+
+
+def check_status():
+    s = status_fetch()
+    if s != 0:
+        raise KernelError("device status word = %d (a bounded wait ran out or an argument was rejected)" % s)
+
+
+def sm_count() -> int:
+    return _fn("lt_sm_count")()
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0, out: torch.Tensor | None = None,
+         out_dtype=torch.bfloat16, bias=None, residual=None, act: int = 0, accumulate: bool = False,
+         alpha: float = 1.0, block_n: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """C = epilogue(alpha * op(A) @ op(B)).
+
+    a_major=0: ``a`` is [M, K];  a_major=1: ``a`` is [K, M] (used transposed).
+    b_major=0: ``b`` is [N, K];  b_major=1: ``b`` is [K, N].
+    Rows may be strided (last dim contiguous).
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if a_major == 0:
+        M, K = a.shape
+    else:
+        K, M = a.shape
+    if b_major == 0:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    assert K == Kb, "inner dimensions differ: %d vs %d" % (K, Kb)
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+    rc = _fn("lt_gemm_bf16")(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                             a_major, b_major, 1 if out.dtype == torch.float32 else 0, _p(bias), _p(residual),
+                             residual.stride(0) if residual is not None else 0, act, 1 if accumulate else 0,
+                             float(alpha), block_n, max_ctas, _stream())
+    _check(rc, "lt_gemm_bf16")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ norms
+def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5, want_sum=True):
+    """Returns (y, sum_or_None, mean_or_None, rstd).  x, residual: [M, D] bf16."""
+    M, D = x.shape
+    y = torch.empty_like(x)
+    s = torch.empty_like(x) if (residual is not None and want_sum) else None
+    mean = torch.empty(M, dtype=torch.float32, device=x.device) if layer_norm else None
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    rc = _fn("lt_norm_fwd")(1 if layer_norm else 0, x.data_ptr(), _p(residual), weight.data_ptr(), _p(bias), y.data_ptr(),
+                            _p(s), _p(mean), rstd.data_ptr(), M, D, float(eps), _stream())
+    _check(rc, "lt_norm_fwd")
+    return y, s, mean, rstd
+
+
+def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None, db=None, accumulate=False):
+    """Returns (dx, dw, db).  `x` is the tensor that was normalised (the residual sum when one was fused)."""
+    M, D = x.shape
+    dx = torch.empty_like(x)
+    ctas = _fn("lt_norm_bwd_ctas")(M)
+    part = torch.empty((2 if layer_norm else 1, ctas, D), dtype=torch.float32, device=x.device)
+    if dw is None:
+        dw = torch.empty(D, dtype=weight.dtype, device=x.device)
+        accumulate = False
+    if layer_norm and db is None:
+        db = torch.empty(D, dtype=weight.dtype, device=x.device)
+    rc = _fn("lt_norm_bwd")(1 if layer_norm else 0, dy.data_ptr(), x.data_ptr(), weight.data_ptr(), _p(mean), rstd.data_ptr(),
+                            _p(dres), dx.data_ptr(), part[0].data_ptr(), part[1].data_ptr() if layer_norm else None,
+                            dw.data_ptr(), _p(db) if layer_norm else None, 1 if dw.dtype == torch.float32 else 0,
+                            1 if accumulate else 0, M, D, _stream())
+    _check(rc, "lt_norm_bwd")
+    return dx, dw, db
+
+
+# ------------------------------------------------------------------------------------------------ pointwise
+def rope_(x2d: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, T: int, heads: int, head_dim: int, *,
+          col_offset: int = 0, positions: torch.Tensor | None = None, backward: bool = False):
+    """In-place interleaved-pair rotation of `heads` heads starting at column `col_offset` of a [rows, pitch] buffer."""
+    rows = x2d.shape[0]
+    base = x2d.data_ptr() + col_offset * x2d.element_size()
+    rc = _fn("lt_rope")(base, cos.data_ptr(), sin.data_ptr(), _p(positions), rows, T, heads, head_dim, x2d.stride(0),
+                        1 if backward else 0, _stream())
+    _check(rc, "lt_rope")
+    return x2d
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    M, F2 = gu.shape
+    h = torch.empty((M, F2 // 2), dtype=gu.dtype, device=gu.device)
+    _check(_fn("lt_swiglu_fwd")(gu.data_ptr(), h.data_ptr(), M, F2 // 2, _stream()), "lt_swiglu_fwd")
+    return h
+
+
+def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor, inplace: bool = True) -> torch.Tensor:
+    M, F2 = gu.shape
+    dgu = gu if inplace else torch.empty_like(gu)
+    _check(_fn("lt_swiglu_bwd")(gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), M, F2 // 2, _stream()), "lt_swiglu_bwd")
+    return dgu
+
+
+def gelu_fwd(x):
+    y = torch.empty_like(x)
+    _check(_fn("lt_gelu_fwd")(x.data_ptr(), y.data_ptr(), x.numel(), _stream()), "lt_gelu_fwd")
+    return y
+
+
+def gelu_bwd(x, dy):
+    dx = torch.empty_like(x)
+    _check(_fn("lt_gelu_bwd")(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(), _stream()), "lt_gelu_bwd")
+    return dx
+
+
+def axpby(a, b=None, alpha=1.0, beta=1.0, out=None):
+    out = torch.empty_like(a) if out is None else out
+    _check(_fn("lt_axpby")(a.data_ptr(), _p(b), out.data_ptr(), float(alpha), float(beta), a.numel(), _stream()), "lt_axpby")
+    return out
+
+
+def embedding_fwd(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    idx = idx.reshape(-1).to(torch.int64)
+    V, D = table.shape
+    out = torch.empty((idx.numel(), D), dtype=table.dtype, device=table.device)
+    _check(_fn("lt_embedding_fwd")(idx.data_ptr(), table.data_ptr(), out.data_ptr(), idx.numel(), D, V, _stream()), "lt_embedding_fwd")
+    return out
+
+
+def embedding_bwd(idx: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor):
+    idx = idx.reshape(-1).to(torch.int64)
+    V, D = dtable.shape
+    _check(_fn("lt_embedding_bwd")(idx.data_ptr(), dout.data_ptr(), dtable.data_ptr(), idx.numel(), D, V, _stream()), "lt_embedding_bwd")
+    return dtable
+
+
+def cast_to_bf16(x: torch.Tensor, out=None):
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _check(_fn("lt_cast_f32_to_bf16")(x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "lt_cast_f32_to_bf16")
+    return out
+
+
+def cast_to_f32(x: torch.Tensor, out=None):
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device) if out is None else out
+    _check(_fn("lt_cast_bf16_to_f32")(x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "lt_cast_bf16_to_f32")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ loss
+def ce_stats(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    N, V = logits.shape
+    stats = torch.empty((N, 3), dtype=torch.float32, device=logits.device)
+    _check(_fn("lt_ce_stats")(logits.data_ptr(), logits.stride(0), targets.data_ptr(), vocab_start, N, V, stats.data_ptr(), _stream()), "lt_ce_stats")
+    return stats
+
+
+def ce_finish(logits, targets, gstats, *, vocab_start=0, grad_scale=1.0, ignore_index=-100, write_grad=True):
+    """Per-row losses; overwrites `logits` with d(loss)/d(logits) * grad_scale when write_grad."""
+    N, V = logits.shape
+    loss = torch.empty(N, dtype=torch.float32, device=logits.device)
+    _check(_fn("lt_ce_finish")(logits.data_ptr(), logits.stride(0), targets.data_ptr(), vocab_start, N, V, gstats.data_ptr(),
+                               loss.data_ptr(), float(grad_scale), ignore_index, 1 if write_grad else 0, _stream()), "lt_ce_finish")
+    return loss
+
+
+# ------------------------------------------------------------------------------------------------ optimizers
+def adam_flat(master, grad, m, v, param_bf16, *, lr, beta1, beta2, eps, wd, step, adamw=True, dyn=None):
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    _check(_fn("lt_adam_flat")(master.data_ptr(), grad.data_ptr(), 1 if grad.dtype == torch.bfloat16 else 0, m.data_ptr(),
+                               v.data_ptr(), _p(param_bf16), master.numel(), lr, beta1, beta2, eps, wd, bc1, bc2,
+                               1 if adamw else 0, _p(dyn), _stream()), "lt_adam_flat")
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor):
+    _check(_fn("lt_sumsq")(x.data_ptr(), 1 if x.dtype == torch.bfloat16 else 0, x.numel(), out.data_ptr(), _stream()), "lt_sumsq")
+    return out
+
+
+def clip_coef(stats: torch.Tensor, dyn: torch.Tensor, max_norm: float, inv_scale: float = 1.0):
+    _check(_fn("lt_clip_coef")(stats.data_ptr(), dyn.data_ptr(), float(max_norm), float(inv_scale), _stream()), "lt_clip_coef")
+    return dyn
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def flash_fwd(q, k, v, *, causal=True, scale=None):
+    """q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D] (last dim contiguous, arbitrary other strides).  Returns (o, lse)."""
+    B, Tq, Hq, D = q.shape
+    _, Tk, Hkv, _ = k.shape
+    scale = (D ** -0.5) if scale is None else scale
+    o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, Tq), dtype=torch.float32, device=q.device)
+    rc = _fn("lt_flash_fwd")(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, Hq, Hkv, D,
+                             q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+                             o.stride(0), o.stride(1), float(scale), 1 if causal else 0, _stream())
+    _check(rc, "lt_flash_fwd")
+    return o, lse
+
+
+def flash_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, dq=None, dk=None, dv=None):
+    """Returns (dq, dk, dv) with the shapes/strides of the given outputs (allocated contiguous when None)."""
+    B, Tq, Hq, D = q.shape
+    _, Tk, Hkv, _ = k.shape
+    scale = (D ** -0.5) if scale is None else scale
+    dq = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device) if dk is None else dk
+    dv = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device) if dv is None else dv
+    delta = torch.empty((B, Hq, Tq), dtype=torch.float32, device=q.device)
+    dq_acc = torch.zeros((B, Tq, Hq, D), dtype=torch.float32, device=q.device)
+    rc = _fn("lt_flash_bwd")(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), do.data_ptr(),
+                             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
+                             B, Tq, Tk, Hq, Hkv, D,
+                             q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+                             o.stride(0), o.stride(1), do.stride(0), do.stride(1),
+                             dq.stride(0), dq.stride(1), dk.stride(0), dk.stride(1),
+                             float(scale), 1 if causal else 0, _stream())
+    _check(rc, "lt_flash_bwd")
+    return dq, dk, dv
