@@ -1,0 +1,452 @@
+// FlashAttention backward for sm_100a: causal or full, grouped-query heads, bf16, head_dim 64 or 128.
+//
+// The reference backward recomputes S and P with cuBLAS into B*H*Tq*Tk fp32 scratch and runs five batched
+// GEMMs plus two kernels (src/backend/gpu_native/nn/flash_attention.cu:395-713); GQA is only handled on the
+// CPU by expanding K/V per head (src/ops/attention.cpp:88-175).  Here one CTA owns a block of 128 keys of one
+// KV head and keeps dK and dV for it in tensor memory while it walks over every query head of the group and
+// every query block that can see those keys:
+//
+//   S  = Q_i K^T        dP = dO_i V^T                 (tcgen05.mma into TMEM, 128 x 128 x D)
+//   P  = exp2(S*c - lse),  dS = P * (dP - delta) * scale   (one query row per thread, written to shared
+//                                                           memory in the swizzled operand layout)
+//   dV += P^T dO_i      dK += dS^T Q_i                (A read M-major from the same P / dS tiles)
+//   dQ_i = dS K         -> red.global.add into an fp32 accumulator, converted to bf16 by a last kernel
+//
+// delta = rowsum(O * dO) comes from a small pre-pass.  All waits are bounded (see common/ptx.cuh).
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace lt {
+
+constexpr int kFbBlock = 128;
+constexpr int kFbThreads = 192;
+
+struct FlashBwdParams {
+  const float* lse;    // [B, Hq, Tq] natural log
+  const float* delta;  // [B, Hq, Tq]
+  float* dq_acc;       // [B, Tq, Hq, D] fp32, zero-initialised
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;   // [B, Tk, Hkv, D] with strides sdk_b / sdk_t
+  long long sdk_b, sdk_t;
+  int B, Tq, Tk, Hq, Hkv;
+  float scale, scale_log2;
+  int causal;
+  int* status;
+};
+
+template <int D>
+struct FaBwdCfg {
+  static constexpr int kTile = kFbBlock * D * 2;          // one 128 x D bf16 tile
+  static constexpr int kPTile = kFbBlock * kFbBlock * 2;  // 128 x 128 bf16
+  static constexpr int kStages = (D == 64) ? 2 : 1;       // Q / dO buffering
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTile;
+  static constexpr int kOffQ = 2 * kTile;
+  static constexpr int kOffDO = kOffQ + kStages * kTile;
+  static constexpr int kOffP = kOffDO + kStages * kTile;
+  static constexpr int kOffDS = kOffP + kPTile;
+  static constexpr int kOffBar = kOffDS + kPTile;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
+  static constexpr int kColDQ = (D == 64) ? 384 : 0;  // aliases S when D == 128
+  static constexpr bool kDqAliasesS = (D != 64);
+};
+
+// delta[b,h,t] = sum_d O * dO ; one warp per (b,t,h) row.
+__global__ void flash_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                       float* __restrict__ delta, int B, int Tq, int Hq, int D, long long so_b,
+                                       long long so_t, long long sdo_b, long long sdo_t) {
+  const long long warp_id = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * Tq * Hq;
+  if (warp_id >= total) return;
+  const int h = int(warp_id % Hq);
+  const int t = int((warp_id / Hq) % Tq);
+  const int b = int(warp_id / ((long long)Hq * Tq));
+  const __nv_bfloat16* o = O + b * so_b + t * so_t + (long long)h * D;
+  const __nv_bfloat16* d = dO + b * sdo_b + t * sdo_t + (long long)h * D;
+  float s = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + c));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + c));
+    s += a.x * g.x + a.y * g.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[((long long)b * Hq + h) * Tq + t] = s;
+}
+
+__global__ void flash_bwd_convert_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int B, int Tq,
+                                            int HD, long long sdq_b, long long sdq_t) {
+  const long long n4 = (long long)B * Tq * HD / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 4;
+    const int c = int(e % HD);
+    const long long bt = e / HD;
+    const int t = int(bt % Tq);
+    const int b = int(bt / Tq);
+    const float4 v = *reinterpret_cast<const float4*>(acc + e);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dq + b * sdq_b + t * sdq_t + c) = o;
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFbThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const FlashBwdParams p) {
+  using Cfg = FaBwdCfg<D>;
+  constexpr int ST = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  const uint32_t bb = smem_u32(bars);
+  const uint32_t kv_full = bb;
+  auto qdo_full = [&](int s) { return bb + 8u * (1 + s); };
+  auto qdo_empty = [&](int s) { return bb + 8u * (3 + s); };
+  const uint32_t sdp_full = bb + 8u * 5;   // S and dP are in TMEM
+  const uint32_t sdp_free = bb + 8u * 6;   // compute threads have read S and dP (count 128)
+  const uint32_t pds_full = bb + 8u * 7;   // P and dS are in shared memory (count 128)
+  const uint32_t pds_empty = bb + 8u * 8;  // the three MMAs that read P / dS have executed
+  const uint32_t dq_full = bb + 8u * 9;    // dQ_i is in TMEM
+  const uint32_t dq_free = bb + 8u * 10;   // compute threads have read dQ_i (count 128)
+  const uint32_t dkv_full = bb + 8u * 11;  // all MMAs done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int kv0 = kv_blk * kFbBlock;
+  const int shift = p.Tk - p.Tq;
+  const int n_q_blocks = (p.Tq + kFbBlock - 1) / kFbBlock;
+  int i_min = 0;
+  if (p.causal) {
+    const int first_q = kv0 - shift;  // first query that sees key kv0
+    i_min = first_q <= 0 ? 0 : first_q / kFbBlock;
+  }
+  const int per_head = n_q_blocks > i_min ? n_q_blocks - i_min : 0;
+  const int n_iter = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
+    mbar_init(sdp_full, 1); mbar_init(sdp_free, 128);
+    mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, 128);
+    mbar_init(dkv_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * Cfg::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(sbase + Cfg::kOffK + c * (kFbBlock * 128), &tmK, kv_full, c * 64, hkv, kv0, b);
+        tma_load_4d(sbase + Cfg::kOffV + c * (kFbBlock * 128), &tmV, kv_full, c * 64, hkv, kv0, b);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % ST;
+        const uint32_t par = (it / ST) & 1;
+        const int h = hkv * G + it / per_head;
+        const int q0 = (i_min + it % per_head) * kFbBlock;
+        if (!mbar_wait(qdo_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(qdo_full(s), 2 * Cfg::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_4d(sbase + Cfg::kOffQ + s * Cfg::kTile + c * (kFbBlock * 128), &tmQ, qdo_full(s), c * 64, h, q0, b);
+          tma_load_4d(sbase + Cfg::kOffDO + s * Cfg::kTile + c * (kFbBlock * 128), &tmDO, qdo_full(s), c * 64, h, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_sd = make_idesc_f16(128, 128, 1, 0, 0);  // S, dP: A K-major, B K-major
+      constexpr uint32_t idesc_kv = make_idesc_f16(128, D, 1, 1, 1);    // dV, dK: A M-major, B N-major
+      constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 1, 0, 1);    // dQ: A K-major, B N-major
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      const uint32_t ka = sbase + Cfg::kOffK, va = sbase + Cfg::kOffV;
+      const uint32_t pa = sbase + Cfg::kOffP, dsa = sbase + Cfg::kOffDS;
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const int s = it % ST;
+        const uint32_t par = (it / ST) & 1;
+        const uint32_t ipar = it & 1;
+        const uint32_t qa = sbase + Cfg::kOffQ + s * Cfg::kTile;
+        const uint32_t doa = sbase + Cfg::kOffDO + s * Cfg::kTile;
+        if (!mbar_wait(qdo_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (!mbar_wait(sdp_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        if (Cfg::kDqAliasesS) {
+          if (!mbar_wait(dq_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (128 * 128) + (k % 4) * 32;
+          umma_f16_ss(tmem_base + Cfg::kColS, make_smem_desc_sw128(qa + off, 16, 1024),
+                      make_smem_desc_sw128(ka + off, 16, 1024), idesc_sd, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (128 * 128) + (k % 4) * 32;
+          umma_f16_ss(tmem_base + Cfg::kColDP, make_smem_desc_sw128(doa + off, 16, 1024),
+                      make_smem_desc_sw128(va + off, 16, 1024), idesc_sd, k > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+        if (!Cfg::kDqAliasesS) {
+          if (!mbar_wait(dq_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        }
+        tc_fence_after();
+        // dV += P^T dO ; dK += dS^T Q      (K dimension = the 128 query rows, 16 rows per instruction)
+#pragma unroll
+        for (int k = 0; k < kFbBlock / 16; ++k) {
+          const uint32_t koff = k * (16 * 128);
+          umma_f16_ss(tmem_base + Cfg::kColDV, make_smem_desc_sw128(pa + koff, 128 * 128, 1024),
+                      make_smem_desc_sw128(doa + koff, 128 * 128, 1024), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < kFbBlock / 16; ++k) {
+          const uint32_t koff = k * (16 * 128);
+          umma_f16_ss(tmem_base + Cfg::kColDK, make_smem_desc_sw128(dsa + koff, 128 * 128, 1024),
+                      make_smem_desc_sw128(qa + koff, 128 * 128, 1024), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        // dQ_i = dS K                      (K dimension = the 128 keys)
+#pragma unroll
+        for (int k = 0; k < kFbBlock / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(dsa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(ka + k * (16 * 128), 128 * 128, 1024);
+          umma_f16_ss(tmem_base + Cfg::kColDQ, adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(qdo_empty(s));
+        umma_commit(pds_empty);
+        umma_commit(dq_full);
+        if (it == n_iter - 1) umma_commit(dkv_full);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const uint32_t ipar = it & 1;
+      const int h = hkv * G + it / per_head;
+      const int q0 = (i_min + it % per_head) * kFbBlock;
+      const int q_idx = q0 + row;
+      const bool q_valid = q_idx < p.Tq;
+      float lse2 = 0.f, dlt = 0.f;
+      if (q_valid) {
+        const long long si = ((long long)b * p.Hq + h) * p.Tq + q_idx;
+        lse2 = p.lse[si] * 1.4426950408889634f;
+        dlt = p.delta[si];
+      }
+      const int limit = p.causal ? min(q_idx + shift, p.Tk - 1) : (p.Tk - 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
+      if (!ok) break;
+      // P / dS tiles are free once the MMAs of the previous iteration have executed.
+      ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
+      if (!ok) break;
+      tc_fence_after();
+      uint8_t* prow = smem + Cfg::kOffP + (row >> 3) * 1024 + (row & 7) * 128;
+      uint8_t* dsrow = smem + Cfg::kOffDS + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dp[32];
+        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + c * 32, sv);
+        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDP + c * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv_idx = kv0 + c * 32 + i;
+          float pv = 0.f;
+          if (q_valid && kv_idx <= limit && lse2 != -INFINITY) pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+          const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
+          sv[i] = __float_as_uint(pv);
+          dp[i] = __float_as_uint(ds);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 w, z;
+          w.x = pack_bf16x2(__uint_as_float(sv[u * 8 + 0]), __uint_as_float(sv[u * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(sv[u * 8 + 2]), __uint_as_float(sv[u * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(sv[u * 8 + 4]), __uint_as_float(sv[u * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(sv[u * 8 + 6]), __uint_as_float(sv[u * 8 + 7]));
+          z.x = pack_bf16x2(__uint_as_float(dp[u * 8 + 0]), __uint_as_float(dp[u * 8 + 1]));
+          z.y = pack_bf16x2(__uint_as_float(dp[u * 8 + 2]), __uint_as_float(dp[u * 8 + 3]));
+          z.z = pack_bf16x2(__uint_as_float(dp[u * 8 + 4]), __uint_as_float(dp[u * 8 + 5]));
+          z.w = pack_bf16x2(__uint_as_float(dp[u * 8 + 6]), __uint_as_float(dp[u * 8 + 7]));
+          const int col16 = c * 4 + u;
+          const int chunk = col16 >> 3;
+          const int unit = (col16 & 7) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * (128 * 128) + unit * 16) = w;
+          *reinterpret_cast<uint4*>(dsrow + chunk * (128 * 128) + unit * 16) = z;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+      fence_proxy_async();
+      mbar_arrive(pds_full);
+      // dQ_i
+      ok = __all_sync(0xffffffffu, mbar_wait(dq_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
+      if (!ok) break;
+      tc_fence_after();
+      float* dq_row = p.dq_acc + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t dq[32];
+        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + c * 32, dq);
+        tmem_ld_wait();
+        if (q_valid) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            red_add_v4(dq_row + c * 32 + u * 4, __uint_as_float(dq[u * 4]), __uint_as_float(dq[u * 4 + 1]),
+                       __uint_as_float(dq[u * 4 + 2]), __uint_as_float(dq[u * 4 + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_free);
+    }
+    // ---------------------------------------------------------------- dK / dV epilogue (row = key index)
+    if (ok && n_iter > 0) ok = __all_sync(0xffffffffu, mbar_wait(dkv_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
+    if (ok) {
+      if (n_iter > 0) tc_fence_after();
+      const int kv_idx = kv0 + row;
+      __nv_bfloat16* dk_row = p.dK + b * p.sdk_b + (long long)kv_idx * p.sdk_t + (long long)hkv * D;
+      __nv_bfloat16* dv_row = p.dV + b * p.sdk_b + (long long)kv_idx * p.sdk_t + (long long)hkv * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t a[32], g[32];
+        if (n_iter > 0) {
+          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDK + c * 32, a);
+          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDV + c * 32, g);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a[i] = 0u; g[i] = 0u; }
+        }
+        if (kv_idx < p.Tk) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w, z;
+            w.x = pack_bf16x2(__uint_as_float(a[u * 8 + 0]), __uint_as_float(a[u * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(a[u * 8 + 2]), __uint_as_float(a[u * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(a[u * 8 + 4]), __uint_as_float(a[u * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(a[u * 8 + 6]), __uint_as_float(a[u * 8 + 7]));
+            z.x = pack_bf16x2(__uint_as_float(g[u * 8 + 0]), __uint_as_float(g[u * 8 + 1]));
+            z.y = pack_bf16x2(__uint_as_float(g[u * 8 + 2]), __uint_as_float(g[u * 8 + 3]));
+            z.z = pack_bf16x2(__uint_as_float(g[u * 8 + 4]), __uint_as_float(g[u * 8 + 5]));
+            z.w = pack_bf16x2(__uint_as_float(g[u * 8 + 6]), __uint_as_float(g[u * 8 + 7]));
+            *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = w;
+            *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = z;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int spin = 0; spin < 2000; ++spin) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+static int launch_flash_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                            const FlashBwdParams& p, cudaStream_t st) {
+  using Cfg = FaBwdCfg<D>;
+  static bool configured = false;
+  auto kern = flash_bwd_kernel<D>;
+  if (!configured) {
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  dim3 grid((p.Tk + kFbBlock - 1) / kFbBlock, p.Hkv, p.B);
+  kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, tdo, p);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace lt
+
+extern "C" {
+
+// Shapes as lt_flash_fwd.  delta: scratch [B, Hq, Tq] fp32.  dq_acc: scratch [B, Tq, Hq, D] fp32, must be zero.
+// dk and dv share the strides sdk_b / sdk_t.
+int lt_flash_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o, void* dq,
+                 void* dk, void* dv, float* delta, float* dq_acc, int B, int Tq, int Tk, int Hq, int Hkv, int D,
+                 long long sq_b, long long sq_t, long long sk_b, long long sk_t, long long sv_b, long long sv_t,
+                 long long so_b, long long so_t, long long sdo_b, long long sdo_t, long long sdq_b, long long sdq_t,
+                 long long sdk_b, long long sdk_t, float scale, int causal, void* stream) {
+  using namespace lt;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -int(kStatusBadArgument);
+  if (B == 0 || Tq == 0 || Tk == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {
+    const long long rows = (long long)B * Tq * Hq;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    flash_bwd_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(o),
+                                                                 static_cast<const __nv_bfloat16*>(d_o), delta, B, Tq, Hq, D,
+                                                                 so_b, so_t, sdo_b, sdo_t);
+    LT_LAUNCH_CHECK();
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  r = encode_tmap_4d(&tq, q, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 1000 + r;
+  r = encode_tmap_4d(&tk, k, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 2000 + r;
+  r = encode_tmap_4d(&tv, v, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 3000 + r;
+  r = encode_tmap_4d(&tdo, d_o, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sdo_t * 2, (uint64_t)sdo_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 4000 + r;
+  FlashBwdParams p{};
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dK = static_cast<__nv_bfloat16*>(dk);
+  p.dV = static_cast<__nv_bfloat16*>(dv);
+  p.sdk_b = sdk_b; p.sdk_t = sdk_t;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = device_status_word();
+  int rc = (D == 64) ? launch_flash_bwd<64>(tq, tk, tv, tdo, p, st) : launch_flash_bwd<128>(tq, tk, tv, tdo, p, st);
+  if (rc) return rc;
+  const long long n4 = (long long)B * Tq * Hq * D / 4;
+  long long blocks = (n4 + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  flash_bwd_convert_dq_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), B, Tq, Hq * D, sdq_b, sdq_t);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,368 @@
+// FlashAttention forward for sm_100a: causal or full, grouped-query heads, bf16, head_dim 64 or 128.
+//
+// The reference's CUDA attention materialises S = Q K^T for all heads in fp32 (four B*H*Tq*Tk scratch
+// buffers), runs a row-softmax kernel and a second batched GEMM, has no causal mask and ignores the number
+// of KV heads (src/backend/gpu_native/nn/flash_attention.cu:188-299).  This kernel never leaves the chip:
+//
+//   warp 0    TMA producer: Q tile once, K/V tiles double-buffered (128-byte swizzle, mbarrier tx)
+//   warp 1    MMA issuer:   S_j = Q K_j^T  (tcgen05.mma, 128x128xD, S double-buffered in TMEM)
+//                           O  += P_j V_j  (A = P_j from shared memory, B = V_j as an N-major operand)
+//   warps 2-5 softmax:      one query row per thread (TMEM lane = row): tcgen05.ld S, online max / sum in
+//                           the exp2 domain, P_j written to shared memory in the swizzled operand layout.
+// The running maximum is updated lazily: O in TMEM is rescaled only when a row's maximum grew by more
+// than 2^8, which keeps exp2 arguments bounded and makes the rescale (tcgen05.ld/st of O) rare.
+// Output: O [B, Tq, Hq, D] bf16 and the natural-log LSE [B, Hq, Tq] fp32 for the backward pass.
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace lt {
+
+constexpr int kFaBlockQ = 128;
+constexpr int kFaBlockKV = 128;
+constexpr int kFaThreads = 192;
+
+struct FlashFwdParams {
+  __nv_bfloat16* O;
+  float* lse;
+  int B, Tq, Tk, Hq, Hkv;
+  long long so_b, so_t;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  int* status;
+};
+
+template <int D>
+struct FaFwdCfg {
+  static constexpr int kQBytes = kFaBlockQ * D * 2;
+  static constexpr int kKVBytes = kFaBlockKV * D * 2;
+  static constexpr int kPBytes = kFaBlockQ * kFaBlockKV * 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kQBytes;
+  static constexpr int kOffV = kOffK + 2 * kKVBytes;
+  static constexpr int kOffP = kOffV + 2 * kKVBytes;
+  static constexpr int kOffBar = kOffP + 2 * kPBytes;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS = 0;     // two S buffers of 128 columns
+  static constexpr int kColO = 256;   // D columns
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
+  using Cfg = FaFwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  const uint32_t bb = smem_u32(bars);
+  // barrier map
+  const uint32_t q_full = bb;
+  auto k_full = [&](int s) { return bb + 8u * (1 + s); };
+  auto v_full = [&](int s) { return bb + 8u * (3 + s); };
+  auto k_empty = [&](int s) { return bb + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bb + 8u * (7 + s); };
+  auto s_full = [&](int s) { return bb + 8u * (9 + s); };
+  auto p_full = [&](int s) { return bb + 8u * (11 + s); };
+  auto p_empty = [&](int s) { return bb + 8u * (13 + s); };
+  const uint32_t o_full = bb + 8u * 15;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_blk = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q0 = q_blk * kFaBlockQ;
+  const int shift = p.Tk - p.Tq;  // key index visible to query i is <= i + shift
+  int n_blocks;
+  if (p.causal) {
+    int last = q0 + kFaBlockQ - 1 + shift;
+    if (last > p.Tk - 1) last = p.Tk - 1;
+    n_blocks = last < 0 ? 0 : last / kFaBlockKV + 1;
+  } else {
+    n_blocks = (p.Tk + kFaBlockKV - 1) / kFaBlockKV;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
+      mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1); mbar_init(p_full(s), 128); mbar_init(p_empty(s), 1);
+    }
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0 && n_blocks > 0) {
+      mbar_expect_tx(q_full, Cfg::kQBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_4d(sbase + Cfg::kOffQ + c * (kFaBlockQ * 128), &tmQ, q_full, c * 64, h, q0, b);
+      for (int j = 0; j < n_blocks; ++j) {
+        const int s = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        if (!mbar_wait(k_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(k_full(s), Cfg::kKVBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(sbase + Cfg::kOffK + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &tmK, k_full(s), c * 64, hkv,
+                      j * kFaBlockKV, b);
+        if (!mbar_wait(v_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(v_full(s), Cfg::kKVBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(sbase + Cfg::kOffV + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &tmV, v_full(s), c * 64, hkv,
+                      j * kFaBlockKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kFaBlockQ, kFaBlockKV, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_f16(kFaBlockQ, D, 1, 0, 1);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t qa = sbase + Cfg::kOffQ;
+        const uint32_t ka = sbase + Cfg::kOffK + s * Cfg::kKVBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (128 * 128) + (k % 4) * 32;
+          umma_f16_ss(tmem_base + Cfg::kColS + s * 128, make_smem_desc_sw128(qa + off, 16, 1024),
+                      make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(k_empty(s));
+        umma_commit(s_full(s));
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      ok = ok && mbar_wait(k_full(0), 0, abort_flag, p.status, kStatusTimeoutFull);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        const int s = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        if (j + 1 < n_blocks) {
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait(k_full(s1), ((j + 1) >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(p_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+        if (!mbar_wait(v_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t pa = sbase + Cfg::kOffP + s * Cfg::kPBytes;
+        const uint32_t va = sbase + Cfg::kOffV + s * Cfg::kKVBytes;
+#pragma unroll
+        for (int k = 0; k < kFaBlockKV / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(pa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(va + k * (16 * 128), kFaBlockKV * 128, 1024);
+          umma_f16_ss(tmem_base + Cfg::kColO, adesc, bdesc, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(v_empty(s));
+        umma_commit(p_empty(s));
+        if (j == n_blocks - 1) umma_commit(o_full);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q_idx = q0 + row;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks; ++j) {
+      const int s = j & 1;
+      const uint32_t par = (j >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + s * 128 + c * 32, r[c]);
+      tmem_ld_wait();
+      const int kv0 = j * kFaBlockKV;
+      const int limit = p.causal ? min(q_idx + shift, p.Tk - 1) : (p.Tk - 1);  // last visible key
+      const bool need_mask = (kv0 + kFaBlockKV - 1 > limit);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[c][i]);
+          if (need_mask && (kv0 + c * 32 + i > limit)) v = -INFINITY;
+          r[c][i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      const float m_blk = mx * p.scale_log2;
+      float m_new = fmaxf(m_used, m_blk);
+      if (j == 0) {
+        m_used = (m_new == -INFINITY) ? 0.f : m_new;
+      } else {
+        const bool need = (m_new - m_used > 8.f);
+        if (__any_sync(0xffffffffu, need)) {
+          // O must be complete up to block j-1 before it is rescaled.
+          ok = __all_sync(0xffffffffu, mbar_wait(p_empty((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, p.status,
+                                                 kStatusTimeoutTmemEmpty));
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = need ? exp2f(m_used - m_new) : 1.f;
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(tmem_base + lane_base + Cfg::kColO + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(tmem_base + lane_base + Cfg::kColO + c * 16, o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          if (need) m_used = m_new;
+        }
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float pv = exp2f(__uint_as_float(r[c][i]) * p.scale_log2 - m_used);
+          sum += pv;
+          r[c][i] = __float_as_uint(pv);
+        }
+      l += sum;
+      // P buffer s is free once PV_{j-2} has been executed.
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
+      if (!ok) break;
+      uint8_t* prow = smem + Cfg::kOffP + s * Cfg::kPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(r[c][u * 8 + 0]), __uint_as_float(r[c][u * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(r[c][u * 8 + 2]), __uint_as_float(r[c][u * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(r[c][u * 8 + 4]), __uint_as_float(r[c][u * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(r[c][u * 8 + 6]), __uint_as_float(r[c][u * 8 + 7]));
+          const int col16 = c * 4 + u;           // 16-byte unit within the 128 kv columns (0..15)
+          const int chunk = col16 >> 3;          // 64-column half
+          const int unit = (col16 & 7) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * (128 * 128) + unit * 16) = w;
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full(s));
+    }
+    if (ok && n_blocks > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
+    }
+    if (ok) {
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      if (n_blocks > 0) tc_fence_after();
+      __nv_bfloat16* orow = p.O + (long long)b * p.so_b + (long long)q_idx * p.so_t + (long long)h * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_blocks > 0) {
+          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColO + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (q_idx < p.Tq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv_l, __uint_as_float(o[u * 8 + 1]) * inv_l);
+            w.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv_l, __uint_as_float(o[u * 8 + 3]) * inv_l);
+            w.z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv_l, __uint_as_float(o[u * 8 + 5]) * inv_l);
+            w.w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv_l, __uint_as_float(o[u * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+          }
+        }
+      }
+      if (q_idx < p.Tq)
+        p.lse[((long long)b * p.Hq + h) * p.Tq + q_idx] = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int spin = 0; spin < 2000; ++spin) __nanosleep(100);  // bounded grace period for copies in flight
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int D>
+static int launch_flash_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashFwdParams& p,
+                            cudaStream_t st) {
+  using Cfg = FaFwdCfg<D>;
+  static bool configured = false;
+  auto kern = flash_fwd_kernel<D>;
+  if (!configured) {
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  dim3 grid((p.Tq + kFaBlockQ - 1) / kFaBlockQ, p.Hq, p.B);
+  kern<<<grid, kFaThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, p);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace lt
+
+extern "C" {
+
+// q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D], o: [B, Tq, Hq, D]; strides in elements for the batch and time
+// dimensions, heads are D apart, D contiguous.  lse: [B, Hq, Tq] fp32 (natural log).
+int lt_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq, int Tk, int Hq, int Hkv,
+                 int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t, long long sv_b, long long sv_t,
+                 long long so_b, long long so_t, float scale, int causal, void* stream) {
+  using namespace lt;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -int(kStatusBadArgument);
+  if (B == 0 || Tq == 0) return 0;
+  CUtensorMap tq, tk, tv;
+  int r;
+  r = encode_tmap_4d(&tq, q, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1, kFaBlockQ, 1, 1);
+  if (r) return 1000 + r;
+  r = encode_tmap_4d(&tk, k, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1, kFaBlockKV, 1, 1);
+  if (r) return 2000 + r;
+  r = encode_tmap_4d(&tv, v, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1, kFaBlockKV, 1, 1);
+  if (r) return 3000 + r;
+  FlashFwdParams p{};
+  p.O = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.so_b = so_b; p.so_t = so_t;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = device_status_word();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return D == 64 ? launch_flash_fwd<64>(tq, tk, tv, p, st) : launch_flash_fwd<128>(tq, tk, tv, p, st);
+}
+
+}  // extern "C"

@@ -25,12 +25,12 @@ __device__ __forceinline__ void ce_ld8(const __nv_bfloat16* p, float (&f)[8]) {
 // stats[row] = {max, sum exp(l - max), target logit if the target falls in [vocab_start, vocab_start+V) else 0}
 __global__ void __launch_bounds__(kCeThreads)
 ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets,
-                int vocab_start, int N, int V, float* __restrict__ stats) {
+                int vocab_start, int N, int V, float* __restrict__ stats, int vec_ok) {
   __shared__ float sm[32], ss[32];
   for (int row = blockIdx.x; row < N; row += gridDim.x) {
     const __nv_bfloat16* lr = logits + (long long)row * ldl;
     float m = -INFINITY, s = 0.f;
-    const int v8 = V / 8;
+    const int v8 = vec_ok ? V / 8 : 0;
     for (int i = threadIdx.x; i < v8; i += blockDim.x) {
       float f[8];
       ce_ld8(lr + i * 8, f);
@@ -89,7 +89,7 @@ ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const l
 __global__ void __launch_bounds__(kCeThreads)
 ce_finish_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets,
                  int vocab_start, int N, int V, const float* __restrict__ gstats, float* __restrict__ loss,
-                 float grad_scale, long long ignore_index, int write_grad) {
+                 float grad_scale, long long ignore_index, int write_grad, int vec_ok) {
   for (int row = blockIdx.x; row < N; row += gridDim.x) {
     __nv_bfloat16* lr = logits + (long long)row * ldl;
     const long long tgt = targets[row];
@@ -99,7 +99,7 @@ ce_finish_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long l
     if (!write_grad) continue;
     const float inv = ignored ? 0.f : grad_scale / gs;
     const long long t = tgt - vocab_start;
-    const int v8 = V / 8;
+    const int v8 = vec_ok ? V / 8 : 0;
     for (int i = threadIdx.x; i < v8; i += blockDim.x) {
       float f[8];
       ce_ld8(lr + i * 8, f);
@@ -281,10 +281,10 @@ int lt_ce_stats(const void* logits, long long ldl, const long long* targets, int
                 void* stream) {
   using namespace lt;
   if (N == 0) return 0;
-  if (ldl % 8 != 0) return -int(kStatusBadArgument);
+  const int vec_ok = (ldl % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   const int grid = N < sm_count() * 8 ? N : sm_count() * 8;
   ce_stats_kernel<<<grid, kCeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, stats);
+      static_cast<const __nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, stats, vec_ok);
   LT_LAUNCH_CHECK();
   return 0;
 }
@@ -293,10 +293,10 @@ int lt_ce_finish(void* logits, long long ldl, const long long* targets, int voca
                  float* loss, float grad_scale, long long ignore_index, int write_grad, void* stream) {
   using namespace lt;
   if (N == 0) return 0;
-  if (ldl % 8 != 0) return -int(kStatusBadArgument);
+  const int vec_ok = (ldl % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   const int grid = N < sm_count() * 8 ? N : sm_count() * 8;
   ce_finish_kernel<<<grid, kCeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, gstats, loss, grad_scale, ignore_index, write_grad);
+      static_cast<__nv_bfloat16*>(logits), ldl, targets, vocab_start, N, V, gstats, loss, grad_scale, ignore_index, write_grad, vec_ok);
   LT_LAUNCH_CHECK();
   return 0;
 }
