@@ -1,0 +1,394 @@
+"""Llama-style decoder (RMSNorm, RoPE, GQA attention, SwiGLU) as an explicit forward/backward engine.
+
+The training hot path does not go through autograd: every layer has a hand-written backward that calls
+the sm_100a kernels directly (tcgen05 GEMMs in the three operand layouts, FlashAttention fwd/bwd, fused
+residual+RMSNorm, RoPE in place on the fused QKV buffer, SwiGLU, in-place cross-entropy gradient,
+flat-buffer AdamW).  Weights live in flat buffers described by `ParamSpec`s so that the optimizer is one
+launch and so that the ZeRO-3 engine (`litetorch_b200.parallel.fsdp`) can shard them by rows.
+
+The reference builds its decoder from `lt.nn.TransformerDecoderLayer` (post-LN, GELU, LayerNorm:
+src/nn/transformer.cpp:7-70) on the autograd tape; RMSNorm/SwiGLU/causal GQA attention are claimed in its
+README (README.md:23-25) but absent from its sources, so this model implements the claimed capability.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field, asdict
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import kernels as K
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    n_layers: int = 22
+    d_model: int = 2048
+    n_heads: int = 32
+    n_kv_heads: int = 4
+    head_dim: int = 64
+    ffn: int = 5632
+    rms_eps: float = 1e-5
+    rope_theta: float = 1e4
+    max_seq: int = 2048
+    init_std: float = 0.02
+    name: str = "llama-1.1b"
+
+    @property
+    def qkv_dim(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+
+    def num_params(self) -> int:
+        per_layer = (self.qkv_dim * self.d_model + self.d_model * self.n_heads * self.head_dim +
+                     3 * self.ffn * self.d_model + 2 * self.d_model)
+        return self.n_layers * per_layer + 2 * self.vocab_size * self.d_model + self.d_model
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Training FLOPs per token (fwd + bwd = 3x forward), causal attention counted at half."""
+        mm = self.n_layers * (self.qkv_dim * self.d_model + self.d_model * self.n_heads * self.head_dim +
+                              3 * self.ffn * self.d_model) + self.vocab_size * self.d_model
+        attn = self.n_layers * 6.0 * seq_len * self.n_heads * self.head_dim  # 3 x (QK^T + PV), causal half
+        return 6.0 * mm + attn
+
+    # ---- presets named by the benchmark configurations
+    @staticmethod
+    def tiny(**kw) -> "LlamaConfig":
+        return LlamaConfig(vocab_size=512, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
+                           max_seq=256, name="llama-tiny", **kw)
+
+    @staticmethod
+    def llama_1b(**kw) -> "LlamaConfig":
+        return LlamaConfig(**kw)
+
+    @staticmethod
+    def llama_3b(**kw) -> "LlamaConfig":
+        return LlamaConfig(vocab_size=32000, n_layers=28, d_model=3072, n_heads=24, n_kv_heads=8, head_dim=128,
+                           ffn=8192, rope_theta=1e4, max_seq=32768, name="llama-3b", **kw)
+
+    @staticmethod
+    def llama3_8b(**kw) -> "LlamaConfig":
+        return LlamaConfig(vocab_size=128256, n_layers=32, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128,
+                           ffn=14336, rope_theta=5e5, max_seq=8192, name="llama3-8b", **kw)
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    kind: str            # "matrix" (row-shardable, weight decay) or "vector" (norm gains: replicated, no decay)
+    offset: int = 0      # element offset in the flat buffer of its kind
+
+
+def param_specs(cfg: LlamaConfig) -> List[ParamSpec]:
+    """Every parameter in `parameters()` order: embedding, per layer (attn_norm, wqkv, wo, mlp_norm, w_gu, w_down),
+    final norm, lm_head."""
+    specs = [ParamSpec("embed", (cfg.vocab_size, cfg.d_model), "matrix")]
+    for i in range(cfg.n_layers):
+        p = "layers.%d." % i
+        specs += [
+            ParamSpec(p + "attn_norm", (cfg.d_model,), "vector"),
+            ParamSpec(p + "wqkv", (cfg.qkv_dim, cfg.d_model), "matrix"),
+            ParamSpec(p + "wo", (cfg.d_model, cfg.n_heads * cfg.head_dim), "matrix"),
+            ParamSpec(p + "mlp_norm", (cfg.d_model,), "vector"),
+            ParamSpec(p + "w_gu", (2 * cfg.ffn, cfg.d_model), "matrix"),
+            ParamSpec(p + "w_down", (cfg.d_model, cfg.ffn), "matrix"),
+        ]
+    specs += [ParamSpec("final_norm", (cfg.d_model,), "vector"),
+              ParamSpec("lm_head", (cfg.vocab_size, cfg.d_model), "matrix")]
+    off = {"matrix": 0, "vector": 0}
+    for s in specs:
+        s.offset = off[s.kind]
+        n = 1
+        for d in s.shape:
+            n *= d
+        off[s.kind] += (n + 127) // 128 * 128
+    return specs
+
+
+def rope_tables(cfg: LlamaConfig, device, max_seq: Optional[int] = None):
+    T = max_seq or cfg.max_seq
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device, dtype=torch.float64) / cfg.head_dim))
+    ang = torch.arange(T, device=device, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().contiguous(), ang.sin().float().contiguous()
+
+
+class LocalWeights:
+    """All parameters resident on one GPU: flat bf16 parameters + flat bf16 gradients + fp32 master/m/v."""
+
+    def __init__(self, cfg: LlamaConfig, device, seed: int = 0):
+        self.cfg = cfg
+        self.specs = param_specs(cfg)
+        self.by_name = {s.name: s for s in self.specs}
+        sizes = {"matrix": 0, "vector": 0}
+        for s in self.specs:
+            sizes[s.kind] = max(sizes[s.kind], s.offset + (math.prod(s.shape) + 127) // 128 * 128)
+        self.n_matrix, self.n_vector = sizes["matrix"], sizes["vector"]
+        n = self.n_matrix + self.n_vector
+        self.flat_p = torch.zeros(n, dtype=torch.bfloat16, device=device)
+        self.flat_g = torch.zeros(n, dtype=torch.bfloat16, device=device)
+        self.master = torch.zeros(n, dtype=torch.float32, device=device)
+        self.m = torch.zeros(n, dtype=torch.float32, device=device)
+        self.v = torch.zeros(n, dtype=torch.float32, device=device)
+        gen = torch.Generator(device=device).manual_seed(seed)
+        for s in self.specs:
+            w = self.master_view(s.name)
+            if s.kind == "matrix":
+                w.normal_(0.0, cfg.init_std, generator=gen)
+            else:
+                w.fill_(1.0)
+        self.flat_p.copy_(self.master)
+
+    def _base(self, s: ParamSpec) -> int:
+        return s.offset if s.kind == "matrix" else self.n_matrix + s.offset
+
+    def _view(self, flat, name):
+        s = self.by_name[name]
+        b = self._base(s)
+        return flat[b:b + math.prod(s.shape)].view(*s.shape)
+
+    def p(self, name) -> torch.Tensor:
+        return self._view(self.flat_p, name)
+
+    def g(self, name) -> torch.Tensor:
+        return self._view(self.flat_g, name)
+
+    def master_view(self, name) -> torch.Tensor:
+        return self._view(self.master, name)
+
+    # ---- GEMM providers (the ZeRO-3 weights object overrides these with fused all-gather variants)
+    def linear(self, x, name, **kw):
+        return K.gemm(x, self.p(name), **kw)
+
+    def dgrad(self, dy, name, **kw):
+        return K.gemm(dy, self.p(name), b_major=1, **kw)
+
+    def wgrad(self, dy, x, name, accumulate=False):
+        return K.gemm(dy, x, a_major=1, b_major=1, out=self.g(name), accumulate=accumulate)
+
+    def vector_grad(self, name):
+        return self.g(name)
+
+    def zero_grad_embed(self):
+        self.g("embed").zero_()
+
+    def embedding(self, tokens):
+        return K.embedding_fwd(tokens, self.p("embed"))
+
+    def embedding_backward(self, tokens, dx):
+        K.embedding_bwd(tokens, dx, self.g("embed"))
+
+    def optimizer_step(self, *, lr, beta1, beta2, eps, weight_decay, step, dyn=None):
+        nm = self.n_matrix
+        K.adam_flat(self.master[:nm], self.flat_g[:nm], self.m[:nm], self.v[:nm], self.flat_p[:nm], lr=lr, beta1=beta1,
+                    beta2=beta2, eps=eps, wd=weight_decay, step=step, adamw=True, dyn=dyn)
+        K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
+                    beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True, dyn=dyn)
+
+    def finish_step(self):
+        pass
+
+    def parameters(self) -> List[torch.Tensor]:
+        return [self.master_view(s.name) for s in self.specs]
+
+    def load_parameters(self, tensors: List[torch.Tensor]):
+        for s, t in zip(self.specs, tensors):
+            self.master_view(s.name).copy_(t.to(self.master.device, torch.float32).view(*s.shape))
+        self.flat_p.copy_(self.master)
+
+
+class LlamaEngine:
+    """Forward + backward + optimizer step of a Llama-style decoder on the sm_100a kernels."""
+
+    def __init__(self, cfg: LlamaConfig, device="cuda", weights=None, seed: int = 0, lr: float = 3e-4,
+                 betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, activation_checkpointing: bool = False,
+                 world_size: int = 1):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.w = weights if weights is not None else LocalWeights(cfg, self.device, seed)
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.ckpt = activation_checkpointing
+        self.world_size = world_size
+        self.step_count = 0
+        self.cos, self.sin = rope_tables(cfg, self.device)
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------------------------------ layer
+    def _layer_fwd(self, i: int, x: torch.Tensor, B: int, T: int):
+        cfg, w = self.cfg, self.w
+        p = "layers.%d." % i
+        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        h1, _, _, rstd1 = K.norm_fwd(x, w.p(p + "attn_norm"), eps=cfg.rms_eps)
+        qkv = w.linear(h1, p + "wqkv")
+        K.rope_(qkv, self.cos, self.sin, T, Hq, hd, col_offset=0)
+        K.rope_(qkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd)
+        q, k, v = self._split_qkv(qkv, B, T)
+        o, lse = K.flash_fwd(q, k, v, causal=True)
+        o2 = o.view(B * T, Hq * hd)
+        x1 = w.linear(o2, p + "wo", residual=x)
+        h2, _, _, rstd2 = K.norm_fwd(x1, w.p(p + "mlp_norm"), eps=cfg.rms_eps)
+        gu = w.linear(h2, p + "w_gu")
+        hm = K.swiglu_fwd(gu)
+        x2 = w.linear(hm, p + "w_down", residual=x1)
+        self.kernel_launches += 11
+        return x2, (x, h1, rstd1, qkv, o, lse, x1, h2, rstd2, gu, hm)
+
+    def _split_qkv(self, qkv, B, T):
+        cfg = self.cfg
+        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        q3 = qkv.view(B, T, cfg.qkv_dim)
+        q = q3[:, :, :Hq * hd].view(B, T, Hq, hd)
+        k = q3[:, :, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
+        v = q3[:, :, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
+        return q, k, v
+
+    def _layer_bwd(self, i: int, dx2: torch.Tensor, ctx, B: int, T: int, accumulate: bool):
+        cfg, w = self.cfg, self.w
+        p = "layers.%d." % i
+        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        x, h1, rstd1, qkv, o, lse, x1, h2, rstd2, gu, hm = ctx
+        # MLP
+        dhm = w.dgrad(dx2, p + "w_down")
+        w.wgrad(dx2, hm, p + "w_down", accumulate)
+        dgu = K.swiglu_bwd(gu, dhm, inplace=True)
+        dh2 = w.dgrad(dgu, p + "w_gu")
+        w.wgrad(dgu, h2, p + "w_gu", accumulate)
+        dx1, _, _ = K.norm_bwd(dh2, x1, w.p(p + "mlp_norm"), None, rstd2, dres=dx2, dw=w.vector_grad(p + "mlp_norm"),
+                               accumulate=accumulate)
+        # attention
+        o2 = o.view(B * T, Hq * hd)
+        do = w.dgrad(dx1, p + "wo")
+        w.wgrad(dx1, o2, p + "wo", accumulate)
+        dqkv = torch.empty_like(qkv)
+        q, k, v = self._split_qkv(qkv, B, T)
+        dq, dk, dv = self._split_qkv(dqkv, B, T)
+        K.flash_bwd(q, k, v, o, lse, do.view(B, T, Hq, hd), causal=True, dq=dq, dk=dk, dv=dv)
+        K.rope_(dqkv, self.cos, self.sin, T, Hq, hd, col_offset=0, backward=True)
+        K.rope_(dqkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd, backward=True)
+        dh1 = w.dgrad(dqkv, p + "wqkv")
+        w.wgrad(dqkv, h1, p + "wqkv", accumulate)
+        dx, _, _ = K.norm_bwd(dh1, x, w.p(p + "attn_norm"), None, rstd1, dres=dx1, dw=w.vector_grad(p + "attn_norm"),
+                              accumulate=accumulate)
+        self.kernel_launches += 22
+        return dx
+
+    # ------------------------------------------------------------------------------------------ model
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, *, accumulate: bool = False,
+                         loss_scale: float = 1.0) -> torch.Tensor:
+        """One micro-batch: returns the mean token loss (device scalar); gradients are left in the flat buffer."""
+        cfg, w = self.cfg, self.w
+        B, T = tokens.shape
+        M = B * T
+        tok = tokens.reshape(-1)
+        tgt = targets.reshape(-1)
+        x = w.embedding(tok)
+        saved = []
+        for i in range(cfg.n_layers):
+            if self.ckpt:
+                saved.append(x)
+                x, _ = self._layer_fwd(i, x, B, T)
+            else:
+                x, ctx = self._layer_fwd(i, x, B, T)
+                saved.append(ctx)
+        hf, _, _, rstd_f = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
+        logits = w.linear(hf, "lm_head")
+        stats = K.ce_stats(logits, tgt)
+        rows = K.ce_finish(logits, tgt, stats, grad_scale=loss_scale / (M * self.world_size))
+        loss = rows.sum() / M
+        dhf = w.dgrad(logits, "lm_head")
+        w.wgrad(logits, hf, "lm_head", accumulate)
+        del logits
+        dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate)
+        for i in reversed(range(cfg.n_layers)):
+            if self.ckpt:
+                _, ctx = self._layer_fwd(i, saved[i], B, T)
+            else:
+                ctx = saved[i]
+            dx = self._layer_bwd(i, dx, ctx, B, T, accumulate)
+            saved[i] = None
+        if not accumulate:
+            w.zero_grad_embed()
+        w.embedding_backward(tok, dx)
+        self.kernel_launches += 12
+        return loss
+
+    def forward_logits(self, tokens: torch.Tensor) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        B, T = tokens.shape
+        x = w.embedding(tokens.reshape(-1))
+        for i in range(cfg.n_layers):
+            x, _ = self._layer_fwd(i, x, B, T)
+        hf, _, _, _ = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
+        return w.linear(hf, "lm_head").view(B, T, cfg.vocab_size)
+
+    def optimizer_step(self, dyn=None):
+        self.step_count += 1
+        self.w.optimizer_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
+                              weight_decay=self.weight_decay, step=self.step_count, dyn=dyn)
+        self.kernel_launches += 2
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """The public one-call training step: forward, backward, AdamW.  Returns the loss (device scalar)."""
+        loss = self.forward_backward(tokens, targets)
+        self.optimizer_step()
+        self.w.finish_step()
+        return loss
+
+
+class TorchLlama(torch.nn.Module):
+    """The same architecture in stock PyTorch (fp32 or bf16): oracle for the tests and the cuBLAS/SDPA baseline."""
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.cfg = cfg
+        nn = torch.nn
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.d_model))
+        self.layers = nn.ParameterList()
+        self.names = []
+        for s in param_specs(cfg):
+            self.names.append(s.name)
+        self.params = nn.ParameterDict({s.name.replace(".", "_"): nn.Parameter(torch.empty(*s.shape)) for s in param_specs(cfg)})
+        del self.embed, self.layers
+
+    def P(self, name):
+        return self.params[name.replace(".", "_")]
+
+    def load_from(self, tensors):
+        with torch.no_grad():
+            for s, t in zip(param_specs(self.cfg), tensors):
+                self.P(s.name).copy_(t.view(*s.shape))
+
+    @staticmethod
+    def _rope(x, cos, sin):
+        # x: [B, T, H, D], interleaved pairs
+        c = cos[None, :x.shape[1], None, :].to(x.dtype)
+        s = sin[None, :x.shape[1], None, :].to(x.dtype)
+        x0, x1 = x[..., 0::2], x[..., 1::2]
+        return torch.stack([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1).flatten(-2)
+
+    def _norm(self, x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.rms_eps)).to(x.dtype) * w
+
+    def forward(self, tokens):
+        cfg = self.cfg
+        B, T = tokens.shape
+        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        cos, sin = rope_tables(cfg, tokens.device, T)
+        x = self.P("embed")[tokens]
+        for i in range(cfg.n_layers):
+            p = "layers.%d." % i
+            h = self._norm(x, self.P(p + "attn_norm"))
+            qkv = h @ self.P(p + "wqkv").t()
+            q = qkv[..., :Hq * hd].view(B, T, Hq, hd)
+            k = qkv[..., Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
+            v = qkv[..., (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
+            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+            o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                                 is_causal=True, enable_gqa=True)
+            x = x + o.transpose(1, 2).reshape(B, T, Hq * hd) @ self.P(p + "wo").t()
+            h = self._norm(x, self.P(p + "mlp_norm"))
+            gu = h @ self.P(p + "w_gu").t()
+            x = x + (torch.nn.functional.silu(gu[..., :cfg.ffn]) * gu[..., cfg.ffn:]) @ self.P(p + "w_down").t()
+        return self._norm(x, self.P("final_norm")) @ self.P("lm_head").t()

@@ -48,6 +48,19 @@ _SIGS = {
 
 _bound = {}
 
+# Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
+_LAUNCHES_PER_CALL = {"lt_norm_bwd": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
+                      "lt_adam_chunk_elems": 0}
+_launches = [0]
+
+
+def launch_count() -> int:
+    return _launches[0]
+
+
+def reset_launch_count():
+    _launches[0] = 0
+
 
 class KernelError(RuntimeError):
     pass
@@ -57,9 +70,16 @@ def _fn(name):
     f = _bound.get(name)
     if f is None:
         lib = cuda_lib()
-        f = getattr(lib, name)
-        f.argtypes = _SIGS[name]
-        f.restype = c_int
+        raw = getattr(lib, name)
+        raw.argtypes = _SIGS[name]
+        raw.restype = c_int
+        n = _LAUNCHES_PER_CALL.get(name, 1)
+        if n:
+            def f(*a, _raw=raw, _n=n):
+                _launches[0] += _n
+                return _raw(*a)
+        else:
+            f = raw
         _bound[name] = f
     return f
 
