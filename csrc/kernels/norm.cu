@@ -8,6 +8,8 @@
 #include "common/host.h"
 #include "common/ptx.cuh"
 
+#include <mutex>
+
 namespace lt {
 
 constexpr int kNormThreads = 256;
@@ -259,3 +261,66 @@ int lt_norm_bwd(int layer_norm, const void* dy, const void* x, const void* w, co
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in norm_noalloc.h).
+// ------------------------------------------------------------------------------------------------
+#include "norm_noalloc.h"
+
+namespace lt {
+// Partial dgamma / dbeta sums: [2][LT_NORM_NOALLOC_MAX_CTAS][LT_NORM_NOALLOC_MAX_D] fp32.
+static __device__ __align__(256) float g_norm_noalloc_scratch[2 * LT_NORM_NOALLOC_MAX_CTAS * LT_NORM_NOALLOC_MAX_D];
+
+// In host code the array's name is only a handle; the device address has to be looked up, once per device,
+// with that device current.
+static float* norm_noalloc_scratch_ptr(int* err) {
+  static float* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *err = LT_NORM_NOALLOC_ERR_SETUP; return nullptr; }
+  if (ptrs[dev]) return ptrs[dev];
+  std::lock_guard<std::mutex> lk(mu);
+  if (ptrs[dev]) return ptrs[dev];
+  float* p = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_noalloc_scratch);
+  if (e != cudaSuccess || p == nullptr) { *err = LT_NORM_NOALLOC_ERR_SETUP; return nullptr; }
+  ptrs[dev] = p;
+  return p;
+}
+}  // namespace lt
+
+extern "C" int lt_norm_bwd_noalloc(int layer_norm, const void* dy, const void* x, const void* w, const float* mean,
+                                   const float* rstd, const void* dres, void* dx, void* dw, void* db, int grads_fp32,
+                                   int accumulate, int M, int D, void* stream) {
+  using namespace lt;
+  if (D % 8 != 0 || D <= 0 || M < 0) return -int(kStatusBadArgument);
+  if (D > LT_NORM_NOALLOC_MAX_D) return LT_NORM_NOALLOC_ERR_TOO_LARGE;
+  if (M == 0) return 0;
+  int err = 0;
+  float* scratch = norm_noalloc_scratch_ptr(&err);
+  if (!scratch) return err;
+  float* dw_part = scratch;
+  float* db_part = scratch + (size_t)LT_NORM_NOALLOC_MAX_CTAS * LT_NORM_NOALLOC_MAX_D;
+  const int grid = M < LT_NORM_NOALLOC_MAX_CTAS ? M : LT_NORM_NOALLOC_MAX_CTAS;
+  const int iters = (D + kNormThreads * 8 - 1) / (kNormThreads * 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+#define LT_NORM_BWD_NA(LN, IT) \
+  norm_bwd_kernel<LN, IT><<<grid, kNormThreads, 0, st>>>(DY, X, W, mean, rstd, DR, DX, dw_part, db_part, M, D)
+  if (layer_norm) {
+    if (iters <= 1) LT_NORM_BWD_NA(true, 1); else LT_NORM_BWD_NA(true, 2);
+  } else {
+    if (iters <= 1) LT_NORM_BWD_NA(false, 1); else LT_NORM_BWD_NA(false, 2);
+  }
+#undef LT_NORM_BWD_NA
+  LT_LAUNCH_CHECK();
+  const int fb = (D + 255) / 256;
+  fold_partials_kernel<<<fb, 256, 0, st>>>(dw_part, dw, grid, D, grads_fp32, accumulate);
+  if (layer_norm && db) fold_partials_kernel<<<fb, 256, 0, st>>>(db_part, db, grid, D, grads_fp32, accumulate);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
