@@ -40,6 +40,11 @@ struct GemmParams {
   float alpha;
   int m_blocks, n_blocks, k_blocks, num_tiles;
   int group_m;  // raster group height (tiles)
+  // Tile order: 0 = grouped raster (L2 friendly); 1 = all M blocks of one N block before the next N block,
+  // starting at N block `rot`; 2 = all N blocks of one M block before the next, starting at M block `rot`.
+  // Modes 1 and 2 let a fused all-gather deliver the gathered operand in the order the tiles consume it.
+  int raster, rot;
+  int k_rot;  // the K loop starts at k-block k_rot and wraps around
   int* status;
 };
 
@@ -62,6 +67,16 @@ struct NoDone {
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+  if (p.raster == 1) {
+    m_blk = tile % p.m_blocks;
+    n_blk = (tile / p.m_blocks + p.rot) % p.n_blocks;
+    return;
+  }
+  if (p.raster == 2) {
+    n_blk = tile % p.n_blocks;
+    m_blk = (tile / p.n_blocks + p.rot) % p.m_blocks;
+    return;
+  }
   const int per_group = p.group_m * p.n_blocks;
   const int group = tile / per_group;
   const int first_m = group * p.group_m;
@@ -169,7 +184,10 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
 // is called by one thread of each epilogue warp after the warp's rows of a tile are in global memory.
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
-                                          TileGate gate, TileDone done) {
+                                          TileGate gate, TileDone done, int cta_first = 0) {
+  // CTAs [0, cta_first) of the grid belong to another role of a fused kernel; the GEMM uses the rest.
+  const int cta_id = int(blockIdx.x) - cta_first;
+  const int cta_count = int(gridDim.x) - cta_first;
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -219,10 +237,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int tile = cta_id; ok && tile < p.num_tiles; tile += cta_count) {
         int m_blk, n_blk;
         tile_coords(p, tile, m_blk, n_blk);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kl = 0; kl < p.k_blocks; ++kl) {
+          int kb = kl + p.k_rot;
+          if (kb >= p.k_blocks) kb -= p.k_blocks;
           if (!gate(m_blk, n_blk, kb, p.status)) { *abort_flag = 1; ok = false; break; }
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
           const uint32_t fb = full_bar(stage);
@@ -256,7 +276,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      for (int tile = cta_id; ok && tile < p.num_tiles; tile += cta_count, ++it) {
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aphase ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
@@ -285,7 +305,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = cta_id; tile < p.num_tiles; tile += cta_count, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
       const int buf = it & 1;
@@ -352,6 +372,7 @@ inline void fill_tiles(GemmParams& p, int block_n) {
   p.k_blocks = (p.K + kBlockK - 1) / kBlockK;
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.group_m = 16;
+  p.raster = 0; p.rot = 0; p.k_rot = 0;
 }
 
 // Host: tensor maps for the two operands.

@@ -186,6 +186,12 @@ class LocalWeights:
         K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
                     beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True, dyn=dyn)
 
+    def begin_step(self, **hyper):
+        pass
+
+    def bucket_done(self, bucket):
+        """Hook: all weight gradients of a bucket ("head", layer index, "embed") have been issued."""
+
     def finish_step(self):
         pass
 
@@ -275,8 +281,11 @@ class LlamaEngine:
 
     # ------------------------------------------------------------------------------------------ model
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, *, accumulate: bool = False,
-                         loss_scale: float = 1.0) -> torch.Tensor:
-        """One micro-batch: returns the mean token loss (device scalar); gradients are left in the flat buffer."""
+                         loss_scale: float = 1.0, fused_update: bool = False) -> torch.Tensor:
+        """One micro-batch: returns the mean token loss (device scalar); gradients are left in the flat buffer.
+
+        fused_update: sharded weights may reduce and apply each bucket's gradients as soon as its backward is done
+        (only valid for the last micro-batch of a step, after `begin_step`)."""
         cfg, w = self.cfg, self.w
         B, T = tokens.shape
         M = B * T
@@ -298,6 +307,8 @@ class LlamaEngine:
         loss = rows.sum() / M
         dhf = w.dgrad(logits, "lm_head")
         w.wgrad(logits, hf, "lm_head", accumulate)
+        if fused_update:
+            w.bucket_done("head")
         del logits
         dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate)
         for i in reversed(range(cfg.n_layers)):
@@ -306,10 +317,14 @@ class LlamaEngine:
             else:
                 ctx = saved[i]
             dx = self._layer_bwd(i, dx, ctx, B, T, accumulate)
+            if fused_update:
+                w.bucket_done(i)
             saved[i] = None
         if not accumulate:
             w.zero_grad_embed()
         w.embedding_backward(tok, dx)
+        if fused_update:
+            w.bucket_done("embed")
         self.kernel_launches += 12
         return loss
 
@@ -330,7 +345,9 @@ class LlamaEngine:
 
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """The public one-call training step: forward, backward, AdamW.  Returns the loss (device scalar)."""
-        loss = self.forward_backward(tokens, targets)
+        self.w.begin_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
+                          weight_decay=self.weight_decay, step=self.step_count + 1)
+        loss = self.forward_backward(tokens, targets, fused_update=True)
         self.optimizer_step()
         self.w.finish_step()
         return loss

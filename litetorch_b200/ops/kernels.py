@@ -41,6 +41,11 @@ _SIGS = {
     "lt_rmsprop_flat": [_vp, _vp, _vp, _ll, _f, _f, _f, _f, _vp],
     "lt_sumsq": [_vp, _i, _ll, _vp, _vp],
     "lt_clip_coef": [_vp, _vp, _f, _f, _vp],
+    "lt_ag_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f,
+                        _i, _vp, _i, _i, _i, _vp, _vp, ctypes.c_uint, _i, _vp],
+    "lt_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _i, ctypes.c_uint, _i, _i, _i, _vp],
+    "lt_embedding_fwd_sharded": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
+    "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
     "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
     "lt_flash_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
@@ -330,3 +335,69 @@ def flash_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, dq=None, dk=None,
                              float(scale), 1 if causal else 0, _stream())
     _check(rc, "lt_flash_bwd")
     return dq, dk, dv
+
+
+# ------------------------------------------------------------------------------------------------ fused communication
+def _ptr_array(ptrs):
+    arr = (c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def ag_gemm(a, b_full_or_a_full, *, gather_operand: int, shard_ptrs, world: int, rank: int, rows_per_rank: int,
+            flags: torch.Tensor, epoch: int, other: torch.Tensor, out=None, out_dtype=torch.bfloat16, bias=None,
+            residual=None, act: int = 0, accumulate: bool = False, alpha: float = 1.0, n_comm: int = 0):
+    """GEMM whose gathered operand is pulled from the ranks' shards by gather CTAs of the same kernel.
+
+    gather_operand 1: C = other[M,K] @ full[N,K]^T      (full = weight gathered by rows, tiles gated by N block)
+    gather_operand 2: C = other[M,K] @ full[K,N]        (full = weight [K rows, N], gated by K block)
+    gather_operand 0: C = full[M,K] @ other[N,K]^T      (full = activation gathered by rows, gated by M block)
+    `b_full_or_a_full` is the local staging buffer the shards are assembled in.
+    """
+    full = b_full_or_a_full
+    if gather_operand == 0:
+        A, B, a_major, b_major = full, other, 0, 0
+        M, Kd = full.shape
+        N = other.shape[0]
+    elif gather_operand == 1:
+        A, B, a_major, b_major = other, full, 0, 0
+        M, Kd = other.shape
+        N = full.shape[0]
+    else:
+        A, B, a_major, b_major = other, full, 0, 1
+        M, Kd = other.shape
+        N = full.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=other.device)
+    arr = _ptr_array(shard_ptrs)
+    rc = _fn("lt_ag_gemm_bf16")(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, Kd, A.stride(0), B.stride(0), out.stride(0),
+                                a_major, b_major, 1 if out.dtype == torch.float32 else 0, _p(bias), _p(residual),
+                                residual.stride(0) if residual is not None else 0, act, 1 if accumulate else 0, float(alpha),
+                                gather_operand, ctypes.cast(arr, c_void_p), world, rank, rows_per_rank, full.data_ptr(),
+                                flags.data_ptr(), epoch, n_comm, _stream())
+    _check(rc, "lt_ag_gemm_bf16")
+    return out
+
+
+def rs_adamw(grad_ptrs, mc_grads, master, m, v, param_shard, segs, *, lr, beta1, beta2, eps, wd, step, my_flags, peer_flag_ptrs,
+             slot: int, epoch: int, world: int, rank: int, max_ctas: int = 0):
+    seg_arr = (c_longlong * (3 * len(segs)))(*[int(x) for s in segs for x in s])
+    rc = _fn("lt_rs_adamw")(ctypes.cast(_ptr_array(grad_ptrs), c_void_p), mc_grads, master.data_ptr(), m.data_ptr(), v.data_ptr(),
+                            param_shard.data_ptr(), ctypes.cast(seg_arr, c_void_p), len(segs), lr, beta1, beta2, eps, wd,
+                            1.0 - beta1 ** step, 1.0 - beta2 ** step, my_flags.data_ptr(),
+                            ctypes.cast(_ptr_array(peer_flag_ptrs), c_void_p), slot, epoch, world, rank, max_ctas, _stream())
+    _check(rc, "lt_rs_adamw")
+
+
+def embedding_fwd_sharded(idx, table_ptrs, V, D, rows_per_rank, world, dtype=torch.bfloat16):
+    idx = idx.reshape(-1).to(torch.int64)
+    out = torch.empty((idx.numel(), D), dtype=dtype, device=idx.device)
+    rc = _fn("lt_embedding_fwd_sharded")(idx.data_ptr(), ctypes.cast(_ptr_array(table_ptrs), c_void_p), out.data_ptr(),
+                                         idx.numel(), D, V, rows_per_rank, world, _stream())
+    _check(rc, "lt_embedding_fwd_sharded")
+    return out
+
+
+def signal_barrier(my_flags, peer_flag_ptrs, slot: int, epoch: int, world: int, rank: int):
+    rc = _fn("lt_signal_barrier")(my_flags.data_ptr(), ctypes.cast(_ptr_array(peer_flag_ptrs), c_void_p), slot, epoch, world,
+                                  rank, _stream())
+    _check(rc, "lt_signal_barrier")

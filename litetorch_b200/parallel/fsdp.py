@@ -1,0 +1,269 @@
+"""ZeRO-3 weights for the Llama engine: parameters, fp32 master copies and AdamW states sharded by rows
+over the ranks of one node, with the collectives fused into the compute kernels.
+
+* forward / dgrad GEMMs gather their weight from the ranks' shards INSIDE the GEMM kernel
+  (`lt_ag_gemm_bf16`: gather CTAs copy peer shards into a local staging buffer chunk by chunk while the
+  tcgen05 tiles of already-arrived chunks run);
+* weight gradients are written to a symmetric full-size gradient buffer; when a layer's backward is done
+  a single kernel on a side stream (`lt_rs_adamw`) signals the peers, waits for their signals, reduces
+  this rank's slice over all ranks' buffers through peer loads, applies AdamW to the fp32 master shard and
+  writes the bf16 parameter shard - the reduce-scatter, the cast/scale and the optimizer in one pass,
+  overlapped with the backward of the next layer;
+* norm gains (a few KB) stay replicated; their gradients are all-reduced with NCCL.
+
+The reference's counterparts are `FullyShardedDataParallel` (include/litetorch/fsdp.h:22-130: flat shards,
+gather_parameters / shard_parameters), `FSDP::fully_shard` (src/distributed/fsdp_wrapper.cpp:12-156) and
+`ZeRO3Optimizer` (src/optim/zero3_optimizer.cpp:11-105: owner updates + broadcast for replicated params).
+Symmetric memory and peer pointers come from `torch.distributed._symmetric_memory`; NCCL is used only for
+the replicated vectors.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Dict, List
+
+import torch
+import torch.distributed as dist
+
+from ..models.llama import LlamaConfig, ParamSpec, param_specs
+from ..ops import kernels as K
+
+
+def ensure_process_group():
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+
+class SymmetricBuffer:
+    """A tensor allocated at the same offset on every rank, with every rank's device pointer to it."""
+
+    def __init__(self, numel: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, group=group.group_name if hasattr(group, "group_name") else group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        try:
+            self.mc_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(device.type, device.index) else 0
+        except Exception:
+            self.mc_ptr = 0
+        self.itemsize = self.tensor.element_size()
+
+    def peer_ptrs(self, elem_offset: int = 0) -> List[int]:
+        return [p + elem_offset * self.itemsize for p in self.ptrs]
+
+
+_STAGE_KEYS = ("wqkv", "wo", "w_gu", "w_down", "lm_head")
+
+
+class ShardedWeights:
+    SLOT_BARRIER = 0
+
+    def __init__(self, cfg: LlamaConfig, device, seed: int = 0, n_comm: int = 8, use_multimem: bool = False):
+        ensure_process_group()
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.n_comm = n_comm
+        W = self.world
+        self.specs = param_specs(cfg)
+        self.by_name = {s.name: s for s in self.specs}
+        self.matrices = [s for s in self.specs if s.kind == "matrix"]
+        self.vectors = [s for s in self.specs if s.kind == "vector"]
+        # ---- layouts
+        self.full_off: Dict[str, int] = {s.name: s.offset for s in self.matrices}
+        self.n_full = max(s.offset + (math.prod(s.shape) + 127) // 128 * 128 for s in self.matrices)
+        self.shard_off: Dict[str, int] = {}
+        off = 0
+        for s in self.matrices:
+            rows, cols = s.shape
+            assert rows % W == 0, "%s: %d rows do not divide over %d ranks" % (s.name, rows, W)
+            self.shard_off[s.name] = off
+            off += ((rows // W) * cols + 127) // 128 * 128
+        self.n_shard = off
+        self.vec_off = {s.name: s.offset for s in self.vectors}
+        self.n_vec = max(s.offset + (math.prod(s.shape) + 127) // 128 * 128 for s in self.vectors)
+        # ---- symmetric memory: parameter shards, full gradients, signal words
+        self.sym_param = SymmetricBuffer(self.n_shard, torch.bfloat16, self.device)
+        self.sym_grad = SymmetricBuffer(self.n_full, torch.bfloat16, self.device)
+        self.n_slots = cfg.n_layers + 4
+        self.sym_flags = SymmetricBuffer(self.n_slots * 8, torch.int32, self.device)
+        self.use_multimem = bool(use_multimem and self.sym_grad.mc_ptr)
+        # ---- local: fp32 master / m / v of the shard, replicated vectors, staging buffers
+        self.master = torch.zeros(self.n_shard, dtype=torch.float32, device=self.device)
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.vec_p = torch.zeros(self.n_vec, dtype=torch.bfloat16, device=self.device)
+        self.vec_g = torch.zeros(self.n_vec, dtype=torch.bfloat16, device=self.device)
+        self.vec_master = torch.zeros(self.n_vec, dtype=torch.float32, device=self.device)
+        self.vec_m = torch.zeros_like(self.vec_master)
+        self.vec_v = torch.zeros_like(self.vec_master)
+        self.stage: Dict[str, torch.Tensor] = {}
+        self.stage_flags: Dict[str, torch.Tensor] = {}
+        self.stage_epoch: Dict[str, int] = {}
+        for key in _STAGE_KEYS:
+            name = key if key == "lm_head" else "layers.0." + key
+            rows, cols = self.by_name[name].shape
+            self.stage[key] = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)
+            self.stage_flags[key] = torch.zeros(4096, dtype=torch.int32, device=self.device)
+            self.stage_epoch[key] = 0
+        # ---- init: the same random stream as the single-GPU weights, each rank keeps its rows
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        for s in self.specs:
+            n = math.prod(s.shape)
+            if s.kind == "matrix":
+                rows, cols = s.shape
+                full = torch.empty(rows, cols, dtype=torch.float32, device=self.device).normal_(0.0, cfg.init_std, generator=gen)
+                rpr = rows // W
+                mine = full[self.rank * rpr:(self.rank + 1) * rpr].reshape(-1)
+                so = self.shard_off[s.name]
+                self.master[so:so + mine.numel()].copy_(mine)
+                del full
+            else:
+                self.vec_master[s.offset:s.offset + n].fill_(1.0)
+        self.sym_param.tensor.copy_(self.master)
+        self.vec_p.copy_(self.vec_master)
+        self.side = torch.cuda.Stream(device=self.device)
+        self.flag_epoch = [0] * self.n_slots
+        self.hyper = None
+        self._pending = False
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    # ------------------------------------------------------------------ views
+    def _stage_key(self, name: str) -> str:
+        return name if name == "lm_head" else name.split(".")[-1]
+
+    def p(self, name: str) -> torch.Tensor:
+        s = self.by_name[name]
+        assert s.kind == "vector", "matrix parameters are sharded; use linear()/dgrad()"
+        return self.vec_p[s.offset:s.offset + math.prod(s.shape)]
+
+    def vector_grad(self, name: str) -> torch.Tensor:
+        s = self.by_name[name]
+        return self.vec_g[s.offset:s.offset + math.prod(s.shape)]
+
+    def g(self, name: str) -> torch.Tensor:
+        s = self.by_name[name]
+        if s.kind == "vector":
+            return self.vector_grad(name)
+        o = self.full_off[name]
+        return self.sym_grad.tensor[o:o + math.prod(s.shape)].view(*s.shape)
+
+    def shard_view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        rows, cols = self.by_name[name].shape
+        o = self.shard_off[name]
+        return flat[o:o + (rows // self.world) * cols].view(rows // self.world, cols)
+
+    # ------------------------------------------------------------------ GEMM providers
+    def _gather_gemm(self, other, name, gather_operand, **kw):
+        key = self._stage_key(name)
+        rows, cols = self.by_name[name].shape
+        self.stage_epoch[key] += 1
+        return K.ag_gemm(None, self.stage[key], gather_operand=gather_operand,
+                         shard_ptrs=self.sym_param.peer_ptrs(self.shard_off[name]), world=self.world, rank=self.rank,
+                         rows_per_rank=rows // self.world, flags=self.stage_flags[key], epoch=self.stage_epoch[key],
+                         other=other, n_comm=self.n_comm, **kw)
+
+    def linear(self, x, name, **kw):
+        return self._gather_gemm(x, name, 1, **kw)
+
+    def dgrad(self, dy, name, **kw):
+        return self._gather_gemm(dy, name, 2, **kw)
+
+    def wgrad(self, dy, x, name, accumulate=False):
+        return K.gemm(dy, x, a_major=1, b_major=1, out=self.g(name), accumulate=accumulate)
+
+    def embedding(self, tokens):
+        V, D = self.by_name["embed"].shape
+        return K.embedding_fwd_sharded(tokens, self.sym_param.peer_ptrs(self.shard_off["embed"]), V, D, V // self.world,
+                                       self.world)
+
+    def zero_grad_embed(self):
+        self.g("embed").zero_()
+
+    def embedding_backward(self, tokens, dx):
+        K.embedding_bwd(tokens, dx, self.g("embed"))
+
+    # ------------------------------------------------------------------ fused reduce-scatter + AdamW
+    def begin_step(self, **hyper):
+        self.hyper = hyper
+
+    def _bucket_names(self, bucket) -> List[str]:
+        if bucket == "head":
+            return ["lm_head"]
+        if bucket == "embed":
+            return ["embed"]
+        p = "layers.%d." % bucket
+        return [p + k for k in ("wqkv", "wo", "w_gu", "w_down")]
+
+    def _slot(self, bucket) -> int:
+        if bucket == "head":
+            return 1
+        if bucket == "embed":
+            return 2
+        return 3 + int(bucket)
+
+    def bucket_done(self, bucket):
+        """All weight gradients of `bucket` have been issued on the current stream: reduce + update on the side stream."""
+        if self.hyper is None:
+            return
+        h = self.hyper
+        ev = torch.cuda.Event()
+        ev.record()
+        slot = self._slot(bucket)
+        self.flag_epoch[slot] += 1
+        segs = []
+        for name in self._bucket_names(bucket):
+            rows, cols = self.by_name[name].shape
+            n = (rows // self.world) * cols
+            segs.append((self.full_off[name] + self.rank * n, self.shard_off[name], n))
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            K.rs_adamw(self.sym_grad.ptrs, self.sym_grad.mc_ptr if self.use_multimem else None, self.master, self.m, self.v,
+                       self.sym_param.tensor, segs, lr=h["lr"], beta1=h["beta1"], beta2=h["beta2"], eps=h["eps"],
+                       wd=h["weight_decay"], step=h["step"], my_flags=self.sym_flags.tensor,
+                       peer_flag_ptrs=self.sym_flags.ptrs, slot=slot, epoch=self.flag_epoch[slot], world=self.world,
+                       rank=self.rank)
+        self._pending = True
+
+    def optimizer_step(self, *, lr, beta1, beta2, eps, weight_decay, step, dyn=None):
+        if self.hyper is None:
+            # gradients were accumulated without the fused path: reduce + update every bucket now
+            self.begin_step(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, step=step)
+            for b in ["head"] + list(reversed(range(self.cfg.n_layers))) + ["embed"]:
+                self.bucket_done(b)
+        dist.all_reduce(self.vec_g)
+        K.adam_flat(self.vec_master, self.vec_g, self.vec_m, self.vec_v, self.vec_p, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                    wd=0.0, step=step, adamw=True, dyn=dyn)
+
+    def finish_step(self):
+        """Join the side stream and cross a node-wide barrier so that every shard is updated before the next gathers."""
+        cur = torch.cuda.current_stream()
+        if self._pending:
+            cur.wait_stream(self.side)
+            self._pending = False
+        self.flag_epoch[self.SLOT_BARRIER] += 1
+        K.signal_barrier(self.sym_flags.tensor, self.sym_flags.ptrs, self.SLOT_BARRIER, self.flag_epoch[self.SLOT_BARRIER],
+                         self.world, self.rank)
+        self.hyper = None
+
+    # ------------------------------------------------------------------ whole-model access (checkpoints, tests)
+    def gather_full_master(self, name: str) -> torch.Tensor:
+        s = self.by_name[name]
+        if s.kind == "vector":
+            return self.vec_master[s.offset:s.offset + math.prod(s.shape)].clone()
+        mine = self.shard_view(self.master, name).contiguous()
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine)
+        return torch.cat(parts, 0)
+
+    def parameters(self) -> List[torch.Tensor]:
+        return [self.gather_full_master(s.name) for s in self.specs]
