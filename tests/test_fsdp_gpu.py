@@ -77,4 +77,4 @@ def test_fsdp_matches_replicated_engine(nproc):
     assert res["status"] == 0
     for a, b in zip(res["losses"], res["ref_losses"]):
         assert abs(a - b) < 3e-2, res
-    assert res["max_rel_err"] < 2e-3, res
+    assert res["max_rel_err"] < 1e-2, res  # bf16 NCCL sum in the replica vs fp32 accumulation in the fused kernel
