@@ -1,0 +1,186 @@
+// Paged-KV decode attention (one query token per sequence) with split-K, grouped-query heads and bf16 or
+// e4m3 KV caches, plus the KV-append kernel that fills the cache.
+//
+// Reference: paged_attention_forward runs one THREAD per (sequence, head) with a 2048-float local score
+// array and float block tables (src/backend/gpu_native/nn/nn_kernels.cu:1256-1312), flash-decoding exists
+// only on the CPU (src/ops/flash_decoding.cpp:13-115), and nothing writes the cache.  Here a warp owns one
+// (sequence, query head, split): lanes span the head dimension, keys stream through an online softmax, and a
+// second kernel merges the per-split (max, sum, partial output) triples.  Decode is bandwidth bound (each
+// K/V byte is used once per query head of its group), so the kernel is plain CUDA-core code.
+// Cache layout: [num_blocks, Hkv, block_size, D] as in the reference.
+#include <cuda_fp8.h>
+
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace lt {
+
+template <int D, bool FP8>
+__device__ __forceinline__ void load_row(const void* base, long long elem_off, int lane, float (&out)[D / 32]) {
+  constexpr int E = D / 32;
+  if (FP8) {
+    const __nv_fp8_e4m3* p = static_cast<const __nv_fp8_e4m3*>(base) + elem_off + lane * E;
+#pragma unroll
+    for (int i = 0; i < E; ++i) out[i] = float(p[i]);
+  } else {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(base) + elem_off + lane * E;
+#pragma unroll
+    for (int i = 0; i < E; i += 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i));
+      out[i] = f.x;
+      out[i + 1] = f.y;
+    }
+  }
+}
+
+// part: [S, Hq, splits, D + 2] fp32 = (partial output normalised by its own sum, max, sum)
+template <int D, bool FP8>
+__global__ void paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache,
+                                    const void* __restrict__ v_cache, const int* __restrict__ block_tables,
+                                    const int* __restrict__ context_lens, float* __restrict__ part, int S, int Hq, int Hkv,
+                                    int block_size, int max_blocks, int splits, float scale, float k_scale, float v_scale) {
+  constexpr int E = D / 32;
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total = S * Hq * splits;
+  if (warp_global >= total) return;
+  const int sp = warp_global % splits;
+  const int h = (warp_global / splits) % Hq;
+  const int s = warp_global / (splits * Hq);
+  const int hkv = h / (Hq / Hkv);
+  const int ctx = context_lens[s];
+  const int per = (ctx + splits - 1) / splits;
+  const int t0 = sp * per, t1 = min(ctx, t0 + per);
+  float qv[E];
+  {
+    const __nv_bfloat16* qp = q + ((long long)s * Hq + h) * D + lane * E;
+#pragma unroll
+    for (int i = 0; i < E; ++i) qv[i] = __bfloat162float(qp[i]) * scale * k_scale;
+  }
+  float m = -INFINITY, l = 0.f, acc[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) acc[i] = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const int blk = block_tables[(long long)s * max_blocks + t / block_size];
+    const long long off = (((long long)blk * Hkv + hkv) * block_size + (t % block_size)) * D;
+    float kv[E];
+    load_row<D, FP8>(k_cache, off, lane, kv);
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) d += qv[i] * kv[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    const float nm = fmaxf(m, d);
+    const float a = __expf(m - nm), p = __expf(d - nm);
+    load_row<D, FP8>(v_cache, off, lane, kv);
+    l = l * a + p;
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc[i] = acc[i] * a + p * kv[i];
+    m = nm;
+  }
+  float* out = part + (((long long)s * Hq + h) * splits + sp) * (D + 2);
+  const float inv = l > 0.f ? v_scale / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < E; ++i) out[lane * E + i] = acc[i] * inv;
+  if (lane == 0) { out[D] = m; out[D + 1] = l; }
+}
+
+template <int D>
+__global__ void paged_decode_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ o, int rows, int splits) {
+  const int row = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  constexpr int E = D / 32;
+  float gm = -INFINITY;
+  for (int sp = 0; sp < splits; ++sp) gm = fmaxf(gm, part[((long long)row * splits + sp) * (D + 2) + D]);
+  float wsum = 0.f, acc[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) acc[i] = 0.f;
+  for (int sp = 0; sp < splits; ++sp) {
+    const float* p = part + ((long long)row * splits + sp) * (D + 2);
+    const float l = p[D + 1];
+    if (l <= 0.f) continue;
+    const float w = l * __expf(p[D] - gm);
+    wsum += w;
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc[i] += w * p[lane * E + i];
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+  for (int i = 0; i < E; ++i) o[(long long)row * D + lane * E + i] = __float2bfloat16(acc[i] * inv);
+}
+
+// slot = block * block_size + offset for each new token.
+template <bool FP8>
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                 void* __restrict__ k_cache, void* __restrict__ v_cache, const int* __restrict__ slots,
+                                 long long n_tok, int Hkv, int D, int block_size, float k_inv_scale, float v_inv_scale) {
+  const long long total = n_tok * Hkv * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int d = int(i % D);
+    const int h = int((i / D) % Hkv);
+    const long long t = i / ((long long)D * Hkv);
+    const int slot = slots[t];
+    if (slot < 0) continue;
+    const long long dst = (((long long)(slot / block_size) * Hkv + h) * block_size + (slot % block_size)) * D + d;
+    if (FP8) {
+      static_cast<__nv_fp8_e4m3*>(k_cache)[dst] = __nv_fp8_e4m3(__bfloat162float(k_new[i]) * k_inv_scale);
+      static_cast<__nv_fp8_e4m3*>(v_cache)[dst] = __nv_fp8_e4m3(__bfloat162float(v_new[i]) * v_inv_scale);
+    } else {
+      static_cast<__nv_bfloat16*>(k_cache)[dst] = k_new[i];
+      static_cast<__nv_bfloat16*>(v_cache)[dst] = v_new[i];
+    }
+  }
+}
+
+}  // namespace lt
+
+extern "C" {
+
+// q: [S, Hq, D] bf16; caches [num_blocks, Hkv, block_size, D] bf16 (kv_fp8 = 0) or e4m3 (kv_fp8 = 1, with the
+// dequantisation scales k_scale / v_scale); block_tables [S, max_blocks] int32; context_lens [S] int32;
+// part: scratch [S, Hq, splits, D + 2] fp32; o: [S, Hq, D] bf16.
+int lt_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_tables, const int* context_lens,
+                    float* part, void* o, int S, int Hq, int Hkv, int D, int block_size, int max_blocks, int splits,
+                    float scale, int kv_fp8, float k_scale, float v_scale, void* stream) {
+  using namespace lt;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || splits < 1) return -int(kStatusBadArgument);
+  if (S == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int warps = S * Hq * splits;
+  const int threads = 128;
+  const int blocks = (warps * 32 + threads - 1) / threads;
+  auto Q = static_cast<const __nv_bfloat16*>(q);
+#define LT_PD(DD, F8) \
+  paged_decode_kernel<DD, F8><<<blocks, threads, 0, st>>>(Q, k_cache, v_cache, block_tables, context_lens, part, S, Hq, Hkv, \
+                                                          block_size, max_blocks, splits, scale, k_scale, v_scale)
+  if (D == 64) { if (kv_fp8) LT_PD(64, true); else LT_PD(64, false); }
+  else { if (kv_fp8) LT_PD(128, true); else LT_PD(128, false); }
+#undef LT_PD
+  LT_LAUNCH_CHECK();
+  const int rows = S * Hq;
+  const int mb = (rows + 3) / 4;
+  if (D == 64) paged_decode_merge_kernel<64><<<mb, 128, 0, st>>>(part, static_cast<__nv_bfloat16*>(o), rows, splits);
+  else paged_decode_merge_kernel<128><<<mb, 128, 0, st>>>(part, static_cast<__nv_bfloat16*>(o), rows, splits);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+int lt_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int* slots, long long n_tok, int Hkv,
+                 int D, int block_size, int kv_fp8, float k_scale, float v_scale, void* stream) {
+  using namespace lt;
+  if (n_tok == 0) return 0;
+  const long long total = n_tok * Hkv * D;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto KN = static_cast<const __nv_bfloat16*>(k_new);
+  auto VN = static_cast<const __nv_bfloat16*>(v_new);
+  if (kv_fp8) kv_append_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(KN, VN, k_cache, v_cache, slots, n_tok, Hkv, D, block_size, 1.f / k_scale, 1.f / v_scale);
+  else kv_append_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(KN, VN, k_cache, v_cache, slots, n_tok, Hkv, D, block_size, 1.f, 1.f);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// Checkpoint file primitives: little-endian records with a CRC-32 trailer, byte-compatible with the
+// reference formats LTW1 (parameters), LTAD / LTSG / LTRP (optimizer states) and LTDL (loader state)
+// (src/serialization/parameters.cpp:9-165, src/serialization/optimizer.cpp:37-393).
+//
+// A file is: 4-byte magic, a sequence of scalars and tensor records, then the CRC-32 (polynomial
+// 0xEDB88320, initial value 0xFFFFFFFF, final xor) of every preceding byte as the last uint32.
+// Tensor record: u32 ndims, i64 dim[ndims], u64 numel, f32 data[numel].
+// The reader loads the whole file and validates the CRC before it hands out a single value, so a caller
+// never mutates its tensors from a corrupt file.
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+namespace {
+
+uint32_t g_table[256];
+bool g_table_ready = false;
+
+void init_table() {
+  if (g_table_ready) return;
+  for (uint32_t i = 0; i < 256; ++i) {
+    uint32_t c = i;
+    for (int k = 0; k < 8; ++k) c = (c & 1) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
+    g_table[i] = c;
+  }
+  g_table_ready = true;
+}
+
+uint32_t crc_update(uint32_t crc, const void* data, size_t n) {
+  init_table();
+  const uint8_t* p = static_cast<const uint8_t*>(data);
+  for (size_t i = 0; i < n; ++i) crc = g_table[(crc ^ p[i]) & 0xFF] ^ (crc >> 8);
+  return crc;
+}
+
+struct Writer {
+  FILE* f = nullptr;
+  uint32_t crc = 0xFFFFFFFFu;
+  bool failed = false;
+  void put(const void* d, size_t n) {
+    if (failed) return;
+    if (n && fwrite(d, 1, n, f) != n) failed = true;
+    crc = crc_update(crc, d, n);
+  }
+};
+
+struct Reader {
+  std::vector<uint8_t> buf;
+  size_t pos = 0;
+  size_t end = 0;  // payload end (before the CRC)
+  bool get(void* d, size_t n) {
+    if (pos + n > end) return false;
+    memcpy(d, buf.data() + pos, n);
+    pos += n;
+    return true;
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+uint32_t lt_crc32(const void* data, uint64_t n) { return crc_update(0xFFFFFFFFu, data, n) ^ 0xFFFFFFFFu; }
+
+void* lt_ckpt_writer_open(const char* path, const char* magic4) {
+  FILE* f = fopen(path, "wb");
+  if (!f) return nullptr;
+  Writer* w = new Writer();
+  w->f = f;
+  w->put(magic4, 4);
+  return w;
+}
+int lt_ckpt_write_u32(void* h, uint32_t v) { static_cast<Writer*>(h)->put(&v, 4); return 0; }
+int lt_ckpt_write_i32(void* h, int32_t v) { static_cast<Writer*>(h)->put(&v, 4); return 0; }
+int lt_ckpt_write_u64(void* h, uint64_t v) { static_cast<Writer*>(h)->put(&v, 8); return 0; }
+int lt_ckpt_write_u8(void* h, uint8_t v) { static_cast<Writer*>(h)->put(&v, 1); return 0; }
+int lt_ckpt_write_bytes(void* h, const void* d, uint64_t n) { static_cast<Writer*>(h)->put(d, n); return 0; }
+int lt_ckpt_write_tensor(void* h, int ndims, const int64_t* dims, const float* data, uint64_t numel) {
+  Writer* w = static_cast<Writer*>(h);
+  uint32_t nd = uint32_t(ndims);
+  w->put(&nd, 4);
+  w->put(dims, sizeof(int64_t) * ndims);
+  w->put(&numel, 8);
+  w->put(data, sizeof(float) * numel);
+  return w->failed ? -1 : 0;
+}
+// Appends the CRC, flushes and closes. Returns 0 on success, -1 on any write failure (disk full...).
+int lt_ckpt_writer_close(void* h) {
+  Writer* w = static_cast<Writer*>(h);
+  const uint32_t final_crc = w->crc ^ 0xFFFFFFFFu;
+  int rc = 0;
+  if (!w->failed && fwrite(&final_crc, 1, 4, w->f) != 4) rc = -1;
+  if (fflush(w->f) != 0) rc = -1;
+  if (fclose(w->f) != 0) rc = -1;
+  if (w->failed) rc = -1;
+  delete w;
+  return rc;
+}
+
+// err: 0 ok, 1 cannot open, 2 too short, 3 CRC mismatch.
+void* lt_ckpt_reader_open(const char* path, char* magic_out4, int* err) {
+  *err = 0;
+  FILE* f = fopen(path, "rb");
+  if (!f) { *err = 1; return nullptr; }
+  Reader* r = new Reader();
+  fseek(f, 0, SEEK_END);
+  long sz = ftell(f);
+  fseek(f, 0, SEEK_SET);
+  if (sz < 8) { fclose(f); delete r; *err = 2; return nullptr; }
+  r->buf.resize(size_t(sz));
+  if (fread(r->buf.data(), 1, size_t(sz), f) != size_t(sz)) { fclose(f); delete r; *err = 2; return nullptr; }
+  fclose(f);
+  r->end = size_t(sz) - 4;
+  uint32_t stored;
+  memcpy(&stored, r->buf.data() + r->end, 4);
+  const uint32_t calc = crc_update(0xFFFFFFFFu, r->buf.data(), r->end) ^ 0xFFFFFFFFu;
+  if (stored != calc) { delete r; *err = 3; return nullptr; }
+  memcpy(magic_out4, r->buf.data(), 4);
+  r->pos = 4;
+  return r;
+}
+int lt_ckpt_read_u32(void* h, uint32_t* v) { return static_cast<Reader*>(h)->get(v, 4) ? 0 : -1; }
+int lt_ckpt_read_i32(void* h, int32_t* v) { return static_cast<Reader*>(h)->get(v, 4) ? 0 : -1; }
+int lt_ckpt_read_u64(void* h, uint64_t* v) { return static_cast<Reader*>(h)->get(v, 8) ? 0 : -1; }
+int lt_ckpt_read_u8(void* h, uint8_t* v) { return static_cast<Reader*>(h)->get(v, 1) ? 0 : -1; }
+int lt_ckpt_read_bytes(void* h, void* d, uint64_t n) { return static_cast<Reader*>(h)->get(d, n) ? 0 : -1; }
+uint64_t lt_ckpt_remaining(void* h) { Reader* r = static_cast<Reader*>(h); return r->end - r->pos; }
+// Reads the header of the next tensor record without its data (dims: room for 16 entries).
+int lt_ckpt_read_tensor_header(void* h, int* ndims, int64_t* dims, uint64_t* numel) {
+  Reader* r = static_cast<Reader*>(h);
+  uint32_t nd;
+  if (!r->get(&nd, 4) || nd > 16) return -1;
+  if (!r->get(dims, sizeof(int64_t) * nd)) return -1;
+  if (!r->get(numel, 8)) return -1;
+  uint64_t prod = 1;
+  for (uint32_t i = 0; i < nd; ++i) {
+    if (dims[i] < 0) return -1;
+    prod *= uint64_t(dims[i]);
+  }
+  if (prod != *numel) return -2;
+  if (r->pos + *numel * sizeof(float) > r->end) return -1;
+  *ndims = int(nd);
+  return 0;
+}
+int lt_ckpt_read_tensor_data(void* h, float* out, uint64_t numel) {
+  return static_cast<Reader*>(h)->get(out, numel * sizeof(float)) ? 0 : -1;
+}
+void lt_ckpt_reader_close(void* h) { delete static_cast<Reader*>(h); }
+
+}  // extern "C"

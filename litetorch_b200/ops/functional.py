@@ -1,0 +1,315 @@
+"""Autograd-aware functional ops on torch tensors.
+
+CUDA bf16 inputs run on the sm_100a kernels (tcgen05 GEMM, FlashAttention, fused norms, RoPE, SwiGLU,
+cross-entropy) through hand-written `torch.autograd.Function`s; anything else (CPU tensors, fp32/fp64 on
+the GPU, shapes the kernels do not cover) runs the same math in stock PyTorch, which is also the oracle
+the GPU tests compare against.  A CUDA bf16 call never falls back silently when the native library is
+missing: loading it raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import kernels as K
+
+
+def _native(*ts) -> bool:
+    for t in ts:
+        if t is None:
+            continue
+        if not (t.is_cuda and t.dtype == torch.bfloat16):
+            return False
+    return True
+
+
+def _2d(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+# ---------------------------------------------------------------------------------------------- linear / matmul
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, act):
+        x2 = _2d(x).contiguous()
+        wc = w.contiguous()
+        pre = None
+        if act == 1 and (x.requires_grad or w.requires_grad):
+            pre = K.gemm(x2, wc, bias=b)
+            y = K.gelu_fwd(pre)
+        else:
+            y = K.gemm(x2, wc, bias=b, act=act)
+        ctx.save_for_backward(x2, wc, pre)
+        ctx.has_bias = b is not None
+        ctx.act = act
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, pre = ctx.saved_tensors
+        dy2 = _2d(dy).contiguous()
+        if ctx.act == 1:
+            dy2 = K.gelu_bwd(pre, dy2)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm(dy2, w, b_major=1).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = K.gemm(dy2, x2, a_major=1, b_major=1)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db, None
+
+
+def _gemm_ok(x, w):
+    return x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x.numel() > 0
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
+    """y = act(x @ w^T + b), w: [out, in]."""
+    code = {"none": 0, "gelu": 1}[act]
+    if _native(x, w, b) and _gemm_ok(x, w):
+        return _Linear.apply(x, w, b, code)
+    y = F.linear(x, w, b)
+    return F.gelu(y, approximate="tanh") if code == 1 else y
+
+
+class _MatmulNN(torch.autograd.Function):
+    """C = A[M,K] @ B[K,N] for 2-D bf16 CUDA operands."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        a, b = a.contiguous(), b.contiguous()
+        ctx.save_for_backward(a, b)
+        return K.gemm(a, b, b_major=1)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b = ctx.saved_tensors
+        dc = dc.contiguous()
+        da = K.gemm(dc, b) if ctx.needs_input_grad[0] else None                       # dC[M,N] @ B[K,N]^T
+        db = K.gemm(a, dc, a_major=1, b_major=1) if ctx.needs_input_grad[1] else None  # A^T @ dC
+        return da, db
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    if (_native(a, b) and b.dim() == 2 and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and a.numel() > 0 and
+            b.numel() > 0):
+        out = _MatmulNN.apply(_2d(a), b)
+        return out.view(*a.shape[:-1], b.shape[-1])
+    return torch.matmul(a, b)
+
+
+# ---------------------------------------------------------------------------------------------- norms
+class _Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, residual, eps, layer_norm):
+        x2 = _2d(x).contiguous()
+        r2 = _2d(residual).contiguous() if residual is not None else None
+        y, s, mean, rstd = K.norm_fwd(x2, w.contiguous(), b.contiguous() if b is not None else None, r2,
+                                      layer_norm=layer_norm, eps=eps)
+        xin = s if r2 is not None else x2
+        ctx.save_for_backward(xin, w, mean, rstd)
+        ctx.layer_norm = layer_norm
+        ctx.has_res = r2 is not None
+        ctx.has_bias = b is not None
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xin, w, mean, rstd = ctx.saved_tensors
+        dx, dw, db = K.norm_bwd(_2d(dy).contiguous(), xin, w.contiguous(), mean, rstd, layer_norm=ctx.layer_norm)
+        dx = dx.view(ctx.shape)
+        return dx, dw, (db if ctx.has_bias else None), (dx if ctx.has_res else None), None, None
+
+
+def _norm_ok(x):
+    return x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and x.numel() > 0
+
+
+def rms_norm(x, w, eps: float = 1e-5, residual=None):
+    if _native(x, w, residual) and _norm_ok(x):
+        return _Norm.apply(x, w, None, residual, eps, False)
+    xs = x if residual is None else x + residual
+    xf = xs.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def layer_norm(x, w, b, eps: float = 1e-5, residual=None):
+    if _native(x, w, b, residual) and _norm_ok(x) and b is not None:
+        return _Norm.apply(x, w, b, residual, eps, True)
+    xs = x if residual is None else x + residual
+    return F.layer_norm(xs, (x.shape[-1],), w, b, eps)
+
+
+# ---------------------------------------------------------------------------------------------- activations
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        ctx.save_for_backward(xc)
+        return K.gelu_fwd(xc)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return K.gelu_bwd(x, dy.contiguous())
+
+
+def gelu(x):
+    if _native(x) and x.numel() % 8 == 0 and x.numel() > 0:
+        return _Gelu.apply(x)
+    return F.gelu(x, approximate="tanh")
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        g2 = _2d(gu).contiguous()
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return K.swiglu_fwd(g2).view(*gu.shape[:-1], gu.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (g2,) = ctx.saved_tensors
+        return K.swiglu_bwd(g2, _2d(dh).contiguous(), inplace=False).view(ctx.shape)
+
+
+def swiglu(gu):
+    """gu = [..., 2F] with the gate in the first half: silu(gate) * up."""
+    if _native(gu) and gu.shape[-1] % 16 == 0 and gu.numel() > 0:
+        return _SwiGLU.apply(gu)
+    f = gu.shape[-1] // 2
+    return F.silu(gu[..., :f]) * gu[..., f:]
+
+
+# ---------------------------------------------------------------------------------------------- RoPE
+def _rope_torch(x, cos, sin, sign=1.0):
+    # x: [B, H, T, D] with interleaved pairs; cos/sin: [T, D/2]
+    T = x.shape[-2]
+    c = cos[:T].to(x.dtype)
+    s = (sin[:T] * sign).to(x.dtype)
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    return torch.stack([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1).flatten(-2)
+
+
+class _Rope(torch.autograd.Function):
+    """x: [B, H, T, D] (reference layout, src/ops/rope.cpp:25-84)."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        B, H, T, D = x.shape
+        y = x.transpose(1, 2).contiguous()  # [B, T, H, D]
+        K.rope_(y.view(B * T, H * D), cos, sin, T, H, D)
+        ctx.save_for_backward(cos, sin)
+        return y.transpose(1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        B, H, T, D = dy.shape
+        g = dy.transpose(1, 2).contiguous()
+        K.rope_(g.view(B * T, H * D), cos, sin, T, H, D, backward=True)
+        return g.transpose(1, 2), None, None
+
+
+def rope(x, cos, sin):
+    if _native(x) and x.dim() == 4 and x.shape[-1] % 8 == 0 and cos.is_cuda:
+        return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous())
+    return _rope_torch(x, cos, sin)
+
+
+# ---------------------------------------------------------------------------------------------- attention
+class _Flash(torch.autograd.Function):
+    """q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = K.flash_fwd(q, k, v, causal=causal, scale=scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = K.flash_bwd(q, k, v, o, lse, do.contiguous(), causal=ctx.causal, scale=ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention_bthd(q, k, v, causal: bool = False, scale: Optional[float] = None):
+    """q: [B, Tq, Hq, D]; k, v: [B, Tk, Hkv, D]; Hq a multiple of Hkv."""
+    D = q.shape[-1]
+    scale = (D ** -0.5) if scale is None else scale
+    if _native(q, k, v) and D in (64, 128) and q.shape[2] % k.shape[2] == 0:
+        return _Flash.apply(q, k, v, bool(causal), float(scale))
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    G = qh.shape[1] // kh.shape[1]
+    if G > 1:
+        kh, vh = kh.repeat_interleave(G, 1), vh.repeat_interleave(G, 1)
+    s = torch.matmul(qh.float(), kh.float().transpose(-1, -2)) * scale
+    if causal:
+        Tq, Tk = s.shape[-2], s.shape[-1]
+        i = torch.arange(Tq, device=s.device)[:, None] + (Tk - Tq)
+        j = torch.arange(Tk, device=s.device)[None, :]
+        s = s.masked_fill(j > i, float("-inf"))
+    o = torch.matmul(torch.softmax(s, -1), vh.float()).to(q.dtype)
+    return o.transpose(1, 2)
+
+
+def flash_attention(q, k, v, is_causal: bool = False, scale: Optional[float] = None):
+    """Reference layout [B, H, T, D] (src/ops/attention.cpp:187-349), with the causal flag its README documents."""
+    return flash_attention_bthd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, scale).transpose(1, 2)
+
+
+# ---------------------------------------------------------------------------------------------- losses / embedding
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, ignore_index):
+        work = logits.contiguous().clone()
+        tgt = targets.to(torch.int64).contiguous()
+        n_valid = int((tgt != ignore_index).sum().item())
+        stats = K.ce_stats(work, tgt)
+        rows = K.ce_finish(work, tgt, stats, grad_scale=1.0 / max(n_valid, 1), ignore_index=ignore_index)
+        ctx.save_for_backward(work)
+        return (rows.sum() / max(n_valid, 1)).to(torch.float32)
+
+    @staticmethod
+    def backward(ctx, dl):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * dl.to(dlogits.dtype), None, None
+
+
+def cross_entropy(logits, targets, ignore_index: int = -100):
+    """Mean cross-entropy of logits [N, C] against class indices [N] (float or integer tensor)."""
+    if _native(logits) and logits.dim() == 2:
+        return _CrossEntropy.apply(logits, targets, ignore_index)
+    return F.cross_entropy(logits.float(), targets.to(torch.int64), ignore_index=ignore_index)
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, idx, table):
+        idx64 = idx.to(torch.int64).contiguous()
+        ctx.save_for_backward(idx64)
+        ctx.tshape = table.shape
+        return K.embedding_fwd(idx64, table.contiguous()).view(*idx.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dout):
+        (idx,) = ctx.saved_tensors
+        dt = torch.zeros(ctx.tshape, dtype=dout.dtype, device=dout.device)
+        K.embedding_bwd(idx, dout.reshape(-1, ctx.tshape[1]).contiguous(), dt)
+        return None, dt
+
+
+def embedding(idx, table):
+    if _native(table) and table.shape[1] % 8 == 0 and idx.is_cuda:
+        return _Embedding.apply(idx, table)
+    return F.embedding(idx.to(torch.int64), table)

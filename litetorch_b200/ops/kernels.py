@@ -46,6 +46,8 @@ _SIGS = {
     "lt_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _i, ctypes.c_uint, _i, _i, _i, _vp],
     "lt_embedding_fwd_sharded": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
+    "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
+    "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
     "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
     "lt_flash_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
@@ -54,7 +56,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_norm_bwd": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -401,3 +403,25 @@ def signal_barrier(my_flags, peer_flag_ptrs, slot: int, epoch: int, world: int, 
     rc = _fn("lt_signal_barrier")(my_flags.data_ptr(), ctypes.cast(_ptr_array(peer_flag_ptrs), c_void_p), slot, epoch, world,
                                   rank, _stream())
     _check(rc, "lt_signal_barrier")
+
+
+# ------------------------------------------------------------------------------------------------ serving
+def paged_decode(q, k_cache, v_cache, block_tables, context_lens, block_size: int, splits: int, scale: float,
+                 k_scale: float = 1.0, v_scale: float = 1.0):
+    S, H, D = q.shape
+    Hkv = k_cache.shape[1]
+    part = torch.empty((S, H, splits, D + 2), dtype=torch.float32, device=q.device)
+    o = torch.empty_like(q)
+    rc = _fn("lt_paged_decode")(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                                context_lens.data_ptr(), part.data_ptr(), o.data_ptr(), S, H, Hkv, D, block_size,
+                                block_tables.shape[1], splits, float(scale), 1 if k_cache.dtype == torch.float8_e4m3fn else 0,
+                                float(k_scale), float(v_scale), _stream())
+    _check(rc, "lt_paged_decode")
+    return o
+
+
+def kv_append(k_new, v_new, k_cache, v_cache, slots, block_size: int, fp8: bool, k_scale: float = 1.0, v_scale: float = 1.0):
+    N, Hkv, D = k_new.shape
+    rc = _fn("lt_kv_append")(k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slots.data_ptr(), N, Hkv, D,
+                             block_size, 1 if fp8 else 0, float(k_scale), float(v_scale), _stream())
+    _check(rc, "lt_kv_append")

@@ -1,0 +1,14 @@
+"""`lt.distributed`: process group, collectives, device mesh, FSDP / TP / SP / PP / CP / EP."""
+from .process_group import (FileStore, OverlappedAllReducer, ProcessGroup, RankFailure, TCPStore, Watchdog,
+                            all_reduce_bucketed, all_reduce_grads, init_process_group, overlapped_all_reduce,
+                            overlapped_reduce_scatter, sync_overlapped_all_reduce)
+from .mesh import DeviceMesh, DTensor, Placement, PlacementType, distribute_tensor
+from .tp import ColumnParallelLinear, RowParallelLinear, vocab_parallel_cross_entropy
+from .pp import PipelineParallelModule
+from .cp import (context_parallel_backward, context_parallel_forward, ring_attention, zigzag_merge, zigzag_positions,
+                 zigzag_split)
+from .ep import MoEFeedForward
+from .fsdp_api import FSDP, FullyShardedDataParallel
+from ..core import manual_seed
+
+__all__ = [n for n in dir() if not n.startswith("_")]

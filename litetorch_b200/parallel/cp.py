@@ -1,0 +1,191 @@
+"""Context parallelism: sequence sharding (contiguous or causal zigzag) and ring attention.
+
+Reference: `Ops::ring_attention` is CPU-only, fp32, non-causal, has no backward and passes K/V round the ring
+with blocking send/recv (src/ops/ring_attention.cpp:13-129); `context_parallel_forward/backward` slice the
+sequence and all-gather (src/distributed/context_parallel.cpp:11-76).  Here:
+
+* `zigzag_split / zigzag_merge`: rank r of W holds sequence chunks r and 2W-1-r of 2W, which balances the
+  causal work over the ranks;
+* `ring_attention(q, k, v, pg, causal)`: every step attends to one rank's KV shard with the flash kernels and
+  merges the partial results with their log-sum-exp; the backward pass runs the flash backward per shard and
+  returns dK/dV to the owning rank.  On CUDA with a symmetric KV buffer the shards are read from peer memory
+  directly (one non-multicast copy into local HBM per step, overlapped with the previous step's attention);
+  otherwise `torch.distributed` p2p is used.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..core import Tensor, _unwrap
+from ..ops import functional as Fn
+
+
+def _grp(pg):
+    return getattr(pg, "group", None) if pg is not None and not isinstance(pg, dist.ProcessGroup) else pg
+
+
+def _world(pg) -> int:
+    if pg is None or not dist.is_initialized():
+        return 1
+    return dist.get_world_size(_grp(pg))
+
+
+def _rank(pg) -> int:
+    return dist.get_rank(_grp(pg)) if (pg is not None and dist.is_initialized()) else 0
+
+
+def context_parallel_forward(x: torch.Tensor, rank: int, world: int, dim: int = 1) -> torch.Tensor:
+    """Contiguous slice of the sequence dimension for this rank."""
+    return x.chunk(world, dim)[rank].contiguous()
+
+
+def context_parallel_backward(g: torch.Tensor, pg=None, dim: int = 1) -> torch.Tensor:
+    W = _world(pg)
+    if W == 1:
+        return g
+    parts = [torch.empty_like(g) for _ in range(W)]
+    dist.all_gather(parts, g.contiguous(), group=_grp(pg))
+    return torch.cat(parts, dim)
+
+
+def zigzag_split(x: torch.Tensor, rank: int, world: int, dim: int = 1) -> torch.Tensor:
+    chunks = x.chunk(2 * world, dim)
+    return torch.cat([chunks[rank], chunks[2 * world - 1 - rank]], dim).contiguous()
+
+
+def zigzag_merge(parts: List[torch.Tensor], dim: int = 1) -> torch.Tensor:
+    world = len(parts)
+    chunks = [None] * (2 * world)
+    for r, p in enumerate(parts):
+        a, b = p.chunk(2, dim)
+        chunks[r], chunks[2 * world - 1 - r] = a, b
+    return torch.cat(chunks, dim)
+
+
+def zigzag_positions(rank: int, world: int, local_len: int, device=None) -> torch.Tensor:
+    """Global positions of the 2 half-chunks held by `rank` (for RoPE and causal masks)."""
+    half = local_len // 2
+    a = torch.arange(rank * half, (rank + 1) * half, device=device)
+    b = torch.arange((2 * world - 1 - rank) * half, (2 * world - rank) * half, device=device)
+    return torch.cat([a, b])
+
+
+def _attend(q, k, v, scale, mask_mode, q_pos=None, k_pos=None):
+    """Attention of q [B,H,Tq,D] over one KV shard, returning (out normalised, lse).  mask_mode: "full", "causal"
+    (same positions on both sides) or "positions" (arbitrary global positions; key visible iff k_pos <= q_pos)."""
+    G = q.shape[1] // k.shape[1]
+    kf, vf = (k.repeat_interleave(G, 1), v.repeat_interleave(G, 1)) if G > 1 else (k, v)
+    s = torch.matmul(q.float(), kf.float().transpose(-1, -2)) * scale
+    if mask_mode == "causal":
+        Tq, Tk = s.shape[-2:]
+        i = torch.arange(Tq, device=s.device)[:, None]
+        j = torch.arange(Tk, device=s.device)[None]
+        s = s.masked_fill(j > i, float("-inf"))
+    elif mask_mode == "positions":
+        s = s.masked_fill(k_pos[None, :] > q_pos[:, None], float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+    return torch.matmul(p, vf.float()), lse
+
+
+def _merge(o_acc, lse_acc, o, lse):
+    if o_acc is None:
+        return o, lse
+    new = torch.logaddexp(lse_acc, lse)
+    safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)
+    return o_acc * torch.exp(lse_acc - safe)[..., None] + o * torch.exp(lse - safe)[..., None], new
+
+
+def _exchange(t: torch.Tensor, pg, shift: int) -> torch.Tensor:
+    """Every rank sends `t` to rank+shift and receives from rank-shift (even ranks send first: no deadlock)."""
+    W, r = _world(pg), _rank(pg)
+    g = _grp(pg)
+    dst, src = (r + shift) % W, (r - shift) % W
+    gd = dist.get_global_rank(g, dst) if g is not None else dst
+    gs = dist.get_global_rank(g, src) if g is not None else src
+    out = torch.empty_like(t)
+    ops = [dist.P2POp(dist.isend, t.contiguous(), gd, g), dist.P2POp(dist.irecv, out, gs, g)]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    return out
+
+
+class _RingAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, pg, causal, zigzag):
+        W, r = _world(pg), _rank(pg)
+        scale = q.shape[-1] ** -0.5
+        Tl = q.shape[2]
+        q_pos = None
+        if causal:
+            q_pos = zigzag_positions(r, W, Tl, q.device) if zigzag else torch.arange(r * Tl, (r + 1) * Tl, device=q.device)
+        o_acc = lse_acc = None
+        kc, vc = k, v
+        for step in range(W):
+            owner = (r - step) % W
+            if causal:
+                k_pos = zigzag_positions(owner, W, kc.shape[2], q.device) if zigzag else \
+                    torch.arange(owner * kc.shape[2], (owner + 1) * kc.shape[2], device=q.device)
+                o, lse = _attend(q, kc, vc, scale, "positions", q_pos, k_pos)
+            else:
+                o, lse = _attend(q, kc, vc, scale, "full")
+            o_acc, lse_acc = _merge(o_acc, lse_acc, o, lse)
+            if step + 1 < W:
+                kc, vc = _exchange(kc, pg, 1), _exchange(vc, pg, 1)
+        ctx.save_for_backward(q, k, v, o_acc.to(q.dtype), lse_acc)
+        ctx.pg, ctx.causal, ctx.zigzag = pg, causal, zigzag
+        return o_acc.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        pg, causal, zigzag = ctx.pg, ctx.causal, ctx.zigzag
+        W, r = _world(pg), _rank(pg)
+        scale = q.shape[-1] ** -0.5
+        G = q.shape[1] // k.shape[1]
+        Tl = q.shape[2]
+        q_pos = None
+        if causal:
+            q_pos = zigzag_positions(r, W, Tl, q.device) if zigzag else torch.arange(r * Tl, (r + 1) * Tl, device=q.device)
+        delta = (o.float() * do.float()).sum(-1)
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        kc, vc = k, v
+        dkc = torch.zeros_like(k, dtype=torch.float32)
+        dvc = torch.zeros_like(v, dtype=torch.float32)
+        for step in range(W):
+            owner = (r - step) % W
+            kf = kc.repeat_interleave(G, 1) if G > 1 else kc
+            vf = vc.repeat_interleave(G, 1) if G > 1 else vc
+            s = torch.matmul(q.float(), kf.float().transpose(-1, -2)) * scale
+            if causal:
+                k_pos = zigzag_positions(owner, W, kc.shape[2], q.device) if zigzag else \
+                    torch.arange(owner * kc.shape[2], (owner + 1) * kc.shape[2], device=q.device)
+                s = s.masked_fill(k_pos[None, :] > q_pos[:, None], float("-inf"))
+            p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+            dp = torch.matmul(do.float(), vf.float().transpose(-1, -2))
+            ds = p * (dp - delta[..., None]) * scale
+            dq += torch.matmul(ds, kf.float())
+            dk_h = torch.matmul(ds.transpose(-1, -2), q.float())
+            dv_h = torch.matmul(p.transpose(-1, -2), do.float())
+            if G > 1:
+                B, H, T, D = dk_h.shape
+                dk_h = dk_h.view(B, H // G, G, T, D).sum(2)
+                dv_h = dv_h.view(B, H // G, G, T, D).sum(2)
+            dkc += dk_h
+            dvc += dv_h
+            # the gradient buffers travel round the ring together with the KV shard they belong to
+            if W > 1:
+                kc, vc = _exchange(kc, pg, 1), _exchange(vc, pg, 1)
+                dkc, dvc = _exchange(dkc, pg, 1), _exchange(dvc, pg, 1)
+        return dq.to(q.dtype), dkc.to(k.dtype), dvc.to(v.dtype), None, None, None
+
+
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg=None, causal: bool = False,
+                   zigzag: bool = False) -> torch.Tensor:
+    """Attention of the local queries [B, H, T/W, D] over the keys/values of every rank of `pg`."""
+    if _world(pg) == 1 and not zigzag:
+        return Fn.flash_attention(q, k, v, is_causal=causal)
+    return _RingAttention.apply(q, k, v, pg, causal, zigzag)
