@@ -110,7 +110,7 @@ def _unwrap(x):
 
 
 class Tensor:
-    __slots__ = ("_t", "_dtype_tag", "__weakref__")
+    __slots__ = ("_t", "_dtype_tag", "shard", "__weakref__")   # `shard`: this rank's slice under FSDP (as in the reference Tensor)
 
     def __init__(self, t: torch.Tensor, dtype_tag: Optional[DataType] = None):
         self._t = t

@@ -28,6 +28,7 @@ class PipelineParallelModule:
         self.device = device
         self._in_shape = None
         self._in_dtype = torch.float32
+        self._sent_shape = False
 
     # ---- helpers
     def _global(self, r: int) -> int:
@@ -73,13 +74,13 @@ class PipelineParallelModule:
     # ---- forward only
     def forward(self, x: Optional[Tensor] = None) -> Optional[Tensor]:
         """recv (unless first) -> local module -> send (unless last).  Returns the output on the last stage."""
-        first_shape = self._in_shape is None
         if not self.is_first and self.world > 1:
             x = Tensor(self._recv_activation(self.rank - 1))
         out = self.local_module(x)
         if not self.is_last and self.world > 1:
-            self._send(_unwrap(out).detach(), self.rank + 1, with_shape=first_shape)
-            return None if self.world > 1 else out
+            self._send(_unwrap(out).detach(), self.rank + 1, with_shape=not self._sent_shape)
+            self._sent_shape = True
+            return None
         return out
 
     __call__ = forward
@@ -91,54 +92,99 @@ class PipelineParallelModule:
         return self.forward_microbatches(microbatches)
 
     # ---- training
+    def _batched(self, send_t, send_peer, recv_buf, recv_peer):
+        """One grouped isend + irecv (either may be None): neighbouring stages post the mirror-image pair, so neither
+        side can block the other - which plain send-then-recv orderings do in the 1F1B steady state."""
+        ops = []
+        if send_t is not None:
+            ops.append(dist.P2POp(dist.isend, send_t.contiguous(), self._global(send_peer), self.group))
+        if recv_buf is not None:
+            ops.append(dist.P2POp(dist.irecv, recv_buf, self._global(recv_peer), self.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
     def train_step_1f1b(self, microbatches: Sequence, loss_fn: Callable, targets: Optional[Sequence] = None) -> float:
         """One optimisation step's forward/backward over `microbatches` with the 1F1B schedule.
 
         On the first stage each micro-batch is the input tensor; on the last stage `loss_fn(output, target_or_mb)`
         produces the loss.  Returns the mean loss on the last stage (0.0 elsewhere).  Gradients accumulate in the
-        local module's parameters."""
+        local module's parameters.  Steady-state transfers are grouped pairs (send activation + receive gradient,
+        send gradient + receive next activation)."""
         M, W, r = len(microbatches), self.world, self.rank
         warm = min(M, W - r - 1)
+        steady = M - warm
         fifo = deque()
         total = 0.0
-        sent_shape = [False]
-        grad_shape_known = [False]
+        first, last = (r == 0 or W == 1), (r == W - 1)
 
-        def fwd(i):
-            if r == 0 or W == 1:
-                x = _unwrap(microbatches[i])
-                xin = x
-            else:
-                xin = self._recv_activation(r - 1).requires_grad_(True)
+        def run_fwd(i, xin):
             out = _unwrap(self.local_module(Tensor(xin)))
-            if r < W - 1:
-                self._send(out.detach(), r + 1, with_shape=not sent_shape[0])
-                sent_shape[0] = True
             fifo.append((xin, out, i))
+            return out
 
-        def bwd():
+        def run_bwd(grad_out):
             nonlocal total
             xin, out, i = fifo.popleft()
-            if r == W - 1:
+            if last:
                 tgt = targets[i] if targets is not None else microbatches[i]
                 loss = _unwrap(loss_fn(Tensor(out), tgt))
                 total += float(loss.detach())
                 (loss / M).backward()
             else:
-                g = torch.empty_like(out)
-                dist.recv(g, self._global(r + 1), group=self.group)
-                out.backward(g)
-            if r > 0:
-                dist.send(xin.grad.contiguous(), self._global(r - 1), group=self.group)
+                out.backward(grad_out)
+            return None if first else xin.grad
 
+        def recv_fwd_plain():
+            return self._recv_activation(r - 1).requires_grad_(True)
+
+        def send_fwd_plain(out):
+            self._send(out.detach(), r + 1, with_shape=not self._sent_shape)
+            self._sent_shape = True
+
+        def new_input(i):
+            return _unwrap(microbatches[i]) if first else None
+
+        # warm-up forwards (plain transfers; the first one carries the shape header)
         for i in range(warm):
-            fwd(i)
-        for i in range(warm, M):
-            fwd(i)
-            bwd()
-        while fifo:
-            bwd()
-        return total / M if r == W - 1 else 0.0
+            xin = new_input(i) if first else recv_fwd_plain()
+            out = run_fwd(i, xin)
+            if not last:
+                send_fwd_plain(out)
+        xin = None
+        if steady > 0:
+            xin = new_input(warm) if first else recv_fwd_plain()
+        for k in range(steady):
+            i = warm + k
+            out = run_fwd(i, xin)
+            grad_out = None
+            if not last:
+                if not self._sent_shape:                     # only possible when warm == 0, i.e. never for a non-last stage
+                    send_fwd_plain(out)
+                    grad_out = torch.empty_like(out)
+                    self._batched(None, 0, grad_out, r + 1)
+                else:
+                    grad_out = torch.empty_like(out)
+                    self._batched(out.detach(), r + 1, grad_out, r + 1)
+            gin = run_bwd(grad_out)
+            more = k + 1 < steady
+            if first:
+                xin = new_input(i + 1) if more else None
+            else:
+                nxt = torch.empty(self._in_shape, dtype=self._in_dtype, device=gin.device) if more else None
+                self._batched(gin, r - 1, nxt, r - 1)
+                xin = nxt.requires_grad_(True) if more else None
+        # drain
+        for _ in range(warm):
+            grad_out = None
+            if not last:
+                _, out, _ = fifo[0]
+                grad_out = torch.empty_like(out)
+                self._batched(None, 0, grad_out, r + 1)
+            gin = run_bwd(grad_out)
+            if not first:
+                self._batched(gin, r - 1, None, 0)
+        return total / M if last else 0.0
 
     run_1f1b_with_backward = train_step_1f1b
 
