@@ -19,7 +19,8 @@
 namespace lt {
 
 constexpr int kFbBlock = 128;
-constexpr int kFbThreads = 192;
+constexpr int kFbThreads = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2-9 compute (two per TMEM lane quarter)
+constexpr int kFbComputeThreads = 256;
 
 struct FlashBwdParams {
   const float* lse;    // [B, Hq, Tq] natural log
@@ -52,28 +53,32 @@ struct FaBwdCfg {
   static constexpr bool kDqAliasesS = (D != 64);
 };
 
-// delta[b,h,t] = sum_d O * dO ; one warp per (b,t,h) row.
+// delta[b,h,t] = sum_d O * dO ; D/8 threads per (b,t,h) row, 16 bytes each.
 __global__ void flash_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                        float* __restrict__ delta, int B, int Tq, int Hq, int D, long long so_b,
                                        long long so_t, long long sdo_b, long long sdo_t) {
-  const long long warp_id = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const int tpr = D / 8;  // 8 or 16 threads per row
+  const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long row = gid / tpr;
+  const int sub = int(gid % tpr);
   const long long total = (long long)B * Tq * Hq;
-  if (warp_id >= total) return;
-  const int h = int(warp_id % Hq);
-  const int t = int((warp_id / Hq) % Tq);
-  const int b = int(warp_id / ((long long)Hq * Tq));
-  const __nv_bfloat16* o = O + b * so_b + t * so_t + (long long)h * D;
-  const __nv_bfloat16* d = dO + b * sdo_b + t * sdo_t + (long long)h * D;
   float s = 0.f;
-  for (int c = lane * 2; c < D; c += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + c));
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + c));
-    s += a.x * g.x + a.y * g.y;
-  }
+  int h = 0, t = 0, b = 0;
+  if (row < total) {
+    h = int(row % Hq);
+    t = int((row / Hq) % Tq);
+    b = int(row / ((long long)Hq * Tq));
+    const uint4 a = *reinterpret_cast<const uint4*>(O + b * so_b + t * so_t + (long long)h * D + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + b * sdo_b + t * sdo_t + (long long)h * D + sub * 8);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) delta[((long long)b * Hq + h) * Tq + t] = s;
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack_bf16x2(av[i]), y = unpack_bf16x2(gv[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int off = tpr / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (row < total && sub == 0) delta[((long long)b * Hq + h) * Tq + t] = s;
 }
 
 __global__ void flash_bwd_convert_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int B, int Tq,
@@ -91,6 +96,12 @@ __global__ void flash_bwd_convert_dq_kernel(const float* __restrict__ acc, __nv_
     o.y = pack_bf16x2(v.z, v.w);
     *reinterpret_cast<uint2*>(dq + b * sdq_b + t * sdq_t + c) = o;
   }
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -139,9 +150,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_free, 128);
-    mbar_init(pds_full, 128); mbar_init(pds_empty, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_free, 128);
+    mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads);
+    mbar_init(pds_full, kFbComputeThreads); mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -247,7 +258,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- compute warps
+    // Two warps share each TMEM lane quarter (a warp may only touch lanes 32*(warp%4)..+31); they split the columns.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     bool ok = true;
@@ -273,7 +286,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint8_t* prow = smem + Cfg::kOffP + (row >> 3) * 1024 + (row & 7) * 128;
       uint8_t* dsrow = smem + Cfg::kOffDS + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv[32], dp[32];
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + c * 32, sv);
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDP + c * 32, dp);
@@ -282,7 +295,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; ++i) {
           const int kv_idx = kv0 + c * 32 + i;
           float pv = 0.f;
-          if (q_valid && kv_idx <= limit && lse2 != -INFINITY) pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+          if (q_valid && kv_idx <= limit && lse2 != -INFINITY) pv = ex2_approx(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
           const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
           sv[i] = __float_as_uint(pv);
           dp[i] = __float_as_uint(ds);
@@ -315,7 +328,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       float* dq_row = p.dq_acc + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t dq[32];
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + c * 32, dq);
         tmem_ld_wait();
@@ -337,7 +350,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __nv_bfloat16* dk_row = p.dK + b * p.sdk_b + (long long)kv_idx * p.sdk_t + (long long)hkv * D;
       __nv_bfloat16* dv_row = p.dV + b * p.sdk_b + (long long)kv_idx * p.sdk_t + (long long)hkv * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t a[32], g[32];
         if (n_iter > 0) {
           tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDK + c * 32, a);
@@ -413,7 +426,7 @@ int lt_flash_bwd(const void* q, const void* k, const void* v, const void* o, con
   {
     const long long rows = (long long)B * Tq * Hq;
     const int threads = 256;
-    const long long blocks = (rows * 32 + threads - 1) / threads;
+    const long long blocks = (rows * (D / 8) + threads - 1) / threads;
     flash_bwd_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(o),
                                                                  static_cast<const __nv_bfloat16*>(d_o), delta, B, Tq, Hq, D,
                                                                  so_b, so_t, sdo_b, sdo_t);

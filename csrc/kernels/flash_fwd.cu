@@ -19,7 +19,8 @@ namespace lt {
 
 constexpr int kFaBlockQ = 128;
 constexpr int kFaBlockKV = 128;
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;          // warp 0 producer, warp 1 MMA issuer, warps 2-9 softmax
+constexpr int kFaSoftmaxThreads = 256;   // two warps per TMEM lane quarter, 64 score columns each
 
 struct FlashFwdParams {
   __nv_bfloat16* O;
@@ -31,6 +32,12 @@ struct FlashFwdParams {
   int* status;
 };
 
+__device__ __forceinline__ float ex2_approx_f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 struct FaFwdCfg {
   static constexpr int kQBytes = kFaBlockQ * D * 2;
@@ -41,7 +48,11 @@ struct FaFwdCfg {
   static constexpr int kOffV = kOffK + 2 * kKVBytes;
   static constexpr int kOffP = kOffV + 2 * kKVBytes;
   static constexpr int kOffBar = kOffP + 2 * kPBytes;
-  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kOffX = kOffBar + 160;                 // row statistics exchanged between the two column halves
+  static constexpr int kNeeded = kOffX + 2 * 2 * 128 * 4;     // [parity][half][128] floats
+  // 1 KB of slack for the 1024-byte alignment where it fits under the 227 KB limit; the kernel checks at run time
+  // that the aligned layout lies inside the allocation and reports kStatusBadArgument otherwise.
+  static constexpr int kSmemBytes = (kNeeded + 1024 <= 232448) ? kNeeded + 1024 : 232448;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0;     // two S buffers of 128 columns
   static constexpr int kColO = 256;   // D columns
@@ -55,6 +66,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
+  if (int(smem - smem_raw) + Cfg::kNeeded > Cfg::kSmemBytes) {  // uniform for the whole grid
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, int(kStatusBadArgument));
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   const uint32_t bb = smem_u32(bars);
   // barrier map
@@ -67,7 +82,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto p_full = [&](int s) { return bb + 8u * (11 + s); };
   auto p_empty = [&](int s) { return bb + 8u * (13 + s); };
   const uint32_t o_full = bb + 8u * 15;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  const uint32_t x_bar = bb + 8u * 16;   // all softmax threads have published their partial row maximum
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+  float* xmax = reinterpret_cast<float*>(smem + Cfg::kOffX);  // [2 (rendezvous parity)][2 (half)][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,9 +107,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
       mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
-      mbar_init(s_full(s), 1); mbar_init(p_full(s), 128); mbar_init(p_empty(s), 1);
+      mbar_init(s_full(s), 1); mbar_init(p_full(s), kFaSoftmaxThreads); mbar_init(p_empty(s), 1);
     }
     mbar_init(o_full, 1);
+    mbar_init(x_bar, kFaSoftmaxThreads);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -182,7 +200,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;          // TMEM lanes this warp may touch
+    const int half = (warp - 2) >> 2;      // which 64 of the 128 score columns (and which half of O) it owns
     const int row = quarter * 32 + lane;
     const int q_idx = q0 + row;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
@@ -194,16 +213,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, mbar_wait(s_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
       tc_fence_after();
-      uint32_t r[4][32];
+      uint32_t r[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + s * 128 + c * 32, r[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + s * 128 + (2 * half + c) * 32, r[c]);
       tmem_ld_wait();
-      const int kv0 = j * kFaBlockKV;
+      const int kv0 = j * kFaBlockKV + half * 64;
       const int limit = p.causal ? min(q_idx + shift, p.Tk - 1) : (p.Tk - 1);  // last visible key
-      const bool need_mask = (kv0 + kFaBlockKV - 1 > limit);
+      const bool need_mask = (kv0 + 63 > limit);
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float v = __uint_as_float(r[c][i]);
@@ -211,6 +230,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           r[c][i] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
+      // combine the row maximum of the two column halves (bounded mbarrier rendezvous, parity j & 1)
+      xmax[(s * 2 + half) * 128 + row] = mx;
+      mbar_arrive(x_bar);
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar, uint32_t(j & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
+      if (!ok) break;
+      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + row]);
       const float m_blk = mx * p.scale_log2;
       float m_new = fmaxf(m_used, m_blk);
       if (j == 0) {
@@ -223,9 +248,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                                                  kStatusTimeoutTmemEmpty));
           if (!ok) break;
           tc_fence_after();
-          const float alpha = need ? exp2f(m_used - m_new) : 1.f;
+          const float alpha = need ? ex2_approx_f(m_used - m_new) : 1.f;
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
+          for (int c = half * (D / 32); c < (half + 1) * (D / 32); ++c) {
             uint32_t o[16];
             tmem_ld_32x16(tmem_base + lane_base + Cfg::kColO + c * 16, o);
             tmem_ld_wait();
@@ -240,10 +265,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float pv = exp2f(__uint_as_float(r[c][i]) * p.scale_log2 - m_used);
+          const float pv = ex2_approx_f(__uint_as_float(r[c][i]) * p.scale_log2 - m_used);
           sum += pv;
           r[c][i] = __float_as_uint(pv);
         }
@@ -251,9 +276,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // P buffer s is free once PV_{j-2} has been executed.
       ok = __all_sync(0xffffffffu, mbar_wait(p_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
       if (!ok) break;
-      uint8_t* prow = smem + Cfg::kOffP + s * Cfg::kPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+      uint8_t* prow = smem + Cfg::kOffP + s * Cfg::kPBytes + half * (128 * 128) + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           uint4 w;
@@ -261,10 +286,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           w.y = pack_bf16x2(__uint_as_float(r[c][u * 8 + 2]), __uint_as_float(r[c][u * 8 + 3]));
           w.z = pack_bf16x2(__uint_as_float(r[c][u * 8 + 4]), __uint_as_float(r[c][u * 8 + 5]));
           w.w = pack_bf16x2(__uint_as_float(r[c][u * 8 + 6]), __uint_as_float(r[c][u * 8 + 7]));
-          const int col16 = c * 4 + u;           // 16-byte unit within the 128 kv columns (0..15)
-          const int chunk = col16 >> 3;          // 64-column half
-          const int unit = (col16 & 7) ^ (row & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * (128 * 128) + unit * 16) = w;
+          const int unit = (c * 4 + u) ^ (row & 7);  // 16-byte unit inside this half's 128-byte row
+          *reinterpret_cast<uint4*>(prow + unit * 16) = w;
         }
       }
       fence_proxy_async();
@@ -275,11 +298,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
     }
     if (ok) {
+      // total row sum = sum of the two halves
+      float* xsum = xmax + (n_blocks & 1) * 256;   // the slot of the next rendezvous parity
+      xsum[half * 128 + row] = l;
+      mbar_arrive(x_bar);
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar, uint32_t(n_blocks & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
+      if (ok) l += xsum[(half ^ 1) * 128 + row];
+    }
+    if (ok) {
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
       if (n_blocks > 0) tc_fence_after();
       __nv_bfloat16* orow = p.O + (long long)b * p.so_b + (long long)q_idx * p.so_t + (long long)h * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t o[32];
         if (n_blocks > 0) {
           tmem_ld_32x32(tmem_base + lane_base + Cfg::kColO + c * 32, o);
@@ -300,7 +331,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (q_idx < p.Tq)
+      if (half == 0 && q_idx < p.Tq)
         p.lse[((long long)b * p.Hq + h) * p.Tq + q_idx] = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }

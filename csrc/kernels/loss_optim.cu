@@ -147,7 +147,35 @@ __global__ void adam_flat_kernel(float* __restrict__ master, const GradT* __rest
     if (dyn[1] != 0.f) return;
     gmul = dyn[0];
   }
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+  // 4 elements per thread per step (16-byte accesses of the fp32 arrays), scalar tail
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float g[4];
+    if (sizeof(GradT) == 2) {
+      const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(grad) + i * 4);
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+      g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
+    } else {
+      const float4 u = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grad) + i * 4);
+      g[0] = u.x; g[1] = u.y; g[2] = u.z; g[3] = u.w;
+    }
+    float4 p4 = *reinterpret_cast<const float4*>(master + i * 4);
+    float4 m4 = *reinterpret_cast<const float4*>(m + i * 4);
+    float4 v4 = *reinterpret_cast<const float4*>(v + i * 4);
+    float pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pp[j] = adam_update(pp[j], g[j] * gmul, mm[j], vv[j], a);
+    *reinterpret_cast<float4*>(master + i * 4) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    *reinterpret_cast<float4*>(m + i * 4) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i * 4) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (param_bf16) {
+      uint2 o;
+      o.x = pack_bf16x2(pp[0], pp[1]);
+      o.y = pack_bf16x2(pp[2], pp[3]);
+      *reinterpret_cast<uint2*>(param_bf16 + i * 4) = o;
+    }
+  }
+  for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float g;
     if (sizeof(GradT) == 2) g = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i]);
     else g = reinterpret_cast<const float*>(grad)[i];

@@ -182,13 +182,20 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-// out[c] (+)= sum_p part[p, c]; out is bf16 or fp32.
+// out[c] (+)= sum_p part[p, c]; out is bf16 or fp32.  A block owns 32 columns; its 8 warps split the partial rows.
 __global__ void fold_partials_kernel(const float* __restrict__ part, void* __restrict__ out, int P, int D,
                                      int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += part[(long long)p * D + c];
+  if (c < D)
+    for (int p = w; p < P; p += 8) s += part[(long long)p * D + c];
+  red[w][lane] = s;
+  __syncthreads();
+  if (w != 0 || c >= D) return;
+#pragma unroll
+  for (int i = 1; i < 8; ++i) s += red[i][lane];
   if (out_fp32) {
     float* o = static_cast<float*>(out);
     o[c] = accumulate ? o[c] + s : s;
@@ -204,7 +211,7 @@ extern "C" {
 
 // Number of CTAs the backward uses; the caller sizes the partial buffers [ctas, D] fp32 with it.
 int lt_norm_bwd_ctas(int M) {
-  const int cap = lt::sm_count() * 4;
+  const int cap = lt::sm_count() * 2;
   return M < cap ? M : cap;
 }
 
@@ -253,7 +260,7 @@ int lt_norm_bwd(int layer_norm, const void* dy, const void* x, const void* w, co
   }
 #undef LT_NORM_BWD
   LT_LAUNCH_CHECK();
-  const int fb = (D + 255) / 256;
+  const int fb = (D + 31) / 32;
   fold_partials_kernel<<<fb, 256, 0, st>>>(dw_part, dw, grid, D, grads_fp32, accumulate);
   if (layer_norm && db && db_part) fold_partials_kernel<<<fb, 256, 0, st>>>(db_part, db, grid, D, grads_fp32, accumulate);
   LT_LAUNCH_CHECK();
@@ -318,7 +325,7 @@ extern "C" int lt_norm_bwd_noalloc(int layer_norm, const void* dy, const void* x
   }
 #undef LT_NORM_BWD_NA
   LT_LAUNCH_CHECK();
-  const int fb = (D + 255) / 256;
+  const int fb = (D + 31) / 32;
   fold_partials_kernel<<<fb, 256, 0, st>>>(dw_part, dw, grid, D, grads_fp32, accumulate);
   if (layer_norm && db) fold_partials_kernel<<<fb, 256, 0, st>>>(db_part, db, grid, D, grads_fp32, accumulate);
   LT_LAUNCH_CHECK();

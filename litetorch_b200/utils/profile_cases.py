@@ -1,0 +1,66 @@
+"""Small, self-terminating workloads for `ncu` captures of one kernel each.
+
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adamw|ce [reps]
+
+Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
+handful of times and exits, so a capture with `-k regex:<kernel> -c 3` ends by itself in a minute or two.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def main():
+    from ..ops import kernels as K
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
+    dev = "cuda"
+    torch.manual_seed(0)
+    if case == "gemm":            # gate_up forward of the 1.1B model: 8192 x 11264 x 2048
+        a = torch.randn(8192, 2048, device=dev).bfloat16()
+        b = torch.randn(11264, 2048, device=dev).bfloat16()
+        c = torch.empty(8192, 11264, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gemm(a, b, out=c)
+    elif case == "gemm_wgrad":    # down-projection weight gradient: 2048 x 5632 x 8192, both operands transposed
+        a = torch.randn(8192, 2048, device=dev).bfloat16()
+        b = torch.randn(8192, 5632, device=dev).bfloat16()
+        c = torch.empty(2048, 5632, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gemm(a, b, a_major=1, b_major=1, out=c)
+    elif case in ("flash_fwd", "flash_bwd"):
+        B, T, Hq, Hkv, D = 4, 2048, 32, 4, 64
+        q = torch.randn(B, T, Hq, D, device=dev).bfloat16()
+        k = torch.randn(B, T, Hkv, D, device=dev).bfloat16()
+        v = torch.randn(B, T, Hkv, D, device=dev).bfloat16()
+        do = torch.randn(B, T, Hq, D, device=dev).bfloat16()
+        o, lse = K.flash_fwd(q, k, v, causal=True)
+        fn = (lambda: K.flash_fwd(q, k, v, causal=True)) if case == "flash_fwd" else (lambda: K.flash_bwd(q, k, v, o, lse, do, causal=True))
+    elif case == "rmsnorm":
+        x = torch.randn(65536, 2048, device=dev).bfloat16()
+        w = torch.ones(2048, device=dev).bfloat16()
+        fn = lambda: K.norm_fwd(x, w, None, x)
+    elif case == "swiglu":
+        gu = torch.randn(16384, 11264, device=dev).bfloat16()
+        fn = lambda: K.swiglu_fwd(gu)
+    elif case == "adamw":
+        n = 1 << 26
+        p, m, v = torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        g = torch.randn(n, device=dev).bfloat16()
+        p16 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.adam_flat(p, g, m, v, p16, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, step=1)
+    elif case == "ce":
+        logits = torch.randn(8192, 32000, device=dev).bfloat16()
+        tgt = torch.randint(0, 32000, (8192,), device=dev)
+        fn = lambda: K.ce_finish(logits, tgt, K.ce_stats(logits, tgt))
+    else:
+        raise SystemExit("unknown case " + case)
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    K.check_status()
+    print("ok", case)
+
+
+if __name__ == "__main__":
+    main()
