@@ -46,6 +46,10 @@ struct GemmParams {
   int raster, rot;
   int k_rot;  // the K loop starts at k-block k_rot and wraps around
   int* status;
+  // Scatter mode (GEMM -> reduce-scatter): when rows_per_rank > 0 the tile rows are not written to C but to the
+  // staging buffer of the rank that owns them, peer_C[owner] + (src_rank * rows_per_rank + local_row) * ldc.
+  void* peer_C[8];
+  int rows_per_rank, src_rank;
 };
 
 template <int BLOCK_N>
@@ -63,7 +67,8 @@ struct NoGate {
   __device__ __forceinline__ bool operator()(int, int, int, int*) const { return true; }
 };
 struct NoDone {
-  __device__ __forceinline__ void operator()(int, int) const {}
+  __device__ __forceinline__ void fence() const {}                 // every epilogue lane, after its stores
+  __device__ __forceinline__ void operator()(int, int) const {}    // one lane per epilogue warp, after the fence
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
@@ -130,8 +135,14 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
       _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(rp[j]);
     }
   }
+  void* c_base = p.C;
+  if (p.rows_per_rank > 0) {
+    const int owner = row / p.rows_per_rank;
+    c_base = p.peer_C[owner];
+    row = p.src_rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
+  }
   if (p.out_fp32) {
-    float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+    float* cp = reinterpret_cast<float*>(c_base) + (long long)row * p.ldc + col0;
     if (full && (p.ldc % 4 == 0)) {
       float4* c4 = reinterpret_cast<float4*>(cp);
 #pragma unroll
@@ -147,7 +158,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
       _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) cp[j] = p.accumulate ? cp[j] + v[j] : v[j];
     }
   } else {
-    __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+    __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(c_base) + (long long)row * p.ldc + col0;
     if (full && (p.ldc % 8 == 0)) {
       uint4* c4 = reinterpret_cast<uint4*>(cp);
 #pragma unroll
@@ -322,6 +333,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
         const int col0 = n_blk * BLOCK_N + c * 32;
         if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
       }
+      done.fence();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {

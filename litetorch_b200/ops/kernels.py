@@ -48,6 +48,7 @@ _SIGS = {
     "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
     "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
     "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
+    "lt_gemm_rs_bf16": [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp, ctypes.c_uint, _i, _i, _i, _vp, _ll, _vp, _vp, _ll, _vp],
     "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
     "lt_flash_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
@@ -425,3 +426,19 @@ def kv_append(k_new, v_new, k_cache, v_cache, slots, block_size: int, fp8: bool,
     rc = _fn("lt_kv_append")(k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slots.data_ptr(), N, Hkv, D,
                              block_size, 1 if fp8 else 0, float(k_scale), float(v_scale), _stream())
     _check(rc, "lt_kv_append")
+
+
+def gemm_rs(a, b, *, b_major: int, stage_ptrs, counter_ptrs, epoch: int, world: int, rank: int, out=None, bias=None, residual=None):
+    """out[M/world, N] = reduce-scatter over ranks of (a[M, K_local] @ op(b)), fused into the GEMM epilogue.
+    b_major 0: b is [N, K_local]; 1: b is [K_local, N]."""
+    M, Kd = a.shape
+    N = b.shape[0] if b_major == 0 else b.shape[1]
+    rpr = M // world
+    if out is None:
+        out = torch.empty((rpr, N), dtype=torch.bfloat16, device=a.device)
+    rc = _fn("lt_gemm_rs_bf16")(a.data_ptr(), b.data_ptr(), M, N, Kd, a.stride(0), b.stride(0), b_major,
+                                ctypes.cast(_ptr_array(stage_ptrs), c_void_p), ctypes.cast(_ptr_array(counter_ptrs), c_void_p),
+                                epoch, world, rank, rpr, out.data_ptr(), out.stride(0), _p(bias), _p(residual),
+                                residual.stride(0) if residual is not None else 0, _stream())
+    _check(rc, "lt_gemm_rs_bf16")
+    return out
