@@ -35,6 +35,23 @@ struct GatherArgs {
   int n_comm;                             // number of gather CTAs (blockIdx.x < n_comm)
 };
 
+// What the gather CTAs fetch once their own operand is complete: the gathered operand of the NEXT GEMM of the
+// layer sequence, into that GEMM's staging buffer and flags.  They stop when this kernel's tiles are done
+// (`progress` reaches `progress_target`), and the next kernel's gather CTAs skip the chunks that already landed.
+struct PrefetchArgs {
+  GatherArgs next;                        // next.n_chunks == 0: nothing to prefetch
+  uint32_t* progress;                     // tile-warp completions of the running kernel (monotonic counter)
+  uint32_t progress_target;
+};
+
+struct ProgressDone {
+  uint32_t* progress;
+  __device__ __forceinline__ void fence() const {}
+  __device__ __forceinline__ void operator()(int, int) const {
+    if (progress) red_add_release_gpu(progress, 1u);
+  }
+};
+
 struct FlagGate {
   const uint32_t* flags;
   uint32_t epoch;
@@ -62,7 +79,8 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t smem_src, uint32_t
 }
 
 // One thread of a gather CTA runs the whole copy pipeline.
-__device__ void gather_cta(const GatherArgs& g, int* status) {
+__device__ void gather_cta(const GatherArgs& g_own, const PrefetchArgs& pf, int* status) {
+  const GatherArgs& g = g_own;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -78,15 +96,22 @@ __device__ void gather_cta(const GatherArgs& g, int* status) {
   __syncthreads();
   if (threadIdx.x != 0) return;
   volatile int* abort_flag = &abort_flag_s;
-  const long long row_bytes = (long long)g.cols * 2;
-  int max_rows = int(kGatherStageBytes / row_bytes);
-  if (max_rows < 1) max_rows = 1;  // rows wider than a stage are split by columns below
   uint32_t use[kGatherStages];
   for (int s = 0; s < kGatherStages; ++s) use[s] = 0;
 
-  for (int o = blockIdx.x; o < g.n_chunks; o += g.n_comm) {
+  const int n_own = g.n_chunks;
+  const int n_all = n_own + pf.next.n_chunks;
+  for (int oo = blockIdx.x; oo < n_all; oo += g.n_comm) {
+    const bool own = oo < n_own;
+    const GatherArgs& g = own ? g_own : pf.next;
+    const int o = own ? oo : oo - n_own;
+    const long long row_bytes = (long long)g.cols * 2;
+    int max_rows = int(kGatherStageBytes / row_bytes);
+    if (max_rows < 1) max_rows = 1;  // rows wider than a stage are split by columns below
+    if (!own && ld_acquire_gpu(pf.progress) >= pf.progress_target) return;   // the GEMM is done: leave the rest
     int c = o + g.chunk_rot;
     if (c >= g.n_chunks) c -= g.n_chunks;
+    if (ld_acquire_gpu(g.flags + c) == g.epoch) continue;                     // already landed (prefetched earlier)
     const int r0 = c * g.chunk_rows;
     const int r1 = min(r0 + g.chunk_rows, g.rows_total);
     // Segment walker: contiguous pieces that stay inside one owner and one stage.
@@ -153,14 +178,14 @@ __device__ void gather_cta(const GatherArgs& g, int* status) {
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-               const GatherArgs g) {
+               const GatherArgs g, const PrefetchArgs pf) {
   if (int(blockIdx.x) < g.n_comm) {
-    gather_cta(g, p.status);
+    gather_cta(g, pf, p.status);
     return;
   }
   // GEMM CTAs see a grid that starts at n_comm.
   FlagGate gate{g.flags, g.epoch, g.gate_dim, -1};
-  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, gate, NoDone(), g.n_comm);
+  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, gate, ProgressDone{pf.progress}, g.n_comm);
 }
 
 // ---------------------------------------------------------------------------------------------- RS + AdamW
@@ -294,8 +319,8 @@ __global__ void signal_barrier_kernel(const BarrierArgs a) {
 }
 
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
-static int launch_ag_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const GatherArgs& g, int grid,
-                          cudaStream_t st) {
+static int launch_ag_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const GatherArgs& g,
+                          const PrefetchArgs& pf, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
   static bool configured = false;
   auto kern = ag_gemm_kernel<BLOCK_N, A_MAJOR, B_MAJOR>;
@@ -303,14 +328,41 @@ static int launch_ag_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
     LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmA, tmB, p, g);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmA, tmB, p, g, pf);
   LT_LAUNCH_CHECK();
   return 0;
 }
 
 }  // namespace lt
 
+namespace lt {
+// Chunking of a gathered operand for a GEMM of shape (M, N, K) with tile width block_n.
+static void setup_gather(GatherArgs& g, int gather_operand, int M, int N, int K, int block_n, int rank, int rows_per_rank,
+                         int& rot_out) {
+  const int m_blocks = (M + kBlockM - 1) / kBlockM, n_blocks = (N + block_n - 1) / block_n, k_blocks = (K + kBlockK - 1) / kBlockK;
+  const int first_row = rank * rows_per_rank;
+  if (gather_operand == 0) {
+    g.rows_total = M; g.cols = K; g.chunk_rows = kBlockM; g.gate_dim = 2; g.n_chunks = m_blocks;
+  } else if (gather_operand == 1) {
+    g.rows_total = N; g.cols = K; g.chunk_rows = block_n; g.gate_dim = 0; g.n_chunks = n_blocks;
+  } else {
+    g.rows_total = K; g.cols = N; g.chunk_rows = kBlockK; g.gate_dim = 1; g.n_chunks = k_blocks;
+  }
+  g.chunk_rot = (first_row / g.chunk_rows) % g.n_chunks;
+  rot_out = g.chunk_rot;
+}
+}  // namespace lt
+
 extern "C" {
+
+// Description of the next gather-GEMM of the sequence, for prefetching (all fields as in lt_ag_gemm_bf16).
+struct LtNextGather {
+  int gather_operand, M, N, K, rows_per_rank, pad;
+  const void* shard_ptrs[8];
+  void* full;
+  void* flags;
+  unsigned epoch, pad2;
+};
 
 // GEMM whose gathered operand is assembled from `world` row shards while the kernel runs.
 //   gather_operand: 0 = A (stored [M, K], rows sharded, tiles gated by M block),
@@ -323,7 +375,8 @@ extern "C" {
 int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                     int a_major, int b_major, int out_fp32, const void* bias, const void* residual, long long ldr, int act,
                     int accumulate, float alpha, int gather_operand, const void* const* shard_ptrs, int world, int rank,
-                    int rows_per_rank, void* full, void* flags, unsigned epoch, int n_comm, void* stream) {
+                    int rows_per_rank, void* full, void* flags, unsigned epoch, int n_comm, const LtNextGather* next,
+                    void* progress, unsigned progress_base, void* stream) {
   using namespace lt;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (world < 1 || world > kMaxRanks) return -int(kStatusBadArgument);
@@ -349,19 +402,25 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   g.world = world; g.rank = rank;
   g.rows_per_rank = rows_per_rank;
   g.n_comm = n_comm;
-  const int first_row = rank * rows_per_rank;
-  if (gather_operand == 0) {
-    g.rows_total = M; g.cols = K; g.chunk_rows = kBlockM; g.gate_dim = 2;
-    g.n_chunks = p.m_blocks; g.chunk_rot = (first_row / kBlockM) % p.m_blocks;
-    p.raster = 2; p.rot = g.chunk_rot;
-  } else if (gather_operand == 1) {
-    g.rows_total = N; g.cols = K; g.chunk_rows = block_n; g.gate_dim = 0;
-    g.n_chunks = p.n_blocks; g.chunk_rot = (first_row / block_n) % p.n_blocks;
-    p.raster = 1; p.rot = g.chunk_rot;
-  } else {
-    g.rows_total = K; g.cols = N; g.chunk_rows = kBlockK; g.gate_dim = 1;
-    g.n_chunks = p.k_blocks; g.chunk_rot = (first_row / kBlockK) % p.k_blocks;
-    p.k_rot = g.chunk_rot;
+  int rot = 0;
+  setup_gather(g, gather_operand, M, N, K, block_n, rank, rows_per_rank, rot);
+  if (gather_operand == 0) { p.raster = 2; p.rot = rot; }
+  else if (gather_operand == 1) { p.raster = 1; p.rot = rot; }
+  else { p.k_rot = rot; }
+  PrefetchArgs pf{};
+  pf.progress = static_cast<uint32_t*>(progress);
+  pf.progress_target = progress_base + uint32_t(p.num_tiles) * 4u;
+  if (next && progress && next->M > 0) {
+    GatherArgs& n = pf.next;
+    for (int r = 0; r < world; ++r) n.shard[r] = static_cast<const __nv_bfloat16*>(next->shard_ptrs[r]);
+    n.full = static_cast<__nv_bfloat16*>(next->full);
+    n.flags = static_cast<uint32_t*>(next->flags);
+    n.epoch = next->epoch;
+    n.world = world; n.rank = rank; n.rows_per_rank = next->rows_per_rank; n.n_comm = n_comm;
+    int nrot = 0;
+    setup_gather(n, next->gather_operand, next->M, next->N, next->K, pick_block_n(next->M, next->N, sms - n_comm), rank,
+                 next->rows_per_rank, nrot);
+    if ((long long)n.cols * 2 % 16 != 0) n.n_chunks = 0;
   }
   if ((long long)g.cols * 2 % 16 != 0) return -int(kStatusBadArgument);
   CUtensorMap tmA, tmB;
@@ -372,12 +431,18 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int key = (block_n == 256 ? 4 : 0) | (a_major ? 2 : 0) | (b_major ? 1 : 0);
   switch (key) {
-    case 0: return launch_ag_gemm<128, 0, 0>(tmA, tmB, p, g, grid, st);
-    case 1: return launch_ag_gemm<128, 0, 1>(tmA, tmB, p, g, grid, st);
-    case 4: return launch_ag_gemm<256, 0, 0>(tmA, tmB, p, g, grid, st);
-    case 5: return launch_ag_gemm<256, 0, 1>(tmA, tmB, p, g, grid, st);
+    case 0: return launch_ag_gemm<128, 0, 0>(tmA, tmB, p, g, pf, grid, st);
+    case 1: return launch_ag_gemm<128, 0, 1>(tmA, tmB, p, g, pf, grid, st);
+    case 4: return launch_ag_gemm<256, 0, 0>(tmA, tmB, p, g, pf, grid, st);
+    case 5: return launch_ag_gemm<256, 0, 1>(tmA, tmB, p, g, pf, grid, st);
     default: return -int(kStatusBadArgument);
   }
+}
+
+int lt_gemm_num_tiles(int M, int N, int n_comm) {
+  using namespace lt;
+  const int bn = pick_block_n(M, N, sm_count() - n_comm);
+  return ((M + kBlockM - 1) / kBlockM) * ((N + bn - 1) / bn);
 }
 
 // segs: n_seg triples (full_off, shard_off, n) in elements, n a multiple of 8.

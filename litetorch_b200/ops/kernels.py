@@ -42,10 +42,11 @@ _SIGS = {
     "lt_sumsq": [_vp, _i, _ll, _vp, _vp],
     "lt_clip_coef": [_vp, _vp, _f, _f, _vp],
     "lt_ag_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f,
-                        _i, _vp, _i, _i, _i, _vp, _vp, ctypes.c_uint, _i, _vp],
+                        _i, _vp, _i, _i, _i, _vp, _vp, ctypes.c_uint, _i, _vp, _vp, ctypes.c_uint, _vp],
     "lt_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _i, ctypes.c_uint, _i, _i, _i, _vp],
     "lt_embedding_fwd_sharded": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
+    "lt_gemm_num_tiles": [_i, _i, _i],
     "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
     "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
     "lt_gemm_rs_bf16": [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp, ctypes.c_uint, _i, _i, _i, _vp, _ll, _vp, _vp, _ll, _vp],
@@ -57,7 +58,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -346,9 +347,25 @@ def _ptr_array(ptrs):
     return arr
 
 
+class NextGather(ctypes.Structure):
+    """The next gather-GEMM of the layer sequence, prefetched by the gather CTAs of the current one."""
+    _fields_ = [("gather_operand", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("rows_per_rank", c_int), ("pad", c_int),
+                ("shard_ptrs", c_void_p * 8), ("full", c_void_p), ("flags", c_void_p), ("epoch", ctypes.c_uint), ("pad2", ctypes.c_uint)]
+
+
+def make_next_gather(gather_operand, M, N, Kd, rows_per_rank, shard_ptrs, full, flags, epoch) -> NextGather:
+    ng = NextGather()
+    ng.gather_operand, ng.M, ng.N, ng.K, ng.rows_per_rank = gather_operand, M, N, Kd, rows_per_rank
+    for i, p in enumerate(shard_ptrs):
+        ng.shard_ptrs[i] = int(p)
+    ng.full, ng.flags, ng.epoch = full.data_ptr(), flags.data_ptr(), epoch
+    return ng
+
+
 def ag_gemm(a, b_full_or_a_full, *, gather_operand: int, shard_ptrs, world: int, rank: int, rows_per_rank: int,
             flags: torch.Tensor, epoch: int, other: torch.Tensor, out=None, out_dtype=torch.bfloat16, bias=None,
-            residual=None, act: int = 0, accumulate: bool = False, alpha: float = 1.0, n_comm: int = 0):
+            residual=None, act: int = 0, accumulate: bool = False, alpha: float = 1.0, n_comm: int = 0,
+            next_gather: "NextGather | None" = None, progress: "torch.Tensor | None" = None, progress_base: int = 0):
     """GEMM whose gathered operand is pulled from the ranks' shards by gather CTAs of the same kernel.
 
     gather_operand 1: C = other[M,K] @ full[N,K]^T      (full = weight gathered by rows, tiles gated by N block)
@@ -376,7 +393,9 @@ def ag_gemm(a, b_full_or_a_full, *, gather_operand: int, shard_ptrs, world: int,
                                 a_major, b_major, 1 if out.dtype == torch.float32 else 0, _p(bias), _p(residual),
                                 residual.stride(0) if residual is not None else 0, act, 1 if accumulate else 0, float(alpha),
                                 gather_operand, ctypes.cast(arr, c_void_p), world, rank, rows_per_rank, full.data_ptr(),
-                                flags.data_ptr(), epoch, n_comm, _stream())
+                                flags.data_ptr(), epoch, n_comm,
+                                ctypes.cast(ctypes.pointer(next_gather), c_void_p) if next_gather is not None else None,
+                                _p(progress), progress_base, _stream())
     _check(rc, "lt_ag_gemm_bf16")
     return out
 
@@ -442,3 +461,8 @@ def gemm_rs(a, b, *, b_major: int, stage_ptrs, counter_ptrs, epoch: int, world: 
                                 residual.stride(0) if residual is not None else 0, _stream())
     _check(rc, "lt_gemm_rs_bf16")
     return out
+
+
+def gemm_num_tiles(M: int, N: int, n_comm: int = 0) -> int:
+    """Output tiles the GEMM launcher will use for an M x N result when `n_comm` SMs are set aside."""
+    return _fn("lt_gemm_num_tiles")(M, N, n_comm)

@@ -71,7 +71,7 @@ class ShardedWeights:
         self.device = torch.device(device)
         self.world = dist.get_world_size()
         self.rank = dist.get_rank()
-        self.n_comm = n_comm
+        self.n_comm = int(os.environ.get("LT_FSDP_GATHER_CTAS", n_comm))
         W = self.world
         self.specs = param_specs(cfg)
         self.by_name = {s.name: s for s in self.specs}
@@ -134,6 +134,10 @@ class ShardedWeights:
         self.flag_epoch = [0] * self.n_slots
         self.hyper = None
         self._pending = False
+        self._trace, self._trace_done, self._trace_pos = [], False, 0
+        self._progress = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._progress_total = 0
+        self.prefetch = os.environ.get("LT_FSDP_PREFETCH", "1") != "0"
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -164,13 +168,40 @@ class ShardedWeights:
 
     # ------------------------------------------------------------------ GEMM providers
     def _gather_gemm(self, other, name, gather_operand, **kw):
+        """One gather-GEMM.  The order of these calls is recorded during the first step; afterwards every call also
+        tells its gather CTAs which operand the NEXT call needs, so that it is prefetched while this GEMM computes."""
         key = self._stage_key(name)
         rows, cols = self.by_name[name].shape
         self.stage_epoch[key] += 1
-        return K.ag_gemm(None, self.stage[key], gather_operand=gather_operand,
-                         shard_ptrs=self.sym_param.peer_ptrs(self.shard_off[name]), world=self.world, rank=self.rank,
-                         rows_per_rank=rows // self.world, flags=self.stage_flags[key], epoch=self.stage_epoch[key],
-                         other=other, n_comm=self.n_comm, **kw)
+        M = other.shape[0]
+        nxt = None
+        if self._trace_done and not (self._trace_pos < len(self._trace) and self._trace[self._trace_pos] == (name, gather_operand)):
+            # the call order changed (e.g. an evaluation pass): drop the schedule and void anything prefetched for it
+            self._trace_done, self._trace, self._trace_pos = False, [], 0
+            for k in self.stage_epoch:
+                self.stage_epoch[k] += 2
+        if self._trace_done:
+            i = self._trace_pos
+            if i + 1 < len(self._trace):
+                n_name, n_op = self._trace[i + 1]
+                n_key = self._stage_key(n_name)
+                if n_key != key:
+                    n_rows, n_cols = self.by_name[n_name].shape
+                    nN, nK = (n_rows, n_cols) if n_op == 1 else (n_cols, n_rows)
+                    nxt = K.make_next_gather(n_op, M, nN, nK, n_rows // self.world,
+                                             self.sym_param.peer_ptrs(self.shard_off[n_name]), self.stage[n_key],
+                                             self.stage_flags[n_key], self.stage_epoch[n_key] + 1)
+            self._trace_pos += 1
+        else:
+            self._trace.append((name, gather_operand))
+        N = rows if gather_operand == 1 else cols
+        base = self._progress_total
+        out = K.ag_gemm(None, self.stage[key], gather_operand=gather_operand,
+                        shard_ptrs=self.sym_param.peer_ptrs(self.shard_off[name]), world=self.world, rank=self.rank,
+                        rows_per_rank=rows // self.world, flags=self.stage_flags[key], epoch=self.stage_epoch[key],
+                        other=other, n_comm=self.n_comm, next_gather=nxt, progress=self._progress, progress_base=base, **kw)
+        self._progress_total = (base + 4 * K.gemm_num_tiles(M, N, self.n_comm)) & 0xFFFFFFFF
+        return out
 
     def linear(self, x, name, **kw):
         return self._gather_gemm(x, name, 1, **kw)
@@ -253,6 +284,11 @@ class ShardedWeights:
         self.flag_epoch[self.SLOT_BARRIER] += 1
         K.signal_barrier(self.sym_flags.tensor, self.sym_flags.ptrs, self.SLOT_BARRIER, self.flag_epoch[self.SLOT_BARRIER],
                          self.world, self.rank)
+        if self.hyper is not None and self.prefetch:
+            self._trace_done = True          # one complete fused step has been seen: its call order is the schedule
+        self._trace_pos = 0
+        if not self._trace_done:
+            self._trace = []
         self.hyper = None
 
     # ------------------------------------------------------------------ whole-model access (checkpoints, tests)

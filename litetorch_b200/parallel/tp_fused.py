@@ -140,7 +140,7 @@ def _ag_gemm_nn(tp, full, w, slot, rows):
     arr = K._ptr_array(tp.shard[slot].ptrs)
     rc = K._fn("lt_ag_gemm_bf16")(full.data_ptr(), w.data_ptr(), out.data_ptr(), M, Kin, N, full.stride(0), w.stride(0), out.stride(0),
                                   0, 1, 0, None, None, 0, 0, 0, 1.0, 0, ctypes.cast(arr, c_void_p), tp.world, tp.rank, rows,
-                                  full.data_ptr(), tp.gather_flags.data_ptr(), tp.ag_calls, tp.n_comm, K._stream())
+                                  full.data_ptr(), tp.gather_flags.data_ptr(), tp.ag_calls, tp.n_comm, None, None, 0, K._stream())
     K._check(rc, "lt_ag_gemm_bf16")
     return out
 
