@@ -22,10 +22,14 @@ constexpr int kFbBlock = 128;
 constexpr int kFbThreads = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2-9 compute (two per TMEM lane quarter)
 constexpr int kFbComputeThreads = 256;
 
+constexpr int kFbMaxRanks = 8;
 struct FlashBwdParams {
-  const float* lse;    // [B, Hq, Tq] natural log
-  const float* delta;  // [B, Hq, Tq]
-  float* dq_acc;       // [B, Tq, Hq, D] fp32, zero-initialised
+  // Per query-owning rank (index 0 only without context parallelism); peer-mapped pointers under CP:
+  const float* lse[kFbMaxRanks];    // [B, Hq, Tq] natural log
+  const float* delta[kFbMaxRanks];  // [B, Hq, Tq]
+  float* dq_acc[kFbMaxRanks];       // [B, Tq, Hq, D] fp32, zero-initialised; remote ranks receive red.add over NVLink
+  // Context parallelism: this rank's keys meet the queries of every rank; dK/dV stay local, dQ goes to its owner.
+  int cp_world, cp_rank, zigzag;
   __nv_bfloat16* dK;
   __nv_bfloat16* dV;   // [B, Tk, Hkv, D] with strides sdk_b / sdk_t
   long long sdk_b, sdk_t;
@@ -34,6 +38,15 @@ struct FlashBwdParams {
   int causal;
   int* status;
 };
+
+struct QMaps {
+  CUtensorMap q[kFbMaxRanks];
+  CUtensorMap d_o[kFbMaxRanks];
+};
+struct QSeg {
+  int n, owner, q0, qbase;   // a run of consecutive visible query blocks of one rank
+};
+constexpr int kFbMaxSegs = 2 * kFbMaxRanks;
 
 template <int D>
 struct FaBwdCfg {
@@ -47,7 +60,8 @@ struct FaBwdCfg {
   static constexpr int kOffP = kOffDO + kStages * kTile;
   static constexpr int kOffDS = kOffP + kPTile;
   static constexpr int kOffBar = kOffDS + kPTile;
-  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kOffSeg = kOffBar + 128;
+  static constexpr int kSmemBytes = kOffSeg + kFbMaxSegs * 16 + 16 + 1024;
   static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
   static constexpr int kColDQ = (D == 64) ? 384 : 0;  // aliases S when D == 128
   static constexpr bool kDqAliasesS = (D != 64);
@@ -110,9 +124,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 
 template <int D>
 __global__ void __launch_bounds__(kFbThreads, 1)
-flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                 const FlashBwdParams p) {
+flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashBwdParams p) {
   using Cfg = FaBwdCfg<D>;
   constexpr int ST = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -137,15 +150,61 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int G = p.Hq / p.Hkv;
   const int kv0 = kv_blk * kFbBlock;
-  const int shift = p.Tk - p.Tq;
-  const int n_q_blocks = (p.Tq + kFbBlock - 1) / kFbBlock;
-  int i_min = 0;
-  if (p.causal) {
-    const int first_q = kv0 - shift;  // first query that sees key kv0
-    i_min = first_q <= 0 ? 0 : first_q / kFbBlock;
+  QSeg* segs = reinterpret_cast<QSeg*>(smem + Cfg::kOffSeg);
+  int* per_head_s = reinterpret_cast<int*>(smem + Cfg::kOffSeg + kFbMaxSegs * 16);
+  // global position of this block's first key
+  int k_base;
+  if (p.cp_world == 1) {
+    k_base = kv0 - (p.Tk - p.Tq);   // expressed on the query axis: query i sees key j iff j - (Tk - Tq) <= i
+  } else if (p.zigzag) {
+    const int hk = p.Tk / 2;
+    k_base = kv0 < hk ? p.cp_rank * hk + kv0 : (2 * p.cp_world - 1 - p.cp_rank) * hk + (kv0 - hk);
+  } else {
+    k_base = p.cp_rank * p.Tk + kv0;
   }
-  const int per_head = n_q_blocks > i_min ? n_q_blocks - i_min : 0;
+  if (threadIdx.x == 0) {
+    // query blocks that see these keys, as runs per owning rank (own rank first)
+    int ns = 0, total = 0;
+    for (int i = 0; i < p.cp_world; ++i) {
+      const int o = (p.cp_rank + i) % p.cp_world;
+      const int parts = (p.cp_world > 1 && p.zigzag) ? 2 : 1;
+      for (int h2 = 0; h2 < parts; ++h2) {
+        int q0s, qbase, nb;
+        if (parts == 2) {
+          const int hq = p.Tq / 2;
+          q0s = h2 * hq;
+          qbase = h2 == 0 ? o * hq : (2 * p.cp_world - 1 - o) * hq;
+          nb = hq / kFbBlock;
+        } else {
+          q0s = 0;
+          qbase = p.cp_world > 1 ? o * p.Tq : 0;
+          nb = (p.Tq + kFbBlock - 1) / kFbBlock;
+        }
+        int skip = 0;
+        if (p.causal) {
+          const int first_q = k_base - qbase;   // first query position (relative to the run) that sees key k_base
+          skip = first_q <= 0 ? 0 : first_q / kFbBlock;
+        }
+        if (nb > skip) {
+          segs[ns] = QSeg{nb - skip, o, q0s + skip * kFbBlock, qbase + skip * kFbBlock};
+          ++ns;
+          total += nb - skip;
+        }
+      }
+    }
+    for (int i = ns; i < kFbMaxSegs; ++i) segs[i] = QSeg{0, 0, 0, 0};
+    *per_head_s = total;
+  }
+  __syncthreads();
+  const int per_head = *per_head_s;
   const int n_iter = per_head * G;
+  auto locate = [&](int j, int& owner, int& q0, int& qbase) {
+    int sidx = 0;
+    while (sidx < kFbMaxSegs - 1 && j >= segs[sidx].n) { j -= segs[sidx].n; ++sidx; }
+    owner = segs[sidx].owner;
+    q0 = segs[sidx].q0 + j * kFbBlock;
+    qbase = segs[sidx].qbase + j * kFbBlock;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -157,7 +216,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&qm.q[p.cp_rank]); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&qm.d_o[p.cp_rank]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), 512);
@@ -181,13 +240,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int s = it % ST;
         const uint32_t par = (it / ST) & 1;
         const int h = hkv * G + it / per_head;
-        const int q0 = (i_min + it % per_head) * kFbBlock;
+        int owner, q0, qbase;
+        locate(it % per_head, owner, q0, qbase);
         if (!mbar_wait(qdo_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
         mbar_expect_tx(qdo_full(s), 2 * Cfg::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(sbase + Cfg::kOffQ + s * Cfg::kTile + c * (kFbBlock * 128), &tmQ, qdo_full(s), c * 64, h, q0, b);
-          tma_load_4d(sbase + Cfg::kOffDO + s * Cfg::kTile + c * (kFbBlock * 128), &tmDO, qdo_full(s), c * 64, h, q0, b);
+          tma_load_4d(sbase + Cfg::kOffQ + s * Cfg::kTile + c * (kFbBlock * 128), &qm.q[owner], qdo_full(s), c * 64, h, q0, b);
+          tma_load_4d(sbase + Cfg::kOffDO + s * Cfg::kTile + c * (kFbBlock * 128), &qm.d_o[owner], qdo_full(s), c * 64, h, q0, b);
         }
       }
     }
@@ -267,16 +327,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_iter; ++it) {
       const uint32_t ipar = it & 1;
       const int h = hkv * G + it / per_head;
-      const int q0 = (i_min + it % per_head) * kFbBlock;
+      int owner, q0, qbase;
+      locate(it % per_head, owner, q0, qbase);
       const int q_idx = q0 + row;
       const bool q_valid = q_idx < p.Tq;
       float lse2 = 0.f, dlt = 0.f;
       if (q_valid) {
         const long long si = ((long long)b * p.Hq + h) * p.Tq + q_idx;
-        lse2 = p.lse[si] * 1.4426950408889634f;
-        dlt = p.delta[si];
+        lse2 = p.lse[owner][si] * 1.4426950408889634f;
+        dlt = p.delta[owner][si];
       }
-      const int limit = p.causal ? min(q_idx + shift, p.Tk - 1) : (p.Tk - 1);
+      // last visible key (index local to this rank's KV) for this query row
+      const int limit = p.causal ? min(kv0 + (qbase + row - k_base), p.Tk - 1) : (p.Tk - 1);
       ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
       // P / dS tiles are free once the MMAs of the previous iteration have executed.
@@ -326,7 +388,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, mbar_wait(dq_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
       tc_fence_after();
-      float* dq_row = p.dq_acc + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
+      float* dq_row = p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
 #pragma unroll 1
       for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t dq[32];
@@ -393,8 +455,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 template <int D>
-static int launch_flash_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                            const FlashBwdParams& p, cudaStream_t st) {
+static int launch_flash_bwd(const QMaps& qm, const CUtensorMap& tk, const CUtensorMap& tv, const FlashBwdParams& p,
+                            cudaStream_t st) {
   using Cfg = FaBwdCfg<D>;
   static bool configured = false;
   auto kern = flash_bwd_kernel<D>;
@@ -403,9 +465,74 @@ static int launch_flash_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const 
     configured = true;
   }
   dim3 grid((p.Tk + kFbBlock - 1) / kFbBlock, p.Hkv, p.B);
-  kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(qm, tk, tv, p);
   LT_LAUNCH_CHECK();
   return 0;
+}
+
+static int bwd_delta(const void* o, const void* d_o, float* delta, int B, int Tq, int Hq, int D, long long so_b, long long so_t,
+                     long long sdo_b, long long sdo_t, cudaStream_t st) {
+  const long long rows = (long long)B * Tq * Hq;
+  const int threads = 256;
+  const long long blocks = (rows * (D / 8) + threads - 1) / threads;
+  flash_bwd_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(o),
+                                                               static_cast<const __nv_bfloat16*>(d_o), delta, B, Tq, Hq, D, so_b,
+                                                               so_t, sdo_b, sdo_t);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+static int bwd_convert(const float* dq_acc, void* dq, int B, int Tq, int Hq, int D, long long sdq_b, long long sdq_t,
+                       cudaStream_t st) {
+  const long long n4 = (long long)B * Tq * Hq * D / 4;
+  long long blocks = (n4 + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  flash_bwd_convert_dq_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), B, Tq, Hq * D, sdq_b, sdq_t);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// Main kernel.  q/d_o/lse/delta/dq_acc are given per query-owning rank (cp_world entries; peer-mapped under CP).
+static int bwd_main(const void* const* q_ptrs, const void* k, const void* v, const void* const* do_ptrs,
+                    const float* const* lse_ptrs, const float* const* delta_ptrs, float* const* dq_acc_ptrs, void* dk, void* dv,
+                    int B, int Tq, int Tk, int Hq, int Hkv, int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t,
+                    long long sv_b, long long sv_t, long long sdo_b, long long sdo_t, long long sdk_b, long long sdk_t,
+                    float scale, int causal, int cp_world, int cp_rank, int zigzag, cudaStream_t st) {
+  if (cp_world < 1 || cp_world > kFbMaxRanks) return -int(kStatusBadArgument);
+  if (cp_world > 1 && zigzag && ((Tq / 2) % kFbBlock != 0 || (Tk / 2) % kFbBlock != 0)) return -int(kStatusBadArgument);
+  if (cp_world > 1 && !zigzag && (Tq % kFbBlock != 0 || Tk % kFbBlock != 0)) return -int(kStatusBadArgument);
+  QMaps qm;
+  CUtensorMap tk, tv;
+  int r;
+  for (int i = 0; i < kFbMaxRanks; ++i) {
+    const int src = i < cp_world ? i : 0;
+    r = encode_tmap_4d(&qm.q[i], q_ptrs[src], 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1,
+                       kFbBlock, 1, 1);
+    if (r) return 1000 + r;
+    r = encode_tmap_4d(&qm.d_o[i], do_ptrs[src], 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sdo_t * 2, (uint64_t)sdo_b * 2, 64,
+                       1, kFbBlock, 1, 1);
+    if (r) return 4000 + r;
+  }
+  r = encode_tmap_4d(&tk, k, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 2000 + r;
+  r = encode_tmap_4d(&tv, v, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1, kFbBlock, 1, 1);
+  if (r) return 3000 + r;
+  FlashBwdParams p{};
+  for (int i = 0; i < cp_world; ++i) {
+    p.lse[i] = lse_ptrs[i];
+    p.delta[i] = delta_ptrs[i];
+    p.dq_acc[i] = dq_acc_ptrs[i];
+  }
+  p.cp_world = cp_world; p.cp_rank = cp_rank; p.zigzag = zigzag;
+  p.dK = static_cast<__nv_bfloat16*>(dk);
+  p.dV = static_cast<__nv_bfloat16*>(dv);
+  p.sdk_b = sdk_b; p.sdk_t = sdk_t;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = device_status_word();
+  return (D == 64) ? launch_flash_bwd<64>(qm, tk, tv, p, st) : launch_flash_bwd<128>(qm, tk, tv, p, st);
 }
 
 }  // namespace lt
@@ -423,43 +550,39 @@ int lt_flash_bwd(const void* q, const void* k, const void* v, const void* o, con
   if ((D != 64 && D != 128) || Hq % Hkv != 0) return -int(kStatusBadArgument);
   if (B == 0 || Tq == 0 || Tk == 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  {
-    const long long rows = (long long)B * Tq * Hq;
-    const int threads = 256;
-    const long long blocks = (rows * (D / 8) + threads - 1) / threads;
-    flash_bwd_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(o),
-                                                                 static_cast<const __nv_bfloat16*>(d_o), delta, B, Tq, Hq, D,
-                                                                 so_b, so_t, sdo_b, sdo_t);
-    LT_LAUNCH_CHECK();
-  }
-  CUtensorMap tq, tk, tv, tdo;
-  int r;
-  r = encode_tmap_4d(&tq, q, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1, kFbBlock, 1, 1);
-  if (r) return 1000 + r;
-  r = encode_tmap_4d(&tk, k, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1, kFbBlock, 1, 1);
-  if (r) return 2000 + r;
-  r = encode_tmap_4d(&tv, v, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1, kFbBlock, 1, 1);
-  if (r) return 3000 + r;
-  r = encode_tmap_4d(&tdo, d_o, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sdo_t * 2, (uint64_t)sdo_b * 2, 64, 1, kFbBlock, 1, 1);
-  if (r) return 4000 + r;
-  FlashBwdParams p{};
-  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
-  p.dK = static_cast<__nv_bfloat16*>(dk);
-  p.dV = static_cast<__nv_bfloat16*>(dv);
-  p.sdk_b = sdk_b; p.sdk_t = sdk_t;
-  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
-  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.causal = causal;
-  p.status = device_status_word();
-  int rc = (D == 64) ? launch_flash_bwd<64>(tq, tk, tv, tdo, p, st) : launch_flash_bwd<128>(tq, tk, tv, tdo, p, st);
+  int rc = bwd_delta(o, d_o, delta, B, Tq, Hq, D, so_b, so_t, sdo_b, sdo_t, st);
   if (rc) return rc;
-  const long long n4 = (long long)B * Tq * Hq * D / 4;
-  long long blocks = (n4 + 255) / 256;
-  const long long cap = (long long)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  flash_bwd_convert_dq_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), B, Tq, Hq * D, sdq_b, sdq_t);
-  LT_LAUNCH_CHECK();
-  return 0;
+  const void* qs[1] = {q};
+  const void* dos[1] = {d_o};
+  const float* lses[1] = {lse};
+  const float* deltas[1] = {delta};
+  float* accs[1] = {dq_acc};
+  rc = bwd_main(qs, k, v, dos, lses, deltas, accs, dk, dv, B, Tq, Tk, Hq, Hkv, D, sq_b, sq_t, sk_b, sk_t, sv_b, sv_t, sdo_b, sdo_t,
+                sdk_b, sdk_t, scale, causal, 1, 0, 0, st);
+  if (rc) return rc;
+  return bwd_convert(dq_acc, dq, B, Tq, Hq, D, sdq_b, sdq_t, st);
+}
+
+// Context-parallel backward in three stream-ordered phases; the caller crosses a rank barrier between them.
+//   phase 0: delta = rowsum(O * dO) of the local queries (into symmetric memory); the caller also zeroes dq_acc.
+//   phase 1: main kernel - this rank's keys against every rank's queries: Q / dO tiles by TMA from peer memory, lse / delta
+//            by peer loads, dK / dV accumulated locally, dQ added to the owner's fp32 accumulator with red.add over NVLink.
+//   phase 2: dq = bf16(dq_acc) once every peer's phase 1 is complete.
+int lt_flash_bwd_cp(int phase, const void* const* q_ptrs, const void* k, const void* v, const void* o, const void* const* do_ptrs,
+                    const float* const* lse_ptrs, const float* const* delta_ptrs, float* const* dq_acc_ptrs, void* dq, void* dk,
+                    void* dv, int B, int Tq, int Tk, int Hq, int Hkv, int D, long long sq_b, long long sq_t, long long sk_b,
+                    long long sk_t, long long sv_b, long long sv_t, long long so_b, long long so_t, long long sdo_b,
+                    long long sdo_t, long long sdq_b, long long sdq_t, long long sdk_b, long long sdk_t, float scale, int causal,
+                    int cp_world, int cp_rank, int zigzag, void* stream) {
+  using namespace lt;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || cp_rank < 0 || cp_rank >= cp_world) return -int(kStatusBadArgument);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (phase == 0)
+    return bwd_delta(o, do_ptrs[cp_rank], const_cast<float*>(delta_ptrs[cp_rank]), B, Tq, Hq, D, so_b, so_t, sdo_b, sdo_t, st);
+  if (phase == 1)
+    return bwd_main(q_ptrs, k, v, do_ptrs, lse_ptrs, delta_ptrs, dq_acc_ptrs, dk, dv, B, Tq, Tk, Hq, Hkv, D, sq_b, sq_t, sk_b, sk_t,
+                    sv_b, sv_t, sdo_b, sdo_t, sdk_b, sdk_t, scale, causal, cp_world, cp_rank, zigzag, st);
+  return bwd_convert(dq_acc_ptrs[cp_rank], dq, B, Tq, Hq, D, sdq_b, sdq_t, st);
 }
 
 }  // extern "C"

@@ -30,7 +30,23 @@ struct FlashFwdParams {
   float scale_log2;  // softmax scale * log2(e)
   int causal;
   int* status;
+  // Context parallelism: the keys/values of cp_world ranks (Tk rows each, read through per-rank tensor maps that may
+  // point at peer memory) are visited in one pass; queries and keys carry global positions (contiguous split, or
+  // zigzag: rank r holds sequence chunks r and 2W-1-r of 2W).  cp_world == 1 is plain attention.
+  int cp_world, cp_rank, zigzag;
 };
+
+constexpr int kFaMaxRanks = 8;
+struct KvMaps {
+  CUtensorMap k[kFaMaxRanks];
+  CUtensorMap v[kFaMaxRanks];
+};
+
+// A run of consecutive visible KV blocks of one rank.
+struct KvSeg {
+  int n, owner, kv0, kbase;
+};
+constexpr int kFaMaxSegs = 2 * kFaMaxRanks;
 
 __device__ __forceinline__ float ex2_approx_f(float x) {
   float y;
@@ -48,7 +64,8 @@ struct FaFwdCfg {
   static constexpr int kOffV = kOffK + 2 * kKVBytes;
   static constexpr int kOffP = kOffV + 2 * kKVBytes;
   static constexpr int kOffBar = kOffP + 2 * kPBytes;
-  static constexpr int kOffX = kOffBar + 160;                 // row statistics exchanged between the two column halves
+  static constexpr int kOffSeg = kOffBar + 160;               // KvSeg table (16 entries) + block count
+  static constexpr int kOffX = kOffSeg + kFaMaxSegs * 16 + 16;                 // row statistics exchanged between the two column halves
   static constexpr int kNeeded = kOffX + 2 * 2 * 128 * 4;     // [parity][half][128] floats
   // 1 KB of slack for the 1024-byte alignment where it fits under the 227 KB limit; the kernel checks at run time
   // that the aligned layout lies inside the allocation and reports kStatusBadArgument otherwise.
@@ -60,8 +77,7 @@ struct FaFwdCfg {
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 1)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps maps, const FlashFwdParams p) {
   using Cfg = FaFwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -92,15 +108,62 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = q_blk * kFaBlockQ;
-  const int shift = p.Tk - p.Tq;  // key index visible to query i is <= i + shift
-  int n_blocks;
-  if (p.causal) {
-    int last = q0 + kFaBlockQ - 1 + shift;
-    if (last > p.Tk - 1) last = p.Tk - 1;
-    n_blocks = last < 0 ? 0 : last / kFaBlockKV + 1;
+  KvSeg* segs = reinterpret_cast<KvSeg*>(smem + Cfg::kOffSeg);
+  int* n_blocks_s = reinterpret_cast<int*>(smem + Cfg::kOffSeg + kFaMaxSegs * 16);
+  // global position of this block's first query
+  int q_base;
+  if (p.cp_world == 1) {
+    q_base = q0 + (p.Tk - p.Tq);  // key index visible to query i is <= i + (Tk - Tq)
+  } else if (p.zigzag) {
+    const int hq = p.Tq / 2;
+    q_base = q0 < hq ? p.cp_rank * hq + q0 : (2 * p.cp_world - 1 - p.cp_rank) * hq + (q0 - hq);
   } else {
-    n_blocks = (p.Tk + kFaBlockKV - 1) / kFaBlockKV;
+    q_base = p.cp_rank * p.Tq + q0;
   }
+  if (threadIdx.x == 0) {
+    // visible KV blocks as runs: own rank first (local memory), then the other ranks
+    const int q_last = q_base + kFaBlockQ - 1;
+    const int nb_all = (p.Tk + kFaBlockKV - 1) / kFaBlockKV;
+    int ns = 0, total = 0;
+    for (int i = 0; i < p.cp_world; ++i) {
+      const int o = (p.cp_rank + i) % p.cp_world;
+      const int parts = (p.cp_world > 1 && p.zigzag) ? 2 : 1;
+      for (int h2 = 0; h2 < parts; ++h2) {
+        int kv0, kbase, nb;
+        if (parts == 2) {
+          const int hk = p.Tk / 2;
+          kv0 = h2 * hk;
+          kbase = h2 == 0 ? o * hk : (2 * p.cp_world - 1 - o) * hk;
+          nb = hk / kFaBlockKV;
+        } else {
+          kv0 = 0;
+          kbase = p.cp_world > 1 ? o * p.Tk : 0;
+          nb = nb_all;
+        }
+        if (p.causal) {
+          const int vis = q_last < kbase ? 0 : (q_last - kbase) / kFaBlockKV + 1;
+          nb = nb < vis ? nb : vis;
+        }
+        if (nb > 0) {
+          segs[ns] = KvSeg{nb, o, kv0, kbase};
+          ++ns;
+          total += nb;
+        }
+      }
+    }
+    for (int i = ns; i < kFaMaxSegs; ++i) segs[i] = KvSeg{0, 0, 0, 0};
+    *n_blocks_s = total;
+  }
+  __syncthreads();
+  const int n_blocks = *n_blocks_s;
+  // block j of the schedule -> (owner rank, first local key row, global position of its first key)
+  auto locate = [&](int j, int& owner, int& kv0, int& kbase) {
+    int sidx = 0;
+    while (sidx < kFaMaxSegs - 1 && j >= segs[sidx].n) { j -= segs[sidx].n; ++sidx; }
+    owner = segs[sidx].owner;
+    kv0 = segs[sidx].kv0 + j * kFaBlockKV;
+    kbase = segs[sidx].kbase + j * kFaBlockKV;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -114,7 +177,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&maps.k[p.cp_rank]); tma_prefetch_desc(&maps.v[p.cp_rank]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), Cfg::kTmemCols);
@@ -135,18 +198,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < n_blocks; ++j) {
         const int s = j & 1;
         const uint32_t par = (j >> 1) & 1;
+        int owner, kv0, kbase;
+        locate(j, owner, kv0, kbase);
         if (!mbar_wait(k_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
         mbar_expect_tx(k_full(s), Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(sbase + Cfg::kOffK + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &tmK, k_full(s), c * 64, hkv,
-                      j * kFaBlockKV, b);
+          tma_load_4d(sbase + Cfg::kOffK + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &maps.k[owner], k_full(s), c * 64, hkv,
+                      kv0, b);
         if (!mbar_wait(v_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
         mbar_expect_tx(v_full(s), Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(sbase + Cfg::kOffV + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &tmV, v_full(s), c * 64, hkv,
-                      j * kFaBlockKV, b);
+          tma_load_4d(sbase + Cfg::kOffV + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &maps.v[owner], v_full(s), c * 64, hkv,
+                      kv0, b);
       }
     }
   } else if (warp == 1) {
@@ -217,8 +282,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < 2; ++c) tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + s * 128 + (2 * half + c) * 32, r[c]);
       tmem_ld_wait();
-      const int kv0 = j * kFaBlockKV + half * 64;
-      const int limit = p.causal ? min(q_idx + shift, p.Tk - 1) : (p.Tk - 1);  // last visible key
+      int owner, kv0b, kbase;
+      locate(j, owner, kv0b, kbase);
+      // last visible column of this 128-key block for this row: causal position and end of the rank's keys
+      int limit = p.Tk - 1 - kv0b;
+      if (p.causal) limit = min(limit, q_base + row - kbase);
+      const int kv0 = half * 64;
       const bool need_mask = (kv0 + 63 > limit);
       float mx = -INFINITY;
 #pragma unroll
@@ -349,8 +418,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 template <int D>
-static int launch_flash_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashFwdParams& p,
-                            cudaStream_t st) {
+static int launch_flash_fwd(const CUtensorMap& tq, const KvMaps& maps, const FlashFwdParams& p, cudaStream_t st) {
   using Cfg = FaFwdCfg<D>;
   static bool configured = false;
   auto kern = flash_fwd_kernel<D>;
@@ -359,9 +427,43 @@ static int launch_flash_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const 
     configured = true;
   }
   dim3 grid((p.Tq + kFaBlockQ - 1) / kFaBlockQ, p.Hq, p.B);
-  kern<<<grid, kFaThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, p);
+  kern<<<grid, kFaThreads, Cfg::kSmemBytes, st>>>(tq, maps, p);
   LT_LAUNCH_CHECK();
   return 0;
+}
+
+static int flash_fwd_common(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* o, float* lse, int B,
+                            int Tq, int Tk, int Hq, int Hkv, int D, long long sq_b, long long sq_t, long long sk_b,
+                            long long sk_t, long long sv_b, long long sv_t, long long so_b, long long so_t, float scale,
+                            int causal, int cp_world, int cp_rank, int zigzag, void* stream) {
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || cp_world < 1 || cp_world > kFaMaxRanks) return -int(kStatusBadArgument);
+  if (cp_world > 1 && zigzag && ((Tq / 2) % kFaBlockQ != 0 || (Tk / 2) % kFaBlockKV != 0)) return -int(kStatusBadArgument);
+  if (cp_world > 1 && !zigzag && (Tq % kFaBlockQ != 0 || Tk % kFaBlockKV != 0)) return -int(kStatusBadArgument);
+  if (B == 0 || Tq == 0) return 0;
+  CUtensorMap tq;
+  KvMaps maps;
+  int r = encode_tmap_4d(&tq, q, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1, kFaBlockQ, 1, 1);
+  if (r) return 1000 + r;
+  for (int i = 0; i < kFaMaxRanks; ++i) {
+    const int src = i < cp_world ? i : 0;
+    r = encode_tmap_4d(&maps.k[i], k_ptrs[src], 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1,
+                       kFaBlockKV, 1, 1);
+    if (r) return 2000 + r;
+    r = encode_tmap_4d(&maps.v[i], v_ptrs[src], 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1,
+                       kFaBlockKV, 1, 1);
+    if (r) return 3000 + r;
+  }
+  FlashFwdParams p{};
+  p.O = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.so_b = so_b; p.so_t = so_t;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.cp_world = cp_world; p.cp_rank = cp_rank; p.zigzag = zigzag;
+  p.status = device_status_word();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return D == 64 ? launch_flash_fwd<64>(tq, maps, p, st) : launch_flash_fwd<128>(tq, maps, p, st);
 }
 
 }  // namespace lt
@@ -373,27 +475,21 @@ extern "C" {
 int lt_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq, int Tk, int Hq, int Hkv,
                  int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t, long long sv_b, long long sv_t,
                  long long so_b, long long so_t, float scale, int causal, void* stream) {
-  using namespace lt;
-  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -int(kStatusBadArgument);
-  if (B == 0 || Tq == 0) return 0;
-  CUtensorMap tq, tk, tv;
-  int r;
-  r = encode_tmap_4d(&tq, q, 2, D, Hq, Tq, B, (uint64_t)D * 2, (uint64_t)sq_t * 2, (uint64_t)sq_b * 2, 64, 1, kFaBlockQ, 1, 1);
-  if (r) return 1000 + r;
-  r = encode_tmap_4d(&tk, k, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sk_t * 2, (uint64_t)sk_b * 2, 64, 1, kFaBlockKV, 1, 1);
-  if (r) return 2000 + r;
-  r = encode_tmap_4d(&tv, v, 2, D, Hkv, Tk, B, (uint64_t)D * 2, (uint64_t)sv_t * 2, (uint64_t)sv_b * 2, 64, 1, kFaBlockKV, 1, 1);
-  if (r) return 3000 + r;
-  FlashFwdParams p{};
-  p.O = static_cast<__nv_bfloat16*>(o);
-  p.lse = lse;
-  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
-  p.so_b = so_b; p.so_t = so_t;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.causal = causal;
-  p.status = device_status_word();
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_flash_fwd<64>(tq, tk, tv, p, st) : launch_flash_fwd<128>(tq, tk, tv, p, st);
+  const void* ks[1] = {k};
+  const void* vs[1] = {v};
+  return lt::flash_fwd_common(q, ks, vs, o, lse, B, Tq, Tk, Hq, Hkv, D, sq_b, sq_t, sk_b, sk_t, sv_b, sv_t, so_b, so_t, scale,
+                              causal, 1, 0, 0, stream);
+}
+
+// Context-parallel forward: k_ptrs[r] / v_ptrs[r] are rank r's KV shards [B, Tk, Hkv, D] (peer-mapped pointers, all with
+// the same strides); the local queries attend to every rank's keys in one pass, the KV tiles of other ranks being
+// read from peer memory by non-multicast TMA loads inside the kernel.
+int lt_flash_fwd_cp(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, void* o, float* lse, int B, int Tq,
+                    int Tk, int Hq, int Hkv, int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t,
+                    long long sv_b, long long sv_t, long long so_b, long long so_t, float scale, int causal, int cp_world,
+                    int cp_rank, int zigzag, void* stream) {
+  return lt::flash_fwd_common(q, k_ptrs, v_ptrs, o, lse, B, Tq, Tk, Hq, Hkv, D, sq_b, sq_t, sk_b, sk_t, sv_b, sv_t, so_b, so_t,
+                              scale, causal, cp_world, cp_rank, zigzag, stream);
 }
 
 }  // extern "C"

@@ -17,7 +17,7 @@
 //    ZeRO3Optimizer::step (src/distributed/fsdp_wrapper.cpp:81-96, src/optim/zero3_optimizer.cpp:11-105).
 // 3. lt_embedding_fwd_sharded: embedding rows fetched from the owning rank.
 // 4. lt_signal_barrier: all-ranks barrier on symmetric flags (bounded wait).
-#include "gemm_sm100.cuh"
+#include "comm_common.cuh"
 
 namespace lt {
 
@@ -51,32 +51,6 @@ struct ProgressDone {
     if (progress) red_add_release_gpu(progress, 1u);
   }
 };
-
-struct FlagGate {
-  const uint32_t* flags;
-  uint32_t epoch;
-  int gate_dim;
-  int last;
-  __device__ __forceinline__ bool operator()(int m_blk, int n_blk, int kb, int* status) {
-    const int idx = gate_dim == 0 ? n_blk : (gate_dim == 1 ? kb : m_blk);
-    if (idx == last) return true;
-    if (!wait_flag_ge_gpu(flags + idx, epoch, status)) return false;
-    asm volatile("fence.proxy.async.global;" ::: "memory");
-    last = idx;
-    return true;
-  }
-};
-
-constexpr int kGatherStageBytes = 32768;
-constexpr int kGatherStages = 5;
-
-__device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
-}
 
 // One thread of a gather CTA runs the whole copy pipeline.
 __device__ void gather_cta(const GatherArgs& g_own, const PrefetchArgs& pf, int* status) {

@@ -50,6 +50,16 @@ struct GemmParams {
   // staging buffer of the rank that owns them, peer_C[owner] + (src_rank * rows_per_rank + local_row) * ldc.
   void* peer_C[8];
   int rows_per_rank, src_rank;
+  // Grouped GEMM (mixture of experts): rows are grouped by expert in blocks of 128; m block i uses the B operand of
+  // expert group_of_mblk[i], i.e. B rows are offset by group * b_group_rows (nullptr: plain GEMM).
+  const int* group_of_mblk;
+  int b_group_rows;
+  // Per-row epilogue extras: multiply row r by row_scale[r]; combine mode: instead of storing, add the row (times
+  // row_scale) into the fp32 accumulator of the rank that owns the token, acc_ptrs[dst_rank] + dst_row * ldc, with
+  // red.add (peer memory over NVLink); row_table[r] = {dst_rank, dst_row}, dst_rank < 0 marks a padding row.
+  const float* row_scale;
+  const int2* row_table;
+  float* acc_ptrs[8];
 };
 
 template <int BLOCK_N>
@@ -134,6 +144,25 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
     } else {
       _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(rp[j]);
     }
+  }
+  if (p.row_scale) {
+    const float rs = p.row_scale[row];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= rs;
+  }
+  if (p.row_table) {
+    const int2 dst = p.row_table[row];
+    if (dst.x < 0) return;
+    float* ap = p.acc_ptrs[dst.x] + (long long)dst.y * p.ldc + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(ap + q * 4), "f"(v[q * 4]), "f"(v[q * 4 + 1]),
+                     "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3]) : "memory");
+    } else {
+      _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) atomicAdd(ap + j, v[j]);
+    }
+    return;
   }
   void* c_base = p.C;
   if (p.rows_per_rank > 0) {
@@ -268,12 +297,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
             for (int i = 0; i < kBlockM / 64; ++i)
               tma_load_2d(a_dst + i * (64 * kBlockK * 2), tmA, fb, m_blk * kBlockM + i * 64, kb * kBlockK);
           }
+          const int b_off = p.group_of_mblk ? p.group_of_mblk[m_blk] * p.b_group_rows : 0;
           if (B_MAJOR == 0) {
-            tma_load_2d(b_dst, tmB, fb, kb * kBlockK, n_blk * BLOCK_N);
+            tma_load_2d(b_dst, tmB, fb, kb * kBlockK, b_off + n_blk * BLOCK_N);
           } else {
 #pragma unroll
             for (int i = 0; i < BLOCK_N / 64; ++i)
-              tma_load_2d(b_dst + i * (64 * kBlockK * 2), tmB, fb, n_blk * BLOCK_N + i * 64, kb * kBlockK);
+              tma_load_2d(b_dst + i * (64 * kBlockK * 2), tmB, fb, n_blk * BLOCK_N + i * 64, b_off + kb * kBlockK);
           }
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }

@@ -51,6 +51,11 @@ _SIGS = {
     "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
     "lt_gemm_rs_bf16": [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp, ctypes.c_uint, _i, _i, _i, _vp, _ll, _vp, _vp, _ll, _vp],
     "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
+    "lt_moe_gather_gemm": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, ctypes.c_uint, _vp, _vp, _i, _vp],
+    "lt_moe_gemm_scatter": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "lt_flash_fwd_cp": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _i, _i, _i, _vp],
+    "lt_flash_bwd_cp": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                        _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _i, _i, _i, _vp],
     "lt_flash_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
 }
@@ -466,3 +471,57 @@ def gemm_rs(a, b, *, b_major: int, stage_ptrs, counter_ptrs, epoch: int, world: 
 def gemm_num_tiles(M: int, N: int, n_comm: int = 0) -> int:
     """Output tiles the GEMM launcher will use for an M x N result when `n_comm` SMs are set aside."""
     return _fn("lt_gemm_num_tiles")(M, N, n_comm)
+
+
+# ------------------------------------------------------------------------------------------------ context-parallel attention
+def flash_fwd_cp(q, k_ptrs, v_ptrs, k_like, *, causal, scale, cp_world, cp_rank, zigzag):
+    """q: local queries [B, Tq, Hq, D]; k_ptrs / v_ptrs: every rank's KV shard (device pointers, layout of `k_like`)."""
+    B, Tq, Hq, D = q.shape
+    _, Tk, Hkv, _ = k_like.shape
+    o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, Tq), dtype=torch.float32, device=q.device)
+    rc = _fn("lt_flash_fwd_cp")(q.data_ptr(), ctypes.cast(_ptr_array(k_ptrs), c_void_p), ctypes.cast(_ptr_array(v_ptrs), c_void_p),
+                                o.data_ptr(), lse.data_ptr(), B, Tq, Tk, Hq, Hkv, D, q.stride(0), q.stride(1), k_like.stride(0),
+                                k_like.stride(1), k_like.stride(0), k_like.stride(1), o.stride(0), o.stride(1), float(scale),
+                                1 if causal else 0, cp_world, cp_rank, 1 if zigzag else 0, _stream())
+    _check(rc, "lt_flash_fwd_cp")
+    return o, lse
+
+
+def flash_bwd_cp(phase, *, q_ptrs, k, v, o, do_ptrs, lse_ptrs, delta_ptrs, dq_acc_ptrs, dq, dk, dv, q_like, causal, scale,
+                 cp_world, cp_rank, zigzag):
+    B, Tq, Hq, D = q_like.shape
+    _, Tk, Hkv, _ = k.shape
+    rc = _fn("lt_flash_bwd_cp")(phase, ctypes.cast(_ptr_array(q_ptrs), c_void_p), k.data_ptr(), v.data_ptr(), _p(o),
+                                ctypes.cast(_ptr_array(do_ptrs), c_void_p), ctypes.cast(_ptr_array(lse_ptrs), c_void_p),
+                                ctypes.cast(_ptr_array(delta_ptrs), c_void_p), ctypes.cast(_ptr_array(dq_acc_ptrs), c_void_p),
+                                _p(dq), _p(dk), _p(dv), B, Tq, Tk, Hq, Hkv, D, q_like.stride(0), q_like.stride(1), k.stride(0),
+                                k.stride(1), v.stride(0), v.stride(1), q_like.stride(0), q_like.stride(1), q_like.stride(0),
+                                q_like.stride(1), q_like.stride(0), q_like.stride(1), k.stride(0), k.stride(1), float(scale),
+                                1 if causal else 0, cp_world, cp_rank, 1 if zigzag else 0, _stream())
+    _check(rc, "lt_flash_bwd_cp")
+
+
+# ------------------------------------------------------------------------------------------------ mixture of experts
+def moe_gather_gemm(src_ptrs, world, slot_src, group_of_mblk, weights, *, b_major, slot_buf, flags, epoch, row_scale=None,
+                    n_comm=0):
+    """out[slots, N] = rows fetched from the ranks' token buffers by `slot_src` @ op(weights[expert of the slot block])."""
+    slots = slot_src.shape[0]
+    E = weights.shape[0]
+    N, Kd = (weights.shape[1], weights.shape[2]) if b_major == 0 else (weights.shape[2], weights.shape[1])
+    out = torch.empty((slots, N), dtype=torch.bfloat16, device=weights.device)
+    rc = _fn("lt_moe_gather_gemm")(ctypes.cast(_ptr_array(src_ptrs), c_void_p), world, slot_src.data_ptr(), group_of_mblk.data_ptr(),
+                                   slots, weights.data_ptr(), E, N, Kd, b_major, slot_buf.data_ptr(), flags.data_ptr(), epoch,
+                                   out.data_ptr(), _p(row_scale), n_comm, _stream())
+    _check(rc, "lt_moe_gather_gemm")
+    return out
+
+
+def moe_gemm_scatter(a, group_of_mblk, weights, *, b_major, slot_dst, row_weight, acc_ptrs, world):
+    """acc[dst rank][dst row] += row_weight * (a[slot] @ op(weights[expert])) with red.add into the owners' accumulators."""
+    slots, Kd = a.shape
+    E = weights.shape[0]
+    N = weights.shape[1] if b_major == 0 else weights.shape[2]
+    rc = _fn("lt_moe_gemm_scatter")(a.data_ptr(), group_of_mblk.data_ptr(), slots, weights.data_ptr(), E, N, Kd, b_major,
+                                    slot_dst.data_ptr(), _p(row_weight), ctypes.cast(_ptr_array(acc_ptrs), c_void_p), world, _stream())
+    _check(rc, "lt_moe_gemm_scatter")

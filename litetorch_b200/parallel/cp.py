@@ -189,3 +189,80 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg=None, c
     if _world(pg) == 1 and not zigzag:
         return Fn.flash_attention(q, k, v, is_causal=causal)
     return _RingAttention.apply(q, k, v, pg, causal, zigzag)
+
+
+# ------------------------------------------------------------------------------------------------ fused CUDA path
+class RingFlashContext:
+    """Context-parallel FlashAttention whose KV exchange happens INSIDE the attention kernels.
+
+    Every rank publishes its K / V shard (and, for the backward, Q / dO / LSE / delta and an fp32 dQ accumulator) in
+    symmetric memory.  The forward kernel walks over the visible KV blocks of all ranks in one pass - tiles of other
+    ranks are fetched from peer memory by non-multicast TMA loads - so no partial results are merged.  The backward
+    kernel keeps this rank's keys resident, reads every rank's Q / dO tiles from peer memory, accumulates dK / dV
+    locally and adds dQ to its owner's accumulator with `red.add` over NVLink.  Rank barriers (flag kernels, bounded
+    waits) separate publish / compute / read-back phases.  Layout [B, T_local, H, D]; contiguous or zigzag split."""
+
+    def __init__(self, B: int, T_local: int, Hq: int, Hkv: int, D: int, device, group=None, zigzag: bool = True):
+        from .fsdp import SymmetricBuffer
+        from ..ops import kernels as K
+        self.K = K
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.shape_q, self.shape_kv = (B, T_local, Hq, D), (B, T_local, Hkv, D)
+        self.zigzag = zigzag
+        dev = torch.device(device)
+        nq, nkv = B * T_local * Hq * D, B * T_local * Hkv * D
+        mk = lambda n, dt: SymmetricBuffer(n, dt, dev, self.group)  # noqa: E731
+        self.k, self.v = mk(nkv, torch.bfloat16), mk(nkv, torch.bfloat16)
+        self.q, self.do = mk(nq, torch.bfloat16), mk(nq, torch.bfloat16)
+        self.lse, self.delta = mk(B * Hq * T_local, torch.float32), mk(B * Hq * T_local, torch.float32)
+        self.dq_acc = mk(nq, torch.float32)
+        self.flags = mk(64, torch.int32)
+        self.epoch = 0
+
+    def barrier(self):
+        self.epoch += 1
+        self.K.signal_barrier(self.flags.tensor, self.flags.ptrs, 0, self.epoch, self.world, self.rank)
+
+    def attention(self, q, k, v, causal: bool = True):
+        """q: [B, T_local, Hq, D]; k, v: [B, T_local, Hkv, D] (bf16 CUDA).  Differentiable."""
+        return _RingFlash.apply(self, q, k, v, causal)
+
+
+class _RingFlash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, c, q, k, v, causal):
+        K = c.K
+        scale = q.shape[-1] ** -0.5
+        kb, vb = c.k.tensor.view(c.shape_kv), c.v.tensor.view(c.shape_kv)
+        c.barrier()                       # nobody still reads the previous contents of the shared KV buffers
+        kb.copy_(k)
+        vb.copy_(v)
+        c.barrier()                       # every rank's shard is published
+        qc = q.contiguous()
+        o, lse = K.flash_fwd_cp(qc, c.k.ptrs, c.v.ptrs, kb, causal=causal, scale=scale, cp_world=c.world, cp_rank=c.rank,
+                                zigzag=c.zigzag)
+        ctx.c, ctx.causal, ctx.scale = c, causal, scale
+        ctx.save_for_backward(qc, k.contiguous(), v.contiguous(), o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        c, K = ctx.c, ctx.c.K
+        q, k, v, o, lse = ctx.saved_tensors
+        qb, dob = c.q.tensor.view(c.shape_q), c.do.tensor.view(c.shape_q)
+        c.barrier()                       # previous users of the shared Q / dO / accumulators are done
+        qb.copy_(q)
+        dob.copy_(do)
+        c.lse.tensor.view(lse.shape).copy_(lse)
+        c.dq_acc.tensor.zero_()
+        args = dict(q_ptrs=c.q.ptrs, k=k, v=v, o=o, do_ptrs=c.do.ptrs, lse_ptrs=c.lse.ptrs, delta_ptrs=c.delta.ptrs,
+                    dq_acc_ptrs=c.dq_acc.ptrs, q_like=qb, causal=ctx.causal, scale=ctx.scale, cp_world=c.world,
+                    cp_rank=c.rank, zigzag=c.zigzag)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        K.flash_bwd_cp(0, dq=None, dk=None, dv=None, **args)          # delta of the local queries
+        c.barrier()                       # every rank's Q, dO, lse, delta are published and its accumulator is zero
+        K.flash_bwd_cp(1, dq=None, dk=dk, dv=dv, **args)
+        c.barrier()                       # every rank has added its dQ contributions
+        K.flash_bwd_cp(2, dq=dq, dk=None, dv=None, **args)
+        return None, dq, dk, dv, None

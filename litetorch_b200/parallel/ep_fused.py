@@ -1,0 +1,171 @@
+"""Expert-parallel SwiGLU MoE whose dispatch and combine are fused into the grouped expert GEMMs.
+
+Forward:  tokens stay in their rank's symmetric buffer; `lt_moe_gather_gemm` fetches the routed rows from the peers
+while the gate/up GEMM of already-arrived slot blocks runs; SwiGLU; `lt_moe_gemm_scatter` multiplies each slot by its
+gate weight in the down-projection epilogue and adds it into the owning rank's fp32 output accumulator.
+Backward: the same two kernels with the roles swapped (gather dY rows -> dH, scatter-add dX rows), per-expert tcgen05
+weight-gradient GEMMs on the saved slot buffers, and the router gradient returned to the source ranks.
+Routing metadata (a few bytes per slot) is exchanged with one NCCL all-gather per pass; no payload all-to-all exists.
+Requires equal token counts per rank.  Router, capacity factor and auxiliary loss are those of `MoEFeedForward`.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..core import Tensor, _unwrap
+from ..ops import kernels as K
+from .ep import MoEFeedForward
+from .fsdp import SymmetricBuffer
+
+
+class MoEFusedFeedForward(MoEFeedForward):
+    def __init__(self, dim, ffn, num_experts, top_k=2, capacity_factor=1.25, aux_loss_coef=0.01, group=None, device="cuda",
+                 seed=0, init_std=0.02, max_tokens=8192, n_comm=8):
+        super().__init__(dim, ffn, num_experts, top_k, capacity_factor, aux_loss_coef, group, torch.bfloat16, device, seed, init_std)
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        dev = torch.device(device)
+        self.max_tokens = max_tokens
+        self.tok = SymmetricBuffer(max_tokens * dim, torch.bfloat16, dev, self.group)      # x (forward) / dy (backward)
+        self.acc = SymmetricBuffer(max_tokens * dim, torch.float32, dev, self.group)       # y (forward) / dx (backward)
+        self.sig = SymmetricBuffer(64, torch.int32, dev, self.group)
+        cap_slots = int(math.ceil(capacity_factor * max_tokens * top_k * self.world / num_experts)) * self.local_E
+        self.max_slots = (cap_slots // 128 + self.local_E + 1) * 128
+        self.slot_buf = torch.zeros(self.max_slots * dim, dtype=torch.bfloat16, device=dev)
+        self.flags = torch.zeros(4096, dtype=torch.int32, device=dev)
+        self.epoch = 0
+        self.sig_epoch = 0
+        self.n_comm = n_comm
+
+    def barrier(self):
+        self.sig_epoch += 1
+        K.signal_barrier(self.sig.tensor, self.sig.ptrs, 0, self.sig_epoch, self.world, self.rank)
+
+    def _build_slots(self, top_w, top_i, keep):
+        """All ranks share (expert, source row, weight) of every kept slot; this rank keeps those of its experts,
+        grouped by expert and padded to blocks of 128."""
+        N, k = top_i.shape
+        dev = top_i.device
+        exp = torch.where(keep, top_i, torch.full_like(top_i, -1)).reshape(-1)
+        meta = torch.stack([exp.float(), torch.arange(N, device=dev).repeat_interleave(k).float(), top_w.detach().reshape(-1).float()], 1)
+        allm = [torch.empty_like(meta) for _ in range(self.world)]
+        dist.all_gather(allm, meta.contiguous(), group=self.group)
+        allm = torch.stack(allm, 0)                                        # [W, N*k, 3]
+        e = allm[:, :, 0].long()
+        mine = (e >= self.first) & (e < self.first + self.local_E)
+        src_rank, flat = mine.nonzero(as_tuple=True)
+        le = e[src_rank, flat] - self.first
+        order = torch.argsort(le, stable=True)
+        src_rank, flat, le = src_rank[order], flat[order], le[order]
+        counts = torch.bincount(le, minlength=self.local_E)
+        padded = (counts + 127) // 128 * 128
+        starts = torch.cumsum(padded, 0) - padded
+        S = int(padded.sum().item())
+        S = max(S, 128)
+        assert S <= self.max_slots, "more routed tokens than the slot buffer holds"
+        pos = starts[le] + (torch.arange(le.numel(), device=dev) - (torch.cumsum(counts, 0) - counts)[le])
+        slot = torch.full((S, 2), -1, dtype=torch.int32, device=dev)
+        slot[pos, 0] = src_rank.int()
+        slot[pos, 1] = allm[src_rank, flat, 1].int()
+        w = torch.zeros(S, dtype=torch.float32, device=dev)
+        w[pos] = allm[src_rank, flat, 2]
+        origin = torch.full((S, 2), -1, dtype=torch.int64, device=dev)    # (source rank, flat slot index n*k+j)
+        origin[pos, 0] = src_rank
+        origin[pos, 1] = flat
+        nblk = S // 128
+        blk_start = torch.arange(nblk, device=dev) * 128
+        group = (torch.searchsorted((starts + padded).contiguous(), blk_start, right=True)).clamp(max=self.local_E - 1).int()
+        return slot.contiguous(), w, group.contiguous(), origin, S
+
+    def forward(self, x: Tensor) -> Tensor:
+        xt = _unwrap(x)
+        shape = xt.shape
+        x2 = xt.reshape(-1, shape[-1])
+        top_w, top_i, keep, aux = self.route(x2)
+        self.last_aux_loss = aux * self.aux_loss_coef
+        self.last_dropped = int((~keep).sum())
+        y = _MoEFused.apply(self, x2, top_w, top_i, keep, _unwrap(self.w_gate_up), _unwrap(self.w_down))
+        return Tensor(y.view(shape))
+
+    __call__ = forward
+
+
+class _MoEFused(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, m, x2, top_w, top_i, keep, w_gu, w_dn):
+        N, d = x2.shape
+        slot, w, group, origin, S = m._build_slots(top_w, top_i, keep)
+        tok = m.tok.tensor[:N * d].view(N, d)
+        acc = m.acc.tensor[:N * d].view(N, d)
+        m.barrier()                                   # peers are done with the previous contents of tok / acc
+        tok.copy_(x2)
+        acc.zero_()
+        m.barrier()                                   # tokens published, accumulators cleared
+        m.epoch += 1
+        sb = m.slot_buf[:S * d].view(S, d)
+        gu = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_gu, b_major=0, slot_buf=sb, flags=m.flags, epoch=m.epoch,
+                               n_comm=m.n_comm)
+        xs = sb.clone()                               # routed inputs, kept for the weight gradient
+        h = K.swiglu_fwd(gu)
+        K.moe_gemm_scatter(h, group, w_dn, b_major=0, slot_dst=slot, row_weight=w, acc_ptrs=m.acc.ptrs, world=m.world)
+        m.barrier()                                   # every rank has added its experts' outputs
+        y = acc.to(torch.bfloat16)
+        ctx.m = m
+        ctx.save_for_backward(slot, w, group, origin, xs, gu, h, w_gu, w_dn)
+        ctx.meta = (N, d, S, top_w.shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        m = ctx.m
+        slot, w, group, origin, xs, gu, h, w_gu, w_dn = ctx.saved_tensors
+        N, d, S, tw_shape = ctx.meta
+        tok = m.tok.tensor[:N * d].view(N, d)
+        acc = m.acc.tensor[:N * d].view(N, d)
+        m.barrier()
+        tok.copy_(dy)
+        acc.zero_()
+        m.barrier()
+        m.epoch += 1
+        sb = m.slot_buf[:S * d].view(S, d)
+        # dh (unweighted) = dy_slot @ W_down : gather dy rows, B stored [E, K=d, N=F]
+        dh_u = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_dn, b_major=1, slot_buf=sb, flags=m.flags, epoch=m.epoch,
+                                 n_comm=m.n_comm)
+        dys = sb                                       # gathered dy rows
+        valid = (slot[:, 0] >= 0)
+        dw_slot = (h.float() * dh_u.float()).sum(-1) * valid
+        dh = (dh_u.float() * w[:, None]).to(torch.bfloat16)
+        hw = (h.float() * w[:, None]).to(torch.bfloat16)
+        dgu = K.swiglu_bwd(gu.clone(), dh, inplace=True)
+        dgu = dgu * valid[:, None].to(dgu.dtype)
+        # weight gradients per expert on its slot range
+        dwgu, dwdn = torch.zeros_like(w_gu), torch.zeros_like(w_dn)
+        g_cpu = group.tolist()
+        b0 = 0
+        while b0 < len(g_cpu):
+            e = g_cpu[b0]
+            b1 = b0
+            while b1 < len(g_cpu) and g_cpu[b1] == e:
+                b1 += 1
+            r0, r1 = b0 * 128, b1 * 128
+            K.gemm(dgu[r0:r1], xs[r0:r1], a_major=1, b_major=1, out=dwgu[e], accumulate=True)
+            K.gemm(dys[r0:r1], hw[r0:r1], a_major=1, b_major=1, out=dwdn[e], accumulate=True)
+            b0 = b1
+        # dx: scatter-add dgu_slot @ W_gu into the token owners' accumulators (B stored [E, K=2F, N=d])
+        K.moe_gemm_scatter(dgu, group, w_gu, b_major=1, slot_dst=slot, row_weight=None, acc_ptrs=m.acc.ptrs, world=m.world)
+        # router gradient: each slot's d(loss)/d(gate weight) goes back to the rank and slot it came from
+        send = torch.stack([origin[:, 0].float(), origin[:, 1].float(), dw_slot], 1)
+        pad = torch.full((m.max_slots, 3), -1.0, device=send.device)
+        pad[:S] = send
+        allg = [torch.empty_like(pad) for _ in range(m.world)]
+        dist.all_gather(allg, pad, group=m.group)
+        allg = torch.cat(allg, 0)
+        mine = allg[:, 0].long() == m.rank
+        dtw = torch.zeros(tw_shape[0] * tw_shape[1], dtype=torch.float32, device=send.device)
+        dtw[allg[mine, 1].long()] = allg[mine, 2]
+        m.barrier()
+        dx = acc.to(torch.bfloat16)
+        return None, dx, dtw.view(tw_shape), None, None, dwgu, dwdn

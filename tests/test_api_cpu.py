@@ -333,3 +333,16 @@ def test_gpt_config_trains_on_cpu():
     from litetorch_b200.models.gpt import train
     out = train(steps=6, verbose=False)
     assert abs(out["losses"][0] - math.log(256)) < 0.1 and out["tokens_per_s"] > 0
+
+
+def test_custom_op_registry():
+    lt.custom_ops.Registry.register(
+        "cube", lambda x: lt.Tensor(_unwrap(x) ** 3),
+        backward=lambda inputs, out, g: [lt.Tensor(3 * _unwrap(inputs[0]) ** 2 * _unwrap(g))])
+    x = T([1.0, 2.0], [2], True)
+    y = lt.custom_ops.Registry.call("cube", [x])
+    lt.Ops.sum(y).backward()
+    assert y.to_vector() == [1.0, 8.0] and x.grad.to_vector() == [3.0, 12.0]
+    assert lt.custom_ops.Registry.has("cube")
+    with pytest.raises(KeyError):
+        lt.custom_ops.Registry.call("nope", [x])
