@@ -19,6 +19,8 @@ _SIGS = {
     "lt_status_fetch": [],
     "lt_sm_count": [],
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
+    "lt_gemm_fp8_block": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp, _vp, _i, _vp, _i, _vp],
+    "lt_quant_fp8_1x128": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
     "lt_norm_bwd_ctas": [_i],
     "lt_norm_fwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_norm_bwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -167,6 +169,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
                              residual.stride(0) if residual is not None else 0, act, 1 if accumulate else 0,
                              float(alpha), block_n, max_ctas, _stream())
     _check(rc, "lt_gemm_bf16")
+    return out
+
+
+def quant_fp8_1x128(x):
+    """x [M, K] bf16 (K a multiple of 128) -> (e4m3 codes [M, K], scales [K/128, M] fp32, K-block major)."""
+    M, K = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and K % 128 == 0
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    st = torch.empty(K // 128, M, dtype=torch.float32, device=x.device)
+    rc = _fn("lt_quant_fp8_1x128")(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), st.data_ptr(), M, K, _stream())
+    _check(rc, "lt_quant_fp8_1x128")
+    return q, st
+
+
+def gemm_fp8_block(a8, a_scale_t, b8, b_scale, out=None, *, bias=None, out_dtype=torch.bfloat16, max_ctas=0):
+    """out[M, N] = block-scaled a8[M, K] @ b8[N, K]^T.  a_scale_t: [K/128, M] fp32; b_scale: [ceil(N/128), K/128] fp32."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    assert a8.dtype == torch.float8_e4m3fn and b8.dtype == torch.float8_e4m3fn and b8.shape[1] == K
+    assert a8.stride(1) == 1 and b8.stride(1) == 1 and K % 128 == 0
+    assert a_scale_t.shape == (K // 128, M) and a_scale_t.is_contiguous() and a_scale_t.dtype == torch.float32
+    assert b_scale.shape == ((N + 127) // 128, K // 128) and b_scale.is_contiguous() and b_scale.dtype == torch.float32
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    rc = _fn("lt_gemm_fp8_block")(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), M, N, K, a8.stride(0), b8.stride(0),
+                                  out.stride(0), a_scale_t.data_ptr(), b_scale.data_ptr(),
+                                  1 if out.dtype == torch.float32 else 0, _p(bias), max_ctas, _stream())
+    _check(rc, "lt_gemm_fp8_block")
     return out
 
 

@@ -146,7 +146,13 @@ def quantize_fp8_128x128(w: torch.Tensor):
 
 def fp8_block_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """y = x @ w^T with both operands rounded to block-scaled e4m3 (1x128 / 128x128) and fp32 accumulation.
-    Reference semantics of the fp8 GEMM path; the arithmetic is carried out on dequantised values."""
+    On a GPU the product runs on the tcgen05 fp8 kernel (two-level accumulation, fp32 scales); on the host the same
+    arithmetic is carried out on dequantised values."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from .ops import kernels as K
+        xq, xst = K.quant_fp8_1x128(x.contiguous())
+        wq, ws = quantize_fp8_128x128(w)
+        return K.gemm_fp8_block(xq, xst, wq, ws.contiguous())
     xq, xs = quantize_fp8_1x128(x)
     wq, ws = quantize_fp8_128x128(w)
     xd = (xq.float().view(x.shape[0], -1, 128) * xs[..., None]).view_as(x)

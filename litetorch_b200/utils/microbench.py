@@ -1,6 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing with an L2 flush between iterations.
 
     python -m litetorch_b200.utils.microbench gemm [--out FILE]
+    python -m litetorch_b200.utils.microbench fp8
     python -m litetorch_b200.utils.microbench attn
     python -m litetorch_b200.utils.microbench pointwise
 
@@ -102,6 +103,37 @@ def bench_gemm(out=None):
     return rows
 
 
+def bench_fp8(out=None):
+    """Block-scaled e4m3 GEMM (1x128 / 128x128 scales) against the bf16 kernel on the same shapes."""
+    from ..ops import kernels as K
+    pk = peaks()
+    rows = []
+    for M, N, Kd, tag in [(8192, 11264, 2048, "gate_up fwd"), (8192, 2048, 5632, "down fwd"), (8192, 8192, 8192, "square"),
+                          (16384, 4096, 7168, "moe 671B-style expert width")]:
+        x = torch.randn(M, Kd, device="cuda").bfloat16()
+        w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+        xq, xst = K.quant_fp8_1x128(x)
+        wq = w.to(torch.float8_e4m3fn)
+        ws = torch.ones((N + 127) // 128, Kd // 128, device="cuda")
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * Kd
+        ms = time_ms(lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c))
+        ms_q = time_ms(lambda: K.quant_fp8_1x128(x))
+        ms_bf = time_ms(lambda: K.gemm(x, w, out=c))
+        K.check_status()
+        row = {"kernel": "gemm_fp8_block", "tag": tag, "M": M, "N": N, "K": Kd, "ms": round(ms, 4),
+               "tflops": round(fl / ms / 1e9, 1), "x_bf16_%s_peak" % pk["src"]: round(fl / ms / 1e9 / pk["tflops"], 3),
+               "quant_ms": round(ms_q, 4), "quant_gbs": round(M * Kd * 3 / ms_q / 1e6, 1),
+               "bf16_kernel_ms": round(ms_bf, 4)}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    if out:
+        with open(out, "w") as f:
+            for r_ in rows:
+                f.write(json.dumps(r_) + "\n")
+    return rows
+
+
 def bench_attn(out=None):
     from ..ops import kernels as K
     pk = peaks()
@@ -180,4 +212,4 @@ def bench_pointwise(out=None):
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     out = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else None
-    {"gemm": bench_gemm, "attn": bench_attn, "pointwise": bench_pointwise}[what](out)
+    {"gemm": bench_gemm, "fp8": bench_fp8, "attn": bench_attn, "pointwise": bench_pointwise}[what](out)
