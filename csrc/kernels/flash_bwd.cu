@@ -137,17 +137,18 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
   auto qdo_full = [&](int s) { return bb + 8u * (1 + s); };
   auto qdo_empty = [&](int s) { return bb + 8u * (3 + s); };
   const uint32_t sdp_full = bb + 8u * 5;   // S and dP are in TMEM
-  const uint32_t sdp_free = bb + 8u * 6;   // compute threads have read S and dP (count 128)
-  const uint32_t pds_full = bb + 8u * 7;   // P and dS are in shared memory (count 128)
+  const uint32_t sdp_free = bb + 8u * 6;   // compute warps have read S and dP (one arrival per warp)
+  const uint32_t pds_full = bb + 8u * 7;   // P and dS are in shared memory (one arrival per warp)
   const uint32_t pds_empty = bb + 8u * 8;  // the three MMAs that read P / dS have executed
   const uint32_t dq_full = bb + 8u * 9;    // dQ_i is in TMEM
-  const uint32_t dq_free = bb + 8u * 10;   // compute threads have read dQ_i (count 128)
+  const uint32_t dq_free = bb + 8u * 10;   // compute warps have read dQ_i (one arrival per warp)
   const uint32_t dkv_full = bb + 8u * 11;  // all MMAs done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  // x fastest in launch order: all (head, batch) pairs of key block 0 (seen by every query, the longest loop) first
+  const int kv_blk = blockIdx.z, hkv = blockIdx.x, b = blockIdx.y;
   const int G = p.Hq / p.Hkv;
   const int kv0 = kv_blk * kFbBlock;
   QSeg* segs = reinterpret_cast<QSeg*>(smem + Cfg::kOffSeg);
@@ -209,9 +210,9 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads);
-    mbar_init(pds_full, kFbComputeThreads); mbar_init(pds_empty, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads);
+    mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads / 32);
+    mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -353,14 +354,25 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + c * 32, sv);
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDP + c * 32, dp);
         tmem_ld_wait();
+        const bool live = q_valid && lse2 != -INFINITY;
+        if (live && kv0 + c * 32 + 31 <= limit) {   // every column of the chunk is visible: no per-element test
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv_idx = kv0 + c * 32 + i;
-          float pv = 0.f;
-          if (q_valid && kv_idx <= limit && lse2 != -INFINITY) pv = ex2_approx(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
-          const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
-          sv[i] = __float_as_uint(pv);
-          dp[i] = __float_as_uint(ds);
+          for (int i = 0; i < 32; ++i) {
+            const float pv = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+            const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
+            sv[i] = __float_as_uint(pv);
+            dp[i] = __float_as_uint(ds);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kv_idx = kv0 + c * 32 + i;
+            float pv = 0.f;
+            if (live && kv_idx <= limit) pv = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+            const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
+            sv[i] = __float_as_uint(pv);
+            dp[i] = __float_as_uint(ds);
+          }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -380,10 +392,14 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
           *reinterpret_cast<uint4*>(dsrow + chunk * (128 * 128) + unit * 16) = z;
         }
       }
+      // one arrival per warp: 256 same-address arrivals on a shared-memory barrier serialise
       tc_fence_before();
-      mbar_arrive(sdp_free);
       fence_proxy_async();
-      mbar_arrive(pds_full);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sdp_free);
+        mbar_arrive(pds_full);
+      }
       // dQ_i
       ok = __all_sync(0xffffffffu, mbar_wait(dq_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
@@ -402,7 +418,8 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         }
       }
       tc_fence_before();
-      mbar_arrive(dq_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
     }
     // ---------------------------------------------------------------- dK / dV epilogue (row = key index)
     if (ok && n_iter > 0) ok = __all_sync(0xffffffffu, mbar_wait(dkv_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
@@ -464,7 +481,7 @@ static int launch_flash_bwd(const QMaps& qm, const CUtensorMap& tk, const CUtens
     LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
   }
-  dim3 grid((p.Tk + kFbBlock - 1) / kFbBlock, p.Hkv, p.B);
+  dim3 grid(p.Hkv, p.B, (p.Tk + kFbBlock - 1) / kFbBlock);
   kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(qm, tk, tv, p);
   LT_LAUNCH_CHECK();
   return 0;

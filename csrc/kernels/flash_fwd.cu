@@ -64,7 +64,7 @@ struct FaFwdCfg {
   static constexpr int kOffV = kOffK + 2 * kKVBytes;
   static constexpr int kOffP = kOffV + 2 * kKVBytes;
   static constexpr int kOffBar = kOffP + 2 * kPBytes;
-  static constexpr int kOffSeg = kOffBar + 160;               // KvSeg table (16 entries) + block count
+  static constexpr int kOffSeg = kOffBar + 192;               // KvSeg table (16 entries) + block count
   static constexpr int kOffX = kOffSeg + kFaMaxSegs * 16 + 16;                 // row statistics exchanged between the two column halves
   static constexpr int kNeeded = kOffX + 2 * 2 * 128 * 4;     // [parity][half][128] floats
   // 1 KB of slack for the 1024-byte alignment where it fits under the 227 KB limit; the kernel checks at run time
@@ -98,14 +98,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto p_full = [&](int s) { return bb + 8u * (11 + s); };
   auto p_empty = [&](int s) { return bb + 8u * (13 + s); };
   const uint32_t o_full = bb + 8u * 15;
-  const uint32_t x_bar = bb + 8u * 16;   // all softmax threads have published their partial row maximum
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+  // x_bar(quarter): both warps of a TMEM lane quarter have published their partial row statistics
+  auto x_bar = [&](int qtr) { return bb + 8u * (16 + qtr); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20);
   float* xmax = reinterpret_cast<float*>(smem + Cfg::kOffX);  // [2 (rendezvous parity)][2 (half)][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_blk = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Launch order is x fastest: every head and batch entry of the heaviest (latest) query block runs before any
+  // lighter block, and neighbouring CTAs are the query heads that share one KV head (the K/V tiles stay in L2).
+  const int q_blk = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = q_blk * kFaBlockQ;
   KvSeg* segs = reinterpret_cast<KvSeg*>(smem + Cfg::kOffSeg);
@@ -170,10 +173,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
       mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
-      mbar_init(s_full(s), 1); mbar_init(p_full(s), kFaSoftmaxThreads); mbar_init(p_empty(s), 1);
+      mbar_init(s_full(s), 1); mbar_init(p_full(s), kFaSoftmaxThreads / 32); mbar_init(p_empty(s), 1);
     }
     mbar_init(o_full, 1);
-    mbar_init(x_bar, kFaSoftmaxThreads);
+    for (int qtr = 0; qtr < 4; ++qtr) mbar_init(x_bar(qtr), 2);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -301,8 +304,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       // combine the row maximum of the two column halves (bounded mbarrier rendezvous, parity j & 1)
       xmax[(s * 2 + half) * 128 + row] = mx;
-      mbar_arrive(x_bar);
-      ok = __all_sync(0xffffffffu, mbar_wait(x_bar, uint32_t(j & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_bar(quarter));
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar(quarter), uint32_t(j & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
       if (!ok) break;
       mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + row]);
       const float m_blk = mx * p.scale_log2;
@@ -361,7 +365,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_full(s));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(s));   // one arrival per warp: same-address arrivals serialise
     }
     if (ok && n_blocks > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
@@ -370,8 +375,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // total row sum = sum of the two halves
       float* xsum = xmax + (n_blocks & 1) * 256;   // the slot of the next rendezvous parity
       xsum[half * 128 + row] = l;
-      mbar_arrive(x_bar);
-      ok = __all_sync(0xffffffffu, mbar_wait(x_bar, uint32_t(n_blocks & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_bar(quarter));
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar(quarter), uint32_t(n_blocks & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
       if (ok) l += xsum[(half ^ 1) * 128 + row];
     }
     if (ok) {
@@ -426,7 +432,7 @@ static int launch_flash_fwd(const CUtensorMap& tq, const KvMaps& maps, const Fla
     LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
   }
-  dim3 grid((p.Tq + kFaBlockQ - 1) / kFaBlockQ, p.Hq, p.B);
+  dim3 grid(p.Hq, p.B, (p.Tq + kFaBlockQ - 1) / kFaBlockQ);
   kern<<<grid, kFaThreads, Cfg::kSmemBytes, st>>>(tq, maps, p);
   LT_LAUNCH_CHECK();
   return 0;

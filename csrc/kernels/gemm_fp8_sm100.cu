@@ -6,12 +6,12 @@
 // the quantised Linear it sketches in python/litetorch/quantization.py.
 //
 // Two-level accumulation.  tcgen05.mma kind::f8f6f4 (128 x 128 x 32 per instruction, fp32 accumulate) computes
-// the UNSCALED product of one K block into one of four 128-column TMEM buffers; the eight epilogue warps read
+// the UNSCALED product of one K block into one of four 128-column TMEM buffers; the sixteen epilogue warps read
 // that partial with tcgen05.ld and fold it into fp32 register accumulators with the block's scale, so that the
 // scales are applied at full fp32 precision while the next K blocks are already running on the tensor core.
 //   warp 0: TMA producer (128-byte-swizzled 128 x 128-byte tiles of A8 and B8, 6 stages)
 //   warp 1: MMA issuer   (4 instructions per K block, commit -> stage free + partial ready)
-//   warps 2-9: promotion + epilogue (2 warps per TMEM lane quarter, 64 columns each)
+//   warps 2-17: promotion + epilogue (4 warps per TMEM lane quarter, 32 columns each)
 #include "common/host.h"
 #include "common/ptx.cuh"
 
@@ -23,7 +23,8 @@ constexpr int kF8BlockK = 128;   // elements == bytes
 constexpr int kF8UmmaK = 32;
 constexpr int kF8Stages = 6;
 constexpr int kF8Bufs = 4;
-constexpr int kF8Threads = 320;
+constexpr int kF8EpiWarps = 16;           // four per TMEM lane quarter, 32 columns each
+constexpr int kF8Threads = 64 + 32 * kF8EpiWarps;
 constexpr int kF8TileBytes = kF8BlockM * kF8BlockK;
 constexpr int kF8StageBytes = 2 * kF8TileBytes;
 constexpr int kF8SmemBytes = kF8Stages * kF8StageBytes + 1024 + 512;
@@ -77,7 +78,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int b = 0; b < kF8Bufs; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 8);
+      mbar_init(tempty_bar(b), kF8EpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -146,16 +147,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else {
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;      // which 64 columns of the tile
+    const int part = (warp - 2) >> 2;      // which 32 columns of the tile
     uint32_t it = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
       const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
       const int row = m_blk * kF8BlockM + quarter * 32 + lane;
       const int srow = row < p.M ? row : p.M - 1;
-      float acc[64];
+      float acc[32];
 #pragma unroll
-      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
       float s_next = p.a_scale[srow] * p.b_scale[(long long)n_blk * p.k_blocks];
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
         const float s = s_next;
@@ -166,44 +167,40 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool got = mbar_wait(tfull_bar(buf), aphase, abort_flag, p.status, kStatusTimeoutTmemFull);
         if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kF8BlockN + half * 64;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(taddr, r0);
-        tmem_ld_32x32(taddr + 32, r1);
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * kF8BlockN + part * 32, r);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          acc[j] = fmaf(s, __uint_as_float(r0[j]), acc[j]);
-          acc[32 + j] = fmaf(s, __uint_as_float(r1[j]), acc[32 + j]);
-        }
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(s, __uint_as_float(r[j]), acc[j]);
       }
       if (!alive || row >= p.M) continue;
-      const int col0 = n_blk * kF8BlockN + half * 64;
-      const bool vec = (col0 + 64 <= p.N) && (p.out_fp32 ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0));
+      const int col0 = n_blk * kF8BlockN + part * 32;
+      if (col0 >= p.N) continue;
+      const bool vec = (col0 + 32 <= p.N) && (p.out_fp32 ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0));
       if (p.bias) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
+        for (int j = 0; j < 32; ++j)
           if (col0 + j < p.N) acc[j] += __bfloat162float(p.bias[col0 + j]);
       }
       if (p.out_fp32) {
         float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
         if (vec) {
 #pragma unroll
-          for (int q = 0; q < 16; ++q)
+          for (int q = 0; q < 8; ++q)
             reinterpret_cast<float4*>(cp)[q] = make_float4(acc[q * 4], acc[q * 4 + 1], acc[q * 4 + 2], acc[q * 4 + 3]);
         } else {
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) cp[j] = acc[j];
         }
       } else {
         __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
         if (vec) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
+          for (int q = 0; q < 4; ++q) {
             uint4 o;
             o.x = pack_bf16x2(acc[q * 8 + 0], acc[q * 8 + 1]);
             o.y = pack_bf16x2(acc[q * 8 + 2], acc[q * 8 + 3]);
@@ -213,7 +210,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) cp[j] = __float2bfloat16(acc[j]);
         }
       }

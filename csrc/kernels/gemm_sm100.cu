@@ -2,6 +2,12 @@
 // Replaces the cuBLAS calls of the reference (src/backend/gpu_native/math/gemm.cu:3-189) and the
 // backward GEMM pair of src/ops/linear.cpp:30-68, with bias / GELU / residual / accumulate epilogues.
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 namespace lt {
 
@@ -25,9 +31,82 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return 0;
 }
 
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p);
+}
+
+template <int A_MAJOR, int B_MAJOR>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_bf16_pair_kernel<A_MAJOR, B_MAJOR>;
+  if (!configured) {
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kPairSmemBytes, st>>>(tmA, tmB, p);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// 0: never use CTA pairs; 1: where the cost model prefers them; 2: wherever the shape allows.
+static std::atomic<int> g_pair_mode{1};
+
+// Workspace of the split tail, one per (device, stream): launches on one stream are serialised, so the partial
+// tiles and the flags of one launch are consumed before the next launch writes them.
+struct SplitWs {
+  float* ws = nullptr;
+  unsigned* flags = nullptr;
+};
+constexpr int kSplitSlots = 160;                                   // >= SM count: at most one partial per CTA
+constexpr size_t kSplitSlotBytes = size_t(kBlockM) * 256 * 4;      // one 128 x 256 fp32 partial
+static std::mutex g_split_mu;
+static std::map<std::pair<int, cudaStream_t>, SplitWs> g_split_ws;
+static std::atomic<int> g_split_enabled{1};
+
+static bool get_split_ws(cudaStream_t st, SplitWs* out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(g_split_mu);
+  auto key = std::make_pair(dev, st);
+  auto it = g_split_ws.find(key);
+  if (it != g_split_ws.end()) { *out = it->second; return out->ws != nullptr; }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return false;   // no allocation while a graph is being captured: this launch runs without the split
+  }
+  SplitWs w;
+  void* base = nullptr;
+  if (cudaMalloc(&base, kSplitSlots * kSplitSlotBytes + kSplitSlots * 4 * sizeof(unsigned)) != cudaSuccess) {
+    cudaGetLastError();
+    g_split_ws[key] = SplitWs{};
+    return false;
+  }
+  w.ws = static_cast<float*>(base);
+  w.flags = reinterpret_cast<unsigned*>(static_cast<char*>(base) + kSplitSlots * kSplitSlotBytes);
+  if (cudaMemsetAsync(w.flags, 0, kSplitSlots * 4 * sizeof(unsigned), st) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(base);
+    g_split_ws[key] = SplitWs{};
+    return false;
+  }
+  g_split_ws[key] = w;
+  *out = w;
+  return true;
+}
+
 }  // namespace lt
 
 extern "C" {
+
+// 0: one CTA per tile only; 1 (default): CTA pairs (256 x 256 tiles on cta_group::2) where the cost model prefers
+// them; 2: CTA pairs for every shape.
+void lt_gemm_set_pair_mode(int mode) { lt::g_pair_mode.store(mode < 0 ? 0 : (mode > 2 ? 2 : mode)); }
+
+// 1 (default): GEMMs whose last wave fills only part of the GPU cut the tiles of that wave along K.  0: off.
+void lt_gemm_set_tail_split(int enable) { lt::g_split_enabled.store(enable ? 1 : 0); }
 
 // C[M,N] = epilogue(alpha * op(A) * op(B)).  See gemm_sm100.cuh for the operand layouts.
 // lda/ldb/ldc/ldr are pitches in elements. block_n: 0 = choose, else 128 or 256. max_ctas: 0 = one per SM.
@@ -41,7 +120,40 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -int(kStatusBadArgument);
   const int sms = sm_count();
-  if (block_n != 128 && block_n != 256) block_n = pick_block_n(M, N, sms);
+  const bool split_on = g_split_enabled.load() != 0;
+  const int pair_mode = g_pair_mode.load();
+  if (pair_mode > 0 && block_n != 128 && (max_ctas <= 0 || max_ctas >= sms)) {
+    const double c256 = wave_cost(M, N, K, sms, 256), c128 = wave_cost(M, N, K, sms, 128);
+    const double single = c256 < c128 ? c256 : c128;
+    if (pair_mode == 2 || pair_cost(M, N, sms) < single) {
+      GemmParams q{};
+      q.M = M; q.N = N; q.K = K;
+      q.C = C; q.ldc = ldc; q.out_fp32 = out_fp32;
+      q.bias = static_cast<const __nv_bfloat16*>(bias);
+      q.residual = static_cast<const __nv_bfloat16*>(residual);
+      q.ldr = ldr; q.act = act; q.accumulate = accumulate; q.alpha = alpha;
+      q.status = device_status_word();
+      fill_tiles(q, kPairBlockN);
+      q.m_blocks = (M + kPairBlockM - 1) / kPairBlockM;
+      q.num_tiles = q.m_blocks * q.n_blocks;
+      q.dp_tiles = q.num_tiles;
+      q.group_m = 8;
+      CUtensorMap tmA, tmB;
+      int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_major, b_major, kPairBlockN / 2);
+      if (r) return r;
+      int pairs = sms / 2;
+      if (pairs > q.num_tiles) pairs = q.num_tiles;
+      cudaStream_t st = static_cast<cudaStream_t>(stream);
+      const int key2 = (a_major ? 2 : 0) | (b_major ? 1 : 0);
+      switch (key2) {
+        case 0: return launch_gemm_pair<0, 0>(tmA, tmB, q, 2 * pairs, st);
+        case 1: return launch_gemm_pair<0, 1>(tmA, tmB, q, 2 * pairs, st);
+        case 2: return launch_gemm_pair<1, 0>(tmA, tmB, q, 2 * pairs, st);
+        default: return launch_gemm_pair<1, 1>(tmA, tmB, q, 2 * pairs, st);
+      }
+    }
+  }
+  if (block_n != 128 && block_n != 256) block_n = split_on ? pick_block_n_split(M, N, K, sms) : pick_block_n(M, N, sms);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
@@ -57,6 +169,17 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > p.num_tiles) grid = p.num_tiles;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (split_on) {
+    const int split = tail_split(p.num_tiles, p.k_blocks, grid);
+    SplitWs w;
+    if (split > 1 && get_split_ws(st, &w)) {
+      p.dp_tiles = (p.num_tiles / grid) * grid;
+      p.sk_tiles = p.num_tiles - p.dp_tiles;
+      p.sk_split = split;
+      p.sk_ws = w.ws;
+      p.sk_flags = w.flags;
+    }
+  }
   const int key = (block_n == 256 ? 4 : 0) | (a_major ? 2 : 0) | (b_major ? 1 : 0);
   switch (key) {
     case 0: return launch_gemm<128, 0, 0>(tmA, tmB, p, grid, st);

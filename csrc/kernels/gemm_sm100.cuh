@@ -60,7 +60,38 @@ struct GemmParams {
   const float* row_scale;
   const int2* row_table;
   float* acc_ptrs[8];
+  // Split tail: tiles [0, dp_tiles) are computed whole, one per CTA per wave; when the last wave would leave most SMs
+  // idle, each of the remaining sk_tiles tiles is cut along K into sk_split parts that run on different CTAs.  Parts
+  // 1..sk_split-1 dump their fp32 accumulators into sk_ws and bump sk_flags[tile * 4 + lane quarter]; part 0 waits for
+  // them (bounded), adds them to its own accumulator and runs the normal epilogue.  sk_split <= 1: no split.
+  int dp_tiles, sk_tiles, sk_split;
+  float* sk_ws;          // [sk_tiles][sk_split - 1][BLOCK_N / 32][128][32]
+  unsigned* sk_flags;    // [sk_tiles][4], zero between launches
 };
+
+struct WorkItem {
+  int tile, kb0, kb1;
+  int split;   // -1: whole tile; 0: owner of a split tile; > 0: contributor
+  int slot;    // index of the split tile (0 .. sk_tiles-1)
+};
+
+// The i-th piece of work of CTA cta_id out of cta_count.
+__device__ __forceinline__ bool get_item(const GemmParams& p, int cta_id, int cta_count, int i, WorkItem& w) {
+  const int tile = cta_id + i * cta_count;
+  if (tile < p.dp_tiles) {
+    w.tile = tile; w.kb0 = 0; w.kb1 = p.k_blocks; w.split = -1; w.slot = 0;
+    return true;
+  }
+  if (p.sk_split > 1 && i == p.dp_tiles / cta_count && cta_id < p.sk_tiles * p.sk_split) {
+    const int t = cta_id % p.sk_tiles, part = cta_id / p.sk_tiles;
+    w.tile = p.dp_tiles + t;
+    w.kb0 = int((long long)part * p.k_blocks / p.sk_split);
+    w.kb1 = int((long long)(part + 1) * p.k_blocks / p.sk_split);
+    w.split = part; w.slot = t;
+    return true;
+  }
+  return false;
+}
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -277,11 +308,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cta_id; ok && tile < p.num_tiles; tile += cta_count) {
+      WorkItem w;
+      for (int i = 0; ok && get_item(p, cta_id, cta_count, i, w); ++i) {
         int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
-        for (int kl = 0; kl < p.k_blocks; ++kl) {
-          int kb = kl + p.k_rot;
+        tile_coords(p, w.tile, m_blk, n_blk);
+        for (int kl = w.kb0; kl < w.kb1; ++kl) {
+          int kb = kl + p.k_rot;   // k_rot is only used with whole tiles
           if (kb >= p.k_blocks) kb -= p.k_blocks;
           if (!gate(m_blk, n_blk, kb, p.status)) { *abort_flag = 1; ok = false; break; }
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
@@ -316,14 +348,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int it = 0;
-      for (int tile = cta_id; ok && tile < p.num_tiles; tile += cta_count, ++it) {
+      WorkItem w;
+      for (int it = 0; ok && get_item(p, cta_id, cta_count, it, w); ++it) {
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aphase ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
@@ -334,7 +366,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -345,21 +377,85 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
-    int it = 0;
-    for (int tile = cta_id; tile < p.num_tiles; tile += cta_count, ++it) {
+    WorkItem w;
+    for (int it = 0; get_item(p, cta_id, cta_count, it, w); ++it) {
       int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      tile_coords(p, w.tile, m_blk, n_blk);
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       const bool got = mbar_wait(tfull_bar(buf), aphase, abort_flag, p.status, kStatusTimeoutTmemFull);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
       const int row = m_blk * kBlockM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
+      if (w.split > 0) {
+        // contributor of a split tile: raw accumulators to the workspace, then one arrival per warp
+        float* ws = p.sk_ws + ((long long)(w.slot * (p.sk_split - 1) + (w.split - 1)) * (BLOCK_N / 32)) * (kBlockM * 32) +
+                    (quarter * 32 + lane) * 32;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(ws + (long long)c * (kBlockM * 32));
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            dst[q] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                 __uint_as_float(r[q * 4 + 3]));
+        }
+        __threadfence();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(tempty_bar(buf));
+          red_add_release_gpu(p.sk_flags + w.slot * 4 + quarter, 1u);
+        }
+        continue;
+      }
+      bool parts_ok = true;
+      if (w.split == 0) {
+        // owner of a split tile: the other parts of this lane quarter must have landed
+        int okf = 1;
+        if (lane == 0) {
+          okf = wait_flag_ge_gpu(p.sk_flags + w.slot * 4 + quarter, uint32_t(p.sk_split - 1), p.status) ? 1 : 0;
+          if (okf) p.sk_flags[w.slot * 4 + quarter] = 0u;   // the only waiter resets it for the next launch
+        }
+        parts_ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+      }
+      if (!parts_ok) { *abort_flag = 1; break; }
+      // Sum of the other parts' accumulators for one 32-column chunk; issued one chunk ahead so that the loads
+      // (L2 latency) overlap the epilogue of the previous chunk.
+      float4 pre[8];
+      auto load_parts = [&](int c) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) pre[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < p.sk_split - 1; ++j) {
+          const float4* src = reinterpret_cast<const float4*>(
+              p.sk_ws + ((long long)(w.slot * (p.sk_split - 1) + j) * (BLOCK_N / 32) + c) * (kBlockM * 32) +
+              (quarter * 32 + lane) * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 v = __ldcg(src + q);
+            pre[q].x += v.x; pre[q].y += v.y; pre[q].z += v.z; pre[q].w += v.w;
+          }
+        }
+      };
+      if (w.split == 0) load_parts(0);
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N + c * 32, r);
+        tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
+        if (w.split == 0) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + pre[q].x);
+            r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + pre[q].y);
+            r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + pre[q].z);
+            r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + pre[q].w);
+          }
+          if (c + 1 < BLOCK_N / 32) load_parts(c + 1);
+        }
         const int col0 = n_blk * BLOCK_N + c * 32;
         if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
       }
@@ -415,6 +511,37 @@ inline void fill_tiles(GemmParams& p, int block_n) {
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.group_m = 16;
   p.raster = 0; p.rot = 0; p.k_rot = 0;
+  p.dp_tiles = p.num_tiles; p.sk_tiles = 0; p.sk_split = 1;
+  p.sk_ws = nullptr; p.sk_flags = nullptr;
+}
+
+// How many ways the tiles of the last, partly filled wave are cut along K (1 = not cut) on `grid` CTAs.
+inline int tail_split(int num_tiles, int k_blocks, int grid) {
+  if (grid <= 0 || num_tiles <= grid) return 1;        // a single wave: nothing to balance against
+  const int rem = num_tiles % grid;
+  if (rem == 0) return 1;
+  // Measured on B200: the cut pays off only when a tile's K loop is long (the tail wave of a short-K GEMM is bound
+  // by L2 bandwidth, not by the tensor core, and already runs faster with fewer CTAs) and with few parts per tile.
+  if (k_blocks < 64) return 1;
+  int s = grid / rem;
+  if (s > 4) s = 4;
+  return s < 1 ? 1 : s;
+}
+
+// Time of a GEMM in units of one full 128 x 256 tile wave, used to pick the tile width.
+inline double wave_cost(int M, int N, int K, int sms, int bn) {
+  const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + bn - 1) / bn);
+  const int grid = tiles < sms ? tiles : sms;
+  const int kb = (K + kBlockK - 1) / kBlockK;
+  const int s = tail_split(tiles, kb, grid);
+  double waves;
+  if (s > 1) waves = double(tiles / grid) + 1.0 / s + 0.06;   // + the workspace round trip of the cut tiles
+  else       waves = double((tiles + grid - 1) / grid);
+  return waves * (bn == 256 ? 1.0 : 0.5 / 0.84);   // measured: the 128-wide tile runs at ~0.84 of the 256-wide one
+}
+
+inline int pick_block_n_split(int M, int N, int K, int sms) {
+  return wave_cost(M, N, K, sms, 256) <= wave_cost(M, N, K, sms, 128) ? 256 : 128;
 }
 
 // Host: tensor maps for the two operands.

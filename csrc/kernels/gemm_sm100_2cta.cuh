@@ -1,0 +1,190 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs computes one 256 x 256 output tile.
+//
+// With one CTA per 128 x 256 tile every SM pulls 48 KB of operands from L2 per 64-deep K block, which is more
+// than an SM can take in while its tensor core runs flat out.  In a pair each CTA loads its own 128 rows of A and
+// only HALF of the B tile (128 of the 256 columns); the MMA, issued by one thread of the even CTA, reads the B
+// halves from both CTAs' shared memory and writes 128 accumulator rows into each CTA's tensor memory.  Operand
+// traffic per SM drops to 32 KB per K block and the pipeline is 6 stages deep.
+//
+// Roles per CTA (192 threads): warp 0 TMA producer (both CTAs; the bytes of both are counted on the even CTA's
+// full barrier), warp 1 TMEM allocation in both CTAs and MMA issue in the even CTA only, warps 2-5 epilogue of the
+// CTA's own 128 rows (they release the accumulator buffer on the even CTA's barrier).
+// The reference reaches its GEMMs through cuBLAS (src/backend/gpu_native/math/gemm.cu:3-189).
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace lt {
+
+constexpr int kPairBlockM = 256;   // rows of the pair's tile (128 per CTA)
+constexpr int kPairBlockN = 256;   // columns of the pair's tile (each CTA stages 128 of them)
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kBlockM * kBlockK * 2 + (kPairBlockN / 2) * kBlockK * 2;   // 32 KB
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 512;
+
+// Time of the GEMM on CTA pairs in the unit of wave_cost (one wave of 128 x 256 tiles on every SM).
+inline double pair_cost(int M, int N, int sms) {
+  const int tiles = ((M + kPairBlockM - 1) / kPairBlockM) * ((N + kPairBlockN - 1) / kPairBlockN);
+  const int pairs = sms / 2;
+  const int waves = (tiles + pairs - 1) / pairs;
+  return waves * 0.88;   // a pair wave does the work of one single-CTA wave, measured 10-14 % faster (operand sharing)
+}
+
+// p.m_blocks / p.n_blocks / p.num_tiles count 256 x 256 tiles; everything else as in gemm_body.
+template <int A_MAJOR, int B_MAJOR>
+__device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p) {
+  constexpr int S = kPairStages;
+  constexpr int kABytes = kBlockM * kBlockK * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kPairStageBytes);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };            // used in the even CTA
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };     // one per CTA, signalled by the MMA commit
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); }; // one per CTA, signalled by the MMA commit
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };  // even CTA: 8 epilogue warps arrive
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = (cta_rank == 0);
+  const int pair_id = int(blockIdx.x) >> 1;
+  const int pair_count = int(gridDim.x) >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(tmA);
+    tma_prefetch_desc(tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_holder), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();   // both CTAs' barriers are initialised before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_count) {
+        int m_blk, n_blk;
+        tile_coords(p, tile, m_blk, n_blk);
+        const int m0 = m_blk * kPairBlockM + int(cta_rank) * kBlockM;
+        const int n0 = n_blk * kPairBlockN + int(cta_rank) * (kPairBlockN / 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
+          const uint32_t fb = full_bar(stage);
+          if (leader) mbar_expect_tx(fb, 2 * kPairStageBytes);   // this CTA's tiles and the odd CTA's
+          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          if (A_MAJOR == 0) {
+            tma_load_2d_pair(a_dst, tmA, fb, kb * kBlockK, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBlockM / 64; ++i)
+              tma_load_2d_pair(a_dst + i * (64 * kBlockK * 2), tmA, fb, m0 + i * 64, kb * kBlockK);
+          }
+          if (B_MAJOR == 0) {
+            tma_load_2d_pair(b_dst, tmB, fb, kb * kBlockK, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < (kPairBlockN / 2) / 64; ++i)
+              tma_load_2d_pair(b_dst + i * (64 * kBlockK * 2), tmB, fb, n0 + i * 64, kb * kBlockK);
+          }
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, 1, A_MAJOR, B_MAJOR);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_count, ++it) {
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aphase ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kPairBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kPairStageBytes;
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t adesc = (A_MAJOR == 0) ? make_smem_desc_sw128(a_addr + k * (kUmmaK * 2), 16, 1024)
+                                                  : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
+            const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
+                                                  : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(tfull_bar(buf), 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps per CTA, own 128 rows)
+    const int quarter = warp & 3;
+    int it = 0;
+    for (int tile = pair_id; tile < p.num_tiles; tile += pair_count, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const bool got = mbar_wait(tfull_bar(buf), aphase, abort_flag, p.status, kStatusTimeoutTmemFull);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      const int row = m_blk * kPairBlockM + int(cta_rank) * kBlockM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kPairBlockN;
+#pragma unroll 1
+      for (int c = 0; c < kPairBlockN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * kPairBlockN + c * 32;
+        if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_bar(buf), 0);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // A bounded wait ran out: give copies that may still be in flight time to land before shared memory goes away.
+    for (int spin = 0; spin < 20000; ++spin) __nanosleep(100);
+  }
+  cluster_sync_all();   // neither CTA frees tensor memory or leaves while its partner's MMAs or loads may touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+}  // namespace lt

@@ -19,6 +19,8 @@ _SIGS = {
     "lt_status_fetch": [],
     "lt_sm_count": [],
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
+    "lt_gemm_set_tail_split": [_i],
+    "lt_gemm_set_pair_mode": [_i],
     "lt_gemm_fp8_block": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp, _vp, _i, _vp, _i, _vp],
     "lt_quant_fp8_1x128": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
     "lt_norm_bwd_ctas": [_i],
@@ -65,7 +67,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_gemm_set_pair_mode": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -170,6 +172,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
                              float(alpha), block_n, max_ctas, _stream())
     _check(rc, "lt_gemm_bf16")
     return out
+
+
+def gemm_set_tail_split(enable: bool):
+    """Turn the K-split of the last, partly filled tile wave of `gemm` on (default) or off."""
+    _fn("lt_gemm_set_tail_split")(1 if enable else 0)
+
+
+def gemm_set_pair_mode(mode: int):
+    """0: one CTA per tile only; 1 (default): CTA pairs (cta_group::2, 256 x 256 tiles) where the cost model
+    prefers them; 2: CTA pairs for every shape."""
+    _fn("lt_gemm_set_pair_mode")(int(mode))
 
 
 def quant_fp8_1x128(x):

@@ -81,17 +81,29 @@ def bench_gemm(out=None):
         b = torch.randn((N, Kd) if bm == 0 else (Kd, N), device="cuda").bfloat16()
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         fl = 2.0 * M * N * Kd
+        K.gemm_set_pair_mode(0)
         best = None
         for bn in (128, 256):
             ms = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c, block_n=bn))
             if best is None or ms < best[0]:
                 best = (ms, bn)
+        K.gemm_set_pair_mode(2)
+        ms_pair = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_pair_mode(1)
+        ms_auto = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_tail_split(False)
+        K.gemm_set_pair_mode(0)
+        ms_whole = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_pair_mode(1)
+        K.gemm_set_tail_split(True)
         A = a if am == 0 else a.t()
         B = b.t() if bm == 0 else b
         ms_ref = time_ms(lambda: torch.matmul(A, B, out=c))
         K.check_status()
         row = {"kernel": "gemm_bf16", "tag": tag, "M": M, "N": N, "K": Kd, "a_major": am, "b_major": bm,
-               "block_n": best[1], "ms": round(best[0], 4), "tflops": round(fl / best[0] / 1e9, 1),
+               "block_n": best[1], "ms": round(best[0], 4), "pair_ms": round(ms_pair, 4), "auto_ms": round(ms_auto, 4),
+               "auto_tflops": round(fl / ms_auto / 1e9, 1),
+               "auto_no_tail_split_ms": round(ms_whole, 4), "tflops": round(fl / best[0] / 1e9, 1),
                "frac_of_%s_peak" % pk["src"]: round(fl / best[0] / 1e9 / pk["tflops"], 3),
                "cublas_ms": round(ms_ref, 4), "cublas_tflops": round(fl / ms_ref / 1e9, 1)}
         rows.append(row)

