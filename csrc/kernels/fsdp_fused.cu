@@ -18,6 +18,7 @@
 // 3. lt_embedding_fwd_sharded: embedding rows fetched from the owning rank.
 // 4. lt_signal_barrier: all-ranks barrier on symmetric flags (bounded wait).
 #include "comm_common.cuh"
+#include "gemm_sm100_2cta.cuh"
 
 namespace lt {
 
@@ -160,6 +161,20 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // GEMM CTAs see a grid that starts at n_comm.
   FlagGate gate{g.flags, g.epoch, g.gate_dim, -1};
   gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, gate, ProgressDone{pf.progress}, g.n_comm);
+}
+
+// The same kernel on CTA pairs (256 x 256 tiles, cta_group::2).  n_comm is even, so gather CTAs pair with gather CTAs
+// and never take part in a pair's barriers.
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+ag_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                    const GatherArgs g, const PrefetchArgs pf) {
+  if (int(blockIdx.x) < g.n_comm) {
+    gather_cta(g, pf, p.status);
+    return;
+  }
+  FlagGate gate{g.flags, g.epoch, g.gate_dim, -1};
+  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, gate, ProgressDone{pf.progress}, g.n_comm);
 }
 
 // ---------------------------------------------------------------------------------------------- RS + AdamW
@@ -307,6 +322,28 @@ static int launch_ag_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return 0;
 }
 
+template <int A_MAJOR, int B_MAJOR>
+static int launch_ag_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const GatherArgs& g,
+                               const PrefetchArgs& pf, int grid, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = ag_gemm_pair_kernel<A_MAJOR, B_MAJOR>;
+  constexpr int kSmem = kPairSmemBytes > kGatherStages * kGatherStageBytes + 2048 ? kPairSmemBytes
+                                                                                  : kGatherStages * kGatherStageBytes + 2048;
+  if (!configured) {
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kSmem, st>>>(tmA, tmB, p, g, pf);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// Whether a gather-GEMM of this shape runs on CTA pairs (the decision must be the same wherever tile counts are
+// derived: the kernel launch, the progress target of a prefetch and lt_gemm_num_tiles).
+static bool ag_use_pairs(int M, int n_comm, int sms) {
+  return gemm_pair_mode() > 0 && M > kBlockM && (n_comm % 2 == 0) && ((sms - n_comm) % 2 == 0);
+}
+
 }  // namespace lt
 
 namespace lt {
@@ -359,7 +396,8 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   const int sms = sm_count();
   if (n_comm <= 0) n_comm = 8;
   if (n_comm > sms / 2) n_comm = sms / 2;
-  int block_n = pick_block_n(M, N, sms - n_comm);
+  const bool pairs = ag_use_pairs(M, n_comm, sms);
+  int block_n = pairs ? kPairBlockN : pick_block_n(M, N, sms - n_comm);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
@@ -378,12 +416,13 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   g.n_comm = n_comm;
   int rot = 0;
   setup_gather(g, gather_operand, M, N, K, block_n, rank, rows_per_rank, rot);
-  if (gather_operand == 0) { p.raster = 2; p.rot = rot; }
+  if (pairs) fill_pair_tiles(p);
+  if (gather_operand == 0) { p.raster = 2; p.rot = pairs ? rot / 2 : rot; }   // chunks of A are 128 rows, pair tiles 256
   else if (gather_operand == 1) { p.raster = 1; p.rot = rot; }
   else { p.k_rot = rot; }
   PrefetchArgs pf{};
   pf.progress = static_cast<uint32_t*>(progress);
-  pf.progress_target = progress_base + uint32_t(p.num_tiles) * 4u;
+  pf.progress_target = progress_base + uint32_t(p.num_tiles) * (pairs ? 8u : 4u);   // epilogue warps per tile
   if (next && progress && next->M > 0) {
     GatherArgs& n = pf.next;
     for (int r = 0; r < world; ++r) n.shard[r] = static_cast<const __nv_bfloat16*>(next->shard_ptrs[r]);
@@ -392,17 +431,24 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
     n.epoch = next->epoch;
     n.world = world; n.rank = rank; n.rows_per_rank = next->rows_per_rank; n.n_comm = n_comm;
     int nrot = 0;
-    setup_gather(n, next->gather_operand, next->M, next->N, next->K, pick_block_n(next->M, next->N, sms - n_comm), rank,
+    setup_gather(n, next->gather_operand, next->M, next->N, next->K,
+                 ag_use_pairs(next->M, n_comm, sms) ? kPairBlockN : pick_block_n(next->M, next->N, sms - n_comm), rank,
                  next->rows_per_rank, nrot);
     if ((long long)n.cols * 2 % 16 != 0) n.n_chunks = 0;
   }
   if ((long long)g.cols * 2 % 16 != 0) return -int(kStatusBadArgument);
   CUtensorMap tmA, tmB;
-  int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_major, b_major, block_n);
+  int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_major, b_major, pairs ? kPairBlockN / 2 : block_n);
   if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pairs) {
+    int grid = sms;
+    if ((grid - n_comm) / 2 > p.num_tiles) grid = 2 * p.num_tiles + n_comm;
+    if (a_major != 0) return -int(kStatusBadArgument);
+    return b_major ? launch_ag_gemm_pair<0, 1>(tmA, tmB, p, g, pf, grid, st) : launch_ag_gemm_pair<0, 0>(tmA, tmB, p, g, pf, grid, st);
+  }
   int grid = sms;
   if (grid - n_comm > p.num_tiles) grid = p.num_tiles + n_comm;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int key = (block_n == 256 ? 4 : 0) | (a_major ? 2 : 0) | (b_major ? 1 : 0);
   switch (key) {
     case 0: return launch_ag_gemm<128, 0, 0>(tmA, tmB, p, g, pf, grid, st);
@@ -413,8 +459,12 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   }
 }
 
+// Tile count of a gather-GEMM in units of four epilogue-warp completions (what the progress counter advances by).
 int lt_gemm_num_tiles(int M, int N, int n_comm) {
   using namespace lt;
+  if (n_comm <= 0) n_comm = 8;
+  if (ag_use_pairs(M, n_comm, sm_count()))
+    return 2 * ((M + kPairBlockM - 1) / kPairBlockM) * ((N + kPairBlockN - 1) / kPairBlockN);
   const int bn = pick_block_n(M, N, sm_count() - n_comm);
   return ((M + kBlockM - 1) / kBlockM) * ((N + bn - 1) / bn);
 }

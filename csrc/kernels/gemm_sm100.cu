@@ -34,7 +34,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 template <int A_MAJOR, int B_MAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p);
+  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), NoDone());
 }
 
 template <int A_MAJOR, int B_MAJOR>
@@ -52,6 +52,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 
 // 0: never use CTA pairs; 1: where the cost model prefers them; 2: wherever the shape allows.
 static std::atomic<int> g_pair_mode{1};
+int gemm_pair_mode() { return g_pair_mode.load(); }
 
 // Workspace of the split tail, one per (device, stream): launches on one stream are serialised, so the partial
 // tiles and the flags of one launch are consumed before the next launch writes them.
@@ -134,10 +135,7 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
       q.ldr = ldr; q.act = act; q.accumulate = accumulate; q.alpha = alpha;
       q.status = device_status_word();
       fill_tiles(q, kPairBlockN);
-      q.m_blocks = (M + kPairBlockM - 1) / kPairBlockM;
-      q.num_tiles = q.m_blocks * q.n_blocks;
-      q.dp_tiles = q.num_tiles;
-      q.group_m = 8;
+      fill_pair_tiles(q);
       CUtensorMap tmA, tmB;
       int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_major, b_major, kPairBlockN / 2);
       if (r) return r;

@@ -21,6 +21,17 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kBlockM * kBlockK * 2 + (kPairBlockN / 2) * kBlockK * 2;   // 32 KB
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 512;
 
+int gemm_pair_mode();   // 0 never, 1 where the cost model prefers pairs, 2 always (set by lt_gemm_set_pair_mode)
+
+// Tile counts of the pair kernel (256 x 256 tiles) in a GemmParams already filled by fill_tiles(p, 256).
+inline void fill_pair_tiles(GemmParams& p) {
+  p.m_blocks = (p.M + kPairBlockM - 1) / kPairBlockM;
+  p.n_blocks = (p.N + kPairBlockN - 1) / kPairBlockN;
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.dp_tiles = p.num_tiles;
+  p.group_m = 8;
+}
+
 // Time of the GEMM on CTA pairs in the unit of wave_cost (one wave of 128 x 256 tiles on every SM).
 inline double pair_cost(int M, int N, int sms) {
   const int tiles = ((M + kPairBlockM - 1) / kPairBlockM) * ((N + kPairBlockN - 1) / kPairBlockN);
@@ -30,8 +41,12 @@ inline double pair_cost(int M, int N, int sms) {
 }
 
 // p.m_blocks / p.n_blocks / p.num_tiles count 256 x 256 tiles; everything else as in gemm_body.
-template <int A_MAJOR, int B_MAJOR>
-__device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p) {
+// `gate(m_chunk, n_blk, kb, status)` and `done(m_chunk, n_blk)` are the hooks of gemm_body; m_chunk counts 128-row
+// blocks (the rows one CTA of the pair loads and writes), n_blk counts 256-column blocks.  CTAs [0, cta_first) of
+// the grid (an even number) belong to another role of a fused kernel.
+template <int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
+__device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
+                                               TileGate gate, TileDone done, int cta_first = 0) {
   constexpr int S = kPairStages;
   constexpr int kABytes = kBlockM * kBlockK * 2;
   extern __shared__ uint8_t smem_raw[];
@@ -50,8 +65,8 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();
   const bool leader = (cta_rank == 0);
-  const int pair_id = int(blockIdx.x) >> 1;
-  const int pair_count = int(gridDim.x) >> 1;
+  const int pair_id = (int(blockIdx.x) - cta_first) >> 1;
+  const int pair_count = (int(gridDim.x) - cta_first) >> 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -88,7 +103,11 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
         tile_coords(p, tile, m_blk, n_blk);
         const int m0 = m_blk * kPairBlockM + int(cta_rank) * kBlockM;
         const int n0 = n_blk * kPairBlockN + int(cta_rank) * (kPairBlockN / 2);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kl = 0; kl < p.k_blocks; ++kl) {
+          int kb = kl + p.k_rot;
+          if (kb >= p.k_blocks) kb -= p.k_blocks;
+          // (the odd CTA of the last pair may lie past M: it waits for the last real row block instead)
+          if (!gate(min(m0, p.M - 1) / kBlockM, n_blk, kb, p.status)) { *abort_flag = 1; ok = false; break; }
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
           const uint32_t fb = full_bar(stage);
           if (leader) mbar_expect_tx(fb, 2 * kPairStageBytes);   // this CTA's tiles and the odd CTA's
@@ -167,9 +186,13 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
         const int col0 = n_blk * kPairBlockN + c * 32;
         if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
       }
+      done.fence();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_bar(buf), 0);
+      if (lane == 0) {
+        mbar_arrive_cluster(tempty_bar(buf), 0);
+        done(m_blk * (kPairBlockM / kBlockM) + int(cta_rank), n_blk);
+      }
     }
   }
 

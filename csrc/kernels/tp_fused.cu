@@ -11,6 +11,7 @@
 // the block's counter shows that all ranks delivered it (bounded wait) and writes the bf16 result, optionally
 // adding a bias and a residual.
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
 
 namespace lt {
 
@@ -32,21 +33,20 @@ struct RsArgs {
 struct ArriveDone {
   uint32_t* const* peer_counters;
   int rows_per_rank;
+  int total_rows;
   __device__ __forceinline__ void fence() const { __threadfence_system(); }
   __device__ __forceinline__ void operator()(int m_blk, int) const {
     const int row0 = m_blk * kBlockM;
+    if (row0 >= total_rows) return;   // the odd CTA of a pair past the last row block
     const int owner = row0 / rows_per_rank;
     const int local_blk = (row0 - owner * rows_per_rank) / kBlockM;
     red_add_release_sys(peer_counters[owner] + local_blk, 1u);
   }
 };
 
-template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-               const RsArgs a) {
-  ArriveDone done{a.peer_counters, a.rows_per_rank};
-  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done);
+// Second phase of the fused kernels: sum the W staged partials of every local row block once its arrival counter
+// shows that all ranks delivered it (bounded wait), add bias / residual, write bf16.
+__device__ __forceinline__ void rs_reduce_phase(const GemmParams& p, const RsArgs& a) {
   // ---------------------------------------------------------------- reduce phase over this rank's row blocks
   __shared__ int ok_s;
   const int local_blocks = a.rows_per_rank / kBlockM;
@@ -98,6 +98,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+               const RsArgs a) {
+  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M};
+  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done);
+  rs_reduce_phase(p, a);
+}
+
+template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
 static int launch_gemm_rs(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const RsArgs& a, int grid,
                           cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
@@ -108,6 +117,29 @@ static int launch_gemm_rs(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
     configured = true;
   }
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmA, tmB, p, a);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                    const RsArgs a) {
+  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M};
+  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done);
+  rs_reduce_phase(p, a);
+}
+
+template <int A_MAJOR, int B_MAJOR>
+static int launch_gemm_rs_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const RsArgs& a, int grid,
+                               cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_rs_pair_kernel<A_MAJOR, B_MAJOR>;
+  if (!configured) {
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kPairSmemBytes, st>>>(tmA, tmB, p, a);
   LT_LAUNCH_CHECK();
   return 0;
 }
@@ -130,7 +162,8 @@ int lt_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long
   if (world < 1 || world > kRsMaxRanks || rows_per_rank % kBlockM != 0 || M != world * rows_per_rank || N % 8 != 0)
     return -int(kStatusBadArgument);
   const int sms = sm_count();
-  const int block_n = pick_block_n(M, N, sms);
+  const bool pairs = gemm_pair_mode() > 0 && M > kBlockM && sms % 2 == 0;
+  const int block_n = pairs ? kPairBlockN : pick_block_n(M, N, sms);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = nullptr; p.ldc = N; p.out_fp32 = 0;
@@ -141,8 +174,9 @@ int lt_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long
   p.rows_per_rank = rows_per_rank;
   p.src_rank = rank;
   // rows of the other ranks first (starting with rank + 1), this rank's rows last
+  if (pairs) fill_pair_tiles(p);
   p.raster = 2;
-  p.rot = (((rank + 1) % world) * rows_per_rank) / kBlockM;
+  p.rot = (((rank + 1) % world) * rows_per_rank) / (pairs ? kPairBlockM : kBlockM);
   RsArgs a{};
   a.stage = static_cast<const __nv_bfloat16*>(stage_ptrs[rank]);
   a.my_counters = static_cast<uint32_t*>(const_cast<void*>(counter_ptrs[rank]));
@@ -155,10 +189,14 @@ int lt_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long
   a.ldr = ldr;
   a.world = world; a.rank = rank; a.rows_per_rank = rows_per_rank; a.N = N; a.block_n = block_n;
   CUtensorMap tmA, tmB;
-  int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, 0, b_major, block_n);
+  int r = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, 0, b_major, pairs ? kPairBlockN / 2 : block_n);
   if (r) return r;
-  int grid = sms < p.num_tiles ? sms : p.num_tiles;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pairs) {
+    const int grid2 = 2 * (sms / 2 < p.num_tiles ? sms / 2 : p.num_tiles);
+    return b_major ? launch_gemm_rs_pair<0, 1>(tmA, tmB, p, a, grid2, st) : launch_gemm_rs_pair<0, 0>(tmA, tmB, p, a, grid2, st);
+  }
+  int grid = sms < p.num_tiles ? sms : p.num_tiles;
   if (block_n == 256) return b_major ? launch_gemm_rs<256, 0, 1>(tmA, tmB, p, a, grid, st) : launch_gemm_rs<256, 0, 0>(tmA, tmB, p, a, grid, st);
   return b_major ? launch_gemm_rs<128, 0, 1>(tmA, tmB, p, a, grid, st) : launch_gemm_rs<128, 0, 0>(tmA, tmB, p, a, grid, st);
 }
