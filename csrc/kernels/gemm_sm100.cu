@@ -126,7 +126,7 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   if (pair_mode > 0 && block_n != 128 && (max_ctas <= 0 || max_ctas >= sms)) {
     const double c256 = wave_cost(M, N, K, sms, 256), c128 = wave_cost(M, N, K, sms, 128);
     const double single = c256 < c128 ? c256 : c128;
-    if (pair_mode == 2 || pair_cost(M, N, sms) < single) {
+    if (pair_mode == 2 || pair_cost(M, N, K, sms, split_on) < single) {
       GemmParams q{};
       q.M = M; q.N = N; q.K = K;
       q.C = C; q.ldc = ldc; q.out_fp32 = out_fp32;
@@ -142,6 +142,17 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
       int pairs = sms / 2;
       if (pairs > q.num_tiles) pairs = q.num_tiles;
       cudaStream_t st = static_cast<cudaStream_t>(stream);
+      if (split_on) {
+        const int split = pair_tail_split(q.num_tiles, q.k_blocks, pairs);
+        SplitWs w;
+        if (split > 1 && get_split_ws(st, &w)) {
+          q.dp_tiles = (q.num_tiles / pairs) * pairs;
+          q.sk_tiles = q.num_tiles - q.dp_tiles;
+          q.sk_split = split;
+          q.sk_ws = w.ws;
+          q.sk_flags = w.flags;
+        }
+      }
       const int key2 = (a_major ? 2 : 0) | (b_major ? 1 : 0);
       switch (key2) {
         case 0: return launch_gemm_pair<0, 0>(tmA, tmB, q, 2 * pairs, st);

@@ -65,7 +65,7 @@ struct GemmParams {
   // 1..sk_split-1 dump their fp32 accumulators into sk_ws and bump sk_flags[tile * 4 + lane quarter]; part 0 waits for
   // them (bounded), adds them to its own accumulator and runs the normal epilogue.  sk_split <= 1: no split.
   int dp_tiles, sk_tiles, sk_split;
-  float* sk_ws;          // [sk_tiles][sk_split - 1][BLOCK_N / 32][128][32]
+  float* sk_ws;          // [sk_tiles][sk_split - 1][BLOCK_N / 32][8][128 rows][4]
   unsigned* sk_flags;    // [sk_tiles][4], zero between launches
 };
 
@@ -391,7 +391,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
       if (w.split > 0) {
         // contributor of a split tile: raw accumulators to the workspace, then one arrival per warp
         float* ws = p.sk_ws + ((long long)(w.slot * (p.sk_split - 1) + (w.split - 1)) * (BLOCK_N / 32)) * (kBlockM * 32) +
-                    (quarter * 32 + lane) * 32;
+                    (quarter * 32 + lane) * 4;
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / 32; ++c) {
           uint32_t r[32];
@@ -399,8 +399,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
           tmem_ld_wait();
           float4* dst = reinterpret_cast<float4*>(ws + (long long)c * (kBlockM * 32));
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            dst[q] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+          for (int q = 0; q < 8; ++q)   // a warp writes 512 contiguous bytes per instruction (whole sectors)
+            dst[q * kBlockM] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
                                  __uint_as_float(r[q * 4 + 3]));
         }
         __threadfence();
@@ -432,10 +432,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
         for (int j = 0; j < p.sk_split - 1; ++j) {
           const float4* src = reinterpret_cast<const float4*>(
               p.sk_ws + ((long long)(w.slot * (p.sk_split - 1) + j) * (BLOCK_N / 32) + c) * (kBlockM * 32) +
-              (quarter * 32 + lane) * 32);
+              (quarter * 32 + lane) * 4);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const float4 v = __ldcg(src + q);
+            const float4 v = __ldcg(src + q * kBlockM);
             pre[q].x += v.x; pre[q].y += v.y; pre[q].z += v.z; pre[q].w += v.w;
           }
         }

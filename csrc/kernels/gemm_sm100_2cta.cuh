@@ -32,11 +32,25 @@ inline void fill_pair_tiles(GemmParams& p) {
   p.group_m = 8;
 }
 
+// Parts per tile of the last, partly filled wave of pair tiles (1 = not cut).
+inline int pair_tail_split(int num_tiles, int k_blocks, int pairs) {
+  if (pairs <= 0 || num_tiles <= pairs) return 1;
+  const int rem = num_tiles % pairs;
+  if (rem == 0) return 1;
+  // Measured: handing partial sums over through L2 costs about as much as a 32-block K loop, so only long-K GEMMs
+  // (weight gradients, the down projection and its input gradient) come out ahead.
+  if (k_blocks < 64) return 1;
+  int s = pairs / rem;
+  if (s > 4) s = 4;
+  return s < 1 ? 1 : s;
+}
+
 // Time of the GEMM on CTA pairs in the unit of wave_cost (one wave of 128 x 256 tiles on every SM).
-inline double pair_cost(int M, int N, int sms) {
+inline double pair_cost(int M, int N, int K, int sms, bool split_on) {
   const int tiles = ((M + kPairBlockM - 1) / kPairBlockM) * ((N + kPairBlockN - 1) / kPairBlockN);
-  const int pairs = sms / 2;
-  const int waves = (tiles + pairs - 1) / pairs;
+  const int pairs = sms / 2 < tiles ? sms / 2 : tiles;
+  const int s = split_on ? pair_tail_split(tiles, (K + kBlockK - 1) / kBlockK, pairs) : 1;
+  const double waves = s > 1 ? double(tiles / pairs) + 1.0 / s + 0.06 : double((tiles + pairs - 1) / pairs);
   return waves * 0.88;   // a pair wave does the work of one single-CTA wave, measured 10-14 % faster (operand sharing)
 }
 
@@ -98,12 +112,13 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_count) {
+      WorkItem w;
+      for (int i = 0; ok && get_item(p, pair_id, pair_count, i, w); ++i) {
         int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
+        tile_coords(p, w.tile, m_blk, n_blk);
         const int m0 = m_blk * kPairBlockM + int(cta_rank) * kBlockM;
         const int n0 = n_blk * kPairBlockN + int(cta_rank) * (kPairBlockN / 2);
-        for (int kl = 0; kl < p.k_blocks; ++kl) {
+        for (int kl = w.kb0; kl < w.kb1; ++kl) {
           int kb = kl + p.k_rot;
           if (kb >= p.k_blocks) kb -= p.k_blocks;
           // (the odd CTA of the last pair may lie past M: it waits for the last real row block instead)
@@ -138,14 +153,14 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int it = 0;
-      for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_count, ++it) {
+      WorkItem w;
+      for (int it = 0; ok && get_item(p, pair_id, pair_count, it, w); ++it) {
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aphase ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairBlockN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * kPairStageBytes;
@@ -156,7 +171,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
           if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -167,10 +182,10 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps per CTA, own 128 rows)
     const int quarter = warp & 3;
-    int it = 0;
-    for (int tile = pair_id; tile < p.num_tiles; tile += pair_count, ++it) {
+    WorkItem w;
+    for (int it = 0; get_item(p, pair_id, pair_count, it, w); ++it) {
       int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      tile_coords(p, w.tile, m_blk, n_blk);
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       const bool got = mbar_wait(tfull_bar(buf), aphase, abort_flag, p.status, kStatusTimeoutTmemFull);
@@ -178,11 +193,75 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
       tc_fence_after();
       const int row = m_blk * kPairBlockM + int(cta_rank) * kBlockM + quarter * 32 + lane;
       const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kPairBlockN;
+      // Split tail (see GemmParams): per split tile the workspace holds, for each other part, the two CTAs'
+      // 128 x 256 fp32 accumulators as [chunk of 32 columns][group of 4 columns][row][4]; one flag per (tile, CTA, lane quarter).
+      constexpr int kChunks = kPairBlockN / 32;
+      auto part_base = [&](int part) {
+        return p.sk_ws + ((long long)((w.slot * (p.sk_split - 1) + part) * 2 + int(cta_rank)) * kChunks) * (kBlockM * 32) +
+               (quarter * 32 + lane) * 4;
+      };
+      unsigned* flag = p.sk_flags + (w.slot * 2 + int(cta_rank)) * 4 + quarter;
+      if (w.split > 0) {
+        float* ws = part_base(w.split - 1);
 #pragma unroll 1
-      for (int c = 0; c < kPairBlockN / 32; ++c) {
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(ws + (long long)c * (kBlockM * 32));
+#pragma unroll
+          for (int q = 0; q < 8; ++q)   // a warp writes 512 contiguous bytes per instruction (whole sectors)
+            dst[q * kBlockM] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                 __uint_as_float(r[q * 4 + 3]));
+        }
+        __threadfence();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_cluster(tempty_bar(buf), 0);
+          red_add_release_gpu(flag, 1u);
+        }
+        continue;
+      }
+      bool parts_ok = true;
+      if (w.split == 0) {
+        int okf = 1;
+        if (lane == 0) {
+          okf = wait_flag_ge_gpu(flag, uint32_t(p.sk_split - 1), p.status) ? 1 : 0;
+          if (okf) *flag = 0u;   // the only waiter resets it for the next launch
+        }
+        parts_ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+      }
+      if (!parts_ok) { *abort_flag = 1; break; }
+      float4 pre[8];
+      auto load_parts = [&](int c) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) pre[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < p.sk_split - 1; ++j) {
+          const float4* src = reinterpret_cast<const float4*>(part_base(j) + (long long)c * (kBlockM * 32));
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 v = __ldcg(src + q * kBlockM);
+            pre[q].x += v.x; pre[q].y += v.y; pre[q].z += v.z; pre[q].w += v.w;
+          }
+        }
+      };
+      if (w.split == 0) load_parts(0);
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
+        if (w.split == 0) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + pre[q].x);
+            r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + pre[q].y);
+            r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + pre[q].z);
+            r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + pre[q].w);
+          }
+          if (c + 1 < kChunks) load_parts(c + 1);
+        }
         const int col0 = n_blk * kPairBlockN + c * 32;
         if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
       }

@@ -89,6 +89,9 @@ def bench_gemm(out=None):
                 best = (ms, bn)
         K.gemm_set_pair_mode(2)
         ms_pair = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_tail_split(False)
+        ms_pair_whole = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_tail_split(True)
         K.gemm_set_pair_mode(1)
         ms_auto = time_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
         K.gemm_set_tail_split(False)
@@ -101,7 +104,7 @@ def bench_gemm(out=None):
         ms_ref = time_ms(lambda: torch.matmul(A, B, out=c))
         K.check_status()
         row = {"kernel": "gemm_bf16", "tag": tag, "M": M, "N": N, "K": Kd, "a_major": am, "b_major": bm,
-               "block_n": best[1], "ms": round(best[0], 4), "pair_ms": round(ms_pair, 4), "auto_ms": round(ms_auto, 4),
+               "block_n": best[1], "ms": round(best[0], 4), "pair_ms": round(ms_pair, 4), "pair_no_tail_split_ms": round(ms_pair_whole, 4), "auto_ms": round(ms_auto, 4),
                "auto_tflops": round(fl / ms_auto / 1e9, 1),
                "auto_no_tail_split_ms": round(ms_whole, 4), "tflops": round(fl / best[0] / 1e9, 1),
                "frac_of_%s_peak" % pk["src"]: round(fl / best[0] / 1e9 / pk["tflops"], 3),

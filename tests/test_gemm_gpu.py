@@ -72,9 +72,11 @@ def test_gemm_strided_rows():
     (4096, 2560, 512, 0, 1, 128),     # 128-wide tiles, short K
     (8192, 2560, 2048, 0, 0, 0),      # tile width chosen by the cost model
 ])
-def test_gemm_split_tail(M, N, K, a_major, b_major, block_n):
+@pytest.mark.parametrize("pair_mode", [0, 2])
+def test_gemm_split_tail(M, N, K, a_major, b_major, block_n, pair_mode):
     """The K-split of the last tile wave gives the same result as whole tiles, call after call."""
     from litetorch_b200.ops import kernels as K_
+    K_.gemm_set_pair_mode(pair_mode)
     torch.manual_seed(1)
     dev = "cuda"
     a = (torch.randn((M, K) if a_major == 0 else (K, M), device=dev) * 0.5).bfloat16()
@@ -90,6 +92,7 @@ def test_gemm_split_tail(M, N, K, a_major, b_major, block_n):
         K_.gemm_set_tail_split(True)
     torch.cuda.synchronize()
     K_.check_status()
+    K_.gemm_set_pair_mode(1)
     for o in outs:
         assert _rel_err(o, ref) < 1e-2
         # fp32 partial sums are added in a different order: bf16 results may differ in the last place only
