@@ -37,6 +37,10 @@ struct FlashBwdParams {
   float scale, scale_log2;
   int causal;
   int* status;
+  // Optional phase timing (nullptr: off): the CTA of key block 0 / head 0 / batch 0 adds the SM cycles its compute
+  // warp 2 and its MMA thread spend in each phase to trace[0..15] and counts iterations in trace[15].
+  long long* trace;
+  int dbg;   // timing experiments only (results are wrong when non-zero): 1 = no bulk reduction, 2 = no staging either
 };
 
 struct QMaps {
@@ -61,9 +65,19 @@ struct FaBwdCfg {
   static constexpr int kOffDS = kOffP + kPTile;
   static constexpr int kOffBar = kOffDS + kPTile;
   static constexpr int kOffSeg = kOffBar + 128;
-  static constexpr int kSmemBytes = kOffSeg + kFbMaxSegs * 16 + 16 + 1024;
+  // dQ tiles staged for TMA reductions into the fp32 accumulator (head_dim 64 only: with head_dim 128 shared memory
+  // is full and the rows go out as red.global.add).  One 32-row x 32-column fp32 tile (4 KB, 128-byte swizzle) per
+  // compute warp, reduced into global memory by ONE cp.reduce.async.bulk.tensor per warp and iteration: the copy
+  // engine does the atomics, not the LSU, and it is given few, large operations.
+  static constexpr bool kBulkDq = (D == 64);
+  static constexpr int kDqTile = 32 * 128;
+  static constexpr int kOffDqStage = ((kOffSeg + kFbMaxSegs * 16 + 16 + 1023) / 1024) * 1024;
+  static constexpr int kSmemBytes = kOffDqStage + (kBulkDq ? (kFbComputeThreads / 32) * kDqTile : 0) + 1024;
   static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
-  static constexpr int kColDQ = (D == 64) ? 384 : 0;  // aliases S when D == 128
+  static constexpr int kColDQ = (D == 64) ? 384 : 0;  // D == 64: two buffers (384, 448); D == 128: aliases S
+  // D == 64: dQ of iteration i is read one iteration later, right after S / dP of iteration i+1 arrive, when the
+  // tensor pipe is idle (a tcgen05.ld issued while MMAs are queued waits behind them) and off the critical chain.
+  static constexpr bool kDeferDq = (D == 64);
   static constexpr bool kDqAliasesS = (D != 64);
 };
 
@@ -122,10 +136,24 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// Asynchronous bulk reduction shared -> global: global[i] += shared[i] for `bytes` / 4 floats (16-byte aligned).
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
+}
+// Tiled TMA reduction shared -> global (fp32 add) of the box of `m` at coordinates (x, h, t, b).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, uint32_t smem_src, int x, int h, int t, int b) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_src), "r"(x), "r"(h), "r"(t), "r"(b) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <int D>
 __global__ void __launch_bounds__(kFbThreads, 1)
 flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const FlashBwdParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDQ, const FlashBwdParams p) {
   using Cfg = FaBwdCfg<D>;
   constexpr int ST = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -143,7 +171,8 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
   const uint32_t dq_full = bb + 8u * 9;    // dQ_i is in TMEM
   const uint32_t dq_free = bb + 8u * 10;   // compute warps have read dQ_i (one arrival per warp)
   const uint32_t dkv_full = bb + 8u * 11;  // all MMAs done
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
+  const uint32_t dq_free1 = bb + 8u * 12;  // second dQ buffer (deferred-dQ flow)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,12 +241,13 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads / 32);
     mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32);
+    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32); mbar_init(dq_free1, kFbComputeThreads / 32);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
     tma_prefetch_desc(&qm.q[p.cp_rank]); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&qm.d_o[p.cp_rank]);
+    tma_prefetch_desc(&tmDQ);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), 512);
@@ -261,14 +291,19 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
       const uint32_t ka = sbase + Cfg::kOffK, va = sbase + Cfg::kOffV;
       const uint32_t pa = sbase + Cfg::kOffP, dsa = sbase + Cfg::kOffDS;
+      const bool tr = p.trace != nullptr && kv_blk == 0 && hkv == 0 && b == 0;
+      long long tm[4] = {0, 0, 0, 0};
       for (int it = 0; ok && it < n_iter; ++it) {
         const int s = it % ST;
         const uint32_t par = (it / ST) & 1;
         const uint32_t ipar = it & 1;
         const uint32_t qa = sbase + Cfg::kOffQ + s * Cfg::kTile;
         const uint32_t doa = sbase + Cfg::kOffDO + s * Cfg::kTile;
+        long long c0 = tr ? clock64() : 0;
         if (!mbar_wait(qdo_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (tr) { const long long c1 = clock64(); tm[0] += c1 - c0; c0 = c1; }
         if (!mbar_wait(sdp_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        if (tr) { const long long c1 = clock64(); tm[1] += c1 - c0; c0 = c1; }
         if (Cfg::kDqAliasesS) {
           if (!mbar_wait(dq_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
         }
@@ -286,9 +321,13 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
                       make_smem_desc_sw128(va + off, 16, 1024), idesc_sd, k > 0 ? 1u : 0u);
         }
         umma_commit(sdp_full);
+        if (tr) c0 = clock64();
         if (!mbar_wait(pds_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+        if (tr) { const long long c1 = clock64(); tm[2] += c1 - c0; c0 = c1; }
         if (!Cfg::kDqAliasesS) {
-          if (!mbar_wait(dq_free, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+          // dQ buffer it & 1 was last used by iteration it - 2
+          if (!mbar_wait((it & 1) ? dq_free1 : dq_free, ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_flag, p.status,
+                         kStatusTimeoutTmemEmpty)) { ok = false; break; }
         }
         tc_fence_after();
         // dV += P^T dO ; dK += dS^T Q      (K dimension = the 128 query rows, 16 rows per instruction)
@@ -309,12 +348,16 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         for (int k = 0; k < kFbBlock / 16; ++k) {
           const uint64_t adesc = make_smem_desc_sw128(dsa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(ka + k * (16 * 128), 128 * 128, 1024);
-          umma_f16_ss(tmem_base + Cfg::kColDQ, adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + Cfg::kColDQ + (Cfg::kDeferDq ? (it & 1) * D : 0), adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
         }
         umma_commit(qdo_empty(s));
         umma_commit(pds_empty);
         umma_commit(dq_full);
         if (it == n_iter - 1) umma_commit(dkv_full);
+      }
+      if (tr) {
+        // MMA thread: wait for Q/dO, for S/dP to be read, for P/dS
+        p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2];
       }
     }
   } else {
@@ -325,26 +368,99 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
-      const uint32_t ipar = it & 1;
-      const int h = hkv * G + it / per_head;
+    const bool tr = p.trace != nullptr && kv_blk == 0 && hkv == 0 && b == 0 && warp == 2 && lane == 0;
+    long long tc[6] = {0, 0, 0, 0, 0, 0};
+    // Row statistics are fetched one iteration ahead (the global-load latency is off the chain); the position of an
+    // iteration (query head, block within the head) is advanced with counters, not divisions.
+    auto fetch_stats = [&](int hh, int jj, float& lse_raw, float& dl) {
+      lse_raw = 0.f; dl = 0.f;
+      if (hh >= G) return;
+      const int h = hkv * G + hh;
       int owner, q0, qbase;
-      locate(it % per_head, owner, q0, qbase);
+      locate(jj, owner, q0, qbase);
+      const int q_idx = q0 + row;
+      if (q_idx < p.Tq) {
+        const long long si = ((long long)b * p.Hq + h) * p.Tq + q_idx;
+        lse_raw = p.lse[owner][si];
+        dl = p.delta[owner][si];
+      }
+    };
+    float lse_next, dlt_next;
+    int hh_next = 0, jj_next = 0;   // position of the iteration whose statistics are in lse_next / dlt_next
+    fetch_stats(n_iter > 0 ? 0 : G, 0, lse_next, dlt_next);
+    bool dq_pending = false;   // this thread has a bulk reduction in flight that reads its staging piece
+    // This warp's 32 x (D / 2) piece of one dQ tile: TMEM -> registers -> global accumulator; the TMEM buffer is
+    // released as soon as the values are in registers.
+    auto emit_dq = [&](int buf, float* dq_row, bool valid, bool local, int h_, int q0_) {
+      if (Cfg::kBulkDq && local) {
+        uint32_t dq[32];
+        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + buf * D + half * 32, dq);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(buf ? dq_free1 : dq_free);
+        if (p.dbg >= 2) return;
+        uint8_t* tile = smem + Cfg::kOffDqStage + (warp - 2) * Cfg::kDqTile;
+        if (dq_pending) {   // the previous reduction has finished reading the tile
+          if (lane == 0) bulk_wait_read0();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)   // row `lane` of the tile, 16-byte units swizzled like the tensor map expects
+          *reinterpret_cast<uint4*>(tile + lane * 128 + ((u ^ (lane & 7)) * 16)) =
+              make_uint4(dq[u * 4], dq[u * 4 + 1], dq[u * 4 + 2], dq[u * 4 + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        dq_pending = false;
+        if (p.dbg == 0) {
+          if (lane == 0) {
+            tma_reduce_add_4d(&tmDQ, smem_u32(tile), half * 32, h_, q0_ + quarter * 32, b);   // rows past Tq are clipped
+            bulk_commit();
+          }
+          dq_pending = true;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+          uint32_t dq[32];
+          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + buf * D + c * 32, dq);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              red_add_v4(dq_row + c * 32 + u * 4, __uint_as_float(dq[u * 4]), __uint_as_float(dq[u * 4 + 1]),
+                         __uint_as_float(dq[u * 4 + 2]), __uint_as_float(dq[u * 4 + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(buf ? dq_free1 : dq_free);
+      }
+    };
+    float* prev_row = nullptr;   // deferred-dQ flow: where the previous iteration's dQ row goes
+    bool prev_valid = false, prev_local = true;
+    int prev_h = 0, prev_q0 = 0;
+    for (int it = 0; it < n_iter; ++it) {
+      long long c0 = tr ? clock64() : 0;
+      const uint32_t ipar = it & 1;
+      const int h = hkv * G + hh_next;
+      int owner, q0, qbase;
+      locate(jj_next, owner, q0, qbase);
       const int q_idx = q0 + row;
       const bool q_valid = q_idx < p.Tq;
-      float lse2 = 0.f, dlt = 0.f;
-      if (q_valid) {
-        const long long si = ((long long)b * p.Hq + h) * p.Tq + q_idx;
-        lse2 = p.lse[owner][si] * 1.4426950408889634f;
-        dlt = p.delta[owner][si];
-      }
+      const float lse2 = lse_next * 1.4426950408889634f, dlt = dlt_next;
+      if (++jj_next == per_head) { jj_next = 0; ++hh_next; }
+      fetch_stats(hh_next, jj_next, lse_next, dlt_next);
       // last visible key (index local to this rank's KV) for this query row
       const int limit = p.causal ? min(kv0 + (qbase + row - k_base), p.Tk - 1) : (p.Tk - 1);
+      if (tr) { const long long c1 = clock64(); tc[0] += c1 - c0; c0 = c1; }   // lse / delta loads issued, index math
       ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
+      if (tr) { const long long c1 = clock64(); tc[1] += c1 - c0; c0 = c1; }   // waiting for S / dP
       // P / dS tiles are free once the MMAs of the previous iteration have executed.
       ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
       if (!ok) break;
+      if (tr) { const long long c1 = clock64(); tc[2] += c1 - c0; c0 = c1; }   // waiting for the P / dS tiles
       tc_fence_after();
       uint8_t* prow = smem + Cfg::kOffP + (row >> 3) * 1024 + (row & 7) * 128;
       uint8_t* dsrow = smem + Cfg::kOffDS + (row >> 3) * 1024 + (row & 7) * 128;
@@ -355,11 +471,12 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDP + c * 32, dp);
         tmem_ld_wait();
         const bool live = q_valid && lse2 != -INFINITY;
+        const float dlt_s = dlt * p.scale;
         if (live && kv0 + c * 32 + 31 <= limit) {   // every column of the chunk is visible: no per-element test
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float pv = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
-            const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
+            const float ds = pv * fmaf(__uint_as_float(dp[i]), p.scale, -dlt_s);
             sv[i] = __float_as_uint(pv);
             dp[i] = __float_as_uint(ds);
           }
@@ -369,7 +486,7 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
             const int kv_idx = kv0 + c * 32 + i;
             float pv = 0.f;
             if (live && kv_idx <= limit) pv = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
-            const float ds = pv * (__uint_as_float(dp[i]) - dlt) * p.scale;
+            const float ds = pv * fmaf(__uint_as_float(dp[i]), p.scale, -dlt_s);
             sv[i] = __float_as_uint(pv);
             dp[i] = __float_as_uint(ds);
           }
@@ -400,29 +517,40 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         mbar_arrive(sdp_free);
         mbar_arrive(pds_full);
       }
+      if (tr) { const long long c1 = clock64(); tc[3] += c1 - c0; c0 = c1; }   // exp / dS / stores to shared memory
+      if (Cfg::kDeferDq) {
+        // While the tensor core works on dV / dK / dQ of this iteration and S / dP of the next, write out dQ of the
+        // PREVIOUS iteration: it is complete (S / dP of this iteration were committed after it), and its transfer
+        // TMEM -> registers -> shared memory -> TMA reduction is off the critical chain here.
+        if (it > 0) {
+          emit_dq((it - 1) & 1, prev_row, prev_valid, prev_local, prev_h, prev_q0);
+          if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }
+        }
+        prev_row = p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
+        prev_valid = q_valid;
+        prev_local = (owner == p.cp_rank);
+        prev_h = h; prev_q0 = q0;
+        continue;
+      }
       // dQ_i
       ok = __all_sync(0xffffffffu, mbar_wait(dq_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
+      if (tr) { const long long c1 = clock64(); tc[4] += c1 - c0; c0 = c1; }   // waiting for dQ
       tc_fence_after();
-      float* dq_row = p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
-#pragma unroll 1
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t dq[32];
-        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + c * 32, dq);
-        tmem_ld_wait();
-        if (q_valid) {
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            red_add_v4(dq_row + c * 32 + u * 4, __uint_as_float(dq[u * 4]), __uint_as_float(dq[u * 4 + 1]),
-                       __uint_as_float(dq[u * 4 + 2]), __uint_as_float(dq[u * 4 + 3]));
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
+      emit_dq(0, p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D, q_valid, owner == p.cp_rank, h, q0);
+      if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }   // dQ read + reduction
+    }
+    if (tr) {
+      for (int i = 0; i < 6; ++i) p.trace[i] = tc[i];
+      p.trace[15] = n_iter;
     }
     // ---------------------------------------------------------------- dK / dV epilogue (row = key index)
     if (ok && n_iter > 0) ok = __all_sync(0xffffffffu, mbar_wait(dkv_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
+    if (Cfg::kDeferDq && ok && n_iter > 0) {
+      tc_fence_after();
+      emit_dq((n_iter - 1) & 1, prev_row, prev_valid, prev_local, prev_h, prev_q0);   // dQ of the last iteration
+    }
+    if (dq_pending && lane == 0) bulk_wait_all0();   // shared memory must outlive the reductions that read it
     if (ok) {
       if (n_iter > 0) tc_fence_after();
       const int kv_idx = kv0 + row;
@@ -472,8 +600,8 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
 }
 
 template <int D>
-static int launch_flash_bwd(const QMaps& qm, const CUtensorMap& tk, const CUtensorMap& tv, const FlashBwdParams& p,
-                            cudaStream_t st) {
+static int launch_flash_bwd(const QMaps& qm, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdq,
+                            const FlashBwdParams& p, cudaStream_t st) {
   using Cfg = FaBwdCfg<D>;
   static bool configured = false;
   auto kern = flash_bwd_kernel<D>;
@@ -482,7 +610,7 @@ static int launch_flash_bwd(const QMaps& qm, const CUtensorMap& tk, const CUtens
     configured = true;
   }
   dim3 grid(p.Hkv, p.B, (p.Tk + kFbBlock - 1) / kFbBlock);
-  kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(qm, tk, tv, p);
+  kern<<<grid, kFbThreads, Cfg::kSmemBytes, st>>>(qm, tk, tv, tdq, p);
   LT_LAUNCH_CHECK();
   return 0;
 }
@@ -511,6 +639,9 @@ static int bwd_convert(const float* dq_acc, void* dq, int B, int Tq, int Hq, int
 }
 
 // Main kernel.  q/d_o/lse/delta/dq_acc are given per query-owning rank (cp_world entries; peer-mapped under CP).
+static long long* g_bwd_trace = nullptr;
+static int g_bwd_dbg = 0;
+
 static int bwd_main(const void* const* q_ptrs, const void* k, const void* v, const void* const* do_ptrs,
                     const float* const* lse_ptrs, const float* const* delta_ptrs, float* const* dq_acc_ptrs, void* dk, void* dv,
                     int B, int Tq, int Tk, int Hq, int Hkv, int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t,
@@ -549,7 +680,14 @@ static int bwd_main(const void* const* q_ptrs, const void* k, const void* v, con
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.status = device_status_word();
-  return (D == 64) ? launch_flash_bwd<64>(qm, tk, tv, p, st) : launch_flash_bwd<128>(qm, tk, tv, p, st);
+  p.trace = g_bwd_trace;
+  p.dbg = g_bwd_dbg;
+  // fp32 dQ accumulator of this rank, [B, Tq, Hq, D]: boxes of 32 rows x 32 columns (128 bytes, swizzled)
+  CUtensorMap tdq;
+  r = encode_tmap_4d(&tdq, dq_acc_ptrs[cp_rank], 4, D, Hq, Tq, B, (uint64_t)D * 4, (uint64_t)Hq * D * 4,
+                     (uint64_t)Tq * Hq * D * 4, 32, 1, 32, 1, 1);
+  if (r) return 5000 + r;
+  return (D == 64) ? launch_flash_bwd<64>(qm, tk, tv, tdq, p, st) : launch_flash_bwd<128>(qm, tk, tv, tdq, p, st);
 }
 
 }  // namespace lt
@@ -558,6 +696,11 @@ extern "C" {
 
 // Shapes as lt_flash_fwd.  delta: scratch [B, Hq, Tq] fp32.  dq_acc: scratch [B, Tq, Hq, D] fp32, must be zero.
 // dk and dv share the strides sdk_b / sdk_t.
+// Debug aid: a device buffer of 16 int64 that the next backward launches fill with per-phase SM cycle counts of one
+// CTA (see FlashBwdParams::trace); nullptr switches it off.
+void lt_flash_bwd_set_trace(void* buf) { lt::g_bwd_trace = static_cast<long long*>(buf); }
+void lt_flash_bwd_set_debug(int v) { lt::g_bwd_dbg = v; }
+
 int lt_flash_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o, void* dq,
                  void* dk, void* dv, float* delta, float* dq_acc, int B, int Tq, int Tk, int Hq, int Hkv, int D,
                  long long sq_b, long long sq_t, long long sk_b, long long sk_t, long long sv_b, long long sv_t,
