@@ -32,6 +32,13 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 t;
+  t = unpack_bf16x2(u.x); f[0] = t.x; f[1] = t.y;
+  t = unpack_bf16x2(u.y); f[2] = t.x; f[3] = t.y;
+  t = unpack_bf16x2(u.z); f[4] = t.x; f[5] = t.y;
+  t = unpack_bf16x2(u.w); f[6] = t.x; f[7] = t.y;
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   uint4 u;
   u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
@@ -182,6 +189,86 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
+// RMSNorm backward with ONE WARP PER ROW (D = 256 * ITERS, ITERS in {1, 2, 4, 8}): dy and x of the row stay in
+// registers between the reduction and the dx pass, the row sums are warp shuffles (no block barrier per row), and a
+// lane has 16 * ITERS bytes x 2 of loads in flight, so a CTA of 8 warps keeps 8 rows moving instead of one.
+// dgamma is accumulated per lane over all rows of the warp and folded to one partial row per CTA at the end.
+template <int ITERS>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw_part, int M) {
+  constexpr int D = 256 * ITERS;
+  constexpr int kWarps = kNormThreads / 32;
+  __shared__ float fold[kWarps][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float dw_acc[ITERS][8];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+
+  for (int row = blockIdx.x * kWarps + warp; row < M; row += gridDim.x * kWarps) {
+    const long long off = (long long)row * D;
+    uint4 gq[ITERS], xq[ITERS];
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      gq[i] = *reinterpret_cast<const uint4*>(dy + off + c);
+      xq[i] = *reinterpret_cast<const uint4*>(x + off + c);
+    }
+    const float rstd = rstd_in[row];
+    float s_gx = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      float g[8], xv[8], wv[8];
+      unpack8(gq[i], g);
+      unpack8(xq[i], xv);
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = xv[j] * rstd;
+        dw_acc[i][j] += g[j] * xh;
+        s_gx += g[j] * wv[j] * xh;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s_gx += __shfl_xor_sync(0xffffffffu, s_gx, o);
+    const float m_gx = s_gx / D;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      float g[8], xv[8], wv[8], o[8];
+      unpack8(gq[i], g);
+      unpack8(xq[i], xv);
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (g[j] * wv[j] - xv[j] * rstd * m_gx);
+      if (dres) {
+        float r[8];
+        load8(dres + off + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      store8(dx + off + c, o);
+    }
+  }
+  // one partial dgamma row per CTA: 256 columns at a time through shared memory
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) fold[warp][lane * 8 + j] = dw_acc[i][j];
+    __syncthreads();
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kWarps; ++k) sum += fold[k][threadIdx.x];
+    dw_part[(long long)blockIdx.x * D + i * 256 + threadIdx.x] = sum;
+    __syncthreads();
+  }
+}
+
 // out[c] (+)= sum_p part[p, c]; out is bf16 or fp32.  A block owns 32 columns; its 8 warps split the partial rows.
 __global__ void fold_partials_kernel(const float* __restrict__ part, void* __restrict__ out, int P, int D,
                                      int out_fp32, int accumulate) {
@@ -249,6 +336,22 @@ int lt_norm_bwd(int layer_norm, const void* dy, const void* x, const void* w, co
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
+  if (!layer_norm && (D == 256 || D == 512 || D == 1024 || D == 2048) && M >= 8 * grid / 2) {
+    // warp-per-row kernel; grid CTAs of 8 warps, one partial dgamma row per CTA
+    int g2 = (M + 7) / 8;
+    if (g2 > grid) g2 = grid;
+    if (g2 > sm_count()) g2 = sm_count();
+    switch (D) {
+      case 256: rmsnorm_bwd_warp_kernel<1><<<g2, kNormThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_part, M); break;
+      case 512: rmsnorm_bwd_warp_kernel<2><<<g2, kNormThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_part, M); break;
+      case 1024: rmsnorm_bwd_warp_kernel<4><<<g2, kNormThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_part, M); break;
+      default: rmsnorm_bwd_warp_kernel<8><<<g2, kNormThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_part, M); break;
+    }
+    LT_LAUNCH_CHECK();
+    fold_partials_kernel<<<(D + 31) / 32, 256, 0, st>>>(dw_part, dw, g2, D, grads_fp32, accumulate);
+    LT_LAUNCH_CHECK();
+    return 0;
+  }
 #define LT_NORM_BWD(LN, IT) \
   norm_bwd_kernel<LN, IT><<<grid, kNormThreads, 0, st>>>(DY, X, W, mean, rstd, DR, DX, dw_part, db_part, M, D)
   if (layer_norm) {
