@@ -30,6 +30,7 @@ struct FlashFwdParams {
   float scale_log2;  // softmax scale * log2(e)
   int causal;
   int* status;
+  long long* trace;   // optional phase timing of one CTA (debug aid; nullptr = off), 16 int64
   // Context parallelism: the keys/values of cp_world ranks (Tk rows each, read through per-rank tensor maps that may
   // point at peer memory) are visited in one pass; queries and keys carry global positions (contiguous split, or
   // zigzag: rank r holds sequence chunks r and 2W-1-r of 2W).  cp_world == 1 is plain attention.
@@ -71,8 +72,11 @@ struct FaFwdCfg {
   // that the aligned layout lies inside the allocation and reports kStatusBadArgument otherwise.
   static constexpr int kSmemBytes = (kNeeded + 1024 <= 232448) ? kNeeded + 1024 : 232448;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0;     // two S buffers of 128 columns
-  static constexpr int kColO = 256;   // D columns
+  // Score buffers of 128 columns: three with head_dim 64, so that S of block j+2 is computed while the softmax of
+  // blocks j and j+1 is still reading theirs; tensor memory only has room for two with head_dim 128.
+  static constexpr int kSBufs = (D == 64) ? 3 : 2;
+  static constexpr int kColS = 0;
+  static constexpr int kColO = kSBufs * 128;   // two accumulators of D columns (KV blocks of even / odd index)
 };
 
 template <int D>
@@ -94,13 +98,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto v_full = [&](int s) { return bb + 8u * (3 + s); };
   auto k_empty = [&](int s) { return bb + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bb + 8u * (7 + s); };
-  auto s_full = [&](int s) { return bb + 8u * (9 + s); };
-  auto p_full = [&](int s) { return bb + 8u * (11 + s); };
-  auto p_empty = [&](int s) { return bb + 8u * (13 + s); };
-  const uint32_t o_full = bb + 8u * 15;
+  auto s_full = [&](int s) { return bb + 8u * (9 + s); };    // up to three
+  auto p_full = [&](int s) { return bb + 8u * (12 + s); };
+  auto p_empty = [&](int s) { return bb + 8u * (14 + s); };
+  const uint32_t o_full = bb + 8u * 16;
   // x_bar(quarter): both warps of a TMEM lane quarter have published their partial row statistics
-  auto x_bar = [&](int qtr) { return bb + 8u * (16 + qtr); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20);
+  auto x_bar = [&](int qtr) { return bb + 8u * (17 + qtr); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 21);
   float* xmax = reinterpret_cast<float*>(smem + Cfg::kOffX);  // [2 (rendezvous parity)][2 (half)][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -173,8 +177,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
       mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
-      mbar_init(s_full(s), 1); mbar_init(p_full(s), kFaSoftmaxThreads / 32); mbar_init(p_empty(s), 1);
+      mbar_init(p_full(s), kFaSoftmaxThreads / 64); mbar_init(p_empty(s), 1);
     }
+    for (int s = 0; s < Cfg::kSBufs; ++s) mbar_init(s_full(s), 1);
     mbar_init(o_full, 1);
     for (int qtr = 0; qtr < 4; ++qtr) mbar_init(x_bar(qtr), 2);
     *abort_flag = 0;
@@ -198,18 +203,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < D / 64; ++c)
         tma_load_4d(sbase + Cfg::kOffQ + c * (kFaBlockQ * 128), &tmQ, q_full, c * 64, h, q0, b);
-      for (int j = 0; j < n_blocks; ++j) {
+      // K runs one block ahead of V: the wait for a free V stage (the PV product two blocks back) must not hold up
+      // the K tile that the next score product needs.
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
-        const uint32_t par = (j >> 1) & 1;
         int owner, kv0, kbase;
         locate(j, owner, kv0, kbase);
-        if (!mbar_wait(k_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        if (!mbar_wait(k_empty(s), ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) return false;
         mbar_expect_tx(k_full(s), Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(sbase + Cfg::kOffK + s * Cfg::kKVBytes + c * (kFaBlockKV * 128), &maps.k[owner], k_full(s), c * 64, hkv,
                       kv0, b);
-        if (!mbar_wait(v_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        return true;
+      };
+      bool okp = load_k(0);
+      for (int j = 0; okp && j < n_blocks; ++j) {
+        if (j + 1 < n_blocks && !load_k(j + 1)) break;
+        const int s = j & 1;
+        int owner, kv0, kbase;
+        locate(j, owner, kv0, kbase);
+        if (!mbar_wait(v_empty(s), ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutEmpty)) break;
         mbar_expect_tx(v_full(s), Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
@@ -222,44 +236,61 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0 && n_blocks > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kFaBlockQ, kFaBlockKV, 1, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_f16(kFaBlockQ, D, 1, 0, 1);
+      // The issuing thread is a single scalar instruction stream on the critical path of every block: the operand
+      // descriptors are built once per buffer and advanced by adding the 16-byte-unit offset of each K step.
+      const uint64_t q_desc = make_smem_desc_sw128(sbase + Cfg::kOffQ, 16, 1024);
+      uint64_t k_desc[2], v_desc[2], p_desc[2];
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        k_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffK + st * Cfg::kKVBytes, 16, 1024);
+        v_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffV + st * Cfg::kKVBytes, kFaBlockKV * 128, 1024);
+        p_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffP + st * Cfg::kPBytes, 16, 1024);
+      }
       auto issue_s = [&](int j) {
-        const int s = j & 1;
-        const uint32_t qa = sbase + Cfg::kOffQ;
-        const uint32_t ka = sbase + Cfg::kOffK + s * Cfg::kKVBytes;
+        const int s = j & 1;                 // K stage
+        const int sb = j % Cfg::kSBufs;      // score buffer
+        const uint64_t kd = s ? k_desc[1] : k_desc[0];
+        const uint32_t d_s = tmem_base + Cfg::kColS + sb * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * (128 * 128) + (k % 4) * 32;
-          umma_f16_ss(tmem_base + Cfg::kColS + s * 128, make_smem_desc_sw128(qa + off, 16, 1024),
-                      make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          constexpr int kUnit = 1;  // descriptor addresses count 16-byte units
+          const uint64_t off = uint64_t(((k / 4) * (128 * 128) + (k % 4) * 32) >> 4) * kUnit;
+          umma_f16_ss(d_s, q_desc + off, kd + off, idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(k_empty(s));
-        umma_commit(s_full(s));
+        umma_commit(s_full(sb));
       };
+      // Score products run kLook blocks ahead of the PV products: buffer (j + kLook) % kSBufs was last read by the
+      // softmax of block j - 1, whose P this thread has already waited for.
+      constexpr int kLook = Cfg::kSBufs - 1;
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
-      ok = ok && mbar_wait(k_full(0), 0, abort_flag, p.status, kStatusTimeoutFull);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
+      for (int j0 = 0; ok && j0 < kLook && j0 < n_blocks; ++j0) {
+        ok = mbar_wait(k_full(j0 & 1), (j0 >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull);
+        if (ok) {
+          tc_fence_after();
+          issue_s(j0);
+        }
       }
       for (int j = 0; ok && j < n_blocks; ++j) {
         const int s = j & 1;
         const uint32_t par = (j >> 1) & 1;
-        if (j + 1 < n_blocks) {
-          const int s1 = (j + 1) & 1;
-          if (!mbar_wait(k_full(s1), ((j + 1) >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (j + kLook < n_blocks) {
+          const int jn = j + kLook;
+          if (!mbar_wait(k_full(jn & 1), (jn >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
           tc_fence_after();
-          issue_s(j + 1);
+          issue_s(jn);
         }
         if (!mbar_wait(p_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
         if (!mbar_wait(v_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pa = sbase + Cfg::kOffP + s * Cfg::kPBytes;
-        const uint32_t va = sbase + Cfg::kOffV + s * Cfg::kKVBytes;
+        const uint64_t pd = s ? p_desc[1] : p_desc[0];
+        const uint64_t vd = s ? v_desc[1] : v_desc[0];
+        const uint32_t d_o = tmem_base + Cfg::kColO + s * D;
 #pragma unroll
         for (int k = 0; k < kFaBlockKV / 16; ++k) {
-          const uint64_t adesc = make_smem_desc_sw128(pa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(va + k * (16 * 128), kFaBlockKV * 128, 1024);
-          umma_f16_ss(tmem_base + Cfg::kColO, adesc, bdesc, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          const uint64_t a_off = uint64_t(((k / 4) * (128 * 128) + (k % 4) * 32) >> 4);
+          const uint64_t b_off = uint64_t((k * (16 * 128)) >> 4);
+          umma_f16_ss(d_o, pd + a_off, vd + b_off, idesc_o, (j > 1 || k > 0) ? 1u : 0u);
         }
         umma_commit(v_empty(s));
         umma_commit(p_empty(s));
@@ -268,146 +299,196 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
+    // Two independent groups of four warps: group g takes the KV blocks of parity g (score buffer g, P buffer g) and
+    // keeps its own running maximum, row sum and output accumulator O_g, so a thread owns a whole score row of its
+    // block (no exchange of row statistics between warps) and the softmax of block j+1 overlaps that of block j.
+    // The two accumulators are merged once, at the end.
     const int quarter = warp & 3;          // TMEM lanes this warp may touch
-    const int half = (warp - 2) >> 2;      // which 64 of the 128 score columns (and which half of O) it owns
+    const int grp = (warp - 2) >> 2;       // which blocks (and, in the epilogue, which half of the output columns)
     const int row = quarter * 32 + lane;
     const int q_idx = q0 + row;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    float m_used = -INFINITY, l = 0.f;
+    const uint32_t o_mine = tmem_base + lane_base + Cfg::kColO + grp * D;
+    float m_used = 0.f, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_blocks; ++j) {
-      const int s = j & 1;
+    const bool tr = p.trace != nullptr && blockIdx.z == 0 && h == 0 && b == 0 && warp == 2 && lane == 0;
+    long long tc[6] = {0, 0, 0, 0, 0, 0};
+    int tn = 0;
+    for (int j = grp; j < n_blocks; j += 2) {
+      long long c0 = tr ? clock64() : 0;
+      ++tn;
       const uint32_t par = (j >> 1) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull));
+      const int sb = j % Cfg::kSBufs;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full(sb), uint32_t(j / Cfg::kSBufs) & 1u, abort_flag, p.status,
+                                             kStatusTimeoutTmemFull));
       if (!ok) break;
+      if (tr) { const long long c1 = clock64(); tc[0] += c1 - c0; c0 = c1; }   // waiting for S
       tc_fence_after();
-      uint32_t r[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + s * 128 + (2 * half + c) * 32, r[c]);
-      tmem_ld_wait();
       int owner, kv0b, kbase;
       locate(j, owner, kv0b, kbase);
       // last visible column of this 128-key block for this row: causal position and end of the rank's keys
       int limit = p.Tk - 1 - kv0b;
       if (p.causal) limit = min(limit, q_base + row - kbase);
-      const int kv0 = half * 64;
-      const bool need_mask = (kv0 + 63 > limit);
+      const uint32_t s_mine = tmem_base + lane_base + Cfg::kColS + sb * 128;
+      // pass 1: row maximum (the scores are read from tensor memory twice, 64 columns at a time, instead of
+      // holding all 128 in registers)
       float mx = -INFINITY;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t r[2][32];
+        tmem_ld_32x32(s_mine + hh * 64, r[0]);
+        tmem_ld_32x32(s_mine + hh * 64 + 32, r[1]);
+        tmem_ld_wait();
+        if (limit >= hh * 64 + 63) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[c][i]);
-          if (need_mask && (kv0 + c * 32 + i > limit)) v = -INFINITY;
-          r[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (hh * 64 + c * 32 + i <= limit) mx = fmaxf(mx, __uint_as_float(r[c][i]));
         }
-      // combine the row maximum of the two column halves (bounded mbarrier rendezvous, parity j & 1)
-      xmax[(s * 2 + half) * 128 + row] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(x_bar(quarter));
-      ok = __all_sync(0xffffffffu, mbar_wait(x_bar(quarter), uint32_t(j & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
-      if (!ok) break;
-      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + row]);
+      }
+      if (tr) { const long long c1 = clock64(); tc[1] += c1 - c0; c0 = c1; }   // pass 1 (row maximum)
       const float m_blk = mx * p.scale_log2;
-      float m_new = fmaxf(m_used, m_blk);
-      if (j == 0) {
-        m_used = (m_new == -INFINITY) ? 0.f : m_new;
+      if (j == grp) {
+        m_used = (m_blk == -INFINITY) ? 0.f : m_blk;
       } else {
+        const float m_new = fmaxf(m_used, m_blk);
         const bool need = (m_new - m_used > 8.f);
         if (__any_sync(0xffffffffu, need)) {
-          // O must be complete up to block j-1 before it is rescaled.
-          ok = __all_sync(0xffffffffu, mbar_wait(p_empty((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, p.status,
-                                                 kStatusTimeoutTmemEmpty));
+          // O_g must be complete up to this group's previous block before it is rescaled.
+          ok = __all_sync(0xffffffffu, mbar_wait(p_empty(grp), par ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
           if (!ok) break;
           tc_fence_after();
           const float alpha = need ? ex2_approx_f(m_used - m_new) : 1.f;
 #pragma unroll
-          for (int c = half * (D / 32); c < (half + 1) * (D / 32); ++c) {
+          for (int c = 0; c < D / 16; ++c) {
             uint32_t o[16];
-            tmem_ld_32x16(tmem_base + lane_base + Cfg::kColO + c * 16, o);
+            tmem_ld_32x16(o_mine + c * 16, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x16(tmem_base + lane_base + Cfg::kColO + c * 16, o);
+            tmem_st_32x16(o_mine + c * 16, o);
           }
           tmem_st_wait();
           l *= alpha;
           if (need) m_used = m_new;
         }
       }
-      float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = ex2_approx_f(__uint_as_float(r[c][i]) * p.scale_log2 - m_used);
-          sum += pv;
-          r[c][i] = __float_as_uint(pv);
-        }
-      l += sum;
-      // P buffer s is free once PV_{j-2} has been executed.
-      ok = __all_sync(0xffffffffu, mbar_wait(p_empty(s), par ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
+      if (tr) { const long long c1 = clock64(); tc[2] += c1 - c0; c0 = c1; }   // rescale of O (rare)
+      // P buffer g is free once this group's previous PV has been executed.
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty(grp), par ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
       if (!ok) break;
-      uint8_t* prow = smem + Cfg::kOffP + s * Cfg::kPBytes + half * (128 * 128) + (row >> 3) * 1024 + (row & 7) * 128;
+      if (tr) { const long long c1 = clock64(); tc[3] += c1 - c0; c0 = c1; }   // waiting for the P buffer
+      // pass 2: exponentials, row sum, bf16 P into the swizzled operand tile (64 keys = one 128-byte row chunk)
+      float sum = 0.f;
+      uint8_t* prow = smem + Cfg::kOffP + grp * Cfg::kPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t r[2][32];
+        tmem_ld_32x32(s_mine + hh * 64, r[0]);
+        tmem_ld_32x32(s_mine + hh * 64 + 32, r[1]);
+        tmem_ld_wait();
+        const bool full_vis = (limit >= hh * 64 + 63);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(r[c][u * 8 + 0]), __uint_as_float(r[c][u * 8 + 1]));
-          w.y = pack_bf16x2(__uint_as_float(r[c][u * 8 + 2]), __uint_as_float(r[c][u * 8 + 3]));
-          w.z = pack_bf16x2(__uint_as_float(r[c][u * 8 + 4]), __uint_as_float(r[c][u * 8 + 5]));
-          w.w = pack_bf16x2(__uint_as_float(r[c][u * 8 + 6]), __uint_as_float(r[c][u * 8 + 7]));
-          const int unit = (c * 4 + u) ^ (row & 7);  // 16-byte unit inside this half's 128-byte row
-          *reinterpret_cast<uint4*>(prow + unit * 16) = w;
+          for (int i = 0; i < 32; ++i) {
+            float pv = ex2_approx_f(fmaf(__uint_as_float(r[c][i]), p.scale_log2, -m_used));
+            if (!full_vis && hh * 64 + c * 32 + i > limit) pv = 0.f;
+            sum += pv;
+            r[c][i] = __float_as_uint(pv);
+          }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(r[c][u * 8 + 0]), __uint_as_float(r[c][u * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(r[c][u * 8 + 2]), __uint_as_float(r[c][u * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(r[c][u * 8 + 4]), __uint_as_float(r[c][u * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(r[c][u * 8 + 6]), __uint_as_float(r[c][u * 8 + 7]));
+            const int unit = (c * 4 + u) ^ (row & 7);  // 16-byte unit inside the 128-byte row of key chunk hh
+            *reinterpret_cast<uint4*>(prow + hh * (128 * 128) + unit * 16) = w;
+          }
         }
       }
+      l += sum;
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(s));   // one arrival per warp: same-address arrivals serialise
+      if (lane == 0) mbar_arrive(p_full(grp));   // one arrival per warp of the group
+      if (tr) { const long long c1 = clock64(); tc[4] += c1 - c0; c0 = c1; }   // pass 2 (exp, P stores, fence, arrive)
+    }
+    if (tr) {
+      for (int i = 0; i < 5; ++i) p.trace[i] = tc[i];
+      p.trace[15] = tn;
     }
     if (ok && n_blocks > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, p.status, kStatusTimeoutTmemFull));
     }
+    // merge the two groups: exchange (maximum, row sum) with the warp of the other group on the same lane quarter
+    const bool mine_used = n_blocks > grp, other_used = n_blocks > (grp ^ 1);
+    float m_o = 0.f, l_o = 0.f;
     if (ok) {
-      // total row sum = sum of the two halves
-      float* xsum = xmax + (n_blocks & 1) * 256;   // the slot of the next rendezvous parity
-      xsum[half * 128 + row] = l;
+      xmax[(grp * 2 + 0) * 128 + row] = m_used;
+      xmax[(grp * 2 + 1) * 128 + row] = l;
       __syncwarp();
       if (lane == 0) mbar_arrive(x_bar(quarter));
-      ok = __all_sync(0xffffffffu, mbar_wait(x_bar(quarter), uint32_t(n_blocks & 1), abort_flag, p.status, kStatusTimeoutLocalFlag));
-      if (ok) l += xsum[(half ^ 1) * 128 + row];
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar(quarter), 0, abort_flag, p.status, kStatusTimeoutLocalFlag));
+      if (ok) {
+        m_o = xmax[((grp ^ 1) * 2 + 0) * 128 + row];
+        l_o = xmax[((grp ^ 1) * 2 + 1) * 128 + row];
+      }
     }
     if (ok) {
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      float m_all = m_used, a_mine = 1.f, a_other = 0.f;
+      if (mine_used && other_used) {
+        m_all = fmaxf(m_used, m_o);
+        a_mine = ex2_approx_f(m_used - m_all);
+        a_other = ex2_approx_f(m_o - m_all);
+      } else if (!mine_used && other_used) {
+        m_all = m_o; a_mine = 0.f; a_other = 1.f;
+      }
+      const float l_all = (mine_used ? l * a_mine : 0.f) + (other_used ? l_o * a_other : 0.f);
+      const float inv_l = (l_all > 0.f) ? 1.f / l_all : 0.f;
+      const float w_mine = a_mine * inv_l, w_other = a_other * inv_l;
       if (n_blocks > 0) tc_fence_after();
       __nv_bfloat16* orow = p.O + (long long)b * p.so_b + (long long)q_idx * p.so_t + (long long)h * D;
+      const uint32_t o_other = tmem_base + lane_base + Cfg::kColO + (grp ^ 1) * D;
+      // this warp writes output columns [grp * D / 2, (grp + 1) * D / 2) of its 32 rows
+#pragma unroll 1
+      for (int c = grp * (D / 32); c < (grp + 1) * (D / 32); ++c) {
+        uint32_t o[16], o2[16];
+        if (mine_used) tmem_ld_32x16(o_mine + c * 16, o);
+        if (other_used) tmem_ld_32x16(o_other + c * 16, o2);
+        if (mine_used || other_used) tmem_ld_wait();
+        float v[16];
 #pragma unroll
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t o[32];
-        if (n_blocks > 0) {
-          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColO + c * 32, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        for (int i = 0; i < 16; ++i) {
+          float acc = 0.f;
+          if (mine_used) acc = __uint_as_float(o[i]) * w_mine;
+          if (other_used) acc = fmaf(__uint_as_float(o2[i]), w_other, acc);
+          v[i] = acc;
         }
         if (q_idx < p.Tq) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < 2; ++u) {
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv_l, __uint_as_float(o[u * 8 + 1]) * inv_l);
-            w.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv_l, __uint_as_float(o[u * 8 + 3]) * inv_l);
-            w.z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv_l, __uint_as_float(o[u * 8 + 5]) * inv_l);
-            w.w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv_l, __uint_as_float(o[u * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+            w.x = pack_bf16x2(v[u * 8 + 0], v[u * 8 + 1]);
+            w.y = pack_bf16x2(v[u * 8 + 2], v[u * 8 + 3]);
+            w.z = pack_bf16x2(v[u * 8 + 4], v[u * 8 + 5]);
+            w.w = pack_bf16x2(v[u * 8 + 6], v[u * 8 + 7]);
+            *reinterpret_cast<uint4*>(orow + c * 16 + u * 8) = w;
           }
         }
       }
-      if (half == 0 && q_idx < p.Tq)
-        p.lse[((long long)b * p.Hq + h) * p.Tq + q_idx] = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (grp == 0 && q_idx < p.Tq)
+        p.lse[((long long)b * p.Hq + h) * p.Tq + q_idx] = (l_all > 0.f) ? (m_all + log2f(l_all)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -422,6 +503,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
+static long long* g_fwd_trace = nullptr;
 
 template <int D>
 static int launch_flash_fwd(const CUtensorMap& tq, const KvMaps& maps, const FlashFwdParams& p, cudaStream_t st) {
@@ -468,6 +551,7 @@ static int flash_fwd_common(const void* q, const void* const* k_ptrs, const void
   p.causal = causal;
   p.cp_world = cp_world; p.cp_rank = cp_rank; p.zigzag = zigzag;
   p.status = device_status_word();
+  p.trace = g_fwd_trace;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return D == 64 ? launch_flash_fwd<64>(tq, maps, p, st) : launch_flash_fwd<128>(tq, maps, p, st);
 }
@@ -478,6 +562,10 @@ extern "C" {
 
 // q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D], o: [B, Tq, Hq, D]; strides in elements for the batch and time
 // dimensions, heads are D apart, D contiguous.  lse: [B, Hq, Tq] fp32 (natural log).
+// Debug aid: a device buffer of 16 int64 that the next forward launches fill with per-phase SM cycle counts of the
+// CTA of the last query block of head 0 / batch 0 (warp 2, lane 0); nullptr switches it off.
+void lt_flash_fwd_set_trace(void* buf) { lt::g_fwd_trace = static_cast<long long*>(buf); }
+
 int lt_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq, int Tk, int Hq, int Hkv,
                  int D, long long sq_b, long long sq_t, long long sk_b, long long sk_t, long long sv_b, long long sv_t,
                  long long so_b, long long so_t, float scale, int causal, void* stream) {
