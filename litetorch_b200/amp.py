@@ -95,15 +95,26 @@ class GradScaler:
 
     def step(self, optimizer) -> bool:
         params = optimizer.params
+        grads = [_unwrap(p).grad for p in params if _unwrap(p).grad is not None]
+        inv = 1.0 / self._scale
+        if grads and all(g.is_cuda and g.is_contiguous() and g.dtype in (torch.float32, torch.bfloat16) for g in grads):
+            # one pass per gradient: unscale and look for inf / nan together; a single flag read at the end
+            from .ops import kernels as K
+            flag = torch.zeros(1, dtype=torch.int32, device=grads[0].device)
+            with torch.no_grad():
+                for g in grads:
+                    K.unscale_check_(g, inv, flag)
+            self._found_inf = bool(flag.item())
+            if self._found_inf:
+                return False     # the gradients are discarded by the caller's zero_grad; the scale backs off in update()
+            optimizer.step()
+            return True
         self._found_inf = _has_overflow(params)
         if self._found_inf:
             return False
-        inv = 1.0 / self._scale
         with torch.no_grad():
-            for p in params:
-                g = _unwrap(p).grad
-                if g is not None:
-                    g.mul_(inv)
+            for g in grads:
+                g.mul_(inv)
         optimizer.step()
         return True
 

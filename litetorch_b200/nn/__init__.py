@@ -287,7 +287,7 @@ class Dropout(Module):
         self.p = p
 
     def forward(self, x):
-        return Tensor(torch.nn.functional.dropout(_unwrap(x), self.p, self.training))
+        return Tensor(Fn.dropout(_unwrap(x), self.p, self.training))
 
 
 def _act(name, fn):

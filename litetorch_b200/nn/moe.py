@@ -18,9 +18,8 @@ from . import Linear, Module  # nn/__init__ imports this file after defining bot
 
 def route_top_k(x2: torch.Tensor, gate_w: torch.Tensor, top_k: int):
     """fp32 router: returns (weights [N,k], expert ids [N,k], full probabilities [N,E])."""
-    probs = torch.softmax(torch.nn.functional.linear(x2.float(), gate_w.float()), -1)
-    top_p, top_i = probs.topk(top_k, -1)
-    return top_p / top_p.sum(-1, keepdim=True), top_i, probs
+    logits = torch.nn.functional.linear(x2.float(), gate_w.float())
+    return Fn.moe_router(logits, top_k, renorm=True)
 
 
 def grouped_expert_apply(x2: torch.Tensor, top_w: torch.Tensor, top_i: torch.Tensor, n_experts: int, expert_fn):

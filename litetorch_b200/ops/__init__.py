@@ -53,11 +53,21 @@ class Ops:
 
     # ------------------------------------------------------------------ reductions (full reduce to shape [1])
     @staticmethod
-    def sum(a): return _w(_unwrap(a).sum().reshape(1))
+    def sum(a):
+        t = _unwrap(a)
+        if t.is_cuda and not t.requires_grad and t.dtype in (torch.float32, torch.bfloat16) and t.numel() > 0:
+            from . import kernels as K
+            return _w(K.reduce_all(t, "sum").to(t.dtype))
+        return _w(t.sum().reshape(1))
     @staticmethod
     def mean(a): return _w(_unwrap(a).mean().reshape(1))
     @staticmethod
-    def max(a): return _w(_unwrap(a).max().reshape(1))
+    def max(a):
+        t = _unwrap(a)
+        if t.is_cuda and not t.requires_grad and t.dtype in (torch.float32, torch.bfloat16) and t.numel() > 0:
+            from . import kernels as K
+            return _w(K.reduce_all(t, "max").to(t.dtype))
+        return _w(t.max().reshape(1))
 
     # ------------------------------------------------------------------ shape
     @staticmethod
@@ -110,7 +120,7 @@ class Ops:
     @staticmethod
     def silu(a): return _w(F.silu(_unwrap(a)))
     @staticmethod
-    def softmax(a, dim: int = -1): return _w(torch.softmax(_unwrap(a), dim))
+    def softmax(a, dim: int = -1): return _w(Fn.softmax(_unwrap(a), dim))
     @staticmethod
     def gelu(a): return _w(Fn.gelu(_unwrap(a)))
     @staticmethod

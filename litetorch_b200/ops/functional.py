@@ -313,3 +313,84 @@ def embedding(idx, table):
     if _native(table) and table.shape[1] % 8 == 0 and idx.is_cuda:
         return _Embedding.apply(idx, table)
     return F.embedding(idx.to(torch.int64), table)
+
+
+# ------------------------------------------------------------------------------------------------ softmax / dropout / router
+class _Softmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        y = K.softmax_fwd(x)
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        return K.softmax_bwd(y, dy.contiguous())
+
+
+def softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """Softmax over `dim`; the last-dimension case of fp32 / bf16 CUDA tensors runs on the warp-per-row kernel
+    (reference: Ops::softmax, src/ops/activation.cpp:507-578)."""
+    if _native(x) and x.dtype in (torch.float32, torch.bfloat16) and dim in (-1, x.dim() - 1) and x.numel() > 0:
+        return _Softmax.apply(x.contiguous())
+    return torch.softmax(x, dim)
+
+
+_dropout_offset = [0]
+
+
+class _Dropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, seed, offset):
+        ctx.p, ctx.seed, ctx.offset = p, seed, offset
+        return K.dropout(x, p, seed, offset)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return K.dropout(dy.contiguous(), ctx.p, ctx.seed, ctx.offset), None, None, None
+
+
+def dropout(x: torch.Tensor, p: float, training: bool = True) -> torch.Tensor:
+    """Inverted dropout. On CUDA the mask comes from a Philox counter keyed by torch's seed and a running offset, and
+    backward regenerates it instead of storing it (reference: nn::Dropout, src/nn/dropout.cpp, which keeps a mask)."""
+    if not training or p <= 0.0:
+        return x
+    if _native(x) and x.dtype in (torch.float32, torch.bfloat16):
+        seed = torch.initial_seed()
+        offset = _dropout_offset[0]
+        _dropout_offset[0] += (x.numel() + 3) // 4
+        return _Dropout.apply(x.contiguous(), float(p), seed, offset)
+    return torch.nn.functional.dropout(x, p, True)
+
+
+class _Router(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, top_k, renorm):
+        probs, tw, ti = K.moe_router(logits, top_k, renorm=renorm)
+        ctx.save_for_backward(probs, tw, ti)
+        ctx.renorm = renorm
+        ctx.in_dtype = logits.dtype
+        ctx.mark_non_differentiable(ti)
+        return tw, ti, probs
+
+    @staticmethod
+    def backward(ctx, d_tw, d_ti, d_probs):
+        probs, tw, ti = ctx.saved_tensors
+        if d_tw is None:
+            d_tw = torch.zeros_like(tw)
+        dl = K.moe_router_bwd(probs, ti, tw, d_tw, d_probs, renorm=ctx.renorm)
+        return dl.to(ctx.in_dtype), None, None
+
+
+def moe_router(logits: torch.Tensor, top_k: int, renorm: bool = True):
+    """(top-k weights [N, k] fp32, expert ids [N, k], softmax probabilities [N, E] fp32) of router logits [N, E];
+    the warp-per-token kernel on CUDA when E <= 256 and k <= 8 (reference: Ops::moe_gate, src/ops/moe_ops.cpp:11-106)."""
+    if _native(logits) and logits.dtype in (torch.float32, torch.bfloat16) and logits.shape[1] <= 256 and top_k <= 8:
+        tw, ti, probs = _Router.apply(logits.contiguous(), top_k, renorm)
+        return tw, ti.long(), probs
+    probs = torch.softmax(logits.float(), -1)
+    top_p, top_i = probs.topk(top_k, -1)
+    if renorm:
+        top_p = top_p / top_p.sum(-1, keepdim=True)
+    return top_p, top_i, probs

@@ -26,6 +26,16 @@ _SIGS = {
     "lt_flash_bwd_set_debug": [_i],
     "lt_gemm_fp8_block": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp, _vp, _i, _vp, _i, _vp],
     "lt_quant_fp8_1x128": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
+    "lt_moe_router": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lt_moe_router_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lt_dropout": [_vp, _vp, _ll, _i, _f, ctypes.c_ulonglong, ctypes.c_ulonglong, _vp],
+    "lt_softmax_fwd": [_vp, _vp, _ll, _i, _i, _vp],
+    "lt_softmax_bwd": [_vp, _vp, _vp, _ll, _i, _i, _vp],
+    "lt_quant_fp8_128x128": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
+    "lt_unscale_check": [_vp, _ll, _i, _f, _vp, _vp],
+    "lt_reduce_parts": [],
+    "lt_reduce_all": [_vp, _ll, _i, _i, _vp, _vp, _vp],
+    "lt_strided_copy": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp],
     "lt_norm_bwd_ctas": [_i],
     "lt_norm_fwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_norm_bwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -70,7 +80,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_flash_bwd_set_debug": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_flash_bwd_set_debug": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -571,3 +581,120 @@ def moe_gemm_scatter(a, group_of_mblk, weights, *, b_major, slot_dst, row_weight
     rc = _fn("lt_moe_gemm_scatter")(a.data_ptr(), group_of_mblk.data_ptr(), slots, weights.data_ptr(), E, N, Kd, b_major,
                                     slot_dst.data_ptr(), _p(row_weight), ctypes.cast(_ptr_array(acc_ptrs), c_void_p), world, _stream())
     _check(rc, "lt_moe_gemm_scatter")
+
+
+# ------------------------------------------------------------------------------------------------ router, dropout, softmax ...
+def _dt(t):
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError("expected float32 or bfloat16, got %s" % t.dtype)
+
+
+def moe_router(logits, top_k: int, *, renorm: bool = True, counts=None, mass=None):
+    """logits [N, E] (fp32 / bf16) -> (probs [N, E] fp32, topk_w [N, k] fp32, topk_idx [N, k] int32).
+    counts [E] int32 and mass [E] fp32 are accumulated into when given (load-balancing statistics)."""
+    N, E = logits.shape
+    logits = logits.contiguous()
+    probs = torch.empty(N, E, dtype=torch.float32, device=logits.device)
+    tw = torch.empty(N, top_k, dtype=torch.float32, device=logits.device)
+    ti = torch.empty(N, top_k, dtype=torch.int32, device=logits.device)
+    rc = _fn("lt_moe_router")(logits.data_ptr(), _dt(logits), probs.data_ptr(), tw.data_ptr(), ti.data_ptr(), _p(counts),
+                              _p(mass), N, E, top_k, 1 if renorm else 0, _stream())
+    _check(rc, "lt_moe_router")
+    return probs, tw, ti
+
+
+def moe_router_bwd(probs, topk_idx, topk_w, d_topk_w, d_probs=None, *, renorm: bool = True):
+    """Gradient of the router logits [N, E] fp32 from d(topk_w) and, optionally, a dense d(probs)."""
+    N, E = probs.shape
+    k = topk_idx.shape[1]
+    dl = torch.empty(N, E, dtype=torch.float32, device=probs.device)
+    d_topk_w = d_topk_w.contiguous().float()
+    if d_probs is not None:
+        d_probs = d_probs.contiguous().float()
+    rc = _fn("lt_moe_router_bwd")(probs.data_ptr(), topk_idx.data_ptr(), topk_w.data_ptr(), d_topk_w.data_ptr(), _p(d_probs),
+                                  dl.data_ptr(), N, E, k, 1 if renorm else 0, _stream())
+    _check(rc, "lt_moe_router_bwd")
+    return dl
+
+
+def dropout(x, p: float, seed: int, offset: int = 0, out=None):
+    """y = x * keep / (1 - p) with a Philox mask that depends only on (seed, offset, element index); the same call on
+    the upstream gradient is the backward pass."""
+    x = x.contiguous()
+    y = torch.empty_like(x) if out is None else out
+    rc = _fn("lt_dropout")(x.data_ptr(), y.data_ptr(), x.numel(), _dt(x), float(p), int(seed) & (2 ** 64 - 1),
+                           int(offset) & (2 ** 64 - 1), _stream())
+    _check(rc, "lt_dropout")
+    return y
+
+
+def softmax_fwd(x):
+    """Softmax over the last dimension of a contiguous fp32 / bf16 tensor."""
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    D = x.shape[-1]
+    rc = _fn("lt_softmax_fwd")(x.data_ptr(), y.data_ptr(), x.numel() // D, D, _dt(x), _stream())
+    _check(rc, "lt_softmax_fwd")
+    return y
+
+
+def softmax_bwd(y, dy):
+    y, dy = y.contiguous(), dy.contiguous()
+    dx = torch.empty_like(y)
+    D = y.shape[-1]
+    rc = _fn("lt_softmax_bwd")(y.data_ptr(), dy.data_ptr(), dx.data_ptr(), y.numel() // D, D, _dt(y), _stream())
+    _check(rc, "lt_softmax_bwd")
+    return dx
+
+
+def quant_fp8_128x128(w):
+    """w [N, K] bf16 (K a multiple of 128) -> (e4m3 codes [N, K], scales [ceil(N/128), K/128] fp32)."""
+    N, K = w.shape
+    assert w.dtype == torch.bfloat16 and w.stride(1) == 1 and K % 128 == 0
+    q = torch.empty(N, K, dtype=torch.float8_e4m3fn, device=w.device)
+    sc = torch.empty((N + 127) // 128, K // 128, dtype=torch.float32, device=w.device)
+    rc = _fn("lt_quant_fp8_128x128")(w.data_ptr(), w.stride(0), q.data_ptr(), q.stride(0), sc.data_ptr(), N, K, _stream())
+    _check(rc, "lt_quant_fp8_128x128")
+    return q, sc
+
+
+def unscale_check_(g, inv_scale: float, found_inf):
+    """g *= inv_scale in place; found_inf (int32 device scalar) is set to 1 if g held an inf or a nan."""
+    assert g.is_contiguous() and found_inf.dtype == torch.int32
+    rc = _fn("lt_unscale_check")(g.data_ptr(), g.numel(), _dt(g), float(inv_scale), found_inf.data_ptr(), _stream())
+    _check(rc, "lt_unscale_check")
+    return g
+
+
+_reduce_scratch = {}
+
+
+def reduce_all(x, mode: str = "sum"):
+    """Sum or maximum of every element of a contiguous fp32 / bf16 tensor -> fp32 tensor of shape [1]."""
+    x = x.contiguous()
+    key = x.device
+    part = _reduce_scratch.get(key)
+    if part is None:
+        part = torch.empty(_fn("lt_reduce_parts")(), dtype=torch.float32, device=x.device)
+        _reduce_scratch[key] = part
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    rc = _fn("lt_reduce_all")(x.data_ptr(), x.numel(), _dt(x), 1 if mode == "max" else 0, part.data_ptr(), out.data_ptr(),
+                              _stream())
+    _check(rc, "lt_reduce_all")
+    return out
+
+
+def strided_copy(src, dst):
+    """dst[...] = src[...] for two views of the same shape (<= 8 dimensions, same element size): the gather behind
+    `contiguous()` and the scatter behind `cat`."""
+    assert src.shape == dst.shape and src.element_size() == dst.element_size() and 1 <= src.dim() <= 8
+    nd = src.dim()
+    arr = ctypes.c_longlong * nd
+    rc = _fn("lt_strided_copy")(src.data_ptr(), dst.data_ptr(), nd, ctypes.cast(arr(*src.shape), c_void_p),
+                                ctypes.cast(arr(*src.stride()), c_void_p), ctypes.cast(arr(*dst.stride()), c_void_p),
+                                src.element_size(), _stream())
+    _check(rc, "lt_strided_copy")
+    return dst

@@ -136,6 +136,9 @@ def quantize_fp8_1x128(x: torch.Tensor):
 def quantize_fp8_128x128(w: torch.Tensor):
     """Weights: e4m3 codes and one fp32 scale per 128 x 128 block."""
     N, Kd = w.shape
+    if w.is_cuda and w.dtype == torch.bfloat16 and Kd % 128 == 0:
+        from .ops import kernels as K
+        return K.quant_fp8_128x128(w.contiguous())
     assert N % 128 == 0 and Kd % 128 == 0
     wb = w.float().view(N // 128, 128, Kd // 128, 128)
     amax = wb.abs().amax((1, 3)).clamp_min(1e-12)
