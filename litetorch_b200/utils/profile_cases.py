@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adamw|ce [reps]
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|flash_fwd|flash_bwd|rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
 handful of times and exits, so a capture with `-k regex:<kernel> -c 3` ends by itself in a minute or two.
@@ -36,6 +36,19 @@ def main():
         do = torch.randn(B, T, Hq, D, device=dev).bfloat16()
         o, lse = K.flash_fwd(q, k, v, causal=True)
         fn = (lambda: K.flash_fwd(q, k, v, causal=True)) if case == "flash_fwd" else (lambda: K.flash_bwd(q, k, v, o, lse, do, causal=True))
+    elif case == "gemm_fp8":      # block-scaled e4m3 GEMM, gate_up forward shape
+        x = torch.randn(8192, 2048, device=dev).bfloat16()
+        w = (torch.randn(11264, 2048, device=dev) * 0.05).bfloat16()
+        xq, xst = K.quant_fp8_1x128(x)
+        wq, ws = K.quant_fp8_128x128(w)
+        c = torch.empty(8192, 11264, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c)
+    elif case == "rmsnorm_bwd":
+        x = torch.randn(65536, 2048, device=dev).bfloat16()
+        dy = torch.randn(65536, 2048, device=dev).bfloat16()
+        w = torch.ones(2048, device=dev).bfloat16()
+        _, _, _, rstd = K.norm_fwd(x, w, None, None)
+        fn = lambda: K.norm_bwd(dy, x, w, None, rstd)
     elif case == "rmsnorm":
         x = torch.randn(65536, 2048, device=dev).bfloat16()
         w = torch.ones(2048, device=dev).bfloat16()
