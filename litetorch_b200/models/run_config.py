@@ -1,0 +1,200 @@
+"""Training throughput of the parallel decoder configurations (tokens/s, device-timed, max over ranks).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        -m litetorch_b200.models.run_config --config tp8 [--tiny] [--steps 5] [--warmup 3]
+
+  tp8    Llama-3-8B shape, tensor parallel over all ranks with sequence parallelism, seq 8192, 8 sequences per step
+  ep8    MoE decoder (8 SwiGLU experts, top-2, capacity 1.25, aux 0.01), expert parallel over all ranks with
+         data-parallel attention, seq 4096, micro-batch 2 per rank
+  hybrid Llama-style 3B, TP2 x CP2 x PP2 (8 ranks), seq 32768 split by zigzag ring attention, 1F1B with 8 micro-batches
+         of one sequence, activation checkpointing
+
+`--tiny` runs the same parallel structure on a small shape (any even world size for tp8 / ep8; 8, 4 or 2 ranks for
+hybrid, dropping axes).  Synthetic uniform-random tokens, N(0, 0.02) initialisation, AdamW (fp32 master weights).
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..core import Tensor, _unwrap
+from ..optim import AdamW
+from .decoder import PRESETS, ParallelDecoder, ParallelDims, shard_batch, tiny
+
+
+def _make_groups(world: int, rank: int, tp: int, cp: int, pp: int, dp: int):
+    """rank = ((pp_i * dp + dp_i) * cp + cp_i) * tp + tp_i; every rank creates every group, in the same order."""
+    assert tp * cp * pp * dp == world
+    coords = lambda r: (r // (dp * cp * tp), (r // (cp * tp)) % dp, (r // tp) % cp, r % tp)   # noqa: E731
+    mine = coords(rank)
+    out = {}
+    for axis, name in ((3, "tp"), (2, "cp"), (1, "dp"), (0, "pp")):
+        sizes = {"tp": tp, "cp": cp, "dp": dp, "pp": pp}
+        if sizes[name] == 1:
+            out[name] = None
+            continue
+        buckets = {}
+        for r in range(world):
+            c = coords(r)
+            key = tuple(v for i, v in enumerate(c) if i != axis)
+            buckets.setdefault(key, []).append(r)
+        for key in sorted(buckets):
+            g = dist.new_group(buckets[key])
+            if rank in buckets[key]:
+                out[name] = g
+    return out, mine
+
+
+class _Stage:
+    """What PipelineParallelModule calls per micro-batch: token ids on the first stage, row activations elsewhere."""
+
+    def __init__(self, model: ParallelDecoder, B: int, T_local: int):
+        self.model, self.B, self.T = model, B, T_local
+
+    def __call__(self, x: Tensor) -> Tensor:
+        from ..core import _unwrap
+        t = _unwrap(x)
+        rows = self.model.embed_tokens(t) if self.model.is_first else t
+        return Tensor(self.model.run_layers(rows, self.B, self.T))
+
+    def parameters(self):
+        return [Tensor(p) for p in self.model.parameters()]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", choices=["tp8", "ep8", "hybrid"], required=True)
+    ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-fused", action="store_true", help="plain NCCL collectives instead of the fused kernels")
+    ap.add_argument("--seq", type=int, default=0)
+    args = ap.parse_args()
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(local)
+    dev = "cuda" if cuda else "cpu"
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", local) if cuda else None)
+    dtype = torch.bfloat16 if cuda else torch.float32
+    fused = cuda and not args.no_fused and world > 1
+
+    if args.config == "tp8":
+        cfg = PRESETS["tiny-dense"] if args.tiny else PRESETS["llama3-8b"]
+        seq = args.seq or (512 if args.tiny else 8192)
+        n_seq, micro = (2 if args.tiny else 8), 1
+        groups, _ = _make_groups(world, rank, world, 1, 1, 1)
+        layout = "tp%d+sp" % world
+    elif args.config == "ep8":
+        cfg = PRESETS["tiny-moe"] if args.tiny else PRESETS["moe-8x2b"]
+        if cfg.n_experts % world:
+            cfg = tiny(cfg, n_experts=world * max(1, cfg.n_experts // world))
+        seq = args.seq or (256 if args.tiny else 4096)
+        n_seq, micro = 2, 1
+        groups = {"tp": None, "cp": None, "pp": None, "dp": None}
+        layout = "ep%d+dp-attention" % world
+    else:
+        cfg = PRESETS["tiny-dense"] if args.tiny else PRESETS["llama-3b-long"]
+        seq = args.seq or (1024 if args.tiny else 32768)
+        n_seq, micro = 1, 8
+        tp, cp, pp = (2, 2, 2) if world >= 8 else ((2, 2, 1) if world == 4 else ((2, 1, 1) if world == 2 else (1, 1, 1)))
+        groups, _ = _make_groups(world, rank, tp, cp, pp, world // (tp * cp * pp))
+        layout = "tp%d x cp%d x pp%d" % (tp, cp, pp)
+    ep_group = dist.group.WORLD if (args.config == "ep8" and world > 1) else None
+
+    dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True)
+    T_local = seq // dims.cp_world
+    hq_l, hkv_l = cfg.n_q // dims.tp_world, cfg.n_kv // dims.tp_world
+    if fused and dims.tp is not None:
+        from ..parallel.tp_fused import TPFusedContext
+        widest = max(cfg.d_model, (hq_l + 2 * hkv_l) * cfg.head_dim, 2 * cfg.ffn // dims.tp_world,
+                     cfg.vocab // dims.tp_world)
+        dims.tp_fused = TPFusedContext(n_seq * T_local, widest, dev, group=dims.tp)
+    if fused and dims.cp is not None:
+        from ..parallel.cp import RingFlashContext
+        dims.cp_fused = RingFlashContext(n_seq, T_local, hq_l, hkv_l, cfg.head_dim, dev, group=dims.cp, zigzag=True)
+
+    pp_world = dist.get_world_size(groups["pp"]) if groups["pp"] is not None else 1
+    pp_rank = dist.get_rank(groups["pp"]) if groups["pp"] is not None else 0
+    per = cfg.n_layers // pp_world
+    model = ParallelDecoder(cfg, dims, device=dev, dtype=dtype, seed=1, first_layer=pp_rank * per,
+                            last_layer=(pp_rank + 1) * per if pp_rank < pp_world - 1 else cfg.n_layers,
+                            max_tokens=n_seq * T_local, activation_checkpointing=(args.config == "hybrid"))
+    opt = AdamW([Tensor(p) for p in model.parameters()], lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
+
+    gen = torch.Generator().manual_seed(1234 + (0 if args.config != "ep8" else rank))
+    def batch():
+        ids = torch.randint(0, cfg.vocab, (n_seq, seq + 1), generator=gen)
+        x, y = ids[:, :-1], ids[:, 1:]
+        return shard_batch(x, dims).to(dev), shard_batch(y, dims).to(dev)
+
+    pipe = None
+    if pp_world > 1:
+        from ..parallel.pp import PipelineParallelModule
+        pipe = PipelineParallelModule(_Stage(model, n_seq, T_local), group=groups["pp"], device=dev)
+
+    def step():
+        opt.zero_grad()
+        if pipe is None:
+            for _ in range(micro):
+                x, y = batch()
+                loss = model.forward_loss(x, y)
+                (loss / micro).backward()
+            last = loss.detach()
+        else:
+            mbs = [batch() for _ in range(micro)]
+            xs, ys = [Tensor(m[0]) for m in mbs], [m[1] for m in mbs]
+            val = pipe.train_step_1f1b(xs, lambda out, tgt: Tensor(model.loss(_unwrap(out), tgt)), ys)
+            last = torch.tensor(val, device=dev)
+        model.reduce_gradients()
+        opt.step()
+        return last
+
+    for _ in range(args.warmup):
+        last = step()
+    if cuda:
+        torch.cuda.synchronize()
+    dist.barrier()
+    if cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    import time
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        last = step()
+    if cuda:
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+    else:
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    lv = last.float().reshape(1).clone()
+    dist.all_reduce(lv, op=dist.ReduceOp.MAX)
+    dp_like = world if args.config == "ep8" else (dist.get_world_size(groups["dp"]) if groups["dp"] is not None else 1)
+    tokens = n_seq * seq * micro * dp_like
+    if rank == 0:
+        status = 0
+        if cuda:
+            from ..ops import kernels as K
+            status = K.status_fetch()
+        print(json.dumps({"config": args.config, "model": cfg.name, "layout": layout, "n_gpus": world, "seq_len": seq,
+                          "tokens_per_step": tokens, "ms_per_step": round(float(t), 3),
+                          "tokens_per_s": round(tokens / float(t) * 1e3, 1), "loss": round(float(lv), 4),
+                          "fused": bool(fused), "dtype": str(dtype).replace("torch.", ""), "device_status": status,
+                          "params_b": round(cfg.n_params() / 1e9, 3)}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -224,6 +224,33 @@ def rope(x, cos, sin):
     return _rope_torch(x, cos, sin)
 
 
+class _RopeBTHD(torch.autograd.Function):
+    """x: [B, T, H, D], the layout of the fused QKV projection: rotated on a copy, no transposes."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        B, T, H, D = x.shape
+        y = x.contiguous().clone()
+        K.rope_(y.view(B * T, H * D), cos, sin, T, H, D)
+        ctx.save_for_backward(cos, sin)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        B, T, H, D = dy.shape
+        g = dy.contiguous().clone()
+        K.rope_(g.view(B * T, H * D), cos, sin, T, H, D, backward=True)
+        return g, None, None
+
+
+def rope_bthd(x, cos, sin):
+    """RoPE on [B, T, H, D] (interleaved pairs, cos/sin [T, D/2])."""
+    if _native(x) and x.dim() == 4 and x.shape[-1] % 8 == 0 and cos.is_cuda:
+        return _RopeBTHD.apply(x, cos.float().contiguous(), sin.float().contiguous())
+    return _rope_torch(x.transpose(1, 2), cos, sin).transpose(1, 2)
+
+
 # ---------------------------------------------------------------------------------------------- attention
 class _Flash(torch.autograd.Function):
     """q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D]."""

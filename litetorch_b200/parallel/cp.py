@@ -106,8 +106,9 @@ def _exchange(t: torch.Tensor, pg, shift: int) -> torch.Tensor:
     dst, src = (r + shift) % W, (r - shift) % W
     gd = dist.get_global_rank(g, dst) if g is not None else dst
     gs = dist.get_global_rank(g, src) if g is not None else src
+    t = t.contiguous()
     out = torch.empty_like(t)
-    ops = [dist.P2POp(dist.isend, t.contiguous(), gd, g), dist.P2POp(dist.irecv, out, gs, g)]
+    ops = [dist.P2POp(dist.isend, t, gd, g), dist.P2POp(dist.irecv, out, gs, g)]
     for w in dist.batch_isend_irecv(ops):
         w.wait()
     return out
