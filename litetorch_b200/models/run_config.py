@@ -115,9 +115,8 @@ def main():
     hq_l, hkv_l = cfg.n_q // dims.tp_world, cfg.n_kv // dims.tp_world
     if fused and dims.tp is not None:
         from ..parallel.tp_fused import TPFusedContext
-        widest = max(cfg.d_model, (hq_l + 2 * hkv_l) * cfg.head_dim, 2 * cfg.ffn // dims.tp_world,
-                     cfg.vocab // dims.tp_world)
-        dims.tp_fused = TPFusedContext(n_seq * T_local, widest, dev, group=dims.tp)
+        # gathered inputs and scattered outputs of the parallel linears are all d_model wide
+        dims.tp_fused = TPFusedContext(n_seq * T_local, cfg.d_model, dev, group=dims.tp)
     if fused and dims.cp is not None:
         from ..parallel.cp import RingFlashContext
         dims.cp_fused = RingFlashContext(n_seq, T_local, hq_l, hkv_l, cfg.head_dim, dev, group=dims.cp, zigzag=True)

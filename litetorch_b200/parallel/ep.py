@@ -95,9 +95,7 @@ class MoEFeedForward:
         """fp32 router. Returns (weights [N,k], experts [N,k], keep mask [N,k], aux loss)."""
         N = x2.shape[0]
         logits = torch.nn.functional.linear(x2.float(), _unwrap(self.gate_weight).float())
-        probs = torch.softmax(logits, -1)
-        top_p, top_i = probs.topk(self.k, -1)
-        top_w = top_p / top_p.sum(-1, keepdim=True)
+        top_w, top_i, probs = Fn.moe_router(logits, self.k, renorm=True)   # warp-per-token kernel on CUDA
         # load balance: f_e = fraction of routed slots on expert e, P_e = mean router probability
         f = torch.zeros(self.E, device=x2.device).index_add_(0, top_i.reshape(-1), torch.ones(N * self.k, device=x2.device)) / (N * self.k)
         aux = self.E * (f * probs.mean(0)).sum()

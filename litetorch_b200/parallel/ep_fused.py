@@ -108,7 +108,13 @@ class _MoEFused(torch.autograd.Function):
         sb = m.slot_buf[:S * d].view(S, d)
         gu = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_gu, b_major=0, slot_buf=sb, flags=m.flags, epoch=m.epoch,
                                n_comm=m.n_comm)
-        xs = sb.clone()                               # routed inputs, kept for the weight gradient
+        # Padding slots (the tail of every expert's last 128-row block) are never fetched: their rows of the staging
+        # buffer and of everything computed from it are whatever was there before, possibly NaN bit patterns.  Nothing
+        # reads them in the forward (the combine skips them), but the weight-gradient GEMMs sum over all rows of a
+        # block, so they are cleared (0 * NaN is NaN: masked, not multiplied).
+        pad = (slot[:, 0] < 0)[:, None]
+        xs = sb.clone().masked_fill_(pad, 0)          # routed inputs, kept for the weight gradient
+        gu = gu.masked_fill(pad, 0)
         h = K.swiglu_fwd(gu)
         K.moe_gemm_scatter(h, group, w_dn, b_major=0, slot_dst=slot, row_weight=w, acc_ptrs=m.acc.ptrs, world=m.world)
         m.barrier()                                   # every rank has added its experts' outputs
@@ -134,13 +140,14 @@ class _MoEFused(torch.autograd.Function):
         # dh (unweighted) = dy_slot @ W_down : gather dy rows, B stored [E, K=d, N=F]
         dh_u = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_dn, b_major=1, slot_buf=sb, flags=m.flags, epoch=m.epoch,
                                  n_comm=m.n_comm)
-        dys = sb                                       # gathered dy rows
         valid = (slot[:, 0] >= 0)
-        dw_slot = (h.float() * dh_u.float()).sum(-1) * valid
+        pad = ~valid[:, None]
+        dys = sb.masked_fill(pad, 0)                   # gathered dy rows (padding rows cleared, see forward)
+        dh_u = dh_u.masked_fill(pad, 0)
+        dw_slot = (h.float() * dh_u.float()).sum(-1)
         dh = (dh_u.float() * w[:, None]).to(torch.bfloat16)
         hw = (h.float() * w[:, None]).to(torch.bfloat16)
-        dgu = K.swiglu_bwd(gu.clone(), dh, inplace=True)
-        dgu = dgu * valid[:, None].to(dgu.dtype)
+        dgu = K.swiglu_bwd(gu.clone(), dh, inplace=True).masked_fill_(pad, 0)
         # weight gradients per expert on its slot range
         dwgu, dwdn = torch.zeros_like(w_gu), torch.zeros_like(w_dn)
         g_cpu = group.tolist()
