@@ -76,9 +76,10 @@ class ParallelDims:
     `None` means that axis has size one.  `tp_fused` / `cp_fused` are the symmetric-memory contexts of the fused
     kernels (None: plain collectives)."""
 
-    def __init__(self, tp=None, cp=None, ep=None, dp=None, pp=None, tp_fused=None, cp_fused=None, zigzag=True):
+    def __init__(self, tp=None, cp=None, ep=None, dp=None, pp=None, tp_fused=None, cp_fused=None, zigzag=True, fp8=False):
         self.tp, self.cp, self.ep, self.dp, self.pp = tp, cp, ep, dp, pp
         self.tp_fused, self.cp_fused, self.zigzag = tp_fused, cp_fused, zigzag
+        self.fp8 = fp8      # e4m3 GEMMs (1x128 / 128x128 block scales) in the parallel linears; collectives stay NCCL
 
     @property
     def tp_world(self): return _w(self.tp)
@@ -93,21 +94,23 @@ class ParallelDims:
 # ------------------------------------------------------------------------------------------------ parallel linears
 def ag_linear(dims: ParallelDims, x_rows: torch.Tensor, w_local: torch.Tensor) -> torch.Tensor:
     """y = all_gather_rows(x) @ w_local^T   (column-parallel weight, sequence-parallel input)."""
+    lin = Fn.linear_fp8 if dims.fp8 else Fn.linear
     if dims.tp_world == 1:
-        return Fn.linear(x_rows, w_local)
-    if dims.tp_fused is not None:
+        return lin(x_rows, w_local)
+    if dims.tp_fused is not None and not dims.fp8:
         return dims.tp_fused.ag_linear(x_rows, w_local, None)
     full = _tp._GatherFwdScatterBwd.apply(x_rows, 0, dims.tp, True)
-    return Fn.linear(full, w_local)
+    return lin(full, w_local)
 
 
 def linear_rs(dims: ParallelDims, x: torch.Tensor, w_local: torch.Tensor) -> torch.Tensor:
     """y_rows = reduce_scatter_rows(x @ w_local^T)   (row-parallel weight, sequence-parallel output)."""
+    lin = Fn.linear_fp8 if dims.fp8 else Fn.linear
     if dims.tp_world == 1:
-        return Fn.linear(x, w_local)
-    if dims.tp_fused is not None:
+        return lin(x, w_local)
+    if dims.tp_fused is not None and not dims.fp8:
         return dims.tp_fused.linear_rs(x, w_local)
-    return _tp._ScatterFwdGatherBwd.apply(Fn.linear(x, w_local), 0, dims.tp)
+    return _tp._ScatterFwdGatherBwd.apply(lin(x, w_local), 0, dims.tp)
 
 
 def _param(shape, std, gen, device, dtype, reduce_groups=()):

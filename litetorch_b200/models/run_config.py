@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-fused", action="store_true", help="plain NCCL collectives instead of the fused kernels")
     ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--fp8", action="store_true", help="e4m3 GEMMs with 1x128 / 128x128 block scales (NCCL collectives)")
     args = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -110,7 +111,8 @@ def main():
         layout = "tp%d x cp%d x pp%d" % (tp, cp, pp)
     ep_group = dist.group.WORLD if (args.config == "ep8" and world > 1) else None
 
-    dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True)
+    dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True,
+                        fp8=args.fp8 and cuda)
     T_local = seq // dims.cp_world
     hq_l, hkv_l = cfg.n_q // dims.tp_world, cfg.n_kv // dims.tp_world
     if fused and dims.tp is not None:
@@ -189,7 +191,7 @@ def main():
         print(json.dumps({"config": args.config, "model": cfg.name, "layout": layout, "n_gpus": world, "seq_len": seq,
                           "tokens_per_step": tokens, "ms_per_step": round(float(t), 3),
                           "tokens_per_s": round(tokens / float(t) * 1e3, 1), "loss": round(float(lv), 4),
-                          "fused": bool(fused), "dtype": str(dtype).replace("torch.", ""), "device_status": status,
+                          "fused": bool(fused) and not dims.fp8, "fp8": bool(dims.fp8), "dtype": str(dtype).replace("torch.", ""), "device_status": status,
                           "params_b": round(cfg.n_params() / 1e9, 3)}), flush=True)
     dist.barrier()
     dist.destroy_process_group()

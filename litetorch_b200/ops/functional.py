@@ -77,6 +77,42 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, a
     return F.gelu(y, approximate="tanh") if code == 1 else y
 
 
+class _LinearFP8(torch.autograd.Function):
+    """y = x @ w^T with e4m3 operands: 1 x 128 scales on the activations (and on dY), 128 x 128 scales on the weight
+    (and on its transpose for the input gradient); the weight gradient stays in bf16.  Master weights are bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _2d(x).contiguous()
+        xq, xs = K.quant_fp8_1x128(x2)
+        wq, ws = K.quant_fp8_128x128(w.contiguous())
+        y = K.gemm_fp8_block(xq, xs, wq, ws)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _2d(dy).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = K.quant_fp8_1x128(dy2)
+            wtq, wts = K.quant_fp8_128x128(w.t().contiguous())      # [K, N]: the B operand of dX = dY @ W
+            dx = K.gemm_fp8_block(gq, gs, wtq, wts).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = K.gemm(dy2, x2, a_major=1, b_major=1)
+        return dx, dw
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Linear layer on the block-scaled fp8 tensor-core path (forward and input gradient); shapes must be multiples
+    of 128 in both feature dimensions.  Falls back to `linear` elsewhere."""
+    if _native(x, w) and x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0 and w.shape[0] % 128 == 0 and x.numel() > 0:
+        return _LinearFP8.apply(x, w)
+    return linear(x, w)
+
+
 class _MatmulNN(torch.autograd.Function):
     """C = A[M,K] @ B[K,N] for 2-D bf16 CUDA operands."""
 

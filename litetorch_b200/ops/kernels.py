@@ -25,6 +25,7 @@ _SIGS = {
     "lt_flash_fwd_set_trace": [_vp],
     "lt_flash_bwd_set_debug": [_i],
     "lt_gemm_fp8_block": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp, _vp, _i, _vp, _i, _vp],
+    "lt_gemm_fp8_block_pair": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp, _vp, _i, _vp, _vp],
     "lt_quant_fp8_1x128": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
     "lt_moe_router": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lt_moe_router_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -209,8 +210,9 @@ def quant_fp8_1x128(x):
     return q, st
 
 
-def gemm_fp8_block(a8, a_scale_t, b8, b_scale, out=None, *, bias=None, out_dtype=torch.bfloat16, max_ctas=0):
-    """out[M, N] = block-scaled a8[M, K] @ b8[N, K]^T.  a_scale_t: [K/128, M] fp32; b_scale: [ceil(N/128), K/128] fp32."""
+def gemm_fp8_block(a8, a_scale_t, b8, b_scale, out=None, *, bias=None, out_dtype=torch.bfloat16, max_ctas=0, pairs=None):
+    """out[M, N] = block-scaled a8[M, K] @ b8[N, K]^T.  a_scale_t: [K/128, M] fp32; b_scale: [ceil(N/128), K/128] fp32.
+    pairs: None = CTA pairs (256 x 256 tiles on cta_group::2) when M > 128, True / False to force."""
     M, K = a8.shape
     N = b8.shape[0]
     assert a8.dtype == torch.float8_e4m3fn and b8.dtype == torch.float8_e4m3fn and b8.shape[1] == K
@@ -219,6 +221,14 @@ def gemm_fp8_block(a8, a_scale_t, b8, b_scale, out=None, *, bias=None, out_dtype
     assert b_scale.shape == ((N + 127) // 128, K // 128) and b_scale.is_contiguous() and b_scale.dtype == torch.float32
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    if pairs is None:
+        pairs = M > 128 and max_ctas == 0
+    if pairs:
+        rc = _fn("lt_gemm_fp8_block_pair")(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), M, N, K, a8.stride(0), b8.stride(0),
+                                           out.stride(0), a_scale_t.data_ptr(), b_scale.data_ptr(),
+                                           1 if out.dtype == torch.float32 else 0, _p(bias), _stream())
+        _check(rc, "lt_gemm_fp8_block_pair")
+        return out
     rc = _fn("lt_gemm_fp8_block")(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), M, N, K, a8.stride(0), b8.stride(0),
                                   out.stride(0), a_scale_t.data_ptr(), b_scale.data_ptr(),
                                   1 if out.dtype == torch.float32 else 0, _p(bias), max_ctas, _stream())

@@ -132,13 +132,14 @@ def bench_fp8(out=None):
         ws = torch.ones((N + 127) // 128, Kd // 128, device="cuda")
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         fl = 2.0 * M * N * Kd
-        ms = time_ms(lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c))
+        ms = time_ms(lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c, pairs=True))
+        ms_one = time_ms(lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c, pairs=False))
         ms_q = time_ms(lambda: K.quant_fp8_1x128(x))
         ms_bf = time_ms(lambda: K.gemm(x, w, out=c))
         K.check_status()
         row = {"kernel": "gemm_fp8_block", "tag": tag, "M": M, "N": N, "K": Kd, "ms": round(ms, 4),
                "tflops": round(fl / ms / 1e9, 1), "x_bf16_%s_peak" % pk["src"]: round(fl / ms / 1e9 / pk["tflops"], 3),
-               "quant_ms": round(ms_q, 4), "quant_gbs": round(M * Kd * 3 / ms_q / 1e6, 1),
+               "one_cta_ms": round(ms_one, 4), "quant_ms": round(ms_q, 4), "quant_gbs": round(M * Kd * 3 / ms_q / 1e6, 1),
                "bf16_kernel_ms": round(ms_bf, 4)}
         rows.append(row)
         print(json.dumps(row), flush=True)

@@ -22,7 +22,8 @@ def _dequant_b(q, s):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (1000, 520, 1024), (4096, 2048, 2048)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_fp8_block_gemm_matches_fp32_reference(M, N, K, out_dtype):
+@pytest.mark.parametrize("pairs", [False, True])
+def test_fp8_block_gemm_matches_fp32_reference(M, N, K, out_dtype, pairs):
     from litetorch_b200.ops import kernels as Kn
     torch.manual_seed(0)
     dev = "cuda"
@@ -35,7 +36,7 @@ def test_fp8_block_gemm_matches_fp32_reference(M, N, K, out_dtype):
     ws = (wb.abs().amax((1, 3)).clamp_min(1e-12) / 448.0).contiguous()
     wq = (wb / ws[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(nb * 128, K)[:N].contiguous()
     bias = torch.randn(N, device=dev).bfloat16()
-    out = Kn.gemm_fp8_block(xq, xst, wq, ws, bias=bias, out_dtype=out_dtype)
+    out = Kn.gemm_fp8_block(xq, xst, wq, ws, bias=bias, out_dtype=out_dtype, pairs=pairs)
     ref = _dequant_a(xq, xst) @ _dequant_b(wq, ws).t() + bias.float()
     tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-4
     err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
@@ -66,3 +67,20 @@ def test_fp8_block_linear_close_to_bf16():
     ref = x.float() @ w.float().t()
     rel = (y.float() - ref).norm() / ref.norm()
     assert rel < 0.05, rel
+
+
+def test_linear_fp8_autograd_close_to_bf16():
+    from litetorch_b200.ops import functional as Fn
+    torch.manual_seed(3)
+    x = torch.randn(512, 1024, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 1024, device="cuda") * 0.03).bfloat16().requires_grad_(True)
+    y = Fn.linear_fp8(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()   # noqa: E731
+    assert rel(y, yr) < 0.05
+    assert rel(x.grad, xr.grad) < 0.06
+    assert rel(w.grad, wr.grad) < 0.02
