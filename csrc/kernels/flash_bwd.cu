@@ -69,10 +69,16 @@ struct FaBwdCfg {
   // is full and the rows go out as red.global.add).  One 32-row x 32-column fp32 tile (4 KB, 128-byte swizzle) per
   // compute warp, reduced into global memory by ONE cp.reduce.async.bulk.tensor per warp and iteration: the copy
   // engine does the atomics, not the LSU, and it is given few, large operations.
-  static constexpr bool kBulkDq = (D == 64);
-  static constexpr int kDqTile = 32 * 128;
-  static constexpr int kOffDqStage = ((kOffSeg + kFbMaxSegs * 16 + 16 + 1023) / 1024) * 1024;
-  static constexpr int kSmemBytes = kOffDqStage + (kBulkDq ? (kFbComputeThreads / 32) * kDqTile : 0) + 1024;
+  static constexpr bool kBulkDq = true;
+  static constexpr int kDqTile = 32 * 128;                 // one 32-row x 32-column fp32 box
+  static constexpr int kDqBoxes = D / 64;                  // boxes per warp: its 32 rows x D / 2 columns
+  // head_dim 64: a staging area of its own.  head_dim 128: shared memory is full, so the staging area IS the P and dS
+  // tiles (64 KB, free between the MMAs of one iteration and the exp phase of the next); a barrier among the compute
+  // warps keeps the next exp phase from overwriting tiles a reduction is still reading.
+  static constexpr bool kStageAliasesP = (D != 64);
+  static constexpr int kOffDqStage = kStageAliasesP ? kOffP : ((kOffSeg + kFbMaxSegs * 16 + 16 + 1023) / 1024) * 1024;
+  static constexpr int kSmemBytes = (kStageAliasesP ? kOffSeg + kFbMaxSegs * 16 + 16
+                                                    : kOffDqStage + (kFbComputeThreads / 32) * kDqTile) + 1024;
   static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
   static constexpr int kColDQ = (D == 64) ? 384 : 0;  // D == 64: two buffers (384, 448); D == 128: aliases S
   // D == 64: dQ of iteration i is read one iteration later, right after S / dP of iteration i+1 arrive, when the
@@ -172,7 +178,8 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
   const uint32_t dq_free = bb + 8u * 10;   // compute warps have read dQ_i (one arrival per warp)
   const uint32_t dkv_full = bb + 8u * 11;  // all MMAs done
   const uint32_t dq_free1 = bb + 8u * 12;  // second dQ buffer (deferred-dQ flow)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  const uint32_t stg_free = bb + 8u * 13;  // every compute warp's dQ reduction has finished reading shared memory
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -242,6 +249,7 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads / 32);
     mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 1);
     mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32); mbar_init(dq_free1, kFbComputeThreads / 32);
+    mbar_init(stg_free, kFbComputeThreads / 32);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -393,28 +401,37 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     // released as soon as the values are in registers.
     auto emit_dq = [&](int buf, float* dq_row, bool valid, bool local, int h_, int q0_) {
       if (Cfg::kBulkDq && local) {
-        uint32_t dq[32];
-        tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + buf * D + half * 32, dq);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(buf ? dq_free1 : dq_free);
-        if (p.dbg >= 2) return;
-        uint8_t* tile = smem + Cfg::kOffDqStage + (warp - 2) * Cfg::kDqTile;
-        if (dq_pending) {   // the previous reduction has finished reading the tile
+        uint8_t* tile = smem + Cfg::kOffDqStage + (warp - 2) * (Cfg::kDqBoxes * Cfg::kDqTile);
+        if (!Cfg::kStageAliasesP && dq_pending) {   // the previous reduction has finished reading the tile
           if (lane == 0) bulk_wait_read0();
           __syncwarp();
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u)   // row `lane` of the tile, 16-byte units swizzled like the tensor map expects
-          *reinterpret_cast<uint4*>(tile + lane * 128 + ((u ^ (lane & 7)) * 16)) =
-              make_uint4(dq[u * 4], dq[u * 4 + 1], dq[u * 4 + 2], dq[u * 4 + 3]);
+        for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
+          uint32_t dq[32];
+          tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDQ + buf * D + (half * Cfg::kDqBoxes + bx) * 32, dq);
+          tmem_ld_wait();
+          if (bx == Cfg::kDqBoxes - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(buf ? dq_free1 : dq_free);
+          }
+          if (p.dbg >= 2) continue;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)   // row `lane` of the box, 16-byte units swizzled like the tensor map expects
+            *reinterpret_cast<uint4*>(tile + bx * Cfg::kDqTile + lane * 128 + ((u ^ (lane & 7)) * 16)) =
+                make_uint4(dq[u * 4], dq[u * 4 + 1], dq[u * 4 + 2], dq[u * 4 + 3]);
+        }
+        if (p.dbg >= 2) return;
         fence_proxy_async();
         __syncwarp();
         dq_pending = false;
         if (p.dbg == 0) {
           if (lane == 0) {
-            tma_reduce_add_4d(&tmDQ, smem_u32(tile), half * 32, h_, q0_ + quarter * 32, b);   // rows past Tq are clipped
+#pragma unroll
+            for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)   // rows past Tq are clipped by the copy engine
+              tma_reduce_add_4d(&tmDQ, smem_u32(tile + bx * Cfg::kDqTile), (half * Cfg::kDqBoxes + bx) * 32, h_,
+                                q0_ + quarter * 32, b);
             bulk_commit();
           }
           dq_pending = true;
@@ -460,6 +477,15 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       // P / dS tiles are free once the MMAs of the previous iteration have executed.
       ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, ipar ^ 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty));
       if (!ok) break;
+      if (Cfg::kStageAliasesP && it > 0) {
+        // ... and once every warp's dQ reduction of the previous iteration has finished reading them
+        if (lane == 0) {
+          if (dq_pending) bulk_wait_read0();
+          mbar_arrive(stg_free);
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(stg_free, uint32_t(it - 1) & 1u, abort_flag, p.status, kStatusTimeoutLocalFlag));
+        if (!ok) break;
+      }
       if (tr) { const long long c1 = clock64(); tc[2] += c1 - c0; c0 = c1; }   // waiting for the P / dS tiles
       tc_fence_after();
       uint8_t* prow = smem + Cfg::kOffP + (row >> 3) * 1024 + (row & 7) * 128;

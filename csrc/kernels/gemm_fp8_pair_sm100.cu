@@ -46,7 +46,8 @@ __device__ __forceinline__ void umma_f8_ss_pair(uint32_t tmem_d, uint64_t adesc,
       : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(112)
+// 18 warps: five on two of the four SM sub-partitions, whose 16 K registers each cap a thread at 96 registers.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kP8Threads, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Fp8PairParams p) {
   constexpr int S = kP8Stages;
   extern __shared__ uint8_t smem_raw[];
@@ -156,18 +157,20 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kP8BlockN + part * 64;
-        uint32_t r[32];
-        tmem_ld_32x32(taddr, r);
-        tmem_ld_wait();
+        // 16 columns at a time: 64 accumulators + 16 loaded values stay inside the 96-register budget
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(s, __uint_as_float(r[j]), acc[j]);
-        tmem_ld_32x32(taddr + 32, r);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty_bar(buf), 0);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c * 16, r);
+          tmem_ld_wait();
+          if (c == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_bar(buf), 0);
+          }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(s, __uint_as_float(r[j]), acc[32 + j]);
+          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(s, __uint_as_float(r[j]), acc[c * 16 + j]);
+        }
       }
       if (!alive || row >= p.M) continue;
       const int col0 = n_blk * kP8BlockN + part * 64;

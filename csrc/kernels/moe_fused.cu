@@ -27,7 +27,12 @@ struct RowGatherArgs {
   uint32_t* flags;                         // one per 128-slot block
   uint32_t epoch;
   int slots, cols, n_blocks, n_comm;
+  const __nv_bfloat16* zero_row;           // kGatherStageBytes of zeros: the source of padding slots
 };
+
+// Zeros that padding slots are "fetched" from, so that the rows of the slot buffer nobody owns are 0 and not stale
+// shared memory (0 * NaN would poison the weight-gradient GEMMs that sum over whole 128-row blocks).
+static __device__ __align__(128) uint8_t g_moe_zero_row[kGatherStageBytes];
 
 // One thread per gather CTA: rows of a 128-slot block are fetched in batches that fill one 32 KB stage.
 __device__ void gather_rows_cta(const RowGatherArgs& g, int* status) {
@@ -63,15 +68,12 @@ __device__ void gather_rows_cta(const RowGatherArgs& g, int* status) {
         const int s = issued % kGatherStages;
         const int n = min(per_stage, r1 - next_row);
         tma_store_wait_read<0>();  // the stage's previous store has finished reading shared memory
-        uint32_t live = 0;
-        for (int i = 0; i < n; ++i) live += (g.slot_src[next_row + i].x >= 0) ? 1u : 0u;
-        if (live) {
-          mbar_expect_tx(bb + 8u * s, live * row_bytes);
-          for (int i = 0; i < n; ++i) {
-            const int2 sr = g.slot_src[next_row + i];
-            if (sr.x >= 0)
-              bulk_g2s(sbase + s * kGatherStageBytes + i * row_bytes, g.src[sr.x] + (long long)sr.y * g.cols, row_bytes, bb + 8u * s);
-          }
+        const uint32_t live = uint32_t(n);
+        mbar_expect_tx(bb + 8u * s, live * row_bytes);
+        for (int i = 0; i < n; ++i) {
+          const int2 sr = g.slot_src[next_row + i];
+          const __nv_bfloat16* from = sr.x >= 0 ? g.src[sr.x] + (long long)sr.y * g.cols : g.zero_row;
+          bulk_g2s(sbase + s * kGatherStageBytes + i * row_bytes, from, row_bytes, bb + 8u * s);
         }
         seg_row[s] = next_row; seg_rows[s] = n; seg_live[s] = int(live);
         next_row += n;
@@ -82,7 +84,6 @@ __device__ void gather_rows_cta(const RowGatherArgs& g, int* status) {
         if (seg_live[s]) {
           if (!mbar_wait(bb + 8u * s, use[s] & 1u, abort_flag, status, kStatusTimeoutFull)) { ok = false; break; }
           use[s]++;
-          // padding rows inside the batch carry stale shared-memory contents; nothing reads their results
           bulk_s2g(g.dst + (long long)seg_row[s] * g.cols, sbase + s * kGatherStageBytes, uint32_t(seg_rows[s]) * row_bytes);
           tma_store_commit();
         }
@@ -157,6 +158,11 @@ int lt_moe_gather_gemm(const void* const* src_ptrs, int world, const void* slot_
   g.flags = static_cast<uint32_t*>(flags);
   g.epoch = epoch;
   g.slots = slots; g.cols = K; g.n_blocks = slots / kBlockM; g.n_comm = n_comm;
+  {
+    void* z = nullptr;
+    LT_RETURN_IF_CUDA(cudaGetSymbolAddress(&z, g_moe_zero_row));
+    g.zero_row = static_cast<const __nv_bfloat16*>(z);
+  }
   CUtensorMap tmA, tmB;
   int r = encode_tmap_2d(&tmA, slot_buf, 2, (uint64_t)K, (uint64_t)slots, (uint64_t)K * 2, kBlockK, kBlockM, 1);
   if (r) return 1000 + r;

@@ -4,6 +4,7 @@ Spawns one child process per GPU (torchrun, 127.0.0.1 rendezvous) so that each r
 import json
 import os
 import subprocess
+import tempfile
 import sys
 
 import pytest
@@ -56,8 +57,7 @@ dist.destroy_process_group()
 
 
 def _run(nproc):
-    script = os.path.join(ROOT, "gpurun_out", "_fsdp_worker.py")
-    os.makedirs(os.path.dirname(script), exist_ok=True)
+    script = os.path.join(tempfile.mkdtemp(prefix="lt_worker_"), "_fsdp_worker.py")
     with open(script, "w") as f:
         f.write(WORKER % {"root": ROOT})
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")

@@ -2,6 +2,7 @@
 import json
 import os
 import subprocess
+import tempfile
 import sys
 
 import pytest
@@ -63,8 +64,7 @@ dist.barrier(); dist.destroy_process_group()
 def test_fused_tp_matches_nccl_path(nproc):
     if torch.cuda.device_count() < nproc:
         pytest.skip("needs %d GPUs" % nproc)
-    script = os.path.join(ROOT, "gpurun_out", "_tp_worker.py")
-    os.makedirs(os.path.dirname(script), exist_ok=True)
+    script = os.path.join(tempfile.mkdtemp(prefix="lt_worker_"), "_tp_worker.py")
     with open(script, "w") as f:
         f.write(WORKER % {"root": ROOT})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
