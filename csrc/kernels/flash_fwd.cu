@@ -271,17 +271,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           issue_s(j0);
         }
       }
+      const bool trm = p.trace != nullptr && blockIdx.z == 0 && h == 0 && b == 0;
+      long long tm[3] = {0, 0, 0};
       for (int j = 0; ok && j < n_blocks; ++j) {
         const int s = j & 1;
         const uint32_t par = (j >> 1) & 1;
+        long long c0 = trm ? clock64() : 0;
         if (j + kLook < n_blocks) {
           const int jn = j + kLook;
           if (!mbar_wait(k_full(jn & 1), (jn >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
           tc_fence_after();
           issue_s(jn);
         }
+        if (trm) { const long long c1 = clock64(); tm[0] += c1 - c0; c0 = c1; }   // K wait + score MMA issue
         if (!mbar_wait(p_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+        if (trm) { const long long c1 = clock64(); tm[1] += c1 - c0; c0 = c1; }   // waiting for P
         if (!mbar_wait(v_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (trm) { const long long c1 = clock64(); tm[2] += c1 - c0; c0 = c1; }   // waiting for V
         tc_fence_after();
         const uint64_t pd = s ? p_desc[1] : p_desc[0];
         const uint64_t vd = s ? v_desc[1] : v_desc[0];
@@ -296,6 +302,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(p_empty(s));
         if (j == n_blocks - 1) umma_commit(o_full);
       }
+      if (trm) { p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2]; p.trace[11] = n_blocks; }
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue

@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-fused", action="store_true", help="plain NCCL collectives instead of the fused kernels")
     ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--n-seq", type=int, default=0, help="sequences per micro-batch (default: the layout's)")
     ap.add_argument("--fp8", action="store_true", help="e4m3 GEMMs with 1x128 / 128x128 block scales (NCCL collectives)")
     args = ap.parse_args()
 
@@ -109,6 +110,8 @@ def main():
         tp, cp, pp = (2, 2, 2) if world >= 8 else ((2, 2, 1) if world == 4 else ((2, 1, 1) if world == 2 else (1, 1, 1)))
         groups, _ = _make_groups(world, rank, tp, cp, pp, world // (tp * cp * pp))
         layout = "tp%d x cp%d x pp%d" % (tp, cp, pp)
+    if args.n_seq:
+        n_seq = args.n_seq
     ep_group = dist.group.WORLD if (args.config == "ep8" and world > 1) else None
 
     dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True,
