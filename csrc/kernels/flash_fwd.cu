@@ -19,7 +19,7 @@ namespace lt {
 
 constexpr int kFaBlockQ = 128;
 constexpr int kFaBlockKV = 128;
-constexpr int kFaThreads = 320;          // warp 0 producer, warp 1 MMA issuer, warps 2-9 softmax
+constexpr int kFaThreads = 352;          // warp 0 producer, warp 1 PV MMA issuer, warps 2-9 softmax, warp 10 score MMA issuer
 constexpr int kFaSoftmaxThreads = 256;   // two warps per TMEM lane quarter, 64 score columns each
 
 struct FlashFwdParams {
@@ -65,7 +65,7 @@ struct FaFwdCfg {
   static constexpr int kOffV = kOffK + 2 * kKVBytes;
   static constexpr int kOffP = kOffV + 2 * kKVBytes;
   static constexpr int kOffBar = kOffP + 2 * kPBytes;
-  static constexpr int kOffSeg = kOffBar + 192;               // KvSeg table (16 entries) + block count
+  static constexpr int kOffSeg = kOffBar + 224;               // KvSeg table (16 entries) + block count
   static constexpr int kOffX = kOffSeg + kFaMaxSegs * 16 + 16;                 // row statistics exchanged between the two column halves
   static constexpr int kNeeded = kOffX + 2 * 2 * 128 * 4;     // [parity][half][128] floats
   // 1 KB of slack for the 1024-byte alignment where it fits under the 227 KB limit; the kernel checks at run time
@@ -104,7 +104,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t o_full = bb + 8u * 16;
   // x_bar(quarter): both warps of a TMEM lane quarter have published their partial row statistics
   auto x_bar = [&](int qtr) { return bb + 8u * (17 + qtr); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 21);
+  auto s_free = [&](int sb) { return bb + 8u * (21 + sb); };   // the group's four warps have read score buffer sb
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 24);
   float* xmax = reinterpret_cast<float*>(smem + Cfg::kOffX);  // [2 (rendezvous parity)][2 (half)][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -179,7 +180,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
       mbar_init(p_full(s), kFaSoftmaxThreads / 64); mbar_init(p_empty(s), 1);
     }
-    for (int s = 0; s < Cfg::kSBufs; ++s) mbar_init(s_full(s), 1);
+    for (int s = 0; s < Cfg::kSBufs; ++s) { mbar_init(s_full(s), 1); mbar_init(s_free(s), kFaSoftmaxThreads / 64); }
     mbar_init(o_full, 1);
     for (int qtr = 0; qtr < 4; ++qtr) mbar_init(x_bar(qtr), 2);
     *abort_flag = 0;
@@ -231,59 +232,52 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       kv0, b);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- score MMA issuer (S = Q K^T)
+    // Issuing a tcgen05.mma costs its thread on the order of a hundred cycles whatever the tile width, so the twelve
+    // MMAs of a KV block are split over two issuing threads: this one runs the score products as far ahead as the
+    // score buffers allow, warp 1 runs the PV products.
     if (lane == 0 && n_blocks > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kFaBlockQ, kFaBlockKV, 1, 0, 0);
-      constexpr uint32_t idesc_o = make_idesc_f16(kFaBlockQ, D, 1, 0, 1);
-      // The issuing thread is a single scalar instruction stream on the critical path of every block: the operand
-      // descriptors are built once per buffer and advanced by adding the 16-byte-unit offset of each K step.
       const uint64_t q_desc = make_smem_desc_sw128(sbase + Cfg::kOffQ, 16, 1024);
-      uint64_t k_desc[2], v_desc[2], p_desc[2];
-#pragma unroll
-      for (int st = 0; st < 2; ++st) {
-        k_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffK + st * Cfg::kKVBytes, 16, 1024);
-        v_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffV + st * Cfg::kKVBytes, kFaBlockKV * 128, 1024);
-        p_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffP + st * Cfg::kPBytes, 16, 1024);
-      }
-      auto issue_s = [&](int j) {
+      const uint64_t k_desc0 = make_smem_desc_sw128(sbase + Cfg::kOffK, 16, 1024);
+      const uint64_t k_desc1 = make_smem_desc_sw128(sbase + Cfg::kOffK + Cfg::kKVBytes, 16, 1024);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      for (int j = 0; ok && j < n_blocks; ++j) {
         const int s = j & 1;                 // K stage
-        const int sb = j % Cfg::kSBufs;      // score buffer
-        const uint64_t kd = s ? k_desc[1] : k_desc[0];
+        const int sb = j % Cfg::kSBufs;      // score buffer, last read by the softmax of block j - kSBufs
+        if (!mbar_wait(k_full(s), (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) break;
+        if (j >= Cfg::kSBufs &&
+            !mbar_wait(s_free(sb), uint32_t(j / Cfg::kSBufs - 1) & 1u, abort_flag, p.status, kStatusTimeoutTmemEmpty)) break;
+        tc_fence_after();
+        const uint64_t kd = s ? k_desc1 : k_desc0;
         const uint32_t d_s = tmem_base + Cfg::kColS + sb * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          constexpr int kUnit = 1;  // descriptor addresses count 16-byte units
-          const uint64_t off = uint64_t(((k / 4) * (128 * 128) + (k % 4) * 32) >> 4) * kUnit;
+          const uint64_t off = uint64_t(((k / 4) * (128 * 128) + (k % 4) * 32) >> 4);   // 16-byte units
           umma_f16_ss(d_s, q_desc + off, kd + off, idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(k_empty(s));
         umma_commit(s_full(sb));
-      };
-      // Score products run kLook blocks ahead of the PV products: buffer (j + kLook) % kSBufs was last read by the
-      // softmax of block j - 1, whose P this thread has already waited for.
-      constexpr int kLook = Cfg::kSBufs - 1;
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
-      for (int j0 = 0; ok && j0 < kLook && j0 < n_blocks; ++j0) {
-        ok = mbar_wait(k_full(j0 & 1), (j0 >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull);
-        if (ok) {
-          tc_fence_after();
-          issue_s(j0);
-        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- PV MMA issuer (O_g += P V)
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_o = make_idesc_f16(kFaBlockQ, D, 1, 0, 1);
+      uint64_t v_desc[2], p_desc[2];
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        v_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffV + st * Cfg::kKVBytes, kFaBlockKV * 128, 1024);
+        p_desc[st] = make_smem_desc_sw128(sbase + Cfg::kOffP + st * Cfg::kPBytes, 16, 1024);
       }
       const bool trm = p.trace != nullptr && blockIdx.z == 0 && h == 0 && b == 0;
       long long tm[3] = {0, 0, 0};
+      bool ok = true;
       for (int j = 0; ok && j < n_blocks; ++j) {
         const int s = j & 1;
         const uint32_t par = (j >> 1) & 1;
         long long c0 = trm ? clock64() : 0;
-        if (j + kLook < n_blocks) {
-          const int jn = j + kLook;
-          if (!mbar_wait(k_full(jn & 1), (jn >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(jn);
-        }
-        if (trm) { const long long c1 = clock64(); tm[0] += c1 - c0; c0 = c1; }   // K wait + score MMA issue
         if (!mbar_wait(p_full(s), par, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
         if (trm) { const long long c1 = clock64(); tm[1] += c1 - c0; c0 = c1; }   // waiting for P
         if (!mbar_wait(v_full(s), par, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
@@ -301,10 +295,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(v_empty(s));
         umma_commit(p_empty(s));
         if (j == n_blocks - 1) umma_commit(o_full);
+        if (trm) { const long long c1 = clock64(); tm[0] += c1 - c0; c0 = c1; }   // issuing the PV MMAs
       }
       if (trm) { p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2]; p.trace[11] = n_blocks; }
     }
-  } else {
+  } else if (warp < 10) {
     // ---------------------------------------------------------------- softmax + epilogue
     // Two independent groups of four warps: group g takes the KV blocks of parity g (score buffer g, P buffer g) and
     // keeps its own running maximum, row sum and output accumulator O_g, so a thread owns a whole score row of its
@@ -428,7 +423,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(grp));   // one arrival per warp of the group
+      if (lane == 0) {   // one arrival per warp of the group
+        mbar_arrive(s_free(sb));
+        mbar_arrive(p_full(grp));
+      }
       if (tr) { const long long c1 = clock64(); tc[4] += c1 - c0; c0 = c1; }   // pass 2 (exp, P stores, fence, arrive)
     }
     if (tr) {
