@@ -19,7 +19,7 @@
 namespace lt {
 
 constexpr int kFbBlock = 128;
-constexpr int kFbThreads = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2-9 compute (two per TMEM lane quarter)
+constexpr int kFbThreads = 352;   // warp 0 producer, warp 1 S/dP/dQ MMA issuer, warps 2-9 compute, warp 10 dV/dK MMA issuer
 constexpr int kFbComputeThreads = 256;
 
 constexpr int kFbMaxRanks = 8;
@@ -247,10 +247,10 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads / 32);
-    mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 1);
+    mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 2);   // both MMA issuers release P / dS
     mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32); mbar_init(dq_free1, kFbComputeThreads / 32);
     mbar_init(stg_free, kFbComputeThreads / 32);
-    mbar_init(dkv_full, 1);
+    mbar_init(dkv_full, 2);   // both MMA issuers have drained
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -338,9 +338,40 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
                          kStatusTimeoutTmemEmpty)) { ok = false; break; }
         }
         tc_fence_after();
-        // dV += P^T dO ; dK += dS^T Q      (K dimension = the 128 query rows, 16 rows per instruction)
+        // dQ_i = dS K                      (K dimension = the 128 keys)
 #pragma unroll
         for (int k = 0; k < kFbBlock / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(dsa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(ka + k * (16 * 128), 128 * 128, 1024);
+          umma_f16_ss(tmem_base + Cfg::kColDQ + (Cfg::kDeferDq ? (it & 1) * D : 0), adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(pds_empty);
+        umma_commit(dq_full);
+        if (it == n_iter - 1) umma_commit(dkv_full);
+      }
+      if (tr) {
+        // MMA thread: wait for Q/dO, for S/dP to be read, for P/dS
+        p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2];
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- second MMA issuer: dV += P^T dO, dK += dS^T Q
+    // Issuing a tcgen05.mma costs its thread on the order of a hundred cycles whatever the tile width, and in this
+    // kernel the issue time sits on the critical chain (the exp phase of the next iteration waits for all of them):
+    // the 16 dV / dK MMAs of an iteration go out from this thread while warp 1 issues dQ and the next S / dP.
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_kv = make_idesc_f16(128, D, 1, 1, 1);    // A M-major, B N-major
+      const uint32_t pa = sbase + Cfg::kOffP, dsa = sbase + Cfg::kOffDS;
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % ST;
+        const uint32_t ipar = it & 1;
+        const uint32_t qa = sbase + Cfg::kOffQ + s * Cfg::kTile;
+        const uint32_t doa = sbase + Cfg::kOffDO + s * Cfg::kTile;
+        // P / dS ready implies Q / dO of this stage are in shared memory (S and dP were computed from them)
+        if (!mbar_wait(pds_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kFbBlock / 16; ++k) {   // K dimension = the 128 query rows, 16 rows per instruction
           const uint32_t koff = k * (16 * 128);
           umma_f16_ss(tmem_base + Cfg::kColDV, make_smem_desc_sw128(pa + koff, 128 * 128, 1024),
                       make_smem_desc_sw128(doa + koff, 128 * 128, 1024), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
@@ -351,21 +382,9 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
           umma_f16_ss(tmem_base + Cfg::kColDK, make_smem_desc_sw128(dsa + koff, 128 * 128, 1024),
                       make_smem_desc_sw128(qa + koff, 128 * 128, 1024), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
         }
-        // dQ_i = dS K                      (K dimension = the 128 keys)
-#pragma unroll
-        for (int k = 0; k < kFbBlock / 16; ++k) {
-          const uint64_t adesc = make_smem_desc_sw128(dsa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(ka + k * (16 * 128), 128 * 128, 1024);
-          umma_f16_ss(tmem_base + Cfg::kColDQ + (Cfg::kDeferDq ? (it & 1) * D : 0), adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
-        }
         umma_commit(qdo_empty(s));
         umma_commit(pds_empty);
-        umma_commit(dq_full);
         if (it == n_iter - 1) umma_commit(dkv_full);
-      }
-      if (tr) {
-        // MMA thread: wait for Q/dO, for S/dP to be read, for P/dS
-        p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2];
       }
     }
   } else {
@@ -562,6 +581,11 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       ok = __all_sync(0xffffffffu, mbar_wait(dq_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull));
       if (!ok) break;
       if (tr) { const long long c1 = clock64(); tc[4] += c1 - c0; c0 = c1; }   // waiting for dQ
+      if (Cfg::kStageAliasesP) {
+        // the staging area is the P / dS tiles: the dV / dK MMAs of the other issuer must be done with them too
+        ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, ipar, abort_flag, p.status, kStatusTimeoutTmemEmpty));
+        if (!ok) break;
+      }
       tc_fence_after();
       emit_dq(0, p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D, q_valid, owner == p.cp_rank, h, q0);
       if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }   // dQ read + reduction
