@@ -19,7 +19,7 @@
 namespace lt {
 
 constexpr int kFbBlock = 128;
-constexpr int kFbThreads = 352;   // warp 0 producer, warp 1 S/dP/dQ MMA issuer, warps 2-9 compute, warp 10 dV/dK MMA issuer
+constexpr int kFbThreads = 384;   // warp 0 producer, warps 1 / 10 / 11 MMA issuers (S,dP / dV,dK / dQ), warps 2-9 compute
 constexpr int kFbComputeThreads = 256;
 
 constexpr int kFbMaxRanks = 8;
@@ -179,7 +179,9 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
   const uint32_t dkv_full = bb + 8u * 11;  // all MMAs done
   const uint32_t dq_free1 = bb + 8u * 12;  // second dQ buffer (deferred-dQ flow)
   const uint32_t stg_free = bb + 8u * 13;  // every compute warp's dQ reduction has finished reading shared memory
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
+  const uint32_t dq_full1 = bb + 8u * 14;  // dQ of odd iterations (deferred-dQ flow: one barrier per dQ buffer, so a
+                                           // waiter can never be overtaken by two completions)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -247,10 +249,10 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     mbar_init(sdp_full, 1); mbar_init(sdp_free, kFbComputeThreads / 32);
-    mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 2);   // both MMA issuers release P / dS
-    mbar_init(dq_full, 1); mbar_init(dq_free, kFbComputeThreads / 32); mbar_init(dq_free1, kFbComputeThreads / 32);
+    mbar_init(pds_full, kFbComputeThreads / 32); mbar_init(pds_empty, 2);   // the dV/dK and the dQ issuer release P / dS
+    mbar_init(dq_full, 1); mbar_init(dq_full1, 1); mbar_init(dq_free, kFbComputeThreads / 32); mbar_init(dq_free1, kFbComputeThreads / 32);
     mbar_init(stg_free, kFbComputeThreads / 32);
-    mbar_init(dkv_full, 2);   // both MMA issuers have drained
+    mbar_init(dkv_full, 2);   // the dV/dK and the dQ issuer have drained
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -291,14 +293,12 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ---------------------------------------------------------------- first MMA issuer: S = Q K^T, dP = dO V^T
+    // (as far ahead as the S / dP columns of tensor memory allow: they are free once the compute warps have loaded them)
     if (lane == 0 && n_iter > 0) {
       constexpr uint32_t idesc_sd = make_idesc_f16(128, 128, 1, 0, 0);  // S, dP: A K-major, B K-major
-      constexpr uint32_t idesc_kv = make_idesc_f16(128, D, 1, 1, 1);    // dV, dK: A M-major, B N-major
-      constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 1, 0, 1);    // dQ: A K-major, B N-major
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
       const uint32_t ka = sbase + Cfg::kOffK, va = sbase + Cfg::kOffV;
-      const uint32_t pa = sbase + Cfg::kOffP, dsa = sbase + Cfg::kOffDS;
       const bool tr = p.trace != nullptr && kv_blk == 0 && hkv == 0 && b == 0;
       long long tm[4] = {0, 0, 0, 0};
       for (int it = 0; ok && it < n_iter; ++it) {
@@ -329,29 +329,36 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
                       make_smem_desc_sw128(va + off, 16, 1024), idesc_sd, k > 0 ? 1u : 0u);
         }
         umma_commit(sdp_full);
-        if (tr) c0 = clock64();
-        if (!mbar_wait(pds_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-        if (tr) { const long long c1 = clock64(); tm[2] += c1 - c0; c0 = c1; }
+      }
+      if (tr) {
+        // MMA thread: wait for Q/dO, for S/dP to be read, for P/dS
+        p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2];
+      }
+    }
+  } else if (warp == 11) {
+    // ---------------------------------------------------------------- third MMA issuer: dQ_i = dS K
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 1, 0, 1);    // A K-major, B N-major
+      const uint32_t ka = sbase + Cfg::kOffK, dsa = sbase + Cfg::kOffDS;
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const uint32_t ipar = it & 1;
+        if (!mbar_wait(pds_full, ipar, abort_flag, p.status, kStatusTimeoutTmemFull)) break;
         if (!Cfg::kDqAliasesS) {
           // dQ buffer it & 1 was last used by iteration it - 2
           if (!mbar_wait((it & 1) ? dq_free1 : dq_free, ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_flag, p.status,
-                         kStatusTimeoutTmemEmpty)) { ok = false; break; }
+                         kStatusTimeoutTmemEmpty)) break;
         }
         tc_fence_after();
-        // dQ_i = dS K                      (K dimension = the 128 keys)
 #pragma unroll
-        for (int k = 0; k < kFbBlock / 16; ++k) {
+        for (int k = 0; k < kFbBlock / 16; ++k) {   // K dimension = the 128 keys
           const uint64_t adesc = make_smem_desc_sw128(dsa + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(ka + k * (16 * 128), 128 * 128, 1024);
           umma_f16_ss(tmem_base + Cfg::kColDQ + (Cfg::kDeferDq ? (it & 1) * D : 0), adesc, bdesc, idesc_dq, k > 0 ? 1u : 0u);
         }
         umma_commit(pds_empty);
-        umma_commit(dq_full);
+        umma_commit((Cfg::kDeferDq && (it & 1)) ? dq_full1 : dq_full);
         if (it == n_iter - 1) umma_commit(dkv_full);
-      }
-      if (tr) {
-        // MMA thread: wait for Q/dO, for S/dP to be read, for P/dS
-        p.trace[8] = tm[0]; p.trace[9] = tm[1]; p.trace[10] = tm[2];
       }
     }
   } else if (warp == 10) {
@@ -515,6 +522,11 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColS + c * 32, sv);
         tmem_ld_32x32(tmem_base + lane_base + Cfg::kColDP + c * 32, dp);
         tmem_ld_wait();
+        if (c == 2 * half + 1) {   // S / dP are in registers: the next iteration's score products may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sdp_free);
+        }
         const bool live = q_valid && lse2 != -INFINITY;
         const float dlt_s = dlt * p.scale;
         if (live && kv0 + c * 32 + 31 <= limit) {   // every column of the chunk is visible: no per-element test
@@ -558,16 +570,17 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(sdp_free);
-        mbar_arrive(pds_full);
-      }
+      if (lane == 0) mbar_arrive(pds_full);
       if (tr) { const long long c1 = clock64(); tc[3] += c1 - c0; c0 = c1; }   // exp / dS / stores to shared memory
       if (Cfg::kDeferDq) {
         // While the tensor core works on dV / dK / dQ of this iteration and S / dP of the next, write out dQ of the
         // PREVIOUS iteration: it is complete (S / dP of this iteration were committed after it), and its transfer
         // TMEM -> registers -> shared memory -> TMA reduction is off the critical chain here.
         if (it > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(((it - 1) & 1) ? dq_full1 : dq_full, (uint32_t(it - 1) >> 1) & 1u, abort_flag,
+                                                 p.status, kStatusTimeoutTmemFull));
+          if (!ok) break;
+          tc_fence_after();
           emit_dq((it - 1) & 1, prev_row, prev_valid, prev_local, prev_h, prev_q0);
           if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }
         }
