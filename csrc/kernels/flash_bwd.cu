@@ -406,6 +406,10 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
     long long tc[6] = {0, 0, 0, 0, 0, 0};
     // Row statistics are fetched one iteration ahead (the global-load latency is off the chain); the position of an
     // iteration (query head, block within the head) is advanced with counters, not divisions.
+    const bool single = (p.cp_world == 1);
+    const float* lse0 = p.lse[0];
+    const float* delta0 = p.delta[0];
+    float* dq0 = p.dq_acc[0];
     auto fetch_stats = [&](int hh, int jj, float& lse_raw, float& dl) {
       lse_raw = 0.f; dl = 0.f;
       if (hh >= G) return;
@@ -415,8 +419,10 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
       const int q_idx = q0 + row;
       if (q_idx < p.Tq) {
         const long long si = ((long long)b * p.Hq + h) * p.Tq + q_idx;
-        lse_raw = p.lse[owner][si];
-        dl = p.delta[owner][si];
+        // (indexing the pointer arrays of the kernel parameters with a run-time rank makes the compiler copy them to
+        // local memory: the single-rank case reads element 0 directly)
+        lse_raw = single ? lse0[si] : p.lse[owner][si];
+        dl = single ? delta0[si] : p.delta[owner][si];
       }
     };
     float lse_next, dlt_next;
@@ -584,7 +590,7 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
           emit_dq((it - 1) & 1, prev_row, prev_valid, prev_local, prev_h, prev_q0);
           if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }
         }
-        prev_row = p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
+        prev_row = (single ? dq0 : p.dq_acc[owner]) + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D;
         prev_valid = q_valid;
         prev_local = (owner == p.cp_rank);
         prev_h = h; prev_q0 = q0;
@@ -600,7 +606,8 @@ flash_bwd_kernel(const __grid_constant__ QMaps qm, const __grid_constant__ CUten
         if (!ok) break;
       }
       tc_fence_after();
-      emit_dq(0, p.dq_acc[owner] + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D, q_valid, owner == p.cp_rank, h, q0);
+      emit_dq(0, (single ? dq0 : p.dq_acc[owner]) + (((long long)b * p.Tq + q_idx) * p.Hq + h) * D, q_valid,
+              owner == p.cp_rank, h, q0);
       if (tr) { const long long c1 = clock64(); tc[5] += c1 - c0; c0 = c1; }   // dQ read + reduction
     }
     if (tr) {
