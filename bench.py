@@ -36,6 +36,8 @@ def _parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama-1.1b", choices=["llama-1.1b", "llama-tiny"])
+    ap.add_argument("--no-comm-breakdown", action="store_true",
+                    help="skip the extra unsharded steps that give exposed_comm_ms_per_step at N > 1")
     return ap.parse_args()
 
 
@@ -167,11 +169,30 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier_sync()
+    h2d_bytes, d2h_bytes = tr.h2d_bytes, tr.d2h_bytes
 
-    t = torch.tensor([ms_total, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    # ---------------- exposed communication (outside the timed regions): the same step on an unsharded copy of the
+    # model, one per GPU, costs the compute alone; what the sharded step takes on top of it is communication that
+    # the overlap did not hide (gather CTAs taken from the GEMMs included).
+    local_ms = 0.0
+    if world > 1 and not args.no_comm_breakdown:
+        del tr
+        torch.cuda.empty_cache()
+        tr_local = Trainer(cfg, seed=1234, parallel="none")
+        for i in range(3):
+            tr_local.step_device(*devb[i % n_batches])
+        torch.cuda.synchronize()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for i in range(4):
+            tr_local.step_device(*devb[i % n_batches])
+        l1.record()
+        torch.cuda.synchronize()
+        local_ms = l0.elapsed_time(l1) / 4
+    t = torch.tensor([ms_total, e2e_s * 1e3, local_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(t[0]), float(t[1])
+    ms_total, e2e_ms, local_ms = float(t[0]), float(t[1]), float(t[2])
     tokens = MICRO_BATCH * T * world * args.steps
     value = tokens / (ms_total / 1e3)
     e2e_value = tokens / (e2e_ms / 1e3)
@@ -189,8 +210,10 @@ def run_ours(args):
                        "l2": "no flush: the step's working set (2.2 GB bf16 weights + ~10 GB activations) is far larger than the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
-                    "h2d_bytes_per_step": tr.h2d_bytes, "d2h_bytes_per_step": tr.d2h_bytes},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches,
+            "exposed_comm_ms_per_step": (round(ms_total / args.steps - local_ms, 3) if local_ms > 0 else (0.0 if world == 1 else None)),
+            "unsharded_step_ms": round(local_ms, 3) if local_ms > 0 else None,
             "final_loss": round(loss_val, 4),
             "device_status": status,
             "model_tflops_per_gpu": round(cfg.flops_per_token(T) * value / world / 1e12, 1),

@@ -35,7 +35,7 @@ class Trainer:
             weights = ShardedWeights(cfg, self.device, seed=seed)
         self.engine = LlamaEngine(cfg, self.device, weights=weights, seed=seed, lr=lr, betas=betas, eps=eps,
                                   weight_decay=weight_decay, activation_checkpointing=activation_checkpointing,
-                                  world_size=self.world_size)
+                                  world_size=self.world_size if weights is not None else 1)
         self._tok = None
         self._tgt = None
         self.h2d_bytes = 0

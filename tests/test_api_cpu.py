@@ -346,3 +346,30 @@ def test_custom_op_registry():
     assert lt.custom_ops.Registry.has("cube")
     with pytest.raises(KeyError):
         lt.custom_ops.Registry.call("nope", [x])
+
+
+def test_functional_fallbacks_softmax_dropout_router_fp8_linear():
+    """CPU paths of the ops whose CUDA versions are hand-written kernels."""
+    import torch
+    from litetorch_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    x = torch.randn(4, 7, 33, requires_grad=True)
+    y = Fn.softmax(x, -1)
+    torch.testing.assert_close(y, torch.softmax(x, -1))
+    y.sum().backward()
+    assert x.grad.abs().max() < 1e-6          # d(sum softmax)/dx = 0
+    d = Fn.dropout(torch.ones(10000), 0.3, True)
+    assert abs(float((d != 0).float().mean()) - 0.7) < 0.03
+    assert Fn.dropout(x, 0.3, False) is x
+    logits = torch.randn(64, 8, requires_grad=True)
+    tw, ti, probs = Fn.moe_router(logits, 2, renorm=True)
+    assert ti.shape == (64, 2) and torch.allclose(tw.sum(-1), torch.ones(64), atol=1e-6)
+    torch.testing.assert_close(probs.sum(-1), torch.ones(64))
+    (tw * torch.randn(64, 2)).sum().backward()
+    assert logits.grad is not None and torch.isfinite(logits.grad).all()
+    a, w = torch.randn(8, 256), torch.randn(128, 256)
+    torch.testing.assert_close(Fn.linear_fp8(a, w), a @ w.t())      # falls back to the plain linear off the GPU
+    q = torch.randn(2, 16, 4, 32)
+    cos = torch.cos(torch.arange(16)[:, None] * torch.ones(16)[None, :] * 0.1)
+    sin = torch.sin(torch.arange(16)[:, None] * torch.ones(16)[None, :] * 0.1)
+    torch.testing.assert_close(Fn.rope_bthd(q, cos, sin), Fn.rope(q.transpose(1, 2), cos, sin).transpose(1, 2))
