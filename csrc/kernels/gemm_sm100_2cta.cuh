@@ -20,6 +20,16 @@ constexpr int kPairBlockN = 256;   // columns of the pair's tile (each CTA stage
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kBlockM * kBlockK * 2 + (kPairBlockN / 2) * kBlockK * 2;   // 32 KB
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 512;
+// Scatter epilogue (GEMM -> reduce-scatter): 8 KB of staging per epilogue warp behind the pipeline stages.
+constexpr int kPairScatterStage = 32 * 128 * 2;          // 32 rows x 128 bf16 columns = two 128-byte-swizzled boxes
+constexpr int kPairScatterSmemBytes = kPairStages * kPairStageBytes + 1024 + 4 * kPairScatterStage + 1024;   // stages, barriers, staging, alignment slack
+
+// One tensor map per destination rank over its staging buffer [world * rows_per_rank, N] bf16, box 64 columns x 32
+// rows, 128-byte swizzle: tiles travel to the owner as TMA stores (whole 128-byte lines over NVLink) instead of
+// one 64-byte piece per lane.
+struct ScatterMaps {
+  CUtensorMap m[8];
+};
 
 int gemm_pair_mode();   // 0 never, 1 where the cost model prefers pairs, 2 always (set by lt_gemm_set_pair_mode)
 
@@ -60,7 +70,8 @@ inline double pair_cost(int M, int N, int K, int sms, bool split_on) {
 // the grid (an even number) belong to another role of a fused kernel.
 template <int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
 __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
-                                               TileGate gate, TileDone done, int cta_first = 0) {
+                                               TileGate gate, TileDone done, int cta_first = 0,
+                                               const ScatterMaps* scatter = nullptr) {
   constexpr int S = kPairStages;
   constexpr int kABytes = kBlockM * kBlockK * 2;
   extern __shared__ uint8_t smem_raw[];
@@ -193,6 +204,60 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
       tc_fence_after();
       const int row = m_blk * kPairBlockM + int(cta_rank) * kBlockM + quarter * 32 + lane;
       const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kPairBlockN;
+      if (scatter != nullptr) {
+        // GEMM -> reduce-scatter: this warp's 32 rows x 256 columns go to the rank that owns the rows as four TMA
+        // stores of 32 x 64 bf16 (staged in shared memory, two boxes at a time).
+        uint8_t* stg = smem + S * kPairStageBytes + 1024 + (warp - 2) * kPairScatterStage;
+        const int row0 = m_blk * kPairBlockM + int(cta_rank) * kBlockM + quarter * 32;
+        const bool live = row0 < p.M;
+        const int owner = live ? row0 / p.rows_per_rank : 0;
+        const int dst_row = p.src_rank * p.rows_per_rank + (row0 - owner * p.rows_per_rank);
+#pragma unroll 1
+        for (int hf = 0; hf < 2; ++hf) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous stores have finished reading the staging area
+          __syncwarp();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_addr + (hf * 4 + c) * 32, r);
+            tmem_ld_wait();
+            uint8_t* box = stg + (c >> 1) * (32 * 128) + lane * 128;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w4;
+              w4.x = pack_bf16x2(__uint_as_float(r[u * 8 + 0]) * p.alpha, __uint_as_float(r[u * 8 + 1]) * p.alpha);
+              w4.y = pack_bf16x2(__uint_as_float(r[u * 8 + 2]) * p.alpha, __uint_as_float(r[u * 8 + 3]) * p.alpha);
+              w4.z = pack_bf16x2(__uint_as_float(r[u * 8 + 4]) * p.alpha, __uint_as_float(r[u * 8 + 5]) * p.alpha);
+              w4.w = pack_bf16x2(__uint_as_float(r[u * 8 + 6]) * p.alpha, __uint_as_float(r[u * 8 + 7]) * p.alpha);
+              const int unit = ((c & 1) * 4 + u) ^ (lane & 7);
+              *reinterpret_cast<uint4*>(box + unit * 16) = w4;
+            }
+          }
+          if (hf == 1) {   // the accumulator buffer is in registers / shared memory: release it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_bar(buf), 0);
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && live) {
+#pragma unroll
+            for (int bx = 0; bx < 2; ++bx) {
+              const int col = n_blk * kPairBlockN + hf * 128 + bx * 64;
+              if (col < p.N) tma_store_2d(&scatter->m[owner], smem_u32(stg + bx * (32 * 128)), col, dst_row);
+            }
+            tma_store_commit();
+          }
+        }
+        if (lane == 0) {
+          tma_store_wait<0>();            // the tile's rows have left this GPU before the owner is told
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence_system();
+          done(m_blk * (kPairBlockM / kBlockM) + int(cta_rank), n_blk);
+        }
+        __syncwarp();
+        continue;
+      }
       // Split tail (see GemmParams): per split tile the workspace holds, for each other part, the two CTAs'
       // 128 x 256 fp32 accumulators as [chunk of 32 columns][group of 4 columns][row][4]; one flag per (tile, CTA, lane quarter).
       constexpr int kChunks = kPairBlockN / 32;

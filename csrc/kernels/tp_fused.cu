@@ -47,52 +47,65 @@ struct ArriveDone {
 // Second phase of the fused kernels: sum the W staged partials of every local row block once its arrival counter
 // shows that all ranks delivered it (bounded wait), add bias / residual, write bf16.
 __device__ __forceinline__ void rs_reduce_phase(const GemmParams& p, const RsArgs& a) {
-  // ---------------------------------------------------------------- reduce phase over this rank's row blocks
+  // Work items are (local 128-row block, 256-column slice) pairs spread over every CTA of the grid, and a thread keeps
+  // the loads of several 16-byte vectors of all W partials in flight: with one CTA per row block and one vector per
+  // thread this phase, not the GEMM, set the kernel's duration.
   __shared__ int ok_s;
+  constexpr int kSlice = 256;
+  constexpr int kVecPerRow = kSlice / 8;
+  constexpr int kUnroll = 4;
   const int local_blocks = a.rows_per_rank / kBlockM;
-  const int col_vecs = a.N / 8;
-  for (int lb = blockIdx.x; lb < local_blocks; lb += gridDim.x) {
-    if (threadIdx.x == 0) ok_s = wait_flag_ge_sys(a.my_counters + lb, a.target, p.status) ? 1 : 0;
-    __syncthreads();
-    const int ok = ok_s;
-    __syncthreads();
-    if (!ok) return;
-    const long long slot = (long long)a.rows_per_rank * a.N;
-    for (int i = threadIdx.x; i < kBlockM * col_vecs; i += blockDim.x) {
-      const int r = lb * kBlockM + i / col_vecs;
-      const int c = (i % col_vecs) * 8;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int col_slices = (a.N + kSlice - 1) / kSlice;
+  const long long slot = (long long)a.rows_per_rank * a.N;
+  int last_lb = -1;
+  for (int item = blockIdx.x; item < local_blocks * col_slices; item += gridDim.x) {
+    const int lb = item / col_slices, cs = item % col_slices;
+    if (lb != last_lb) {
+      if (threadIdx.x == 0) ok_s = wait_flag_ge_sys(a.my_counters + lb, a.target, p.status) ? 1 : 0;
+      __syncthreads();
+      const int ok = ok_s;
+      __syncthreads();
+      if (!ok) return;
+      last_lb = lb;
+    }
+    const int total = kBlockM * kVecPerRow;
+    for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * kUnroll) {
+      uint4 u[kUnroll][kRsMaxRanks];
+      int rr[kUnroll], cc[kUnroll];
+      bool on[kUnroll];
 #pragma unroll
-      for (int src = 0; src < kRsMaxRanks; ++src) {
-        if (src < a.world) {
-          const uint4 u = ld_relaxed_sys_v4(a.stage + src * slot + (long long)r * a.N + c);
-          float2 f;
-          f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-          f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-          f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-          f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
+      for (int q = 0; q < kUnroll; ++q) {
+        const int i = i0 + q * blockDim.x;
+        rr[q] = lb * kBlockM + i / kVecPerRow;
+        cc[q] = cs * kSlice + (i % kVecPerRow) * 8;
+        on[q] = (i < total) && (cc[q] < a.N);
+        if (on[q]) {
+#pragma unroll
+          for (int src = 0; src < kRsMaxRanks; ++src)
+            if (src < a.world) u[q][src] = ld_relaxed_sys_v4(a.stage + src * slot + (long long)rr[q] * a.N + cc[q]);
         }
       }
-      if (a.bias) {
-        const uint4 u = *reinterpret_cast<const uint4*>(a.bias + c);
-        float2 f;
-        f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
+#pragma unroll
+      for (int q = 0; q < kUnroll; ++q) {
+        if (!on[q]) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        auto add8 = [&](const uint4& v) {
+          float2 f;
+          f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
+          f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
+          f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
+          f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+        };
+#pragma unroll
+        for (int src = 0; src < kRsMaxRanks; ++src)
+          if (src < a.world) add8(u[q][src]);
+        if (a.bias) add8(*reinterpret_cast<const uint4*>(a.bias + cc[q]));
+        if (a.residual) add8(*reinterpret_cast<const uint4*>(a.residual + (long long)rr[q] * a.ldr + cc[q]));
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(a.out + (long long)rr[q] * a.ldo + cc[q]) = o;
       }
-      if (a.residual) {
-        const uint4 u = *reinterpret_cast<const uint4*>(a.residual + (long long)r * a.ldr + c);
-        float2 f;
-        f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
-      }
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(a.out + (long long)r * a.ldo + c) = o;
     }
   }
 }
@@ -124,22 +137,22 @@ static int launch_gemm_rs(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
 template <int A_MAJOR, int B_MAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-                    const RsArgs a) {
+                    const RsArgs a, const __grid_constant__ ScatterMaps sm) {
   ArriveDone done{a.peer_counters, a.rows_per_rank, p.M};
-  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done);
+  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done, 0, &sm);
   rs_reduce_phase(p, a);
 }
 
 template <int A_MAJOR, int B_MAJOR>
-static int launch_gemm_rs_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const RsArgs& a, int grid,
-                               cudaStream_t st) {
+static int launch_gemm_rs_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const RsArgs& a,
+                               const ScatterMaps& sm, int grid, cudaStream_t st) {
   static bool configured = false;
   auto kern = gemm_rs_pair_kernel<A_MAJOR, B_MAJOR>;
   if (!configured) {
-    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+    LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairScatterSmemBytes));
     configured = true;
   }
-  kern<<<grid, kGemmThreads, kPairSmemBytes, st>>>(tmA, tmB, p, a);
+  kern<<<grid, kGemmThreads, kPairScatterSmemBytes, st>>>(tmA, tmB, p, a, sm);
   LT_LAUNCH_CHECK();
   return 0;
 }
@@ -194,7 +207,14 @@ int lt_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (pairs) {
     const int grid2 = 2 * (sms / 2 < p.num_tiles ? sms / 2 : p.num_tiles);
-    return b_major ? launch_gemm_rs_pair<0, 1>(tmA, tmB, p, a, grid2, st) : launch_gemm_rs_pair<0, 0>(tmA, tmB, p, a, grid2, st);
+    ScatterMaps sm;
+    for (int q = 0; q < kRsMaxRanks; ++q) {
+      const void* base = stage_ptrs[q < world ? q : 0];
+      const int e = encode_tmap_2d(&sm.m[q], base, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, 1);
+      if (e) return 3000 + e;
+    }
+    return b_major ? launch_gemm_rs_pair<0, 1>(tmA, tmB, p, a, sm, grid2, st)
+                   : launch_gemm_rs_pair<0, 0>(tmA, tmB, p, a, sm, grid2, st);
   }
   int grid = sms < p.num_tiles ? sms : p.num_tiles;
   if (block_n == 256) return b_major ? launch_gemm_rs<256, 0, 1>(tmA, tmB, p, a, grid, st) : launch_gemm_rs<256, 0, 0>(tmA, tmB, p, a, grid, st);
