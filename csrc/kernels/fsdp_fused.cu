@@ -230,21 +230,27 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const RsAdamArgs a) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
       float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       const long long fo = sg.full_off + i * 8;
+      const long long so = sg.shard_off + i * 8;
+      // every load of the iteration is issued before the first use: the optimizer state (HBM) travels under the
+      // NVLink latency of the peers' gradients instead of after it
+      uint4 u[kMaxRanks];
       if (a.mc_grads) {
-        acc_bf16x8(g, multimem_ld_reduce_bf16x8(a.mc_grads + fo));
+        u[0] = multimem_ld_reduce_bf16x8(a.mc_grads + fo);
       } else {
-        uint4 u[kMaxRanks];
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
           if (r < a.world) u[r] = ld_relaxed_sys_v4(a.grads[r] + fo);
+      }
+      float4 p0 = __ldcs(reinterpret_cast<const float4*>(a.master + so)), p1 = __ldcs(reinterpret_cast<const float4*>(a.master + so + 4));
+      float4 m0 = __ldcs(reinterpret_cast<const float4*>(a.m + so)), m1 = __ldcs(reinterpret_cast<const float4*>(a.m + so + 4));
+      float4 v0 = __ldcs(reinterpret_cast<const float4*>(a.v + so)), v1 = __ldcs(reinterpret_cast<const float4*>(a.v + so + 4));
+      if (a.mc_grads) {
+        acc_bf16x8(g, u[0]);
+      } else {
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
           if (r < a.world) acc_bf16x8(g, u[r]);
       }
-      const long long so = sg.shard_off + i * 8;
-      float4 p0 = *reinterpret_cast<const float4*>(a.master + so), p1 = *reinterpret_cast<const float4*>(a.master + so + 4);
-      float4 m0 = *reinterpret_cast<const float4*>(a.m + so), m1 = *reinterpret_cast<const float4*>(a.m + so + 4);
-      float4 v0 = *reinterpret_cast<const float4*>(a.v + so), v1 = *reinterpret_cast<const float4*>(a.v + so + 4);
       float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
       float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
       float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -417,7 +423,14 @@ int lt_ag_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   int rot = 0;
   setup_gather(g, gather_operand, M, N, K, block_n, rank, rows_per_rank, rot);
   if (pairs) fill_pair_tiles(p);
-  if (gather_operand == 0) { p.raster = 2; p.rot = pairs ? rot / 2 : rot; }   // chunks of A are 128 rows, pair tiles 256
+  if (gather_operand == 0) {
+    // A arrives by 128-row chunks starting at this rank's rows.  All N blocks of one M block before the next M block
+    // would stream the whole B operand from DRAM once per M block; instead M blocks are taken in groups (B tiles are
+    // reused across the group out of L2) and the groups start at the one that holds the local rows.
+    const int m_rot = pairs ? rot / 2 : rot;   // chunks of A are 128 rows, pair tiles 256
+    if (p.m_blocks % p.group_m == 0 && p.m_blocks > p.group_m) { p.raster = 0; p.rot = m_rot / p.group_m; }
+    else { p.raster = 2; p.rot = m_rot; }
+  }
   else if (gather_operand == 1) { p.raster = 1; p.rot = rot; }
   else { p.k_rot = rot; }
   PrefetchArgs pf{};

@@ -40,7 +40,7 @@ struct GemmParams {
   float alpha;
   int m_blocks, n_blocks, k_blocks, num_tiles;
   int group_m;  // raster group height (tiles)
-  // Tile order: 0 = grouped raster (L2 friendly); 1 = all M blocks of one N block before the next N block,
+  // Tile order: 0 = grouped raster (L2 friendly; groups of group_m M blocks, starting at group `rot`); 1 = all M blocks of one N block before the next N block,
   // starting at N block `rot`; 2 = all N blocks of one M block before the next, starting at M block `rot`.
   // Modes 1 and 2 let a fused all-gather deliver the gathered operand in the order the tiles consume it.
   int raster, rot;
@@ -124,7 +124,12 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     return;
   }
   const int per_group = p.group_m * p.n_blocks;
-  const int group = tile / per_group;
+  int group = tile / per_group;
+  if (p.rot > 0) {   // groups start at group `rot` and wrap (only set when every group is full)
+    const int n_groups = p.m_blocks / p.group_m;
+    group += p.rot;
+    if (group >= n_groups) group -= n_groups;
+  }
   const int first_m = group * p.group_m;
   const int rows = min(p.m_blocks - first_m, p.group_m);
   const int in_group = tile - group * per_group;

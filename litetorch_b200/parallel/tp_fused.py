@@ -52,8 +52,13 @@ class TPFusedContext:
         self.ag_calls += 1
         sh = self.shard[slot].tensor[:rows * Kd].view(rows, Kd)
         sh.copy_(x_shard)
-        self._barrier()                                    # every rank's shard is in place
         full = self.full[:M * Kd].view(M, Kd)
+        # This rank's own rows need no gather: they go straight into the assembled operand and their chunk flags are
+        # set to this call's epoch, so the gather CTAs only fetch the peers' rows and the first tiles start at once.
+        full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
+        if rows % 128 == 0:
+            self.gather_flags[self.rank * rows // 128:(self.rank + 1) * rows // 128].fill_(self.ag_calls)
+        self._barrier()                                    # every rank's shard is in place
         assert b_major == 0
         y = K.ag_gemm(None, full, gather_operand=0, shard_ptrs=self.shard[slot].ptrs, world=self.world, rank=self.rank,
                       rows_per_rank=rows, flags=self.gather_flags, epoch=self.ag_calls, other=w, bias=bias, n_comm=self.n_comm)
