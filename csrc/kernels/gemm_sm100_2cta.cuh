@@ -193,6 +193,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps per CTA, own 128 rows)
     const int quarter = warp & 3;
+    int pend_m = -1, pend_n = 0;   // scatter epilogue: tile whose completion signal is still owed
     WorkItem w;
     for (int it = 0; get_item(p, pair_id, pair_count, it, w); ++it) {
       int m_blk, n_blk;
@@ -240,20 +241,30 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
           }
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0 && live) {
+          if (lane == 0) {
+            if (live) {
 #pragma unroll
-            for (int bx = 0; bx < 2; ++bx) {
-              const int col = n_blk * kPairBlockN + hf * 128 + bx * 64;
-              if (col < p.N) tma_store_2d(&scatter->m[owner], smem_u32(stg + bx * (32 * 128)), col, dst_row);
+              for (int bx = 0; bx < 2; ++bx) {
+                const int col = n_blk * kPairBlockN + hf * 128 + bx * 64;
+                if (col < p.N) tma_store_2d(&scatter->m[owner], smem_u32(stg + bx * (32 * 128)), col, dst_row);
+              }
             }
-            tma_store_commit();
+            tma_store_commit();   // always two groups per tile (possibly empty): the deferred signal counts on it
           }
         }
+        // The owner is told about a tile only once its stores have completed at the owner, a round trip over NVLink.
+        // Waiting for that here would put the round trip into every tile's epilogue, so the signal of a tile is sent
+        // after the NEXT tile's stores have been committed (its own two groups are then the only ones that may
+        // still be pending); the last tile's signal follows the loop.
         if (lane == 0) {
-          tma_store_wait<0>();            // the tile's rows have left this GPU before the owner is told
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-          __threadfence_system();
-          done(m_blk * (kPairBlockM / kBlockM) + int(cta_rank), n_blk);
+          if (pend_m >= 0) {
+            tma_store_wait<2>();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence_system();
+            done(pend_m, pend_n);
+          }
+          pend_m = m_blk * (kPairBlockM / kBlockM) + int(cta_rank);
+          pend_n = n_blk;
         }
         __syncwarp();
         continue;
@@ -337,6 +348,12 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
         mbar_arrive_cluster(tempty_bar(buf), 0);
         done(m_blk * (kPairBlockM / kBlockM) + int(cta_rank), n_blk);
       }
+    }
+    if (scatter != nullptr && lane == 0 && pend_m >= 0) {
+      tma_store_wait<0>();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence_system();
+      done(pend_m, pend_n);
     }
   }
 

@@ -181,19 +181,55 @@ class LocalWeights:
 
     def optimizer_step(self, *, lr, beta1, beta2, eps, weight_decay, step, dyn=None):
         nm = self.n_matrix
+        if getattr(self, "_hyper", None) is not None and getattr(self, "_updated", 0) == nm and dyn is None:
+            # every matrix was updated bucket by bucket on the side stream during the backward pass
+            K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
+                        beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True)
+            torch.cuda.current_stream().wait_stream(self._side)
+            self._updated = 0
+            return
+        if getattr(self, "_updated", 0):
+            raise RuntimeError("optimizer_step after a partial overlapped update")
         K.adam_flat(self.master[:nm], self.flat_g[:nm], self.m[:nm], self.v[:nm], self.flat_p[:nm], lr=lr, beta1=beta1,
                     beta2=beta2, eps=eps, wd=weight_decay, step=step, adamw=True, dyn=dyn)
         K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
                     beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True, dyn=dyn)
 
+    # ---- AdamW overlapped with the backward pass: as soon as the weight gradients of a bucket ("head", a layer, "embed")
+    # have been issued, its slice of the flat buffers is updated on a side stream.  The update is bound by HBM
+    # bandwidth and the GEMMs it runs beside are bound by the tensor cores, so most of it is hidden; the vectors
+    # (norm gains) and whatever was not covered are updated at the end.
+    def _bucket_range(self, bucket):
+        if bucket == "embed":
+            names = ["embed"]
+        elif bucket == "head":
+            names = ["lm_head"]
+        else:
+            names = ["layers.%d.%s" % (bucket, n) for n in ("wqkv", "wo", "w_gu", "w_down")]
+        lo = min(self.by_name[n].offset for n in names)
+        hi = max(self.by_name[n].offset + (math.prod(self.by_name[n].shape) + 127) // 128 * 128 for n in names)
+        return lo, hi
+
     def begin_step(self, **hyper):
-        pass
+        self._hyper = hyper
+        self._updated = 0
+        if getattr(self, "_side", None) is None and self.flat_p.is_cuda:
+            self._side = torch.cuda.Stream(device=self.flat_p.device)
 
     def bucket_done(self, bucket):
         """Hook: all weight gradients of a bucket ("head", layer index, "embed") have been issued."""
+        h = getattr(self, "_hyper", None)
+        if h is None or getattr(self, "_side", None) is None:
+            return
+        a, b = self._bucket_range(bucket)
+        self._side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._side):
+            K.adam_flat(self.master[a:b], self.flat_g[a:b], self.m[a:b], self.v[a:b], self.flat_p[a:b], lr=h["lr"],
+                        beta1=h["beta1"], beta2=h["beta2"], eps=h["eps"], wd=h["weight_decay"], step=h["step"], adamw=True)
+        self._updated += b - a
 
     def finish_step(self):
-        pass
+        self._hyper = None
 
     def parameters(self) -> List[torch.Tensor]:
         return [self.master_view(s.name) for s in self.specs]

@@ -19,8 +19,9 @@ from .fsdp import SymmetricBuffer
 
 
 class TPFusedContext:
-    def __init__(self, max_rows: int, max_cols: int, device, group=None, n_comm: int = 8):
-        """max_rows: global sequence rows (tokens) of the largest activation; max_cols: its widest feature dimension."""
+    def __init__(self, max_rows: int, max_cols: int, device, group=None, n_comm: int = 0):
+        """max_rows: global sequence rows (tokens) of the largest activation; max_cols: its widest feature dimension;
+        n_comm: gather CTAs of the all-gather GEMMs (0: chosen per call from the GEMM's FLOPs and the bytes to fetch)."""
         self.group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.device = torch.device(device)
