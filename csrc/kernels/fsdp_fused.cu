@@ -347,12 +347,13 @@ static int launch_ag_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, c
 // Whether a gather-GEMM of this shape runs on CTA pairs (the decision must be the same wherever tile counts are
 // derived: the kernel launch, the progress target of a prefetch and lt_gemm_num_tiles).
 // Gather CTAs for one call when the caller leaves the choice open.  One gather CTA moves 20-30 GB/s (its bulk copies are
-// bound by the requests a single SM keeps in flight over NVLink), so the gather's rate grows with the CTAs given to it
-// while the GEMM loses those SMs.  Picks the count (a multiple of 4, so that CTA pairs stay aligned) with the smallest
-// larger-of-the-two time, never fewer than 8.  Measured on [8192, 3584, 4096] with half of A remote: 8 / 12 / 16 / 24
-// gather CTAs take 0.295 / 0.265 / 0.242 / 0.270 ms.
+// bound by the requests a single SM keeps in flight over NVLink) but whole chunks land late, so the model counts
+// 14 GB/s; the gather's rate grows with the CTAs given to it while the GEMM loses those SMs.  Picks the count (a
+// multiple of 4, so that CTA pairs stay aligned) with the smallest larger-of-the-two time, never fewer than 8.
+// Measured on [8192, 3584, 4096] with half of A remote: 8 / 12 / 16 / 24 gather CTAs take 0.295 / 0.265 / 0.242 /
+// 0.270 ms.
 static int pick_gather_ctas(double flops, double remote_bytes, int sms) {
-  constexpr double kPerCtaBytesPerSec = 20e9;
+  constexpr double kPerCtaBytesPerSec = 14e9;
   constexpr double kPerSmFlopsPerSec = 1.5e15 / 148.0;
   int best = 8;
   double best_t = 1e30;

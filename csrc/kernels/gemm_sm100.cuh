@@ -125,6 +125,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   }
   const int per_group = p.group_m * p.n_blocks;
   int group = tile / per_group;
+  const int in_group = tile - group * per_group;   // position inside the group, taken before the group is rotated
   if (p.rot > 0) {   // groups start at group `rot` and wrap (only set when every group is full)
     const int n_groups = p.m_blocks / p.group_m;
     group += p.rot;
@@ -132,7 +133,6 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   }
   const int first_m = group * p.group_m;
   const int rows = min(p.m_blocks - first_m, p.group_m);
-  const int in_group = tile - group * per_group;
   m_blk = first_m + in_group % rows;
   n_blk = in_group / rows;
 }

@@ -260,8 +260,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
           if (pend_m >= 0) {
             tma_store_wait<2>();
             asm volatile("fence.proxy.async.global;" ::: "memory");
-            __threadfence_system();
-            done(pend_m, pend_n);
+            done(pend_m, pend_n);   // a release at the scope the owner needs
           }
           pend_m = m_blk * (kPairBlockM / kBlockM) + int(cta_rank);
           pend_n = n_blk;
@@ -352,7 +351,6 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
     if (scatter != nullptr && lane == 0 && pend_m >= 0) {
       tma_store_wait<0>();
       asm volatile("fence.proxy.async.global;" ::: "memory");
-      __threadfence_system();
       done(pend_m, pend_n);
     }
   }

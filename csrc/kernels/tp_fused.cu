@@ -34,13 +34,17 @@ struct ArriveDone {
   uint32_t* const* peer_counters;
   int rows_per_rank;
   int total_rows;
-  __device__ __forceinline__ void fence() const { __threadfence_system(); }
+  int rank;
+  // No fence per lane: the lanes' stores are ordered before lane 0's release by the warp barrier between them, and a
+  // release is cumulative.  A system-scope fence in every lane of every tile cost more than the tile's main loop.
+  __device__ __forceinline__ void fence() const {}
   __device__ __forceinline__ void operator()(int m_blk, int) const {
     const int row0 = m_blk * kBlockM;
     if (row0 >= total_rows) return;   // the odd CTA of a pair past the last row block
     const int owner = row0 / rows_per_rank;
     const int local_blk = (row0 - owner * rows_per_rank) / kBlockM;
-    red_add_release_sys(peer_counters[owner] + local_blk, 1u);
+    if (owner == rank) red_add_release_gpu(peer_counters[owner] + local_blk, 1u);   // own rows: nothing left this GPU
+    else red_add_release_sys(peer_counters[owner] + local_blk, 1u);
   }
 };
 
@@ -114,7 +118,7 @@ template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                const RsArgs a) {
-  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M};
+  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M, a.rank};
   gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done);
   rs_reduce_phase(p, a);
 }
@@ -138,7 +142,7 @@ template <int A_MAJOR, int B_MAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                     const RsArgs a, const __grid_constant__ ScatterMaps sm) {
-  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M};
+  ArriveDone done{a.peer_counters, a.rows_per_rank, p.M, a.rank};
   gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), done, 0, &sm);
   rs_reduce_phase(p, a);
 }

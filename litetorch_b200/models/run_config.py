@@ -76,6 +76,8 @@ def main():
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--n-seq", type=int, default=0, help="sequences per micro-batch (default: the layout's)")
     ap.add_argument("--fp8", action="store_true", help="e4m3 GEMMs with 1x128 / 128x128 block scales (NCCL collectives)")
+    ap.add_argument("--layout", default="", help="hybrid only: tp,cp,pp sizes (e.g. 1,2,2) instead of the default for the world size")
+    ap.add_argument("--micro", type=int, default=0, help="micro-batches per step (default: the layout's)")
     args = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -108,10 +110,14 @@ def main():
         seq = args.seq or (1024 if args.tiny else 32768)
         n_seq, micro = 1, 8
         tp, cp, pp = (2, 2, 2) if world >= 8 else ((2, 2, 1) if world == 4 else ((2, 1, 1) if world == 2 else (1, 1, 1)))
+        if args.layout:
+            tp, cp, pp = (int(v) for v in args.layout.split(","))
         groups, _ = _make_groups(world, rank, tp, cp, pp, world // (tp * cp * pp))
         layout = "tp%d x cp%d x pp%d" % (tp, cp, pp)
     if args.n_seq:
         n_seq = args.n_seq
+    if args.micro:
+        micro = args.micro
     ep_group = dist.group.WORLD if (args.config == "ep8" and world > 1) else None
 
     dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True,
@@ -182,7 +188,8 @@ def main():
         ms = (time.perf_counter() - t0) * 1e3 / args.steps
     t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    lv = last.float().reshape(1).clone()
+    # the last pipeline stage holds the loss (0.0 elsewhere); a NaN must not be hidden by the maximum
+    lv = torch.nan_to_num(last.float().reshape(1).clone(), nan=float("inf"))
     dist.all_reduce(lv, op=dist.ReduceOp.MAX)
     dp_like = world if args.config == "ep8" else (dist.get_world_size(groups["dp"]) if groups["dp"] is not None else 1)
     tokens = n_seq * seq * micro * dp_like

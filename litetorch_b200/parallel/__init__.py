@@ -8,6 +8,7 @@ from .pp import PipelineParallelModule
 from .cp import (context_parallel_backward, context_parallel_forward, ring_attention, zigzag_merge, zigzag_positions,
                  zigzag_split)
 from .ep import MoEFeedForward
+from .ulysses import head_to_seq, seq_to_head, ulysses_attention
 from .fsdp_api import FSDP, FullyShardedDataParallel
 from ..core import manual_seed
 

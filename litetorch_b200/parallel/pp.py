@@ -115,7 +115,7 @@ class PipelineParallelModule:
         warm = min(M, W - r - 1)
         steady = M - warm
         fifo = deque()
-        total = 0.0
+        total = None                      # sum of the micro-batch losses, kept on the device until the step's end
         first, last = (r == 0 or W == 1), (r == W - 1)
 
         def run_fwd(i, xin):
@@ -129,7 +129,7 @@ class PipelineParallelModule:
             if last:
                 tgt = targets[i] if targets is not None else microbatches[i]
                 loss = _unwrap(loss_fn(Tensor(out), tgt))
-                total += float(loss.detach())
+                total = loss.detach().float() if total is None else total + loss.detach().float()
                 (loss / M).backward()
             else:
                 out.backward(grad_out)
@@ -184,7 +184,7 @@ class PipelineParallelModule:
             gin = run_bwd(grad_out)
             if not first:
                 self._batched(gin, r - 1, None, 0)
-        return total / M if last else 0.0
+        return float(total) / M if (last and total is not None) else 0.0
 
     run_1f1b_with_backward = train_step_1f1b
 

@@ -23,13 +23,14 @@ dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 rank, world = dist.get_rank(), dist.get_world_size()
 dev = torch.device("cuda", local)
 worst = 0.0
-for (D, zig, causal) in [(64, True, True), (128, True, True), (64, False, True), (128, False, False)]:
+for (D, zig, causal, direct) in [(64, True, True, False), (128, True, True, False), (64, False, True, False),
+                                (128, False, False, False), (64, True, True, True), (128, True, True, True)]:
     B, Hq, Hkv, Tl = 2, 4, 2, 512
     T = Tl * world
     g = torch.Generator(device="cpu").manual_seed(11)
     q, k, v, do = (torch.randn(B, T, h, D, generator=g) for h in (Hq, Hkv, Hkv, Hq))
     sp = (lambda t: zigzag_split(t, rank, world, 1)) if zig else (lambda t: t.chunk(world, 1)[rank].contiguous())
-    ctx = RingFlashContext(B, Tl, Hq, Hkv, D, dev, zigzag=zig)
+    ctx = RingFlashContext(B, Tl, Hq, Hkv, D, dev, zigzag=zig, direct_peer=direct)
     ql, kl, vl = (sp(t).to(dev).bfloat16().requires_grad_(True) for t in (q, k, v))
     for rep in range(2):
         for t in (ql, kl, vl): t.grad = None
