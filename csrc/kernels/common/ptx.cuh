@@ -28,6 +28,12 @@ enum DeviceStatus : int {
 #ifndef LT_WAIT_CYCLES
 #define LT_WAIT_CYCLES 2500000000ll
 #endif
+// Waits on a flag that ANOTHER GPU writes get a longer budget (about 10 s): at start-up the ranks of a job can be more
+// than a second apart (lazy module loading, communicator set-up, first allocations), and a wait that gives up there
+// leaves that step's result wrong although nothing failed.
+#ifndef LT_PEER_WAIT_CYCLES
+#define LT_PEER_WAIT_CYCLES 18000000000ll
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -316,7 +322,7 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* p, uint32_t tar
   for (uint32_t it = 1;; ++it) {
     if (ld_acquire_sys(p) >= target) return true;
     if ((it & 63u) == 0u) {
-      if (clock64() - t0 > LT_WAIT_CYCLES) {
+      if (clock64() - t0 > LT_PEER_WAIT_CYCLES) {
         if (status) atomicCAS(status, 0, int(kStatusTimeoutPeerFlag));
         return false;
       }

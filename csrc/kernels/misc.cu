@@ -378,6 +378,67 @@ static inline unsigned grid_for(long long n, int threads, int per_sm) {
   return unsigned(b);
 }
 
+// ------------------------------------------------------------------------------------------------ MoE expert backward, pointwise part
+// One warp per routed slot.  From gu = [gate | up] (bf16 [S, 2F]), the unweighted gradient of the expert output's input
+// dh_u (bf16 [S, F]) and the slot's gate weight w it produces, in one pass over the rows:
+//   h = silu(gate) * up (rounded to bf16 as the forward stored it),
+//   dw[s] = sum_f h * dh_u                  (gradient of the gate weight),
+//   hw = h * w                              (A operand of the down-projection weight gradient),
+//   dgu = SwiGLU backward of dh = dh_u * w  (input of the up-projection weight gradient and of dX).
+// Padding slots (slot_src[s][0] < 0) write zeros and read nothing.
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+__global__ void moe_expert_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh_u,
+                                      const float* __restrict__ w, const int* __restrict__ slot_src,
+                                      __nv_bfloat16* __restrict__ dgu, __nv_bfloat16* __restrict__ hw,
+                                      float* __restrict__ dw, int S, int F) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= S) return;
+  const long long r = warp;
+  const bool valid = slot_src[2 * r] >= 0;
+  const float wr = valid ? w[r] : 0.f;
+  float dot = 0.f;
+  for (int c = lane * 8; c < F; c += 32 * 8) {
+    uint4 og = make_uint4(0, 0, 0, 0), ou = og, oh = og;
+    if (valid) {
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + r * 2 * F + c);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + r * 2 * F + F + c);
+      const uint4 d4 = *reinterpret_cast<const uint4*>(dh_u + r * F + c);
+      const uint32_t gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+      uint32_t rg[4], ru[4], rh[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = unpack_bf16x2(gs[j]), u = unpack_bf16x2(us[j]), d = unpack_bf16x2(ds[j]);
+        float dg[2], du[2], hh[2];
+        const float gg[2] = {g.x, g.y}, uu[2] = {u.x, u.y}, dd[2] = {d.x, d.y};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float sg = 1.f / (1.f + __expf(-gg[q]));
+          const float silu = gg[q] * sg;
+          const float h = round_bf16(silu * uu[q]);
+          dot += h * dd[q];
+          const float dh = round_bf16(dd[q] * wr);
+          du[q] = dh * silu;
+          dg[q] = dh * uu[q] * (sg + silu * (1.f - sg));
+          hh[q] = h * wr;
+        }
+        rg[j] = pack_bf16x2(dg[0], dg[1]);
+        ru[j] = pack_bf16x2(du[0], du[1]);
+        rh[j] = pack_bf16x2(hh[0], hh[1]);
+      }
+      og = make_uint4(rg[0], rg[1], rg[2], rg[3]);
+      ou = make_uint4(ru[0], ru[1], ru[2], ru[3]);
+      oh = make_uint4(rh[0], rh[1], rh[2], rh[3]);
+    }
+    *reinterpret_cast<uint4*>(dgu + r * 2 * F + c) = og;
+    *reinterpret_cast<uint4*>(dgu + r * 2 * F + F + c) = ou;
+    *reinterpret_cast<uint4*>(hw + r * F + c) = oh;
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dw[r] = dot;
+}
+
 }  // namespace lt
 
 extern "C" {
@@ -522,6 +583,23 @@ int lt_strided_copy(const void* src, void* dst, int ndim, const long long* shape
     case 8: strided_copy_kernel<8><<<blocks, 256, 0, st>>>(s, t, n, d); break;
     default: return -int(kStatusBadArgument);
   }
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// gu [S, 2F], dh_u [S, F] bf16; w [S] fp32; slot_src [S, 2] int32 (first column < 0: padding slot);
+// dgu [S, 2F], hw [S, F] bf16 and dw [S] fp32 are written.  F must be a multiple of 8.
+int lt_moe_expert_bwd(const void* gu, const void* dh_u, const void* w, const void* slot_src, void* dgu, void* hw, void* dw,
+                      int S, int F, void* stream) {
+  using namespace lt;
+  if (S <= 0) return 0;
+  if (F <= 0 || F % 8 != 0) return -int(kStatusBadArgument);
+  const int threads = 256;
+  const unsigned blocks = unsigned((S * 32ll + threads - 1) / threads);
+  moe_expert_bwd_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh_u), static_cast<const float*>(w),
+      static_cast<const int*>(slot_src), static_cast<__nv_bfloat16*>(dgu), static_cast<__nv_bfloat16*>(hw),
+      static_cast<float*>(dw), S, F);
   LT_LAUNCH_CHECK();
   return 0;
 }

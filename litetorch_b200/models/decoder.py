@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import functional as Fn
+from ..utils.sections import section
 from ..parallel import tp as _tp
 
 
@@ -176,31 +177,36 @@ class DecoderBlock:
     def forward(self, x_rows: torch.Tensor, B: int, T_local: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         cfg, dims = self.cfg, self.dims
         D = cfg.head_dim
-        h = Fn.rms_norm(x_rows, self.norm1, cfg.eps)
-        qkv = ag_linear(dims, h, self.wqkv).view(B, T_local, self.hq + 2 * self.hkv, D)
-        q, k, v = qkv[:, :, :self.hq], qkv[:, :, self.hq:self.hq + self.hkv], qkv[:, :, self.hq + self.hkv:]
-        q = Fn.rope_bthd(q, cos, sin).contiguous()
-        k = Fn.rope_bthd(k, cos, sin).contiguous()
-        v = v.contiguous()
-        if dims.cp_world > 1:
-            if dims.cp_fused is not None:
-                a = dims.cp_fused.attention(q, k, v, causal=True)
+        with section("blk.fwd.qkv_rope"):
+            h = Fn.rms_norm(x_rows, self.norm1, cfg.eps)
+            qkv = ag_linear(dims, h, self.wqkv).view(B, T_local, self.hq + 2 * self.hkv, D)
+            q, k, v = qkv[:, :, :self.hq], qkv[:, :, self.hq:self.hq + self.hkv], qkv[:, :, self.hq + self.hkv:]
+            q = Fn.rope_bthd(q, cos, sin).contiguous()
+            k = Fn.rope_bthd(k, cos, sin).contiguous()
+            v = v.contiguous()
+        with section("blk.fwd.attention"):
+            if dims.cp_world > 1:
+                if dims.cp_fused is not None:
+                    a = dims.cp_fused.attention(q, k, v, causal=True)
+                else:
+                    from ..parallel.cp import ring_attention
+                    a = ring_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dims.cp, causal=True,
+                                       zigzag=dims.zigzag).transpose(1, 2)
             else:
-                from ..parallel.cp import ring_attention
-                a = ring_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dims.cp, causal=True,
-                                   zigzag=dims.zigzag).transpose(1, 2)
-        else:
-            a = Fn.flash_attention_bthd(q, k, v, causal=True)
-        a = a.reshape(B * T_local, self.hq * D)
-        x_rows = x_rows + linear_rs(dims, a, self.wo)
-        h = Fn.rms_norm(x_rows, self.norm2, cfg.eps)
+                a = Fn.flash_attention_bthd(q, k, v, causal=True)
+        with section("blk.fwd.attn_out"):
+            a = a.reshape(B * T_local, self.hq * D)
+            x_rows = x_rows + linear_rs(dims, a, self.wo)
+            h = Fn.rms_norm(x_rows, self.norm2, cfg.eps)
         if self.moe is not None:
             from ..core import Tensor, _unwrap
-            y = _unwrap(self.moe.forward(Tensor(h)))
+            with section("blk.fwd.moe"):
+                y = _unwrap(self.moe.forward(Tensor(h)))
             self.aux_loss = self.moe.last_aux_loss
             return x_rows + y
-        gu = ag_linear(dims, h, self.w_gu)
-        return x_rows + linear_rs(dims, Fn.swiglu(gu), self.w_dn)
+        with section("blk.fwd.ffn"):
+            gu = ag_linear(dims, h, self.w_gu)
+            return x_rows + linear_rs(dims, Fn.swiglu(gu), self.w_dn)
 
 
 class ParallelDecoder:

@@ -25,6 +25,8 @@ import torch.distributed as dist
 from ..core import Tensor, _unwrap
 from ..optim import AdamW
 from .decoder import PRESETS, ParallelDecoder, ParallelDims, shard_batch, tiny
+from ..utils import sections
+from ..utils.sections import section
 
 
 def _make_groups(world: int, rank: int, tp: int, cp: int, pp: int, dp: int):
@@ -156,20 +158,33 @@ def main():
         if pipe is None:
             for _ in range(micro):
                 x, y = batch()
-                loss = model.forward_loss(x, y)
-                (loss / micro).backward()
+                with section("step.forward"):
+                    loss = model.forward_loss(x, y)
+                with section("step.backward"):
+                    (loss / micro).backward()
             last = loss.detach()
         else:
             mbs = [batch() for _ in range(micro)]
             xs, ys = [Tensor(m[0]) for m in mbs], [m[1] for m in mbs]
             val = pipe.train_step_1f1b(xs, lambda out, tgt: Tensor(model.loss(_unwrap(out), tgt)), ys)
             last = torch.tensor(val, device=dev)
-        model.reduce_gradients()
-        opt.step()
+        with section("step.reduce_gradients"):
+            model.reduce_gradients()
+        with section("step.optimizer"):
+            opt.step()
         return last
 
+    # Bring the ranks together before the first step: every group's communicator is created by a first small collective
+    # here rather than inside the step, where seconds of skew between ranks would meet the bounded waits of the fused kernels.
+    for g in list(groups.values()) + [ep_group, None]:
+        if g is not None or world > 1:
+            dist.all_reduce(torch.zeros(1, device=dev), group=g)
+    if cuda:
+        torch.cuda.synchronize()
+    dist.barrier()
     for _ in range(args.warmup):
         last = step()
+    sections.reset()
     if cuda:
         torch.cuda.synchronize()
     dist.barrier()
@@ -203,6 +218,10 @@ def main():
                           "tokens_per_s": round(tokens / float(t) * 1e3, 1), "loss": round(float(lv), 4),
                           "fused": bool(fused) and not dims.fp8, "fp8": bool(dims.fp8), "dtype": str(dtype).replace("torch.", ""), "device_status": status,
                           "params_b": round(cfg.n_params() / 1e9, 3)}), flush=True)
+    if rank == 0 and sections.enabled():
+        # per-section CUDA-event totals over the timed steps (LT_SECTIONS=1); nested sections are included in their parents
+        print(json.dumps({"sections_ms_per_step": {k: [v[0] // max(args.steps, 1), round(v[1] / max(args.steps, 1), 3)]
+                                                   for k, v in sections.report().items()}}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -37,6 +37,7 @@ _SIGS = {
     "lt_reduce_parts": [],
     "lt_reduce_all": [_vp, _ll, _i, _i, _vp, _vp, _vp],
     "lt_strided_copy": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp],
+    "lt_moe_expert_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_norm_bwd_ctas": [_i],
     "lt_norm_fwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_norm_bwd": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -710,3 +711,17 @@ def strided_copy(src, dst):
                                 src.element_size(), _stream())
     _check(rc, "lt_strided_copy")
     return dst
+
+
+def moe_expert_bwd(gu, dh_u, w, slot_src):
+    """Pointwise part of the expert backward in one pass: gu [S, 2F], dh_u [S, F] bf16, gate weights w [S] fp32,
+    slot_src [S, 2] int32 (first column < 0 marks a padding slot).  Returns (dgu [S, 2F], h * w [S, F], dw [S] fp32)."""
+    S, F2 = gu.shape
+    F = F2 // 2
+    dgu = torch.empty_like(gu)
+    hw = torch.empty((S, F), dtype=gu.dtype, device=gu.device)
+    dw = torch.empty(S, dtype=torch.float32, device=gu.device)
+    rc = _fn("lt_moe_expert_bwd")(gu.data_ptr(), dh_u.data_ptr(), w.data_ptr(), slot_src.data_ptr(), dgu.data_ptr(),
+                                  hw.data_ptr(), dw.data_ptr(), S, F, _stream())
+    _check(rc, "lt_moe_expert_bwd")
+    return dgu, hw, dw

@@ -96,7 +96,14 @@ class _AdamBase(Optimizer):
             return
         for i in live:
             self._ensure_state(i, ts[i])
-        key = tuple((ts[i].data_ptr(), ts[i].grad.data_ptr()) for i in live)
+        # The table is keyed on the parameters only: gradients are usually freed every step (`zero_grad` drops them) and
+        # come back at other addresses, and rebuilding the per-chunk arrays for that would cost more than the update.
+        key = tuple((ts[i].data_ptr(), ts[i].grad.dtype) for i in live)
+        gptrs = tuple(ts[i].grad.data_ptr() for i in live)
+        if self._table is not None and self._table[0] == key and self._table[1]["gptrs"] != gptrs:
+            tab = self._table[1]
+            tab["g"] = torch.tensor(gptrs, dtype=torch.int64, device=tab["g"].device)
+            tab["gptrs"] = gptrs
         if self._table is None or self._table[0] != key:
             dev = ts[live[0]].device
             chunk = K._fn("lt_adam_chunk_elems")()
@@ -107,7 +114,7 @@ class _AdamBase(Optimizer):
                    "p16": i64([ts[i].data_ptr() if self.master[i] is not None else 0 for i in live]),
                    "numel": i64([ts[i].numel() for i in live]),
                    "gbf": torch.tensor([1 if ts[i].grad.dtype == torch.bfloat16 else 0 for i in live], dtype=torch.int32, device=dev),
-                   "has16": any(self.master[i] is not None for i in live)}
+                   "has16": any(self.master[i] is not None for i in live), "gptrs": gptrs}
             ct, co = [], []
             for k, i in enumerate(live):
                 for off in range(0, ts[i].numel(), chunk):

@@ -97,13 +97,17 @@ class MoEFeedForward:
         logits = torch.nn.functional.linear(x2.float(), _unwrap(self.gate_weight).float())
         top_w, top_i, probs = Fn.moe_router(logits, self.k, renorm=True)   # warp-per-token kernel on CUDA
         # load balance: f_e = fraction of routed slots on expert e, P_e = mean router probability
-        f = torch.zeros(self.E, device=x2.device).index_add_(0, top_i.reshape(-1), torch.ones(N * self.k, device=x2.device)) / (N * self.k)
+        flat = top_i.reshape(-1).long()
+        counts = torch.bincount(flat, minlength=self.E)
+        f = counts.float() / (N * self.k)
         aux = self.E * (f * probs.mean(0)).sum()
-        # capacity: position of each slot inside its expert's queue, in token order
+        # capacity: position of each slot inside its expert's queue, in token order.  A stable sort by expert gives the
+        # queues directly (a cumulative sum over a one-hot [N k, E] matrix walks the N k rows one after the other on a GPU)
         cap = max(1, int(math.ceil(self.capacity_factor * N * self.k / self.E)))
-        flat = top_i.reshape(-1)
-        onehot = torch.nn.functional.one_hot(flat, self.E)
-        pos = (onehot.cumsum(0) - 1).gather(1, flat[:, None])[:, 0]
+        order = torch.argsort(flat, stable=True)
+        starts = torch.cumsum(counts, 0) - counts
+        pos = torch.empty_like(flat)
+        pos[order] = torch.arange(flat.numel(), device=flat.device) - starts[flat[order]]
         keep = (pos < cap).view(N, self.k)
         return top_w, top_i, keep, aux
 

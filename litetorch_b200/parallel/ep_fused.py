@@ -19,6 +19,7 @@ from ..core import Tensor, _unwrap
 from ..ops import kernels as K
 from .ep import MoEFeedForward
 from .fsdp import SymmetricBuffer
+from ..utils.sections import section
 
 
 class MoEFusedFeedForward(MoEFeedForward):
@@ -84,7 +85,8 @@ class MoEFusedFeedForward(MoEFeedForward):
         xt = _unwrap(x)
         shape = xt.shape
         x2 = xt.reshape(-1, shape[-1])
-        top_w, top_i, keep, aux = self.route(x2)
+        with section("moe.route"):
+            top_w, top_i, keep, aux = self.route(x2)
         self.last_aux_loss = aux * self.aux_loss_coef
         self.last_dropped = int((~keep).sum())
         y = _MoEFused.apply(self, x2, top_w, top_i, keep, _unwrap(self.w_gate_up), _unwrap(self.w_down))
@@ -97,82 +99,89 @@ class _MoEFused(torch.autograd.Function):
     @staticmethod
     def forward(ctx, m, x2, top_w, top_i, keep, w_gu, w_dn):
         N, d = x2.shape
-        slot, w, group, origin, S = m._build_slots(top_w, top_i, keep)
+        with section("moe.fwd.build_slots"):
+            slot, w, group, origin, S = m._build_slots(top_w, top_i, keep)
         tok = m.tok.tensor[:N * d].view(N, d)
         acc = m.acc.tensor[:N * d].view(N, d)
-        m.barrier()                                   # peers are done with the previous contents of tok / acc
-        tok.copy_(x2)
-        acc.zero_()
-        m.barrier()                                   # tokens published, accumulators cleared
+        with section("moe.fwd.publish"):
+            m.barrier()                                   # peers are done with the previous contents of tok / acc
+            tok.copy_(x2)
+            acc.zero_()
+            m.barrier()                                   # tokens published, accumulators cleared
         m.epoch += 1
         sb = m.slot_buf[:S * d].view(S, d)
-        gu = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_gu, b_major=0, slot_buf=sb, flags=m.flags, epoch=m.epoch,
-                               n_comm=m.n_comm)
+        with section("moe.fwd.gather_gemm"):
+            gu = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_gu, b_major=0, slot_buf=sb, flags=m.flags, epoch=m.epoch,
+                                   n_comm=m.n_comm)
         # Padding slots (the tail of every expert's last 128-row block) are never fetched: their rows of the staging
         # buffer and of everything computed from it are whatever was there before, possibly NaN bit patterns.  Nothing
         # reads them in the forward (the combine skips them), but the weight-gradient GEMMs sum over all rows of a
         # block, so they are cleared (0 * NaN is NaN: masked, not multiplied).
-        pad = (slot[:, 0] < 0)[:, None]
-        xs = sb.clone().masked_fill_(pad, 0)          # routed inputs, kept for the weight gradient
-        gu = gu.masked_fill(pad, 0)
-        h = K.swiglu_fwd(gu)
-        K.moe_gemm_scatter(h, group, w_dn, b_major=0, slot_dst=slot, row_weight=w, acc_ptrs=m.acc.ptrs, world=m.world)
-        m.barrier()                                   # every rank has added its experts' outputs
-        y = acc.to(torch.bfloat16)
+        with section("moe.fwd.pointwise"):
+            pad = (slot[:, 0] < 0)[:, None]
+            xs = sb.clone().masked_fill_(pad, 0)          # routed inputs, kept for the weight gradient
+            gu = gu.masked_fill(pad, 0)
+            h = K.swiglu_fwd(gu)
+        with section("moe.fwd.gemm_scatter"):
+            K.moe_gemm_scatter(h, group, w_dn, b_major=0, slot_dst=slot, row_weight=w, acc_ptrs=m.acc.ptrs, world=m.world)
+            m.barrier()                                   # every rank has added its experts' outputs
+            y = acc.to(torch.bfloat16)
         ctx.m = m
-        ctx.save_for_backward(slot, w, group, origin, xs, gu, h, w_gu, w_dn)
+        ctx.save_for_backward(slot, w, group, origin, xs, gu, w_gu, w_dn)
         ctx.meta = (N, d, S, top_w.shape)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         m = ctx.m
-        slot, w, group, origin, xs, gu, h, w_gu, w_dn = ctx.saved_tensors
+        slot, w, group, origin, xs, gu, w_gu, w_dn = ctx.saved_tensors
         N, d, S, tw_shape = ctx.meta
         tok = m.tok.tensor[:N * d].view(N, d)
         acc = m.acc.tensor[:N * d].view(N, d)
-        m.barrier()
-        tok.copy_(dy)
-        acc.zero_()
-        m.barrier()
+        with section("moe.bwd.publish"):
+            m.barrier()
+            tok.copy_(dy)
+            acc.zero_()
+            m.barrier()
         m.epoch += 1
         sb = m.slot_buf[:S * d].view(S, d)
         # dh (unweighted) = dy_slot @ W_down : gather dy rows, B stored [E, K=d, N=F]
-        dh_u = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_dn, b_major=1, slot_buf=sb, flags=m.flags, epoch=m.epoch,
-                                 n_comm=m.n_comm)
-        valid = (slot[:, 0] >= 0)
-        pad = ~valid[:, None]
-        dys = sb.masked_fill(pad, 0)                   # gathered dy rows (padding rows cleared, see forward)
-        dh_u = dh_u.masked_fill(pad, 0)
-        dw_slot = (h.float() * dh_u.float()).sum(-1)
-        dh = (dh_u.float() * w[:, None]).to(torch.bfloat16)
-        hw = (h.float() * w[:, None]).to(torch.bfloat16)
-        dgu = K.swiglu_bwd(gu.clone(), dh, inplace=True).masked_fill_(pad, 0)
+        with section("moe.bwd.gather_gemm"):
+            dh_u = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_dn, b_major=1, slot_buf=sb, flags=m.flags, epoch=m.epoch,
+                                     n_comm=m.n_comm)
+        with section("moe.bwd.pointwise"):
+            pad = (slot[:, 0] < 0)[:, None]
+            dys = sb.masked_fill(pad, 0)                   # gathered dy rows (padding rows cleared, see forward)
+            # gate-weight gradient, weighted h and SwiGLU backward in one pass over the slot rows; padding rows come out 0
+            dgu, hw, dw_slot = K.moe_expert_bwd(gu, dh_u.contiguous(), w.contiguous(), slot)
         # weight gradients per expert on its slot range
-        dwgu, dwdn = torch.zeros_like(w_gu), torch.zeros_like(w_dn)
-        g_cpu = group.tolist()
-        b0 = 0
-        while b0 < len(g_cpu):
-            e = g_cpu[b0]
-            b1 = b0
-            while b1 < len(g_cpu) and g_cpu[b1] == e:
-                b1 += 1
-            r0, r1 = b0 * 128, b1 * 128
-            K.gemm(dgu[r0:r1], xs[r0:r1], a_major=1, b_major=1, out=dwgu[e], accumulate=True)
-            K.gemm(dys[r0:r1], hw[r0:r1], a_major=1, b_major=1, out=dwdn[e], accumulate=True)
-            b0 = b1
+        with section("moe.bwd.wgrad"):
+            dwgu, dwdn = torch.zeros_like(w_gu), torch.zeros_like(w_dn)
+            g_cpu = group.tolist()
+            b0 = 0
+            while b0 < len(g_cpu):
+                e = g_cpu[b0]
+                b1 = b0
+                while b1 < len(g_cpu) and g_cpu[b1] == e:
+                    b1 += 1
+                r0, r1 = b0 * 128, b1 * 128
+                K.gemm(dgu[r0:r1], xs[r0:r1], a_major=1, b_major=1, out=dwgu[e], accumulate=True)
+                K.gemm(dys[r0:r1], hw[r0:r1], a_major=1, b_major=1, out=dwdn[e], accumulate=True)
+                b0 = b1
         # dx: scatter-add dgu_slot @ W_gu into the token owners' accumulators (B stored [E, K=2F, N=d])
-        K.moe_gemm_scatter(dgu, group, w_gu, b_major=1, slot_dst=slot, row_weight=None, acc_ptrs=m.acc.ptrs, world=m.world)
+        with section("moe.bwd.gemm_scatter"):
+            K.moe_gemm_scatter(dgu, group, w_gu, b_major=1, slot_dst=slot, row_weight=None, acc_ptrs=m.acc.ptrs, world=m.world)
         # router gradient: each slot's d(loss)/d(gate weight) goes back to the rank and slot it came from
-        send = torch.stack([origin[:, 0].float(), origin[:, 1].float(), dw_slot], 1)
-        pad = torch.full((m.max_slots, 3), -1.0, device=send.device)
-        pad[:S] = send
-        allg = [torch.empty_like(pad) for _ in range(m.world)]
-        dist.all_gather(allg, pad, group=m.group)
-        allg = torch.cat(allg, 0)
-        mine = allg[:, 0].long() == m.rank
-        dtw = torch.zeros(tw_shape[0] * tw_shape[1], dtype=torch.float32, device=send.device)
-        dtw[allg[mine, 1].long()] = allg[mine, 2]
-        m.barrier()
-        dx = acc.to(torch.bfloat16)
+        with section("moe.bwd.router_grad"):
+            send = torch.stack([origin[:, 0].float(), origin[:, 1].float(), dw_slot], 1)
+            pad = torch.full((m.max_slots, 3), -1.0, device=send.device)
+            pad[:S] = send
+            allg = [torch.empty_like(pad) for _ in range(m.world)]
+            dist.all_gather(allg, pad, group=m.group)
+            allg = torch.cat(allg, 0)
+            mine = allg[:, 0].long() == m.rank
+            dtw = torch.zeros(tw_shape[0] * tw_shape[1], dtype=torch.float32, device=send.device)
+            dtw[allg[mine, 1].long()] = allg[mine, 2]
+            m.barrier()
+            dx = acc.to(torch.bfloat16)
         return None, dx, dtw.view(tw_shape), None, None, dwgu, dwdn

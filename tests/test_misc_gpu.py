@@ -138,3 +138,32 @@ def test_strided_copy_permute_and_cat():
     Kn.strided_copy(a, cat[:, :3])
     Kn.strided_copy(b, cat[:, 3:])
     assert torch.equal(cat, torch.cat([a, b], 1))
+
+
+@pytest.mark.parametrize("S,F", [(384, 512), (130, 5632)])
+def test_moe_expert_bwd_pointwise(S, F):
+    from litetorch_b200.ops import kernels as K
+    torch.manual_seed(2)
+    gu = torch.randn(S, 2 * F, device="cuda").bfloat16()
+    dh_u = torch.randn(S, F, device="cuda").bfloat16()
+    w = torch.rand(S, device="cuda")
+    slot = torch.stack([torch.randint(0, 4, (S,), device="cuda"), torch.arange(S, device="cuda")], 1).int()
+    slot[S // 3::7, 0] = -1                                    # padding slots
+    gu[S // 3::7] = float("nan")                                # whatever is there must not leak out
+    dgu, hw, dw = K.moe_expert_bwd(gu, dh_u, w, slot.contiguous())
+    valid = (slot[:, 0] >= 0)
+    g, u = gu[:, :F].float(), gu[:, F:].float()
+    sg = torch.sigmoid(g)
+    h = (g * sg * u).bfloat16().float()
+    dh = (dh_u.float() * w[:, None]).bfloat16().float()
+    ref_dg = dh * u * (sg + g * sg * (1 - sg))
+    ref_du = dh * g * sg
+    ref = torch.cat([ref_dg, ref_du], 1)
+    ref_hw = h * w[:, None]
+    ref_dw = (h * dh_u.float()).sum(-1)
+    z = ~valid
+    assert not torch.isnan(dgu.float()).any() and not torch.isnan(hw.float()).any() and not torch.isnan(dw).any()
+    assert float(dgu[z].float().abs().max()) == 0 and float(hw[z].float().abs().max()) == 0 and float(dw[z].abs().max()) == 0
+    torch.testing.assert_close(dgu[valid].float(), ref[valid], rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(hw[valid].float(), ref_hw[valid], rtol=2e-2, atol=1e-2)
+    torch.testing.assert_close(dw[valid], ref_dw[valid], rtol=1e-2, atol=5e-2 * F ** 0.5)
