@@ -217,7 +217,44 @@ __global__ void adam_table_kernel(TensorTable tb, int n_chunks, AdamArgs a, cons
     float* v = tb.v[t];
     __nv_bfloat16* p16 = tb.p16 ? tb.p16[t] : nullptr;
     const bool gb = tb.g_is_bf16[t] != 0;
-    for (long long i = off + threadIdx.x; i < end; i += blockDim.x) {
+    // 4 elements per thread per step where every array is 16-byte aligned (chunk offsets are multiples of 4, so this is
+    // a property of the tensors' base addresses); the scalar loop below takes the tail, or everything otherwise
+    long long done_to = off;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                           (reinterpret_cast<uintptr_t>(tb.g[t]) << (gb ? 1 : 0)) |
+                           (p16 ? (reinterpret_cast<uintptr_t>(p16) << 1) : 0);
+    if ((bits & 15u) == 0) {
+      const long long n4 = (end - off) / 4;
+      for (long long q = threadIdx.x; q < n4; q += blockDim.x) {
+        const long long i = off + q * 4;
+        float g[4];
+        if (gb) {
+          const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(tb.g[t]) + i);
+          const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y);
+          g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
+        } else {
+          const float4 u = *reinterpret_cast<const float4*>(static_cast<const float*>(tb.g[t]) + i);
+          g[0] = u.x; g[1] = u.y; g[2] = u.z; g[3] = u.w;
+        }
+        const float4 p4 = *reinterpret_cast<const float4*>(p + i);
+        const float4 m4 = *reinterpret_cast<const float4*>(m + i);
+        const float4 v4 = *reinterpret_cast<const float4*>(v + i);
+        float pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pp[j] = adam_update(pp[j], g[j] * gmul, mm[j], vv[j], a);
+        *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        if (p16) {
+          uint2 o;
+          o.x = pack_bf16x2(pp[0], pp[1]);
+          o.y = pack_bf16x2(pp[2], pp[3]);
+          *reinterpret_cast<uint2*>(p16 + i) = o;
+        }
+      }
+      done_to = off + n4 * 4;
+    }
+    for (long long i = done_to + threadIdx.x; i < end; i += blockDim.x) {
       float g = gb ? __bfloat162float(static_cast<const __nv_bfloat16*>(tb.g[t])[i]) : static_cast<const float*>(tb.g[t])[i];
       g *= gmul;
       float mm = m[i], vv = v[i];

@@ -113,14 +113,14 @@ class _MoEFused(torch.autograd.Function):
         with section("moe.fwd.gather_gemm"):
             gu = K.moe_gather_gemm(m.tok.ptrs, m.world, slot, group, w_gu, b_major=0, slot_buf=sb, flags=m.flags, epoch=m.epoch,
                                    n_comm=m.n_comm)
-        # Padding slots (the tail of every expert's last 128-row block) are never fetched: their rows of the staging
-        # buffer and of everything computed from it are whatever was there before, possibly NaN bit patterns.  Nothing
-        # reads them in the forward (the combine skips them), but the weight-gradient GEMMs sum over all rows of a
-        # block, so they are cleared (0 * NaN is NaN: masked, not multiplied).
+        # Padding slots (the tail of every expert's last 128-row block) carry no token: the gather fills their rows of
+        # the staging buffer from a row of zeros.  Nothing reads them in the forward (the combine skips them), but the
+        # weight-gradient GEMMs sum over all rows of a block, so the saved copy of the routed inputs is cleared there
+        # once more (masked, not multiplied: 0 * NaN is NaN); the rows of gu need no clearing, the backward's pointwise
+        # kernel never reads them.
         with section("moe.fwd.pointwise"):
             pad = (slot[:, 0] < 0)[:, None]
             xs = sb.clone().masked_fill_(pad, 0)          # routed inputs, kept for the weight gradient
-            gu = gu.masked_fill(pad, 0)
             h = K.swiglu_fwd(gu)
         with section("moe.fwd.gemm_scatter"):
             K.moe_gemm_scatter(h, group, w_dn, b_major=0, slot_dst=slot, row_weight=w, acc_ptrs=m.acc.ptrs, world=m.world)
