@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|flash_fwd|flash_bwd|rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
 handful of times and exits, so a capture with `-k regex:<kernel> -c 3` ends by itself in a minute or two.
@@ -66,6 +66,18 @@ def main():
         logits = torch.randn(8192, 32000, device=dev).bfloat16()
         tgt = torch.randint(0, 32000, (8192,), device=dev)
         fn = lambda: K.ce_finish(logits, tgt, K.ce_stats(logits, tgt))
+    elif case == "gemm_rs":
+        # GEMM -> reduce-scatter on a one-rank group: the scatter epilogue and the reduce phase without NVLink
+        import os
+        import torch.distributed as dist
+        from ..parallel.tp_fused import TPFusedContext
+        for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
+            os.environ.setdefault(k, v)
+        dist.init_process_group("nccl", device_id=dev)
+        tp = TPFusedContext(8192, 4096, dev)
+        h = torch.randn(8192, 1792, device=dev).bfloat16()
+        w_row = (torch.randn(4096, 1792, device=dev) * 0.02).bfloat16()
+        fn = lambda: tp.gemm_scatter(h, w_row)
     else:
         raise SystemExit("unknown case " + case)
     for _ in range(reps):
