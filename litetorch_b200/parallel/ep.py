@@ -85,11 +85,16 @@ class MoEFeedForward:
         self.w_gate_up = Tensor(w_gu[sl].clone().to(device=device, dtype=dtype).requires_grad_(True))
         self.w_down = Tensor(w_dn[sl].clone().to(device=device, dtype=dtype).requires_grad_(True))
         self.last_aux_loss: Optional[torch.Tensor] = None
-        self.last_dropped = 0
+        self._dropped = 0
         self.training = True
 
     def parameters(self):
         return [self.gate_weight, self.w_gate_up, self.w_down]
+
+    @property
+    def last_dropped(self) -> int:
+        """Slots cut by the capacity limit in the last forward pass."""
+        return int(self._dropped)
 
     def route(self, x2: torch.Tensor):
         """fp32 router. Returns (weights [N,k], experts [N,k], keep mask [N,k], aux loss)."""
@@ -119,7 +124,7 @@ class MoEFeedForward:
         W = _world(self.group)
         top_w, top_i, keep, aux = self.route(x2)
         self.last_aux_loss = aux * self.aux_loss_coef
-        self.last_dropped = int((~keep).sum())
+        self._dropped = (~keep).sum()                 # read lazily: no host sync in the step
         # slots that survive the capacity cut, sorted by expert (hence by destination rank)
         slot_tok = torch.arange(N, device=x2.device).repeat_interleave(self.k)[keep.reshape(-1)]
         slot_exp = top_i.reshape(-1)[keep.reshape(-1)]

@@ -56,18 +56,26 @@ class MoEFusedFeedForward(MoEFeedForward):
         dist.all_gather(allm, meta.contiguous(), group=self.group)
         allm = torch.stack(allm, 0)                                        # [W, N*k, 3]
         e = allm[:, :, 0].long()
+        NK = e.shape[1]
         mine = (e >= self.first) & (e < self.first + self.local_E)
-        src_rank, flat = mine.nonzero(as_tuple=True)
-        le = e[src_rank, flat] - self.first
-        order = torch.argsort(le, stable=True)
-        src_rank, flat, le = src_rank[order], flat[order], le[order]
-        counts = torch.bincount(le, minlength=self.local_E)
-        padded = (counts + 127) // 128 * 128
-        starts = torch.cumsum(padded, 0) - padded
-        S = int(padded.sum().item())
-        S = max(S, 128)
+        # local expert of every slot of every rank, `local_E` for slots routed elsewhere (they sort last)
+        le_all = torch.where(mine, e - self.first, torch.full_like(e, self.local_E)).reshape(-1)
+        counts_cpu = torch.bincount(le_all, minlength=self.local_E + 1)[:self.local_E].tolist()   # the layer's one host sync
+        n_mine = sum(counts_cpu)
+        order = torch.argsort(le_all, stable=True)[:n_mine]        # grouped by expert, (source rank, slot) order inside
+        src_rank, flat, le = order // NK, order % NK, le_all[order]
+        padded_cpu = [(c + 127) // 128 * 128 for c in counts_cpu]
+        starts_cpu, excl_cpu, acc_p, acc_c = [], [], 0, 0
+        for c, pc in zip(counts_cpu, padded_cpu):
+            starts_cpu.append(acc_p)
+            excl_cpu.append(acc_c)
+            acc_p += pc
+            acc_c += c
+        S = max(acc_p, 128)
         assert S <= self.max_slots, "more routed tokens than the slot buffer holds"
-        pos = starts[le] + (torch.arange(le.numel(), device=dev) - (torch.cumsum(counts, 0) - counts)[le])
+        starts = torch.tensor(starts_cpu, dtype=torch.int64, device=dev)
+        excl = torch.tensor(excl_cpu, dtype=torch.int64, device=dev)
+        pos = starts[le] + (torch.arange(n_mine, device=dev) - excl[le])
         slot = torch.full((S, 2), -1, dtype=torch.int32, device=dev)
         slot[pos, 0] = src_rank.int()
         slot[pos, 1] = allm[src_rank, flat, 1].int()
@@ -76,9 +84,11 @@ class MoEFusedFeedForward(MoEFeedForward):
         origin = torch.full((S, 2), -1, dtype=torch.int64, device=dev)    # (source rank, flat slot index n*k+j)
         origin[pos, 0] = src_rank
         origin[pos, 1] = flat
-        nblk = S // 128
-        blk_start = torch.arange(nblk, device=dev) * 128
-        group = (torch.searchsorted((starts + padded).contiguous(), blk_start, right=True)).clamp(max=self.local_E - 1).int()
+        # expert of every 128-row block: the first expert whose padded range ends beyond the block's first row
+        ends_cpu = [st + pc for st, pc in zip(starts_cpu, padded_cpu)]
+        group_cpu = [min(sum(1 for en in ends_cpu if en <= b * 128), self.local_E - 1) for b in range(S // 128)]
+        group = torch.tensor(group_cpu, dtype=torch.int32, device=dev)
+        self._group_cpu = group_cpu
         return slot.contiguous(), w, group.contiguous(), origin, S
 
     def forward(self, x: Tensor) -> Tensor:
@@ -88,7 +98,7 @@ class MoEFusedFeedForward(MoEFeedForward):
         with section("moe.route"):
             top_w, top_i, keep, aux = self.route(x2)
         self.last_aux_loss = aux * self.aux_loss_coef
-        self.last_dropped = int((~keep).sum())
+        self._dropped = (~keep).sum()                 # read lazily: no host sync in the step
         y = _MoEFused.apply(self, x2, top_w, top_i, keep, _unwrap(self.w_gate_up), _unwrap(self.w_down))
         return Tensor(y.view(shape))
 
@@ -127,6 +137,7 @@ class _MoEFused(torch.autograd.Function):
             m.barrier()                                   # every rank has added its experts' outputs
             y = acc.to(torch.bfloat16)
         ctx.m = m
+        ctx.group_cpu = m._group_cpu
         ctx.save_for_backward(slot, w, group, origin, xs, gu, w_gu, w_dn)
         ctx.meta = (N, d, S, top_w.shape)
         return y
@@ -157,7 +168,7 @@ class _MoEFused(torch.autograd.Function):
         # weight gradients per expert on its slot range
         with section("moe.bwd.wgrad"):
             dwgu, dwdn = torch.zeros_like(w_gu), torch.zeros_like(w_dn)
-            g_cpu = group.tolist()
+            g_cpu = ctx.group_cpu
             b0 = 0
             while b0 < len(g_cpu):
                 e = g_cpu[b0]

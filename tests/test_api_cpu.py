@@ -373,3 +373,27 @@ def test_functional_fallbacks_softmax_dropout_router_fp8_linear():
     cos = torch.cos(torch.arange(16)[:, None] * torch.ones(16)[None, :] * 0.1)
     sin = torch.sin(torch.arange(16)[:, None] * torch.ones(16)[None, :] * 0.1)
     torch.testing.assert_close(Fn.rope_bthd(q, cos, sin), Fn.rope(q.transpose(1, 2), cos, sin).transpose(1, 2))
+
+
+def test_moe_capacity_positions_and_section_timer():
+    """The router's capacity cut keeps, per expert, the first `cap` slots in token order (the sort-based position equals
+    a running count per expert), and the section timer is inert without a GPU."""
+    import math
+    from litetorch_b200.parallel.ep import MoEFeedForward
+    from litetorch_b200.utils import sections
+    torch.manual_seed(4)
+    moe = MoEFeedForward(16, 32, 4, top_k=2, capacity_factor=0.6, device="cpu", dtype=torch.float32)
+    x = torch.randn(50, 16)
+    top_w, top_i, keep, aux = moe.route(x)
+    cap = max(1, int(math.ceil(0.6 * 50 * 2 / 4)))
+    seen = [0, 0, 0, 0]
+    ref = torch.zeros_like(keep)
+    for n in range(50):
+        for j in range(2):
+            e = int(top_i[n, j])
+            ref[n, j] = seen[e] < cap
+            seen[e] += 1
+    assert torch.equal(keep, ref) and not bool(keep.all()) and float(aux) > 0
+    with sections.section("x"):
+        pass
+    assert sections.report() == {} or not torch.cuda.is_available()
