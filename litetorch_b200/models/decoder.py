@@ -77,9 +77,16 @@ class ParallelDims:
     `None` means that axis has size one.  `tp_fused` / `cp_fused` are the symmetric-memory contexts of the fused
     kernels (None: plain collectives)."""
 
-    def __init__(self, tp=None, cp=None, ep=None, dp=None, pp=None, tp_fused=None, cp_fused=None, zigzag=True, fp8=False):
+    def __init__(self, tp=None, cp=None, ep=None, dp=None, pp=None, tp_fused=None, cp_fused=None, zigzag=True, fp8=False,
+                 cp_mode="ring"):
         self.tp, self.cp, self.ep, self.dp, self.pp = tp, cp, ep, dp, pp
         self.tp_fused, self.cp_fused, self.zigzag = tp_fused, cp_fused, zigzag
+        # "ring": KV blocks of all context-parallel ranks walked by the attention kernels (zigzag split);
+        # "ulysses": sequence <-> head all-to-all around a local full-sequence attention (contiguous split)
+        assert cp_mode in ("ring", "ulysses")
+        self.cp_mode = cp_mode
+        if cp_mode == "ulysses":
+            self.zigzag = False
         self.fp8 = fp8      # e4m3 GEMMs (1x128 / 128x128 block scales) in the parallel linears; collectives stay NCCL
 
     @property
@@ -185,7 +192,10 @@ class DecoderBlock:
             k = Fn.rope_bthd(k, cos, sin).contiguous()
             v = v.contiguous()
         with section("blk.fwd.attention"):
-            if dims.cp_world > 1:
+            if dims.cp_world > 1 and dims.cp_mode == "ulysses":
+                from ..parallel.ulysses import ulysses_attention
+                a = ulysses_attention(q, k, v, dims.cp, causal=True)
+            elif dims.cp_world > 1:
                 if dims.cp_fused is not None:
                     a = dims.cp_fused.attention(q, k, v, causal=True)
                 else:

@@ -21,9 +21,10 @@ def test_tp_sp_and_cp_match_single_rank(tmp_path):
         ids = torch.randint(0, cfg.vocab, (2, 129))
         x, y = ids[:, :-1], ids[:, 1:]
         out = {}
-        for mode in ("tp", "cp"):
+        for mode in ("tp", "cp", "ulysses"):
             grp = dist.group.WORLD
-            dims = ParallelDims(tp=grp if mode == "tp" else None, cp=grp if mode == "cp" else None, zigzag=True)
+            dims = ParallelDims(tp=grp if mode == "tp" else None, cp=grp if mode != "tp" else None, zigzag=True,
+                                cp_mode="ulysses" if mode == "ulysses" else "ring")
             m = ParallelDecoder(cfg, dims, device="cpu", dtype=torch.float32, seed=3)
             loss = m.forward_loss(shard_batch(x, dims), shard_batch(y, dims))
             loss.backward()
@@ -55,13 +56,13 @@ def test_tp_sp_and_cp_match_single_rank(tmp_path):
             ref_loss = ref.forward_loss(x, y)
             ref_loss.backward()
             lv = loss.detach().clone()
-            if mode == "cp":
+            if mode != "tp":
                 dist.all_reduce(lv); lv /= world       # every rank holds the mean over its own tokens
             # gradients of replicated parameters must agree with the single-rank model
             g_err = max(float((a.grad - b.grad).abs().max() / (b.grad.abs().max() + 1e-12))
                         for a, b in [(m.embed, ref.embed), (m.blocks[0].norm1, ref.blocks[0].norm1),
                                      (m.blocks[1].norm2, ref.blocks[1].norm2), (m.final_norm, ref.final_norm)])
-            if mode == "cp":
+            if mode != "tp":
                 g_err = max(g_err, float((m.blocks[0].wqkv.grad - ref.blocks[0].wqkv.grad).abs().max()
                                          / ref.blocks[0].wqkv.grad.abs().max()))
             else:
@@ -71,7 +72,7 @@ def test_tp_sp_and_cp_match_single_rank(tmp_path):
             out[mode] = [float(lv), float(ref_loss), g_err]
         done(**out)
     ''', nproc=2, port=29841, tmp_path=tmp_path, timeout=600)
-    for mode in ("tp", "cp"):
+    for mode in ("tp", "cp", "ulysses"):
         loss, ref, g_err = res[mode]
         assert abs(loss - ref) < 2e-4 * abs(ref), (mode, loss, ref)
         assert g_err < 2e-3, (mode, g_err)
