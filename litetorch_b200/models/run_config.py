@@ -80,6 +80,8 @@ def main():
     ap.add_argument("--fp8", action="store_true", help="e4m3 GEMMs with 1x128 / 128x128 block scales (NCCL collectives)")
     ap.add_argument("--layout", default="", help="hybrid only: tp,cp,pp sizes (e.g. 1,2,2) instead of the default for the world size")
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per step (default: the layout's)")
+    ap.add_argument("--cp-mode", choices=["ring", "ulysses"], default="ring",
+                    help="context parallelism: all-ranks ring attention (zigzag split) or Ulysses all-to-all (contiguous split)")
     args = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -123,14 +125,14 @@ def main():
     ep_group = dist.group.WORLD if (args.config == "ep8" and world > 1) else None
 
     dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], ep=ep_group, dp=groups["dp"], pp=groups["pp"], zigzag=True,
-                        fp8=args.fp8 and cuda)
+                        fp8=args.fp8 and cuda, cp_mode=args.cp_mode)
     T_local = seq // dims.cp_world
     hq_l, hkv_l = cfg.n_q // dims.tp_world, cfg.n_kv // dims.tp_world
     if fused and dims.tp is not None:
         from ..parallel.tp_fused import TPFusedContext
         # gathered inputs and scattered outputs of the parallel linears are all d_model wide
         dims.tp_fused = TPFusedContext(n_seq * T_local, cfg.d_model, dev, group=dims.tp)
-    if fused and dims.cp is not None:
+    if fused and dims.cp is not None and dims.cp_mode == "ring":
         from ..parallel.cp import RingFlashContext
         dims.cp_fused = RingFlashContext(n_seq, T_local, hq_l, hkv_l, cfg.head_dim, dev, group=dims.cp, zigzag=True)
 
