@@ -11,6 +11,7 @@ of its example trainers (train_cat_dog.py:312-319).
 from __future__ import annotations
 
 import os
+import time
 from typing import Optional
 
 import torch
@@ -40,6 +41,23 @@ class Trainer:
         self._tgt = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._metrics, self._step_no, self._last_t = None, 0, None
+
+    @classmethod
+    def from_config(cls, run, **kw) -> "Trainer":
+        """Build the trainer of a `config.RunConfig` (a preset name or JSON path is loaded first).  This entry point
+        covers the data-parallel / ZeRO-3 layouts of the hand-scheduled Llama engine; layouts with tensor, context,
+        expert or pipeline parallelism run through `models/run_config.py`."""
+        from . import config as _config
+        if isinstance(run, str):
+            run = _config.load(run)
+        p = run.parallel
+        if p.tp * p.pp * p.cp * max(p.ep, 1) != 1:
+            raise ValueError("Trainer.from_config runs dp / ZeRO-3 layouts; use models.run_config for tp/pp/cp/ep")
+        o = run.optim
+        return cls(run.llama_config(), lr=o.lr, betas=(o.beta1, o.beta2), eps=o.eps, weight_decay=o.weight_decay,
+                   seed=run.seed, activation_checkpointing=run.activation_checkpointing,
+                   parallel="fsdp" if p.zero_stage >= 1 else "none", **kw)
 
     def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Batch already on the device; returns the loss as a device scalar (no host sync)."""
@@ -55,4 +73,18 @@ class Trainer:
         loss = self.engine.train_step(self._tok, self._tgt)
         out = loss.float().cpu()
         self.d2h_bytes = out.numel() * out.element_size()
+        if self._metrics is not None:
+            now = time.perf_counter()
+            self._step_no += 1
+            rec = {"step": self._step_no, "loss": float(out)}
+            if self._last_t is not None:          # host time between two loss read-backs = one full step
+                ms = (now - self._last_t) * 1e3
+                rec.update(step_ms=round(ms, 3), tokens_per_s=round(tokens_cpu.numel() * self.world_size / ms * 1e3, 1))
+            self._last_t = now
+            self._metrics.write(**rec)
         return float(out)
+
+    def log_metrics(self, path: str) -> None:
+        """Append one JSON line per `step` (step, loss, step_ms, tokens_per_s, allocator high-water mark) to `path`."""
+        from .utils.logging import MetricsWriter
+        self._metrics = MetricsWriter(path)

@@ -3,7 +3,8 @@
     LT_SECTIONS=1 python -m torch.distributed.run ... -m litetorch_b200.models.run_config --config ep8
 
 Code brackets a region with `with section("moe.route"):`; when the environment variable is unset the context manager
-does nothing.  `report()` synchronises once, sums the event pairs per name and returns {name: (calls, total ms)};
+does nothing.  With `LT_NVTX=1` every section also opens an NVTX range of the same name, so the fused paths show up
+by name on a timeline profiler.  `report()` synchronises once, sums the event pairs per name and returns {name: (calls, total ms)};
 `run_config` prints it from rank 0 after the timed steps.  Sections on the same stream may nest; the times of nested
 sections are included in their parents.
 """
@@ -16,6 +17,7 @@ from collections import defaultdict
 import torch
 
 _ENABLED = os.environ.get("LT_SECTIONS", "") not in ("", "0")
+_NVTX = os.environ.get("LT_NVTX", "") not in ("", "0")
 _events = defaultdict(list)
 
 
@@ -25,8 +27,15 @@ def enabled() -> bool:
 
 @contextlib.contextmanager
 def section(name: str):
+    nvtx = _NVTX and torch.cuda.is_available()
+    if nvtx:
+        torch.cuda.nvtx.range_push(name)
     if not enabled():
-        yield
+        try:
+            yield
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -35,6 +44,8 @@ def section(name: str):
     finally:
         e1.record()
         _events[name].append((e0, e1))
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
 
 
 def reset() -> None:

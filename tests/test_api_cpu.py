@@ -397,3 +397,50 @@ def test_moe_capacity_positions_and_section_timer():
     with sections.section("x"):
         pass
     assert sections.report() == {} or not torch.cuda.is_available()
+
+
+def test_run_config_presets_json_and_env(tmp_path):
+    from litetorch_b200 import config as C
+    assert set(C.PRESETS) == {"gpt-cpu", "llama-1.1b-fsdp", "llama3-8b-tp8", "llama3-8b-tp8-fp8", "moe-8x2b-ep8",
+                              "llama-3b-long-hybrid"}
+    hy = C.load("llama-3b-long-hybrid", env={})
+    assert hy.mesh_sizes(8) == {"dp": 1, "tp": 2, "pp": 2, "cp": 2, "ep": 1} and hy.tokens_per_step(8) == 8 * 32768
+    assert C.load("llama-1.1b-fsdp", env={}).tokens_per_step(8) == 8 * 4 * 2048
+    assert C.load("llama3-8b-tp8-fp8", env={}).precision == "fp8"
+    with pytest.raises(ValueError):
+        hy.mesh_sizes(4)
+    # JSON round trip, unknown fields refused
+    path = str(tmp_path / "job.json")
+    hy.to_json(path)
+    again = C.load(path, env={})
+    assert again.to_dict() == hy.to_dict()
+    with pytest.raises(KeyError):
+        C.RunConfig.from_dict({"model": {"n_layer": 3}})
+    # environment overrides: top-level field and SECTION__FIELD, typed by the field's default
+    env = {"LT_CFG_SEQ_LEN": "4096", "LT_CFG_PARALLEL__TP": "4", "LT_CFG_ACTIVATION_CHECKPOINTING": "true",
+           "LT_CFG_OPTIM__LR": "1e-4", "UNRELATED": "x"}
+    c = C.load("llama-1.1b-fsdp", env=env)
+    assert c.seq_len == 4096 and c.parallel.tp == 4 and c.activation_checkpointing is True and c.optim.lr == 1e-4
+    with pytest.raises(KeyError):
+        C.load("llama-1.1b-fsdp", env={"LT_CFG_PARALLEL__NOPE": "1"})
+    d = c.decoder_config()
+    assert (d.n_layers, d.d_model, d.n_q, d.n_kv) == (22, 2048, 32, 4)
+    assert C.load("llama-1.1b-fsdp", env={}).llama_config().num_params() > 1.0e9
+
+
+def test_logger_and_metrics_writer(tmp_path):
+    import io
+    import json as _json
+    from litetorch_b200.utils.logging import MetricsWriter, get_logger
+    buf = io.StringIO()
+    log = get_logger("lt-test", level="WARNING", stream=buf)
+    log.info("hidden")
+    log.warning("shown %d", 7)
+    out = buf.getvalue()
+    assert "hidden" not in out and "shown 7" in out and out.startswith("[rank 0]")
+    path = str(tmp_path / "m.jsonl")
+    with MetricsWriter(path) as mw:
+        mw.write(step=1, loss=2.5, tokens_per_s=1000.0)
+        mw.write(step=2, loss=2.25, tokens_per_s=1100.0, exposed_comm_ms=0.5)
+    recs = [_json.loads(l) for l in open(path)]
+    assert [r["step"] for r in recs] == [1, 2] and recs[1]["exposed_comm_ms"] == 0.5 and recs[0]["rank"] == 0

@@ -54,3 +54,22 @@ def test_trainer_public_api_host_batches():
     l = tr.step(tok, tgt)
     assert l == l and 4.0 < l < 8.0
     assert tr.h2d_bytes == 2 * 2 * 128 * 8 and tr.d2h_bytes == 4
+
+
+def test_trainer_from_config_and_metrics_log(tmp_path):
+    import json
+    from litetorch_b200 import config as C
+    from litetorch_b200.trainer import Trainer
+    run = C.load("llama-1.1b-fsdp", env={"LT_CFG_MODEL__N_LAYERS": "2", "LT_CFG_MODEL__D_MODEL": "256", "LT_CFG_MODEL__N_Q": "4",
+                                         "LT_CFG_MODEL__N_KV": "2", "LT_CFG_MODEL__FFN": "512", "LT_CFG_MODEL__VOCAB": "512",
+                                         "LT_CFG_SEQ_LEN": "128"})
+    tr = Trainer.from_config(run, device="cuda:0")
+    path = str(tmp_path / "metrics.jsonl")
+    tr.log_metrics(path)
+    tok = torch.randint(0, 512, (2, 128)).pin_memory()
+    tgt = torch.roll(tok, -1, 1).pin_memory()
+    losses = [tr.step(tok, tgt) for _ in range(3)]
+    recs = [json.loads(l) for l in open(path)]
+    assert [r["step"] for r in recs] == [1, 2, 3] and abs(recs[2]["loss"] - losses[2]) < 1e-6
+    assert recs[1]["tokens_per_s"] > 0 and recs[1]["max_memory_allocated_mb"] > 0
+    assert losses[2] < losses[0]
