@@ -39,24 +39,60 @@ def ensure_process_group():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
 
+_CANARY_BYTES = 256          # guard area in front of and behind every symmetric buffer
+_CANARY_VALUE = 0x5A
+_live_buffers = []           # weak references, for check_symmetric_canaries()
+
+
 class SymmetricBuffer:
-    """A tensor allocated at the same offset on every rank, with every rank's device pointer to it."""
+    """A tensor allocated at the same offset on every rank, with every rank's device pointer to it.
+
+    The allocation carries a 256-byte guard area on both sides filled with a fixed byte; peers write into these buffers
+    from inside kernels, and `check()` (or `check_symmetric_canaries()` over all live buffers) tells whether anything
+    wrote past either end."""
 
     def __init__(self, numel: int, dtype, device, group=None):
+        import weakref
         import torch.distributed._symmetric_memory as symm_mem
         group = group or dist.group.WORLD
-        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
-        self.tensor.zero_()
-        self.handle = symm_mem.rendezvous(self.tensor, group=group.group_name if hasattr(group, "group_name") else group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        guard = _CANARY_BYTES // itemsize
+        self._raw = symm_mem.empty(numel + 2 * guard, dtype=dtype, device=device)
+        self._raw.zero_()
+        self._guards = (self._raw[:guard].view(torch.uint8), self._raw[guard + numel:].view(torch.uint8))
+        for g in self._guards:
+            g.fill_(_CANARY_VALUE)
+        self.tensor = self._raw[guard:guard + numel]
+        self.handle = symm_mem.rendezvous(self._raw, group=group.group_name if hasattr(group, "group_name") else group)
+        self.ptrs = [int(p) + _CANARY_BYTES for p in self.handle.buffer_ptrs]
         try:
-            self.mc_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(device.type, device.index) else 0
+            self.mc_ptr = (int(self.handle.multicast_ptr) + _CANARY_BYTES
+                           if self.handle.has_multicast_support(device.type, device.index) else 0)
         except Exception:
             self.mc_ptr = 0
         self.itemsize = self.tensor.element_size()
+        _live_buffers.append(weakref.ref(self))
 
     def peer_ptrs(self, elem_offset: int = 0) -> List[int]:
         return [p + elem_offset * self.itemsize for p in self.ptrs]
+
+    def check(self) -> bool:
+        """True when both guard areas of this rank's copy still hold the canary byte (synchronises the device)."""
+        return all(bool((g == _CANARY_VALUE).all()) for g in self._guards)
+
+
+def check_symmetric_canaries() -> int:
+    """Number of live symmetric buffers of this rank whose guard areas were overwritten."""
+    bad, keep = 0, []
+    for ref in _live_buffers:
+        buf = ref()
+        if buf is None:
+            continue
+        keep.append(ref)
+        if not buf.check():
+            bad += 1
+    _live_buffers[:] = keep
+    return bad
 
 
 _STAGE_KEYS = ("wqkv", "wo", "w_gu", "w_down", "lm_head")

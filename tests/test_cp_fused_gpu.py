@@ -48,7 +48,8 @@ for (D, zig, causal, direct) in [(64, True, True, False), (128, True, True, Fals
     errs = [rel(o, sp(of.detach())), rel(ql.grad, sp(qf.grad)), rel(kl.grad, sp(kf.grad)), rel(vl.grad, sp(vf.grad))]
     worst = max(worst, max(errs))
 torch.cuda.synchronize()
-t = torch.tensor([worst, float(K.status_fetch())], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+from litetorch_b200.parallel.fsdp import check_symmetric_canaries
+t = torch.tensor([worst, float(K.status_fetch()) + 1000.0 * check_symmetric_canaries()], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
 if rank == 0:
     print("RESULT " + json.dumps({"worst_rel_err": t[0].item(), "status": t[1].item()}))
 dist.barrier(); dist.destroy_process_group()

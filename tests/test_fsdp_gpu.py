@@ -43,7 +43,8 @@ for step in range(3):
     ref.optimizer_step()
     ref_losses.append(float(l))
 torch.cuda.synchronize()
-status = K.status_fetch()
+from litetorch_b200.parallel.fsdp import check_symmetric_canaries
+status = K.status_fetch() + 1000 * check_symmetric_canaries()
 err = 0.0
 for s in w.specs:
     a = w.gather_full_master(s.name).float().view(-1)

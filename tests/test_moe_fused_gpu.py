@@ -43,7 +43,8 @@ for it in range(3):
     worst = max([worst] + [rel(a, b) for a, b in zip(outs[1], outs[0])])
     assert fus.last_dropped == ref.last_dropped
 torch.cuda.synchronize()
-t = torch.tensor([worst, float(K.status_fetch())], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+from litetorch_b200.parallel.fsdp import check_symmetric_canaries
+t = torch.tensor([worst, float(K.status_fetch()) + 1000.0 * check_symmetric_canaries()], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
 if rank == 0:
     print("RESULT " + json.dumps({"worst_rel_err": t[0].item(), "status": t[1].item(), "dropped": fus.last_dropped}))
 dist.barrier(); dist.destroy_process_group()

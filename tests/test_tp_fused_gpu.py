@@ -53,7 +53,8 @@ worst = 0.0
 for it in range(3):
     for a, b in zip(outs[(True, it)], outs[(False, it)]):
         worst = max(worst, rel(a, b))
-t = torch.tensor([worst, float(K.status_fetch())], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+from litetorch_b200.parallel.fsdp import check_symmetric_canaries
+t = torch.tensor([worst, float(K.status_fetch()) + 1000.0 * check_symmetric_canaries()], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
 if rank == 0:
     print("RESULT " + json.dumps({"worst_rel_err": t[0].item(), "status": t[1].item()}))
 dist.barrier(); dist.destroy_process_group()
@@ -123,7 +124,8 @@ for it in range(3):
         dist.all_gather(parts, dy)
         worst = max(worst, rel(dx, K.gemm(torch.cat(parts, 0), w2, b_major=1)))
 torch.cuda.synchronize()
-t = torch.tensor([worst, float(K.status_fetch())], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+from litetorch_b200.parallel.fsdp import check_symmetric_canaries
+t = torch.tensor([worst, float(K.status_fetch()) + 1000.0 * check_symmetric_canaries()], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
 if rank == 0:
     print("RESULT " + json.dumps({"worst_rel_err": t[0].item(), "status": t[1].item()}))
 dist.barrier(); dist.destroy_process_group()
