@@ -6,6 +6,7 @@
 #include <condition_variable>
 #include <cstdint>
 #include <functional>
+#include <memory>
 #include <mutex>
 #include <queue>
 #include <thread>
@@ -63,25 +64,32 @@ void lt_parallel_for(void* fn_ptr, void* ctx, uint64_t n, uint64_t min_parallel)
   const uint64_t nthreads = p.workers.size() + 1;
   if (n < (min_parallel ? min_parallel : 50000) || nthreads == 1) { fn(0, n, ctx); return; }
   const uint64_t chunk = (n + nthreads - 1) / nthreads;
-  std::atomic<uint64_t> pending{0};
-  std::mutex done_mu;
-  std::condition_variable done_cv;
+  // Completion state shared with the tasks: it lives on the heap and every task holds a reference, so a worker that is
+  // still inside its notification when the caller wakes up never touches a destroyed mutex (the counter is changed and
+  // read under the mutex for the same reason).
+  struct Done {
+    std::mutex mu;
+    std::condition_variable cv;
+    uint64_t pending = 0;
+  };
+  auto done = std::make_shared<Done>();
   uint64_t begin = 0;
   std::vector<std::pair<uint64_t, uint64_t>> ranges;
   while (begin < n) { ranges.push_back({begin, std::min(n, begin + chunk)}); begin += chunk; }
-  pending = ranges.size() - 1;
+  done->pending = ranges.size() - 1;
   for (size_t i = 0; i + 1 < ranges.size(); ++i) {
     auto r = ranges[i];
     std::lock_guard<std::mutex> lk(p.mu);
-    p.tasks.push([=, &pending, &done_mu, &done_cv] {
+    p.tasks.push([=] {
       fn(r.first, r.second, ctx);
-      if (pending.fetch_sub(1) == 1) { std::lock_guard<std::mutex> lk2(done_mu); done_cv.notify_all(); }
+      std::lock_guard<std::mutex> lk2(done->mu);
+      if (--done->pending == 0) done->cv.notify_all();
     });
   }
   p.cv.notify_all();
   fn(ranges.back().first, ranges.back().second, ctx);
-  std::unique_lock<std::mutex> lk(done_mu);
-  done_cv.wait(lk, [&] { return pending.load() == 0; });
+  std::unique_lock<std::mutex> lk(done->mu);
+  done->cv.wait(lk, [&] { return done->pending == 0; });
 }
 
 }  // extern "C"
