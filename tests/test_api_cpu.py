@@ -444,3 +444,17 @@ def test_logger_and_metrics_writer(tmp_path):
         mw.write(step=2, loss=2.25, tokens_per_s=1100.0, exposed_comm_ms=0.5)
     recs = [_json.loads(l) for l in open(path)]
     assert [r["step"] for r in recs] == [1, 2] and recs[1]["exposed_comm_ms"] == 0.5 and recs[0]["rank"] == 0
+
+
+def test_vit_trains_on_synthetic_images():
+    from litetorch_b200.models.vit import ViT, ViTConfig, synthetic_images, train
+    cfg = ViTConfig()
+    model = ViT(cfg)
+    x, y = synthetic_images(8, cfg)
+    logits = model(lt.Tensor(x))
+    assert logits.shape == [8, 2]
+    lt.Ops.cross_entropy_loss(logits, lt.Tensor(y)).backward()
+    assert all(p.grad is not None for p in model.parameters())
+    assert any(p is model.pos for p in model.parameters())
+    out = train(epochs=3, images=128, verbose=False)
+    assert out["loss"][-1] < 0.5 * out["loss"][0] and out["accuracy"][-1] > 0.9 and out["inference_ms_per_image"] > 0
