@@ -88,3 +88,56 @@ def test_benchmark_layouts_run_on_small_shapes(config, nproc, extra):
     d = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert d["n_gpus"] == nproc and d["tokens_per_s"] > 0
     assert 4.0 < d["loss"] < 8.0          # ln(512) = 6.24 at initialisation
+
+
+def test_tp2_x_cp2_on_four_ranks_matches_single_rank(tmp_path):
+    """Tensor + sequence parallelism inside context parallelism (the two inner axes of the hybrid layout): loss and
+    gradients of sharded and replicated parameters equal the single-rank model."""
+    res = run_ranks('''
+        from litetorch_b200.models.decoder import PRESETS, ParallelDecoder, ParallelDims, shard_batch
+        from litetorch_b200.models.run_config import _make_groups
+        cfg = PRESETS["tiny-dense"]
+        torch.manual_seed(0)
+        ids = torch.randint(0, cfg.vocab, (2, 129))
+        x, y = ids[:, :-1], ids[:, 1:]
+        groups, _ = _make_groups(world, rank, 2, 2, 1, 1)
+        dims = ParallelDims(tp=groups["tp"], cp=groups["cp"], zigzag=True)
+        m = ParallelDecoder(cfg, dims, device="cpu", dtype=torch.float32, seed=3)
+        loss = m.forward_loss(shard_batch(x, dims), shard_batch(y, dims))
+        loss.backward()
+        m.reduce_gradients()
+        ref = ParallelDecoder(cfg, ParallelDims(), device="cpu", dtype=torch.float32, seed=3)
+        tpw = 2
+        def gather(t, dim):
+            parts = [torch.empty_like(t) for _ in range(tpw)]
+            dist.all_gather(parts, t.detach().contiguous(), group=groups["tp"])
+            return parts if dim is None else torch.cat(parts, dim)
+        with torch.no_grad():
+            D = cfg.head_dim
+            for b, rb in zip(m.blocks, ref.blocks):
+                parts = gather(b.wqkv, None)
+                q = torch.cat([p[:b.hq * D] for p in parts]); k = torch.cat([p[b.hq * D:(b.hq + b.hkv) * D] for p in parts])
+                v = torch.cat([p[(b.hq + b.hkv) * D:] for p in parts])
+                rb.wqkv.copy_(torch.cat([q, k, v]))
+                rb.wo.copy_(gather(b.wo, 1))
+                F = cfg.ffn // tpw
+                gu = gather(b.w_gu, None)
+                rb.w_gu.copy_(torch.cat([torch.cat([p[:F] for p in gu]), torch.cat([p[F:] for p in gu])]))
+                rb.w_dn.copy_(gather(b.w_dn, 1))
+            ref.head.copy_(gather(m.head, 0))
+            ref.embed.copy_(m.embed)
+        ref_loss = ref.forward_loss(x, y)
+        ref_loss.backward()
+        lv = loss.detach().clone()
+        dist.all_reduce(lv, group=groups["cp"]); lv /= 2      # every context-parallel rank holds the mean over its tokens
+        g_err = max(float((a.grad - b.grad).abs().max() / (b.grad.abs().max() + 1e-12))
+                    for a, b in [(m.embed, ref.embed), (m.blocks[0].norm1, ref.blocks[0].norm1),
+                                 (m.blocks[1].norm2, ref.blocks[1].norm2), (m.final_norm, ref.final_norm)])
+        F = cfg.ffn // tpw
+        tr = dist.get_rank(groups["tp"])
+        mine = ref.blocks[1].w_dn.grad[:, tr * F:(tr + 1) * F]
+        g_err = max(g_err, float((m.blocks[1].w_dn.grad - mine).abs().max() / mine.abs().max()))
+        done(loss=float(lv), ref=float(ref_loss), g_err=g_err)
+    ''', nproc=4, port=29861, tmp_path=tmp_path, timeout=600)
+    assert abs(res["loss"] - res["ref"]) < 2e-4 * abs(res["ref"]), res
+    assert res["g_err"] < 2e-3, res
