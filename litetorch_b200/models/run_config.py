@@ -207,6 +207,12 @@ def main():
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     # the last pipeline stage holds the loss (0.0 elsewhere); a NaN must not be hidden by the maximum
     lv = torch.nan_to_num(last.float().reshape(1).clone(), nan=float("inf"))
+    # every rank's loss is the mean over its own tokens: average over the ranks that hold other tokens of the same step
+    # (context- and data-parallel groups; all ranks in the expert-parallel layout), then take the last stage's value
+    for g in ([dist.group.WORLD] if (args.config == "ep8" and world > 1) else [groups["cp"], groups["dp"]]):
+        if g is not None and dist.get_world_size(g) > 1:
+            dist.all_reduce(lv, group=g)
+            lv /= dist.get_world_size(g)
     dist.all_reduce(lv, op=dist.ReduceOp.MAX)
     dp_like = world if args.config == "ep8" else (dist.get_world_size(groups["dp"]) if groups["dp"] is not None else 1)
     tokens = n_seq * seq * micro * dp_like

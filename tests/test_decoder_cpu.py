@@ -141,3 +141,18 @@ def test_tp2_x_cp2_on_four_ranks_matches_single_rank(tmp_path):
     ''', nproc=4, port=29861, tmp_path=tmp_path, timeout=600)
     assert abs(res["loss"] - res["ref"]) < 2e-4 * abs(res["ref"]), res
     assert res["g_err"] < 2e-3, res
+
+
+def test_cp2_x_pp2_training_follows_the_single_rank_loss_curve():
+    """Three optimisation steps of the tiny hybrid model: context parallel x pipeline parallel on four ranks ends on the
+    same loss as one rank (same data, same initial weights; the reported loss is the global mean)."""
+    def run(layout, nproc, port):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
+               "127.0.0.1", "--master-port", str(port), "-m", "litetorch_b200.models.run_config", "--config", "hybrid", "--tiny",
+               "--steps", "2", "--warmup", "1", "--layout", layout, "--micro", "1", "--seq", "256"]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT, env=dict(os.environ, OMP_NUM_THREADS="1"))
+        assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+        return json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])["loss"]
+    one = run("1,1,1", 1, 29871)
+    four = run("1,2,2", 4, 29872)
+    assert abs(one - four) < 2e-4, (one, four)
