@@ -121,10 +121,22 @@ def linear_rs(dims: ParallelDims, x: torch.Tensor, w_local: torch.Tensor) -> tor
     return _tp._ScatterFwdGatherBwd.apply(lin(x, w_local), 0, dims.tp)
 
 
-def _param(shape, std, gen, device, dtype, reduce_groups=()):
-    t = torch.empty(*shape).normal_(0, std, generator=gen).to(device=device, dtype=dtype).requires_grad_(True)
+def _units(units, unit_shape, cat_dim, std, key, device, dtype, reduce_groups=()):
+    """A parameter assembled from independently seeded units (a head, a block of feed-forward or vocabulary rows).
+    A tensor-parallel rank draws exactly the units it owns, so the same seed gives the same model under every layout:
+    the shards of a tensor-parallel group, put side by side, are the tensor one rank alone would draw."""
+    parts = []
+    for u in units:
+        g = torch.Generator().manual_seed((key * 1000003 + int(u)) % (2 ** 62))
+        parts.append(torch.empty(*unit_shape).normal_(0, std, generator=g))
+    t = torch.cat(parts, cat_dim).to(device=device, dtype=dtype).requires_grad_(True)
     t.reduce_groups = [g for g in reduce_groups if g is not None]
     return t
+
+
+def _unit_rows(n: int) -> int:
+    """Rows per unit of a dimension that tensor parallelism may split up to eight ways."""
+    return math.gcd(n // 8, 64) if n % 8 == 0 else 1
 
 
 def _ones(n, device, dtype, reduce_groups=()):
@@ -140,14 +152,21 @@ class DecoderBlock:
         assert cfg.n_q % Wt == 0 and cfg.n_kv % Wt == 0 and cfg.ffn % Wt == 0
         self.hq, self.hkv = cfg.n_q // Wt, cfg.n_kv // Wt
         D, d = cfg.head_dim, cfg.d_model
-        # every tensor-parallel rank draws its own slice: the seed depends on (layer, tp rank), not on other axes
-        gen = torch.Generator().manual_seed(seed * 1000003 + layer_idx * 101 + rt)
+        # weights are drawn unit by unit (see _units): a rank draws the heads / feed-forward rows it owns
+        key = lambda tensor_id: (seed * 1009 + layer_idx + 1) * 16 + tensor_id      # noqa: E731
         rep = (dims.cp, dims.dp)                     # replicas of a tensor-parallel shard
         rep_all = (dims.cp, dims.dp, dims.tp)        # replicated everywhere; row-sliced activations give partial sums
         self.norm1 = _ones(d, device, dtype, rep_all)
         self.norm2 = _ones(d, device, dtype, rep_all)
-        self.wqkv = _param(((self.hq + 2 * self.hkv) * D, d), 0.02, gen, device, dtype, rep)
-        self.wo = _param((d, self.hq * D), 0.02, gen, device, dtype, rep)
+        q_heads = range(rt * self.hq, (rt + 1) * self.hq)
+        kv_heads = range(rt * self.hkv, (rt + 1) * self.hkv)
+        with torch.no_grad():
+            qkv = torch.cat([_units(q_heads, (D, d), 0, 0.02, key(0), "cpu", torch.float32),
+                             _units(kv_heads, (D, d), 0, 0.02, key(1), "cpu", torch.float32),
+                             _units(kv_heads, (D, d), 0, 0.02, key(2), "cpu", torch.float32)], 0)
+        self.wqkv = qkv.to(device=device, dtype=dtype).requires_grad_(True)        # [q heads | k heads | v heads] of this rank
+        self.wqkv.reduce_groups = [g for g in rep if g is not None]
+        self.wo = _units(q_heads, (d, D), 1, 0.02, key(3), device, dtype, rep)
         self.moe = None
         if cfg.n_experts > 0:
             assert Wt == 1, "the MoE block uses data-parallel attention (no tensor parallelism)"
@@ -169,8 +188,15 @@ class DecoderBlock:
                 t.grad_scale = 1.0 / _w(dims.ep)
         else:
             F = cfg.ffn // Wt
-            self.w_gu = _param((2 * F, d), 0.02, gen, device, dtype, rep)            # [gate slice | up slice]
-            self.w_dn = _param((d, F), 0.02, gen, device, dtype, rep)
+            ch = _unit_rows(cfg.ffn)
+            assert F % ch == 0
+            chunks = range(rt * F // ch, (rt + 1) * F // ch)
+            with torch.no_grad():
+                gu = torch.cat([_units(chunks, (ch, d), 0, 0.02, key(4), "cpu", torch.float32),
+                                _units(chunks, (ch, d), 0, 0.02, key(5), "cpu", torch.float32)], 0)
+            self.w_gu = gu.to(device=device, dtype=dtype).requires_grad_(True)       # [gate slice | up slice]
+            self.w_gu.reduce_groups = [g for g in rep if g is not None]
+            self.w_dn = _units(chunks, (d, ch), 1, 0.02, key(6), device, dtype, rep)
 
     def parameters(self) -> List[torch.Tensor]:
         ps = [self.norm1, self.norm2, self.wqkv, self.wo]
@@ -232,16 +258,19 @@ class ParallelDecoder:
         self.ckpt = activation_checkpointing
         self.blocks = [DecoderBlock(cfg, dims, i, device, dtype, seed, max_tokens) for i in range(first_layer, last_layer)]
         rep_all = (dims.cp, dims.dp, dims.tp)
-        gen = torch.Generator().manual_seed(seed * 31 + 5)
-        self.embed = _param((cfg.vocab, cfg.d_model), 0.02, gen, device, dtype, rep_all) if self.is_first else None
+        vch = _unit_rows(cfg.vocab)
+        mkey = lambda tensor_id: (seed * 1009) * 16 + tensor_id                      # noqa: E731
+        self.embed = (_units(range(cfg.vocab // vch), (vch, cfg.d_model), 0, 0.02, mkey(7), device, dtype, rep_all)
+                      if self.is_first else None)
         if self.is_last:
             Wt, rt = dims.tp_world, dims.tp_rank
             assert cfg.vocab % Wt == 0
             self.v_local = cfg.vocab // Wt
             self.v_start = rt * self.v_local
             self.final_norm = _ones(cfg.d_model, device, dtype, rep_all)
-            hg = torch.Generator().manual_seed(seed * 31 + 7 + rt)
-            self.head = _param((self.v_local, cfg.d_model), 0.02, hg, device, dtype, (dims.cp, dims.dp))
+            assert self.v_local % vch == 0
+            self.head = _units(range(rt * self.v_local // vch, (rt + 1) * self.v_local // vch), (vch, cfg.d_model), 0, 0.02,
+                               mkey(8), device, dtype, (dims.cp, dims.dp))
         self._rope_cache = {}
 
     # ---- parameters and gradient reductions

@@ -143,7 +143,7 @@ def test_tp2_x_cp2_on_four_ranks_matches_single_rank(tmp_path):
     assert res["g_err"] < 2e-3, res
 
 
-def test_cp2_x_pp2_training_follows_the_single_rank_loss_curve():
+def test_parallel_layouts_follow_the_single_rank_loss_curve():
     """Three optimisation steps of the tiny hybrid model: context parallel x pipeline parallel on four ranks ends on the
     same loss as one rank (same data, same initial weights; the reported loss is the global mean)."""
     def run(layout, nproc, port):
@@ -156,3 +156,7 @@ def test_cp2_x_pp2_training_follows_the_single_rank_loss_curve():
     one = run("1,1,1", 1, 29871)
     four = run("1,2,2", 4, 29872)
     assert abs(one - four) < 2e-4, (one, four)
+    # weights are drawn unit by unit, so tensor parallelism starts from the same model too: the full 4D layout
+    # (TP2 x CP2 x PP2 on eight ranks) follows the same curve
+    eight = run("2,2,2", 8, 29873)
+    assert abs(one - eight) < 5e-4, (one, eight)
