@@ -322,3 +322,43 @@ def test_file_store(tmp_path):
     assert fs.get("nccl_id") == b"x" * 128
     with pytest.raises(TimeoutError):
         fs.get("missing", timeout_s=0.1)
+
+
+def test_store_delayed_rendezvous_lost_server_and_unreachable_host():
+    """Host-side fault injection on the rendezvous store: a client that starts before the server keeps retrying and gets
+    through; a client of a server that has gone away gets an error instead of hanging; nobody listening is a timeout."""
+    import socket
+    import threading
+    import time
+    from litetorch_b200.parallel.process_group import TCPStore
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()                                              # a free port nobody listens on yet
+    got = {}
+
+    def late_client():
+        c = TCPStore("127.0.0.1", port, is_server=False, timeout_s=10.0)     # the server is not up yet
+        got["v"] = c.get("ready", timeout_s=10.0)
+        c.close()
+    t = threading.Thread(target=late_client)
+    t.start()
+    time.sleep(1.0)                                        # the delayed rendezvous
+    server = TCPStore("127.0.0.1", port, is_server=True)
+    server.set("ready", b"yes")
+    t.join(timeout=20)
+    assert not t.is_alive() and got.get("v") == b"yes"
+    # the server goes away under a connected client
+    client = TCPStore("127.0.0.1", port, is_server=False, timeout_s=5.0)
+    client.set("k", b"1")
+    server.close()
+    t0 = time.time()
+    with pytest.raises((RuntimeError, TimeoutError)):
+        client.get("never", timeout_s=3.0)
+    assert time.time() - t0 < 10
+    client.close()
+    # nobody listening: connecting gives up after its timeout
+    t0 = time.time()
+    with pytest.raises(RuntimeError):
+        TCPStore("127.0.0.1", port, is_server=False, timeout_s=1.0)
+    assert 0.5 < time.time() - t0 < 5
