@@ -1,7 +1,10 @@
 #!/usr/bin/env python
-"""Headline benchmark: training tokens/s of the Llama-style 1.1B model (vocab 32000, 22 layers, d 2048,
-32 q / 4 kv heads of 64, SwiGLU 5632, seq 2048, micro-batch 4 per GPU, bf16 compute, fp32 master + AdamW),
-ZeRO-3 sharded over N GPUs of one node (weak scaling: the per-GPU batch is fixed).
+"""Headline benchmark: training tokens/s of the Llama-3-8B shape (vocab 128256, 32 layers, d 4096, 32 q / 8 kv heads
+of 128, SwiGLU 14336, RoPE 5e5, seq 8192, one sequence per GPU and step, bf16 compute, fp32 master + AdamW states)
+under FSDP (ZeRO-3) x tensor parallelism with sequence parallelism on N GPUs of one node (weak scaling: tokens per
+GPU are fixed).  Mesh per N (dp x tp): 1 -> 1x1, 2 -> 1x2, 4 -> 2x2, 8 -> 4x2: tensor parallelism stays inside a pair
+of GPUs, where the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels run near their roofline, and the other
+ranks shard parameters, gradients and optimizer state the ZeRO-3 way (`--tp` changes the split).
 
     python bench.py --gpus 1 --steps 10 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
@@ -11,7 +14,10 @@ ZeRO-3 sharded over N GPUs of one node (weak scaling: the per-GPU batch is fixed
 Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events around exactly K steps, barrier +
 synchronize on both sides, max over ranks) with batches already on the device; `e2e` times the public
 `Trainer.step` call, which copies each batch from pinned host memory and reads the loss back every step.
-Data are synthetic uniform-random tokens, weights N(0, 0.02).
+Outside the timed regions the line also carries: `exposed_comm_ms_per_step` (the step minus the same per-GPU
+compute without any communication), `llama_1b` (the 1.1B ZeRO-3 configuration: vocab 32000, 22 layers, d 2048,
+seq 2048, micro-batch 4 per GPU) and `probe` (a two-layer model small enough for the reference library to train,
+for a same-configuration ratio).  Data are synthetic uniform-random tokens, weights N(0, 0.02).
 """
 from __future__ import annotations
 
@@ -25,7 +31,9 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-MICRO_BATCH = 4
+# name -> (sequences per GPU and step, sequence length)
+SHAPES = {"llama3-8b": (1, 8192), "llama-1.1b": (4, 2048), "llama-tiny": (4, 256)}
+MICRO_BATCH = 4          # of the 1.1B configuration and of the probe (the reference arm uses the same)
 SEQ_LEN = 2048
 
 
@@ -35,9 +43,13 @@ def _parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama-1.1b", choices=["llama-1.1b", "llama-tiny"])
+    ap.add_argument("--model", default="llama3-8b", choices=list(SHAPES))
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0: 1 on one GPU, else 2)")
+    ap.add_argument("--ckpt", default="auto", choices=["auto", "on", "off"],
+                    help="activation checkpointing (auto: on where weights + optimizer state of one rank leave no room)")
     ap.add_argument("--no-comm-breakdown", action="store_true",
-                    help="skip the extra unsharded steps that give exposed_comm_ms_per_step at N > 1")
+                    help="skip the extra communication-free steps that give exposed_comm_ms_per_step at N > 1")
+    ap.add_argument("--no-extras", action="store_true", help="skip the llama_1b and probe measurements")
     return ap.parse_args()
 
 
@@ -105,10 +117,66 @@ class ClockSampler:
         return out
 
 
+def _model_config(name):
+    from litetorch_b200.models.llama import LlamaConfig
+    return {"llama3-8b": LlamaConfig.llama3_8b, "llama-1.1b": LlamaConfig.llama_1b, "llama-tiny": LlamaConfig.tiny}[name]()
+
+
+def _describe(cfg):
+    return "%s (vocab %d, %d layers, d %d, %dq/%dkv heads x %d, SwiGLU %d, RMSNorm, RoPE %g)" % (
+        cfg.name, cfg.vocab_size, cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.rope_theta)
+
+
+def _measure(tr, host, devb, steps, warmup, sync, sampler=None):
+    """Device-timed steps on resident batches, then the same number end to end through Trainer.step.
+    Returns (ms_total, e2e_ms_total, launches, last loss, clocks)."""
+    import torch
+    from litetorch_b200.ops import kernels as K
+    n = len(devb)
+    for i in range(warmup):
+        tr.step_device(*devb[i % n])
+    sync()
+    if sampler is not None:
+        sampler.start()
+    K.reset_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    last = None
+    for i in range(steps):
+        last = tr.step_device(*devb[i % n])
+    e1.record()
+    sync()
+    launches = K.launch_count()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler is not None else {}
+    loss_val = float(last)
+    for i in range(warmup):
+        tr.step(*host[i % n])
+    sync()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        tr.step(*host[i % n])
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    sync()
+    return ms_total, e2e_ms, launches, loss_val, clocks
+
+
+def _batches(cfg, n_seq, T, seed, dev, n_batches=4):
+    import torch
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    host = []
+    for _ in range(n_batches):
+        seq = torch.randint(0, cfg.vocab_size, (n_seq, T + 1), generator=gen, dtype=torch.int64)
+        host.append((seq[:, :-1].contiguous().pin_memory(), seq[:, 1:].contiguous().pin_memory()))
+    return host, [(a.to(dev), b.to(dev)) for a, b in host]
+
+
 def run_ours(args):
+    import dataclasses
     import torch
     import torch.distributed as dist
-    from litetorch_b200.models.llama import LlamaConfig
     from litetorch_b200.ops import kernels as K
     from litetorch_b200.trainer import Trainer
 
@@ -116,108 +184,152 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    cfg = LlamaConfig.llama_1b() if args.model == "llama-1.1b" else LlamaConfig.tiny()
-    T = min(SEQ_LEN, cfg.max_seq)
-    tr = Trainer(cfg, seed=1234)
-    dev = tr.device
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = _model_config(args.model)
+    per_gpu, T = SHAPES[args.model]
+    T = min(T, cfg.max_seq)
+    big = args.model == "llama3-8b"
+    tp = args.tp or int(os.environ.get("LT_BENCH_TP", "0")) or (2 if (world > 1 and big) else 1)
+    dp = world // tp
+    # One rank of the 8B shape holds 128 GB of parameters, gradients and fp32 optimizer state when nothing is sharded:
+    # the activations of 32 layers no longer fit beside them, so every layer is recomputed in the backward pass.
+    ckpt = (big and world == 1) if args.ckpt == "auto" else args.ckpt == "on"
+    n_seq = per_gpu * tp                           # sequences of one tensor-parallel group (all its ranks get the same batch)
 
-    def barrier_sync():
+    def sync():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
-    n_batches = 4
-    host = []
-    for _ in range(n_batches):
-        seq = torch.randint(0, cfg.vocab_size, (MICRO_BATCH, T + 1), generator=gen, dtype=torch.int64)
-        host.append((seq[:, :-1].contiguous().pin_memory(), seq[:, 1:].contiguous().pin_memory()))
-    devb = [(a.to(dev), b.to(dev)) for a, b in host]
-
-    # ---------------- device-timed region (inputs resident on the device)
-    for i in range(args.warmup):
-        tr.step_device(*devb[i % n_batches])
-    barrier_sync()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    K.reset_launch_count()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    barrier_sync()
-    e0.record()
-    last = None
-    for i in range(args.steps):
-        last = tr.step_device(*devb[i % n_batches])
-    e1.record()
-    barrier_sync()
-    launches = K.launch_count()
-    ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else {}
-    loss_val = float(last)
-    status = K.status_fetch()
-
-    # ---------------- end to end through Trainer.step (pinned host batch in, loss out, every step)
-    for i in range(args.warmup):
-        tr.step(*host[i % n_batches])
-    barrier_sync()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        tr.step(*host[i % n_batches])
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    barrier_sync()
+    tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt, parallel="hybrid" if tp > 1 else "auto")
+    host, devb = _batches(cfg, n_seq, T, 1000 + rank // tp, dev)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_total, e2e_ms, launches, loss_val, clocks = _measure(tr, host, devb, args.steps, args.warmup, sync, sampler)
     h2d_bytes, d2h_bytes = tr.h2d_bytes, tr.d2h_bytes
+    status = K.status_fetch()
+    peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+    del tr
+    torch.cuda.empty_cache()
 
-    # ---------------- exposed communication (outside the timed regions): the same step on an unsharded copy of the
-    # model, one per GPU, costs the compute alone; what the sharded step takes on top of it is communication that
-    # the overlap did not hide (gather CTAs taken from the GEMMs included).
+    # ---------------- exposed communication (outside the timed regions): the same per-GPU compute with no
+    # communication at all.  For the ZeRO-3 layout that is an unsharded copy of the model on each GPU; for a
+    # tensor-parallel group it is the group's batch through a model whose heads, feed-forward width and vocabulary
+    # are divided by tp (exactly the GEMM / attention shapes one rank executes).  What the sharded step takes on top
+    # of it is communication that the overlap did not hide (gather CTAs taken from the GEMMs included).
     local_ms = 0.0
     if world > 1 and not args.no_comm_breakdown:
-        del tr
-        torch.cuda.empty_cache()
-        tr_local = Trainer(cfg, seed=1234, parallel="none")
+        twin = dataclasses.replace(cfg, n_heads=cfg.n_heads // tp, n_kv_heads=cfg.n_kv_heads // tp, ffn=cfg.ffn // tp,
+                                   vocab_size=cfg.vocab_size // tp)
+        tr_local = Trainer(twin, seed=1234, parallel="none", activation_checkpointing=ckpt)
+        _, tb = _batches(twin, n_seq, T, 1000 + rank // tp, dev)
         for i in range(3):
-            tr_local.step_device(*devb[i % n_batches])
+            tr_local.step_device(*tb[i % len(tb)])
         torch.cuda.synchronize()
         l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0.record()
         for i in range(4):
-            tr_local.step_device(*devb[i % n_batches])
+            tr_local.step_device(*tb[i % len(tb)])
         l1.record()
         torch.cuda.synchronize()
         local_ms = l0.elapsed_time(l1) / 4
-    t = torch.tensor([ms_total, e2e_s * 1e3, local_ms], device=dev, dtype=torch.float64)
+        del tr_local, tb
+        torch.cuda.empty_cache()
+
+    # ---------------- extras, outside the timed regions
+    extras = {}
+    if not args.no_extras and big:
+        try:
+            c1 = _model_config("llama-1.1b")
+            b1, t1 = SHAPES["llama-1.1b"]
+            tr1 = Trainer(c1, seed=1234)
+            h1, d1 = _batches(c1, b1, t1, 2000 + rank, dev)
+            ms1, e2e1, _, loss1, _ = _measure(tr1, h1, d1, 6, 3, sync)
+            loc1 = 0.0
+            del tr1
+            torch.cuda.empty_cache()
+            if world > 1:
+                tl = Trainer(c1, seed=1234, parallel="none")
+                for i in range(3):
+                    tl.step_device(*d1[i % len(d1)])
+                torch.cuda.synchronize()
+                l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                l0.record()
+                for i in range(4):
+                    tl.step_device(*d1[i % len(d1)])
+                l1.record()
+                torch.cuda.synchronize()
+                loc1 = l0.elapsed_time(l1) / 4
+                del tl
+                torch.cuda.empty_cache()
+            extras["llama_1b"] = (ms1, e2e1, loc1, loss1)
+        except Exception as e:  # pragma: no cover
+            extras["llama_1b_error"] = repr(e)[:200]
+        try:
+            cp_ = _model_config("llama-tiny")
+            bp, tpb = SHAPES["llama-tiny"]
+            trp = Trainer(cp_, seed=1234, parallel="none")
+            hp, dpb = _batches(cp_, bp, tpb, 3000, dev)
+            msp, e2ep, _, lossp, _ = _measure(trp, hp, dpb, 20, 5, lambda: torch.cuda.synchronize())
+            extras["probe"] = (msp, e2ep, lossp)
+            del trp
+        except Exception as e:  # pragma: no cover
+            extras["probe_error"] = repr(e)[:200]
+
+    vals = [ms_total, e2e_ms, local_ms]
+    if "llama_1b" in extras:
+        vals += list(extras["llama_1b"][:3])
+    t = torch.tensor(vals, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, local_ms = float(t[0]), float(t[1]), float(t[2])
-    tokens = MICRO_BATCH * T * world * args.steps
+    tokens = per_gpu * T * world * args.steps
     value = tokens / (ms_total / 1e3)
     e2e_value = tokens / (e2e_ms / 1e3)
     if rank == 0:
+        par = "single" if world == 1 else ("fsdp%d (ZeRO-3)" % world if tp == 1 else
+                                            "dp%d (ZeRO-3) x tp%d (+ sequence parallel)" % (dp, tp))
         out = {
             "metric": "train tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "llama-1.1b (vocab 32000, 22 layers, d 2048, 32q/4kv heads x 64, SwiGLU 5632, RMSNorm, RoPE 1e4)"
-                       if args.model == "llama-1.1b" else cfg.name,
-                       "global_batch": MICRO_BATCH * world, "seq_len": T,
-                       "parallelism": "single" if world == 1 else "fsdp%d (ZeRO-3)" % world,
+            "config": {"model": _describe(cfg), "global_batch": per_gpu * world, "seq_len": T, "parallelism": par,
+                       "dp": dp, "tp": tp, "activation_checkpointing": bool(ckpt),
                        "optimizer": "AdamW fp32 master+states, bf16 params/grads",
-                       "l2": "no flush: the step's working set (2.2 GB bf16 weights + ~10 GB activations) is far larger than the 126 MB L2"},
+                       "l2": "no flush: the step's working set (weights and activations, tens of GB) is far larger than the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches,
             "exposed_comm_ms_per_step": (round(ms_total / args.steps - local_ms, 3) if local_ms > 0 else (0.0 if world == 1 else None)),
-            "unsharded_step_ms": round(local_ms, 3) if local_ms > 0 else None,
+            "comm_free_step_ms": round(local_ms, 3) if local_ms > 0 else None,
             "final_loss": round(loss_val, 4),
             "device_status": status,
+            "peak_memory_gb": round(peak_gb, 1),
             "model_tflops_per_gpu": round(cfg.flops_per_token(T) * value / world / 1e12, 1),
         }
+        if "llama_1b" in extras:
+            ms1, e2e1, loc1 = float(t[3]), float(t[4]), float(t[5])
+            tok1 = SHAPES["llama-1.1b"][0] * SHAPES["llama-1.1b"][1] * world
+            out["llama_1b"] = {"value": round(tok1 * 6 / (ms1 / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms1 / 6, 3),
+                               "e2e_value": round(tok1 * 6 / (e2e1 / 1e3), 1),
+                               "exposed_comm_ms_per_step": round(ms1 / 6 - loc1, 3) if loc1 > 0 else 0.0,
+                               "parallelism": "single" if world == 1 else "fsdp%d (ZeRO-3)" % world,
+                               "global_batch": SHAPES["llama-1.1b"][0] * world, "seq_len": SHAPES["llama-1.1b"][1],
+                               "steps": 6, "warmup": 3, "final_loss": round(extras["llama_1b"][3], 4)}
+        if "probe" in extras:
+            msp, e2ep, lossp = extras["probe"]
+            tokp = SHAPES["llama-tiny"][0] * SHAPES["llama-tiny"][1]
+            out["probe"] = {"model": "llama-tiny (vocab 512, 2 layers, d 256, 4q/2kv heads x 64, SwiGLU 512)", "n_gpus": 1,
+                            "global_batch": SHAPES["llama-tiny"][0], "seq_len": SHAPES["llama-tiny"][1], "dtype": "bf16",
+                            "value": round(tokp * 20 / (msp / 1e3), 1), "e2e_value": round(tokp * 20 / (e2ep / 1e3), 1),
+                            "unit": "tokens/s", "ms_per_step": round(msp / 20, 4), "steps": 20, "warmup": 5,
+                            "final_loss": round(lossp, 4)}
+        for k in ("llama_1b_error", "probe_error"):
+            if k in extras:
+                out[k] = extras[k]
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()

@@ -313,6 +313,48 @@ __global__ void signal_barrier_kernel(const BarrierArgs a) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- shard gather
+// Weight all-gather without a GEMM attached: pulls `world` row shards of up to 8 matrices from the ranks'
+// parameter buffers into local full-size staging areas with 16-byte peer loads, four in flight per thread.
+// Used one layer ahead on a side stream when the GEMM's own gather slot is taken by the tensor-parallel
+// activation gather (FSDP x TP): the next layer's weights need a fraction of the link rate, so a few CTAs
+// that share SMs with the running GEMM are enough.  Same role as the reference's pre-forward all-gather
+// (src/distributed/fsdp_wrapper.cpp:123-145), read from peer memory instead of through NCCL.
+struct ShardGatherArgs {
+  const __nv_bfloat16* shard[kMaxRanks];   // every rank's parameter shard buffer (peer-mapped)
+  __nv_bfloat16* dst[8];                   // staging area of segment s (holds world * n elements)
+  long long shard_off[8], n[8];            // element offset in the shard buffer, elements per rank
+  long long vec_end[8];                    // running total of 16-byte vectors up to and including segment s
+  int n_seg, world;
+};
+__global__ void __launch_bounds__(512) shard_gather_kernel(const ShardGatherArgs a) {
+  const long long total = a.vec_end[a.n_seg - 1];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < total; base += 4 * stride) {
+    uint4 v[4];
+    __nv_bfloat16* out[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = base + u * stride;
+      out[u] = nullptr;
+      if (i >= total) continue;
+      int s = 0;
+      while (i >= a.vec_end[s]) ++s;
+      const long long j = i - (s ? a.vec_end[s - 1] : 0);      // vector index inside segment s
+      const long long per_rank = a.n[s] / 8;
+      const int r = int(j / per_rank);
+      const long long e = (j - r * per_rank) * 8;
+      v[u] = ld_relaxed_sys_v4(a.shard[r] + a.shard_off[s] + e);
+      out[u] = a.dst[s] + r * a.n[s] + e;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (out[u]) *reinterpret_cast<uint4*>(out[u]) = v[u];
+  }
+}
+
+
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
 static int launch_ag_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const GatherArgs& g,
                           const PrefetchArgs& pf, int grid, cudaStream_t st) {
@@ -536,6 +578,33 @@ int lt_rs_adamw(const void* const* grad_ptrs, const void* mc_grads, float* maste
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   rs_adamw_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+
+// Copies, for each of n_seg segments, `n` elements starting at `shard_off` of every rank's shard buffer into
+// dst[s] + r * n (rank order).  segs: n_seg triples (shard_off, n, unused) in elements, multiples of 8;
+// dst_ptrs: n_seg local destination pointers, 16-byte aligned.  max_ctas: 0 = 16.
+int lt_gather_shards(const void* const* shard_ptrs, int world, const long long* segs, const void* const* dst_ptrs, int n_seg,
+                     int max_ctas, void* stream) {
+  using namespace lt;
+  if (world < 1 || world > kMaxRanks || n_seg < 1 || n_seg > 8) return -int(kStatusBadArgument);
+  ShardGatherArgs a{};
+  for (int r = 0; r < world; ++r) a.shard[r] = static_cast<const __nv_bfloat16*>(shard_ptrs[r]);
+  long long total = 0;
+  for (int s = 0; s < n_seg; ++s) {
+    a.shard_off[s] = segs[3 * s]; a.n[s] = segs[3 * s + 1];
+    a.dst[s] = static_cast<__nv_bfloat16*>(const_cast<void*>(dst_ptrs[s]));
+    if (a.n[s] <= 0 || a.n[s] % 8 != 0 || a.shard_off[s] % 8 != 0 || (reinterpret_cast<uintptr_t>(a.dst[s]) & 15) != 0)
+      return -int(kStatusBadArgument);
+    total += a.n[s] / 8 * world;
+    a.vec_end[s] = total;
+  }
+  a.n_seg = n_seg; a.world = world;
+  long long blocks = (total + 4 * 512 - 1) / (4 * 512);
+  const long long cap = max_ctas > 0 ? max_ctas : 16;
+  if (blocks > cap) blocks = cap;
+  shard_gather_kernel<<<(unsigned)blocks, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
   LT_LAUNCH_CHECK();
   return 0;
 }

@@ -19,6 +19,36 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..ops import kernels as K
+from ..ops import kernels_ref as K_ref
+
+
+def kernels_for(device):
+    """The kernel front-end for tensors on `device`: the sm_100a library on CUDA, its PyTorch twin on the CPU."""
+    return K if torch.device(device).type == "cuda" else K_ref
+
+
+class SingleTPMixin:
+    """Weight-provider methods of the tensor-parallel schedule for providers that hold whole matrices (tp = 1):
+    a column-parallel linear is a plain GEMM that hands back its own input as the "gathered" activation, a
+    row-parallel linear is a plain GEMM with the residual in the epilogue."""
+    tp = 1
+    tp_rank = 0
+    vocab_start = 0
+
+    def col_linear(self, x, name):
+        return self.linear(x, name), x
+
+    def row_linear(self, x, name, residual=None):
+        return self.linear(x, name, residual=residual)
+
+    def col_dgrad(self, dy, name):
+        return self.dgrad(dy, name)
+
+    def row_dgrad(self, dy, name):
+        return self.dgrad(dy, name), dy
+
+    def reduce_ce_stats(self, stats):
+        return stats
 
 
 @dataclass
@@ -114,11 +144,12 @@ def rope_tables(cfg: LlamaConfig, device, max_seq: Optional[int] = None):
     return ang.cos().float().contiguous(), ang.sin().float().contiguous()
 
 
-class LocalWeights:
+class LocalWeights(SingleTPMixin):
     """All parameters resident on one GPU: flat bf16 parameters + flat bf16 gradients + fp32 master/m/v."""
 
-    def __init__(self, cfg: LlamaConfig, device, seed: int = 0):
+    def __init__(self, cfg: LlamaConfig, device, seed: int = 0, param_dtype=torch.bfloat16):
         self.cfg = cfg
+        self.K = kernels_for(device)
         self.specs = param_specs(cfg)
         self.by_name = {s.name: s for s in self.specs}
         sizes = {"matrix": 0, "vector": 0}
@@ -126,8 +157,8 @@ class LocalWeights:
             sizes[s.kind] = max(sizes[s.kind], s.offset + (math.prod(s.shape) + 127) // 128 * 128)
         self.n_matrix, self.n_vector = sizes["matrix"], sizes["vector"]
         n = self.n_matrix + self.n_vector
-        self.flat_p = torch.zeros(n, dtype=torch.bfloat16, device=device)
-        self.flat_g = torch.zeros(n, dtype=torch.bfloat16, device=device)
+        self.flat_p = torch.zeros(n, dtype=param_dtype, device=device)
+        self.flat_g = torch.zeros(n, dtype=param_dtype, device=device)
         self.master = torch.zeros(n, dtype=torch.float32, device=device)
         self.m = torch.zeros(n, dtype=torch.float32, device=device)
         self.v = torch.zeros(n, dtype=torch.float32, device=device)
@@ -159,13 +190,13 @@ class LocalWeights:
 
     # ---- GEMM providers (the ZeRO-3 weights object overrides these with fused all-gather variants)
     def linear(self, x, name, **kw):
-        return K.gemm(x, self.p(name), **kw)
+        return self.K.gemm(x, self.p(name), **kw)
 
     def dgrad(self, dy, name, **kw):
-        return K.gemm(dy, self.p(name), b_major=1, **kw)
+        return self.K.gemm(dy, self.p(name), b_major=1, **kw)
 
     def wgrad(self, dy, x, name, accumulate=False):
-        return K.gemm(dy, x, a_major=1, b_major=1, out=self.g(name), accumulate=accumulate)
+        return self.K.gemm(dy, x, a_major=1, b_major=1, out=self.g(name), accumulate=accumulate)
 
     def vector_grad(self, name):
         return self.g(name)
@@ -174,25 +205,25 @@ class LocalWeights:
         self.g("embed").zero_()
 
     def embedding(self, tokens):
-        return K.embedding_fwd(tokens, self.p("embed"))
+        return self.K.embedding_fwd(tokens, self.p("embed"))
 
     def embedding_backward(self, tokens, dx):
-        K.embedding_bwd(tokens, dx, self.g("embed"))
+        self.K.embedding_bwd(tokens, dx, self.g("embed"))
 
     def optimizer_step(self, *, lr, beta1, beta2, eps, weight_decay, step, dyn=None):
         nm = self.n_matrix
         if getattr(self, "_hyper", None) is not None and getattr(self, "_updated", 0) == nm and dyn is None:
             # every matrix was updated bucket by bucket on the side stream during the backward pass
-            K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
+            self.K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
                         beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True)
             torch.cuda.current_stream().wait_stream(self._side)
             self._updated = 0
             return
         if getattr(self, "_updated", 0):
             raise RuntimeError("optimizer_step after a partial overlapped update")
-        K.adam_flat(self.master[:nm], self.flat_g[:nm], self.m[:nm], self.v[:nm], self.flat_p[:nm], lr=lr, beta1=beta1,
+        self.K.adam_flat(self.master[:nm], self.flat_g[:nm], self.m[:nm], self.v[:nm], self.flat_p[:nm], lr=lr, beta1=beta1,
                     beta2=beta2, eps=eps, wd=weight_decay, step=step, adamw=True, dyn=dyn)
-        K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
+        self.K.adam_flat(self.master[nm:], self.flat_g[nm:], self.m[nm:], self.v[nm:], self.flat_p[nm:], lr=lr, beta1=beta1,
                     beta2=beta2, eps=eps, wd=0.0, step=step, adamw=True, dyn=dyn)
 
     # ---- AdamW overlapped with the backward pass: as soon as the weight gradients of a bucket ("head", a layer, "embed")
@@ -224,7 +255,7 @@ class LocalWeights:
         a, b = self._bucket_range(bucket)
         self._side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._side):
-            K.adam_flat(self.master[a:b], self.flat_g[a:b], self.m[a:b], self.v[a:b], self.flat_p[a:b], lr=h["lr"],
+            self.K.adam_flat(self.master[a:b], self.flat_g[a:b], self.m[a:b], self.v[a:b], self.flat_p[a:b], lr=h["lr"],
                         beta1=h["beta1"], beta2=h["beta2"], eps=h["eps"], wd=h["weight_decay"], step=h["step"], adamw=True)
         self._updated += b - a
 
@@ -241,75 +272,92 @@ class LocalWeights:
 
 
 class LlamaEngine:
-    """Forward + backward + optimizer step of a Llama-style decoder on the sm_100a kernels."""
+    """Forward + backward + optimizer step of a Llama-style decoder on the sm_100a kernels.
+
+    The schedule is written once for tensor parallelism with sequence parallelism and degenerates to the plain
+    single-GPU schedule when the weight provider has `tp == 1`: the residual stream, the norms and their
+    gradients live on this rank's block of M / tp token rows; a column-parallel linear (QKV, gate/up, LM head)
+    gathers its input over the tensor-parallel group and produces this rank's heads / feed-forward columns /
+    vocabulary slice for all M rows; a row-parallel linear (attention output, down projection) reduces its
+    partial products over the group and scatters the rows back (`col_linear`, `row_linear`, `col_dgrad`,
+    `row_dgrad` of the provider - fused all-gather -> GEMM and GEMM -> reduce-scatter kernels in
+    `parallel.hybrid.HybridWeights`).  Every rank of a tensor-parallel group is given the same [B, T] batch.
+    Counterparts in the reference: ColumnParallelLinear / RowParallelLinear (src/nn/parallel_linear.cpp:31-106)
+    inside an FSDP-wrapped module (src/distributed/fsdp_wrapper.cpp:106-156).
+    """
 
     def __init__(self, cfg: LlamaConfig, device="cuda", weights=None, seed: int = 0, lr: float = 3e-4,
                  betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, activation_checkpointing: bool = False,
                  world_size: int = 1):
         self.cfg = cfg
         self.device = torch.device(device)
+        self.K = kernels_for(self.device)
         self.w = weights if weights is not None else LocalWeights(cfg, self.device, seed)
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.ckpt = activation_checkpointing
-        self.world_size = world_size
+        self.world_size = world_size          # data-parallel replicas the gradient is averaged over
         self.step_count = 0
         self.cos, self.sin = rope_tables(cfg, self.device)
         self.kernel_launches = 0
+        tp = self.w.tp
+        assert cfg.n_heads % tp == 0 and cfg.n_kv_heads % tp == 0 and cfg.ffn % tp == 0 and cfg.vocab_size % tp == 0, \
+            "heads, kv heads, ffn and vocabulary must divide over the tensor-parallel group"
+        self.Hq, self.Hkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
+        self.qkv_local = (self.Hq + 2 * self.Hkv) * cfg.head_dim
 
     # ------------------------------------------------------------------------------------------ layer
     def _layer_fwd(self, i: int, x: torch.Tensor, B: int, T: int):
-        cfg, w = self.cfg, self.w
+        cfg, w, K = self.cfg, self.w, self.K
         p = "layers.%d." % i
-        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        Hq, Hkv, hd = self.Hq, self.Hkv, cfg.head_dim
         h1, _, _, rstd1 = K.norm_fwd(x, w.p(p + "attn_norm"), eps=cfg.rms_eps)
-        qkv = w.linear(h1, p + "wqkv")
+        qkv, h1f = w.col_linear(h1, p + "wqkv")
         K.rope_(qkv, self.cos, self.sin, T, Hq, hd, col_offset=0)
         K.rope_(qkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd)
         q, k, v = self._split_qkv(qkv, B, T)
         o, lse = K.flash_fwd(q, k, v, causal=True)
         o2 = o.view(B * T, Hq * hd)
-        x1 = w.linear(o2, p + "wo", residual=x)
+        x1 = w.row_linear(o2, p + "wo", residual=x)
         h2, _, _, rstd2 = K.norm_fwd(x1, w.p(p + "mlp_norm"), eps=cfg.rms_eps)
-        gu = w.linear(h2, p + "w_gu")
+        gu, h2f = w.col_linear(h2, p + "w_gu")
         hm = K.swiglu_fwd(gu)
-        x2 = w.linear(hm, p + "w_down", residual=x1)
+        x2 = w.row_linear(hm, p + "w_down", residual=x1)
         self.kernel_launches += 11
-        return x2, (x, h1, rstd1, qkv, o, lse, x1, h2, rstd2, gu, hm)
+        return x2, (x, h1f, rstd1, qkv, o, lse, x1, h2f, rstd2, gu, hm)
 
     def _split_qkv(self, qkv, B, T):
-        cfg = self.cfg
-        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
-        q3 = qkv.view(B, T, cfg.qkv_dim)
+        Hq, Hkv, hd = self.Hq, self.Hkv, self.cfg.head_dim
+        q3 = qkv.view(B, T, self.qkv_local)
         q = q3[:, :, :Hq * hd].view(B, T, Hq, hd)
         k = q3[:, :, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
         v = q3[:, :, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
         return q, k, v
 
     def _layer_bwd(self, i: int, dx2: torch.Tensor, ctx, B: int, T: int, accumulate: bool):
-        cfg, w = self.cfg, self.w
+        cfg, w, K = self.cfg, self.w, self.K
         p = "layers.%d." % i
-        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
-        x, h1, rstd1, qkv, o, lse, x1, h2, rstd2, gu, hm = ctx
+        Hq, Hkv, hd = self.Hq, self.Hkv, cfg.head_dim
+        x, h1f, rstd1, qkv, o, lse, x1, h2f, rstd2, gu, hm = ctx
         # MLP
-        dhm = w.dgrad(dx2, p + "w_down")
-        w.wgrad(dx2, hm, p + "w_down", accumulate)
+        dhm, dx2f = w.row_dgrad(dx2, p + "w_down")
+        w.wgrad(dx2f, hm, p + "w_down", accumulate)
         dgu = K.swiglu_bwd(gu, dhm, inplace=True)
-        dh2 = w.dgrad(dgu, p + "w_gu")
-        w.wgrad(dgu, h2, p + "w_gu", accumulate)
+        dh2 = w.col_dgrad(dgu, p + "w_gu")
+        w.wgrad(dgu, h2f, p + "w_gu", accumulate)
         dx1, _, _ = K.norm_bwd(dh2, x1, w.p(p + "mlp_norm"), None, rstd2, dres=dx2, dw=w.vector_grad(p + "mlp_norm"),
                                accumulate=accumulate)
         # attention
         o2 = o.view(B * T, Hq * hd)
-        do = w.dgrad(dx1, p + "wo")
-        w.wgrad(dx1, o2, p + "wo", accumulate)
+        do, dx1f = w.row_dgrad(dx1, p + "wo")
+        w.wgrad(dx1f, o2, p + "wo", accumulate)
         dqkv = torch.empty_like(qkv)
         q, k, v = self._split_qkv(qkv, B, T)
         dq, dk, dv = self._split_qkv(dqkv, B, T)
         K.flash_bwd(q, k, v, o, lse, do.view(B, T, Hq, hd), causal=True, dq=dq, dk=dk, dv=dv)
         K.rope_(dqkv, self.cos, self.sin, T, Hq, hd, col_offset=0, backward=True)
         K.rope_(dqkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd, backward=True)
-        dh1 = w.dgrad(dqkv, p + "wqkv")
-        w.wgrad(dqkv, h1, p + "wqkv", accumulate)
+        dh1 = w.col_dgrad(dqkv, p + "wqkv")
+        w.wgrad(dqkv, h1f, p + "wqkv", accumulate)
         dx, _, _ = K.norm_bwd(dh1, x, w.p(p + "attn_norm"), None, rstd1, dres=dx1, dw=w.vector_grad(p + "attn_norm"),
                               accumulate=accumulate)
         self.kernel_launches += 22
@@ -322,7 +370,7 @@ class LlamaEngine:
 
         fused_update: sharded weights may reduce and apply each bucket's gradients as soon as its backward is done
         (only valid for the last micro-batch of a step, after `begin_step`)."""
-        cfg, w = self.cfg, self.w
+        cfg, w, K = self.cfg, self.w, self.K
         B, T = tokens.shape
         M = B * T
         tok = tokens.reshape(-1)
@@ -337,15 +385,15 @@ class LlamaEngine:
                 x, ctx = self._layer_fwd(i, x, B, T)
                 saved.append(ctx)
         hf, _, _, rstd_f = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
-        logits = w.linear(hf, "lm_head")
-        stats = K.ce_stats(logits, tgt)
-        rows = K.ce_finish(logits, tgt, stats, grad_scale=loss_scale / (M * self.world_size))
+        logits, hff = w.col_linear(hf, "lm_head")
+        stats = w.reduce_ce_stats(K.ce_stats(logits, tgt, w.vocab_start))
+        rows = K.ce_finish(logits, tgt, stats, vocab_start=w.vocab_start, grad_scale=loss_scale / (M * self.world_size))
         loss = rows.sum() / M
-        dhf = w.dgrad(logits, "lm_head")
-        w.wgrad(logits, hf, "lm_head", accumulate)
+        dhf = w.col_dgrad(logits, "lm_head")
+        w.wgrad(logits, hff, "lm_head", accumulate)
         if fused_update:
             w.bucket_done("head")
-        del logits
+        del logits, hff
         dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate)
         for i in reversed(range(cfg.n_layers)):
             if self.ckpt:
@@ -365,13 +413,14 @@ class LlamaEngine:
         return loss
 
     def forward_logits(self, tokens: torch.Tensor) -> torch.Tensor:
-        cfg, w = self.cfg, self.w
+        """Logits of this rank's vocabulary slice for every token ([B, T, vocab / tp])."""
+        cfg, w, K = self.cfg, self.w, self.K
         B, T = tokens.shape
         x = w.embedding(tokens.reshape(-1))
         for i in range(cfg.n_layers):
             x, _ = self._layer_fwd(i, x, B, T)
         hf, _, _, _ = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
-        return w.linear(hf, "lm_head").view(B, T, cfg.vocab_size)
+        return w.col_linear(hf, "lm_head")[0].view(B, T, cfg.vocab_size // w.tp)
 
     def optimizer_step(self, dyn=None):
         self.step_count += 1

@@ -65,6 +65,7 @@ _SIGS = {
     "lt_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _i, ctypes.c_uint, _i, _i, _i, _vp],
     "lt_embedding_fwd_sharded": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
+    "lt_gather_shards": [_vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_gemm_num_tiles": [_i, _i, _i],
     "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
     "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
@@ -491,6 +492,16 @@ def embedding_fwd_sharded(idx, table_ptrs, V, D, rows_per_rank, world, dtype=tor
                                          idx.numel(), D, V, rows_per_rank, world, _stream())
     _check(rc, "lt_embedding_fwd_sharded")
     return out
+
+
+def gather_shards(shard_ptrs, segs, dsts, max_ctas: int = 0):
+    """All-gather of row shards by peer loads.  segs: (shard_off, n) element pairs; dsts: one local tensor per segment
+    that receives every rank's `n` elements in rank order (world * n elements)."""
+    world = len(shard_ptrs)
+    seg_arr = (c_longlong * (3 * len(segs)))(*[int(x) for s in segs for x in (s[0], s[1], 0)])
+    rc = _fn("lt_gather_shards")(ctypes.cast(_ptr_array(shard_ptrs), c_void_p), world, ctypes.cast(seg_arr, c_void_p),
+                                 ctypes.cast(_ptr_array([d.data_ptr() for d in dsts]), c_void_p), len(segs), max_ctas, _stream())
+    _check(rc, "lt_gather_shards")
 
 
 def signal_barrier(my_flags, peer_flag_ptrs, slot: int, epoch: int, world: int, rank: int):

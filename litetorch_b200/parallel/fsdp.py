@@ -26,7 +26,7 @@ from typing import Dict, List
 import torch
 import torch.distributed as dist
 
-from ..models.llama import LlamaConfig, ParamSpec, param_specs
+from ..models.llama import LlamaConfig, ParamSpec, SingleTPMixin, param_specs
 from ..ops import kernels as K
 
 
@@ -98,7 +98,7 @@ def check_symmetric_canaries() -> int:
 _STAGE_KEYS = ("wqkv", "wo", "w_gu", "w_down", "lm_head")
 
 
-class ShardedWeights:
+class ShardedWeights(SingleTPMixin):
     SLOT_BARRIER = 0
 
     def __init__(self, cfg: LlamaConfig, device, seed: int = 0, n_comm: int = 8, use_multimem: bool = False):

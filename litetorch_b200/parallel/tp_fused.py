@@ -45,24 +45,32 @@ class TPFusedContext:
         self.barrier_epoch += 1
         K.signal_barrier(self.flags.tensor, self.flags.ptrs, 0, self.barrier_epoch, self.world, self.rank)
 
-    def gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, bias=None, b_major: int = 0):
-        """Returns (y [M, N], x_full [M, K] view of the local gathered buffer, valid until the next gather)."""
+    def gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, bias=None, b_major: int = 0, full_out: torch.Tensor = None):
+        """y = all_gather(x_shard) @ op(w) with the gather inside the GEMM kernel.
+        b_major 0: w is [N, K] (y = x @ w^T); 1: w is [K, N] (y = x @ w).
+        Returns (y [M, N], x_full [M, K]).  x_full is `full_out` when given (a local [M, K] tensor the caller keeps),
+        else a view of the context's own buffer that is only valid until the next gather."""
         rows, Kd = x_shard.shape
         M = rows * self.world
         slot = self.ag_calls & 1
         self.ag_calls += 1
         sh = self.shard[slot].tensor[:rows * Kd].view(rows, Kd)
         sh.copy_(x_shard)
-        full = self.full[:M * Kd].view(M, Kd)
+        full = self.full[:M * Kd].view(M, Kd) if full_out is None else full_out
+        assert full.shape == (M, Kd) and full.is_contiguous()
         # This rank's own rows need no gather: they go straight into the assembled operand and their chunk flags are
         # set to this call's epoch, so the gather CTAs only fetch the peers' rows and the first tiles start at once.
         full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
         if rows % 128 == 0:
             self.gather_flags[self.rank * rows // 128:(self.rank + 1) * rows // 128].fill_(self.ag_calls)
         self._barrier()                                    # every rank's shard is in place
-        assert b_major == 0
-        y = K.ag_gemm(None, full, gather_operand=0, shard_ptrs=self.shard[slot].ptrs, world=self.world, rank=self.rank,
-                      rows_per_rank=rows, flags=self.gather_flags, epoch=self.ag_calls, other=w, bias=bias, n_comm=self.n_comm)
+        if b_major == 0:
+            y = K.ag_gemm(None, full, gather_operand=0, shard_ptrs=self.shard[slot].ptrs, world=self.world, rank=self.rank,
+                          rows_per_rank=rows, flags=self.gather_flags, epoch=self.ag_calls, other=w, bias=bias,
+                          n_comm=self.n_comm)
+        else:
+            assert bias is None
+            y = _ag_gemm_nn(self, full, w, slot, rows)
         return y, full
 
     def gemm_scatter(self, x: torch.Tensor, w: torch.Tensor, b_major: int = 0, bias=None, residual=None):

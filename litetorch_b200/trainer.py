@@ -4,7 +4,9 @@
     loss = tr.step(tokens_cpu, targets_cpu)       # pinned host int64 [B, T] -> float
 
 `step` copies the batch from pinned host memory, runs forward + backward + AdamW on the sm_100a kernels
-(ZeRO-3 sharded over the process group when world_size > 1) and reads the loss back.
+(ZeRO-3 sharded over the process group when world_size > 1; with `tp > 1` the ranks form a dp x tp mesh, matrices are
+cut over the tp axis with sequence parallelism and their slices are ZeRO-3 sharded over the dp axis) and reads the
+loss back.  Every rank of a tensor-parallel group must be given the same batch.
 The reference's equivalent is the hand-written loop `zero_grad / forward / backward / step / loss.item()`
 of its example trainers (train_cat_dog.py:312-319).
 """
@@ -22,7 +24,7 @@ from .models.llama import LlamaConfig, LlamaEngine
 class Trainer:
     def __init__(self, cfg: LlamaConfig, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, seed: int = 0, activation_checkpointing: bool = False,
-                 device: Optional[str] = None, parallel: str = "auto"):
+                 device: Optional[str] = None, parallel: str = "auto", tp: int = 1):
         self.rank = int(os.environ.get("RANK", "0"))
         self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -30,13 +32,21 @@ class Trainer:
         torch.cuda.set_device(self.device)
         self.cfg = cfg
         weights = None
-        if self.world_size > 1 and parallel in ("auto", "fsdp"):
+        self.tp = tp
+        self.dp = 1
+        if self.world_size > 1 and parallel in ("auto", "fsdp", "hybrid"):
             from .parallel.fsdp import ShardedWeights, ensure_process_group
             ensure_process_group()
-            weights = ShardedWeights(cfg, self.device, seed=seed)
+            if tp > 1 or parallel == "hybrid":
+                from .parallel.hybrid import HybridWeights
+                weights = HybridWeights(cfg, self.device, tp=tp, seed=seed)
+            else:
+                weights = ShardedWeights(cfg, self.device, seed=seed)
+            self.dp = self.world_size // tp
+        self.dp_rank = self.rank // tp
         self.engine = LlamaEngine(cfg, self.device, weights=weights, seed=seed, lr=lr, betas=betas, eps=eps,
                                   weight_decay=weight_decay, activation_checkpointing=activation_checkpointing,
-                                  world_size=self.world_size if weights is not None else 1)
+                                  world_size=self.dp)
         self._tok = None
         self._tgt = None
         self.h2d_bytes = 0
@@ -46,18 +56,18 @@ class Trainer:
     @classmethod
     def from_config(cls, run, **kw) -> "Trainer":
         """Build the trainer of a `config.RunConfig` (a preset name or JSON path is loaded first).  This entry point
-        covers the data-parallel / ZeRO-3 layouts of the hand-scheduled Llama engine; layouts with tensor, context,
-        expert or pipeline parallelism run through `models/run_config.py`."""
+        covers the dp (ZeRO-3) x tp (+ sequence parallel) layouts of the hand-scheduled Llama engine; layouts with
+        context, expert or pipeline parallelism run through `models/run_config.py`."""
         from . import config as _config
         if isinstance(run, str):
             run = _config.load(run)
         p = run.parallel
-        if p.tp * p.pp * p.cp * max(p.ep, 1) != 1:
-            raise ValueError("Trainer.from_config runs dp / ZeRO-3 layouts; use models.run_config for tp/pp/cp/ep")
+        if p.pp * p.cp * max(p.ep, 1) != 1:
+            raise ValueError("Trainer.from_config runs dp (ZeRO-3) x tp layouts; use models.run_config for pp/cp/ep")
         o = run.optim
         return cls(run.llama_config(), lr=o.lr, betas=(o.beta1, o.beta2), eps=o.eps, weight_decay=o.weight_decay,
                    seed=run.seed, activation_checkpointing=run.activation_checkpointing,
-                   parallel="fsdp" if p.zero_stage >= 1 else "none", **kw)
+                   parallel=("hybrid" if p.tp > 1 else "fsdp") if (p.zero_stage >= 1 or p.tp > 1) else "none", tp=p.tp, **kw)
 
     def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Batch already on the device; returns the loss as a device scalar (no host sync)."""
@@ -79,7 +89,7 @@ class Trainer:
             rec = {"step": self._step_no, "loss": float(out)}
             if self._last_t is not None:          # host time between two loss read-backs = one full step
                 ms = (now - self._last_t) * 1e3
-                rec.update(step_ms=round(ms, 3), tokens_per_s=round(tokens_cpu.numel() * self.world_size / ms * 1e3, 1))
+                rec.update(step_ms=round(ms, 3), tokens_per_s=round(tokens_cpu.numel() * self.dp / ms * 1e3, 1))
             self._last_t = now
             self._metrics.write(**rec)
         return float(out)
