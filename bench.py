@@ -45,8 +45,9 @@ def _parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3-8b", choices=list(SHAPES))
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0: 1 on one GPU, else 2)")
-    ap.add_argument("--ckpt", default="auto", choices=["auto", "on", "off"],
-                    help="activation checkpointing (auto: on where weights + optimizer state of one rank leave no room)")
+    ap.add_argument("--ckpt", default="auto",
+                    help="activation checkpointing: auto (as many layers as the memory of one rank needs), on, off, "
+                         "or the number of layers whose activations are recomputed in the backward pass")
     ap.add_argument("--no-comm-breakdown", action="store_true",
                     help="skip the extra communication-free steps that give exposed_comm_ms_per_step at N > 1")
     ap.add_argument("--no-extras", action="store_true", help="skip the llama_1b and probe measurements")
@@ -193,9 +194,11 @@ def run_ours(args):
     big = args.model == "llama3-8b"
     tp = args.tp or int(os.environ.get("LT_BENCH_TP", "0")) or (2 if (world > 1 and big) else 1)
     dp = world // tp
-    # One rank of the 8B shape holds 128 GB of parameters, gradients and fp32 optimizer state when nothing is sharded:
-    # the activations of 32 layers no longer fit beside them, so every layer is recomputed in the backward pass.
-    ckpt = (big and world == 1) if args.ckpt == "auto" else args.ckpt == "on"
+    if args.ckpt == "auto":
+        ckpt = 0        # 8B on one GPU: 156 GB peak of 180 GB without recomputation (falls back to full recomputation if it does not fit)
+    else:
+        ckpt = {"on": cfg.n_layers, "off": 0}.get(args.ckpt, None)
+        ckpt = int(args.ckpt) if ckpt is None else ckpt
     n_seq = per_gpu * tp                           # sequences of one tensor-parallel group (all its ranks get the same batch)
 
     def sync():
@@ -203,10 +206,25 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt, parallel="hybrid" if tp > 1 else "auto")
     host, devb = _batches(cfg, n_seq, T, 1000 + rank // tp, dev)
     sampler = ClockSampler(local) if rank == 0 else None
-    ms_total, e2e_ms, launches, loss_val, clocks = _measure(tr, host, devb, args.steps, args.warmup, sync, sampler)
+    try:
+        tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt, parallel="hybrid" if tp > 1 else "auto")
+        ms_total, e2e_ms, launches, loss_val, clocks = _measure(tr, host, devb, args.steps, args.warmup, sync, sampler)
+    except torch.cuda.OutOfMemoryError:
+        # Single GPU only (no peer is left waiting): saved activations did not fit beside 128 GB of weights and
+        # optimizer state on this device, so recompute every layer in the backward pass instead.
+        if world > 1 or ckpt == cfg.n_layers:
+            raise
+        if sampler is not None:
+            sampler.stop()
+        tr = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        ckpt = cfg.n_layers
+        tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt)
+        ms_total, e2e_ms, launches, loss_val, clocks = _measure(tr, host, devb, args.steps, args.warmup, sync, sampler)
     h2d_bytes, d2h_bytes = tr.h2d_bytes, tr.d2h_bytes
     status = K.status_fetch()
     peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
@@ -296,7 +314,7 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": _describe(cfg), "global_batch": per_gpu * world, "seq_len": T, "parallelism": par,
-                       "dp": dp, "tp": tp, "activation_checkpointing": bool(ckpt),
+                       "dp": dp, "tp": tp, "checkpointed_layers": int(ckpt),
                        "optimizer": "AdamW fp32 master+states, bf16 params/grads",
                        "l2": "no flush: the step's working set (weights and activations, tens of GB) is far larger than the 126 MB L2"},
             "clocks": clocks,

@@ -294,7 +294,9 @@ class LlamaEngine:
         self.K = kernels_for(self.device)
         self.w = weights if weights is not None else LocalWeights(cfg, self.device, seed)
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
-        self.ckpt = activation_checkpointing
+        # True: every layer is recomputed in the backward pass; an integer k: only the first k layers are
+        self.ckpt_layers = cfg.n_layers if activation_checkpointing is True else int(activation_checkpointing or 0)
+        self.ckpt = self.ckpt_layers > 0
         self.world_size = world_size          # data-parallel replicas the gradient is averaged over
         self.step_count = 0
         self.cos, self.sin = rope_tables(cfg, self.device)
@@ -378,7 +380,7 @@ class LlamaEngine:
         x = w.embedding(tok)
         saved = []
         for i in range(cfg.n_layers):
-            if self.ckpt:
+            if i < self.ckpt_layers:
                 saved.append(x)
                 x, _ = self._layer_fwd(i, x, B, T)
             else:
@@ -396,7 +398,7 @@ class LlamaEngine:
         del logits, hff
         dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate)
         for i in reversed(range(cfg.n_layers)):
-            if self.ckpt:
+            if i < self.ckpt_layers:
                 _, ctx = self._layer_fwd(i, saved[i], B, T)
             else:
                 ctx = saved[i]

@@ -213,6 +213,11 @@ class HybridWeights:
         self.hyper = None
         self._pending = False
         self.tpctx = None
+        # Create every group's communicator now, with a first small collective, rather than inside the first step,
+        # where seconds of skew between ranks would meet the bounded waits of the fused kernels.
+        for grp in (self.tp_group, self.dp_group, None):
+            if grp is not None or self.world > 1:
+                dist.all_reduce(torch.zeros(1, device=dev), group=grp)
         if self.cuda:
             torch.cuda.synchronize()
         dist.barrier()
@@ -509,18 +514,18 @@ class HybridWeights:
                          eps=eps, wd=0.0, step=step, adamw=True, dyn=dyn)
 
     def finish_step(self):
-        """Join the side streams; with dp > 1 cross a barrier of the dp group so that every shard is updated before
-        the next step gathers it.  Staged weights of this step become stale."""
+        """Join the side streams and cross a barrier of ALL ranks: the next step reads parameter shards of dp peers
+        (weight gathers) and of any rank (embedding rows), so every rank's update must be complete first.  Staged
+        weights of this step become stale."""
         if self.fused:
             cur = torch.cuda.current_stream()
             if self._pending:
                 cur.wait_stream(self.side)
                 self._pending = False
             cur.wait_stream(self.gstream)
-            if self.dp > 1:
+            if self.world > 1:
                 self.flag_epoch[0] += 1
-                self.K.signal_barrier(self.sym_flags.tensor, self._dp_ptrs(self.sym_flags), 0, self.flag_epoch[0], self.dp,
-                                      self.dp_rank)
+                self.K.signal_barrier(self.sym_flags.tensor, self.sym_flags.ptrs, 0, self.flag_epoch[0], self.world, self.rank)
         self.version += 1
         if self.dp > 1:
             if self.hyper is not None and not self._trace_done and self._trace:
