@@ -66,6 +66,7 @@ class _AdamBase(Optimizer):
         self.m = [None] * len(self.params)
         self.v = [None] * len(self.params)
         self.master = [None] * len(self.params)  # fp32 master copies of low-precision parameters
+        self._pver = [None] * len(self.params)   # version counter of each low-precision parameter after our last write
         self._table = None
 
     def _state_device(self, p):
@@ -78,6 +79,26 @@ class _AdamBase(Optimizer):
             self.v[i] = torch.zeros(p.shape, dtype=torch.float32, device=dev)
             if p.dtype != torch.float32:
                 self.master[i] = p.detach().to(device=dev, dtype=torch.float32).clone()
+                self._pver[i] = p._version
+
+    def _refresh_masters(self, ts):
+        """A low-precision parameter that was written by someone else since our last step (a checkpoint load, a manual
+        copy_) no longer matches its fp32 master: take over the new values.  Elements whose master still rounds to the
+        parameter keep their extra fp32 bits, so loading the same checkpoint into both is exact in either order."""
+        for i, p in enumerate(ts):
+            mst = self.master[i]
+            if mst is None or self._pver[i] == p._version:
+                continue
+            cur = p.detach().to(mst.device)
+            stale = mst.to(p.dtype) != cur
+            if bool(stale.any()):
+                mst[stale] = cur[stale].float()
+            self._pver[i] = p._version
+
+    def _mark_versions(self, ts):
+        for i, p in enumerate(ts):
+            if self.master[i] is not None:
+                self._pver[i] = p._version
 
     def _native_ok(self, ts):
         for t in ts:
@@ -161,10 +182,12 @@ class _AdamBase(Optimizer):
     def step(self):
         self.step_count += 1
         ts = self._tensors()
+        self._refresh_masters(ts)
         if ts and self._native_ok(ts):
             self._step_native(ts)
         else:
             self._step_torch(ts)
+        self._mark_versions(ts)
 
 
 class Adam(_AdamBase):

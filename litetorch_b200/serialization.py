@@ -152,26 +152,42 @@ def _opt_kind(opt):
     raise CheckpointError("unsupported optimizer type %s" % type(opt).__name__)
 
 
+_MASTER_TRAILER = 0x5254534D          # "MSTR": optional record after the moments of an LTAD / LTAW file
+
+
+def _state_target(p):
+    """The tensor an optimizer state belongs to: the rank's shard for FSDP-sharded parameters, else the parameter."""
+    shard = getattr(p, "shard", None)
+    return _unwrap(shard) if shard is not None else _unwrap(p)
+
+
 def _adam_states(opt):
+    """(m, v) per parameter in the parameter's (or its shard's) shape; a state that does not exist on this rank
+    (a replicated parameter of ZeRO3Optimizer that another rank owns, a parameter that never had a gradient) is
+    written as an empty tensor."""
     from . import optim as O
     ms, vs = [], []
+    none = torch.zeros(0)
     for i, p in enumerate(opt.params):
-        shape = _unwrap(p).shape
         if isinstance(opt, O.AdamW8bit):
-            m = opt.m_q[i].float() * opt.m_scale[i] if opt.m_q[i] is not None else torch.zeros(shape)
-            v = opt.v_q[i].float() * opt.v_scale[i] if opt.v_q[i] is not None else torch.zeros(shape)
+            m = opt.m_q[i].float() * opt.m_scale[i] if opt.m_q[i] is not None else none
+            v = opt.v_q[i].float() * opt.v_scale[i] if opt.v_q[i] is not None else none
         elif isinstance(opt, O.AdamWFP8):
-            m = opt.m8[i].float() * opt.m_scale[i] if opt.m8[i] is not None else torch.zeros(shape)
-            v = opt.v8[i].float() * opt.v_scale[i] if opt.v8[i] is not None else torch.zeros(shape)
+            m = opt.m8[i].float() * opt.m_scale[i] if opt.m8[i] is not None else none
+            v = opt.v8[i].float() * opt.v_scale[i] if opt.v8[i] is not None else none
         else:
-            m = opt.m[i] if opt.m[i] is not None else torch.zeros(shape)
-            v = opt.v[i] if opt.v[i] is not None else torch.zeros(shape)
+            m = opt.m[i] if opt.m[i] is not None else none
+            v = opt.v[i] if opt.v[i] is not None else none
         ms.append(m)
         vs.append(v)
     return ms, vs
 
 
 def save_optimizer_state(opt, filepath: str) -> None:
+    """SGD -> LTSG, RMSprop -> LTRP, Adam -> LTAD, AdamW family -> LTAW.  The Adam formats hold step count, m and v
+    (the reference's layout, src/serialization/checkpoint.cpp) and, when the optimizer keeps fp32 master copies of
+    low-precision parameters, those masters in a trailing record, so that a resumed bf16 run continues from the
+    exact fp32 weights instead of their rounded copies."""
     lib = _lib()
     kind = _opt_kind(opt)
     w = lib.lt_ckpt_writer_open(filepath.encode(), kind)
@@ -184,6 +200,12 @@ def save_optimizer_state(opt, filepath: str) -> None:
         ms, vs = _adam_states(opt)
         for t in ms + vs:
             _write_tensor(lib, w, t)
+        masters = getattr(opt, "master", None)
+        if masters is not None and any(m is not None for m in masters):
+            lib.lt_ckpt_write_u32(w, _MASTER_TRAILER)
+            lib.lt_ckpt_write_u32(w, n)
+            for m in masters:
+                _write_tensor(lib, w, m if m is not None else torch.zeros(0))
     else:
         lib.lt_ckpt_write_u32(w, n)
         states = opt.velocity if kind == b"LTSG" else opt.square_avg
@@ -206,12 +228,25 @@ def load_optimizer_state(opt, filepath: str) -> None:
                 raise CheckpointError("%s holds %d states, the optimizer has %d parameters" % (filepath, n, n_model))
             ms = [r.tensor() for _ in range(n)]
             vs = [r.tensor() for _ in range(n)]
+            masters = None
+            try:
+                tag = r.u32()
+            except CheckpointError:
+                tag = None                                  # a file without the master record (the reference's layout)
+            if tag == _MASTER_TRAILER:
+                if r.u32() != n:
+                    raise CheckpointError("%s: master record count differs" % filepath)
+                masters = [r.tensor() for _ in range(n)]
             for i, p in enumerate(opt.params):
-                if list(ms[i].shape) != list(_unwrap(p).shape) or list(vs[i].shape) != list(_unwrap(p).shape):
-                    raise CheckpointError("state %d: shape differs from its parameter" % i)
+                want = list(_state_target(p).shape)
+                for t in (ms[i], vs[i]):
+                    if t.numel() and list(t.shape) != want:
+                        raise CheckpointError("state %d: shape %s differs from its parameter's %s" % (i, list(t.shape), want))
             opt.step_count = step
             for i, p in enumerate(opt.params):
-                pt = _unwrap(p)
+                pt = _state_target(p)
+                if ms[i].numel() == 0 and pt.numel() != 0:
+                    continue                                # no state on this rank for this parameter
                 if isinstance(opt, O.AdamW8bit):
                     opt.m_q[i], opt.m_scale[i] = opt._quant(ms[i].to(pt.device))
                     opt.v_q[i], opt.v_scale[i] = opt._quant(vs[i].to(pt.device))
@@ -222,6 +257,14 @@ def load_optimizer_state(opt, filepath: str) -> None:
                     opt._ensure_state(i, pt)
                     opt.m[i].copy_(ms[i])
                     opt.v[i].copy_(vs[i])
+                    if masters is not None and masters[i].numel() and opt.master[i] is not None:
+                        if list(masters[i].shape) != want_shape(pt):
+                            raise CheckpointError("master %d: shape differs from its parameter" % i)
+                        # Take the saved fp32 values; the next step keeps them wherever they round to the parameter
+                        # as it is then (whether the parameters are loaded before or after this call) and falls back
+                        # to the parameter's own value elsewhere.
+                        opt.master[i].copy_(masters[i])
+                        opt._pver[i] = None
         else:
             n = r.u32()
             if n != n_model:
@@ -235,6 +278,31 @@ def load_optimizer_state(opt, filepath: str) -> None:
                 tgt[i] = ss[i].to(_unwrap(p).device, torch.float32 if kind == b"LTRP" else _unwrap(p).dtype)
     finally:
         r.close()
+
+
+def want_shape(t) -> list:
+    return list(t.shape)
+
+
+def save_optimizer_sharded(opt, directory: str, rank: int, world: int, tag: str = "optim") -> None:
+    """One optimizer-state file per rank (shard-shaped states of ZeRO3Optimizer / FSDP) plus a manifest by rank 0."""
+    os.makedirs(directory, exist_ok=True)
+    save_optimizer_state(opt, os.path.join(directory, "%s.rank%05d.bin" % (tag, rank)))
+    if rank == 0:
+        man = {"format": "optimizer-sharded", "tag": tag, "world_size": world,
+               "files": ["%s.rank%05d.bin" % (tag, r) for r in range(world)]}
+        tmp = os.path.join(directory, "%s.manifest.json.tmp" % tag)
+        with open(tmp, "w") as f:
+            json.dump(man, f, indent=1)
+        os.replace(tmp, os.path.join(directory, "%s.manifest.json" % tag))
+
+
+def load_optimizer_sharded(opt, directory: str, rank: int, world: int, tag: str = "optim") -> None:
+    with open(os.path.join(directory, "%s.manifest.json" % tag)) as f:
+        man = json.load(f)
+    if man["world_size"] != world:
+        raise CheckpointError("optimizer state was written by %d ranks, this job has %d" % (man["world_size"], world))
+    load_optimizer_state(opt, os.path.join(directory, man["files"][rank]))
 
 
 def save(obj, filepath: str) -> None:

@@ -71,3 +71,128 @@ def test_crash_after_checkpoint_then_resume_matches_uninterrupted_run(tmp_path):
     open(os.path.join(ck, "model.ltw"), "wb").write(bytes(blob))
     r = subprocess.run([sys.executable, script, "resume", ck], capture_output=True, text=True, timeout=600)
     assert r.returncode != 0 and "CRC" in (r.stdout + r.stderr).upper()
+
+
+def _bf16_run(steps, params, opt, data):
+    import torch
+    from litetorch_b200.core import _unwrap
+    for x, y in data[:steps]:
+        opt.zero_grad()
+        w1, w2 = (_unwrap(p) for p in params)
+        loss = ((torch.tanh(x.bfloat16() @ w1) @ w2).float() - y).pow(2).mean()
+        loss.backward()
+        opt.step()
+
+
+def _bf16_setup(seed):
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor
+    g = torch.Generator().manual_seed(seed)
+    params = [Tensor((torch.randn(16, 32, generator=g) * 0.3).bfloat16().requires_grad_(True)),
+              Tensor((torch.randn(32, 4, generator=g) * 0.3).bfloat16().requires_grad_(True))]
+    return params, lt.optim.AdamW(params, lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.1)
+
+
+def test_bf16_parameters_resume_exactly_in_either_load_order(tmp_path):
+    """AdamW keeps fp32 masters of bf16 parameters; a checkpoint carries them, and a resumed run must neither write
+    stale masters back over loaded weights nor lose the masters' low bits, whichever file is loaded first."""
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200.core import _unwrap
+    g = torch.Generator().manual_seed(11)
+    data = [(torch.randn(8, 16, generator=g), torch.randn(8, 4, generator=g)) for _ in range(6)]
+    ref_p, ref_o = _bf16_setup(1)
+    _bf16_run(6, ref_p, ref_o, data)
+    p, o = _bf16_setup(1)
+    _bf16_run(3, p, o, data)
+    lt.save_parameters(p, str(tmp_path / "m.ltw"))
+    lt.save(o, str(tmp_path / "o.bin"))
+    for order in ("params_first", "optimizer_first"):
+        q, qo = _bf16_setup(99)                       # another initialisation: everything must come from the files
+        _bf16_run(1, q, qo, data[5:])                 # and the optimizer already holds (soon stale) masters
+        if order == "params_first":
+            lt.load_parameters(q, str(tmp_path / "m.ltw"))
+            lt.load(qo, str(tmp_path / "o.bin"))
+        else:
+            lt.load(qo, str(tmp_path / "o.bin"))
+            lt.load_parameters(q, str(tmp_path / "m.ltw"))
+        _bf16_run(3, q, qo, data[3:])
+        for a, b, ma, mb in zip(q, ref_p, qo.master, ref_o.master):
+            assert torch.equal(_unwrap(a), _unwrap(b)), order
+            assert torch.equal(ma, mb), order
+    # a parameter overwritten by hand is taken over by the master instead of being reverted at the next step
+    with torch.no_grad():
+        _unwrap(p[0]).fill_(0.5)
+    _bf16_run(1, p, o, data[3:])
+    assert abs(float(_unwrap(p[0]).float().mean()) - 0.5) < 0.05
+
+
+ZERO3_WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, %(root)r)
+import torch.distributed as dist
+import litetorch_b200 as lt
+from litetorch_b200.core import Tensor, _unwrap
+from litetorch_b200.parallel.fsdp_api import FullyShardedDataParallel
+from litetorch_b200.serialization import save_optimizer_sharded, load_optimizer_sharded, save_sharded, load_sharded
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%%s" %% os.environ["MASTER_PORT"], rank=rank, world_size=world)
+ck = sys.argv[1]
+
+def build(seed):
+    torch.manual_seed(seed)
+    m = lt.nn.Sequential([lt.nn.Linear(12, 10), lt.nn.Linear(10, 6)])
+    f = FullyShardedDataParallel(m)
+    o = lt.optim.ZeRO3Optimizer([p for p in m.parameters()], lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.1)
+    return m, f, o
+
+def steps(f, o, m, n, start):
+    out = []
+    for s in range(start, start + n):
+        g = torch.Generator().manual_seed(100 + s)
+        x = torch.randn(4, 12, generator=g)
+        f.gather_parameters()
+        for p in m.parameters():
+            _unwrap(p).grad = None
+        y = _unwrap(f.forward(Tensor(x)))
+        loss = y.pow(2).mean()
+        loss.backward()
+        f.shard_parameters()
+        o.step()
+        out.append(float(loss))
+    return out
+
+m, f, o = build(1)
+full = steps(f, o, m, 6, 0)
+m, f, o = build(1)
+first = steps(f, o, m, 3, 0)
+save_sharded(ck, [_unwrap(p.shard).detach() for p in m.parameters()], rank, world, tag="model")
+save_optimizer_sharded(o, ck, rank, world)
+dist.barrier()
+m2, f2, o2 = build(5)
+for p, t in zip(m2.parameters(), load_sharded(ck, rank, world, tag="model")):
+    with torch.no_grad():
+        _unwrap(p.shard).copy_(t.view_as(_unwrap(p.shard)))
+load_optimizer_sharded(o2, ck, rank, world)
+rest = steps(f2, o2, m2, 3, 3)
+if rank == 0:
+    print("RESULT " + json.dumps({"full": full, "first": first, "rest": rest, "step": o2.step_count}))
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_zero3_optimizer_sharded_save_and_load_on_two_ranks(tmp_path):
+    script = str(tmp_path / "zero3_worker.py")
+    with open(script, "w") as f:
+        f.write(ZERO3_WORKER % {"root": ROOT})
+    ck = str(tmp_path / "ck3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29893", script, ck]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["first"] == res["full"][:3]
+    assert all(abs(a - b) < 1e-6 for a, b in zip(res["rest"], res["full"][3:])), res
+    assert res["step"] == 6
