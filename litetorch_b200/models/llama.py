@@ -265,6 +265,13 @@ class LocalWeights(SingleTPMixin):
     def parameters(self) -> List[torch.Tensor]:
         return [self.master_view(s.name) for s in self.specs]
 
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        """Everything a restart needs besides the step count: fp32 masters and AdamW moments (flat buffers)."""
+        return {"master": self.master, "m": self.m, "v": self.v}
+
+    def after_load(self) -> None:
+        self.flat_p.copy_(self.master)
+
     def load_parameters(self, tensors: List[torch.Tensor]):
         for s, t in zip(self.specs, tensors):
             self.master_view(s.name).copy_(t.to(self.master.device, torch.float32).view(*s.shape))

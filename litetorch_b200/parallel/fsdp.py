@@ -339,3 +339,17 @@ class ShardedWeights(SingleTPMixin):
 
     def parameters(self) -> List[torch.Tensor]:
         return [self.gather_full_master(s.name) for s in self.specs]
+
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        """This rank's shard of the fp32 masters and AdamW moments plus the replicated vectors."""
+        return {"master": self.master, "m": self.m, "v": self.v, "vec_master": self.vec_master, "vec_m": self.vec_m,
+                "vec_v": self.vec_v}
+
+    def after_load(self) -> None:
+        """Rebuild the bf16 shards that the gathers read from the loaded masters; void anything staged or prefetched."""
+        self.sym_param.tensor.copy_(self.master)
+        self.vec_p.copy_(self.vec_master)
+        for k in self.stage_epoch:
+            self.stage_epoch[k] += 2
+        torch.cuda.synchronize()
+        dist.barrier()

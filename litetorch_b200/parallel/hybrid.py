@@ -590,6 +590,20 @@ class HybridWeights:
     def parameters(self) -> List[torch.Tensor]:
         return [self.gather_full_master(s.name) for s in self.specs]
 
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        """This rank's shard of the fp32 masters and AdamW moments plus the replicated vectors."""
+        return {"master": self.master, "m": self.m, "v": self.v, "vec_master": self.vec_master, "vec_m": self.vec_m,
+                "vec_v": self.vec_v}
+
+    def after_load(self) -> None:
+        """Rebuild the low-precision shards from the loaded masters; staged weights become stale."""
+        self.param_shard.copy_(self.master)
+        self.vec_p.copy_(self.vec_master)
+        self.version += 1
+        if self.cuda:
+            torch.cuda.synchronize()
+        dist.barrier()
+
     def load_parameters(self, tensors: List[torch.Tensor]) -> None:
         for s, t in zip(self.specs, tensors):
             t = t.to(self.device, torch.float32).view(*s.shape)

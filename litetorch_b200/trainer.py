@@ -24,26 +24,33 @@ from .models.llama import LlamaConfig, LlamaEngine
 class Trainer:
     def __init__(self, cfg: LlamaConfig, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, seed: int = 0, activation_checkpointing: bool = False,
-                 device: Optional[str] = None, parallel: str = "auto", tp: int = 1):
+                 device: Optional[str] = None, parallel: str = "auto", tp: int = 1, param_dtype=torch.bfloat16):
         self.rank = int(os.environ.get("RANK", "0"))
         self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
         local = int(os.environ.get("LOCAL_RANK", "0"))
         self.device = torch.device(device) if device else torch.device("cuda", local)
-        torch.cuda.set_device(self.device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
         self.cfg = cfg
         weights = None
         self.tp = tp
         self.dp = 1
         if self.world_size > 1 and parallel in ("auto", "fsdp", "hybrid"):
+            import torch.distributed as dist
             from .parallel.fsdp import ShardedWeights, ensure_process_group
+            if not dist.is_initialized() and self.device.type != "cuda":
+                dist.init_process_group("gloo")
             ensure_process_group()
-            if tp > 1 or parallel == "hybrid":
+            if tp > 1 or parallel == "hybrid" or self.device.type != "cuda":
                 from .parallel.hybrid import HybridWeights
-                weights = HybridWeights(cfg, self.device, tp=tp, seed=seed)
+                weights = HybridWeights(cfg, self.device, tp=tp, seed=seed, param_dtype=param_dtype)
             else:
                 weights = ShardedWeights(cfg, self.device, seed=seed)
             self.dp = self.world_size // tp
         self.dp_rank = self.rank // tp
+        if weights is None and (param_dtype != torch.bfloat16 or self.device.type != "cuda"):
+            from .models.llama import LocalWeights
+            weights = LocalWeights(cfg, self.device, seed, param_dtype=param_dtype)
         self.engine = LlamaEngine(cfg, self.device, weights=weights, seed=seed, lr=lr, betas=betas, eps=eps,
                                   weight_decay=weight_decay, activation_checkpointing=activation_checkpointing,
                                   world_size=self.dp)
@@ -93,6 +100,53 @@ class Trainer:
             self._last_t = now
             self._metrics.write(**rec)
         return float(out)
+
+    # ---- checkpoint / resume of the whole training state
+    def _layout(self) -> dict:
+        from dataclasses import asdict
+        return {"weights": type(self.engine.w).__name__, "world_size": self.world_size if self.engine.w.__class__.__name__ != "LocalWeights" else 1,
+                "tp": self.tp, "model": asdict(self.cfg)}
+
+    def save(self, directory: str) -> None:
+        """Write everything a restart needs: per rank, its fp32 master weights and AdamW moments (the shard it owns
+        under ZeRO-3 / tensor parallelism, the replicated norm gains included) as one LTW1 file, and by rank 0 a
+        manifest with the model, the layout and the optimizer's step count (bias correction depends on it)."""
+        from .serialization import save_sharded
+        w = self.engine.w
+        state = w.state_tensors()
+        lay = self._layout()
+        sharded = lay["world_size"] > 1
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        meta = dict(lay, names=list(state), step_count=self.engine.step_count)
+        save_sharded(directory, [t.detach().float().cpu() for t in state.values()], self.rank if sharded else 0,
+                     lay["world_size"], tag="trainer", meta=meta)
+        if sharded:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def load(self, directory: str) -> None:
+        """Resume from `save`: the checkpoint must come from the same model on the same layout (world size, tp)."""
+        import json
+        from .serialization import CheckpointError, load_sharded
+        w = self.engine.w
+        state = w.state_tensors()
+        lay = self._layout()
+        with open(os.path.join(directory, "trainer.manifest.json")) as f:
+            meta = json.load(f)["meta"]
+        for k in ("weights", "world_size", "tp", "model"):
+            if meta.get(k) != lay[k]:
+                raise CheckpointError("checkpoint %s differs: written with %r, this trainer has %r" % (k, meta.get(k), lay[k]))
+        if meta["names"] != list(state):
+            raise CheckpointError("checkpoint holds %r, this trainer expects %r" % (meta["names"], list(state)))
+        sharded = lay["world_size"] > 1
+        tensors = load_sharded(directory, self.rank if sharded else 0, lay["world_size"], tag="trainer")
+        for (name, dst), src in zip(state.items(), tensors):
+            if src.numel() != dst.numel():
+                raise CheckpointError("%s: %d elements in the file, %d in this trainer" % (name, src.numel(), dst.numel()))
+            dst.copy_(src.view_as(dst))
+        self.engine.step_count = int(meta["step_count"])
+        w.after_load()
 
     def log_metrics(self, path: str) -> None:
         """Append one JSON line per `step` (step, loss, step_ms, tokens_per_s, allocator high-water mark) to `path`."""

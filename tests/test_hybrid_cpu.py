@@ -82,3 +82,70 @@ def test_hybrid_matches_single_rank(tmp_path, nproc, tp, ckpt):
     assert res["perr"] < 1e-4
     if nproc // tp > 1:
         assert res["trace"]                                  # the prefetch schedule was recorded after the first full step
+
+
+RESUME_WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, %(root)r)
+import torch.distributed as dist
+from litetorch_b200.models.llama import LlamaConfig
+from litetorch_b200.trainer import Trainer
+from litetorch_b200.serialization import CheckpointError
+rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+tp, ck = %(tp)d, sys.argv[1]
+torch.set_num_threads(2)
+cfg = LlamaConfig.tiny()
+B, T = 2, 64
+dp = world // tp
+gen = torch.Generator().manual_seed(7)
+data = torch.randint(0, cfg.vocab_size, (6, dp * B, T + 1), generator=gen)
+def batch(s):
+    d = rank // tp
+    return data[s, d * B:(d + 1) * B, :-1].contiguous(), data[s, d * B:(d + 1) * B, 1:].contiguous()
+def make(seed):
+    return Trainer(cfg, seed=seed, tp=tp, device="cpu", param_dtype=torch.float32, parallel="hybrid" if world > 1 else "none")
+a = make(3)
+full = [a.step(*batch(s)) for s in range(6)]
+b = make(3)
+first = [b.step(*batch(s)) for s in range(3)]
+b.save(ck)
+c = make(11)                     # other weights, fresh optimizer: everything must come from the checkpoint
+c.step(*batch(5))
+c.load(ck)
+rest = [c.step(*batch(s)) for s in range(3, 6)]
+refused = False
+try:
+    import dataclasses
+    other = Trainer(dataclasses.replace(LlamaConfig.tiny(), ffn=1024), seed=3, tp=tp, device="cpu", param_dtype=torch.float32,
+                    parallel="hybrid" if world > 1 else "none")
+    other.load(ck)
+except CheckpointError:
+    refused = True
+if rank == 0:
+    print("RESULT " + json.dumps({"full": full, "first": first, "rest": rest, "refused": refused, "step": c.engine.step_count}))
+if world > 1:
+    dist.barrier()
+    dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("nproc,tp", [(1, 1), (4, 2)])
+def test_trainer_save_load_resumes_on_the_same_curve(tmp_path, nproc, tp):
+    script = os.path.join(str(tmp_path), "resume_worker.py")
+    with open(script, "w") as f:
+        f.write(RESUME_WORKER % {"root": ROOT, "tp": tp})
+    ck = os.path.join(str(tmp_path), "ck")
+    if nproc == 1:
+        cmd = [sys.executable, script, ck]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
+               "127.0.0.1", "--master-port", "29877", script, ck]
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["first"] == res["full"][:3]
+    assert all(abs(x - y) < 1e-6 for x, y in zip(res["rest"], res["full"][3:])), res
+    assert res["refused"] and res["step"] == 6

@@ -73,3 +73,25 @@ def test_trainer_from_config_and_metrics_log(tmp_path):
     assert [r["step"] for r in recs] == [1, 2, 3] and abs(recs[2]["loss"] - losses[2]) < 1e-6
     assert recs[1]["tokens_per_s"] > 0 and recs[1]["max_memory_allocated_mb"] > 0
     assert losses[2] < losses[0]
+
+
+def test_trainer_save_then_load_continues_the_loss_curve(tmp_path):
+    """The benchmarked path (Trainer -> LlamaEngine -> flat bf16 weights, fp32 master + AdamW moments, step count)
+    saved after step 3 and loaded into a trainer with other weights: the resumed losses equal the uninterrupted run."""
+    from litetorch_b200.trainer import Trainer
+    cfg = LlamaConfig.tiny()
+    g = torch.Generator().manual_seed(3)
+    data = torch.randint(0, cfg.vocab_size, (6, 2, 129), generator=g)
+    batch = lambda s: (data[s, :, :-1].contiguous(), data[s, :, 1:].contiguous())  # noqa: E731
+    a = Trainer(cfg, seed=5, parallel="none")
+    full = [a.step(*batch(s)) for s in range(6)]
+    b = Trainer(cfg, seed=5, parallel="none")
+    first = [b.step(*batch(s)) for s in range(3)]
+    b.save(str(tmp_path / "ck"))
+    c = Trainer(cfg, seed=9, parallel="none")
+    c.step(*batch(5))
+    c.load(str(tmp_path / "ck"))
+    rest = [c.step(*batch(s)) for s in range(3, 6)]
+    assert first == full[:3]
+    assert all(abs(x - y) < 2e-3 for x, y in zip(rest, full[3:])), (rest, full[3:])   # bf16 atomics in two kernels
+    assert c.engine.step_count == 6
