@@ -11,9 +11,10 @@ Nothing of litetorch_b200 is imported here.  The model is composed from the refe
 The reference has no bf16 GEMM path on CUDA (bf16 tensors fall into the fp32 branch of Ops::matmul), so
 this arm computes in fp32 (TF32 tensor cores are the reference's default for cublasSgemm).
 
-The step is first tried on a small slice under a wall-clock budget; when the full configuration cannot
-run (error, out of memory, or slower than the budget allows) the arm prints
-{"impl": "reference", "unavailable": "<why>"} and exits 0.
+A two-layer probe model is always trained and timed (key "probe": the same model bench.py's own arm times), so a
+same-configuration ratio exists even when the full configuration cannot run.  The full configuration is first
+projected from two layers at the 1.1B width under a wall-clock budget; when it cannot run (error, out of memory,
+slower than the budget allows, more than one GPU) the line carries "unavailable": "<why>" and the arm exits 0.
 """
 from __future__ import annotations
 
@@ -140,14 +141,34 @@ def _train_steps(lt, model, opt, dev, n, rnd, sync):
     return times, losses, h2d
 
 
+TINY = (512, 2, 256, 4, 2, 64, 512)                 # vocab, layers, d, q heads, kv heads, head dim, ffn: bench.py's probe model
+W1B = (32000, 22, 2048, 32, 4, 64, 5632)            # the 1.1B configuration
+W8B = (128256, 32, 4096, 32, 8, 128, 14336)         # the Llama-3-8B shape of the headline
+
+
+def _time_model(lt, dev, shape, layers, T, B, steps, warmup, sync, seed=1234):
+    V, _, D, Hq, Hkv, hd, F = shape
+    rnd = random.Random(seed)
+    model = RefLlama(lt, dev, V, layers, D, Hq, Hkv, hd, F, T, B)
+    opt = lt.optim.AdamW(model.parameters(), lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
+    if warmup:
+        _train_steps(lt, model, opt, dev, warmup, rnd, sync)
+    times, losses, h2d = _train_steps(lt, model, opt, dev, steps, rnd, sync)
+    del model, opt
+    try:
+        lt.empty_cache()
+    except Exception:
+        pass
+    return times, losses, h2d
+
+
 def run(args, micro_batch: int, seq_len: int):
+    """Prints one JSON line.  The two-layer `probe` model (the same one bench.py's own arm reports under "probe") is
+    always trained and timed, on one GPU, so that a same-configuration ratio exists; the full configuration is run
+    only when a width probe shows that it fits the time budget, else the line says `unavailable` and why."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1:
-        _unavailable("reference multi-GPU path not run: NCCLBridge::init passes a pointer where ncclCommInitRank takes the "
-                     "128-byte ncclUniqueId by value (src/distributed/distributed.cpp:888-889), its FSDP hooks "
-                     "(FSDP::fully_shard) are not bound to Python, and every process pins device 0 "
-                     "(src/backend/gpu_native/entrypoint.cu:90-94)")
-        return
+    if int(os.environ.get("RANK", "0")) != 0:
+        return                                         # the reference runs on one GPU (see below); other ranks have nothing to do
     if not os.path.isdir(REF):
         _unavailable("baseline/_ref is missing (pip install of the reference was not done on this machine)")
         return
@@ -174,46 +195,78 @@ def run(args, micro_batch: int, seq_len: int):
         except Exception:
             pass
 
-    small = args.model != "llama-1.1b"
-    V, L, D, Hq, Hkv, hd, F = (512, 2, 256, 4, 2, 64, 512) if small else (32000, 22, 2048, 32, 4, 64, 5632)
-    T = 256 if small else seq_len
-    B = micro_batch
-    rnd = random.Random(1234)
+    name = getattr(args, "model", "llama3-8b")
+    out = {"impl": "reference"}
+    # ---- the probe model: runs on the reference's stock CUDA path
     try:
-        # probe: two layers of the full width, to project the cost of a full step before committing to it
-        if not small:
-            probe = RefLlama(lt, dev, V, 2, D, Hq, Hkv, hd, F, T, B)
-            popt = lt.optim.AdamW(probe.parameters(), lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
-            pt, pl, _ = _train_steps(lt, probe, popt, dev, 2, rnd, sync)
-            per_layer = pt[-1] / 2.0
-            projected = per_layer * L * 1.1
-            del probe, popt
-            lt.empty_cache()
-            need = projected * (args.steps + args.warmup)
-            if need > BUDGET_S - (time.time() - t_start):
-                _unavailable("reference too slow for the full configuration: 2-layer probe took %.1f s/step (loss %.3f), "
-                             "projecting %.0f s/step for 22 layers and %.0f s for %d+%d steps, over the %.0f s budget; "
-                             "backend %s, fp32" % (pt[-1], pl[-1], projected, need, args.warmup, args.steps, BUDGET_S, backend))
-                return
-        model = RefLlama(lt, dev, V, L, D, Hq, Hkv, hd, F, T, B)
-        opt = lt.optim.AdamW(model.parameters(), lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
-        _train_steps(lt, model, opt, dev, args.warmup, rnd, sync)
-        times, losses, h2d = _train_steps(lt, model, opt, dev, args.steps, rnd, sync)
+        pt, pl, ph2d = _time_model(lt, dev, TINY, 2, 256, 4, 20, 5, sync)
+        out["probe"] = {"model": "llama-tiny (vocab 512, 2 layers, d 256, 4q/2kv heads x 64, SwiGLU 512)", "n_gpus": 1,
+                        "global_batch": 4, "seq_len": 256, "dtype": "fp32 (reference has no bf16 GEMM path)",
+                        "value": round(4 * 256 * 20 / sum(pt), 2), "e2e_value": round(4 * 256 * 20 / sum(pt), 2), "unit": "tokens/s",
+                        "ms_per_step": round(sum(pt) / 20 * 1e3, 3), "steps": 20, "warmup": 5, "final_loss": round(pl[-1], 4),
+                        "timing": "host wall clock around each step ending in loss.item()", "backend": backend}
     except Exception as e:
-        _unavailable("reference failed on its own stock path: %r (backend %s)" % (e, backend))
+        out["probe_error"] = repr(e)[:200]
+    if name == "llama-tiny":
+        p = out.get("probe")
+        if p is None:
+            _unavailable("reference failed on the probe model: %s" % out.get("probe_error"))
+            return
+        out.update({"metric": "train tokens/s", "value": p["value"], "unit": "tokens/s", "n_gpus": 1, "steps": 20, "warmup": 5,
+                    "ms_per_step": p["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                    "dtype": p["dtype"], "data": "synthetic",
+                    "config": {"model": "llama-tiny", "global_batch": 4, "seq_len": 256, "parallelism": "single", "backend": backend},
+                    "e2e": {"value": p["value"], "unit": "tokens/s", "h2d_bytes_per_step": 4 * 257 * 4 * 2, "d2h_bytes_per_step": 4},
+                    "gpu_launches": None})
+        print(json.dumps(out), flush=True)
+        return
+    # ---- the full configuration: project its cost from two layers at the 1.1B width (the 8B layers are 5x larger)
+    shape = W8B if name == "llama3-8b" else W1B
+    T, B = (8192, 1) if name == "llama3-8b" else (seq_len, micro_batch)
+    why = None
+    try:
+        if os.environ.get("LT_REFERENCE_WIDTH_PROBE", "1") != "0":
+            wt, wl, _ = _time_model(lt, dev, W1B, 2, 2048, 4, 1, 0, sync)
+            per_layer = wt[-1] / 2.0
+            scale = 1.0 if shape is W1B else (shape[2] * (shape[3] + 2 * shape[4]) * shape[5] + shape[2] * shape[3] * shape[5]
+                                              + 3 * shape[2] * shape[6]) / float(2048 * 2560 + 2048 * 2048 + 3 * 2048 * 5632)
+            projected = per_layer * shape[1] * scale
+            need = projected * (args.steps + args.warmup)
+            fact = ("two layers at the 1.1B width (d 2048, seq 2048, batch 4, fp32: its only working CUDA GEMM dtype) took %.1f s "
+                    "per step on this GPU (loss %.3f); the %s configuration has %d layers of %.1fx that size: about %.0f s per step, "
+                    "%.0f s for %d+%d steps against a budget of %.0f s" % (wt[-1], wl[-1], name, shape[1], scale, projected, need,
+                                                                          args.warmup, args.steps, BUDGET_S))
+            if need > BUDGET_S - (time.time() - t_start):
+                why = "reference too slow for the full configuration: " + fact
+        else:
+            why = "reference too slow for the full configuration (width probe skipped by LT_REFERENCE_WIDTH_PROBE=0)"
+    except Exception as e:
+        why = "reference failed on its own stock path at the 1.1B width: %r (backend %s)" % (e, backend)
+    if world > 1:
+        why = ((why + "; ") if why else "") + (
+            "and it cannot use %d GPUs: NCCLBridge::init passes a pointer where ncclCommInitRank takes the 128-byte id by value "
+            "(src/distributed/distributed.cpp:888-889), FSDP::fully_shard is not bound to Python, every process pins device 0 "
+            "(src/backend/gpu_native/entrypoint.cu:90-94); measured on one GPU of this box instead" % world)
+    if why is not None:
+        out["unavailable"] = why[:900]
+        print(json.dumps(out), flush=True)
+        return
+    try:
+        times, losses, h2d = _time_model(lt, dev, shape, shape[1], T, B, args.steps, args.warmup, sync)
+    except Exception as e:
+        out["unavailable"] = "reference failed on its own stock path: %r (backend %s)" % (e, backend)
+        print(json.dumps(out), flush=True)
         return
     total = sum(times)
-    tokens = B * T * args.steps
-    val = tokens / total
-    out = {
-        "impl": "reference", "metric": "train tokens/s", "value": round(val, 2), "unit": "tokens/s", "n_gpus": 1,
+    val = B * T * args.steps / total
+    out.update({
+        "metric": "train tokens/s", "value": round(val, 2), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total / args.steps * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (reference has no bf16 GEMM path)",
         "data": "synthetic",
-        "config": {"model": "llama-1.1b composed from the reference's stock ops" if not small else "llama-tiny",
-                   "global_batch": B, "seq_len": T, "parallelism": "single", "backend": backend,
+        "config": {"model": "%s composed from the reference's stock ops" % name, "global_batch": B, "seq_len": T,
+                   "parallelism": "single", "backend": backend,
                    "timing": "host wall clock around each step ending in loss.item() (the reference exposes no events)"},
         "e2e": {"value": round(val, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-        "gpu_launches": None, "final_loss": round(losses[-1], 4),
-    }
+        "gpu_launches": None, "final_loss": round(losses[-1], 4)})
     print(json.dumps(out), flush=True)

@@ -22,9 +22,6 @@ namespace {
 
 // ------------------------------------------------------------------ allocator
 struct Block { void* ptr; size_t size; };
-struct DevicePool {
-  std::multimap<size_t, void*> free_by_stream[1];  // placeholder to keep the struct trivially constructible
-};
 struct Allocator {
   std::mutex mu;
   // (device, stream) -> size-ordered free blocks; a block is only reused on the stream it was freed on,

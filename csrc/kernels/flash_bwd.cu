@@ -710,7 +710,6 @@ static int bwd_convert(const float* dq_acc, void* dq, int B, int Tq, int Hq, int
 
 // Main kernel.  q/d_o/lse/delta/dq_acc are given per query-owning rank (cp_world entries; peer-mapped under CP).
 static long long* g_bwd_trace = nullptr;
-static int g_bwd_dbg = 0;
 
 static int bwd_main(const void* const* q_ptrs, const void* k, const void* v, const void* const* do_ptrs,
                     const float* const* lse_ptrs, const float* const* delta_ptrs, float* const* dq_acc_ptrs, void* dk, void* dv,
@@ -751,7 +750,7 @@ static int bwd_main(const void* const* q_ptrs, const void* k, const void* v, con
   p.causal = causal;
   p.status = device_status_word();
   p.trace = g_bwd_trace;
-  p.dbg = g_bwd_dbg;
+  p.dbg = 0;
   // fp32 dQ accumulator of this rank, [B, Tq, Hq, D]: boxes of 32 rows x 32 columns (128 bytes, swizzled)
   CUtensorMap tdq;
   r = encode_tmap_4d(&tdq, dq_acc_ptrs[cp_rank], 4, D, Hq, Tq, B, (uint64_t)D * 4, (uint64_t)Hq * D * 4,
@@ -769,7 +768,6 @@ extern "C" {
 // Debug aid: a device buffer of 16 int64 that the next backward launches fill with per-phase SM cycle counts of one
 // CTA (see FlashBwdParams::trace); nullptr switches it off.
 void lt_flash_bwd_set_trace(void* buf) { lt::g_bwd_trace = static_cast<long long*>(buf); }
-void lt_flash_bwd_set_debug(int v) { lt::g_bwd_dbg = v; }
 
 int lt_flash_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o, void* dq,
                  void* dk, void* dv, float* delta, float* dq_acc, int B, int Tq, int Tk, int Hq, int Hkv, int D,

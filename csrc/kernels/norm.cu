@@ -375,6 +375,8 @@ int lt_norm_bwd(int layer_norm, const void* dy, const void* x, const void* w, co
 // ------------------------------------------------------------------------------------------------
 // Allocation-free variant (declared and documented in norm_noalloc.h).
 // ------------------------------------------------------------------------------------------------
+#include <atomic>
+#include <initializer_list>
 #include "norm_noalloc.h"
 
 namespace lt {
@@ -384,17 +386,17 @@ static __device__ __align__(256) float g_norm_noalloc_scratch[2 * LT_NORM_NOALLO
 // In host code the array's name is only a handle; the device address has to be looked up, once per device,
 // with that device current.
 static float* norm_noalloc_scratch_ptr(int* err) {
-  static float* ptrs[64] = {nullptr};
+  static std::atomic<float*> ptrs[64];    // zero-initialised; published with release, read with acquire
   static std::mutex mu;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *err = LT_NORM_NOALLOC_ERR_SETUP; return nullptr; }
-  if (ptrs[dev]) return ptrs[dev];
+  if (float* known = ptrs[dev].load(std::memory_order_acquire)) return known;
   std::lock_guard<std::mutex> lk(mu);
-  if (ptrs[dev]) return ptrs[dev];
+  if (float* known = ptrs[dev].load(std::memory_order_acquire)) return known;
   float* p = nullptr;
   const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_noalloc_scratch);
   if (e != cudaSuccess || p == nullptr) { *err = LT_NORM_NOALLOC_ERR_SETUP; return nullptr; }
-  ptrs[dev] = p;
+  ptrs[dev].store(p, std::memory_order_release);
   return p;
 }
 }  // namespace lt
@@ -406,6 +408,14 @@ extern "C" int lt_norm_bwd_noalloc(int layer_norm, const void* dy, const void* x
   if (D % 8 != 0 || D <= 0 || M < 0) return -int(kStatusBadArgument);
   if (D > LT_NORM_NOALLOC_MAX_D) return LT_NORM_NOALLOC_ERR_TOO_LARGE;
   if (M == 0) return 0;
+  // Nothing is launched on a missing or misaligned pointer: the kernels use 16-byte accesses on every row, and a
+  // bad address on the device would be a memory fault instead of an error code.
+  if (!dy || !x || !w || !rstd || !dx || !dw || (layer_norm && (!mean || !db))) return -int(kStatusBadArgument);
+  for (const void* q : {dy, x, w, static_cast<const void*>(dx), dres})
+    if (q && (reinterpret_cast<uintptr_t>(q) & 15u) != 0) return -int(kStatusBadArgument);
+  for (const void* q : {static_cast<const void*>(mean), static_cast<const void*>(rstd), static_cast<const void*>(dw),
+                        static_cast<const void*>(db)})
+    if (q && (reinterpret_cast<uintptr_t>(q) & 3u) != 0) return -int(kStatusBadArgument);
   int err = 0;
   float* scratch = norm_noalloc_scratch_ptr(&err);
   if (!scratch) return err;

@@ -37,6 +37,8 @@ extern "C" {
 //   dy, x, w: bf16 [M, D], [M, D], [D];  mean, rstd: fp32 [M];  dres: optional bf16 [M, D] added to dx.
 //   dx: bf16 [M, D];  dw, db: [D], fp32 when grads_fp32 != 0 else bf16; accumulate != 0 adds into them.
 // Returns 0, one of the LT_NORM_NOALLOC_ERR_* codes, a negative argument error, or a cudaError_t.
+// A required pointer that is null (dy, x, w, rstd, dx, dw; mean and db too for LayerNorm) or a bf16 base that is not
+// 16-byte aligned is an argument error (-6): nothing is launched.
 int lt_norm_bwd_noalloc(int layer_norm, const void* dy, const void* x, const void* w, const float* mean,
                         const float* rstd, const void* dres, void* dx, void* dw, void* db, int grads_fp32,
                         int accumulate, int M, int D, void* stream);

@@ -78,6 +78,7 @@ def test_trainer_from_config_and_metrics_log(tmp_path):
 def test_trainer_save_then_load_continues_the_loss_curve(tmp_path):
     """The benchmarked path (Trainer -> LlamaEngine -> flat bf16 weights, fp32 master + AdamW moments, step count)
     saved after step 3 and loaded into a trainer with other weights: the resumed losses equal the uninterrupted run."""
+    from litetorch_b200.models.llama import LlamaConfig
     from litetorch_b200.trainer import Trainer
     cfg = LlamaConfig.tiny()
     g = torch.Generator().manual_seed(3)

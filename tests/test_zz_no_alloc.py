@@ -44,14 +44,29 @@ def test_noalloc_matches_regular_entry_point_twice(layer_norm):
         dx = torch.empty_like(x)
         dw = torch.empty(D, device="cuda", dtype=torch.bfloat16)
         db = torch.empty(D, device="cuda", dtype=torch.bfloat16) if layer_norm else None
+        # fp32 reference of the same backward pass, by autograd on plain PyTorch
+        xf = x.float().requires_grad_(True)
+        wf = w.float().requires_grad_(True)
+        bf = b.float().requires_grad_(True) if layer_norm else None
+        if layer_norm:
+            yf = torch.nn.functional.layer_norm(xf, (D,), wf, bf, 1e-5)
+        else:
+            yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        yf.backward(dy.float())
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]          # the driver's view: would also see a raw cudaMalloc
         rc = fn(1 if layer_norm else 0, dy.data_ptr(), x.data_ptr(), w.data_ptr(),
                 mean.data_ptr() if mean is not None else None, rstd.data_ptr(), dres.data_ptr(), dx.data_ptr(),
                 dw.data_ptr(), db.data_ptr() if db is not None else None, 0, 0, M, D, stream)
         assert rc == 0, rc
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
+        _close(dx, xf.grad + dres.float())
+        _close(dw, wf.grad)
+        if layer_norm:
+            _close(db, bf.grad)
         _close(dx, dx_ref)
         _close(dw, dw_ref)
         if layer_norm:
@@ -71,3 +86,24 @@ def test_noalloc_rejects_rows_beyond_the_maximum():
     rc = fn(0, x.data_ptr(), x.data_ptr(), w.data_ptr(), None, r.data_ptr(), None, x.data_ptr(), w.data_ptr(), None, 0, 0,
             4, D, torch.cuda.current_stream().cuda_stream)
     assert rc == -100
+
+
+def test_noalloc_rejects_missing_or_misaligned_pointers_without_launching():
+    from litetorch_b200._native import cuda_lib
+    from litetorch_b200.ops import kernels as K
+    fn = cuda_lib().lt_norm_bwd_noalloc
+    fn.argtypes = _ARGS
+    fn.restype = c_int
+    M, D = 16, 256
+    x = torch.zeros(M + 1, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    r = torch.ones(M, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    # LayerNorm without its mean (and without db): an argument error, not a device fault
+    assert fn(1, x.data_ptr(), x.data_ptr(), w.data_ptr(), None, r.data_ptr(), None, x.data_ptr(), w.data_ptr(), None, 0, 0, M, D, st) == -6
+    # a required pointer missing
+    assert fn(0, None, x.data_ptr(), w.data_ptr(), None, r.data_ptr(), None, x.data_ptr(), w.data_ptr(), None, 0, 0, M, D, st) == -6
+    # a bf16 base that is not 16-byte aligned
+    assert fn(0, x.data_ptr() + 2, x.data_ptr(), w.data_ptr(), None, r.data_ptr(), None, x.data_ptr(), w.data_ptr(), None, 0, 0, M, D, st) == -6
+    torch.cuda.synchronize()
+    K.check_status()
