@@ -51,6 +51,9 @@ def _parse():
     ap.add_argument("--no-comm-breakdown", action="store_true",
                     help="skip the extra communication-free steps that give exposed_comm_ms_per_step at N > 1")
     ap.add_argument("--no-extras", action="store_true", help="skip the llama_1b and probe measurements")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="with --tp 1: shard over dp with the FSDP x TP provider (weights prefetched by peer-pull kernels) "
+                         "instead of the ZeRO-3 provider whose all-gather runs inside the GEMMs")
     return ap.parse_args()
 
 
@@ -209,7 +212,7 @@ def run_ours(args):
     host, devb = _batches(cfg, n_seq, T, 1000 + rank // tp, dev)
     sampler = ClockSampler(local) if rank == 0 else None
     try:
-        tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt, parallel="hybrid" if tp > 1 else "auto")
+        tr = Trainer(cfg, seed=1234, tp=tp, activation_checkpointing=ckpt, parallel="hybrid" if (tp > 1 or args.hybrid) else "auto")
         ms_total, e2e_ms, launches, loss_val, clocks = _measure(tr, host, devb, args.steps, args.warmup, sync, sampler)
     except torch.cuda.OutOfMemoryError:
         # Single GPU only (no peer is left waiting): saved activations did not fit beside 128 GB of weights and

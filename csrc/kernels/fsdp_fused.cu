@@ -209,7 +209,11 @@ __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 u) {
   f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
 }
 
-__global__ void __launch_bounds__(256) rs_adamw_kernel(const RsAdamArgs a) {
+// 128 threads per CTA: with ~120 registers a CTA then takes under a quarter of an SM's register file, so it can run
+// on an SM that a persistent GEMM CTA (192 threads x 200-232 registers) already occupies; a 256-thread CTA cannot,
+// and the whole kernel would wait for the gaps between GEMMs instead of running beside them.
+constexpr int kRsAdamThreads = 128;
+__global__ void __launch_bounds__(kRsAdamThreads) rs_adamw_kernel(const RsAdamArgs a) {
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
@@ -328,7 +332,9 @@ struct ShardGatherArgs {
   long long vec_end[8];                    // running total of 16-byte vectors up to and including segment s
   int n_seg, world;
 };
-__global__ void __launch_bounds__(512) shard_gather_kernel(const ShardGatherArgs a) {
+// 128-thread CTAs of < 48 registers: three of them fit beside a persistent GEMM CTA on the same SM.
+constexpr int kShardGatherThreads = 128;
+__global__ void __launch_bounds__(kShardGatherThreads) shard_gather_kernel(const ShardGatherArgs a) {
   const long long total = a.vec_end[a.n_seg - 1];
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < total; base += 4 * stride) {
@@ -573,18 +579,18 @@ int lt_rs_adamw(const void* const* grad_ptrs, const void* mc_grads, float* maste
   a.my_flags = static_cast<uint32_t*>(my_flags);
   a.slot = slot; a.epoch = epoch; a.world = world; a.rank = rank;
   a.status = device_status_word();
-  long long blocks = (total / 8 + 255) / 256;
-  long long cap = max_ctas > 0 ? max_ctas : (long long)sm_count() * 2;
+  long long blocks = (total / 8 + kRsAdamThreads - 1) / kRsAdamThreads;
+  long long cap = max_ctas > 0 ? max_ctas : (long long)sm_count() * 4;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  rs_adamw_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  rs_adamw_kernel<<<(unsigned)blocks, kRsAdamThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   LT_LAUNCH_CHECK();
   return 0;
 }
 
 // Copies, for each of n_seg segments, `n` elements starting at `shard_off` of every rank's shard buffer into
 // dst[s] + r * n (rank order).  segs: n_seg triples (shard_off, n, unused) in elements, multiples of 8;
-// dst_ptrs: n_seg local destination pointers, 16-byte aligned.  max_ctas: 0 = 16.
+// dst_ptrs: n_seg local destination pointers, 16-byte aligned.  max_ctas: 0 = 64 (of 128 threads).
 int lt_gather_shards(const void* const* shard_ptrs, int world, const long long* segs, const void* const* dst_ptrs, int n_seg,
                      int max_ctas, void* stream) {
   using namespace lt;
@@ -601,10 +607,10 @@ int lt_gather_shards(const void* const* shard_ptrs, int world, const long long* 
     a.vec_end[s] = total;
   }
   a.n_seg = n_seg; a.world = world;
-  long long blocks = (total + 4 * 512 - 1) / (4 * 512);
-  const long long cap = max_ctas > 0 ? max_ctas : 16;
+  long long blocks = (total + 4 * kShardGatherThreads - 1) / (4 * kShardGatherThreads);
+  const long long cap = max_ctas > 0 ? max_ctas : 64;
   if (blocks > cap) blocks = cap;
-  shard_gather_kernel<<<(unsigned)blocks, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  shard_gather_kernel<<<(unsigned)blocks, kShardGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   LT_LAUNCH_CHECK();
   return 0;
 }

@@ -1,0 +1,139 @@
+"""KV-cache serving on the Llama engine's weights: chunked prefill into a paged cache, batched one-token decode on
+the split-K paged attention kernel, greedy sampling on the device.
+
+`LlamaKVModel` is the model side of `serving.ServingScheduler.step`: the native scheduler (admission, block tables,
+chunked prefill within a token budget, completion) hands it prompt chunks and the running sequences' newest tokens
+together with their block tables, and gets next tokens back.  Nothing is recomputed: every token's K and V are
+written once (`lt_kv_append`) and read by the attention of later tokens (`lt_paged_decode`, `lt_flash_fwd` for a
+prompt chunk).  The reference's counterparts: ContinuousBatchingScheduler::step and its block tables
+(src/llm/continuous_batching.cpp:20-197), paged attention (src/ops/attention.cpp:351-477) and flash-decoding
+(src/ops/flash_decoding.cpp:13-115); its cache is never filled, here `PagedKVCache.append` is the write path.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..serving import PagedKVCache
+from .llama import LlamaEngine
+
+
+class LlamaKVModel:
+    def __init__(self, engine: LlamaEngine, num_blocks: int, block_size: int = 16, kv_dtype=torch.bfloat16, num_splits: int = 0):
+        assert engine.w.tp == 1 and hasattr(engine.w, "flat_p"), "serving runs on whole (unsharded) weights"
+        self.e = engine
+        cfg = engine.cfg
+        self.block_size = block_size
+        self.num_splits = num_splits
+        self.cache = PagedKVCache(cfg.n_layers, num_blocks, block_size, cfg.n_kv_heads, cfg.head_dim, device=engine.device,
+                                  dtype=kv_dtype)
+        self.kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * self.cache.k[0].element_size()
+
+    # ------------------------------------------------------------------ shared layer body
+    def _layers(self, x, positions, attend):
+        e, cfg, w, K = self.e, self.e.cfg, self.e.w, self.e.K
+        Hq, Hkv, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        n = x.shape[0]
+        for i in range(cfg.n_layers):
+            p = "layers.%d." % i
+            h, _, _, _ = K.norm_fwd(x, w.p(p + "attn_norm"), eps=cfg.rms_eps)
+            qkv = K.gemm(h, w.p(p + "wqkv"))
+            K.rope_(qkv, e.cos, e.sin, 1, Hq, hd, col_offset=0, positions=positions)
+            K.rope_(qkv, e.cos, e.sin, 1, Hkv, hd, col_offset=Hq * hd, positions=positions)
+            q = qkv[:, :Hq * hd].view(n, Hq, hd)
+            k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(n, Hkv, hd)
+            v = qkv[:, (Hq + Hkv) * hd:].view(n, Hkv, hd)
+            o = attend(i, q, k, v)
+            x1 = K.gemm(o.reshape(n, Hq * hd), w.p(p + "wo"), residual=x)
+            h2, _, _, _ = K.norm_fwd(x1, w.p(p + "mlp_norm"), eps=cfg.rms_eps)
+            hm = K.swiglu_fwd(K.gemm(h2, w.p(p + "w_gu")))
+            x = K.gemm(hm, w.p(p + "w_down"), residual=x1)
+        return x
+
+    def _next_tokens(self, x_rows):
+        e, K = self.e, self.e.K
+        hf, _, _, _ = K.norm_fwd(x_rows, e.w.p("final_norm"), eps=e.cfg.rms_eps)
+        logits = K.gemm(hf, e.w.p("lm_head"))
+        return logits.float().argmax(-1)
+
+    def _slots(self, block_ids: Sequence[int], start: int, n: int) -> torch.Tensor:
+        bs = self.block_size
+        return torch.tensor([block_ids[p // bs] * bs + p % bs for p in range(start, start + n)], dtype=torch.int32)
+
+    # ------------------------------------------------------------------ prompt chunks
+    @torch.no_grad()
+    def prefill_chunk(self, tokens: Sequence[int], start: int, block_ids: Sequence[int], want_token: bool) -> int:
+        """Run prompt positions [start, start + len(tokens)) of one sequence: their K / V go into the sequence's blocks,
+        their queries attend to everything cached so far.  Returns the greedy next token when `want_token` (the chunk
+        completes the prompt), else -1."""
+        e, K = self.e, self.e.K
+        dev = e.device
+        n = len(tokens)
+        host = torch.empty(3, n, dtype=torch.int64)
+        host[0] = torch.tensor(tokens, dtype=torch.int64)
+        host[1] = torch.arange(start, start + n)
+        host[2] = self._slots(block_ids, start, n)
+        d = host.to(dev, non_blocking=True)
+        tok, pos, slots = d[0], d[1].to(torch.int32), d[2].to(torch.int32)
+        bs = self.block_size
+        nb = (start + n + bs - 1) // bs
+        blocks = torch.tensor(list(block_ids[:nb]), dtype=torch.int64, device=dev) if start > 0 else None
+
+        def attend(i, q, k, v):
+            self.cache.append(i, k.contiguous(), v.contiguous(), slots)
+            if start == 0:
+                o, _ = K.flash_fwd(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), causal=True)
+                return o[0]
+            # later chunk: keys and values of the whole context so far, read back from the sequence's blocks
+            Hkv, hd = k.shape[1], k.shape[2]
+            kc = self.cache.k[i][blocks].permute(0, 2, 1, 3).reshape(nb * bs, Hkv, hd)[:start + n]
+            vc = self.cache.v[i][blocks].permute(0, 2, 1, 3).reshape(nb * bs, Hkv, hd)[:start + n]
+            if self.cache.fp8:
+                kc = (kc.float() * self.cache.k_scale).to(q.dtype)
+                vc = (vc.float() * self.cache.v_scale).to(q.dtype)
+            o, _ = K.flash_fwd(q.unsqueeze(0), kc.contiguous().unsqueeze(0), vc.contiguous().unsqueeze(0), causal=True)
+            return o[0]
+
+        x = self._layers(K.embedding_fwd(tok, e.w.p("embed")), pos, attend)
+        if not want_token:
+            return -1
+        return int(self._next_tokens(x[-1:]).item())
+
+    # ------------------------------------------------------------------ one token for every running sequence
+    @torch.no_grad()
+    def decode_batch(self, last_tokens: Sequence[int], positions: Sequence[int], block_tables: List[Sequence[int]]) -> List[int]:
+        """last_tokens[s] sits at position positions[s] of sequence s and is not in the cache yet: append its K / V,
+        attend over positions[s] + 1 cached keys, return the greedy next token of every sequence."""
+        from ..serving import paged_attention
+        e, K = self.e, self.e.K
+        dev = e.device
+        S = len(last_tokens)
+        bs = self.block_size
+        width = max((p + bs) // bs for p in positions)
+        host = torch.zeros(4 + width, S, dtype=torch.int64)
+        host[0] = torch.tensor(list(last_tokens), dtype=torch.int64)
+        host[1] = torch.tensor(list(positions), dtype=torch.int64)
+        for s in range(S):
+            p = positions[s]
+            host[2, s] = block_tables[s][p // bs] * bs + p % bs
+            row = block_tables[s][:width]
+            host[4:4 + len(row), s] = torch.tensor(list(row), dtype=torch.int64)
+        host[3] = host[1] + 1
+        d = host.to(dev, non_blocking=True)
+        tok = d[0]
+        pos, slots, ctx = d[1].to(torch.int32), d[2].to(torch.int32), d[3].to(torch.int32)
+        bt = d[4:].t().contiguous().to(torch.int32)
+
+        def attend(i, q, k, v):
+            self.cache.append(i, k.contiguous(), v.contiguous(), slots)
+            return paged_attention(q.contiguous(), self.cache.k[i], self.cache.v[i], bt, ctx, bs, num_splits=self.num_splits or self._splits(S, width * bs),
+                                   k_scale=self.cache.k_scale, v_scale=self.cache.v_scale)
+
+        x = self._layers(K.embedding_fwd(tok, e.w.p("embed")), pos, attend)
+        return self._next_tokens(x).tolist()
+
+    def _splits(self, S: int, max_ctx: int) -> int:
+        """Splits of the key range per (sequence, head): enough warps to fill the GPU, at least 256 keys per split."""
+        H = self.e.cfg.n_heads
+        return max(1, min(32, max_ctx // 256, (148 * 16 + S * H - 1) // (S * H)))

@@ -232,7 +232,19 @@ class Ops:
     def flash_decoding(q, k, v, num_splits: int = 4):
         """Split-K decode attention for Tq == 1: per-split (max, sum, partial output) merged at the end
         (src/ops/flash_decoding.cpp:13-115)."""
-        tq, tk, tv = _unwrap(q).float(), _unwrap(k).float(), _unwrap(v).float()
+        qt, kt, vt = _unwrap(q), _unwrap(k), _unwrap(v)
+        if (qt.is_cuda and qt.dtype == torch.bfloat16 and qt.dim() == 4 and qt.shape[2] == 1 and qt.shape[-1] in (64, 128)
+                and kt.dtype == torch.bfloat16 and kt.is_contiguous() and vt.is_contiguous()):
+            # q [B, H, 1, D], k / v [B, Hkv, T, D]: a contiguous KV tensor is a paged cache with one block of T keys per
+            # sequence, so the split-K paged kernel (a warp per sequence, head and split; a merge kernel) serves it.
+            from . import kernels as K
+            B, H, _, D = qt.shape
+            T = kt.shape[2]
+            bt = torch.arange(B, dtype=torch.int32, device=qt.device).view(B, 1)
+            cl = torch.full((B,), T, dtype=torch.int32, device=qt.device)
+            o = K.paged_decode(qt.reshape(B, H, D).contiguous(), kt, vt, bt, cl, T, max(1, min(int(num_splits), 32)), D ** -0.5)
+            return _w(o.view(B, H, 1, D))
+        tq, tk, tv = qt.float(), kt.float(), vt.float()
         G = tq.shape[1] // tk.shape[1]
         if G > 1:
             tk, tv = tk.repeat_interleave(G, 1), tv.repeat_interleave(G, 1)
@@ -266,10 +278,11 @@ class Ops:
         """logits = x @ Wg^T -> softmax over experts (fp32) -> top-k -> renormalise.  Returns (probs [N,k], indices [N,k]
         as floats), as src/ops/moe_ops.cpp:11-106."""
         xt, wt = _unwrap(x), _unwrap(gate_weight)
-        probs = torch.softmax(F.linear(xt.float(), wt.float()), -1)
-        top_p, top_i = probs.topk(top_k, -1)
-        top_p = top_p / top_p.sum(-1, keepdim=True)
-        return _w(top_p), _w(top_i.to(torch.float32))
+        logits = F.linear(xt.float(), wt.float())
+        # the warp-per-token router kernel on CUDA (fp32 softmax, top-k, renormalisation; differentiable), torch elsewhere
+        top_p, top_i, _ = Fn.moe_router(logits.reshape(-1, logits.shape[-1]), top_k, True)
+        lead = tuple(logits.shape[:-1])
+        return _w(top_p.reshape(*lead, top_k)), _w(top_i.reshape(*lead, top_k).to(torch.float32))
 
     @staticmethod
     def fake_quantize(x, scale: float, zero_point: float = 0.0, bits: int = 8):

@@ -106,7 +106,7 @@ class TPSlicer:
 
 class HybridWeights:
     def __init__(self, cfg: LlamaConfig, device, *, tp: int = 1, seed: int = 0, backend: str = "auto",
-                 param_dtype=torch.bfloat16, prefetch: bool = True, gather_ctas: int = 16):
+                 param_dtype=torch.bfloat16, prefetch: bool = True, gather_ctas: int = 64):
         assert dist.is_initialized(), "HybridWeights needs an initialised process group"
         self.cfg = cfg
         self.device = torch.device(device)

@@ -180,6 +180,11 @@ class ServingScheduler:
         return r.prompt_tokens + r.generated_tokens
 
     def step(self, model) -> List[Request]:
+        """One scheduling step.  A model with `prefill_chunk` / `decode_batch` (e.g. `models.llama_serving.LlamaKVModel`)
+        owns a paged KV cache and is driven with the scheduler's block tables: every token is computed once.  Any other
+        callable `model(tokens) -> logits` is served by recomputing each context (the reference's behaviour)."""
+        if hasattr(model, "prefill_chunk") and hasattr(model, "decode_batch"):
+            return self._step_kv(model)
         cap = max(self.max_num_seqs, 1)
         ids = (c_int64 * cap)()
         starts = (c_int32 * cap)()
@@ -218,6 +223,41 @@ class ServingScheduler:
                 self._sync(rid)
         for i in range(k):
             r = self._reqs[int(fin[i])]
+            r.is_finished = True
+            r.block_ids = []
+            out.append(r)
+        return out
+
+    def _step_kv(self, model) -> List[Request]:
+        cap = max(self.max_num_seqs, 1)
+        ids = (c_int64 * cap)()
+        starts = (c_int32 * cap)()
+        lens = (c_int32 * cap)()
+        n = self._lib.lt_sched_plan(self._s, ids, starts, lens, cap)
+        if n == 0:
+            return []
+        dec = []
+        for i in range(n):
+            rid, st, ln = int(ids[i]), int(starts[i]), int(lens[i])
+            self._sync(rid)
+            r = self._reqs[rid]
+            if ln > 0:
+                done = st + ln >= len(r.prompt_tokens)
+                nxt = model.prefill_chunk(r.prompt_tokens[st:st + ln], st, r.block_ids, done)
+                self._lib.lt_sched_commit(self._s, rid, int(nxt) if done else -1)
+            else:
+                dec.append((rid, st))
+        if dec:
+            toks = [self._tokens(rid)[pos] for rid, pos in dec]
+            nxt = model.decode_batch(toks, [pos for _, pos in dec], [self._reqs[rid].block_ids for rid, _ in dec])
+            for (rid, _), t in zip(dec, nxt):
+                self._lib.lt_sched_commit(self._s, rid, int(t))
+        fin = (c_int64 * cap)()
+        k = self._lib.lt_sched_pop_finished(self._s, fin, cap)
+        out = []
+        for i in range(k):
+            r = self._reqs[int(fin[i])]
+            self._sync(r.id)
             r.is_finished = True
             r.block_ids = []
             out.append(r)
