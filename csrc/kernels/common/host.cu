@@ -3,7 +3,18 @@
 
 #include <mutex>
 
+#include <vector>
+
 namespace lt {
+
+namespace {
+std::vector<int (*)(long long, long long)>& wait_budget_setters() {
+  static std::vector<int (*)(long long, long long)> v;   // function-local: safe to use from other units' static initialisers
+  return v;
+}
+}  // namespace
+
+void register_wait_budget_setter(int (*fn)(long long, long long)) { wait_budget_setters().push_back(fn); }
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -128,3 +139,15 @@ int lt_status_fetch() {
 int lt_sm_count() { return lt::sm_count(); }
 
 }  // extern "C"
+
+// Budgets of the bounded waits on the current device, in SM cycles: `local_cycles` for mbarriers and flags written on
+// this GPU, `peer_cycles` for flags written by another GPU.  Values <= 0 restore the built-in defaults (about 1.5 s
+// and 10 s).  Returns 0 or the first cudaError_t.  Call with no kernel of this library in flight.
+extern "C" int lt_set_wait_budget_cycles(long long local_cycles, long long peer_cycles) {
+  int rc = 0;
+  for (auto fn : lt::wait_budget_setters()) {
+    const int r = fn(local_cycles, peer_cycles);
+    if (r != 0 && rc == 0) rc = r;
+  }
+  return rc;
+}

@@ -28,6 +28,10 @@ int encode_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
                    uint64_t d3, uint64_t stride1_bytes, uint64_t stride2_bytes, uint64_t stride3_bytes,
                    uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3, int swizzle_128b);
 
+// Every translation unit with bounded waits registers a function that stores the two wait budgets (SM cycles) into
+// its own device globals; lt_set_wait_budget_cycles() calls them all for the current device.
+void register_wait_budget_setter(int (*fn)(long long local_cycles, long long peer_cycles));
+
 inline int cuda_ok(cudaError_t e) { return e == cudaSuccess ? 0 : int(e); }
 
 }  // namespace lt

@@ -35,6 +35,26 @@ enum DeviceStatus : int {
 #define LT_PEER_WAIT_CYCLES 18000000000ll
 #endif
 
+// The budgets are read from device globals (one copy per translation unit, initialised to the constants above) so
+// that they can be changed at run time: lt_set_wait_budget_cycles() runs every translation unit's setter.  A test
+// shortens them to about a millisecond, lets a wait on a flag that nobody sets run out, and reads the status word.
+static __device__ long long g_wait_cycles = LT_WAIT_CYCLES;
+static __device__ long long g_peer_wait_cycles = LT_PEER_WAIT_CYCLES;
+
+static int set_wait_budget_this_tu(long long local_cycles, long long peer_cycles) {
+  if (local_cycles <= 0) local_cycles = LT_WAIT_CYCLES;
+  if (peer_cycles <= 0) peer_cycles = LT_PEER_WAIT_CYCLES;
+  cudaError_t e = cudaMemcpyToSymbol(g_wait_cycles, &local_cycles, sizeof(local_cycles));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_peer_wait_cycles, &peer_cycles, sizeof(peer_cycles));
+  return int(e);
+}
+namespace {
+struct WaitBudgetRegistrar {
+  WaitBudgetRegistrar() { register_wait_budget_setter(&set_wait_budget_this_tu); }
+};
+static WaitBudgetRegistrar g_wait_budget_registrar;
+}  // namespace
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -82,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > LT_WAIT_CYCLES) {
+      if (clock64() - t0 > g_wait_cycles) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -322,7 +342,7 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* p, uint32_t tar
   for (uint32_t it = 1;; ++it) {
     if (ld_acquire_sys(p) >= target) return true;
     if ((it & 63u) == 0u) {
-      if (clock64() - t0 > LT_PEER_WAIT_CYCLES) {
+      if (clock64() - t0 > g_peer_wait_cycles) {
         if (status) atomicCAS(status, 0, int(kStatusTimeoutPeerFlag));
         return false;
       }
@@ -337,7 +357,7 @@ __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* p, uint32_t tar
   for (uint32_t it = 1;; ++it) {
     if (ld_acquire_gpu(p) >= target) return true;
     if ((it & 63u) == 0u) {
-      if (clock64() - t0 > LT_WAIT_CYCLES) {
+      if (clock64() - t0 > g_wait_cycles) {
         if (status) atomicCAS(status, 0, int(kStatusTimeoutLocalFlag));
         return false;
       }

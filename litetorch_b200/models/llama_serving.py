@@ -55,6 +55,7 @@ class LlamaKVModel:
         e, K = self.e, self.e.K
         hf, _, _, _ = K.norm_fwd(x_rows, e.w.p("final_norm"), eps=e.cfg.rms_eps)
         logits = K.gemm(hf, e.w.p("lm_head"))
+        self.last_logits = logits            # [rows, vocab] of the newest step (kept for inspection and tests)
         return logits.float().argmax(-1)
 
     def _slots(self, block_ids: Sequence[int], start: int, n: int) -> torch.Tensor:

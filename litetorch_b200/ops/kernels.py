@@ -18,6 +18,7 @@ _vp, _i, _ll, _f = c_void_p, c_int, c_longlong, c_float
 _SIGS = {
     "lt_status_fetch": [],
     "lt_sm_count": [],
+    "lt_set_wait_budget_cycles": [_ll, _ll],
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
     "lt_gemm_set_tail_split": [_i],
     "lt_gemm_set_pair_mode": [_i],
@@ -82,7 +83,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_set_wait_budget_cycles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -146,6 +147,14 @@ def check_status():
     s = status_fetch()
     if s != 0:
         raise KernelError("device status word = %d (a bounded wait ran out or an argument was rejected)" % s)
+
+
+def set_wait_budget(local_cycles: int = 0, peer_cycles: int = 0):
+    """Clock budget (SM cycles) of the bounded waits inside the kernels on the current device: `local_cycles` for
+    mbarriers and flags set on this GPU, `peer_cycles` for flags set by another GPU; 0 restores the defaults (about
+    1.5 s / 10 s).  A wait that runs out records a code in the status word (`status_fetch`) and the kernel returns."""
+    torch.cuda.synchronize()
+    _check(_fn("lt_set_wait_budget_cycles")(int(local_cycles), int(peer_cycles)), "lt_set_wait_budget_cycles")
 
 
 def sm_count() -> int:
