@@ -9,6 +9,8 @@
 // exposed so that tensor-parallel ranks can combine them with one tiny collective before the in-place
 // gradient pass; AdamW/Adam/SGD/RMSprop run over flat buffers or over a pointer table in ONE launch,
 // with the gradient unscale and the skip-on-overflow decision read from device memory.
+#include <cuda_fp8.h>
+
 #include "common/host.h"
 #include "common/ptx.cuh"
 
@@ -288,6 +290,90 @@ __global__ void rmsprop_flat_kernel(float* __restrict__ p, const float* __restri
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- AdamW, 8-bit moments
+// m and v are stored as int8 codes (one absmax scale per tensor: value = code * scale, scale = absmax / 127) or as
+// e4m3 codes (delayed scaling: scale = max of the last ten absmax values / 240).  Reference: AdamW8bit / AdamWFP8
+// (src/optim/adamw_8bit.cpp:13-104, src/optim/adamw_fp8.cpp:13-126), CPU loops there.  Here one step of one tensor
+// is three launches and no host synchronisation: pass 0 computes the updated moments only to find their absmax
+// (atomicMax on the float's bit pattern), a one-thread kernel turns the absmax into the new scales (and keeps the
+// e4m3 history), pass 1 recomputes the moments, updates the parameter and stores the codes with the new scales.
+struct AdamQArgs {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;
+  int fp8, first, p_bf16, g_bf16;
+};
+__device__ __forceinline__ float ldf(const void* base, int is_bf16, long long i) {
+  return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]) : static_cast<const float*>(base)[i];
+}
+__device__ __forceinline__ float deq8(const void* q, int fp8, long long i, float scale) {
+  if (fp8) return float(static_cast<const __nv_fp8_e4m3*>(q)[i]) * scale;
+  return float(static_cast<const signed char*>(q)[i]) * scale;
+}
+__global__ void adam_q_kernel(void* __restrict__ p, const void* __restrict__ g, void* __restrict__ mq, void* __restrict__ vq,
+                              long long n, AdamQArgs a, const float* __restrict__ scale_old, const float* __restrict__ scale_new,
+                              unsigned* __restrict__ amax, int pass) {
+  const float so_m = scale_old[0], so_v = scale_old[1];
+  float sn_m = 1.f, sn_v = 1.f;
+  if (pass == 1) { sn_m = scale_new[0]; sn_v = scale_new[1]; }
+  float am = 0.f, av = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gg = ldf(g, a.g_bf16, i);
+    const float m0 = a.first ? 0.f : deq8(mq, a.fp8, i, so_m);
+    const float v0 = a.first ? 0.f : deq8(vq, a.fp8, i, so_v);
+    const float m = a.beta1 * m0 + (1.f - a.beta1) * gg;
+    const float v = a.beta2 * v0 + (1.f - a.beta2) * gg * gg;
+    if (pass == 0) {
+      am = fmaxf(am, fabsf(m));
+      av = fmaxf(av, fabsf(v));
+      continue;
+    }
+    float w = ldf(p, a.p_bf16, i);
+    w -= a.lr * a.wd * w;
+    w -= a.lr * (m / a.bc1) / (sqrtf(v / a.bc2) + a.eps);
+    if (a.p_bf16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(w);
+    else static_cast<float*>(p)[i] = w;
+    if (a.fp8) {
+      static_cast<__nv_fp8_e4m3*>(mq)[i] = __nv_fp8_e4m3(fminf(fmaxf(m / sn_m, -448.f), 448.f));
+      static_cast<__nv_fp8_e4m3*>(vq)[i] = __nv_fp8_e4m3(fminf(fmaxf(v / sn_v, -448.f), 448.f));
+    } else {
+      static_cast<signed char*>(mq)[i] = (signed char)fminf(fmaxf(rintf(m / sn_m), -127.f), 127.f);
+      static_cast<signed char*>(vq)[i] = (signed char)fminf(fmaxf(rintf(v / sn_v), -127.f), 127.f);
+    }
+  }
+  if (pass == 0) {
+    for (int o = 16; o > 0; o >>= 1) {
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, o));
+    }
+    if ((threadIdx.x & 31) == 0) {               // non-negative floats order like their bit patterns
+      atomicMax(amax, __float_as_uint(am));
+      atomicMax(amax + 1, __float_as_uint(av));
+    }
+  }
+}
+// state: [0..1] absmax of this step (bit patterns, cleared here), hist: [2][10] floats, hist_n: steps recorded so far.
+__global__ void adam_q_scales_kernel(unsigned* __restrict__ amax, float* __restrict__ scale_new, float* __restrict__ hist,
+                                     int* __restrict__ hist_n, int fp8) {
+  if (threadIdx.x >= 2) return;
+  const int k = threadIdx.x;
+  const float a = __uint_as_float(amax[k]);
+  amax[k] = 0u;
+  float s;
+  if (fp8) {
+    const int nrec = *hist_n;
+    hist[k * 10 + nrec % 10] = a;
+    const int have = nrec + 1 < 10 ? nrec + 1 : 10;
+    float mx = 0.f;
+    for (int j = 0; j < have; ++j) mx = fmaxf(mx, hist[k * 10 + j]);
+    s = mx > 0.f ? mx / 240.f : 1.f;
+  } else {
+    s = a > 0.f ? a / 127.f : 1.f;
+  }
+  scale_new[k] = s;
+  __syncwarp(0x3u);
+  if (k == 0 && fp8) *hist_n += 1;
+}
+
 // out[0] += sum x^2, out[1] += number of non-finite elements.
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
@@ -401,6 +487,22 @@ int lt_adam_table(const void* p_ptrs, const void* g_ptrs, const void* m_ptrs, co
 }
 int lt_adam_chunk_elems() { return lt::kChunk; }
 
+// One AdamW step of one tensor whose moments are int8 (fp8 = 0) or e4m3 (fp8 = 1) codes.  scale_old / scale_new: two
+// floats each (m, v); amax: two uint32, zero before the first step; hist: 20 floats, hist_n: one int (both zero at
+// the start; used by the e4m3 variant).  first != 0: the moments do not exist yet (treated as zero).
+int lt_adam_q8(void* p, int p_bf16, const void* g, int g_bf16, void* mq, void* vq, long long n, float lr, float beta1, float beta2,
+               float eps, float wd, float bc1, float bc2, int fp8, int first, const float* scale_old, float* scale_new,
+               void* amax, float* hist, int* hist_n, void* stream) {
+  using namespace lt;
+  if (n == 0) return 0;
+  AdamQArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, fp8, first, p_bf16, g_bf16};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  adam_q_kernel<<<flat_grid(n), 256, 0, st>>>(p, g, mq, vq, n, a, scale_old, scale_new, static_cast<unsigned*>(amax), 0);
+  adam_q_scales_kernel<<<1, 32, 0, st>>>(static_cast<unsigned*>(amax), scale_new, hist, hist_n, fp8);
+  adam_q_kernel<<<flat_grid(n), 256, 0, st>>>(p, g, mq, vq, n, a, scale_old, scale_new, static_cast<unsigned*>(amax), 1);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
 int lt_sgd_flat(float* p, const float* g, float* vel, long long n, float lr, float momentum, float wd, void* stream) {
   using namespace lt;
   if (n == 0) return 0;

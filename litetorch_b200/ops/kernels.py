@@ -56,6 +56,7 @@ _SIGS = {
     "lt_adam_flat": [_vp, _vp, _i, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _i, _vp, _vp],
     "lt_adam_table": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _f, _i, _vp, _vp],
     "lt_adam_chunk_elems": [],
+    "lt_adam_q8": [_vp, _i, _vp, _i, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "lt_sgd_flat": [_vp, _vp, _vp, _ll, _f, _f, _f, _vp],
     "lt_rmsprop_flat": [_vp, _vp, _vp, _ll, _f, _f, _f, _f, _vp],
     "lt_sumsq": [_vp, _i, _ll, _vp, _vp],
@@ -83,7 +84,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_set_wait_budget_cycles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_adam_q8": 3, "lt_set_wait_budget_cycles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -376,6 +377,23 @@ def adam_flat(master, grad, m, v, param_bf16, *, lr, beta1, beta2, eps, wd, step
     _check(_fn("lt_adam_flat")(master.data_ptr(), grad.data_ptr(), 1 if grad.dtype == torch.bfloat16 else 0, m.data_ptr(),
                                v.data_ptr(), _p(param_bf16), master.numel(), lr, beta1, beta2, eps, wd, bc1, bc2,
                                1 if adamw else 0, _p(dyn), _stream()), "lt_adam_flat")
+
+
+def sgd_flat(p, g, vel, *, lr, momentum, wd):
+    """p -= lr * (momentum * vel + g + wd * p) on contiguous fp32 tensors (vel None: no momentum)."""
+    _check(_fn("lt_sgd_flat")(p.data_ptr(), g.data_ptr(), _p(vel), p.numel(), lr, momentum, wd, _stream()), "lt_sgd_flat")
+
+
+def rmsprop_flat(p, g, sq, *, lr, alpha, eps, wd):
+    _check(_fn("lt_rmsprop_flat")(p.data_ptr(), g.data_ptr(), sq.data_ptr(), p.numel(), lr, alpha, eps, wd, _stream()), "lt_rmsprop_flat")
+
+
+def adam_q8(p, g, mq, vq, *, lr, beta1, beta2, eps, wd, step, fp8, first, scale_old, scale_new, amax, hist, hist_n):
+    """AdamW step with int8 / e4m3 moment codes; scales, absmax and history stay on the device (no host sync)."""
+    _check(_fn("lt_adam_q8")(p.data_ptr(), 1 if p.dtype == torch.bfloat16 else 0, g.data_ptr(), 1 if g.dtype == torch.bfloat16 else 0,
+                             mq.data_ptr(), vq.data_ptr(), p.numel(), lr, beta1, beta2, eps, wd, 1.0 - beta1 ** step,
+                             1.0 - beta2 ** step, 1 if fp8 else 0, 1 if first else 0, scale_old.data_ptr(), scale_new.data_ptr(),
+                             amax.data_ptr(), hist.data_ptr(), hist_n.data_ptr(), _stream()), "lt_adam_q8")
 
 
 def sumsq(x: torch.Tensor, out: torch.Tensor):

@@ -34,6 +34,65 @@ class Optimizer:
         return [_unwrap(p) for p in self.params]
 
 
+def _flat_native(p) -> bool:
+    """fp32 parameter and gradient, contiguous, on a CUDA device: the flat optimizer kernels apply."""
+    g = p.grad
+    return (p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and g is not None and g.dtype == torch.float32
+            and g.is_contiguous())
+
+
+class _QState:
+    """Device-side bookkeeping of one tensor's quantised moments: two scale pairs (this step's and the next), the
+    running absmax words and the e4m3 absmax history."""
+
+    def __init__(self, p, code_dtype):
+        dev = p.device
+        self.mq = torch.zeros(p.shape, dtype=code_dtype, device=dev)
+        self.vq = torch.zeros(p.shape, dtype=code_dtype, device=dev)
+        self.scales = torch.ones(2, 2, dtype=torch.float32, device=dev)
+        self.cur = 0
+        self.amax = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.hist = torch.zeros(20, dtype=torch.float32, device=dev)
+        self.hist_n = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.first = True
+
+
+def _q_native(p) -> bool:
+    g = p.grad
+    return (p.is_cuda and p.is_contiguous() and p.dtype in (torch.float32, torch.bfloat16) and g is not None
+            and g.is_contiguous() and g.dtype in (torch.float32, torch.bfloat16))
+
+
+def _q_step(opt, i, p, fp8: bool):
+    """One tensor's step on the GPU kernel; keeps `m_q / v_q / m_scale / v_scale` (or the e4m3 names) pointing at the
+    live codes and device-resident scales so that checkpoints read them the usual way."""
+    from ..ops import kernels as K
+    st = opt._qstate[i]
+    if st is None:
+        st = opt._qstate[i] = _QState(p, torch.float8_e4m3fn if fp8 else torch.int8)
+        codes_m, codes_v = (opt.m8, opt.v8) if fp8 else (opt.m_q, opt.v_q)
+        if codes_m[i] is not None:                       # state loaded from a checkpoint or left by the torch path
+            st.mq.copy_(codes_m[i])
+            st.vq.copy_(codes_v[i])
+            st.scales[0, 0], st.scales[0, 1] = float(opt.m_scale[i]), float(opt.v_scale[i])
+            st.first = False
+            if fp8:
+                for k, h in enumerate((opt.m_hist[i], opt.v_hist[i])):
+                    for j, a in enumerate(h[-10:]):
+                        st.hist[k * 10 + j] = a
+                st.hist_n.fill_(min(len(opt.m_hist[i]), 10))
+    old, new = st.scales[st.cur], st.scales[1 - st.cur]
+    K.adam_q8(p, p.grad, st.mq, st.vq, lr=opt.lr, beta1=opt.beta1, beta2=opt.beta2, eps=opt.eps, wd=opt.weight_decay,
+              step=opt.step_count, fp8=fp8, first=st.first, scale_old=old, scale_new=new, amax=st.amax, hist=st.hist,
+              hist_n=st.hist_n)
+    st.cur, st.first = 1 - st.cur, False
+    if fp8:
+        opt.m8[i], opt.v8[i] = st.mq, st.vq
+    else:
+        opt.m_q[i], opt.v_q[i] = st.mq, st.vq
+    opt.m_scale[i], opt.v_scale[i] = new[0], new[1]      # 0-dim device tensors: no host sync
+
+
 class SGD(Optimizer):
     def __init__(self, params, lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0):
         super().__init__(params, lr)
@@ -45,6 +104,14 @@ class SGD(Optimizer):
         self.step_count += 1
         for i, p in enumerate(self._tensors()):
             if p.grad is None:
+                continue
+            if _flat_native(p):
+                # one fused pass on the GPU (sgd_step_kernel of the reference: src/backend/gpu_native/optim/optimizers.cu:87-104)
+                from ..ops import kernels as K
+                if self.momentum and self.velocity[i] is None:
+                    self.velocity[i] = torch.zeros_like(p)
+                K.sgd_flat(p, p.grad, self.velocity[i] if self.momentum else None, lr=self.lr, momentum=self.momentum,
+                           wd=self.weight_decay)
                 continue
             g = p.grad.to(p.dtype)
             if self.weight_decay:
@@ -220,6 +287,11 @@ class RMSprop(Optimizer):
                 continue
             if self.square_avg[i] is None:
                 self.square_avg[i] = torch.zeros_like(p, dtype=torch.float32)
+            if _flat_native(p):
+                # rmsprop_step_kernel of the reference (src/backend/gpu_native/optim/optimizers.cu:106-124), one pass
+                from ..ops import kernels as K
+                K.rmsprop_flat(p, p.grad, self.square_avg[i], lr=self.lr, alpha=self.alpha, eps=self.eps, wd=self.weight_decay)
+                continue
             g = p.grad.float()
             if self.weight_decay:
                 g = g + self.weight_decay * p.float()
@@ -237,6 +309,7 @@ class AdamW8bit(_AdamBase):
         n = len(self.params)
         self.m_q, self.v_q = [None] * n, [None] * n
         self.m_scale, self.v_scale = [1.0] * n, [1.0] * n
+        self._qstate = [None] * n
 
     @staticmethod
     def _quant(x):
@@ -250,6 +323,9 @@ class AdamW8bit(_AdamBase):
         bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count
         for i, p in enumerate(self._tensors()):
             if p.grad is None:
+                continue
+            if _q_native(p):
+                _q_step(self, i, p, fp8=False)
                 continue
             g = p.grad.float()
             m = self.m_q[i].float() * self.m_scale[i] if self.m_q[i] is not None else torch.zeros_like(g)
@@ -279,6 +355,7 @@ class AdamWFP8(_AdamBase):
         self.m8, self.v8 = [None] * n, [None] * n
         self.m_scale, self.v_scale = [1.0] * n, [1.0] * n
         self.m_hist, self.v_hist = [[] for _ in range(n)], [[] for _ in range(n)]
+        self._qstate = [None] * n
 
     def _store(self, x, hist):
         hist.append(float(x.abs().max()))
@@ -293,6 +370,9 @@ class AdamWFP8(_AdamBase):
         bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count
         for i, p in enumerate(self._tensors()):
             if p.grad is None:
+                continue
+            if _q_native(p):
+                _q_step(self, i, p, fp8=True)
                 continue
             g = p.grad.float()
             m = self.m8[i].float() * self.m_scale[i] if self.m8[i] is not None else torch.zeros_like(g)

@@ -250,9 +250,11 @@ def load_optimizer_state(opt, filepath: str) -> None:
                 if isinstance(opt, O.AdamW8bit):
                     opt.m_q[i], opt.m_scale[i] = opt._quant(ms[i].to(pt.device))
                     opt.v_q[i], opt.v_scale[i] = opt._quant(vs[i].to(pt.device))
+                    opt._qstate[i] = None                   # the GPU kernel path re-imports codes and scales at its next step
                 elif isinstance(opt, O.AdamWFP8):
                     opt.m8[i], opt.m_scale[i] = opt._store(ms[i].to(pt.device), opt.m_hist[i])
                     opt.v8[i], opt.v_scale[i] = opt._store(vs[i].to(pt.device), opt.v_hist[i])
+                    opt._qstate[i] = None
                 else:
                     opt._ensure_state(i, pt)
                     opt.m[i].copy_(ms[i])

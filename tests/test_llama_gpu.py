@@ -93,6 +93,6 @@ def test_trainer_save_then_load_continues_the_loss_curve(tmp_path):
     c.step(*batch(5))
     c.load(str(tmp_path / "ck"))
     rest = [c.step(*batch(s)) for s in range(3, 6)]
-    assert first == full[:3]
+    assert all(abs(x - y) < 2e-3 for x, y in zip(first, full[:3])), (first, full[:3])   # atomics: not bit-reproducible
     assert all(abs(x - y) < 2e-3 for x, y in zip(rest, full[3:])), (rest, full[3:])   # bf16 atomics in two kernels
     assert c.engine.step_count == 6

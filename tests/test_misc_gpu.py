@@ -167,3 +167,30 @@ def test_moe_expert_bwd_pointwise(S, F):
     torch.testing.assert_close(dgu[valid].float(), ref[valid], rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(hw[valid].float(), ref_hw[valid], rtol=2e-2, atol=1e-2)
     torch.testing.assert_close(dw[valid], ref_dw[valid], rtol=1e-2, atol=5e-2 * F ** 0.5)
+
+
+@pytest.mark.parametrize("name", ["SGD", "RMSprop", "AdamW8bit", "AdamWFP8"])
+def test_optimizer_kernels_follow_the_torch_path(name):
+    """SGD / RMSprop flat kernels and the int8 / e4m3-moment AdamW kernels against the same optimizer's PyTorch path on
+    the CPU, over several steps with identical gradients (fp32 reference arithmetic)."""
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor, _unwrap
+    g = torch.Generator().manual_seed(0)
+    w0 = torch.randn(257, 33, generator=g)
+    grads = [torch.randn(257, 33, generator=g) * (0.5 + k) for k in range(6)]
+    kw = {"SGD": dict(lr=0.05, momentum=0.9, weight_decay=0.01), "RMSprop": dict(lr=0.01, alpha=0.95, weight_decay=0.01),
+          "AdamW8bit": dict(lr=0.01, weight_decay=0.1), "AdamWFP8": dict(lr=0.01, weight_decay=0.1)}[name]
+    res = []
+    for dev in ("cpu", "cuda"):
+        p = Tensor(w0.clone().to(dev).requires_grad_(True))
+        opt = getattr(lt.optim, name)([p], **kw)
+        for gr in grads:
+            _unwrap(p).grad = gr.to(dev)
+            opt.step()
+        res.append(_unwrap(p).detach().float().cpu())
+        if dev == "cuda" and name.startswith("AdamW"):
+            codes = opt.m_q[0] if name == "AdamW8bit" else opt.m8[0]
+            assert codes.dtype == (torch.int8 if name == "AdamW8bit" else torch.float8_e4m3fn) and codes.is_cuda
+            assert torch.is_tensor(opt.m_scale[0]) and opt.m_scale[0].is_cuda        # scales never left the device
+    tol = 1e-5 if name in ("SGD", "RMSprop") else 2e-2      # a code may round the other way when fp32 sums are fused differently
+    assert float((res[0] - res[1]).abs().max()) < tol * max(1.0, float(res[0].abs().max()))
