@@ -29,6 +29,24 @@ class PipelineParallelModule:
         self._in_shape = None
         self._in_dtype = torch.float32
         self._sent_shape = False
+        self._group_bwd = None
+        self.overlap = True
+
+    def _backward_group(self):
+        """A second communicator over the same ranks, used only for gradients (stage r+1 -> r).  With activations on one
+        communicator and gradients on the other, every communicator carries traffic in one direction only: a send can
+        only wait for a receive that its neighbour has already posted, never for one queued behind the neighbour's own
+        send, so sends and receives need not be grouped into pairs and a receive can be posted long before its data is
+        needed.  Every rank of the job creates every stage group's twin, in the same order (new_group is collective)."""
+        if self._group_bwd is None and dist.is_initialized() and self.world > 1:
+            mine = tuple(dist.get_process_group_ranks(self.group) if self.group is not None else range(dist.get_world_size()))
+            lists = [None] * dist.get_world_size()
+            dist.all_gather_object(lists, mine)
+            for ranks in sorted(set(tuple(l) for l in lists)):
+                g = dist.new_group(list(ranks))
+                if ranks == mine:
+                    self._group_bwd = g
+        return self._group_bwd
 
     # ---- helpers
     def _global(self, r: int) -> int:
@@ -109,8 +127,12 @@ class PipelineParallelModule:
 
         On the first stage each micro-batch is the input tensor; on the last stage `loss_fn(output, target_or_mb)`
         produces the loss.  Returns the mean loss on the last stage (0.0 elsewhere).  Gradients accumulate in the
-        local module's parameters.  Steady-state transfers are grouped pairs (send activation + receive gradient,
-        send gradient + receive next activation)."""
+        local module's parameters.  With `self.overlap` (default) the receive of the gradient is posted before the
+        forward it will follow and the receive of the next activation before the backward, sends are not waited for
+        until the step ends, and a transfer is only waited for where its tensor is consumed; `overlap = False` is the
+        grouped send+receive pair that is waited for at once (kept for comparison)."""
+        if self.overlap and self.world > 1:
+            return self._train_step_1f1b_overlapped(microbatches, loss_fn, targets)
         M, W, r = len(microbatches), self.world, self.rank
         warm = min(M, W - r - 1)
         steady = M - warm
@@ -184,6 +206,89 @@ class PipelineParallelModule:
             gin = run_bwd(grad_out)
             if not first:
                 self._batched(gin, r - 1, None, 0)
+        return float(total) / M if (last and total is not None) else 0.0
+
+    def _train_step_1f1b_overlapped(self, microbatches, loss_fn, targets) -> float:
+        M, W, r = len(microbatches), self.world, self.rank
+        warm = min(M, W - r - 1)
+        steady = M - warm
+        first, last = r == 0, r == W - 1
+        gf, gb = self.group, self._backward_group()
+        fifo = deque()
+        sends = []                         # (work, tensor) of sends in flight: waited for once, at the end of the step
+        total = None
+
+        def isend(t, peer, group):
+            t = t.contiguous()
+            sends.append((dist.isend(t, self._global(peer), group=group), t))
+
+        def post_recv_x():
+            if first:
+                return None
+            if self._in_shape is None:     # the first message of a shape carries a header (blocking, once)
+                return ("now", self._recv_activation(r - 1))
+            buf = torch.empty(self._in_shape, dtype=self._in_dtype, device=self._dev())
+            return (dist.irecv(buf, self._global(r - 1), group=gf), buf)
+
+        def take_x(pending, i):
+            if first:
+                return _unwrap(microbatches[i])
+            w, buf = pending
+            if w != "now":
+                w.wait()
+            return buf.requires_grad_(True)
+
+        def run_fwd(i, xin):
+            out = _unwrap(self.local_module(Tensor(xin)))
+            fifo.append((xin, out, i))
+            if not last:
+                if not self._sent_shape:
+                    self._send(out.detach(), r + 1, with_shape=True)
+                    self._sent_shape = True
+                else:
+                    isend(out.detach(), r + 1, gf)
+            return out
+
+        def run_bwd(pending_grad):
+            nonlocal total
+            xin, out, i = fifo.popleft()
+            if last:
+                tgt = targets[i] if targets is not None else microbatches[i]
+                loss = _unwrap(loss_fn(Tensor(out), tgt))
+                total = loss.detach().float() if total is None else total + loss.detach().float()
+                (loss / M).backward()
+            else:
+                w, g = pending_grad
+                w.wait()
+                out.backward(g)
+            if not first:
+                isend(xin.grad, r - 1, gb)
+
+        def post_recv_grad(out_like):
+            if last:
+                return None
+            g = torch.empty_like(out_like)
+            return (dist.irecv(g, self._global(r + 1), group=gb), g)
+
+        pend_x = post_recv_x()
+        for i in range(warm):
+            xin = take_x(pend_x, i)
+            pend_x = post_recv_x() if i + 1 < M else None      # the next activation travels while this forward runs
+            run_fwd(i, xin)
+        for k in range(steady):
+            i = warm + k
+            xin = take_x(pend_x, i)
+            # the gradient this stage will need right after the forward: posted now, arrives under the forward
+            pend_g = post_recv_grad(fifo[0][1]) if fifo else None
+            out = run_fwd(i, xin)
+            if pend_g is None:
+                pend_g = post_recv_grad(out)
+            pend_x = post_recv_x() if i + 1 < M else None      # the next activation arrives under the backward
+            run_bwd(pend_g)
+        for _ in range(warm):
+            run_bwd(post_recv_grad(fifo[0][1]))
+        for w, _t in sends:
+            w.wait()
         return float(total) / M if (last and total is not None) else 0.0
 
     run_1f1b_with_backward = train_step_1f1b

@@ -142,6 +142,52 @@ def test_pipeline_1f1b_matches_single_process(tmp_path):
     assert res["err"] < 1e-6 and abs(res["loss"] - res["ref"]) < 1e-6
 
 
+def test_pipeline_1f1b_posts_receives_before_the_compute_they_overlap(tmp_path):
+    """Order of events on the first of two stages in the 1F1B steady state: with overlap the receive of the gradient
+    is posted before the forward that it runs under (R F B R F B ...); the grouped mode posts it after the forward.
+    Both modes give the same gradients."""
+    res = run_ranks('''
+        import torch.distributed as tdist
+        def run(overlap):
+            torch.manual_seed(0)
+            l1, l2 = lt.nn.Linear(4, 8), lt.nn.Linear(8, 2)
+            log = []
+            class Stage(lt.nn.Module):
+                def __init__(s, lin):
+                    super().__init__(); s.lin = lin
+                def forward(s, x):
+                    log.append("F"); return s.lin(x)
+            mbs = [lt.Tensor(torch.randn(3, 4, generator=torch.Generator().manual_seed(10 + i))) for i in range(4)]
+            tg = [lt.Tensor(torch.randn(3, 2, generator=torch.Generator().manual_seed(50 + i))) for i in range(4)]
+            pp = lt.distributed.PipelineParallelModule(Stage(l1 if rank == 0 else l2))
+            pp.overlap = overlap
+            orig_irecv, orig_batch = tdist.irecv, tdist.batch_isend_irecv
+            def irecv(*a, **k):
+                log.append("R"); return orig_irecv(*a, **k)
+            def batch(ops):
+                if any(o.op is orig_irecv or o.op is irecv for o in ops): log.append("R")
+                return orig_batch(ops)
+            if overlap:
+                tdist.irecv = irecv
+            else:
+                tdist.batch_isend_irecv = batch
+            try:
+                pp.train_step_1f1b(mbs, lambda out, t: lt.Ops.mse_loss(out, t), targets=tg)
+            finally:
+                tdist.irecv, tdist.batch_isend_irecv = orig_irecv, orig_batch
+            g = _unwrap((l1 if rank == 0 else l2).weight).grad.clone()
+            return "".join(log), g
+        log_o, g_o = run(True)
+        log_g, g_g = run(False)
+        err = torch.tensor([float((g_o - g_g).abs().max())]); dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        done(overlapped=log_o, grouped=log_g, err=err.item())
+    ''', tmp_path=tmp_path, port=29835)
+    assert res["err"] < 1e-7
+    # stage 0 of 2 with 4 micro-batches: one warm-up forward, three steady iterations, one drain backward
+    assert res["overlapped"] == "F" + "RF" * 3 + "R", res
+    assert res["grouped"] == "F" + "FR" * 3 + "R", res
+
+
 def test_ring_attention_zigzag_and_moe_expert_parallel(tmp_path):
     res = run_ranks('''
         from litetorch_b200.parallel.cp import zigzag_split, zigzag_merge
