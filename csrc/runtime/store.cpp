@@ -120,6 +120,13 @@ struct Server {
         break;
       }
     }
+    {
+      // forget the descriptor before closing it: the number may be reused by another socket of the process at
+      // once, and the stop path must not shut that one down
+      std::lock_guard<std::mutex> lk(mu);
+      for (auto it = client_fds.begin(); it != client_fds.end(); ++it)
+        if (*it == fd) { client_fds.erase(it); break; }
+    }
     ::close(fd);
   }
 };
@@ -128,10 +135,25 @@ struct Client {
   int fd = -1;
   std::mutex mu;
   int timeout_ms = 30000;
+  // After a failed send or a receive that timed out the stream is in the middle of a message: the next request would
+  // read the tail of the old answer.  The connection is closed instead and every later call fails at once.
+  void drop() {
+    if (fd >= 0) ::close(fd);
+    fd = -1;
+  }
   bool request(uint8_t op, const std::string& key, const void* val, uint64_t vlen) {
+    if (fd < 0) return false;
     uint32_t klen = uint32_t(key.size());
-    return send_all(fd, &op, 1) && send_all(fd, &klen, 4) && (klen == 0 || send_all(fd, key.data(), klen)) &&
-           send_all(fd, &vlen, 8) && (vlen == 0 || send_all(fd, val, vlen));
+    const bool ok = send_all(fd, &op, 1) && send_all(fd, &klen, 4) && (klen == 0 || send_all(fd, key.data(), klen)) &&
+                    send_all(fd, &vlen, 8) && (vlen == 0 || send_all(fd, val, vlen));
+    if (!ok) drop();
+    return ok;
+  }
+  bool recv(void* p, size_t n) {
+    if (fd < 0) return false;
+    const bool ok = recv_all(fd, p, n, timeout_ms);
+    if (!ok) drop();
+    return ok;
   }
 };
 
@@ -216,7 +238,7 @@ int lt_store_set(void* h, const char* key, const void* val, uint64_t len) {
   Client* c = static_cast<Client*>(h);
   std::lock_guard<std::mutex> lk(c->mu);
   uint8_t ok = 0;
-  if (!c->request(1, key, val, len) || !recv_all(c->fd, &ok, 1, c->timeout_ms)) return -1;
+  if (!c->request(1, key, val, len) || !c->recv(&ok, 1)) return -1;
   return ok ? 0 : -2;
 }
 // Polls until the key exists or timeout_ms passed. Returns the value length (copied up to cap), -1 on I/O
@@ -229,9 +251,9 @@ int64_t lt_store_get(void* h, const char* key, void* buf, uint64_t cap, int time
       std::lock_guard<std::mutex> lk(c->mu);
       uint8_t found;
       uint64_t n;
-      if (!c->request(2, key, nullptr, 0) || !recv_all(c->fd, &found, 1, c->timeout_ms) || !recv_all(c->fd, &n, 8, c->timeout_ms)) return -1;
+      if (!c->request(2, key, nullptr, 0) || !c->recv(&found, 1) || !c->recv(&n, 8)) return -1;
       std::string tmp(n, '\0');
-      if (n && !recv_all(c->fd, &tmp[0], n, c->timeout_ms)) return -1;
+      if (n && !c->recv(&tmp[0], n)) return -1;
       if (found) {
         memcpy(buf, tmp.data(), n < cap ? n : cap);
         return int64_t(n);
@@ -245,7 +267,7 @@ int64_t lt_store_add(void* h, const char* key, int64_t delta) {
   Client* c = static_cast<Client*>(h);
   std::lock_guard<std::mutex> lk(c->mu);
   int64_t out = 0;
-  if (!c->request(3, key, &delta, 8) || !recv_all(c->fd, &out, 8, c->timeout_ms)) return INT64_MIN;
+  if (!c->request(3, key, &delta, 8) || !c->recv(&out, 8)) return INT64_MIN;
   return out;
 }
 int lt_store_heartbeat(void* h, int rank) {
@@ -253,20 +275,51 @@ int lt_store_heartbeat(void* h, int rank) {
   std::lock_guard<std::mutex> lk(c->mu);
   uint8_t ok = 0;
   const std::string key = std::to_string(rank);
-  if (!c->request(4, key, nullptr, 0) || !recv_all(c->fd, &ok, 1, c->timeout_ms)) return -1;
+  if (!c->request(4, key, nullptr, 0) || !c->recv(&ok, 1)) return -1;
   return 0;
+}
+// Time a client waits for the answer to one request (default 30 s).
+void lt_store_set_timeout(void* h, int timeout_ms) {
+  Client* c = static_cast<Client*>(h);
+  std::lock_guard<std::mutex> lk(c->mu);
+  c->timeout_ms = timeout_ms;
+}
+// 1 while the connection is usable, 0 after an I/O error or a timeout closed it.
+int lt_store_alive(void* h) {
+  Client* c = static_cast<Client*>(h);
+  std::lock_guard<std::mutex> lk(c->mu);
+  return c->fd >= 0 ? 1 : 0;
+}
+// Ranks of [0, world) with no heartbeat at all, or whose last beat is older than ttl_ms.  A rank that died before its
+// first beat is only visible this way; the caller applies its own grace period after start-up.  Returns the count.
+int lt_store_silent_ranks(void* h, int world, int ttl_ms, int32_t* ranks, int cap) {
+  Client* c = static_cast<Client*>(h);
+  std::lock_guard<std::mutex> lk(c->mu);
+  uint32_t n;
+  if (!c->request(5, "", nullptr, 0) || !c->recv(&n, 4)) return -1;
+  std::vector<int64_t> age(size_t(world > 0 ? world : 0), -1);
+  for (uint32_t i = 0; i < n; ++i) {
+    int32_t r;
+    int64_t a;
+    if (!c->recv(&r, 4) || !c->recv(&a, 8)) return -1;
+    if (r >= 0 && r < world) age[size_t(r)] = a;
+  }
+  int out = 0;
+  for (int r = 0; r < world; ++r)
+    if ((age[size_t(r)] < 0 || age[size_t(r)] > ttl_ms) && out < cap) ranks[out++] = r;
+  return out;
 }
 // Ranks (among those that ever sent a heartbeat) whose last beat is older than ttl_ms. Returns the count.
 int lt_store_dead_ranks(void* h, int ttl_ms, int32_t* ranks, int cap) {
   Client* c = static_cast<Client*>(h);
   std::lock_guard<std::mutex> lk(c->mu);
   uint32_t n;
-  if (!c->request(5, "", nullptr, 0) || !recv_all(c->fd, &n, 4, c->timeout_ms)) return -1;
+  if (!c->request(5, "", nullptr, 0) || !c->recv(&n, 4)) return -1;
   int out = 0;
   for (uint32_t i = 0; i < n; ++i) {
     int32_t r;
     int64_t age;
-    if (!recv_all(c->fd, &r, 4, c->timeout_ms) || !recv_all(c->fd, &age, 8, c->timeout_ms)) return -1;
+    if (!c->recv(&r, 4) || !c->recv(&age, 8)) return -1;
     if (age > ttl_ms && out < cap) ranks[out++] = r;
   }
   return out;
@@ -281,7 +334,12 @@ int lt_store_barrier(void* h, const char* key, int world, int timeout_ms) {
     const int64_t cur = lt_store_add(h, key, 0);
     if (cur == INT64_MIN) return -1;
     if (cur >= target) return 0;
-    if (now_ms() >= deadline) return -2;
+    if (now_ms() >= deadline) {
+      // take this rank's arrival back: otherwise the counter stays off a multiple of `world` and every later
+      // barrier on the key releases early or never
+      lt_store_add(h, key, -1);
+      return -2;
+    }
     usleep(2 * 1000);
   }
 }

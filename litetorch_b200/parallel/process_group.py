@@ -43,6 +43,9 @@ def _store_lib():
         lib.lt_store_heartbeat.argtypes = [c_void_p, c_int]
         lib.lt_store_dead_ranks.argtypes = [c_void_p, c_int, POINTER(c_int32), c_int]
         lib.lt_store_barrier.argtypes = [c_void_p, c_char_p, c_int, c_int]
+        lib.lt_store_silent_ranks.argtypes = [c_void_p, c_int, c_int, POINTER(c_int32), c_int]
+        lib.lt_store_alive.argtypes = [c_void_p]
+        lib.lt_store_set_timeout.argtypes = [c_void_p, c_int]
         lib.lt_filestore_set.argtypes = [c_char_p, c_char_p, c_void_p, c_uint64]
         lib.lt_filestore_get.restype = c_int64
         lib.lt_filestore_get.argtypes = [c_char_p, c_char_p, c_void_p, c_uint64, c_int]
@@ -102,6 +105,18 @@ class TCPStore:
         n = self._lib.lt_store_dead_ranks(self._c, int(ttl_s * 1000), out, 1024)
         return [int(out[i]) for i in range(max(n, 0))]
 
+    def silent_ranks(self, world: int, ttl_s: float) -> List[int]:
+        """Ranks of [0, world) without any heartbeat so far, or with a last heartbeat older than `ttl_s`."""
+        out = (c_int32 * max(world, 1))()
+        n = self._lib.lt_store_silent_ranks(self._c, world, int(ttl_s * 1000), out, max(world, 1))
+        if n < 0:
+            raise RuntimeError("store connection lost")
+        return [int(out[i]) for i in range(n)]
+
+    def alive(self) -> bool:
+        """False once an I/O error or a timeout has closed the connection (every later call fails at once)."""
+        return bool(self._c) and self._lib.lt_store_alive(self._c) == 1
+
     def close(self):
         if self._c:
             self._lib.lt_store_close(self._c)
@@ -133,8 +148,13 @@ class FileStore:
 class Watchdog:
     """Background heartbeat; `check()` raises RankFailure when a peer's heartbeat is older than `ttl_s`."""
 
-    def __init__(self, store: TCPStore, rank: int, interval_s: float = 0.5, ttl_s: float = 5.0):
+    def __init__(self, store: TCPStore, rank: int, interval_s: float = 0.5, ttl_s: float = 5.0,
+                 world_size: Optional[int] = None, grace_s: float = 10.0):
+        """world_size: when given, `check()` also reports ranks that never sent a heartbeat once `grace_s` seconds have
+        passed since this watchdog started (a rank that died during start-up never shows up in the heartbeat table)."""
         self.store, self.rank, self.interval, self.ttl = store, rank, interval_s, ttl_s
+        self.world_size, self.grace = world_size, grace_s
+        self._t0 = time.monotonic()
         self._stop = threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
         self._t.start()
@@ -148,7 +168,10 @@ class Watchdog:
             self._stop.wait(self.interval)
 
     def check(self):
-        dead = [r for r in self.store.dead_ranks(self.ttl) if r != self.rank]
+        if self.world_size is not None and time.monotonic() - self._t0 >= self.grace:
+            dead = [r for r in self.store.silent_ranks(self.world_size, self.ttl) if r != self.rank]
+        else:
+            dead = [r for r in self.store.dead_ranks(self.ttl) if r != self.rank]
         if dead:
             raise RankFailure("ranks %s stopped sending heartbeats (ttl %.1f s)" % (dead, self.ttl))
 
@@ -187,7 +210,7 @@ class ProcessGroup:
                                     world_size=world_size, timeout=timedelta(seconds=timeout_s), **kw)
         if with_store:
             self.store = TCPStore(master_addr, master_port + 1, is_server=(rank == 0))
-            self.watchdog = Watchdog(self.store, rank)
+            self.watchdog = Watchdog(self.store, rank, world_size=world_size)
         self._initialized = True
 
     def shutdown(self) -> None:

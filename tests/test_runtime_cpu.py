@@ -362,3 +362,55 @@ def test_store_delayed_rendezvous_lost_server_and_unreachable_host():
     with pytest.raises(RuntimeError):
         TCPStore("127.0.0.1", port, is_server=False, timeout_s=1.0)
     assert 0.5 < time.time() - t0 < 5
+
+
+def test_store_edge_cases_of_rendezvous_and_failure_detection():
+    """Four host-side failure paths of the native store: a rank that dies before its first heartbeat is reported once
+    the grace period is over; a barrier that timed out leaves the counter usable for the next barrier; a client that
+    disconnects does not leave a stale descriptor behind for the server's stop path; a client whose request timed out
+    drops its connection instead of reading the tail of the old answer."""
+    import socket
+    import threading
+    import time
+    from litetorch_b200.parallel.process_group import RankFailure, TCPStore, Watchdog
+    server = TCPStore("127.0.0.1", 0, is_server=True)
+    # ---- 1. rank 1 of a world of 2 never starts: invisible to dead_ranks, reported through silent_ranks after the grace period
+    w0 = Watchdog(server, 0, interval_s=0.05, ttl_s=0.5, world_size=2, grace_s=0.3)
+    time.sleep(0.15)
+    w0.check()                                     # inside the grace period: nothing to report yet
+    assert server.dead_ranks(0.5) == []
+    time.sleep(0.3)
+    with pytest.raises(RankFailure):
+        w0.check()
+    assert server.silent_ranks(2, 0.5) == [1]
+    w0.stop()
+    # ---- 2. a barrier nobody else joins times out; the next barrier on the same key, with both ranks, completes
+    peer = TCPStore("127.0.0.1", server.port, is_server=False)
+    with pytest.raises(TimeoutError):
+        server.barrier("b", 2, timeout_s=0.2)
+    done = []
+    t = threading.Thread(target=lambda: (peer.barrier("b", 2, timeout_s=5.0), done.append(1)))
+    t.start()
+    server.barrier("b", 2, timeout_s=5.0)
+    t.join(timeout=5)
+    assert done == [1]
+    # ---- 3. a client disconnects; descriptors opened afterwards must survive the server's stop
+    peer.close()
+    time.sleep(0.1)
+    a, b = socket.socketpair()                     # likely reuses the descriptor number the server just closed
+    # ---- 4. a request that times out closes the client's connection
+    mute = socket.socket()
+    mute.bind(("127.0.0.1", 0))
+    mute.listen(1)                                 # accepts the connection but never answers
+    c = TCPStore("127.0.0.1", mute.getsockname()[1], is_server=False, timeout_s=2.0)
+    c._lib.lt_store_set_timeout(c._c, 200)
+    assert c.alive()
+    with pytest.raises(Exception):
+        c.set("k", b"v")                           # no answer within 200 ms
+    assert not c.alive()                           # the half-finished exchange is gone with the connection
+    with pytest.raises(Exception):
+        c.set("k", b"v")                           # and later calls fail at once instead of parsing stale bytes
+    server.close()
+    a.send(b"x")
+    assert b.recv(1) == b"x"                       # the unrelated socket pair was not shut down by the stop path
+    a.close(); b.close(); mute.close()
