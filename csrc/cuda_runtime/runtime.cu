@@ -21,17 +21,48 @@
 namespace {
 
 // ------------------------------------------------------------------ allocator
-struct Block { void* ptr; size_t size; };
+struct Live {
+  size_t size;
+  std::vector<cudaStream_t> extra;   // streams other than the allocation stream that used the block (lt_cuda_record_stream)
+};
+struct Deferred {                    // a freed block that other streams may still be reading
+  void* ptr; size_t size; int device; cudaStream_t stream;
+  std::vector<cudaEvent_t> events;
+};
 struct Allocator {
   std::mutex mu;
-  // (device, stream) -> size-ordered free blocks; a block is only reused on the stream it was freed on,
-  // so no event is needed between the free and the next use.
+  // (device, stream) -> size-ordered free blocks.  A block is reused only on the stream it was allocated on, so
+  // stream order alone separates its old and new use - unless another stream used it too: those uses are
+  // announced with lt_cuda_record_stream, and the block then waits in `deferred` until an event recorded on each
+  // of those streams at free time has completed.
   std::map<std::pair<int, cudaStream_t>, std::multimap<size_t, void*>> free_lists;
-  std::unordered_map<void*, size_t> live;
+  std::unordered_map<void*, Live> live;
+  std::vector<Deferred> deferred;
   size_t cached = 0, allocated = 0, peak = 0, hits = 0, misses = 0;
   size_t max_cached = 0;  // 0 = unlimited
 };
 Allocator g_alloc;
+
+bool stream_is_capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess) { cudaGetLastError(); return false; }
+  return st != cudaStreamCaptureStatusNone;
+}
+
+// Moves deferred blocks whose events have all completed to the free lists.  Caller holds the lock.
+void reap_deferred_locked() {
+  for (size_t i = 0; i < g_alloc.deferred.size();) {
+    Deferred& d = g_alloc.deferred[i];
+    bool done = true;
+    for (cudaEvent_t e : d.events)
+      if (cudaEventQuery(e) != cudaSuccess) { cudaGetLastError(); done = false; break; }
+    if (!done) { ++i; continue; }
+    for (cudaEvent_t e : d.events) cudaEventDestroy(e);
+    g_alloc.free_lists[{d.device, d.stream}].emplace(d.size, d.ptr);
+    g_alloc.deferred[i] = std::move(g_alloc.deferred.back());
+    g_alloc.deferred.pop_back();
+  }
+}
 
 size_t round_size(size_t n) {
   if (n < 512) return 512;
@@ -96,6 +127,8 @@ void* lt_cuda_alloc(ssize_t size, int device, cudaStream_t stream) {
   if (size <= 0) size = 1;
   const size_t sz = round_size(size_t(size));
   std::lock_guard<std::mutex> lk(g_alloc.mu);
+  const bool capturing = stream_is_capturing(stream);
+  if (!capturing && !g_alloc.deferred.empty()) reap_deferred_locked();
   auto& fl = g_alloc.free_lists[{device, stream}];
   auto it = fl.lower_bound(sz);
   void* ptr = nullptr;
@@ -107,6 +140,9 @@ void* lt_cuda_alloc(ssize_t size, int device, cudaStream_t stream) {
     g_alloc.cached -= got;
     g_alloc.hits++;
   } else {
+    // cudaMalloc is not allowed while the stream records a graph: refuse (the caller sees an out-of-memory error)
+    // rather than invalidate the capture.  Warm the cache with one eager run before capturing.
+    if (capturing) { g_alloc.misses++; return nullptr; }
     int prev = 0;
     cudaGetDevice(&prev);
     if (prev != device) cudaSetDevice(device);
@@ -119,7 +155,7 @@ void* lt_cuda_alloc(ssize_t size, int device, cudaStream_t stream) {
     g_alloc.misses++;
     if (!ptr) return nullptr;
   }
-  g_alloc.live[ptr] = got;
+  g_alloc.live[ptr] = Live{got, {}};
   g_alloc.allocated += got;
   if (g_alloc.allocated > g_alloc.peak) g_alloc.peak = g_alloc.allocated;
   return ptr;
@@ -129,19 +165,45 @@ void lt_cuda_free(void* ptr, ssize_t, int device, cudaStream_t stream) {
   std::lock_guard<std::mutex> lk(g_alloc.mu);
   auto it = g_alloc.live.find(ptr);
   if (it == g_alloc.live.end()) return;
-  const size_t sz = it->second;
+  const size_t sz = it->second.size;
+  std::vector<cudaStream_t> extra = std::move(it->second.extra);
   g_alloc.live.erase(it);
   g_alloc.allocated -= sz;
-  if (g_alloc.max_cached && g_alloc.cached + sz > g_alloc.max_cached) {
-    cudaFree(ptr);
+  const bool capturing = stream_is_capturing(stream);
+  if (!capturing && g_alloc.max_cached && g_alloc.cached + sz > g_alloc.max_cached && extra.empty()) {
+    cudaFree(ptr);       // implicit device synchronisation: nothing can still be using the block afterwards
+    return;
+  }
+  g_alloc.cached += sz;
+  if (!extra.empty() && !capturing) {
+    Deferred d{ptr, sz, device, stream, {}};
+    for (cudaStream_t s : extra) {
+      cudaEvent_t e = nullptr;
+      if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(e, s) == cudaSuccess) d.events.push_back(e);
+      else { cudaGetLastError(); if (e) cudaEventDestroy(e); }
+    }
+    g_alloc.deferred.push_back(std::move(d));
     return;
   }
   g_alloc.free_lists[{device, stream}].emplace(sz, ptr);
-  g_alloc.cached += sz;
+}
+// Announces that `stream` (not the block's allocation stream) uses the block: when the block is freed it is handed
+// out again only after the work queued on `stream` up to that moment has finished.  PyTorch's pluggable-allocator
+// binding does not forward tensor.record_stream() to the allocator from Python, so callers that pass temporaries
+// to side streams call this (lt.cuda.record_stream); a temporary shared with another stream WITHOUT this call may
+// be reused too early.
+void lt_cuda_record_stream(void* ptr, cudaStream_t stream) {
+  if (!ptr) return;
+  std::lock_guard<std::mutex> lk(g_alloc.mu);
+  auto it = g_alloc.live.find(ptr);
+  if (it == g_alloc.live.end()) return;
+  for (cudaStream_t s : it->second.extra) if (s == stream) return;
+  it->second.extra.push_back(stream);
 }
 void lt_cuda_empty_cache() {
   std::lock_guard<std::mutex> lk(g_alloc.mu);
   cudaDeviceSynchronize();
+  reap_deferred_locked();
   release_cached_locked();
 }
 void lt_cuda_set_max_cached(uint64_t bytes) { std::lock_guard<std::mutex> lk(g_alloc.mu); g_alloc.max_cached = bytes; }

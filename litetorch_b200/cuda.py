@@ -42,7 +42,13 @@ _installed = [False]
 
 
 def use_caching_allocator() -> bool:
-    """Install the native allocator as PyTorch's CUDA allocator. Must run before the first CUDA allocation."""
+    """Install the native allocator as PyTorch's CUDA allocator. Must run before the first CUDA allocation.
+
+    Blocks are cached per (device, stream) and reused in stream order.  A temporary that another stream also uses
+    must be announced with `lt.cuda.record_stream(tensor, stream)`: PyTorch does not forward
+    `tensor.record_stream` to a pluggable allocator from Python.  While a stream records a CUDA graph the allocator
+    serves requests from its cache only (it never calls cudaMalloc inside a capture); run the region once eagerly
+    first."""
     if _installed[0]:
         return True
     from ._native import _LIB
@@ -51,6 +57,16 @@ def use_caching_allocator() -> bool:
     torch.cuda.memory.change_current_allocator(alloc)
     _installed[0] = True
     return True
+
+
+def record_stream(t: torch.Tensor, stream: "torch.cuda.Stream") -> None:
+    """`t` is used on `stream` (not the stream it was allocated on): keep its memory from being handed out again,
+    after `t` is freed, until the work queued on `stream` so far has finished.  Works with PyTorch's own allocator
+    (tensor.record_stream) and with the native one (lt_cuda_record_stream)."""
+    t.record_stream(stream)
+    if _installed[0]:
+        from ._native import cuda_lib
+        cuda_lib().lt_cuda_record_stream(ctypes.c_void_p(t.untyped_storage().data_ptr()), ctypes.c_void_p(stream.cuda_stream))
 
 
 def allocator_stats() -> dict:
