@@ -51,6 +51,9 @@ def _parse():
     ap.add_argument("--no-comm-breakdown", action="store_true",
                     help="skip the extra communication-free steps that give exposed_comm_ms_per_step at N > 1")
     ap.add_argument("--no-extras", action="store_true", help="skip the llama_1b and probe measurements")
+    ap.add_argument("--configs", default="auto", choices=["auto", "on", "off"],
+                    help="also time the three other 8-GPU layouts (tp8, ep8, tp2 x cp2 x pp2) outside the timed region "
+                         "(auto: on 8 GPUs)")
     ap.add_argument("--hybrid", action="store_true",
                     help="with --tp 1: shard over dp with the FSDP x TP provider (weights prefetched by peer-pull kernels) "
                          "instead of the ZeRO-3 provider whose all-gather runs inside the GEMMs")
@@ -190,6 +193,9 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
+        # NCCL carries only small messages here (norm-gain gradients, cross-entropy statistics, one embedding-gradient
+        # gather); in-switch reduction is left off so that no rank's memory is bound to a multicast object
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     cfg = _model_config(args.model)
     per_gpu, T = SHAPES[args.model]
@@ -298,6 +304,26 @@ def run_ours(args):
         except Exception as e:  # pragma: no cover
             extras["probe_error"] = repr(e)[:200]
 
+    # ---------------- the other multi-GPU layouts (8 GPUs), outside the timed regions, under a wall-clock limit: when it
+    # runs out the line is printed without them (a stuck collective must not take the headline with it)
+    want_cfgs = (args.configs == "on") or (args.configs == "auto" and world == 8 and big and not args.no_extras)
+    state = {"partial": None}
+    if want_cfgs and world > 1:
+        import threading
+        limit = float(os.environ.get("LT_BENCH_CONFIGS_LIMIT_S", "420"))
+
+        def give_up():
+            if rank == 0 and state["partial"] is not None:
+                line = dict(state["partial"])
+                line["configs"] = dict(state.get("configs", {}), error="time limit of %.0f s reached" % limit)
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+
+        timer = threading.Timer(limit, give_up)
+        timer.daemon = True
+    else:
+        timer = None
+
     vals = [ms_total, e2e_ms, local_ms]
     if "llama_1b" in extras:
         vals += list(extras["llama_1b"][:3])
@@ -351,6 +377,29 @@ def run_ours(args):
         for k in ("llama_1b_error", "probe_error"):
             if k in extras:
                 out[k] = extras[k]
+        state["partial"] = out
+    if timer is not None:
+        from litetorch_b200.models import run_config
+        timer.start()
+        cfgs = state.setdefault("configs", {})
+        tiny = ["--tiny"] if not big else []
+        for name in ("tp8", "ep8", "hybrid"):
+            if name == "hybrid" and world not in (2, 4, 8):
+                continue
+            try:
+                ns = run_config._parser().parse_args(["--config", name, "--steps", "3", "--warmup", "2"] + tiny)
+                rec = run_config.run(ns, quiet=True)
+                cfgs[name] = {k: rec[k] for k in ("model", "layout", "seq_len", "tokens_per_step", "ms_per_step", "tokens_per_s",
+                                                  "loss", "fused", "device_status", "params_b", "steps", "warmup")}
+            except Exception as e:  # pragma: no cover
+                cfgs[name] = {"error": repr(e)[:200]}
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+        timer.cancel()
+        if rank == 0:
+            out["configs"] = cfgs
+    if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()

@@ -68,7 +68,7 @@ class _Stage:
         return [Tensor(p) for p in self.model.parameters()]
 
 
-def main():
+def _parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", choices=["tp8", "ep8", "hybrid"], required=True)
     ap.add_argument("--tiny", action="store_true")
@@ -82,16 +82,27 @@ def main():
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per step (default: the layout's)")
     ap.add_argument("--cp-mode", choices=["ring", "ulysses"], default="ring",
                     help="context parallelism: all-ranks ring attention (zigzag split) or Ulysses all-to-all (contiguous split)")
-    args = ap.parse_args()
+    return ap
 
+
+def main():
+    run(_parser().parse_args())
+
+
+def run(args, quiet: bool = False):
+    """Runs one configuration (`args`: the namespace of `_parser()`) and returns its result record (rank 0 also prints it unless `quiet`).  When the
+    process group already exists (a caller that measures several configurations in one job) it is used and left
+    alive; otherwise it is created here and destroyed at the end."""
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     cuda = torch.cuda.is_available()
     if cuda:
         torch.cuda.set_device(local)
     dev = "cuda" if cuda else "cpu"
-    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", local) if cuda else None)
+    own_pg = not dist.is_initialized()
+    if own_pg:
+        dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local) if cuda else None)
     dtype = torch.bfloat16 if cuda else torch.float32
     fused = cuda and not args.no_fused and world > 1
 
@@ -216,22 +227,27 @@ def main():
     dist.all_reduce(lv, op=dist.ReduceOp.MAX)
     dp_like = world if args.config == "ep8" else (dist.get_world_size(groups["dp"]) if groups["dp"] is not None else 1)
     tokens = n_seq * seq * micro * dp_like
-    if rank == 0:
-        status = 0
-        if cuda:
-            from ..ops import kernels as K
-            status = K.status_fetch()
-        print(json.dumps({"config": args.config, "model": cfg.name, "layout": layout, "n_gpus": world, "seq_len": seq,
-                          "tokens_per_step": tokens, "ms_per_step": round(float(t), 3),
-                          "tokens_per_s": round(tokens / float(t) * 1e3, 1), "loss": round(float(lv), 4),
-                          "fused": bool(fused) and not dims.fp8, "fp8": bool(dims.fp8), "dtype": str(dtype).replace("torch.", ""), "device_status": status,
-                          "params_b": round(cfg.n_params() / 1e9, 3)}), flush=True)
+    status = 0
+    if cuda:
+        from ..ops import kernels as K
+        st = torch.tensor([K.status_fetch()], device=dev)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        status = int(st)
+    record = {"config": args.config, "model": cfg.name, "layout": layout, "n_gpus": world, "seq_len": seq,
+              "tokens_per_step": tokens, "ms_per_step": round(float(t), 3),
+              "tokens_per_s": round(tokens / float(t) * 1e3, 1), "loss": round(float(lv), 4),
+              "fused": bool(fused) and not dims.fp8, "fp8": bool(dims.fp8), "dtype": str(dtype).replace("torch.", ""),
+              "device_status": status, "params_b": round(cfg.n_params() / 1e9, 3), "steps": args.steps, "warmup": args.warmup}
+    if rank == 0 and not quiet:
+        print(json.dumps(record), flush=True)
     if rank == 0 and sections.enabled():
         # per-section CUDA-event totals over the timed steps (LT_SECTIONS=1); nested sections are included in their parents
         print(json.dumps({"sections_ms_per_step": {k: [v[0] // max(args.steps, 1), round(v[1] / max(args.steps, 1), 3)]
                                                    for k, v in sections.report().items()}}), flush=True)
     dist.barrier()
-    dist.destroy_process_group()
+    if own_pg:
+        dist.destroy_process_group()
+    return record
 
 
 if __name__ == "__main__":
