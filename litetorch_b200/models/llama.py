@@ -50,6 +50,10 @@ class SingleTPMixin:
     def reduce_ce_stats(self, stats):
         return stats
 
+    def gather_slot(self, rows, cols):
+        """Where the producer of the next gathered activation should write it (None: anywhere)."""
+        return None
+
 
 @dataclass
 class LlamaConfig:
@@ -319,7 +323,7 @@ class LlamaEngine:
         cfg, w, K = self.cfg, self.w, self.K
         p = "layers.%d." % i
         Hq, Hkv, hd = self.Hq, self.Hkv, cfg.head_dim
-        h1, _, _, rstd1 = K.norm_fwd(x, w.p(p + "attn_norm"), eps=cfg.rms_eps)
+        h1, _, _, rstd1 = K.norm_fwd(x, w.p(p + "attn_norm"), eps=cfg.rms_eps, out=w.gather_slot(*x.shape))
         qkv, h1f = w.col_linear(h1, p + "wqkv")
         K.rope_(qkv, self.cos, self.sin, T, Hq, hd, col_offset=0)
         K.rope_(qkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd)
@@ -327,7 +331,7 @@ class LlamaEngine:
         o, lse = K.flash_fwd(q, k, v, causal=True)
         o2 = o.view(B * T, Hq * hd)
         x1 = w.row_linear(o2, p + "wo", residual=x)
-        h2, _, _, rstd2 = K.norm_fwd(x1, w.p(p + "mlp_norm"), eps=cfg.rms_eps)
+        h2, _, _, rstd2 = K.norm_fwd(x1, w.p(p + "mlp_norm"), eps=cfg.rms_eps, out=w.gather_slot(*x1.shape))
         gu, h2f = w.col_linear(h2, p + "w_gu")
         hm = K.swiglu_fwd(gu)
         x2 = w.row_linear(hm, p + "w_down", residual=x1)
@@ -354,7 +358,7 @@ class LlamaEngine:
         dh2 = w.col_dgrad(dgu, p + "w_gu")
         w.wgrad(dgu, h2f, p + "w_gu", accumulate)
         dx1, _, _ = K.norm_bwd(dh2, x1, w.p(p + "mlp_norm"), None, rstd2, dres=dx2, dw=w.vector_grad(p + "mlp_norm"),
-                               accumulate=accumulate)
+                               accumulate=accumulate, out=w.gather_slot(*x1.shape))
         # attention
         o2 = o.view(B * T, Hq * hd)
         do, dx1f = w.row_dgrad(dx1, p + "wo")
@@ -367,8 +371,9 @@ class LlamaEngine:
         K.rope_(dqkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd, backward=True)
         dh1 = w.col_dgrad(dqkv, p + "wqkv")
         w.wgrad(dqkv, h1f, p + "wqkv", accumulate)
+        # the gradient that leaves this layer is the next layer's input to a gathered GEMM (not for layer 0: embedding)
         dx, _, _ = K.norm_bwd(dh1, x, w.p(p + "attn_norm"), None, rstd1, dres=dx1, dw=w.vector_grad(p + "attn_norm"),
-                              accumulate=accumulate)
+                              accumulate=accumulate, out=w.gather_slot(*x.shape) if i > 0 else None)
         self.kernel_launches += 22
         return dx
 
@@ -393,7 +398,7 @@ class LlamaEngine:
             else:
                 x, ctx = self._layer_fwd(i, x, B, T)
                 saved.append(ctx)
-        hf, _, _, rstd_f = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
+        hf, _, _, rstd_f = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps, out=w.gather_slot(*x.shape))
         logits, hff = w.col_linear(hf, "lm_head")
         stats = w.reduce_ce_stats(K.ce_stats(logits, tgt, w.vocab_start))
         rows = K.ce_finish(logits, tgt, stats, vocab_start=w.vocab_start, grad_scale=loss_scale / (M * self.world_size))
@@ -403,7 +408,8 @@ class LlamaEngine:
         if fused_update:
             w.bucket_done("head")
         del logits, hff
-        dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate)
+        dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate,
+                              out=w.gather_slot(*x.shape))
         for i in reversed(range(cfg.n_layers)):
             if i < self.ckpt_layers:
                 _, ctx = self._layer_fwd(i, saved[i], B, T)

@@ -250,10 +250,12 @@ def gemm_fp8_block(a8, a_scale_t, b8, b_scale, out=None, *, bias=None, out_dtype
 
 
 # ------------------------------------------------------------------------------------------------ norms
-def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5, want_sum=True):
-    """Returns (y, sum_or_None, mean_or_None, rstd).  x, residual: [M, D] bf16."""
+def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5, want_sum=True, out=None):
+    """Returns (y, sum_or_None, mean_or_None, rstd).  x, residual: [M, D] bf16.  `out`: optional contiguous [M, D]
+    buffer for y (e.g. the symmetric-memory slot a tensor-parallel gather reads from)."""
     M, D = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
+    assert y.shape == x.shape and y.is_contiguous() and y.dtype == x.dtype
     s = torch.empty_like(x) if (residual is not None and want_sum) else None
     mean = torch.empty(M, dtype=torch.float32, device=x.device) if layer_norm else None
     rstd = torch.empty(M, dtype=torch.float32, device=x.device)
@@ -263,10 +265,12 @@ def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5,
     return y, s, mean, rstd
 
 
-def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None, db=None, accumulate=False):
-    """Returns (dx, dw, db).  `x` is the tensor that was normalised (the residual sum when one was fused)."""
+def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None, db=None, accumulate=False, out=None):
+    """Returns (dx, dw, db).  `x` is the tensor that was normalised (the residual sum when one was fused).
+    `out`: optional contiguous [M, D] buffer for dx."""
     M, D = x.shape
-    dx = torch.empty_like(x)
+    dx = torch.empty_like(x) if out is None else out
+    assert dx.shape == x.shape and dx.is_contiguous() and dx.dtype == x.dtype
     ctas = _fn("lt_norm_bwd_ctas")(M)
     part = torch.empty((2 if layer_norm else 1, ctas, D), dtype=torch.float32, device=x.device)
     if dw is None:

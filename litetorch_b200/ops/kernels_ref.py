@@ -51,7 +51,7 @@ def gemm(a, b, *, a_major=0, b_major=0, out=None, out_dtype=None, bias=None, res
     return out
 
 
-def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5, want_sum=True):
+def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5, want_sum=True, out=None):
     xf = x.float()
     s = None
     if residual is not None:
@@ -68,10 +68,13 @@ def norm_fwd(x, weight, bias=None, residual=None, *, layer_norm=False, eps=1e-5,
     y = xc * rstd[:, None] * weight.float()
     if bias is not None:
         y = y + bias.float()
+    if out is not None:
+        out.copy_(y.to(x.dtype))
+        return out, s, mean, rstd
     return y.to(x.dtype), s, mean, rstd
 
 
-def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None, db=None, accumulate=False):
+def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None, db=None, accumulate=False, out=None):
     xf, g = x.float(), dy.float()
     xc = xf - mean[:, None] if layer_norm else xf
     xhat = xc * rstd[:, None]
@@ -98,6 +101,9 @@ def norm_bwd(dy, x, weight, mean, rstd, *, layer_norm=False, dres=None, dw=None,
             db.copy_((db.float() + dbv).to(db.dtype))
         else:
             db.copy_(dbv.to(db.dtype))
+    if out is not None:
+        out.copy_(dx.to(x.dtype))
+        return out, dw, db
     return dx.to(x.dtype), dw, db
 
 

@@ -342,6 +342,13 @@ class HybridWeights:
         dist.all_reduce(y, group=self.tp_group)
         return y[self.tp_rank * rows:(self.tp_rank + 1) * rows].contiguous()
 
+    def gather_slot(self, rows, cols):
+        """The symmetric-memory slot that the next fused gather will read this rank's rows from: a norm kernel that
+        writes its output there saves the copy into the slot (None when nothing is gathered that way)."""
+        if self.tp == 1 or not self.fused:
+            return None
+        return self._tp(rows * self.tp).input_slot(rows, cols)
+
     def col_linear(self, x, name):
         """(all_gather(x) @ W^T, all_gather(x)): x is this rank's block of token rows, W its slice of output rows."""
         W = self.weight(name)

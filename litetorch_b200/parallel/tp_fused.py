@@ -45,6 +45,13 @@ class TPFusedContext:
         self.barrier_epoch += 1
         K.signal_barrier(self.flags.tensor, self.flags.ptrs, 0, self.barrier_epoch, self.world, self.rank)
 
+    def input_slot(self, rows: int, cols: int) -> torch.Tensor:
+        """[rows, cols] view of the symmetric slot the NEXT gather reads this rank's rows from.  A producer that writes
+        its result here and passes the view to `gather_gemm` saves the copy into the slot.  The slot alternates with
+        every gather; the one returned here was last read by the peers two gathers ago, and the barrier of the gather
+        in between has shown that they are done with it."""
+        return self.shard[self.ag_calls & 1].tensor[:rows * cols].view(rows, cols)
+
     def gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, bias=None, b_major: int = 0, full_out: torch.Tensor = None):
         """y = all_gather(x_shard) @ op(w) with the gather inside the GEMM kernel.
         b_major 0: w is [N, K] (y = x @ w^T); 1: w is [K, N] (y = x @ w).
@@ -55,7 +62,8 @@ class TPFusedContext:
         slot = self.ag_calls & 1
         self.ag_calls += 1
         sh = self.shard[slot].tensor[:rows * Kd].view(rows, Kd)
-        sh.copy_(x_shard)
+        if x_shard.data_ptr() != sh.data_ptr():
+            sh.copy_(x_shard)
         full = self.full[:M * Kd].view(M, Kd) if full_out is None else full_out
         assert full.shape == (M, Kd) and full.is_contiguous()
         # This rank's own rows need no gather: they go straight into the assembled operand and their chunk flags are
