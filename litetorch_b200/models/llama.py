@@ -299,8 +299,11 @@ class LlamaEngine:
 
     def __init__(self, cfg: LlamaConfig, device="cuda", weights=None, seed: int = 0, lr: float = 3e-4,
                  betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, activation_checkpointing: bool = False,
-                 world_size: int = 1):
+                 world_size: int = 1, head_chunk_rows: int = 0):
         self.cfg = cfg
+        # > 0: the LM head and the loss go through in chunks of that many token rows, so that only [chunk, vocab]
+        # logits exist at a time (whole weights on this rank only)
+        self.head_chunk_rows = int(head_chunk_rows)
         self.device = torch.device(device)
         self.K = kernels_for(self.device)
         self.w = weights if weights is not None else LocalWeights(cfg, self.device, seed)
@@ -399,15 +402,28 @@ class LlamaEngine:
                 x, ctx = self._layer_fwd(i, x, B, T)
                 saved.append(ctx)
         hf, _, _, rstd_f = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps, out=w.gather_slot(*x.shape))
-        logits, hff = w.col_linear(hf, "lm_head")
-        stats = w.reduce_ce_stats(K.ce_stats(logits, tgt, w.vocab_start))
-        rows = K.ce_finish(logits, tgt, stats, vocab_start=w.vocab_start, grad_scale=loss_scale / (M * self.world_size))
-        loss = rows.sum() / M
-        dhf = w.col_dgrad(logits, "lm_head")
-        w.wgrad(logits, hff, "lm_head", accumulate)
+        if self.head_chunk_rows > 0 and isinstance(w, LocalWeights):
+            # chunked head: logits of one chunk -> their gradient in place -> the two gradient GEMMs; no [M, V] tensor
+            dhf = torch.empty_like(hf)
+            loss = torch.zeros((), dtype=torch.float32, device=hf.device)
+            for ci, s0 in enumerate(range(0, M, self.head_chunk_rows)):
+                hc, tc = hf[s0:s0 + self.head_chunk_rows], tgt[s0:s0 + self.head_chunk_rows]
+                lg = w.linear(hc, "lm_head")
+                rows = K.ce_finish(lg, tc, K.ce_stats(lg, tc), grad_scale=loss_scale / (M * self.world_size))
+                loss = loss + rows.sum()
+                K.gemm(lg, w.p("lm_head"), b_major=1, out=dhf[s0:s0 + self.head_chunk_rows])
+                w.wgrad(lg, hc, "lm_head", accumulate or ci > 0)
+            loss = loss / M
+        else:
+            logits, hff = w.col_linear(hf, "lm_head")
+            stats = w.reduce_ce_stats(K.ce_stats(logits, tgt, w.vocab_start))
+            rows = K.ce_finish(logits, tgt, stats, vocab_start=w.vocab_start, grad_scale=loss_scale / (M * self.world_size))
+            loss = rows.sum() / M
+            dhf = w.col_dgrad(logits, "lm_head")
+            w.wgrad(logits, hff, "lm_head", accumulate)
+            del logits, hff
         if fused_update:
             w.bucket_done("head")
-        del logits, hff
         dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate,
                               out=w.gather_slot(*x.shape))
         for i in reversed(range(cfg.n_layers)):

@@ -189,6 +189,12 @@ class Ops:
         from torch.utils.checkpoint import checkpoint as ckpt
         xt, wt, tt = _unwrap(x), _unwrap(weight), _unwrap(target).to(torch.int64)
         bt = _unwrap(bias)
+        if bt is None:
+            # CUDA bf16: chunks on the tcgen05 GEMM and the cross-entropy kernels, gradients formed in the forward
+            # pass, nothing recomputed and no [N, V] tensor at any time
+            fused = Fn.fused_linear_cross_entropy(xt, wt, tt, chunk_rows)
+            if fused is not None:
+                return _w(fused.reshape(1))
         N = xt.shape[0]
         total = xt.new_zeros((), dtype=torch.float32)
 

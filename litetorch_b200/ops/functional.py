@@ -457,3 +457,47 @@ def moe_router(logits: torch.Tensor, top_k: int, renorm: bool = True):
     if renorm:
         top_p = top_p / top_p.sum(-1, keepdim=True)
     return top_p, top_i, probs
+
+
+class _FusedLinearCE(torch.autograd.Function):
+    """Mean cross-entropy of x @ W^T against integer targets without ever holding the [N, V] logits: rows go through in
+    chunks, and because the gradient of the loss with respect to the logits needs nothing from upstream but one scalar,
+    each chunk's logits are turned into their gradient in place (`lt_ce_finish`) and consumed at once by the two
+    gradient GEMMs - d(x) for the chunk and the running d(W).  Backward only scales the two stored gradients.  The
+    reference chunks the same way but recomputes the logits in backward (src/ops/fused_loss.cpp:12-195)."""
+
+    @staticmethod
+    def forward(ctx, x, w, target, chunk_rows):
+        from . import kernels as K
+        N, Kd = x.shape
+        V = w.shape[0]
+        tgt = target.to(torch.int64).contiguous()
+        x = x.contiguous()
+        w = w.contiguous()
+        n_chunks = (N + chunk_rows - 1) // chunk_rows
+        dx = torch.empty_like(x)
+        dw = torch.empty((V, Kd), dtype=torch.float32 if n_chunks > 4 else torch.bfloat16, device=x.device)
+        total = torch.zeros((), dtype=torch.float32, device=x.device)
+        for ci, s0 in enumerate(range(0, N, chunk_rows)):
+            xc, tc = x[s0:s0 + chunk_rows], tgt[s0:s0 + chunk_rows]
+            logits = K.gemm(xc, w)                                    # [chunk, V]: the only piece of the logits that exists
+            stats = K.ce_stats(logits, tc)
+            rows = K.ce_finish(logits, tc, stats, grad_scale=1.0 / N)  # logits now hold d(loss)/d(logits)
+            total = total + rows.sum()
+            K.gemm(logits, w, b_major=1, out=dx[s0:s0 + chunk_rows])
+            K.gemm(logits, xc, a_major=1, b_major=1, out=dw, accumulate=ci > 0)
+        ctx.save_for_backward(dx, dw)
+        ctx.w_dtype = w.dtype
+        return total / N
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        return dx * g.to(dx.dtype), (dw * g).to(ctx.w_dtype), None, None
+
+
+def fused_linear_cross_entropy(x: torch.Tensor, w: torch.Tensor, target: torch.Tensor, chunk_rows: int = 4096):
+    """Kernel path of `Ops.fused_linear_cross_entropy` (CUDA, bf16, no bias); None when it does not apply."""
+    if not (_native(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.is_cuda):
+        return None
+    return _FusedLinearCE.apply(x, w, target, int(chunk_rows))

@@ -96,3 +96,38 @@ def test_trainer_save_then_load_continues_the_loss_curve(tmp_path):
     assert all(abs(x - y) < 2e-3 for x, y in zip(first, full[:3])), (first, full[:3])   # atomics: not bit-reproducible
     assert all(abs(x - y) < 2e-3 for x, y in zip(rest, full[3:])), (rest, full[3:])   # bf16 atomics in two kernels
     assert c.engine.step_count == 6
+
+
+def test_chunked_head_and_fused_linear_cross_entropy_never_hold_full_logits():
+    """The chunked LM head of the engine and `Ops.fused_linear_cross_entropy` on the kernels: same loss and gradients as
+    the unchunked path / an fp32 PyTorch reference, with a peak allocation far below the [N, V] logits."""
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor, _unwrap
+    from litetorch_b200.models.llama import LlamaConfig, LlamaEngine
+    cfg = LlamaConfig.tiny()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    tok = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda", generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    a = LlamaEngine(cfg, "cuda", seed=2)
+    b = LlamaEngine(cfg, "cuda", seed=2, head_chunk_rows=128)
+    la, lb = a.forward_backward(tok, tgt), b.forward_backward(tok, tgt)
+    assert abs(float(la) - float(lb)) < 2e-3
+    assert _err(b.w.flat_g, a.w.flat_g) < 2e-2
+    # the op: N x V = 8192 x 32768 logits would be 512 MB in bf16; chunks of 1024 rows keep 64 MB at a time
+    N, Kd, V = 8192, 256, 32768
+    x = (torch.randn(N, Kd, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(V, Kd, device="cuda", generator=g) * 0.05).bfloat16().requires_grad_(True)
+    t = torch.randint(0, V, (N,), device="cuda", generator=g)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    loss = _unwrap(lt.Ops.fused_linear_cross_entropy(Tensor(x), Tensor(w), Tensor(t.float()), chunk_rows=1024))
+    loss.sum().backward()
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    assert peak < 0.5 * N * V * 2, peak
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xf @ wf.t(), t)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3
+    assert _err(x.grad, xf.grad) < 2e-2 and _err(w.grad, wf.grad) < 2e-2
