@@ -112,9 +112,38 @@ void lt_gemm_set_tail_split(int enable) { lt::g_split_enabled.store(enable ? 1 :
 // C[M,N] = epilogue(alpha * op(A) * op(B)).  See gemm_sm100.cuh for the operand layouts.
 // lda/ldb/ldc/ldr are pitches in elements. block_n: 0 = choose, else 128 or 256. max_ctas: 0 = one per SM.
 // Returns 0, a cudaError_t, or 1000+/2000+ CUresult when a tensor map could not be encoded.
+static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
+                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream);
+
 int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                  long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
                  long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream) {
+  return gemm_launch(0, A, B, C, M, N, K, lda, ldb, ldc, a_major, b_major, out_fp32, bias, residual, ldr, act, accumulate, alpha,
+                     block_n, max_ctas, stream);
+}
+
+// The same GEMM for fp16 operands (kind 1: any operand layout, C bf16 or fp32) and for fp32 operands on the tensor cores
+// as tf32 (kind 2: both operands K-major, i.e. a_major = b_major = 0, K a multiple of 4, C fp32).  bias / residual
+// stay bf16.  Takes the place of the reference's cublasHgemm / cublasSgemm-with-TF32 paths
+// (src/backend/gpu_native/math/gemm.cu:3-47, 75-120).
+int lt_gemm_typed(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                  long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
+                  long long ldr, int act, int accumulate, float alpha, void* stream) {
+  using namespace lt;
+  if (kind < 0 || kind > 2) return -int(kStatusBadArgument);
+  if (kind == 2) {
+    if (a_major != 0 || b_major != 0 || !out_fp32 || (K & 3) || (lda & 3) || (ldb & 3)) return -int(kStatusBadArgument);
+    // fp32 rows seen as rows of 2-byte units: twice the K extent and twice the pitches
+    return gemm_launch(2, A, B, C, M, N, 2 * K, 2 * lda, 2 * ldb, ldc, 0, 0, 1, bias, residual, ldr, act, accumulate, alpha, 0, 0, stream);
+  }
+  return gemm_launch(kind, A, B, C, M, N, K, lda, ldb, ldc, a_major, b_major, out_fp32, bias, residual, ldr, act, accumulate,
+                     alpha, 0, 0, stream);
+}
+
+static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
+                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream) {
   using namespace lt;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) ||
@@ -128,6 +157,7 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
     const double single = c256 < c128 ? c256 : c128;
     if (pair_mode == 2 || pair_cost(M, N, K, sms, split_on) < single) {
       GemmParams q{};
+      q.kind = kind;
       q.M = M; q.N = N; q.K = K;
       q.C = C; q.ldc = ldc; q.out_fp32 = out_fp32;
       q.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -164,6 +194,7 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   }
   if (block_n != 128 && block_n != 256) block_n = split_on ? pick_block_n_split(M, N, K, sms) : pick_block_n(M, N, sms);
   GemmParams p{};
+  p.kind = kind;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
   p.bias = static_cast<const __nv_bfloat16*>(bias);

@@ -28,6 +28,11 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
 struct GemmParams {
+  // Operand element kind: 0 = bf16, 1 = fp16 (both kind::f16), 2 = fp32 used as tf32 (kind::tf32).  For tf32 the
+  // host describes the operands to TMA as 2-byte elements of twice the K extent (the copy is byte-identical) and
+  // K below counts those 2-byte units, so the tiling, the 128-byte swizzled stage rows and the 32-byte descriptor
+  // step per MMA are the same for every kind; only the instruction and the format bits of its descriptor differ.
+  int kind;
   int M, N, K;
   void* C;
   long long ldc;
@@ -349,7 +354,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, 1, A_MAJOR, B_MAJOR);
+      const uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
+      const bool tf32 = p.kind == 2;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -371,7 +377,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            if (tf32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }

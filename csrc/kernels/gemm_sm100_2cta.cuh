@@ -160,7 +160,8 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, 1, A_MAJOR, B_MAJOR);
+      const uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
+      const bool tf32 = p.kind == 2;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -182,7 +183,8 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            if (tf32) umma_tf32_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
           if (++stage == S) { stage = 0; phase ^= 1u; }

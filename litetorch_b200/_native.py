@@ -86,8 +86,9 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
                 if verbose:
                     print("compiled", o)
     if jobs or not os.path.exists(out) or os.path.getmtime(out) < _newest(objs):
-        cmd = [nvcc, "-shared", "-o", out] + objs + ["-ldl"]
+        cmd = [nvcc, "-shared", "-o", out + ".tmp"] + objs + ["-ldl"]
         _compile_one(cmd, out)
+        os.replace(out + ".tmp", out)      # a reader never sees a half-written library
     return out
 
 
@@ -112,7 +113,8 @@ def build_host(force: bool = False, verbose: bool = False) -> str:
                 if verbose:
                     print("compiled", o)
     if srcs and (jobs or not os.path.exists(out) or os.path.getmtime(out) < _newest(objs)):
-        _compile_one([cxx, "-shared", "-pthread", "-o", out] + objs + ["-lrt", "-ldl"], out)
+        _compile_one([cxx, "-shared", "-pthread", "-o", out + ".tmp"] + objs + ["-lrt", "-ldl"], out)
+        os.replace(out + ".tmp", out)
     return out
 
 

@@ -90,7 +90,7 @@ class Ops:
         return _w(Fn.matmul(ta, tb))
 
     @staticmethod
-    def bmm(a, b): return _w(torch.bmm(_unwrap(a), _unwrap(b)))
+    def bmm(a, b): return _w(Fn.bmm(_unwrap(a), _unwrap(b)))
 
     @staticmethod
     def scaled_matmul(a, b, a_scale: float, b_scale: float, bias=None, out_dtype: DataType = DataType.FP32):

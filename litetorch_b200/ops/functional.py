@@ -68,11 +68,85 @@ def _gemm_ok(x, w):
     return x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x.numel() > 0
 
 
+def _tc_other(*ts) -> bool:
+    """fp16 tensors, or fp32 tensors while TF32 is enabled (`lt.cuda.set_tf32_enabled`, on by default as in the
+    reference), on a CUDA device: they run on the same tcgen05 GEMM as bf16 (`kernels.gemm_any`)."""
+    from .. import cuda as _cuda
+    dt = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype not in (torch.float16, torch.float32) or (dt is not None and t.dtype != dt):
+            return False
+        dt = t.dtype
+    return dt == torch.float16 or (dt == torch.float32 and _cuda.is_tf32_enabled())
+
+
+class _LinearAny(torch.autograd.Function):
+    """y = x @ w^T (+ b) for fp16 / fp32 (tf32) CUDA tensors on the tcgen05 GEMM; same three GEMMs as `_Linear`."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = _2d(x).contiguous()
+        wc = w.contiguous()
+        y = K.gemm_any(x2, wc)
+        if b is not None:
+            y = y + b
+        ctx.save_for_backward(x2, wc)
+        ctx.has_bias = b is not None
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _2d(dy).contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm_any(dy2, w, b_major=1).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = K.gemm_any(dy2, x2, a_major=1, b_major=1)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+class _MatmulAny(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        a, b = a.contiguous(), b.contiguous()
+        ctx.save_for_backward(a, b)
+        return K.gemm_any(a, b, b_major=1)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b = ctx.saved_tensors
+        dc = dc.contiguous()
+        da = K.gemm_any(dc, b) if ctx.needs_input_grad[0] else None
+        db = K.gemm_any(a, dc, a_major=1, b_major=1) if ctx.needs_input_grad[1] else None
+        return da, db
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """[B, M, K] @ [B, K, N] on the tcgen05 GEMM, one launch per batch entry (CUDA bf16 / fp16 / tf32 with dimensions
+    that are multiples of 8); `torch.bmm` elsewhere.  Reference: cublasSgemmStridedBatched
+    (src/backend/gpu_native/math/gemm.cu:49-73)."""
+    ok = (a.dim() == 3 and b.dim() == 3 and a.shape[0] == b.shape[0] and a.shape[0] <= 64 and a.shape[-1] % 8 == 0
+          and b.shape[-1] % 8 == 0 and a.shape[1] % 8 == 0 and a.numel() > 0 and b.numel() > 0)
+    if ok and (_native(a, b) or _tc_other(a, b)):
+        fn = _MatmulNN if a.dtype == torch.bfloat16 else _MatmulAny
+        return torch.stack([fn.apply(a[i], b[i]) for i in range(a.shape[0])], 0)
+    return torch.bmm(a, b)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
     """y = act(x @ w^T + b), w: [out, in]."""
     code = {"none": 0, "gelu": 1}[act]
     if _native(x, w, b) and _gemm_ok(x, w):
         return _Linear.apply(x, w, b, code)
+    if _tc_other(x, w, b) and _gemm_ok(x, w) and w.shape[1] % 8 == 0:
+        y = _LinearAny.apply(x, w, b)
+        return F.gelu(y, approximate="tanh") if code == 1 else y
     y = F.linear(x, w, b)
     return F.gelu(y, approximate="tanh") if code == 1 else y
 
@@ -135,6 +209,10 @@ def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     if (_native(a, b) and b.dim() == 2 and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and a.numel() > 0 and
             b.numel() > 0):
         out = _MatmulNN.apply(_2d(a), b)
+        return out.view(*a.shape[:-1], b.shape[-1])
+    if (_tc_other(a, b) and b.dim() == 2 and a.dim() >= 2 and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and a.numel() > 0
+            and b.numel() > 0 and _2d(a).shape[0] % 8 == 0):
+        out = _MatmulAny.apply(_2d(a), b)
         return out.view(*a.shape[:-1], b.shape[-1])
     return torch.matmul(a, b)
 

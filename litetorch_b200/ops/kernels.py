@@ -20,6 +20,7 @@ _SIGS = {
     "lt_sm_count": [],
     "lt_set_wait_budget_cycles": [_ll, _ll],
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
+    "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
     "lt_gemm_set_tail_split": [_i],
     "lt_gemm_set_pair_mode": [_i],
     "lt_flash_bwd_set_trace": [_vp],
@@ -197,6 +198,37 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
                              float(alpha), block_n, max_ctas, _stream())
     _check(rc, "lt_gemm_bf16")
     return out
+
+
+def gemm_any(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0, out_dtype=None) -> torch.Tensor:
+    """The tcgen05 GEMM for bf16, fp16 and fp32 operands (layouts as in `gemm`).  fp16 runs as kind::f16 with an fp32
+    result that is rounded to fp16 afterwards; fp32 runs on the tensor cores as tf32 (both operands are brought to the
+    K-major layout first) and returns fp32."""
+    dt = a.dtype
+    assert b.dtype == dt and a.dim() == 2 and b.dim() == 2
+    if dt == torch.bfloat16:
+        return gemm(a, b, a_major=a_major, b_major=b_major, out_dtype=out_dtype or torch.bfloat16)
+    if dt == torch.float32:
+        if a_major == 1:
+            a, a_major = a.t().contiguous(), 0
+        if b_major == 1:
+            b, b_major = b.t().contiguous(), 0
+        kind = 2
+    elif dt == torch.float16:
+        kind = 1
+    else:
+        raise TypeError("gemm_any: %s" % dt)
+    a = a if a.stride(1) == 1 else a.contiguous()
+    b = b if b.stride(1) == 1 else b.contiguous()
+    M, Kd = a.shape if a_major == 0 else (a.shape[1], a.shape[0])
+    N = b.shape[0] if b_major == 0 else b.shape[1]
+    assert (b.shape[1] if b_major == 0 else b.shape[0]) == Kd, "inner dimensions differ"
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    rc = _fn("lt_gemm_typed")(kind, a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, Kd, a.stride(0), b.stride(0), out.stride(0),
+                              a_major, b_major, 1, None, None, 0, 0, 0, 1.0, _stream())
+    _check(rc, "lt_gemm_typed")
+    want = out_dtype or dt
+    return out if want == torch.float32 else out.to(want)
 
 
 def gemm_set_tail_split(enable: bool):

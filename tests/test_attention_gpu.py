@@ -77,3 +77,64 @@ def test_flash_strided_qkv_buffer():
     o_ref, _ = _ref(q, k, v, True, D ** -0.5)
     assert _err(o, o_ref) < 1e-2
     K.check_status()
+
+
+def _ref_rows(q, k, v, do, rows, scale):
+    """fp32 causal attention forward restricted to the query rows `rows` of one (batch, head): (o, lse) there, plus the
+    contribution of those rows to dK / dV and their dQ (enough to check a long sequence without a T x T matrix)."""
+    qf, kf, vf, dof = q.float(), k.float(), v.float(), do.float()          # [T, D] each; qf / dof indexed by rows
+    s = qf[rows] @ kf.t() * scale
+    j = torch.arange(kf.shape[0], device=q.device)[None, :]
+    s = s.masked_fill(j > rows[:, None], float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - lse[:, None])
+    o = p @ vf
+    dp = dof[rows] @ vf.t()
+    delta = (dof[rows] * o).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    return o, lse, ds @ kf
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,D", [(4, 2048, 32, 4, 64), (1, 8192, 32, 8, 128)])
+def test_flash_at_the_benchmark_shapes(B, T, Hq, Hkv, D):
+    """The shapes the training benchmarks run (1.1B: batch 4 x 2048, 32 q / 4 kv heads of 64; 8B: 8192 tokens, 32 q /
+    8 kv heads of 128) against fp32 on a subsample of query rows, and dK / dV / dQ against an fp32 reference on one
+    (batch, kv head) group."""
+    from litetorch_b200.ops import kernels as K
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(B, T, Hq, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(B, T, Hkv, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, T, Hkv, D, device="cuda", generator=g).bfloat16()
+    do = torch.randn(B, T, Hq, D, device="cuda", generator=g).bfloat16()
+    scale = D ** -0.5
+    o, lse = K.flash_fwd(q, k, v, causal=True, scale=scale)
+    dq, dk, dv = K.flash_bwd(q, k, v, o, lse, do, causal=True, scale=scale)
+    torch.cuda.synchronize()
+    K.check_status()
+    rows = torch.cat([torch.arange(0, 130, device="cuda"), torch.randint(0, T, (254,), device="cuda", generator=g),
+                      torch.arange(T - 128, T, device="cuda")])
+    G = Hq // Hkv
+    for b, h in ((0, 0), (B - 1, Hq - 1), (B // 2, Hq // 2 + 1)):
+        o_r, lse_r, dq_r = _ref_rows(q[b, :, h], k[b, :, h // G], v[b, :, h // G], do[b, :, h], rows, scale)
+        assert _err(o[b, rows, h], o_r) < 1e-2
+        assert (lse[b, h, rows] - lse_r).abs().max().item() < 2e-2
+        assert _err(dq[b, rows, h], dq_r) < 2e-2
+    # dK / dV of one kv head: sum over its G query heads, all rows, in fp32 but one head at a time (T x T fits for one head)
+    b, hk = B - 1, Hkv - 1
+    dk_r = torch.zeros(T, D, device="cuda")
+    dv_r = torch.zeros(T, D, device="cuda")
+    kf, vf = k[b, :, hk].float(), v[b, :, hk].float()
+    all_rows = torch.arange(T, device="cuda")
+    for h in range(hk * G, (hk + 1) * G):
+        qf, dof = q[b, :, h].float(), do[b, :, h].float()
+        for r0 in range(0, T, 2048):                       # query rows in slabs to bound the score matrix
+            rr = all_rows[r0:r0 + 2048]
+            s = (qf[rr] @ kf.t() * scale).masked_fill(all_rows[None, :] > rr[:, None], float("-inf"))
+            p = torch.softmax(s, -1)
+            o_s = p @ vf
+            dp = dof[rr] @ vf.t()
+            ds = p * (dp - (dof[rr] * o_s).sum(-1, keepdim=True)) * scale
+            dv_r += p.t() @ dof[rr]
+            dk_r += ds.t() @ qf[rr]
+    assert _err(dv[b, :, hk], dv_r) < 2e-2
+    assert _err(dk[b, :, hk], dk_r) < 2e-2

@@ -127,3 +127,52 @@ def test_gemm_cta_pairs(a_major, b_major, M, N, K):
     ref = _ref(a, b, a_major, b_major)
     assert _rel_err(out2, ref) < 1e-2
     assert _rel_err(out, ref + bias.float() + res.float()) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1000, 264, 136), (8, 8, 8)])
+def test_gemm_fp16_and_tf32_all_layouts(dtype, M, N, K):
+    """fp16 (kind::f16) and fp32-as-tf32 (kind::tf32) operands through the same tcgen05 kernels, three operand layouts,
+    against fp64 PyTorch; tf32 keeps 10 mantissa bits, so its bound is looser."""
+    from litetorch_b200.ops import kernels as K
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    b = torch.randn(N, K, device="cuda", generator=g).to(dtype)
+    tol = 2e-3 if dtype == torch.float16 else 2e-3
+    ref = (a.double() @ b.double().t())
+    def err(x, r):
+        return float((x.double() - r).norm() / r.norm())
+    assert err(K.gemm_any(a, b), ref) < tol                                                     # x @ W^T
+    assert err(K.gemm_any(a, b.t().contiguous(), b_major=1), ref) < tol                         # A @ B
+    assert err(K.gemm_any(a.t().contiguous(), b.t().contiguous(), a_major=1, b_major=1), ref) < tol   # A^T @ B
+    K.check_status()
+
+
+def test_linear_matmul_bmm_ops_reach_the_tensor_cores_for_fp32_and_fp16():
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor, _unwrap
+    from litetorch_b200.ops import kernels as K
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        x = torch.randn(4, 64, 128, device="cuda", generator=g).to(dtype).requires_grad_(True)
+        w = (torch.randn(96, 128, device="cuda", generator=g) * 0.1).to(dtype).requires_grad_(True)
+        n0 = K.launch_count()
+        y = _unwrap(lt.Ops.bmm(Tensor(x), Tensor(w.t().contiguous().expand(4, 128, 96).contiguous())))
+        assert K.launch_count() > n0                          # our GEMM ran (not a library fallback)
+        ref = x.detach().double() @ w.detach().double().t()
+        assert float((y.double() - ref).norm() / ref.norm()) < 1e-2
+        lin = lt.nn.Linear(128, 96)
+        lin.to(lt.Device("cuda")) if hasattr(lt, "Device") else None
+    # autograd through the fp32 (tf32) linear
+    from litetorch_b200.ops import functional as Fn
+    x = torch.randn(256, 128, device="cuda", generator=g, requires_grad=True)
+    w = (torch.randn(96, 128, device="cuda", generator=g) * 0.1).requires_grad_(True)
+    b = torch.randn(96, device="cuda", generator=g, requires_grad=True)
+    n0 = K.launch_count()
+    y = Fn.linear(x, w, b)
+    y.square().sum().backward()
+    assert K.launch_count() >= n0 + 3
+    xr, wr, br = (t.detach().double().requires_grad_(True) for t in (x, w, b))
+    (torch.nn.functional.linear(xr, wr, br)).square().sum().backward()
+    for got, want in ((x.grad, xr.grad), (w.grad, wr.grad), (b.grad, br.grad)):
+        assert float((got.double() - want).norm() / want.norm()) < 5e-3
