@@ -13,7 +13,7 @@ __version__ = "0.1.0"
 from .core import (DataType, Device, DeviceType, NoGradGuard, Tensor, auto_device, checkpoint, get_backend_name,
                    is_gpu_available, is_tpu_available, manual_seed)
 from .ops import Ops
-from . import amp, config, cuda, custom_ops, data, jit, nn, optim, quantization
+from . import amp, config, cuda, custom_ops, data, jit, memory, nn, optim, quantization
 from . import parallel as distributed
 from .serialization import (load, load_optimizer_state, load_parameters, save, save_optimizer_state, save_parameters)
 

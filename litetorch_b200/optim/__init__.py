@@ -220,10 +220,10 @@ class _AdamBase(Optimizer):
                                     1 if self.decoupled else 0, None, torch.cuda.current_stream().cuda_stream)
         K._check(rc, "lt_adam_table")
 
-    def _step_torch(self, ts):
+    def _step_torch(self, ts, offset: int = 0):
         bc1 = 1.0 - self.beta1 ** self.step_count
         bc2 = 1.0 - self.beta2 ** self.step_count
-        for i, p in enumerate(ts):
+        for i, p in enumerate(ts, start=offset):
             if p.grad is None:
                 continue
             self._ensure_state(i, p)
@@ -265,9 +265,41 @@ class AdamW(_AdamBase):
     """Decoupled weight decay, bias-corrected.  `offload_to_cpu` keeps m, v (and masters) in host memory."""
     decoupled = True
 
-    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, offload_to_cpu=False):
+    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, offload_to_cpu=False,
+                 state_limit_bytes: int = 0):
+        """state_limit_bytes > 0: the moments live under an `lt.memory.ResidencyManager` with that device-memory limit -
+        at most that many bytes of m / v are on the device at a time, the least recently used tensors wait in pinned
+        host memory and are swapped in for their parameter's update (the reference's storage eviction,
+        src/memory_manager/memory_manager.cpp:54-107, applied to optimizer state)."""
         super().__init__(params, lr, beta1, beta2, eps, weight_decay)
         self.offload_to_cpu = offload_to_cpu
+        self._mm = None
+        self._handles = {}
+        if state_limit_bytes > 0:
+            from ..memory import ResidencyManager
+            dev = next((t.device for t in self._tensors()), torch.device("cpu"))
+            self._mm = ResidencyManager(state_limit_bytes, dev)
+
+    @torch.no_grad()
+    def step(self):
+        if self._mm is None:
+            return super().step()
+        self.step_count += 1
+        ts = self._tensors()
+        self._refresh_masters(ts)
+        for i, p in enumerate(ts):
+            if p.grad is None:
+                continue
+            if i not in self._handles:
+                self._ensure_state(i, p)
+                self._handles[i] = (self._mm.register(self.m[i]), self._mm.register(self.v[i]))
+                self.m[i] = self.v[i] = None          # the manager's handles are now the only owners
+            hm, hv = self._handles[i]
+            with self._mm.use(hm) as m, self._mm.use(hv) as v:
+                self.m[i], self.v[i] = m, v
+                self._step_torch([p], offset=i)
+                self.m[i] = self.v[i] = None
+        self._mark_versions(ts)
 
     def _state_device(self, p):
         return torch.device("cpu") if self.offload_to_cpu else p.device

@@ -414,3 +414,38 @@ def test_store_edge_cases_of_rendezvous_and_failure_detection():
     a.send(b"x")
     assert b.recv(1) == b"x"                       # the unrelated socket pair was not shut down by the stop path
     a.close(); b.close(); mute.close()
+
+
+def test_residency_manager_evicts_to_host_and_swaps_back_in_under_a_2mb_limit():
+    """Sixteen 512 KB tensors under a 2 MB limit (the reference's stress test uses the same limit,
+    tests/stress_test.cpp:36-70): at most four are resident, the others wait on the host and come back intact in LRU
+    order; a tensor in use is never the victim; AdamW with its moments under a limit takes the same steps as without."""
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor, _unwrap
+    mm = lt.memory.ResidencyManager(2 << 20, device="cpu")
+    hs = [mm.register(torch.full((128 * 1024,), float(i))) for i in range(16)]
+    assert mm.resident_bytes <= 2 << 20 and sum(h.resident for h in hs) == 4 and mm.evictions == 12
+    assert [h.resident for h in hs[-4:]] == [True] * 4
+    for i, h in enumerate(hs):                      # every tensor comes back with its contents
+        assert float(mm.fetch(h)[777]) == float(i)
+        assert mm.resident_bytes <= 2 << 20
+    assert mm.swap_ins == 12 + 4 - 4 or mm.swap_ins >= 12
+    with mm.use(hs[0]) as t0:                       # pinned: stays while four others are brought in
+        for h in hs[1:6]:
+            mm.fetch(h)
+        assert hs[0].resident and t0 is hs[0].tensor
+    mm.release(hs[3])
+    # AdamW: moments of 6 x 256 KB parameters under a 1 MB limit follow the unlimited optimizer exactly
+    def run(limit):
+        g = torch.Generator().manual_seed(0)
+        ps = [Tensor(torch.randn(64 * 1024, generator=g).requires_grad_(True)) for _ in range(6)]
+        opt = lt.optim.AdamW(ps, lr=1e-2, weight_decay=0.1, state_limit_bytes=limit)
+        for step in range(3):
+            for k, p in enumerate(ps):
+                _unwrap(p).grad = torch.full((64 * 1024,), 0.1 * (k + 1) * (step + 1))
+            opt.step()
+        return [_unwrap(p).detach().clone() for p in ps], opt
+    free, _ = run(0)
+    lim, opt = run(1 << 20)
+    assert all(torch.equal(a, b) for a, b in zip(free, lim))
+    assert opt._mm.evictions > 0 and opt._mm.resident_bytes <= 1 << 20
