@@ -1,6 +1,7 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
+                                                 rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
 handful of times and exits, so a capture with `-k regex:<kernel> -c 3` ends by itself in a minute or two.
@@ -66,6 +67,28 @@ def main():
         logits = torch.randn(8192, 32000, device=dev).bfloat16()
         tgt = torch.randint(0, 32000, (8192,), device=dev)
         fn = lambda: K.ce_finish(logits, tgt, K.ce_stats(logits, tgt))
+    elif case in ("flash_fwd_d128", "flash_bwd_d128"):      # the 8B shape: one sequence of 8192, 32 q / 8 kv heads of 128
+        B, T, Hq, Hkv, D = 1, 8192, 32, 8, 128
+        q = torch.randn(B, T, Hq, D, device=dev).bfloat16()
+        k = torch.randn(B, T, Hkv, D, device=dev).bfloat16()
+        v = torch.randn(B, T, Hkv, D, device=dev).bfloat16()
+        do = torch.randn(B, T, Hq, D, device=dev).bfloat16()
+        o, lse = K.flash_fwd(q, k, v, causal=True)
+        fn = (lambda: K.flash_fwd(q, k, v, causal=True)) if case == "flash_fwd_d128" else (lambda: K.flash_bwd(q, k, v, o, lse, do, causal=True))
+    elif case == "paged_decode":     # batch 32, 16 k context, 32 q / 4 kv heads of 64: 1 GB of K / V per launch
+        S, H, Hkv, D, bs, ctx = 32, 32, 4, 64, 16, 16384
+        nb = S * ctx // bs
+        kc = torch.randn(nb, Hkv, bs, D, device=dev).bfloat16()
+        vc = torch.randn(nb, Hkv, bs, D, device=dev).bfloat16()
+        q = torch.randn(S, H, D, device=dev).bfloat16()
+        bt = torch.arange(nb, device=dev, dtype=torch.int32).view(S, ctx // bs)
+        cl = torch.full((S,), ctx, device=dev, dtype=torch.int32)
+        fn = lambda: K.paged_decode(q, kc, vc, bt, cl, bs, 8, D ** -0.5)
+    elif case == "shard_gather":     # 512 MB pulled from four "ranks" (local buffers stand in for peers)
+        n = 1 << 26
+        shards = [torch.randn(n, device=dev).bfloat16() for _ in range(4)]
+        dst = torch.empty(4 * n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gather_shards([s.data_ptr() for s in shards], [(0, n)], [dst], max_ctas=64)
     elif case == "gemm_rs":
         # GEMM -> reduce-scatter on a one-rank group: the scatter epilogue and the reduce phase without NVLink
         import os
