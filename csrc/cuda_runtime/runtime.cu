@@ -213,6 +213,46 @@ void lt_cuda_alloc_stats(uint64_t* out5) {
   out5[0] = g_alloc.cached; out5[1] = g_alloc.allocated; out5[2] = g_alloc.peak; out5[3] = g_alloc.hits; out5[4] = g_alloc.misses;
 }
 
+// ------------------------------------------------------------------ peer memory through CUDA IPC
+// A rank exports a device allocation as a 64-byte handle plus the offset of `ptr` inside the allocation that holds it
+// (PyTorch sub-allocates its segments); the other processes of the node open the handle and get an address in their
+// own address space through which their kernels load from and store to that memory over NVLink.  This is the symmetric
+// heap of the fused communication kernels without any framework in between; the handles travel through the process
+// group's host-side store.  The reference shares host memory the same way with shm_open (src/distributed/shm_ipc.cpp:71-143).
+int lt_ipc_export(void* ptr, void* handle_out, unsigned long long* offset_out) {
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range = nullptr;
+  if (!range) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return -1;
+    range = reinterpret_cast<RangeFn>(fn);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) return -2;
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) { cudaGetLastError(); return int(e); }
+  memcpy(handle_out, &h, sizeof(h));
+  *offset_out = static_cast<unsigned long long>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return 0;
+}
+// Returns the peer's `ptr` as an address of this process (base of the mapping + offset), or nullptr (*err = cudaError_t).
+// *base_out receives the mapping's base, to be passed to lt_ipc_close.
+void* lt_ipc_open(const void* handle, unsigned long long offset, void** base_out, int* err) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* base = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { cudaGetLastError(); if (err) *err = int(e); return nullptr; }
+  if (base_out) *base_out = base;
+  if (err) *err = 0;
+  return static_cast<char*>(base) + offset;
+}
+int lt_ipc_close(void* base) { return int(cudaIpcCloseMemHandle(base)); }
+
 // ------------------------------------------------------------------ CUDA graphs
 int lt_graph_begin_capture(void* stream) {
   return int(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));

@@ -44,8 +44,22 @@ _CANARY_VALUE = 0x5A
 _live_buffers = []           # weak references, for check_symmetric_canaries()
 
 
+def _symm_backend() -> str:
+    return os.environ.get("LT_SYMM_BACKEND", "torch")
+
+
+# CUDA allows an IPC handle to be opened once per process: several buffers that PyTorch placed in one device segment
+# share a handle, so mappings are kept here by handle and stay open until the process exits.
+_ipc_mappings: Dict[bytes, int] = {}
+
+
 class SymmetricBuffer:
     """A tensor allocated at the same offset on every rank, with every rank's device pointer to it.
+
+    Two back-ends give the peer pointers: `torch.distributed._symmetric_memory` (default; also offers a multicast
+    address) and the native CUDA-IPC path (`LT_SYMM_BACKEND=ipc`: an ordinary device allocation exported with
+    `lt_ipc_export`, the handles exchanged through the process group's host-side store, opened on every peer with
+    `lt_ipc_open`; no framework-private API involved).
 
     The allocation carries a 256-byte guard area on both sides filled with a fixed byte; peers write into these buffers
     from inside kernels, and `check()` (or `check_symmetric_canaries()` over all live buffers) tells whether anything
@@ -57,21 +71,59 @@ class SymmetricBuffer:
         group = group or dist.group.WORLD
         itemsize = torch.empty((), dtype=dtype).element_size()
         guard = _CANARY_BYTES // itemsize
-        self._raw = symm_mem.empty(numel + 2 * guard, dtype=dtype, device=device)
+        ipc = _symm_backend() == "ipc"
+        if ipc:
+            self._raw = torch.empty(numel + 2 * guard, dtype=dtype, device=device)
+        else:
+            self._raw = symm_mem.empty(numel + 2 * guard, dtype=dtype, device=device)
         self._raw.zero_()
         self._guards = (self._raw[:guard].view(torch.uint8), self._raw[guard + numel:].view(torch.uint8))
         for g in self._guards:
             g.fill_(_CANARY_VALUE)
         self.tensor = self._raw[guard:guard + numel]
-        self.handle = symm_mem.rendezvous(self._raw, group=group.group_name if hasattr(group, "group_name") else group)
-        self.ptrs = [int(p) + _CANARY_BYTES for p in self.handle.buffer_ptrs]
-        try:
-            self.mc_ptr = (int(self.handle.multicast_ptr) + _CANARY_BYTES
-                           if self.handle.has_multicast_support(device.type, device.index) else 0)
-        except Exception:
+        if ipc:
+            self.ptrs = [p + _CANARY_BYTES for p in self._ipc_rendezvous(group)]
             self.mc_ptr = 0
+        else:
+            self.handle = symm_mem.rendezvous(self._raw, group=group.group_name if hasattr(group, "group_name") else group)
+            self.ptrs = [int(p) + _CANARY_BYTES for p in self.handle.buffer_ptrs]
+            try:
+                self.mc_ptr = (int(self.handle.multicast_ptr) + _CANARY_BYTES
+                               if self.handle.has_multicast_support(device.type, device.index) else 0)
+            except Exception:
+                self.mc_ptr = 0
         self.itemsize = self.tensor.element_size()
         _live_buffers.append(weakref.ref(self))
+
+    def _ipc_rendezvous(self, group) -> List[int]:
+        """Export this rank's allocation, exchange (handle, offset) over the group's store, open every peer's."""
+        import ctypes
+        from .._native import cuda_lib
+        lib = cuda_lib()
+        lib.lt_ipc_open.restype = ctypes.c_void_p
+        torch.cuda.synchronize()
+        handle = (ctypes.c_char * 64)()
+        off = ctypes.c_ulonglong(0)
+        rc = lib.lt_ipc_export(ctypes.c_void_p(self._raw.data_ptr()), handle, ctypes.byref(off))
+        if rc != 0:
+            raise RuntimeError("lt_ipc_export failed with code %d" % rc)
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        infos = [None] * world
+        dist.all_gather_object(infos, (bytes(handle.raw), int(off.value)), group=group)
+        ptrs = []
+        for r, (h, o) in enumerate(infos):
+            if r == rank:
+                ptrs.append(self._raw.data_ptr())
+                continue
+            if h not in _ipc_mappings:
+                base, err = ctypes.c_void_p(0), ctypes.c_int(0)
+                p = lib.lt_ipc_open(h, ctypes.c_ulonglong(0), ctypes.byref(base), ctypes.byref(err))
+                if not p:
+                    raise RuntimeError("lt_ipc_open of rank %d's buffer failed with cudaError %d" % (r, err.value))
+                _ipc_mappings[h] = int(base.value)
+            ptrs.append(_ipc_mappings[h] + o)
+        dist.barrier(group=group)
+        return ptrs
 
     def peer_ptrs(self, elem_offset: int = 0) -> List[int]:
         return [p + elem_offset * self.itemsize for p in self.ptrs]
