@@ -85,6 +85,155 @@ __global__ void paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const v
   if (lane == 0) { out[D] = m; out[D + 1] = l; }
 }
 
+
+// ---------------------------------------------------------------------------------------------- grouped-query decode
+// One CTA of four warps owns one (sequence, KV head, split): every K / V byte of its key range is read once for the
+// whole group of G = Hq / Hkv query heads (the warp-per-query-head kernel above reads it G times and walks the keys
+// one at a time).  A warp takes 32 keys at a time:
+//   scores   lane = key: the lane reads its key row with 16-byte loads (the 32 rows of a chunk are contiguous in a
+//            cache block) and forms the dot products with the G query vectors, which sit in shared memory pre-scaled
+//            (all lanes read the same address: a broadcast);
+//   softmax  per head, one max and one sum reduction per 32 keys; running (max, sum) kept per warp;
+//   P V      lane = pair (D 64) or quad (D 128) of output columns: the probabilities of the chunk go through shared
+//            memory, then for each key the warp reads the V row as one coalesced line and every lane updates its G x E
+//            accumulators.
+// The warps' partial results are merged in shared memory and written in the (normalised output, max, sum) form that
+// the merge kernel above already combines across splits.  bf16 caches only (e4m3 stays on the kernel above).
+constexpr int kPdWarps = 4;
+constexpr int kPdMaxG = 8;
+
+template <int D>
+__global__ void __launch_bounds__(kPdWarps * 32)
+paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables,
+                        const int* __restrict__ context_lens, float* __restrict__ part, int S, int Hq, int Hkv, int block_size,
+                        int max_blocks, int splits, float scale) {
+  constexpr int E = D / 32;
+  const int G = Hq / Hkv;
+  const int sp = blockIdx.x % splits;
+  const int hkv = (blockIdx.x / splits) % Hkv;
+  const int s = blockIdx.x / (splits * Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float q_s[kPdMaxG][D];
+  __shared__ float p_s[kPdWarps][32][kPdMaxG];            // [warp][key of the chunk][head]
+  __shared__ float red_m[kPdWarps][kPdMaxG], red_l[kPdWarps][kPdMaxG];
+  __shared__ float red_o[kPdWarps][kPdMaxG][D];
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i % D;
+    q_s[g][d] = __bfloat162float(q[((long long)s * Hq + hkv * G + g) * D + d]) * scale;
+  }
+  __syncthreads();
+  const int ctx = context_lens[s];
+  const int per = ((ctx + splits - 1) / splits + 31) / 32 * 32;      // whole 32-key chunks per split
+  const int t0 = sp * per, t1 = min(ctx, t0 + per);
+  float m[kPdMaxG], l[kPdMaxG], acc[kPdMaxG][E];
+#pragma unroll
+  for (int g = 0; g < kPdMaxG; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+  }
+  const int* bt = block_tables + (long long)s * max_blocks;
+  for (int c0 = t0 + warp * 32; c0 < t1; c0 += kPdWarps * 32) {
+    // ---- scores of this lane's key for every head of the group
+    const int t = c0 + lane;
+    const bool live = t < t1;
+    float sc[kPdMaxG];
+#pragma unroll
+    for (int g = 0; g < kPdMaxG; ++g) sc[g] = 0.f;
+    if (live) {
+      const int blk = bt[t / block_size];
+      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + (((long long)blk * Hkv + hkv) * block_size + (t % block_size)) * D);
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        const uint4 u = kr[j];
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+#pragma unroll
+        for (int g = 0; g < kPdMaxG; ++g) {
+          if (g < G) {
+            const float4 q0 = *reinterpret_cast<const float4*>(&q_s[g][j * 8]);
+            const float4 q1 = *reinterpret_cast<const float4*>(&q_s[g][j * 8 + 4]);
+            sc[g] += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + c.x * q1.x + c.y * q1.y + d.x * q1.z + d.y * q1.w;
+          }
+        }
+      }
+    }
+    // ---- online softmax per head over the 32 keys of the chunk
+#pragma unroll
+    for (int g = 0; g < kPdMaxG; ++g) {
+      if (g < G) {
+        float mx = live ? sc[g] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float nm = fmaxf(m[g], mx);
+        const float a = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - nm);
+        const float pv = live ? __expf(sc[g] - nm) : 0.f;
+        float ps = pv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l[g] = l[g] * a + ps;
+        m[g] = nm;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[g][e] *= a;
+        p_s[warp][lane][g] = pv;
+      }
+    }
+    __syncwarp();
+    // ---- P V: lane = E output columns; one coalesced V row per key
+    const int nk = min(32, t1 - c0);
+    for (int kk = 0; kk < nk; ++kk) {
+      const int tk = c0 + kk;
+      const int blk = bt[tk / block_size];
+      const __nv_bfloat16* vr = v_cache + (((long long)blk * Hkv + hkv) * block_size + (tk % block_size)) * D + lane * E;
+      float vv[E];
+      if (E == 2) {
+        const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vr));
+        vv[0] = f.x; vv[1] = f.y;
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(vr);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
+        vv[0] = f0.x; vv[1] = f0.y; vv[E - 2] = f1.x; vv[E - 1] = f1.y;
+      }
+      const float4 p0 = *reinterpret_cast<const float4*>(&p_s[warp][kk][0]);
+      const float4 p1 = *reinterpret_cast<const float4*>(&p_s[warp][kk][4]);
+      const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+      for (int g = 0; g < kPdMaxG; ++g)
+        if (g < G) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[e];
+        }
+    }
+    __syncwarp();
+  }
+  // ---- merge the four warps, write this split's partial result
+#pragma unroll
+  for (int g = 0; g < kPdMaxG; ++g)
+    if (g < G) {
+      if (lane == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
+#pragma unroll
+      for (int e = 0; e < E; ++e) red_o[warp][g][lane * E + e] = acc[g][e];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i % D;
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) gm = fmaxf(gm, red_m[w][g]);
+    float lsum = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) {
+      if (red_m[w][g] == -INFINITY) continue;
+      const float a = __expf(red_m[w][g] - gm);
+      lsum += red_l[w][g] * a;
+      o += red_o[w][g][d] * a;
+    }
+    float* out = part + (((long long)s * Hq + hkv * G + g) * splits + sp) * (D + 2);
+    out[d] = lsum > 0.f ? o / lsum : 0.f;
+    if (d == 0) { out[D] = gm; out[D + 1] = lsum; }
+  }
+}
+
 template <int D>
 __global__ void paged_decode_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ o, int rows, int splits) {
   const int row = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
@@ -154,7 +303,15 @@ int lt_paged_decode(const void* q, const void* k_cache, const void* v_cache, con
 #define LT_PD(DD, F8) \
   paged_decode_kernel<DD, F8><<<blocks, threads, 0, st>>>(Q, k_cache, v_cache, block_tables, context_lens, part, S, Hq, Hkv, \
                                                           block_size, max_blocks, splits, scale, k_scale, v_scale)
-  if (D == 64) { if (kv_fp8) LT_PD(64, true); else LT_PD(64, false); }
+  const int G = Hq / Hkv;
+  if (!kv_fp8 && G <= kPdMaxG && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0) {
+    // bf16 caches: every K / V byte is read once for the whole group of query heads
+    const int ctas = S * Hkv * splits;
+    auto KC = static_cast<const __nv_bfloat16*>(k_cache);
+    auto VC = static_cast<const __nv_bfloat16*>(v_cache);
+    if (D == 64) paged_decode_gqa_kernel<64><<<ctas, kPdWarps * 32, 0, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale);
+    else paged_decode_gqa_kernel<128><<<ctas, kPdWarps * 32, 0, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale);
+  } else if (D == 64) { if (kv_fp8) LT_PD(64, true); else LT_PD(64, false); }
   else { if (kv_fp8) LT_PD(128, true); else LT_PD(128, false); }
 #undef LT_PD
   LT_LAUNCH_CHECK();

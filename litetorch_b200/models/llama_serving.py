@@ -20,12 +20,15 @@ from .llama import LlamaEngine
 
 
 class LlamaKVModel:
-    def __init__(self, engine: LlamaEngine, num_blocks: int, block_size: int = 16, kv_dtype=torch.bfloat16, num_splits: int = 0):
+    def __init__(self, engine: LlamaEngine, num_blocks: int, block_size: int = 16, kv_dtype=torch.bfloat16, num_splits: int = 0,
+                 graphs: bool = True):
         assert engine.w.tp == 1 and hasattr(engine.w, "flat_p"), "serving runs on whole (unsharded) weights"
         self.e = engine
         cfg = engine.cfg
         self.block_size = block_size
         self.num_splits = num_splits
+        self.graphs = graphs                 # record the decode step per (batch size, table width) and replay it
+        self._graphs = {}
         self.cache = PagedKVCache(cfg.n_layers, num_blocks, block_size, cfg.n_kv_heads, cfg.head_dim, device=engine.device,
                                   dtype=kv_dtype)
         self.kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * self.cache.k[0].element_size()
@@ -102,16 +105,40 @@ class LlamaKVModel:
         return int(self._next_tokens(x[-1:]).item())
 
     # ------------------------------------------------------------------ one token for every running sequence
+    def _decode_body(self, d: torch.Tensor, S: int, width: int) -> torch.Tensor:
+        """The device work of one decode step on the packed int64 input block `d` [4 + width, S]: rows 0-3 are token,
+        position, cache slot and context length of every sequence, the rest its block table (transposed)."""
+        from ..serving import paged_attention
+        e, K = self.e, self.e.K
+        bs = self.block_size
+        tok = d[0]
+        pos, slots, ctx = d[1].to(torch.int32), d[2].to(torch.int32), d[3].to(torch.int32)
+        bt = d[4:].t().contiguous().to(torch.int32)
+        splits = self.num_splits or self._splits(S, width * bs)
+
+        def attend(i, q, k, v):
+            self.cache.append(i, k.contiguous(), v.contiguous(), slots)
+            return paged_attention(q.contiguous(), self.cache.k[i], self.cache.v[i], bt, ctx, bs, num_splits=splits,
+                                   k_scale=self.cache.k_scale, v_scale=self.cache.v_scale)
+
+        x = self._layers(K.embedding_fwd(tok, e.w.p("embed")), pos, attend)
+        return self._next_tokens(x)
+
     @torch.no_grad()
     def decode_batch(self, last_tokens: Sequence[int], positions: Sequence[int], block_tables: List[Sequence[int]]) -> List[int]:
         """last_tokens[s] sits at position positions[s] of sequence s and is not in the cache yet: append its K / V,
-        attend over positions[s] + 1 cached keys, return the greedy next token of every sequence."""
-        from ..serving import paged_attention
-        e, K = self.e, self.e.K
+        attend over positions[s] + 1 cached keys, return the greedy next token of every sequence.
+
+        On a GPU the step's ~270 launches are recorded once per (batch size, block-table width) into a CUDA graph and
+        replayed: the step then costs its kernels, not their launch overhead.  The inputs of a replay are copied
+        into the graph's static input block first."""
+        e = self.e
         dev = e.device
         S = len(last_tokens)
         bs = self.block_size
         width = max((p + bs) // bs for p in positions)
+        if self.graphs and dev.type == "cuda":
+            width = (width + 15) // 16 * 16                     # fewer distinct graphs: table widths in steps of 16 blocks
         host = torch.zeros(4 + width, S, dtype=torch.int64)
         host[0] = torch.tensor(list(last_tokens), dtype=torch.int64)
         host[1] = torch.tensor(list(positions), dtype=torch.int64)
@@ -121,20 +148,29 @@ class LlamaKVModel:
             row = block_tables[s][:width]
             host[4:4 + len(row), s] = torch.tensor(list(row), dtype=torch.int64)
         host[3] = host[1] + 1
-        d = host.to(dev, non_blocking=True)
-        tok = d[0]
-        pos, slots, ctx = d[1].to(torch.int32), d[2].to(torch.int32), d[3].to(torch.int32)
-        bt = d[4:].t().contiguous().to(torch.int32)
-
-        def attend(i, q, k, v):
-            self.cache.append(i, k.contiguous(), v.contiguous(), slots)
-            return paged_attention(q.contiguous(), self.cache.k[i], self.cache.v[i], bt, ctx, bs, num_splits=self.num_splits or self._splits(S, width * bs),
-                                   k_scale=self.cache.k_scale, v_scale=self.cache.v_scale)
-
-        x = self._layers(K.embedding_fwd(tok, e.w.p("embed")), pos, attend)
-        return self._next_tokens(x).tolist()
+        if not (self.graphs and dev.type == "cuda"):
+            return self._decode_body(host.to(dev, non_blocking=True), S, width).tolist()
+        key = (S, width)
+        entry = self._graphs.get(key)
+        if entry is None:
+            static_in = host.to(dev)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                        # eager run on the capture stream: workspaces, caches
+                self._decode_body(static_in, S, width)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                static_out = self._decode_body(static_in, S, width)
+            entry = self._graphs[key] = (g, static_in, static_out)
+            # the two recording passes appended this step's K / V already; the replay below rewrites the same slots
+        g, static_in, static_out = entry
+        static_in.copy_(host, non_blocking=True)
+        g.replay()
+        return static_out.tolist()
 
     def _splits(self, S: int, max_ctx: int) -> int:
-        """Splits of the key range per (sequence, head): enough warps to fill the GPU, at least 256 keys per split."""
-        H = self.e.cfg.n_heads
-        return max(1, min(32, max_ctx // 256, (148 * 16 + S * H - 1) // (S * H)))
+        """Splits of the key range per (sequence, KV head): about four CTAs per SM, at least 256 keys per split."""
+        ctas = S * self.e.cfg.n_kv_heads
+        return max(1, min(32, max_ctx // 256, (148 * 4 + ctas - 1) // ctas))

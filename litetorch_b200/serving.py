@@ -94,8 +94,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and k_cache.dtype in (torch.bfloat16, torch.float8_e4m3fn):
         from .ops import kernels as K
         if num_splits <= 0:
+            # about four CTAs (one per sequence, KV head and split) per SM, at least 256 keys per split
             max_ctx = int(cl.max().item()) if S else 0
-            num_splits = max(1, min(16, (max_ctx + 511) // 512, max(1, (148 * 8) // max(S * H, 1))))
+            num_splits = max(1, min(32, max_ctx // 256, (148 * 4 + S * Hkv - 1) // max(S * Hkv, 1)))
         return K.paged_decode(q.contiguous(), k_cache, v_cache, bt, cl, block_size, num_splits, scale, k_scale, v_scale)
     out = torch.zeros(S, H, D, dtype=torch.float32, device=q.device)
     G = H // Hkv
