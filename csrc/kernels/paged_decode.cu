@@ -141,9 +141,11 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float sc[kPdMaxG];
 #pragma unroll
     for (int g = 0; g < kPdMaxG; ++g) sc[g] = 0.f;
+    int my_blk = 0, my_off = 0;
     if (live) {
-      const int blk = bt[t / block_size];
-      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + (((long long)blk * Hkv + hkv) * block_size + (t % block_size)) * D);
+      my_blk = bt[t / block_size];
+      my_off = t % block_size;
+      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + (((long long)my_blk * Hkv + hkv) * block_size + my_off) * D);
 #pragma unroll
       for (int j = 0; j < D / 8; ++j) {
         const uint4 u = kr[j];
@@ -176,33 +178,52 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[g][e] *= a;
         p_s[warp][lane][g] = pv;
+      } else {
+        p_s[warp][lane][g] = 0.f;
       }
     }
     __syncwarp();
-    // ---- P V: lane = E output columns; one coalesced V row per key
+    // ---- P V: lane = E output columns; one coalesced V row per key.  U rows are requested before the first is used,
+    // so a warp keeps U x D x 2 bytes in flight instead of one row (a single row per warp left the kernel bound by
+    // memory latency at a tenth of the copy bandwidth).
+    constexpr int U = (D == 64) ? 16 : 8;
     const int nk = min(32, t1 - c0);
-    for (int kk = 0; kk < nk; ++kk) {
-      const int tk = c0 + kk;
-      const int blk = bt[tk / block_size];
-      const __nv_bfloat16* vr = v_cache + (((long long)blk * Hkv + hkv) * block_size + (tk % block_size)) * D + lane * E;
-      float vv[E];
-      if (E == 2) {
-        const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vr));
-        vv[0] = f.x; vv[1] = f.y;
-      } else {
-        const uint2 u = *reinterpret_cast<const uint2*>(vr);
-        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
-        vv[0] = f0.x; vv[1] = f0.y; vv[E - 2] = f1.x; vv[E - 1] = f1.y;
-      }
-      const float4 p0 = *reinterpret_cast<const float4*>(&p_s[warp][kk][0]);
-      const float4 p1 = *reinterpret_cast<const float4*>(&p_s[warp][kk][4]);
-      const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll 1
+    for (int kk0 = 0; kk0 < nk; kk0 += U) {
+      float vv[U][E];
 #pragma unroll
-      for (int g = 0; g < kPdMaxG; ++g)
-        if (g < G) {
+      for (int u = 0; u < U; ++u) {
+        const int kk = kk0 + u;
+        const int blk_u = __shfl_sync(0xffffffffu, my_blk, kk & 31);
+        const int off_u = __shfl_sync(0xffffffffu, my_off, kk & 31);
+        if (kk < nk) {
+          const __nv_bfloat16* vr = v_cache + (((long long)blk_u * Hkv + hkv) * block_size + off_u) * D + lane * E;
+          if (E == 2) {
+            const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vr));
+            vv[u][0] = f.x; vv[u][1] = f.y;
+          } else {
+            const uint2 w2 = *reinterpret_cast<const uint2*>(vr);
+            const float2 f0 = unpack_bf16x2(w2.x), f1 = unpack_bf16x2(w2.y);
+            vv[u][0] = f0.x; vv[u][1] = f0.y; vv[u][E - 2] = f1.x; vv[u][E - 1] = f1.y;
+          }
+        } else {
 #pragma unroll
-          for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[e];
+          for (int e = 0; e < E; ++e) vv[u][e] = 0.f;
         }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int kk = (kk0 + u) & 31;                  // rows beyond nk carry zeros (and their probabilities are zero)
+        const float4 p0 = *reinterpret_cast<const float4*>(&p_s[warp][kk][0]);
+        const float4 p1 = *reinterpret_cast<const float4*>(&p_s[warp][kk][4]);
+        const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int g = 0; g < kPdMaxG; ++g)
+          if (g < G) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[u][e];
+          }
+      }
     }
     __syncwarp();
   }

@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--model", default="llama-1.1b", choices=["llama-1.1b", "llama-tiny", "llama3-8b"])
     ap.add_argument("--batches", default="1,32,128")
     ap.add_argument("--contexts", default="2048,16384")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a step instead of replaying a CUDA graph")
     ap.add_argument("--hbm-gbs", type=float, default=6552.0, help="measured copy bandwidth used as the roofline denominator")
     a = ap.parse_args()
     from ..models.llama import LlamaConfig, LlamaEngine
@@ -61,7 +62,7 @@ def main():
     for B in batches:
         for ctx in contexts:
             blocks_per_seq = (ctx + 1 + bs - 1) // bs
-            model = LlamaKVModel(eng, num_blocks=B * blocks_per_seq + 1, block_size=bs)
+            model = LlamaKVModel(eng, num_blocks=B * blocks_per_seq + 1, block_size=bs, graphs=not a.no_graphs)
             for layer in range(cfg.n_layers):
                 model.cache.k[layer].normal_(0.0, 1.0)
                 model.cache.v[layer].normal_(0.0, 1.0)
