@@ -21,6 +21,7 @@ _SIGS = {
     "lt_set_wait_budget_cycles": [_ll, _ll],
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
     "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
+    "lt_gemv_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
     "lt_gemm_set_tail_split": [_i],
     "lt_gemm_set_pair_mode": [_i],
     "lt_flash_bwd_set_trace": [_vp],
@@ -175,6 +176,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1
+    if (a_major == 0 and b_major == 0 and a.shape[0] <= 8 and out is None and out_dtype == torch.bfloat16 and bias is None and act == 0
+            and alpha == 1.0 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and a.shape[0] > 0
+            and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+        # a handful of rows (decode): the weight-streaming kernel, one warp per output column
+        M, Kd = a.shape
+        N = b.shape[0]
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        rc = _fn("lt_gemv_bf16")(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), y.data_ptr(), y.stride(0), _p(residual),
+                                 residual.stride(0) if residual is not None else 0, M, N, Kd, _stream())
+        _check(rc, "lt_gemv_bf16")
+        return y
     if a_major == 0:
         M, K = a.shape
     else:

@@ -176,3 +176,21 @@ def test_linear_matmul_bmm_ops_reach_the_tensor_cores_for_fp32_and_fp16():
     (torch.nn.functional.linear(xr, wr, br)).square().sum().backward()
     for got, want in ((x.grad, xr.grad), (w.grad, wr.grad), (b.grad, br.grad)):
         assert float((got.double() - want).norm() / want.norm()) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (3, 1000, 264), (8, 11264, 2048), (5, 2048, 5632)])
+def test_weight_streaming_gemm_for_a_few_rows(M, N, K):
+    """`gemm` with at most eight rows takes the warp-per-column kernel; result (with and without a fused residual)
+    against fp32 PyTorch."""
+    from litetorch_b200.ops import kernels as KK
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    r = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    ref = x.float() @ w.float().t()
+    y = KK.gemm(x, w)
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    y2 = KK.gemm(x, w, residual=r)
+    ref2 = ref + r.float()
+    assert float((y2.float() - ref2).abs().max() / ref2.abs().max()) < 1e-2
+    KK.check_status()
