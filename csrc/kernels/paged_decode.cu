@@ -15,6 +15,13 @@
 
 namespace lt {
 
+// Plain (non-multicast) bulk asynchronous copy global -> this CTA's shared memory; bytes a multiple of 16, both
+// addresses 16-byte aligned; completion is counted on the mbarrier.
+__device__ __forceinline__ void bulk_g2s_pd(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar) : "memory");
+}
+
 template <int D, bool FP8>
 __device__ __forceinline__ void load_row(const void* base, long long elem_off, int lane, float (&out)[D / 32]) {
   constexpr int E = D / 32;
@@ -89,43 +96,93 @@ __global__ void paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const v
 // ---------------------------------------------------------------------------------------------- grouped-query decode
 // One CTA of four warps owns one (sequence, KV head, split): every K / V byte of its key range is read once for the
 // whole group of G = Hq / Hkv query heads (the warp-per-query-head kernel above reads it G times and walks the keys
-// one at a time).  A warp takes 32 keys at a time:
-//   scores   lane = key: the lane reads its key row with 16-byte loads (the 32 rows of a chunk are contiguous in a
-//            cache block) and forms the dot products with the G query vectors, which sit in shared memory pre-scaled
-//            (all lanes read the same address: a broadcast);
+// one at a time).  A warp takes 32 keys at a time, and the K and V rows of the chunks ahead are already on their way:
+//   loads    the rows of one cache block are contiguous, so a chunk is one or two bulk asynchronous copies each for K
+//            and V (cp.async.bulk global -> shared with an mbarrier per stage); one lane requests chunk i + kStages - 1
+//            before the warp starts on chunk i, so several KB per warp are in flight whatever the occupancy;
+//   scores   lane = key: the lane reads its key row from shared memory 16 bytes at a time, starting at a unit rotated
+//            by its lane number (rows are 128 / 256 bytes apart, so unrotated reads would all hit the same banks), and
+//            forms the dot products with the G query vectors, which sit in shared memory pre-scaled;
 //   softmax  per head, one max and one sum reduction per 32 keys; running (max, sum) kept per warp;
 //   P V      lane = pair (D 64) or quad (D 128) of output columns: the probabilities of the chunk go through shared
-//            memory, then for each key the warp reads the V row as one coalesced line and every lane updates its G x E
-//            accumulators.
+//            memory, each V row is read as one conflict-free line and every lane updates its G x E accumulators.
 // The warps' partial results are merged in shared memory and written in the (normalised output, max, sum) form that
-// the merge kernel above already combines across splits.  bf16 caches only (e4m3 stays on the kernel above).
+// the merge kernel below combines across splits.  bf16 caches only (e4m3 stays on the kernel above); block_size must
+// divide 32 or be a multiple of it.
 constexpr int kPdWarps = 4;
 constexpr int kPdMaxG = 8;
+
+template <int D>
+struct PdCfg {
+  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kTileBytes = 32 * kRowBytes;                       // 32 keys of K (or V)
+  static constexpr int kWarpBytes = kStages * 2 * kTileBytes;             // K and V tiles of every stage
+  static constexpr int kOffQ = kPdWarps * kWarpBytes;                     // float q_s[G][D]
+  static constexpr int kOffP = kOffQ + kPdMaxG * D * 4;                   // float p_s[warps][32][G]
+  static constexpr int kOffBar = kOffP + kPdWarps * 32 * kPdMaxG * 4;     // mbarriers [warps][stages]
+  static constexpr int kSmemBytes = kOffBar + kPdWarps * kStages * 8 + 16;
+};
 
 template <int D>
 __global__ void __launch_bounds__(kPdWarps * 32)
 paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables,
                         const int* __restrict__ context_lens, float* __restrict__ part, int S, int Hq, int Hkv, int block_size,
-                        int max_blocks, int splits, float scale) {
+                        int max_blocks, int splits, float scale, int* status) {
+  using Cfg = PdCfg<D>;
   constexpr int E = D / 32;
+  constexpr int ST = Cfg::kStages;
+  constexpr int UNITS = D / 8;                     // 16-byte units per row
+  extern __shared__ __align__(128) uint8_t pd_smem[];
   const int G = Hq / Hkv;
   const int sp = blockIdx.x % splits;
   const int hkv = (blockIdx.x / splits) % Hkv;
   const int s = blockIdx.x / (splits * Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ float q_s[kPdMaxG][D];
-  __shared__ float p_s[kPdWarps][32][kPdMaxG];            // [warp][key of the chunk][head]
-  __shared__ float red_m[kPdWarps][kPdMaxG], red_l[kPdWarps][kPdMaxG];
-  __shared__ float red_o[kPdWarps][kPdMaxG][D];
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, d = i % D;
-    q_s[g][d] = __bfloat162float(q[((long long)s * Hq + hkv * G + g) * D + d]) * scale;
+  float* q_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffQ);                       // [G][D]
+  float* p_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffP) + warp * 32 * kPdMaxG; // [32][G] of this warp
+  uint8_t* my_tiles = pd_smem + warp * Cfg::kWarpBytes;
+  const uint32_t bar0 = smem_u32(pd_smem + Cfg::kOffBar) + warp * ST * 8;
+  __shared__ int abort_s, drain_s;
+  // the reduction at the end reuses the tile area (all copies have been consumed by then)
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x)
+    q_s[i] = __bfloat162float(q[((long long)s * Hq + hkv * G + i / D) * D + i % D]) * scale;
+  if (threadIdx.x == 0) { abort_s = 0; drain_s = 0; }
+  if (lane == 0) {
+    for (int st = 0; st < ST; ++st) mbar_init(bar0 + 8u * st, 1);
+    fence_barrier_init();
   }
   __syncthreads();
+  volatile int* abort_flag = &abort_s;
   const int ctx = context_lens[s];
   const int per = ((ctx + splits - 1) / splits + 31) / 32 * 32;      // whole 32-key chunks per split
   const int t0 = sp * per, t1 = min(ctx, t0 + per);
+  const int* bt = block_tables + (long long)s * max_blocks;
+  const int n_chunks = t1 > t0 ? (t1 - t0 + 31) / 32 : 0;
+  const int my_n = n_chunks > warp ? (n_chunks - warp + kPdWarps - 1) / kPdWarps : 0;   // chunks warp, warp + 4, ...
+
+  // one lane requests the K and V rows of this warp's i-th chunk into stage i % ST
+  auto request = [&](int i) {
+    const int c0 = t0 + (warp + i * kPdWarps) * 32;
+    const uint32_t bar = bar0 + 8u * (i % ST);
+    uint8_t* kt = my_tiles + (i % ST) * 2 * Cfg::kTileBytes;
+    uint8_t* vt = kt + Cfg::kTileBytes;
+    // rows [c0, c0 + 32) clipped to the blocks the sequence owns (the last block is allocated whole)
+    const int last_row = ((t1 - 1) / block_size + 1) * block_size;            // end of the last block holding a live key
+    const int r_end = min(c0 + 32, last_row);
+    mbar_expect_tx(bar, uint32_t(2 * (r_end - c0) * Cfg::kRowBytes));
+    for (int r = c0; r < r_end;) {
+      const int blk = bt[r / block_size];
+      const int in_blk = r % block_size;
+      const int n = min(block_size - in_blk, r_end - r);
+      const long long src = (((long long)blk * Hkv + hkv) * block_size + in_blk) * D;
+      bulk_g2s_pd(smem_u32(kt + (r - c0) * Cfg::kRowBytes), k_cache + src, uint32_t(n * Cfg::kRowBytes), bar);
+      bulk_g2s_pd(smem_u32(vt + (r - c0) * Cfg::kRowBytes), v_cache + src, uint32_t(n * Cfg::kRowBytes), bar);
+      r += n;
+    }
+  };
+
   float m[kPdMaxG], l[kPdMaxG], acc[kPdMaxG][E];
 #pragma unroll
   for (int g = 0; g < kPdMaxG; ++g) {
@@ -133,28 +190,39 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
   }
-  const int* bt = block_tables + (long long)s * max_blocks;
-  for (int c0 = t0 + warp * 32; c0 < t1; c0 += kPdWarps * 32) {
+  if (lane == 0)
+    for (int i = 0; i < ST - 1 && i < my_n; ++i) request(i);
+  bool ok = true;
+  for (int i = 0; i < my_n; ++i) {
+    if (lane == 0 && i + ST - 1 < my_n) request(i + ST - 1);      // its stage was consumed in iteration i - 1
+    ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8u * (i % ST), uint32_t(i / ST) & 1u, abort_flag, status, kStatusTimeoutFull));
+    if (!ok) {
+      // a copy never arrived: give the other requested stages one more bounded wait each, so that no copy of this
+      // warp is still writing shared memory when the CTA leaves, then drop out (the result of the CTA is discarded)
+      for (int r = i + 1; r < my_n && r < i + ST; ++r)
+        mbar_wait(bar0 + 8u * (r % ST), uint32_t(r / ST) & 1u, &drain_s, status, kStatusTimeoutFull);
+      break;
+    }
+    const int c0 = t0 + (warp + i * kPdWarps) * 32;
+    const uint8_t* kt = my_tiles + (i % ST) * 2 * Cfg::kTileBytes;
+    const uint8_t* vt = kt + Cfg::kTileBytes;
     // ---- scores of this lane's key for every head of the group
-    const int t = c0 + lane;
-    const bool live = t < t1;
+    const bool live = c0 + lane < t1;
     float sc[kPdMaxG];
 #pragma unroll
     for (int g = 0; g < kPdMaxG; ++g) sc[g] = 0.f;
-    int my_blk = 0, my_off = 0;
     if (live) {
-      my_blk = bt[t / block_size];
-      my_off = t % block_size;
-      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + (((long long)my_blk * Hkv + hkv) * block_size + my_off) * D);
+      const uint4* kr = reinterpret_cast<const uint4*>(kt + lane * Cfg::kRowBytes);
 #pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
+      for (int jj = 0; jj < UNITS; ++jj) {
+        const int j = (jj + lane) & (UNITS - 1);                  // rotated start: conflict-free across the quarter-warp
         const uint4 u = kr[j];
         const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
 #pragma unroll
         for (int g = 0; g < kPdMaxG; ++g) {
           if (g < G) {
-            const float4 q0 = *reinterpret_cast<const float4*>(&q_s[g][j * 8]);
-            const float4 q1 = *reinterpret_cast<const float4*>(&q_s[g][j * 8 + 4]);
+            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * D + j * 8);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * D + j * 8 + 4);
             sc[g] += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + c.x * q1.x + c.y * q1.y + d.x * q1.z + d.y * q1.w;
           }
         }
@@ -177,77 +245,64 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         m[g] = nm;
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[g][e] *= a;
-        p_s[warp][lane][g] = pv;
+        p_s[lane * kPdMaxG + g] = pv;
       } else {
-        p_s[warp][lane][g] = 0.f;
+        p_s[lane * kPdMaxG + g] = 0.f;
       }
     }
     __syncwarp();
-    // ---- P V: lane = E output columns; one coalesced V row per key.  U rows are requested before the first is used,
-    // so a warp keeps U x D x 2 bytes in flight instead of one row (a single row per warp left the kernel bound by
-    // memory latency at a tenth of the copy bandwidth).
-    constexpr int U = (D == 64) ? 16 : 8;
+    // ---- P V: lane = E output columns; V rows come from shared memory, one conflict-free line per key
     const int nk = min(32, t1 - c0);
-#pragma unroll 1
-    for (int kk0 = 0; kk0 < nk; kk0 += U) {
-      float vv[U][E];
+#pragma unroll 4
+    for (int kk = 0; kk < nk; ++kk) {
+      const __nv_bfloat16* vr = reinterpret_cast<const __nv_bfloat16*>(vt + kk * Cfg::kRowBytes) + lane * E;
+      float vv[E];
+      if (E == 2) {
+        const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vr));
+        vv[0] = f.x; vv[1] = f.y;
+      } else {
+        const uint2 w2 = *reinterpret_cast<const uint2*>(vr);
+        const float2 f0 = unpack_bf16x2(w2.x), f1 = unpack_bf16x2(w2.y);
+        vv[0] = f0.x; vv[1] = f0.y; vv[E - 2] = f1.x; vv[E - 1] = f1.y;
+      }
+      const float4 p0 = *reinterpret_cast<const float4*>(p_s + kk * kPdMaxG);
+      const float4 p1 = *reinterpret_cast<const float4*>(p_s + kk * kPdMaxG + 4);
+      const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int kk = kk0 + u;
-        const int blk_u = __shfl_sync(0xffffffffu, my_blk, kk & 31);
-        const int off_u = __shfl_sync(0xffffffffu, my_off, kk & 31);
-        if (kk < nk) {
-          const __nv_bfloat16* vr = v_cache + (((long long)blk_u * Hkv + hkv) * block_size + off_u) * D + lane * E;
-          if (E == 2) {
-            const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vr));
-            vv[u][0] = f.x; vv[u][1] = f.y;
-          } else {
-            const uint2 w2 = *reinterpret_cast<const uint2*>(vr);
-            const float2 f0 = unpack_bf16x2(w2.x), f1 = unpack_bf16x2(w2.y);
-            vv[u][0] = f0.x; vv[u][1] = f0.y; vv[u][E - 2] = f1.x; vv[u][E - 1] = f1.y;
-          }
-        } else {
+      for (int g = 0; g < kPdMaxG; ++g)
+        if (g < G) {
 #pragma unroll
-          for (int e = 0; e < E; ++e) vv[u][e] = 0.f;
+          for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[e];
         }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int kk = (kk0 + u) & 31;                  // rows beyond nk carry zeros (and their probabilities are zero)
-        const float4 p0 = *reinterpret_cast<const float4*>(&p_s[warp][kk][0]);
-        const float4 p1 = *reinterpret_cast<const float4*>(&p_s[warp][kk][4]);
-        const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-        for (int g = 0; g < kPdMaxG; ++g)
-          if (g < G) {
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[u][e];
-          }
-      }
     }
-    __syncwarp();
+    __syncwarp();            // every lane is done with this stage and with p_s before lane 0 requests into it again
   }
-  // ---- merge the four warps, write this split's partial result
+  // ---- merge the four warps (the tile area is free now: every requested copy has been waited for), write the partial result
+  __syncthreads();
+  float* red_m = reinterpret_cast<float*>(pd_smem);                 // [warps][G]
+  float* red_l = red_m + kPdWarps * kPdMaxG;                         // [warps][G]
+  float* red_o = red_l + kPdWarps * kPdMaxG;                         // [warps][G][D]
 #pragma unroll
   for (int g = 0; g < kPdMaxG; ++g)
     if (g < G) {
-      if (lane == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
+      if (lane == 0) { red_m[warp * kPdMaxG + g] = ok ? m[g] : -INFINITY; red_l[warp * kPdMaxG + g] = ok ? l[g] : 0.f; }
 #pragma unroll
-      for (int e = 0; e < E; ++e) red_o[warp][g][lane * E + e] = acc[g][e];
+      for (int e = 0; e < E; ++e) red_o[(warp * kPdMaxG + g) * D + lane * E + e] = acc[g][e];
     }
   __syncthreads();
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i % D;
     float gm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kPdWarps; ++w) gm = fmaxf(gm, red_m[w][g]);
+    for (int w = 0; w < kPdWarps; ++w) gm = fmaxf(gm, red_m[w * kPdMaxG + g]);
     float lsum = 0.f, o = 0.f;
 #pragma unroll
     for (int w = 0; w < kPdWarps; ++w) {
-      if (red_m[w][g] == -INFINITY) continue;
-      const float a = __expf(red_m[w][g] - gm);
-      lsum += red_l[w][g] * a;
-      o += red_o[w][g][d] * a;
+      const float mw = red_m[w * kPdMaxG + g];
+      if (mw == -INFINITY) continue;
+      const float a = __expf(mw - gm);
+      lsum += red_l[w * kPdMaxG + g] * a;
+      o += red_o[(w * kPdMaxG + g) * D + d] * a;
     }
     float* out = part + (((long long)s * Hq + hkv * G + g) * splits + sp) * (D + 2);
     out[d] = lsum > 0.f ? o / lsum : 0.f;
@@ -325,13 +380,21 @@ int lt_paged_decode(const void* q, const void* k_cache, const void* v_cache, con
   paged_decode_kernel<DD, F8><<<blocks, threads, 0, st>>>(Q, k_cache, v_cache, block_tables, context_lens, part, S, Hq, Hkv, \
                                                           block_size, max_blocks, splits, scale, k_scale, v_scale)
   const int G = Hq / Hkv;
-  if (!kv_fp8 && G <= kPdMaxG && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0) {
-    // bf16 caches: every K / V byte is read once for the whole group of query heads
+  const bool bs_ok = block_size > 0 && (32 % block_size == 0 || block_size % 32 == 0);
+  if (!kv_fp8 && G <= kPdMaxG && bs_ok && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0) {
+    // bf16 caches: every K / V byte is read once for the whole group of query heads, through a shared-memory pipeline
     const int ctas = S * Hkv * splits;
     auto KC = static_cast<const __nv_bfloat16*>(k_cache);
     auto VC = static_cast<const __nv_bfloat16*>(v_cache);
-    if (D == 64) paged_decode_gqa_kernel<64><<<ctas, kPdWarps * 32, 0, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale);
-    else paged_decode_gqa_kernel<128><<<ctas, kPdWarps * 32, 0, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale);
+    static bool configured = false;
+    if (!configured) {
+      LT_RETURN_IF_CUDA(cudaFuncSetAttribute(paged_decode_gqa_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PdCfg<64>::kSmemBytes));
+      LT_RETURN_IF_CUDA(cudaFuncSetAttribute(paged_decode_gqa_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PdCfg<128>::kSmemBytes));
+      configured = true;
+    }
+    int* status = device_status_word();
+    if (D == 64) paged_decode_gqa_kernel<64><<<ctas, kPdWarps * 32, PdCfg<64>::kSmemBytes, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale, status);
+    else paged_decode_gqa_kernel<128><<<ctas, kPdWarps * 32, PdCfg<128>::kSmemBytes, st>>>(Q, KC, VC, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale, status);
   } else if (D == 64) { if (kv_fp8) LT_PD(64, true); else LT_PD(64, false); }
   else { if (kv_fp8) LT_PD(128, true); else LT_PD(128, false); }
 #undef LT_PD
