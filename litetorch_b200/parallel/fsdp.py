@@ -128,6 +128,15 @@ class SymmetricBuffer:
     def peer_ptrs(self, elem_offset: int = 0) -> List[int]:
         return [p + elem_offset * self.itemsize for p in self.ptrs]
 
+    def peer_tensor(self, rank: int) -> "torch.Tensor | None":
+        """Rank `rank`'s copy of this buffer as a tensor of this process (its memory is mapped here), for copies that
+        the copy engines can carry (`dst.copy_(buf.peer_tensor(r)[a:b])`); None with the CUDA-IPC back-end."""
+        handle = getattr(self, "handle", None)
+        if handle is None:
+            return None
+        guard = _CANARY_BYTES // self.itemsize
+        return handle.get_buffer(rank, (self.tensor.numel(),), self.tensor.dtype, guard)
+
     def check(self) -> bool:
         """True when both guard areas of this rank's copy still hold the canary byte (synchronises the device)."""
         return all(bool((g == _CANARY_VALUE).all()) for g in self._guards)

@@ -164,7 +164,15 @@ class HybridWeights:
                 self.sym_grad = None
                 self.grad_full = torch.zeros(self.n_full, dtype=torch.bfloat16, device=dev)
             self.flag_epoch = [0] * self.n_slots
+            # the dp peers' parameter shards as tensors of this process, for copy-engine gathers (LT_HYBRID_GATHER=kernel
+            # keeps the peer-load kernel instead)
+            self.peer_param = None
+            if self.dp > 1 and os.environ.get("LT_HYBRID_GATHER", "copy") == "copy":
+                views = [self.sym_param.peer_tensor(r) for r in self.mesh.ranks_along("dp")]
+                if all(v is not None for v in views):
+                    self.peer_param = views
         else:
+            self.peer_param = None
             self.sym_param = self.sym_grad = self.sym_flags = None
             self.param_shard = torch.zeros(self.n_shard, dtype=param_dtype, device=dev)
             self.grad_full = torch.zeros(self.n_full, dtype=param_dtype, device=dev)
@@ -269,8 +277,16 @@ class HybridWeights:
             with torch.cuda.stream(self.gstream):
                 if after_event is not None:
                     self.gstream.wait_event(after_event)
-                self.K.gather_shards(self._dp_ptrs(self.sym_param, self.shard_off[name]), [(0, n)], [dst],
-                                     max_ctas=self.gather_ctas)
+                if self.peer_param is not None:
+                    # copy engines: one device-to-device copy per dp rank out of its mapped shard; no SM is involved,
+                    # so the transfer runs under whatever kernels the compute stream has resident
+                    so = self.shard_off[name]
+                    flat = dst.view(-1)
+                    for j, peer in enumerate(self.peer_param):
+                        flat[j * n:(j + 1) * n].copy_(peer[so:so + n], non_blocking=True)
+                else:
+                    self.K.gather_shards(self._dp_ptrs(self.sym_param, self.shard_off[name]), [(0, n)], [dst],
+                                         max_ctas=self.gather_ctas)
                 ev = torch.cuda.Event()
                 ev.record(self.gstream)
             self.ready[key][b] = ev
