@@ -374,9 +374,11 @@ class LlamaEngine:
         K.rope_(dqkv, self.cos, self.sin, T, Hkv, hd, col_offset=Hq * hd, backward=True)
         dh1 = w.col_dgrad(dqkv, p + "wqkv")
         w.wgrad(dqkv, h1f, p + "wqkv", accumulate)
-        # the gradient that leaves this layer is the next layer's input to a gathered GEMM (not for layer 0: embedding)
+        # The gradient that leaves this layer is the input of the next gathered GEMM - unless that layer recomputes its
+        # forward pass first (its gathers would take the slot), or there is no next layer (embedding).
+        direct = i > 0 and (i - 1) >= self.ckpt_layers
         dx, _, _ = K.norm_bwd(dh1, x, w.p(p + "attn_norm"), None, rstd1, dres=dx1, dw=w.vector_grad(p + "attn_norm"),
-                              accumulate=accumulate, out=w.gather_slot(*x.shape) if i > 0 else None)
+                              accumulate=accumulate, out=w.gather_slot(*x.shape) if direct else None)
         self.kernel_launches += 22
         return dx
 
@@ -425,7 +427,7 @@ class LlamaEngine:
         if fused_update:
             w.bucket_done("head")
         dx, _, _ = K.norm_bwd(dhf, x, w.p("final_norm"), None, rstd_f, dw=w.vector_grad("final_norm"), accumulate=accumulate,
-                              out=w.gather_slot(*x.shape))
+                              out=w.gather_slot(*x.shape) if cfg.n_layers - 1 >= self.ckpt_layers else None)
         for i in reversed(range(cfg.n_layers)):
             if i < self.ckpt_layers:
                 _, ctx = self._layer_fwd(i, saved[i], B, T)
