@@ -119,7 +119,8 @@ struct PdCfg {
   static constexpr int kTileBytes = 32 * kRowBytes;                       // 32 keys of K (or V)
   static constexpr int kWarpBytes = kStages * 2 * kTileBytes;             // K and V tiles of every stage
   static constexpr int kOffQ = kPdWarps * kWarpBytes;                     // float q_s[G][D]
-  static constexpr int kOffP = kOffQ + kPdMaxG * D * 4;                   // float p_s[warps][32][G]
+  static constexpr int kQUnitStride = kPdMaxG * 8 + 4;                    // floats per 8-column unit of q (all heads) + pad
+  static constexpr int kOffP = kOffQ + (D / 8) * kQUnitStride * 4;       // float p_s[warps][G][32]
   static constexpr int kOffBar = kOffP + kPdWarps * 32 * kPdMaxG * 4;     // mbarriers [warps][stages]
   static constexpr int kSmemBytes = kOffBar + kPdWarps * kStages * 8 + 16;
 };
@@ -140,14 +141,18 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int hkv = (blockIdx.x / splits) % Hkv;
   const int s = blockIdx.x / (splits * Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* q_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffQ);                       // [G][D]
-  float* p_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffP) + warp * 32 * kPdMaxG; // [32][G] of this warp
+  float* q_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffQ);                       // [D / 8][kQUnitStride]
+  float* p_s = reinterpret_cast<float*>(pd_smem + Cfg::kOffP) + warp * 32 * kPdMaxG; // [G][32] of this warp
   uint8_t* my_tiles = pd_smem + warp * Cfg::kWarpBytes;
   const uint32_t bar0 = smem_u32(pd_smem + Cfg::kOffBar) + warp * ST * 8;
   __shared__ int abort_s, drain_s;
   // the reduction at the end reuses the tile area (all copies have been consumed by then)
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x)
-    q_s[i] = __bfloat162float(q[((long long)s * Hq + hkv * G + i / D) * D + i % D]) * scale;
+  // q_s[unit j][head g][8 columns], units kQUnitStride floats apart: a lane that starts at unit (lane & 7) reads 32-byte
+  // pieces whose 16-byte halves fall into distinct bank groups across its quarter-warp
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i % D;
+    q_s[(d >> 3) * Cfg::kQUnitStride + g * 8 + (d & 7)] = __bfloat162float(q[((long long)s * Hq + hkv * G + g) * D + d]) * scale;
+  }
   if (threadIdx.x == 0) { abort_s = 0; drain_s = 0; }
   if (lane == 0) {
     for (int st = 0; st < ST; ++st) mbar_init(bar0 + 8u * st, 1);
@@ -221,8 +226,8 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
         for (int g = 0; g < kPdMaxG; ++g) {
           if (g < G) {
-            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * D + j * 8);
-            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * D + j * 8 + 4);
+            const float4 q0 = *reinterpret_cast<const float4*>(q_s + j * Cfg::kQUnitStride + g * 8);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_s + j * Cfg::kQUnitStride + g * 8 + 4);
             sc[g] += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + c.x * q1.x + c.y * q1.y + d.x * q1.z + d.y * q1.w;
           }
         }
@@ -245,9 +250,7 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         m[g] = nm;
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[g][e] *= a;
-        p_s[lane * kPdMaxG + g] = pv;
-      } else {
-        p_s[lane * kPdMaxG + g] = 0.f;
+        p_s[g * 32 + lane] = pv;
       }
     }
     __syncwarp();
@@ -265,14 +268,12 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const float2 f0 = unpack_bf16x2(w2.x), f1 = unpack_bf16x2(w2.y);
         vv[0] = f0.x; vv[1] = f0.y; vv[E - 2] = f1.x; vv[E - 1] = f1.y;
       }
-      const float4 p0 = *reinterpret_cast<const float4*>(p_s + kk * kPdMaxG);
-      const float4 p1 = *reinterpret_cast<const float4*>(p_s + kk * kPdMaxG + 4);
-      const float pg[kPdMaxG] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
       for (int g = 0; g < kPdMaxG; ++g)
         if (g < G) {
+          const float pgk = p_s[g * 32 + kk];              // same address for every lane: a broadcast
 #pragma unroll
-          for (int e = 0; e < E; ++e) acc[g][e] += pg[g] * vv[e];
+          for (int e = 0; e < E; ++e) acc[g][e] += pgk * vv[e];
         }
     }
     __syncwarp();            // every lane is done with this stage and with p_s before lane 0 requests into it again
