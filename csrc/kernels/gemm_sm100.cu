@@ -123,15 +123,22 @@ int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
                      block_n, max_ctas, stream);
 }
 
-// The same GEMM for fp16 operands (kind 1: any operand layout, C bf16 or fp32) and for fp32 operands on the tensor cores
-// as tf32 (kind 2: both operands K-major, i.e. a_major = b_major = 0, K a multiple of 4, C fp32).  bias / residual
+// The same GEMM for fp16 operands (kind 1: any operand layout, C bf16 or fp32), for fp32 operands on the tensor cores
+// as tf32 (kind 2: both operands K-major, i.e. a_major = b_major = 0, K a multiple of 4, C fp32) and for signed int8
+// operands (kind 3: both K-major, K a multiple of 16, C = alpha * integer sums as fp32; the reference's
+// w8a8_matmul_kernel, src/backend/gpu_native/nn/nn_kernels.cu:1314-1337).  bias / residual
 // stay bf16.  Takes the place of the reference's cublasHgemm / cublasSgemm-with-TF32 paths
 // (src/backend/gpu_native/math/gemm.cu:3-47, 75-120).
 int lt_gemm_typed(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                   long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
                   long long ldr, int act, int accumulate, float alpha, void* stream) {
   using namespace lt;
-  if (kind < 0 || kind > 2) return -int(kStatusBadArgument);
+  if (kind < 0 || kind > 3) return -int(kStatusBadArgument);
+  if (kind == 3) {
+    // signed int8 operands, both K-major, C = alpha * (int32 sums) as fp32; rows seen as 2-byte units of half the extent
+    if (a_major != 0 || b_major != 0 || !out_fp32 || (K & 15) || (lda & 15) || (ldb & 15) || bias || residual) return -int(kStatusBadArgument);
+    return gemm_launch(3, A, B, C, M, N, K / 2, lda / 2, ldb / 2, ldc, 0, 0, 1, nullptr, nullptr, 0, 0, accumulate, alpha, 0, 0, stream);
+  }
   if (kind == 2) {
     if (a_major != 0 || b_major != 0 || !out_fp32 || (K & 3) || (lda & 3) || (ldb & 3)) return -int(kStatusBadArgument);
     // fp32 rows seen as rows of 2-byte units: twice the K extent and twice the pitches
@@ -150,8 +157,9 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -int(kStatusBadArgument);
   const int sms = sm_count();
-  const bool split_on = g_split_enabled.load() != 0;
-  const int pair_mode = g_pair_mode.load();
+  // int8: integer accumulators are converted in the one-CTA kernel's epilogue; no K split (its workspace holds floats)
+  const bool split_on = kind != 3 && g_split_enabled.load() != 0;
+  const int pair_mode = kind == 3 ? 0 : g_pair_mode.load();
   if (pair_mode > 0 && block_n != 128 && (max_ctas <= 0 || max_ctas >= sms)) {
     const double c256 = wave_cost(M, N, K, sms, 256), c128 = wave_cost(M, N, K, sms, 128);
     const double single = c256 < c128 ? c256 : c128;

@@ -28,7 +28,8 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
 struct GemmParams {
-  // Operand element kind: 0 = bf16, 1 = fp16 (both kind::f16), 2 = fp32 used as tf32 (kind::tf32).  For tf32 the
+  // Operand element kind: 0 = bf16, 1 = fp16 (both kind::f16), 2 = fp32 used as tf32 (kind::tf32), 3 = signed int8
+  // (kind::i8, 32-bit integer accumulators that the epilogue converts to float; one-CTA kernel only).  For tf32 / int8 the
   // host describes the operands to TMA as 2-byte elements of twice the K extent (the copy is byte-identical) and
   // K below counts those 2-byte units, so the tiling, the 128-byte swizzled stage rows and the 32-byte descriptor
   // step per MMA are the same for every kind; only the instruction and the format bits of its descriptor differ.
@@ -146,7 +147,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32]) {
   float v[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  for (int j = 0; j < 32; ++j) v[j] = (p.kind == 3 ? float(int(r[j])) : __uint_as_float(r[j])) * p.alpha;
   const bool full = (col0 + 32 <= p.N);
   const int ncols = full ? 32 : (p.N - col0);
   if (p.bias) {
@@ -354,8 +355,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
-      const bool tf32 = p.kind == 2;
+      const uint32_t idesc = p.kind == 3 ? make_idesc_i8(kBlockM, BLOCK_N)
+                                         : make_idesc_f16(kBlockM, BLOCK_N, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
+      const bool tf32 = p.kind == 2, i8 = p.kind == 3;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -378,6 +380,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             if (tf32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else if (i8) umma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));

@@ -605,3 +605,47 @@ int lt_moe_expert_bwd(const void* gu, const void* dh_u, const void* w, const voi
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------- int8 quantisers
+// Per-tensor: q = clamp(round(x / scale), -127, 127).  Per-row: scale[r] = absmax(row r) / 127 (1 for an all-zero row),
+// a warp per row.  x is fp32 (is_bf16 = 0) or bf16.  Reference: include/litetorch/quantization.h:15-40 (CPU loops).
+namespace lt {
+__device__ __forceinline__ float ldq(const void* x, int is_bf16, long long i) {
+  return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]) : static_cast<const float*>(x)[i];
+}
+__global__ void quant_int8_tensor_kernel(const void* __restrict__ x, int is_bf16, signed char* __restrict__ q, long long n, float inv_scale) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    q[i] = (signed char)fminf(fmaxf(rintf(ldq(x, is_bf16, i) * inv_scale), -127.f), 127.f);
+}
+__global__ void quant_int8_rows_kernel(const void* __restrict__ x, int is_bf16, signed char* __restrict__ q, float* __restrict__ scale,
+                                       int rows, int cols) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long base = (long long)row * cols;
+  float am = 0.f;
+  for (int c = lane; c < cols; c += 32) am = fmaxf(am, fabsf(ldq(x, is_bf16, base + c)));
+  for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  const float sc = am > 0.f ? am / 127.f : 1.f;
+  if (lane == 0) scale[row] = sc;
+  const float inv = 1.f / sc;
+  for (int c = lane; c < cols; c += 32)
+    q[base + c] = (signed char)fminf(fmaxf(rintf(ldq(x, is_bf16, base + c) * inv), -127.f), 127.f);
+}
+}  // namespace lt
+
+extern "C" {
+int lt_quant_int8_tensor(const void* x, int is_bf16, void* q, long long n, float scale, void* stream) {
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  lt::quant_int8_tensor_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, is_bf16, static_cast<signed char*>(q), n, 1.f / scale);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+int lt_quant_int8_rows(const void* x, int is_bf16, void* q, float* scale, int rows, int cols, void* stream) {
+  if (rows == 0 || cols == 0) return 0;
+  lt::quant_int8_rows_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, is_bf16, static_cast<signed char*>(q), scale, rows, cols);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
+}  // extern "C"

@@ -104,8 +104,16 @@ class Ops:
     @staticmethod
     def w8a8_matmul(x, w, x_scale: float, w_scale: float):
         """int8 x int8 with int32 accumulation and per-tensor scales (src/ops/w8a8_ops.cpp:28-107)."""
-        xq = torch.clamp(torch.round(_unwrap(x).float() / x_scale), -127, 127)
-        wq = torch.clamp(torch.round(_unwrap(w).float() / w_scale), -127, 127)
+        xt, wt = _unwrap(x), _unwrap(w)
+        if (xt.is_cuda and xt.dim() == 2 and wt.dim() == 2 and xt.dtype in (torch.float32, torch.bfloat16) and wt.dtype == xt.dtype
+                and xt.shape[1] % 16 == 0 and xt.numel() > 0 and wt.numel() > 0):
+            # quantiser kernels + the tcgen05 int8 GEMM (exact int32 sums); w is [K, N]: its codes are laid out K-major first
+            from . import kernels as K
+            xq = K.quant_int8_tensor(xt, x_scale)
+            wq = K.quant_int8_tensor(wt.t().contiguous(), w_scale)
+            return _w(K.gemm_i8(xq, wq, alpha=x_scale * w_scale))
+        xq = torch.clamp(torch.round(xt.float() / x_scale), -127, 127)
+        wq = torch.clamp(torch.round(wt.float() / w_scale), -127, 127)
         return _w(torch.matmul(xq, wq) * (x_scale * w_scale))
 
     # ------------------------------------------------------------------ activations

@@ -22,6 +22,8 @@ _SIGS = {
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
     "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
     "lt_gemv_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
+    "lt_quant_int8_tensor": [_vp, _i, _vp, _ll, _f, _vp],
+    "lt_quant_int8_rows": [_vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_gemm_set_tail_split": [_i],
     "lt_gemm_set_pair_mode": [_i],
     "lt_flash_bwd_set_trace": [_vp],
@@ -241,6 +243,38 @@ def gemm_any(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int
     _check(rc, "lt_gemm_typed")
     want = out_dtype or dt
     return out if want == torch.float32 else out.to(want)
+
+
+def quant_int8_tensor(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """clamp(round(x / scale), -127, 127) as int8 (x fp32 or bf16, contiguous)."""
+    x = x.contiguous()
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    _check(_fn("lt_quant_int8_tensor")(x.data_ptr(), _dt(x), q.data_ptr(), x.numel(), float(scale), _stream()), "lt_quant_int8_tensor")
+    return q
+
+
+def quant_int8_rows(x: torch.Tensor):
+    """Per-row absmax int8 codes of a 2-D tensor: (q int8 [R, C], scale fp32 [R]) with x ~ q * scale[:, None]."""
+    x = x.contiguous()
+    R, C = x.shape
+    q = torch.empty((R, C), dtype=torch.int8, device=x.device)
+    sc = torch.empty(R, dtype=torch.float32, device=x.device)
+    _check(_fn("lt_quant_int8_rows")(x.data_ptr(), _dt(x), q.data_ptr(), sc.data_ptr(), R, C, _stream()), "lt_quant_int8_rows")
+    return q, sc
+
+
+def gemm_i8(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+    """fp32 C[M, N] = alpha * (a[M, K] @ b[N, K]^T) for int8 operands with exact 32-bit integer accumulation on the
+    tensor cores (tcgen05 kind::i8); K a multiple of 16."""
+    assert a.dtype == torch.int8 and b.dtype == torch.int8 and a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
+    a, b = a.contiguous(), b.contiguous()
+    M, Kd = a.shape
+    N = b.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    rc = _fn("lt_gemm_typed")(3, a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, Kd, a.stride(0), b.stride(0), out.stride(0),
+                              0, 0, 1, None, None, 0, 0, 0, float(alpha), _stream())
+    _check(rc, "lt_gemm_typed(int8)")
+    return out
 
 
 def gemm_set_tail_split(enable: bool):

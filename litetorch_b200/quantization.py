@@ -80,10 +80,15 @@ def fake_quantize(x: torch.Tensor, scale: float, zero_point: float = 0.0, bits: 
 
 def quantize_linear(layer) -> None:
     """Replace `layer.weight` by int8 codes with one scale per output row (dequantised on the fly in forward)."""
-    W = _unwrap(layer.weight).detach().float()
-    amax = W.abs().amax(1)
-    scales = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
-    q = torch.round(W / scales[:, None]).to(torch.int8)
+    Wt = _unwrap(layer.weight).detach()
+    if Wt.is_cuda and Wt.dim() == 2 and Wt.dtype in (torch.float32, torch.bfloat16):
+        from .ops import kernels as K                  # warp-per-row absmax + rounding kernel
+        q, scales = K.quant_int8_rows(Wt)
+    else:
+        W = Wt.float()
+        amax = W.abs().amax(1)
+        scales = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+        q = torch.round(W / scales[:, None]).to(torch.int8)
     layer.weight = Tensor(q)
     layer.scales = Tensor(scales)
 

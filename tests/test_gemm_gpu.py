@@ -194,3 +194,31 @@ def test_weight_streaming_gemm_for_a_few_rows(M, N, K):
     ref2 = ref + r.float()
     assert float((y2.float() - ref2).abs().max() / ref2.abs().max()) < 1e-2
     KK.check_status()
+
+
+def test_int8_gemm_and_quantisers_are_exact():
+    """tcgen05 kind::i8: integer sums are exact, so the result must equal an int64 reference bit for bit; the per-tensor and
+    per-row quantisers against the PyTorch formulas; `Ops.w8a8_matmul` through them."""
+    import litetorch_b200 as lt
+    from litetorch_b200.core import Tensor, _unwrap
+    from litetorch_b200.ops import kernels as KK
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for (M, N, Kd) in [(256, 384, 512), (100, 72, 48), (1000, 264, 2048)]:
+        a = torch.randint(-127, 128, (M, Kd), device="cuda", generator=g, dtype=torch.int8)
+        b = torch.randint(-127, 128, (N, Kd), device="cuda", generator=g, dtype=torch.int8)
+        c = KK.gemm_i8(a, b, alpha=0.5)
+        ref = (a.long() @ b.long().t()).double() * 0.5
+        assert torch.equal(c.double(), ref), (M, N, Kd)
+    x = torch.randn(300, 160, device="cuda", generator=g)
+    q = KK.quant_int8_tensor(x, 0.03)
+    assert torch.equal(q, torch.clamp(torch.round(x / 0.03), -127, 127).to(torch.int8))
+    qr, sc = KK.quant_int8_rows(x.bfloat16())
+    xb = x.bfloat16().float()
+    sref = xb.abs().amax(1) / 127.0
+    assert float((sc - sref).abs().max()) < 1e-6
+    assert int((qr.int() - torch.clamp(torch.round(xb / sref[:, None]), -127, 127).int()).abs().max()) <= 1
+    w = torch.randn(160, 96, device="cuda", generator=g)
+    y = _unwrap(lt.Ops.w8a8_matmul(Tensor(x), Tensor(w), 0.03, 0.02))
+    yr = torch.clamp(torch.round(x / 0.03), -127, 127) @ torch.clamp(torch.round(w / 0.02), -127, 127) * (0.03 * 0.02)
+    assert float((y - yr).abs().max()) < 1e-3
+    KK.check_status()
