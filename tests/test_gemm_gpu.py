@@ -207,7 +207,7 @@ def test_int8_gemm_and_quantisers_are_exact():
         a = torch.randint(-127, 128, (M, Kd), device="cuda", generator=g, dtype=torch.int8)
         b = torch.randint(-127, 128, (N, Kd), device="cuda", generator=g, dtype=torch.int8)
         c = KK.gemm_i8(a, b, alpha=0.5)
-        ref = (a.long() @ b.long().t()).double() * 0.5
+        ref = (a.double() @ b.double().t()) * 0.5          # exact: every partial sum is an integer below 2^53
         assert torch.equal(c.double(), ref), (M, N, Kd)
     x = torch.randn(300, 160, device="cuda", generator=g)
     q = KK.quant_int8_tensor(x, 0.03)
