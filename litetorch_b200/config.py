@@ -183,12 +183,16 @@ def _presets() -> Dict[str, RunConfig]:
     llama8b = RunConfig(model=ModelConfig("llama3-8b", 128256, 32, 4096, 32, 8, 128, 14336, rope_theta=5e5),
                         parallel=ParallelConfig(tp=8, zero_stage=0), seq_len=8192, micro_batch=8)
     llama8b_fp8 = RunConfig.from_dict(dict(llama8b.to_dict(), precision="fp8"))
+    # the benchmark's headline layout: tensor parallelism inside a pair of GPUs, ZeRO-3 over the rest of the node
+    llama8b_fsdp_tp2 = RunConfig(model=ModelConfig("llama3-8b", 128256, 32, 4096, 32, 8, 128, 14336, rope_theta=5e5),
+                                 parallel=ParallelConfig(tp=2, zero_stage=3), seq_len=8192, micro_batch=2)
     moe = RunConfig(model=ModelConfig("moe-8x2b", 32000, 16, 2048, 16, 4, 128, 5632, n_experts=8, top_k=2),
                     parallel=ParallelConfig(ep=8, zero_stage=0), seq_len=4096, micro_batch=2)
     hybrid = RunConfig(model=ModelConfig("llama-3b-long", 32000, 28, 3072, 24, 8, 128, 8192),
                        parallel=ParallelConfig(tp=2, cp=2, pp=2, zero_stage=0), seq_len=32768, micro_batch=1, micro_batches=8,
                        activation_checkpointing=True)
     return {"gpt-cpu": gpt, "llama-1.1b-fsdp": llama1b, "llama3-8b-tp8": llama8b, "llama3-8b-tp8-fp8": llama8b_fp8,
+            "llama3-8b-fsdp-tp2": llama8b_fsdp_tp2,
             "moe-8x2b-ep8": moe, "llama-3b-long-hybrid": hybrid}
 
 

@@ -149,3 +149,38 @@ def test_trainer_save_load_resumes_on_the_same_curve(tmp_path, nproc, tp):
     assert res["first"] == res["full"][:3]
     assert all(abs(x - y) < 1e-6 for x, y in zip(res["rest"], res["full"][3:])), res
     assert res["refused"] and res["step"] == 6
+
+
+CONFIG_WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, %(root)r)
+import torch.distributed as dist
+import litetorch_b200 as lt
+from litetorch_b200.trainer import Trainer
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+run = lt.config.load("llama3-8b-fsdp-tp2")          # tensor parallelism 2 x ZeRO-3, shrunk to a toy model by overrides
+run = lt.config.apply_env(run, {"LT_CFG_MODEL__VOCAB": "512", "LT_CFG_MODEL__N_LAYERS": "2", "LT_CFG_MODEL__D_MODEL": "256",
+                                "LT_CFG_MODEL__N_Q": "4", "LT_CFG_MODEL__N_KV": "2", "LT_CFG_MODEL__HEAD_DIM": "64",
+                                "LT_CFG_MODEL__FFN": "512", "LT_CFG_SEQ_LEN": "64"})
+tr = Trainer.from_config(run, device="cpu", param_dtype=torch.float32)
+g = torch.Generator().manual_seed(rank // tr.tp)
+tok = torch.randint(0, 512, (2, 65), generator=g)
+losses = [tr.step(tok[:, :-1].contiguous(), tok[:, 1:].contiguous()) for _ in range(3)]
+if rank == 0:
+    print("RESULT " + json.dumps({"tp": tr.tp, "dp": tr.dp, "weights": type(tr.engine.w).__name__, "losses": losses}))
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_trainer_from_config_builds_the_fsdp_tp_layout(tmp_path):
+    script = os.path.join(str(tmp_path), "config_worker.py")
+    with open(script, "w") as f:
+        f.write(CONFIG_WORKER % {"root": ROOT})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
+           "--master-port", "29879", script]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["tp"] == 2 and res["dp"] == 2 and res["weights"] == "HybridWeights"
+    assert res["losses"][2] < res["losses"][0]
