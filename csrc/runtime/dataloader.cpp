@@ -19,11 +19,48 @@
 #include <vector>
 
 extern "C" uint32_t lt_crc32(const void* data, uint64_t n);
+extern "C" void lt_parallel_for(void* fn_ptr, void* ctx, uint64_t n, uint64_t min_parallel);
+extern "C" void* lt_pool_create(void* ralloc, void* rfree, void* ctx, uint64_t max_cached, uint64_t max_block, uint64_t round_to);
+extern "C" void* lt_pool_alloc(void* pool, uint64_t bytes);
+extern "C" void lt_pool_free(void* pool, void* ptr);
 
 namespace {
 
+// Batch storage comes from the host block pool shared by all loaders: a prefetch thread allocates and the consumer
+// frees a few multi-megabyte blocks per step, which the pool turns into reuse of the same blocks.
+void* batch_pool() {
+  static void* pool = lt_pool_create(nullptr, nullptr, nullptr, 1ull << 30, 0, 4096);
+  return pool;
+}
+
+struct PoolBuf {
+  float* ptr = nullptr;
+  uint64_t n = 0;
+  PoolBuf() = default;
+  PoolBuf(const PoolBuf&) = delete;
+  PoolBuf& operator=(const PoolBuf&) = delete;
+  PoolBuf(PoolBuf&& o) noexcept : ptr(o.ptr), n(o.n) { o.ptr = nullptr; o.n = 0; }
+  PoolBuf& operator=(PoolBuf&& o) noexcept {
+    if (this != &o) { reset(); ptr = o.ptr; n = o.n; o.ptr = nullptr; o.n = 0; }
+    return *this;
+  }
+  ~PoolBuf() { reset(); }
+  void reset() {
+    if (ptr) lt_pool_free(batch_pool(), ptr);
+    ptr = nullptr; n = 0;
+  }
+  void resize(uint64_t count) {
+    reset();
+    ptr = static_cast<float*>(lt_pool_alloc(batch_pool(), count * sizeof(float)));
+    n = ptr ? count : 0;
+  }
+  float* data() { return ptr; }
+  const float* data() const { return ptr; }
+  uint64_t size() const { return n; }
+};
+
 struct Batch {
-  std::vector<float> x, y;
+  PoolBuf x, y;
   uint64_t count = 0;
   uint64_t generation = 0;
   uint64_t next_index = 0;  // dataset position after this batch
@@ -58,6 +95,20 @@ struct Loader {
     }
   }
 
+  struct CopyJob {
+    const Loader* self;
+    Batch* out;
+    const uint64_t* idx;
+  };
+  static void copy_range(uint64_t begin, uint64_t end, void* ctx) {
+    const CopyJob& j = *static_cast<const CopyJob*>(ctx);
+    const Loader* d = j.self;
+    for (uint64_t i = begin; i < end; ++i) {
+      memcpy(j.out->x.data() + i * d->xs, d->x + j.idx[i] * d->xs, d->xs * sizeof(float));
+      memcpy(j.out->y.data() + i * d->ys, d->y + j.idx[i] * d->ys, d->ys * sizeof(float));
+    }
+  }
+
   void run() {
     std::unique_lock<std::mutex> lk(mu);
     while (!stop) {
@@ -81,10 +132,10 @@ struct Loader {
       Batch b;
       b.x.resize(cnt * xs);
       b.y.resize(cnt * ys);
-      for (uint64_t i = 0; i < cnt; ++i) {
-        memcpy(b.x.data() + i * xs, x + idx[i] * xs, xs * sizeof(float));
-        memcpy(b.y.data() + i * ys, y + idx[i] * ys, ys * sizeof(float));
-      }
+      // Sample rows are copied by the host thread pool once a batch is worth splitting (about 1 MB and up).
+      CopyJob job{this, &b, idx.data()};
+      const uint64_t floats_per_sample = xs + ys ? xs + ys : 1;
+      lt_parallel_for(reinterpret_cast<void*>(&Loader::copy_range), &job, cnt, std::max<uint64_t>(2, (1u << 18) / floats_per_sample));
       b.count = cnt;
       b.generation = gen;
       b.next_index = start + cnt;

@@ -156,6 +156,32 @@ int main(int argc, char** argv) {
     lt_dl_destroy(dl2);
     lt_dl_destroy(dl);
   }
+  // ---- data loader, batches large enough to be assembled on the thread pool out of pooled host blocks; two loaders at once
+  {
+    const uint64_t n = 3000, xs = 300, ys = 1, batch = 1024;
+    std::vector<float> x(n * xs), y(n * ys);
+    for (uint64_t i = 0; i < n; ++i) { y[i] = float(i); for (uint64_t k = 0; k < xs; ++k) x[i * xs + k] = float(i) + float(k) / 1024.f; }
+    std::atomic<int> bad{0};
+    auto consume = [&](uint64_t seed) {
+      void* dl = lt_dl_create(x.data(), y.data(), n, xs, ys, batch, 1, seed, 2);
+      std::vector<float> bx(batch * xs), by(batch * ys);
+      uint64_t count = 0, seen = 0;
+      for (int epoch = 0; epoch < 2; ++epoch) {
+        while (lt_dl_next(dl, bx.data(), by.data(), &count)) {
+          for (uint64_t i = 0; i < count; ++i)
+            if (bx[i * xs] != by[i] || bx[i * xs + xs - 1] != by[i] + float(xs - 1) / 1024.f) bad++;
+          seen += count;
+        }
+        lt_dl_reset(dl);
+      }
+      if (seen != 2 * n) bad++;
+      lt_dl_destroy(dl);
+    };
+    std::thread other(consume, 7);
+    consume(8);
+    other.join();
+    CHECK(bad.load() == 0);
+  }
   // ---- checkpoint: round trip, one flipped byte, truncation
   {
     const std::string path = dir + "/w.ltw";

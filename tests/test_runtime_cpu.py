@@ -109,6 +109,20 @@ def test_dataloader_epoch_covers_dataset_and_reshuffles():
     assert sorted(second) == list(range(100)) and second != seen
 
 
+def test_dataloader_large_batches_are_assembled_by_the_thread_pool():
+    """Batches above about 1 MB are copied sample by sample on the host thread pool; rows must land in order."""
+    n, w = 3000, 700
+    x = torch.arange(n, dtype=torch.float32)[:, None] + torch.arange(w, dtype=torch.float32)[None] / 1024
+    dl = lt.data.DataLoader(lt.data.TensorDataset(lt.Tensor(x), lt.Tensor(torch.arange(n, dtype=torch.float32))), 1024, True,
+                            lt.Device("cpu"), 2, seed=5)
+    rows = 0
+    for bx, by in dl:
+        bx, by = _unwrap(bx), _unwrap(by)
+        assert torch.equal(bx, x[by.long()])
+        rows += by.numel()
+    assert rows == n
+
+
 def test_dataloader_state_file_layout_and_deterministic_resume(tmp_path):
     dl = _loader()
     for _ in range(3):
