@@ -11,17 +11,18 @@
 
 namespace lt {
 
-template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
+// MMA_KIND: 0 = bf16 / fp16 operands (kind::f16), 2 = fp32 operands as tf32, 3 = int8; one instruction kind per kernel.
+template <int BLOCK_N, int A_MAJOR, int B_MAJOR, int MMA_KIND = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), NoDone());
+  gemm_body<BLOCK_N, A_MAJOR, B_MAJOR, MMA_KIND>(&tmA, &tmB, p, NoGate(), NoDone());
 }
 
-template <int BLOCK_N, int A_MAJOR, int B_MAJOR>
+template <int BLOCK_N, int A_MAJOR, int B_MAJOR, int MMA_KIND = 0>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
   static bool configured = false;
-  auto kern = gemm_bf16_kernel<BLOCK_N, A_MAJOR, B_MAJOR>;
+  auto kern = gemm_bf16_kernel<BLOCK_N, A_MAJOR, B_MAJOR, MMA_KIND>;
   if (!configured) {
     LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
@@ -31,16 +32,16 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return 0;
 }
 
-template <int A_MAJOR, int B_MAJOR>
+template <int A_MAJOR, int B_MAJOR, int MMA_KIND = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-  gemm_body_pair<A_MAJOR, B_MAJOR>(&tmA, &tmB, p, NoGate(), NoDone());
+  gemm_body_pair<A_MAJOR, B_MAJOR, MMA_KIND>(&tmA, &tmB, p, NoGate(), NoDone());
 }
 
-template <int A_MAJOR, int B_MAJOR>
+template <int A_MAJOR, int B_MAJOR, int MMA_KIND = 0>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t st) {
   static bool configured = false;
-  auto kern = gemm_bf16_pair_kernel<A_MAJOR, B_MAJOR>;
+  auto kern = gemm_bf16_pair_kernel<A_MAJOR, B_MAJOR, MMA_KIND>;
   if (!configured) {
     LT_RETURN_IF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
     configured = true;
@@ -191,6 +192,7 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
           q.sk_flags = w.flags;
         }
       }
+      if (kind == 2) return launch_gemm_pair<0, 0, 2>(tmA, tmB, q, 2 * pairs, st);   // tf32: both operands K-major
       const int key2 = (a_major ? 2 : 0) | (b_major ? 1 : 0);
       switch (key2) {
         case 0: return launch_gemm_pair<0, 0>(tmA, tmB, q, 2 * pairs, st);
@@ -228,6 +230,8 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
       p.sk_flags = w.flags;
     }
   }
+  if (kind == 2) return block_n == 256 ? launch_gemm<256, 0, 0, 2>(tmA, tmB, p, grid, st) : launch_gemm<128, 0, 0, 2>(tmA, tmB, p, grid, st);
+  if (kind == 3) return block_n == 256 ? launch_gemm<256, 0, 0, 3>(tmA, tmB, p, grid, st) : launch_gemm<128, 0, 0, 3>(tmA, tmB, p, grid, st);
   const int key = (block_n == 256 ? 4 : 0) | (a_major ? 2 : 0) | (b_major ? 1 : 0);
   switch (key) {
     case 0: return launch_gemm<128, 0, 0>(tmA, tmB, p, grid, st);

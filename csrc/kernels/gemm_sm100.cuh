@@ -264,7 +264,11 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
 // The body shared by all GEMM kernels. `gate(m_blk, n_blk, kb, status)` is called by the producer
 // before it loads k-block kb of a tile and returns false if a bounded wait ran out; `done(m_blk, n_blk)`
 // is called by one thread of each epilogue warp after the warp's rows of a tile are in global memory.
-template <int BLOCK_N, int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
+// MMA_KIND selects the instruction a kernel is built around: 0 = kind::f16 (bf16 and fp16 operands, told apart by the
+// format bits of the run-time instruction descriptor), 2 = kind::tf32, 3 = kind::i8.  It is a template parameter and
+// not a run-time branch on purpose: a kernel that contains tcgen05.mma instructions of more than one kind ran its
+// bf16 MMAs at half rate (measured: 1000 instead of 512 cycles per 256 x 256 x 64 block with no loads in flight).
+template <int BLOCK_N, int A_MAJOR, int B_MAJOR, int MMA_KIND = 0, class TileGate, class TileDone>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
                                           TileGate gate, TileDone done, int cta_first = 0) {
   // CTAs [0, cta_first) of the grid belong to another role of a fused kernel; the GEMM uses the rest.
@@ -355,9 +359,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = p.kind == 3 ? make_idesc_i8(kBlockM, BLOCK_N)
-                                         : make_idesc_f16(kBlockM, BLOCK_N, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
-      const bool tf32 = p.kind == 2, i8 = p.kind == 3;
+      const uint32_t idesc = MMA_KIND == 3 ? make_idesc_i8(kBlockM, BLOCK_N)
+                                           : make_idesc_f16(kBlockM, BLOCK_N, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -379,8 +382,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            if (tf32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
-            else if (i8) umma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            if constexpr (MMA_KIND == 2) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else if constexpr (MMA_KIND == 3) umma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));

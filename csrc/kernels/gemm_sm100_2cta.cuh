@@ -68,7 +68,7 @@ inline double pair_cost(int M, int N, int K, int sms, bool split_on) {
 // `gate(m_chunk, n_blk, kb, status)` and `done(m_chunk, n_blk)` are the hooks of gemm_body; m_chunk counts 128-row
 // blocks (the rows one CTA of the pair loads and writes), n_blk counts 256-column blocks.  CTAs [0, cta_first) of
 // the grid (an even number) belong to another role of a fused kernel.
-template <int A_MAJOR, int B_MAJOR, class TileGate, class TileDone>
+template <int A_MAJOR, int B_MAJOR, int MMA_KIND = 0, class TileGate, class TileDone>   // MMA_KIND: see gemm_body
 __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
                                                TileGate gate, TileDone done, int cta_first = 0,
                                                const ScatterMaps* scatter = nullptr) {
@@ -160,8 +160,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, p.kind == 0 ? 1 : (p.kind == 1 ? 0 : 2), A_MAJOR, B_MAJOR);
-      const bool tf32 = p.kind == 2;
+      const uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -183,7 +182,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
                                                   : make_smem_desc_sw128(a_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
-            if (tf32) umma_tf32_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            if constexpr (MMA_KIND == 2) umma_tf32_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs

@@ -1,6 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing with an L2 flush between iterations.
 
     python -m litetorch_b200.utils.microbench gemm [--out FILE]
+    python -m litetorch_b200.utils.microbench gemm8b       # one 8B layer's GEMMs, sustained, next to cuBLAS
     python -m litetorch_b200.utils.microbench fp8
     python -m litetorch_b200.utils.microbench attn
     python -m litetorch_b200.utils.microbench pointwise
@@ -109,6 +110,89 @@ def bench_gemm(out=None):
                "auto_no_tail_split_ms": round(ms_whole, 4), "tflops": round(fl / best[0] / 1e9, 1),
                "frac_of_%s_peak" % pk["src"]: round(fl / best[0] / 1e9 / pk["tflops"], 3),
                "cublas_ms": round(ms_ref, 4), "cublas_tflops": round(fl / ms_ref / 1e9, 1)}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    if out:
+        with open(out, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+    return rows
+
+
+def bench_gemm_sustained(out=None):
+    """The GEMMs of one Llama-3-8B layer (8192 tokens) timed the way they run inside a training step: each kernel
+    back to back for about a second, so that the figure is taken at the clocks the 1 kW power cap allows, next to
+    cuBLAS (torch.matmul) under the same load.  Operands are larger than L2 or nearly so; nothing is flushed."""
+    from ..ops import kernels as K
+    shapes = [
+        (8192, 6144, 4096, 0, 0, "qkv fwd"), (8192, 4096, 4096, 0, 0, "o fwd"), (8192, 28672, 4096, 0, 0, "gate_up fwd"),
+        (8192, 4096, 14336, 0, 0, "down fwd"), (8192, 4096, 28672, 0, 1, "gate_up dgrad"), (8192, 14336, 4096, 0, 1, "down dgrad"),
+        (8192, 4096, 6144, 0, 1, "qkv dgrad"), (28672, 4096, 8192, 1, 1, "gate_up wgrad"), (4096, 14336, 8192, 1, 1, "down wgrad"),
+        (6144, 4096, 8192, 1, 1, "qkv wgrad"),
+    ]
+
+    import threading
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        nv = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    except Exception:
+        pynvml = nv = None
+
+    def loop_ms(fn, seconds=1.2):
+        """(ms per call, median SM MHz, median board W) over a loop of about `seconds`; clocks and power are read-only
+        NVML queries made every 20 ms from a side thread once the loop has run for 0.3 s."""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+        n = max(10, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+        mhz, watts, stop = [], [], threading.Event()
+
+        def sample():
+            import time
+            time.sleep(0.3)
+            while not stop.is_set():
+                try:
+                    mhz.append(pynvml.nvmlDeviceGetClockInfo(nv, pynvml.NVML_CLOCK_SM))
+                    watts.append(pynvml.nvmlDeviceGetPowerUsage(nv) / 1000.0)
+                except Exception:
+                    return
+                time.sleep(0.02)
+
+        th = threading.Thread(target=sample, daemon=True) if nv is not None else None
+        if th:
+            th.start()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        stop.set()
+        if th:
+            th.join()
+        med = lambda v: sorted(v)[len(v) // 2] if v else None
+        return e0.elapsed_time(e1) / n, med(mhz), med(watts)
+
+    rows = []
+    for M, N, Kd, am, bm, tag in shapes:
+        a = torch.randn((M, Kd) if am == 0 else (Kd, M), device="cuda").bfloat16()
+        b = torch.randn((N, Kd) if bm == 0 else (Kd, N), device="cuda").bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        A = a if am == 0 else a.t()
+        B = b.t() if bm == 0 else b
+        fl = 2.0 * M * N * Kd
+        ms, mhz, w = loop_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_pair_mode(0)
+        ms1, mhz1, w1 = loop_ms(lambda: K.gemm(a, b, a_major=am, b_major=bm, out=c))
+        K.gemm_set_pair_mode(1)
+        ms_ref, mhz_ref, w_ref = loop_ms(lambda: torch.matmul(A, B, out=c))
+        K.check_status()
+        row = {"kernel": "gemm_bf16 sustained", "tag": tag, "M": M, "N": N, "K": Kd, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+               "sm_mhz": mhz, "watts": w, "one_cta_ms": round(ms1, 4), "one_cta_tflops": round(fl / ms1 / 1e9, 1), "one_cta_sm_mhz": mhz1,
+               "cublas_ms": round(ms_ref, 4), "cublas_tflops": round(fl / ms_ref / 1e9, 1), "cublas_sm_mhz": mhz_ref, "cublas_watts": w_ref,
+               "ratio_to_cublas": round(ms_ref / ms, 3)}
         rows.append(row)
         print(json.dumps(row), flush=True)
     if out:
@@ -228,4 +312,4 @@ def bench_pointwise(out=None):
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     out = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else None
-    {"gemm": bench_gemm, "fp8": bench_fp8, "attn": bench_attn, "pointwise": bench_pointwise}[what](out)
+    {"gemm": bench_gemm, "gemm8b": bench_gemm_sustained, "fp8": bench_fp8, "attn": bench_attn, "pointwise": bench_pointwise}[what](out)

@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_vs_cublas|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
                                                  rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
@@ -24,6 +24,11 @@ def main():
         b = torch.randn(11264, 2048, device=dev).bfloat16()
         c = torch.empty(8192, 11264, device=dev, dtype=torch.bfloat16)
         fn = lambda: K.gemm(a, b, out=c)
+    elif case == "gemm_vs_cublas":   # o-projection of the 8B model, once through this kernel and once through torch.matmul
+        a = torch.randn(8192, 4096, device=dev).bfloat16()
+        b = torch.randn(4096, 4096, device=dev).bfloat16()
+        c = torch.empty(8192, 4096, device=dev, dtype=torch.bfloat16)
+        fn = lambda: (K.gemm(a, b, out=c), torch.matmul(a, b.t(), out=c))
     elif case == "gemm_wgrad":    # down-projection weight gradient: 2048 x 5632 x 8192, both operands transposed
         a = torch.randn(8192, 2048, device=dev).bfloat16()
         b = torch.randn(8192, 5632, device=dev).bfloat16()
