@@ -311,6 +311,265 @@ paged_decode_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Grouped-query decode with the scores and the P V product on the warp-level tensor-core instruction.
+//
+// Same split of the work as paged_decode_gqa_kernel (one CTA of four warps per sequence, KV head and context split;
+// a warp streams chunks of 32 keys through its own shared-memory stages), but the tiles arrive as TMA tensor copies in
+// the 128-byte-swizzled layout, so that ldmatrix reads them without bank conflicts, and a chunk costs 16 ldmatrix.x4 and
+// 32 mma.sync (m16n8k16: the group's query heads padded to 16 rows, 8 keys or 8 output columns per instruction) instead
+// of one shared-memory pass over the whole query block per key.  The scores stay in registers: their accumulator
+// fragments are, after the softmax, exactly the A fragments of the P V product.  tcgen05 is not the tool here: its
+// smallest tile is 64 rows and the kernel is bound by the K / V stream, not by arithmetic.
+template <int D>
+struct PdMmaCfg {
+  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kTileBytes = 32 * D * 2;                           // 32 keys of K (or V); D = 128: two 4 KB halves of 64 columns
+  static constexpr int kWarpBytes = kStages * 2 * kTileBytes;
+  static constexpr int kOffBar = kPdWarps * kWarpBytes;
+  static constexpr int kSmemBytes = kOffBar + kPdWarps * kStages * 8 + 16 + 1024;   // + slack to align the tiles to 1024 bytes
+};
+constexpr int kPdMmaMaxG = 16;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// tmK / tmV: the caches seen as [num_blocks * Hkv * block_size rows, D] bf16, box 64 columns x min(block_size, 32) rows,
+// 128-byte swizzle.  block_size is a multiple of 8 and divides 32 or is a multiple of it.
+template <int D>
+__global__ void __launch_bounds__(kPdWarps * 32)
+paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_tables,
+                        const int* __restrict__ context_lens, float* __restrict__ part, int S, int Hq, int Hkv, int block_size,
+                        int max_blocks, int splits, float scale, int* status) {
+  using Cfg = PdMmaCfg<D>;
+  constexpr int ST = Cfg::kStages;
+  constexpr int KS = D / 16;     // k-steps of the score product
+  constexpr int NT = D / 8;      // 8-column blocks of the output
+  extern __shared__ uint8_t pd_raw[];
+  uint8_t* pd_smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pd_raw) + 1023) & ~uintptr_t(1023));
+  const int G = Hq / Hkv;
+  const int sp = blockIdx.x % splits;
+  const int hkv = (blockIdx.x / splits) % Hkv;
+  const int s = blockIdx.x / (splits * Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, qd = lane & 3;
+  uint8_t* my_tiles = pd_smem + warp * Cfg::kWarpBytes;
+  const uint32_t bar0 = smem_u32(pd_smem + Cfg::kOffBar) + warp * ST * 8;
+  __shared__ int abort_s, drain_s;
+  if (threadIdx.x == 0) { abort_s = 0; drain_s = 0; }
+  if (lane == 0) {
+    for (int st = 0; st < ST; ++st) mbar_init(bar0 + 8u * st, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  // A fragments of the query block: rows = heads of the group (g and g + 8), zero past G
+  uint32_t qa[KS][4];
+  {
+    const bool lo = g < G, hi = g + 8 < G;
+    const __nv_bfloat16* qlo = q + ((long long)s * Hq + hkv * G + (lo ? g : 0)) * D + qd * 2;
+    const __nv_bfloat16* qhi = q + ((long long)s * Hq + hkv * G + (hi ? g + 8 : 0)) * D + qd * 2;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      qa[kk][0] = lo ? *reinterpret_cast<const uint32_t*>(qlo + kk * 16) : 0u;
+      qa[kk][1] = hi ? *reinterpret_cast<const uint32_t*>(qhi + kk * 16) : 0u;
+      qa[kk][2] = lo ? *reinterpret_cast<const uint32_t*>(qlo + kk * 16 + 8) : 0u;
+      qa[kk][3] = hi ? *reinterpret_cast<const uint32_t*>(qhi + kk * 16 + 8) : 0u;
+    }
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_s;
+  const int ctx = context_lens[s];
+  const int per = ((ctx + splits - 1) / splits + 31) / 32 * 32;      // whole 32-key chunks per split
+  const int t0 = sp * per, t1 = min(ctx, t0 + per);
+  const int* bt = block_tables + (long long)s * max_blocks;
+  const int n_chunks = t1 > t0 ? (t1 - t0 + 31) / 32 : 0;
+  const int my_n = n_chunks > warp ? (n_chunks - warp + kPdWarps - 1) / kPdWarps : 0;   // chunks warp, warp + 4, ...
+  const int run = block_size < 32 ? block_size : 32;                 // rows per tensor copy
+
+  auto request = [&](int i) {
+    const int c0 = t0 + (warp + i * kPdWarps) * 32;
+    const uint32_t bar = bar0 + 8u * (i % ST);
+    uint8_t* kt = my_tiles + (i % ST) * 2 * Cfg::kTileBytes;
+    uint8_t* vt = kt + Cfg::kTileBytes;
+    const int last_row = ((t1 - 1) / block_size + 1) * block_size;   // end of the last block holding a live key
+    const int r_end = min(c0 + 32, last_row);
+    mbar_expect_tx(bar, uint32_t(2 * (r_end - c0) * D * 2));
+    for (int r = c0; r < r_end; r += run) {
+      const int blk = bt[r / block_size];
+      const int row = (blk * Hkv + hkv) * block_size + r % block_size;
+#pragma unroll
+      for (int h = 0; h < D / 64; ++h) {
+        tma_load_2d(smem_u32(kt + h * 4096 + (r - c0) * 128), &tmK, bar, h * 64, row);
+        tma_load_2d(smem_u32(vt + h * 4096 + (r - c0) * 128), &tmV, bar, h * 64, row);
+      }
+    }
+  };
+
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;   // l: this lane's share of the row sums
+  float oacc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) oacc[nt][r] = 0.f;
+
+  if (lane == 0)
+    for (int i = 0; i < ST - 1 && i < my_n; ++i) request(i);
+  bool ok = true;
+  const int lj = lane >> 3, lr = lane & 7;   // ldmatrix: this lane addresses row lr of matrix lj
+  for (int i = 0; i < my_n; ++i) {
+    if (lane == 0 && i + ST - 1 < my_n) request(i + ST - 1);      // its stage was consumed in iteration i - 1
+    ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8u * (i % ST), uint32_t(i / ST) & 1u, abort_flag, status, kStatusTimeoutFull));
+    if (!ok) {
+      // a copy never arrived: give the other requested stages one more bounded wait each, so that no copy of this
+      // warp is still writing shared memory when the CTA leaves, then drop out (the result of the CTA is discarded)
+      for (int r = i + 1; r < my_n && r < i + ST; ++r)
+        mbar_wait(bar0 + 8u * (r % ST), uint32_t(r / ST) & 1u, &drain_s, status, kStatusTimeoutFull);
+      break;
+    }
+    const int c0 = t0 + (warp + i * kPdWarps) * 32;
+    uint8_t* kt = my_tiles + (i % ST) * 2 * Cfg::kTileBytes;
+    uint8_t* vt = kt + Cfg::kTileBytes;
+    const uint32_t kt_addr = smem_u32(kt), vt_addr = smem_u32(vt);
+    const int nk = min(32, t1 - c0);
+    if (nk < 32) {
+      // rows past the context (the tail of the last block, or never copied) may hold anything: zero them in V so that
+      // their zero probabilities do not meet a NaN
+      if (lane >= nk) {
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          uint4* row = reinterpret_cast<uint4*>(vt + h * 4096 + lane * 128);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) row[u] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      __syncwarp();
+    }
+    // ---- S = Q K^T: four blocks of 8 keys
+    float sacc[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) sacc[t][r] = 0.f;
+      const int key = t * 8 + lr;
+#pragma unroll
+      for (int kk2 = 0; kk2 < KS / 2; ++kk2) {
+        const int u = kk2 * 4 + lj;                                 // 16-byte unit of the row: columns 8 u .. 8 u + 7
+        uint32_t b00, b01, b10, b11;
+        ldsm_x4(kt_addr + (u >> 3) * 4096 + key * 128 + (((u & 7) ^ (key & 7)) << 4), b00, b01, b10, b11);
+        mma_16816(sacc[t], qa[2 * kk2], b00, b01);
+        mma_16816(sacc[t], qa[2 * kk2 + 1], b10, b11);
+      }
+    }
+    // ---- online softmax: this lane holds columns t * 8 + qd * 2 + {0, 1} of rows g (registers 0, 1) and g + 8 (2, 3)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool live = t * 8 + qd * 2 + e < nk;
+        sacc[t][e] = live ? sacc[t][e] * scale : -INFINITY;
+        sacc[t][2 + e] = live ? sacc[t][2 + e] * scale : -INFINITY;
+        mx_lo = fmaxf(mx_lo, sacc[t][e]);
+        mx_hi = fmaxf(mx_hi, sacc[t][2 + e]);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float nm_lo = fmaxf(m_lo, mx_lo), nm_hi = fmaxf(m_hi, mx_hi);   // finite: every chunk has a live key
+    const float a_lo = (m_lo == -INFINITY) ? 0.f : __expf(m_lo - nm_lo);
+    const float a_hi = (m_hi == -INFINITY) ? 0.f : __expf(m_hi - nm_hi);
+    m_lo = nm_lo; m_hi = nm_hi;
+    float ps_lo = 0.f, ps_hi = 0.f;
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float p0 = __expf(sacc[t][0] - nm_lo), p1 = __expf(sacc[t][1] - nm_lo);
+      const float p2 = __expf(sacc[t][2] - nm_hi), p3 = __expf(sacc[t][3] - nm_hi);
+      ps_lo += p0 + p1;
+      ps_hi += p2 + p3;
+      pa[t >> 1][(t & 1) * 2] = pack_bf16x2(p0, p1);         // keys 16 ks + 8 (t & 1) + ..: registers 0 / 2 rows g, 1 / 3 rows g + 8
+      pa[t >> 1][(t & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+    }
+    l_lo = l_lo * a_lo + ps_lo;
+    l_hi = l_hi * a_hi + ps_hi;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      oacc[nt][0] *= a_lo; oacc[nt][1] *= a_lo;
+      oacc[nt][2] *= a_hi; oacc[nt][3] *= a_hi;
+    }
+    // ---- O += P V: two steps of 16 keys, transposed loads of V
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const int key = ks * 16 + (lj & 1) * 8 + lr;
+#pragma unroll
+      for (int nt2 = 0; nt2 < NT / 2; ++nt2) {
+        const int u = nt2 * 2 + (lj >> 1);
+        uint32_t b0a, b1a, b0b, b1b;
+        ldsm_x4_trans(vt_addr + (u >> 3) * 4096 + key * 128 + (((u & 7) ^ (key & 7)) << 4), b0a, b1a, b0b, b1b);
+        mma_16816(oacc[2 * nt2], pa[ks], b0a, b1a);
+        mma_16816(oacc[2 * nt2 + 1], pa[ks], b0b, b1b);
+      }
+    }
+    __syncwarp();            // every lane is done with this stage before lane 0 requests into it again
+  }
+  // ---- merge the four warps (the tile area is free now: every requested copy has been waited for), write the partial result
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  __syncthreads();
+  float* red_m = reinterpret_cast<float*>(pd_smem);                 // [warps][16]
+  float* red_l = red_m + kPdWarps * kPdMmaMaxG;                      // [warps][16]
+  float* red_o = red_l + kPdWarps * kPdMmaMaxG;                      // [warps][16][D]
+  if (qd == 0) {
+    red_m[warp * kPdMmaMaxG + g] = ok ? m_lo : -INFINITY;
+    red_l[warp * kPdMmaMaxG + g] = ok ? l_lo : 0.f;
+    red_m[warp * kPdMmaMaxG + g + 8] = ok ? m_hi : -INFINITY;
+    red_l[warp * kPdMmaMaxG + g + 8] = ok ? l_hi : 0.f;
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    float* lo = red_o + (warp * kPdMmaMaxG + g) * D + nt * 8 + qd * 2;
+    float* hi = red_o + (warp * kPdMmaMaxG + g + 8) * D + nt * 8 + qd * 2;
+    *reinterpret_cast<float2*>(lo) = make_float2(oacc[nt][0], oacc[nt][1]);
+    *reinterpret_cast<float2*>(hi) = make_float2(oacc[nt][2], oacc[nt][3]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int gg = i / D, d = i % D;
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) gm = fmaxf(gm, red_m[w * kPdMmaMaxG + gg]);
+    float lsum = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) {
+      const float mw = red_m[w * kPdMmaMaxG + gg];
+      if (mw == -INFINITY) continue;
+      const float a = __expf(mw - gm);
+      lsum += red_l[w * kPdMmaMaxG + gg] * a;
+      o += red_o[(w * kPdMmaMaxG + gg) * D + d] * a;
+    }
+    float* out = part + (((long long)s * Hq + hkv * G + gg) * splits + sp) * (D + 2);
+    out[d] = lsum > 0.f ? o / lsum : 0.f;
+    if (d == 0) { out[D] = gm; out[D + 1] = lsum; }
+  }
+}
+
 template <int D>
 __global__ void paged_decode_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ o, int rows, int splits) {
   const int row = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
@@ -365,10 +624,11 @@ extern "C" {
 
 // q: [S, Hq, D] bf16; caches [num_blocks, Hkv, block_size, D] bf16 (kv_fp8 = 0) or e4m3 (kv_fp8 = 1, with the
 // dequantisation scales k_scale / v_scale); block_tables [S, max_blocks] int32; context_lens [S] int32;
-// part: scratch [S, Hq, splits, D + 2] fp32; o: [S, Hq, D] bf16.
+// part: scratch [S, Hq, splits, D + 2] fp32; o: [S, Hq, D] bf16.  num_blocks: blocks in the caches (0: not known, which
+// rules out the tensor-copy kernel).
 int lt_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_tables, const int* context_lens,
-                    float* part, void* o, int S, int Hq, int Hkv, int D, int block_size, int max_blocks, int splits,
-                    float scale, int kv_fp8, float k_scale, float v_scale, void* stream) {
+                    float* part, void* o, int S, int Hq, int Hkv, int D, int block_size, int max_blocks, int num_blocks,
+                    int splits, float scale, int kv_fp8, float k_scale, float v_scale, void* stream) {
   using namespace lt;
   if ((D != 64 && D != 128) || Hq % Hkv != 0 || splits < 1) return -int(kStatusBadArgument);
   if (S == 0) return 0;
@@ -382,7 +642,27 @@ int lt_paged_decode(const void* q, const void* k_cache, const void* v_cache, con
                                                           block_size, max_blocks, splits, scale, k_scale, v_scale)
   const int G = Hq / Hkv;
   const bool bs_ok = block_size > 0 && (32 % block_size == 0 || block_size % 32 == 0);
-  if (!kv_fp8 && G <= kPdMaxG && bs_ok && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
+  if (!kv_fp8 && G <= kPdMmaMaxG && bs_ok && block_size % 8 == 0 && num_blocks > 0 && aligned &&
+      (long long)num_blocks * Hkv * block_size < (1ll << 31)) {
+    // bf16 caches in blocks of 8 keys or more: tiles by TMA in the swizzled layout, scores and P V on mma.sync
+    const int ctas = S * Hkv * splits;
+    static bool configured_mma = false;
+    if (!configured_mma) {
+      LT_RETURN_IF_CUDA(cudaFuncSetAttribute(paged_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PdMmaCfg<64>::kSmemBytes));
+      LT_RETURN_IF_CUDA(cudaFuncSetAttribute(paged_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PdMmaCfg<128>::kSmemBytes));
+      configured_mma = true;
+    }
+    const uint64_t rows = uint64_t(num_blocks) * Hkv * block_size;
+    const uint32_t run = block_size < 32 ? block_size : 32;
+    CUtensorMap tmK, tmV;
+    int r = encode_tmap_2d(&tmK, k_cache, 2, D, rows, uint64_t(D) * 2, 64, run, 1);
+    if (r == 0) r = encode_tmap_2d(&tmV, v_cache, 2, D, rows, uint64_t(D) * 2, 64, run, 1);
+    if (r) return r > 0 ? 1000 + r : r;
+    int* status = device_status_word();
+    if (D == 64) paged_decode_mma_kernel<64><<<ctas, kPdWarps * 32, PdMmaCfg<64>::kSmemBytes, st>>>(tmK, tmV, Q, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale, status);
+    else paged_decode_mma_kernel<128><<<ctas, kPdWarps * 32, PdMmaCfg<128>::kSmemBytes, st>>>(tmK, tmV, Q, block_tables, context_lens, part, S, Hq, Hkv, block_size, max_blocks, splits, scale, status);
+  } else if (!kv_fp8 && G <= kPdMaxG && bs_ok && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0) {
     // bf16 caches: every K / V byte is read once for the whole group of query heads, through a shared-memory pipeline
     const int ctas = S * Hkv * splits;
     auto KC = static_cast<const __nv_bfloat16*>(k_cache);

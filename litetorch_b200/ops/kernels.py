@@ -22,6 +22,7 @@ _SIGS = {
     "lt_gemm_bf16": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _i, _i, _vp],
     "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
     "lt_gemv_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
+    "lt_gemm_skinny_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
     "lt_quant_int8_tensor": [_vp, _i, _vp, _ll, _f, _vp],
     "lt_quant_int8_rows": [_vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_gemm_set_tail_split": [_i],
@@ -72,7 +73,7 @@ _SIGS = {
     "lt_signal_barrier": [_vp, _vp, _i, ctypes.c_uint, _i, _i, _vp],
     "lt_gather_shards": [_vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_gemm_num_tiles": [_i, _i, _i],
-    "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
+    "lt_paged_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp],
     "lt_kv_append": [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp],
     "lt_gemm_rs_bf16": [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp, ctypes.c_uint, _i, _i, _i, _vp, _ll, _vp, _vp, _ll, _vp],
     "lt_flash_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp],
@@ -188,6 +189,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
         rc = _fn("lt_gemv_bf16")(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), y.data_ptr(), y.stride(0), _p(residual),
                                  residual.stride(0) if residual is not None else 0, M, N, Kd, _stream())
         _check(rc, "lt_gemv_bf16")
+        return y
+    if (a_major == 0 and b_major == 0 and 8 < a.shape[0] <= 128 and out_dtype == torch.bfloat16 and bias is None and act == 0
+            and alpha == 1.0 and not accumulate and a.shape[1] % 32 == 0 and b.shape[0] % 8 == 0 and a.stride(0) % 8 == 0
+            and b.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0 and a.shape[1] == b.shape[1]
+            and (out is None or (out.dtype == torch.bfloat16 and out.shape == (a.shape[0], b.shape[0]) and out.stride(1) == 1
+                                 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0))
+            and (residual is None or (residual.dtype == torch.bfloat16 and residual.shape == (a.shape[0], b.shape[0])
+                                      and residual.stride(1) == 1 and residual.stride(0) % 2 == 0 and residual.data_ptr() % 4 == 0))):
+        # 9 to 128 rows (decode with a batch of sequences): the weight-streaming tensor-core kernel
+        M, Kd = a.shape
+        N = b.shape[0]
+        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        rc = _fn("lt_gemm_skinny_bf16")(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), y.data_ptr(), y.stride(0), _p(residual),
+                                        residual.stride(0) if residual is not None else 0, M, N, Kd, _stream())
+        _check(rc, "lt_gemm_skinny_bf16")
         return y
     if a_major == 0:
         M, K = a.shape
@@ -627,7 +643,8 @@ def paged_decode(q, k_cache, v_cache, block_tables, context_lens, block_size: in
     o = torch.empty_like(q)
     rc = _fn("lt_paged_decode")(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                                 context_lens.data_ptr(), part.data_ptr(), o.data_ptr(), S, H, Hkv, D, block_size,
-                                block_tables.shape[1], splits, float(scale), 1 if k_cache.dtype == torch.float8_e4m3fn else 0,
+                                block_tables.shape[1], k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0, splits,
+                                float(scale), 1 if k_cache.dtype == torch.float8_e4m3fn else 0,
                                 float(k_scale), float(v_scale), _stream())
     _check(rc, "lt_paged_decode")
     return o

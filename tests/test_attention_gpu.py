@@ -138,3 +138,47 @@ def test_flash_at_the_benchmark_shapes(B, T, Hq, Hkv, D):
             dk_r += ds.t() @ qf[rr]
     assert _err(dv[b, :, hk], dv_r) < 2e-2
     assert _err(dk[b, :, hk], dk_r) < 2e-2
+
+
+@pytest.mark.parametrize("D,H,Hkv,bs", [(64, 32, 4, 16), (64, 8, 8, 8), (64, 16, 1, 32), (128, 32, 8, 16), (128, 12, 3, 64), (64, 6, 2, 16)])
+def test_paged_decode_tensor_core_kernel_against_fp32(D, H, Hkv, bs):
+    """Decode attention over a paged bf16 cache (tiles by TMA in the swizzled layout, scores and P V on mma.sync): group sizes 1 to 16,
+    blocks of 8 to 64 keys, contexts that end inside a block and inside a 32-key chunk, scattered blocks, 1 to 8 context splits."""
+    from litetorch_b200.ops import kernels as K
+    torch.manual_seed(D + H + bs)
+    ctx = [1, 31, 32, 33, 200, 515, 1024, 7]
+    S = len(ctx)
+    nblk = sum((c + bs - 1) // bs for c in ctx) + 3
+    # poisoned cache: slots no context owns hold NaN, as uninitialised memory might
+    kc = torch.full((nblk, Hkv, bs, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    vc = torch.full((nblk, Hkv, bs, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(nblk).tolist()
+    maxb = max((c + bs - 1) // bs for c in ctx)
+    bt = torch.zeros(S, maxb, dtype=torch.int32)
+    ks, vs, used = [], [], 0
+    for s_, c in enumerate(ctx):
+        nb = (c + bs - 1) // bs
+        blocks = perm[used:used + nb]
+        used += nb
+        bt[s_, :nb] = torch.tensor(blocks)
+        k = torch.randn(c, Hkv, D, device="cuda").bfloat16()
+        v = torch.randn(c, Hkv, D, device="cuda").bfloat16()
+        for t in range(0, c, bs):
+            n = min(bs, c - t)
+            kc[blocks[t // bs], :, :n] = k[t:t + n].permute(1, 0, 2)
+            vc[blocks[t // bs], :, :n] = v[t:t + n].permute(1, 0, 2)
+        ks.append(k)
+        vs.append(v)
+    q = torch.randn(S, H, D, device="cuda").bfloat16()
+    cl = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    for splits in (1, 3, 8):
+        out = K.paged_decode(q, kc, vc, bt.cuda(), cl, bs, splits, D ** -0.5)
+        K.check_status()
+        assert torch.isfinite(out.float()).all()
+        for s_, c in enumerate(ctx):
+            kk = ks[s_].float().permute(1, 0, 2).repeat_interleave(H // Hkv, 0)
+            vv = vs[s_].float().permute(1, 0, 2).repeat_interleave(H // Hkv, 0)
+            p = torch.softmax(torch.einsum("hd,htd->ht", q[s_].float(), kk) * D ** -0.5, -1)
+            ref = torch.einsum("ht,htd->hd", p, vv)
+            err = float((out[s_].float() - ref).norm() / ref.norm())
+            assert err < 1.5e-2, (s_, c, splits, err)

@@ -222,3 +222,28 @@ def test_int8_gemm_and_quantisers_are_exact():
     yr = torch.clamp(torch.round(x / 0.03), -127, 127) @ torch.clamp(torch.round(w / 0.02), -127, 127) * (0.03 * 0.02)
     assert float((y - yr).abs().max()) < 1e-3
     KK.check_status()
+
+
+@pytest.mark.parametrize("M", [9, 16, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,Kd", [(2048, 2048), (2560, 2048), (11264, 2048), (2048, 5632), (1000, 64), (32000, 2048), (40, 4096)])
+def test_skinny_gemm_against_fp32(M, N, Kd):
+    """9 to 128 rows go to the weight-streaming mma.sync kernel (K split over the warps of a CTA and, for narrow outputs, over
+    CTAs whose partial sums the last one adds in a fixed order): against fp32, with and without a residual, twice for bit equality."""
+    from litetorch_b200.ops import kernels as KK
+    torch.manual_seed(M + N)
+    a = torch.randn(M, Kd, device="cuda").bfloat16()
+    b = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    y = KK.gemm(a, b)
+    y2 = KK.gemm(a, b)
+    KK.check_status()
+    assert y.shape == (M, N) and torch.equal(y, y2)
+    assert float((y.float() - ref).norm() / ref.norm()) < 6e-3
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    KK.gemm(a, b, out=out, residual=res)
+    assert float((out.float() - (ref + res.float())).norm() / (ref + res.float()).norm()) < 6e-3
+    # rows of a wider buffer (strided operands)
+    wide = torch.randn(M, Kd + 64, device="cuda").bfloat16()
+    y3 = KK.gemm(wide[:, :Kd], b)
+    assert float((y3.float() - wide[:, :Kd].float() @ b.float().t()).norm() / ref.norm()) < 6e-3
