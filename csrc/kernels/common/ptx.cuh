@@ -261,6 +261,26 @@ __device__ __forceinline__ void umma_tf32_ss_pair(uint32_t tmem_d, uint64_t ades
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
       : "memory");
 }
+// kind::f8f6f4 with e4m3 operands in shared memory (format code 0 for both), fp32 accumulators; K = 32 elements = 32 bytes
+// per instruction, so descriptors advance by the same 32 bytes as the 16-bit kinds.
+__device__ __forceinline__ void umma_e4m3_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_e4m3_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  const uint32_t z = 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
 // When every MMA issued so far has executed, arrive on the barrier at this offset in each CTA of `cta_mask`.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -281,6 +301,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
 __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int fmt, int a_major, int b_major) {
   return (1u << 4) | (uint32_t(fmt) << 7) | (uint32_t(fmt) << 10) | (uint32_t(a_major) << 15) |
          (uint32_t(b_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Instruction descriptor for kind::f8f6f4 with e4m3 operands (format code 0), fp32 accumulation, K-major only.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
+  return (1u << 4) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
 // Instruction descriptor for kind::i8: signed 8-bit operands (format code 1), s32 accumulation (code 2), K-major only.

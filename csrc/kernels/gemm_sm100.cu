@@ -115,7 +115,8 @@ void lt_gemm_set_tail_split(int enable) { lt::g_split_enabled.store(enable ? 1 :
 // Returns 0, a cudaError_t, or 1000+/2000+ CUresult when a tensor map could not be encoded.
 static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
-                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream);
+                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream,
+                       const float* a_scale = nullptr, const float* b_scale = nullptr);
 
 int lt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                  long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
@@ -149,9 +150,25 @@ int lt_gemm_typed(int kind, const void* A, const void* B, void* C, int M, int N,
                      alpha, 0, 0, stream);
 }
 
+// C = epilogue((A[M, K] @ B[N, K]^T) * a_scale[row] * b_scale[column]) for e4m3 operands, both K-major, on tcgen05
+// kind::f8f6f4 (twice the bf16 MMA rate): the whole K extent accumulates in tensor memory and the scales are applied
+// once in the epilogue, so the kernel is the bf16 CTA-pair kernel with another instruction.  Scales per row of the
+// activations and per row of the weight (its output channel) are what per-token / per-channel fp8 training recipes use;
+// the 1x128 / 128x128 block-scaled variant (gemm_fp8_sm100.cu) pays a tensor-memory round trip per 128-deep K block
+// instead.  K a multiple of 16, pitches in elements (bytes).  C bf16 or fp32; bias / residual bf16.
+int lt_gemm_e4m3(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                 int out_fp32, const float* a_scale, const float* b_scale, const void* bias, const void* residual,
+                 long long ldr, int act, float alpha, void* stream) {
+  if ((K & 15) || (lda & 15) || (ldb & 15)) return -int(lt::kStatusBadArgument);
+  // e4m3 rows seen as rows of 2-byte units of half the extent (the copy is byte-identical)
+  return gemm_launch(4, A, B, C, M, N, K / 2, lda / 2, ldb / 2, ldc, 0, 0, out_fp32, bias, residual, ldr, act, 0, alpha, 0, 0, stream,
+                     a_scale, b_scale);
+}
+
 static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int a_major, int b_major, int out_fp32, const void* bias, const void* residual,
-                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream) {
+                       long long ldr, int act, int accumulate, float alpha, int block_n, int max_ctas, void* stream,
+                       const float* a_scale, const float* b_scale) {
   using namespace lt;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda * 2) % 16 != 0 || (ldb * 2) % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) ||
@@ -172,6 +189,7 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
       q.bias = static_cast<const __nv_bfloat16*>(bias);
       q.residual = static_cast<const __nv_bfloat16*>(residual);
       q.ldr = ldr; q.act = act; q.accumulate = accumulate; q.alpha = alpha;
+      q.a_scale = a_scale; q.b_scale = b_scale;
       q.status = device_status_word();
       fill_tiles(q, kPairBlockN);
       fill_pair_tiles(q);
@@ -193,6 +211,7 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
         }
       }
       if (kind == 2) return launch_gemm_pair<0, 0, 2>(tmA, tmB, q, 2 * pairs, st);   // tf32: both operands K-major
+      if (kind == 4) return launch_gemm_pair<0, 0, 4>(tmA, tmB, q, 2 * pairs, st);   // e4m3: both operands K-major
       const int key2 = (a_major ? 2 : 0) | (b_major ? 1 : 0);
       switch (key2) {
         case 0: return launch_gemm_pair<0, 0>(tmA, tmB, q, 2 * pairs, st);
@@ -210,6 +229,7 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr; p.act = act; p.accumulate = accumulate; p.alpha = alpha;
+  p.a_scale = a_scale; p.b_scale = b_scale;
   p.status = device_status_word();
   fill_tiles(p, block_n);
   CUtensorMap tmA, tmB;
@@ -232,6 +252,7 @@ static int gemm_launch(int kind, const void* A, const void* B, void* C, int M, i
   }
   if (kind == 2) return block_n == 256 ? launch_gemm<256, 0, 0, 2>(tmA, tmB, p, grid, st) : launch_gemm<128, 0, 0, 2>(tmA, tmB, p, grid, st);
   if (kind == 3) return block_n == 256 ? launch_gemm<256, 0, 0, 3>(tmA, tmB, p, grid, st) : launch_gemm<128, 0, 0, 3>(tmA, tmB, p, grid, st);
+  if (kind == 4) return block_n == 256 ? launch_gemm<256, 0, 0, 4>(tmA, tmB, p, grid, st) : launch_gemm<128, 0, 0, 4>(tmA, tmB, p, grid, st);
   const int key = (block_n == 256 ? 4 : 0) | (a_major ? 2 : 0) | (b_major ? 1 : 0);
   switch (key) {
     case 0: return launch_gemm<128, 0, 0>(tmA, tmB, p, grid, st);

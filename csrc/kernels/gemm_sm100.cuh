@@ -29,7 +29,8 @@ constexpr int kGemmThreads = 192;
 
 struct GemmParams {
   // Operand element kind: 0 = bf16, 1 = fp16 (both kind::f16), 2 = fp32 used as tf32 (kind::tf32), 3 = signed int8
-  // (kind::i8, 32-bit integer accumulators that the epilogue converts to float; one-CTA kernel only).  For tf32 / int8 the
+  // (kind::i8, 32-bit integer accumulators that the epilogue converts to float; one-CTA kernel only), 4 = e4m3 (kind::f8f6f4,
+  // scaled per row of A and per row of B through a_scale / b_scale).  For tf32 / int8 / e4m3 the
   // host describes the operands to TMA as 2-byte elements of twice the K extent (the copy is byte-identical) and
   // K below counts those 2-byte units, so the tiling, the 128-byte swizzled stage rows and the 32-byte descriptor
   // step per MMA are the same for every kind; only the instruction and the format bits of its descriptor differ.
@@ -73,6 +74,10 @@ struct GemmParams {
   int dp_tiles, sk_tiles, sk_split;
   float* sk_ws;          // [sk_tiles][sk_split - 1][BLOCK_N / 32][8][128 rows][4]
   unsigned* sk_flags;    // [sk_tiles][4], zero between launches
+  // Dequantisation of 8-bit operands, applied to the accumulator before bias / residual: row r times a_scale[r], column c
+  // times b_scale[c] (fp32, nullptr: 1).
+  const float* a_scale;
+  const float* b_scale;
 };
 
 struct WorkItem {
@@ -150,6 +155,24 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
   for (int j = 0; j < 32; ++j) v[j] = (p.kind == 3 ? float(int(r[j])) : __uint_as_float(r[j])) * p.alpha;
   const bool full = (col0 + 32 <= p.N);
   const int ncols = full ? 32 : (p.N - col0);
+  if (p.a_scale) {
+    const float as = __ldg(p.a_scale + row);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= as;
+  }
+  if (p.b_scale) {
+    if (full && (reinterpret_cast<uintptr_t>(p.b_scale) & 15) == 0) {
+      const float4* b4 = reinterpret_cast<const float4*>(p.b_scale + col0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 f = __ldg(b4 + q);
+        v[q * 4 + 0] *= f.x; v[q * 4 + 1] *= f.y; v[q * 4 + 2] *= f.z; v[q * 4 + 3] *= f.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < ncols) v[j] *= __ldg(p.b_scale + col0 + j);
+    }
+  }
   if (p.bias) {
     if (full) {
       const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
@@ -265,7 +288,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, int ro
 // before it loads k-block kb of a tile and returns false if a bounded wait ran out; `done(m_blk, n_blk)`
 // is called by one thread of each epilogue warp after the warp's rows of a tile are in global memory.
 // MMA_KIND selects the instruction a kernel is built around: 0 = kind::f16 (bf16 and fp16 operands, told apart by the
-// format bits of the run-time instruction descriptor), 2 = kind::tf32, 3 = kind::i8.  It is a template parameter and
+// format bits of the run-time instruction descriptor), 2 = kind::tf32, 3 = kind::i8, 4 = kind::f8f6f4 with e4m3 operands.  It is a template parameter and
 // not a run-time branch on purpose: a kernel that contains tcgen05.mma instructions of more than one kind ran its
 // bf16 MMAs at half rate (measured: 1000 instead of 512 cycles per 256 x 256 x 64 block with no loads in flight).
 template <int BLOCK_N, int A_MAJOR, int B_MAJOR, int MMA_KIND = 0, class TileGate, class TileDone>
@@ -360,7 +383,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = MMA_KIND == 3 ? make_idesc_i8(kBlockM, BLOCK_N)
-                                           : make_idesc_f16(kBlockM, BLOCK_N, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
+                             : MMA_KIND == 4 ? make_idesc_e4m3(kBlockM, BLOCK_N)
+                                             : make_idesc_f16(kBlockM, BLOCK_N, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -384,6 +408,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA, const CUtensor
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             if constexpr (MMA_KIND == 2) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else if constexpr (MMA_KIND == 3) umma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else if constexpr (MMA_KIND == 4) umma_e4m3_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));

@@ -160,7 +160,8 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = make_idesc_f16(kPairBlockM, kPairBlockN, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
+      const uint32_t idesc = MMA_KIND == 4 ? make_idesc_e4m3(kPairBlockM, kPairBlockN)
+                                           : make_idesc_f16(kPairBlockM, kPairBlockN, MMA_KIND == 2 ? 2 : (p.kind == 1 ? 0 : 1), A_MAJOR, B_MAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -183,6 +184,7 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
             const uint64_t bdesc = (B_MAJOR == 0) ? make_smem_desc_sw128(b_addr + k * (kUmmaK * 2), 16, 1024)
                                                   : make_smem_desc_sw128(b_addr + k * (kUmmaK * 128), 64 * kBlockK * 2, 1024);
             if constexpr (MMA_KIND == 2) umma_tf32_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            else if constexpr (MMA_KIND == 4) umma_e4m3_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
             else umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
@@ -323,23 +325,31 @@ __device__ __forceinline__ void gemm_body_pair(const CUtensorMap* tmA, const CUt
         }
       };
       if (w.split == 0) load_parts(0);
+      auto add_parts = [&](uint32_t (&r)[32]) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + pre[q].x);
+          r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + pre[q].y);
+          r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + pre[q].z);
+          r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + pre[q].w);
+        }
+      };
+      // two 32-column chunks per step: both tensor-memory loads are in flight before the first is consumed
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
+      for (int c = 0; c < kChunks; c += 2) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(t_addr + c * 32, r0);
+        tmem_ld_32x32(t_addr + (c + 1) * 32, r1);
         tmem_ld_wait();
         if (w.split == 0) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + pre[q].x);
-            r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + pre[q].y);
-            r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + pre[q].z);
-            r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + pre[q].w);
-          }
-          if (c + 1 < kChunks) load_parts(c + 1);
+          add_parts(r0);
+          load_parts(c + 1);
+          add_parts(r1);
+          if (c + 2 < kChunks) load_parts(c + 2);
         }
         const int col0 = n_blk * kPairBlockN + c * 32;
-        if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r);
+        if (row < p.M && col0 < p.N) epilogue_store_chunk(p, row, col0, r0);
+        if (row < p.M && col0 + 32 < p.N) epilogue_store_chunk(p, row, col0 + 32, r1);
       }
       done.fence();
       tc_fence_before();

@@ -14,6 +14,7 @@
 //     elementwise/elementwise_ops.cu:133-179, 432-502).
 #include "common/host.h"
 #include "common/ptx.cuh"
+#include <cuda_fp8.h>
 
 namespace lt {
 
@@ -633,7 +634,56 @@ __global__ void quant_int8_rows_kernel(const void* __restrict__ x, int is_bf16, 
 }
 }  // namespace lt
 
+namespace lt {
+// Per-row e4m3 quantiser for the row-scaled fp8 GEMM (lt_gemm_e4m3): scale[r] = absmax(row r) / 448 (1 for an all-zero row),
+// q = x / scale rounded to e4m3 with saturation.  A warp per row, 16 bytes per lane and step; cols a multiple of 8.
+__global__ void quant_e4m3_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_fp8_e4m3* __restrict__ q, long long ldq,
+                                       float* __restrict__ scale, int rows, int cols) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (long long)row * ldx;
+  float am = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack_bf16x2(w[i]);
+      am = fmaxf(am, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  const float sc = am > 0.f ? am / 448.f : 1.f;
+  if (lane == 0) scale[row] = sc;
+  const float inv = 1.f / sc;
+  __nv_fp8_e4m3* qr = q + (long long)row * ldq;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    __nv_fp8_e4m3 o8[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack_bf16x2(w[i]);
+      o8[2 * i] = __nv_fp8_e4m3(f.x * inv);
+      o8[2 * i + 1] = __nv_fp8_e4m3(f.y * inv);
+    }
+    *reinterpret_cast<uint2*>(qr + c) = *reinterpret_cast<const uint2*>(o8);
+  }
+}
+}  // namespace lt
+
 extern "C" {
+// x [rows, cols] bf16 (pitch ldx elements, rows 16-byte aligned), q [rows, cols] e4m3 (pitch ldq bytes, rows 8-byte aligned),
+// scale [rows] fp32.
+int lt_quant_e4m3_rows(const void* x, long long ldx, void* q, long long ldq, float* scale, int rows, int cols, void* stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if ((cols & 7) || (ldx & 7) || (ldq & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    return -int(lt::kStatusBadArgument);
+  lt::quant_e4m3_rows_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_fp8_e4m3*>(q), ldq, scale, rows, cols);
+  LT_LAUNCH_CHECK();
+  return 0;
+}
 int lt_quant_int8_tensor(const void* x, int is_bf16, void* q, long long n, float scale, void* stream) {
   if (n == 0) return 0;
   long long blocks = (n + 255) / 256;

@@ -179,10 +179,45 @@ class _LinearFP8(torch.autograd.Function):
         return dx, dw
 
 
-def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """Linear layer on the block-scaled fp8 tensor-core path (forward and input gradient); shapes must be multiples
-    of 128 in both feature dimensions.  Falls back to `linear` elsewhere."""
-    if _native(x, w) and x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0 and w.shape[0] % 128 == 0 and x.numel() > 0:
+class _LinearFP8Rows(torch.autograd.Function):
+    """y = x @ w^T with e4m3 operands scaled per row: one scale per token for the activations (and for dY), one per output
+    channel for the weight (per input channel for its transpose in the input gradient).  The products accumulate over the
+    whole K extent in tensor memory and the scales are applied once in the epilogue (`K.gemm_e4m3`), which is what lets this
+    path run faster than bf16; the weight gradient stays in bf16.  Master weights are bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _2d(x).contiguous()
+        xq, xs = K.quant_e4m3_rows(x2)
+        wq, ws = K.quant_e4m3_rows(w.contiguous())
+        y = K.gemm_e4m3(xq, xs, wq, ws)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _2d(dy).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = K.quant_e4m3_rows(dy2)
+            wtq, wts = K.quant_e4m3_rows(w.t().contiguous())      # [K, N]: the B operand of dX = dY @ W, scaled per input channel
+            dx = K.gemm_e4m3(gq, gs, wtq, wts).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = K.gemm(dy2, x2, a_major=1, b_major=1)
+        return dx, dw
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor, scaling: str = "rows") -> torch.Tensor:
+    """Linear layer with e4m3 operands on the tensor cores (forward and input gradient; the weight gradient stays bf16).
+    scaling="rows" (default): one scale per token and per channel, applied in the GEMM epilogue - the fast path;
+    scaling="block": 1 x 128 / 128 x 128 block scales with two-level accumulation (feature dimensions multiples of 128).
+    Falls back to `linear` where the shapes do not fit."""
+    ok = _native(x, w) and x.dtype == torch.bfloat16 and x.numel() > 0
+    if ok and scaling == "rows" and x.shape[-1] % 16 == 0 and w.shape[0] % 16 == 0:
+        return _LinearFP8Rows.apply(x, w)
+    if ok and scaling == "block" and x.shape[-1] % 128 == 0 and w.shape[0] % 128 == 0:
         return _LinearFP8.apply(x, w)
     return linear(x, w)
 

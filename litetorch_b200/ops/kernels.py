@@ -23,6 +23,8 @@ _SIGS = {
     "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
     "lt_gemv_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
     "lt_gemm_skinny_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
+    "lt_gemm_e4m3": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp],
+    "lt_quant_e4m3_rows": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
     "lt_quant_int8_tensor": [_vp, _i, _vp, _ll, _f, _vp],
     "lt_quant_int8_rows": [_vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_gemm_set_tail_split": [_i],
@@ -302,6 +304,43 @@ def gemm_set_pair_mode(mode: int):
     """0: one CTA per tile only; 1 (default): CTA pairs (cta_group::2, 256 x 256 tiles) where the cost model
     prefers them; 2: CTA pairs for every shape."""
     _fn("lt_gemm_set_pair_mode")(int(mode))
+
+
+def quant_e4m3_rows(x: torch.Tensor):
+    """x [M, K] bf16 (K a multiple of 8, rows may be strided) -> (e4m3 codes [M, K], fp32 scales [M]): row r is divided by
+    scale[r] = absmax(row r) / 448 before rounding, so x ~ codes * scale[:, None]."""
+    M, Kd = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and Kd % 8 == 0
+    q = torch.empty((M, Kd), dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty(M, dtype=torch.float32, device=x.device)
+    rc = _fn("lt_quant_e4m3_rows")(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), sc.data_ptr(), M, Kd, _stream())
+    _check(rc, "lt_quant_e4m3_rows")
+    return q, sc
+
+
+def gemm_e4m3(aq: torch.Tensor, a_scale, bq: torch.Tensor, b_scale, *, out=None, out_dtype=torch.bfloat16, bias=None, residual=None,
+              act: int = 0, alpha: float = 1.0) -> torch.Tensor:
+    """C[M, N] = epilogue((aq[M, K] @ bq[N, K]^T) * a_scale[:, None] * b_scale[None, :]) for e4m3 operands on tcgen05
+    kind::f8f6f4 (CTA pairs, the whole K extent accumulated in tensor memory, scales applied once in the epilogue).
+    a_scale [M] / b_scale [N] fp32 or None; K a multiple of 16."""
+    assert aq.dtype == torch.float8_e4m3fn and bq.dtype == torch.float8_e4m3fn and aq.dim() == 2 and bq.dim() == 2
+    assert aq.stride(1) == 1 and bq.stride(1) == 1 and aq.shape[1] == bq.shape[1]
+    M, Kd = aq.shape
+    N = bq.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=aq.device)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    for sc, n in ((a_scale, M), (b_scale, N)):
+        assert sc is None or (sc.dtype == torch.float32 and sc.numel() == n and sc.is_contiguous())
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+    rc = _fn("lt_gemm_e4m3")(aq.data_ptr(), bq.data_ptr(), out.data_ptr(), M, N, Kd, aq.stride(0), bq.stride(0), out.stride(0),
+                             1 if out.dtype == torch.float32 else 0, _p(a_scale), _p(b_scale), _p(bias), _p(residual),
+                             residual.stride(0) if residual is not None else 0, act, float(alpha), _stream())
+    _check(rc, "lt_gemm_e4m3")
+    return out
 
 
 def quant_fp8_1x128(x):

@@ -203,7 +203,7 @@ def bench_gemm_sustained(out=None):
 
 
 def bench_fp8(out=None):
-    """Block-scaled e4m3 GEMM (1x128 / 128x128 scales) against the bf16 kernel on the same shapes."""
+    """Block-scaled e4m3 GEMM (1x128 / 128x128 scales) and the row-scaled e4m3 GEMM against the bf16 kernel on the same shapes."""
     from ..ops import kernels as K
     pk = peaks()
     rows = []
@@ -220,11 +220,37 @@ def bench_fp8(out=None):
         ms_one = time_ms(lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c, pairs=False))
         ms_q = time_ms(lambda: K.quant_fp8_1x128(x))
         ms_bf = time_ms(lambda: K.gemm(x, w, out=c))
+        # the row-scaled kernel (one scale per token / channel, applied in the epilogue), burst and sustained
+        rq, rs = K.quant_e4m3_rows(x)
+        wq2, ws2 = K.quant_e4m3_rows(w)
+        ms_rows = time_ms(lambda: K.gemm_e4m3(rq, rs, wq2, ws2, out=c))
+        ms_rq = time_ms(lambda: K.quant_e4m3_rows(x))
+
+        def sustained(fn, seconds=1.0):
+            for _ in range(3):
+                fn()
+            n = max(10, int(seconds * 1e3 / max(ms_rows, 1e-3)))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        y32 = K.gemm_e4m3(rq[:512], rs[:512], wq2, ws2, out_dtype=torch.float32)
+        ref = (rq[:512].double() * rs[:512, None].double()) @ (wq2.double() * ws2[:, None].double()).t()
+        acc_err = float((y32.double() - ref).norm() / ref.norm())      # accumulation error alone (same codes, float64)
+        ms_rows_s = sustained(lambda: K.gemm_e4m3(rq, rs, wq2, ws2, out=c))
+        ms_bf_s = sustained(lambda: K.gemm(x, w, out=c))
         K.check_status()
         row = {"kernel": "gemm_fp8_block", "tag": tag, "M": M, "N": N, "K": Kd, "ms": round(ms, 4),
                "tflops": round(fl / ms / 1e9, 1), "x_bf16_%s_peak" % pk["src"]: round(fl / ms / 1e9 / pk["tflops"], 3),
                "one_cta_ms": round(ms_one, 4), "quant_ms": round(ms_q, 4), "quant_gbs": round(M * Kd * 3 / ms_q / 1e6, 1),
-               "bf16_kernel_ms": round(ms_bf, 4)}
+               "bf16_kernel_ms": round(ms_bf, 4), "rows_ms": round(ms_rows, 4), "rows_tflops": round(fl / ms_rows / 1e9, 1),
+               "rows_quant_ms": round(ms_rq, 4), "rows_sustained_tflops": round(fl / ms_rows_s / 1e9, 1),
+               "bf16_sustained_tflops": round(fl / ms_bf_s / 1e9, 1), "rows_accumulation_rel_err": acc_err}
         rows.append(row)
         print(json.dumps(row), flush=True)
     if out:

@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_vs_cublas|gemm_wgrad|gemm_fp8|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_vs_cublas|gemm_wgrad|gemm_fp8|gemm_e4m3|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
                                                  rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
@@ -49,6 +49,13 @@ def main():
         wq, ws = K.quant_fp8_128x128(w)
         c = torch.empty(8192, 11264, device=dev, dtype=torch.bfloat16)
         fn = lambda: K.gemm_fp8_block(xq, xst, wq, ws, out=c)
+    elif case == "gemm_e4m3":     # row-scaled e4m3 GEMM, gate_up forward shape
+        x = torch.randn(8192, 2048, device=dev).bfloat16()
+        w = (torch.randn(11264, 2048, device=dev) * 0.05).bfloat16()
+        xq, xs = K.quant_e4m3_rows(x)
+        wq, ws = K.quant_e4m3_rows(w)
+        c = torch.empty(8192, 11264, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gemm_e4m3(xq, xs, wq, ws, out=c)
     elif case == "rmsnorm_bwd":
         x = torch.randn(65536, 2048, device=dev).bfloat16()
         dy = torch.randn(65536, 2048, device=dev).bfloat16()

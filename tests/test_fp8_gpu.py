@@ -69,12 +69,13 @@ def test_fp8_block_linear_close_to_bf16():
     assert rel < 0.05, rel
 
 
-def test_linear_fp8_autograd_close_to_bf16():
+@pytest.mark.parametrize("scaling", ["rows", "block"])
+def test_linear_fp8_autograd_close_to_bf16(scaling):
     from litetorch_b200.ops import functional as Fn
     torch.manual_seed(3)
     x = torch.randn(512, 1024, device="cuda").bfloat16().requires_grad_(True)
     w = (torch.randn(768, 1024, device="cuda") * 0.03).bfloat16().requires_grad_(True)
-    y = Fn.linear_fp8(x, w)
+    y = Fn.linear_fp8(x, w, scaling=scaling)
     g = torch.randn_like(y)
     y.backward(g)
     xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
@@ -84,3 +85,32 @@ def test_linear_fp8_autograd_close_to_bf16():
     assert rel(y, yr) < 0.05
     assert rel(x.grad, xr.grad) < 0.06
     assert rel(w.grad, wr.grad) < 0.02
+
+
+@pytest.mark.parametrize("M,N,Kd", [(256, 256, 256), (8192, 2816, 2048), (300, 520, 4096), (1000, 136, 48), (129, 4096, 14336)])
+def test_gemm_e4m3_row_scaled_is_exact_on_the_codes(M, N, Kd):
+    """The row-scaled e4m3 GEMM (tcgen05 kind::f8f6f4, whole K in tensor memory, scales in the epilogue) against the same product
+    of the dequantised codes in float64: the only error left is the fp32 accumulation and the rounding of the output."""
+    from litetorch_b200.ops import kernels as K
+    torch.manual_seed(M + N + Kd)
+    x = torch.randn(M, Kd, device="cuda").bfloat16()
+    x[:, ::7] *= 8                                           # rows with a wide dynamic range
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    xq, xs = K.quant_e4m3_rows(x)
+    wq, ws = K.quant_e4m3_rows(w)
+    assert float((xq.float() * xs[:, None] - x.float()).abs().max() / x.float().abs().max()) < 0.07   # e4m3: 3 mantissa bits
+    assert float(xq.float().abs().max()) <= 448.0
+    ref = (xq.double() * xs[:, None].double()) @ (wq.double() * ws[:, None].double()).t()
+    y32 = K.gemm_e4m3(xq, xs, wq, ws, out_dtype=torch.float32)
+    K.check_status()
+    acc_err = float((y32.double() - ref).norm() / ref.norm())
+    assert acc_err < 1e-3, acc_err
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    y16 = K.gemm_e4m3(xq, xs, wq, ws, bias=bias, residual=res)
+    full = ref + bias.double()[None] + res.double()
+    assert float((y16.double() - full).norm() / full.norm()) < 6e-3
+    # against the unquantised product: the quantisation error itself
+    exact = x.double() @ w.double().t()
+    assert float((y32.double() - exact).norm() / exact.norm()) < 0.06
+    assert torch.equal(K.gemm_e4m3(xq, xs, wq, ws, out_dtype=torch.float32), y32)
