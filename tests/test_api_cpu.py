@@ -401,8 +401,8 @@ def test_moe_capacity_positions_and_section_timer():
 
 def test_run_config_presets_json_and_env(tmp_path):
     from litetorch_b200 import config as C
-    assert set(C.PRESETS) == {"gpt-cpu", "llama-1.1b-fsdp", "llama3-8b-tp8", "llama3-8b-tp8-fp8", "moe-8x2b-ep8",
-                              "llama-3b-long-hybrid"}
+    assert set(C.PRESETS) == {"gpt-cpu", "llama-1.1b-fsdp", "llama3-8b-fsdp-tp2", "llama3-8b-tp8", "llama3-8b-tp8-fp8",
+                              "moe-8x2b-ep8", "llama-3b-long-hybrid"}
     hy = C.load("llama-3b-long-hybrid", env={})
     assert hy.mesh_sizes(8) == {"dp": 1, "tp": 2, "pp": 2, "cp": 2, "ep": 1} and hy.tokens_per_step(8) == 8 * 32768
     assert C.load("llama-1.1b-fsdp", env={}).tokens_per_step(8) == 8 * 4 * 2048
