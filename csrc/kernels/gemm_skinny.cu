@@ -15,6 +15,7 @@
 #include "common/host.h"
 #include "common/ptx.cuh"
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -184,6 +185,10 @@ struct SkinnyWs {
   unsigned* counters = nullptr;
 };
 static std::mutex g_sk_mu;
+// Measured under graph replay (Llama-1.1B shapes, 32 and 128 rows): the hand-over of partial sums through L2 costs about 3 us, more
+// than a 2048-deep K loop on a third of the SMs, so by default K is split only when a warp still keeps 16 chunks (K >= 8192).
+static std::atomic<int> g_sk_target{1};       // CTAs per SM the K split aims for (lt_gemm_skinny_set_target)
+static std::atomic<int> g_sk_min_chunks{16};  // 32-element chunks a warp keeps at least when K is split
 static std::map<std::pair<int, cudaStream_t>, SkinnyWs> g_sk_ws;
 
 // Workspace of the K split, one per (device, stream): launches on one stream are serialised and the last CTA of a
@@ -233,8 +238,9 @@ static int launch_skinny(const __nv_bfloat16* X, long long ldx, const __nv_bfloa
   const int sms = sm_count();
   const int groups = (N + kSkCols - 1) / kSkCols;
   const int nchunks = K / 32;
-  int splits = (2 * sms + groups - 1) / groups;
-  const int max_splits = nchunks / (2 * kSkWarps) > 1 ? nchunks / (2 * kSkWarps) : 1;   // at least two chunks per warp
+  int splits = (g_sk_target.load() * sms + groups - 1) / groups;
+  const int mc = g_sk_min_chunks.load();
+  const int max_splits = nchunks / (mc * kSkWarps) > 1 ? nchunks / (mc * kSkWarps) : 1;   // at least `mc` chunks per warp
   if (splits > max_splits) splits = max_splits;
   SkinnyWs wsp;
   if (splits > 1) {
@@ -252,6 +258,14 @@ static int launch_skinny(const __nv_bfloat16* X, long long ldx, const __nv_bfloa
 }  // namespace lt
 
 extern "C" {
+
+// How many CTAs per SM the K split of narrow outputs aims for (default 1; 1 to 8) and how many 32-element chunks of K a
+// warp keeps at least (default 16; 1 to 16).
+int lt_gemm_skinny_set_target(int ctas_per_sm, int min_chunks_per_warp) {
+  lt::g_sk_target.store(ctas_per_sm < 1 ? 1 : (ctas_per_sm > 8 ? 8 : ctas_per_sm));
+  lt::g_sk_min_chunks.store(min_chunks_per_warp < 1 ? 1 : (min_chunks_per_warp > 16 ? 16 : min_chunks_per_warp));
+  return 0;
+}
 
 // y[M, N] = x[M, K] @ w[N, K]^T (+ residual[M, N]), all bf16; 1 <= M <= 128, K a multiple of 32, N a multiple of 8, operand
 // rows 16-byte aligned, y / residual rows 4-byte aligned.

@@ -23,6 +23,7 @@ _SIGS = {
     "lt_gemm_typed": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _i, _i, _f, _vp],
     "lt_gemv_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
     "lt_gemm_skinny_bf16": [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _vp],
+    "lt_gemm_skinny_set_target": [_i, _i],
     "lt_gemm_e4m3": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp],
     "lt_quant_e4m3_rows": [_vp, _ll, _vp, _ll, _vp, _i, _i, _vp],
     "lt_quant_int8_tensor": [_vp, _i, _vp, _ll, _f, _vp],
@@ -91,7 +92,7 @@ _SIGS = {
 _bound = {}
 
 # Kernels launched per native call; `launch_count()` is what bench.py reports as "gpu_launches".
-_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_adam_q8": 3, "lt_set_wait_budget_cycles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
+_LAUNCHES_PER_CALL = {"lt_gemm_num_tiles": 0, "lt_gemm_skinny_set_target": 0, "lt_adam_q8": 3, "lt_set_wait_budget_cycles": 0, "lt_norm_bwd": 2, "lt_paged_decode": 2, "lt_flash_bwd": 3, "lt_status_fetch": 0, "lt_sm_count": 0, "lt_gemm_set_tail_split": 0, "lt_reduce_parts": 0, "lt_reduce_all": 2, "lt_gemm_set_pair_mode": 0, "lt_flash_bwd_set_trace": 0, "lt_flash_fwd_set_trace": 0, "lt_norm_bwd_ctas": 0,
                       "lt_adam_chunk_elems": 0}
 _launches = [0]
 
@@ -298,6 +299,12 @@ def gemm_i8(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0) -> torch.Tenso
 def gemm_set_tail_split(enable: bool):
     """Turn the K-split of the last, partly filled tile wave of `gemm` on (default) or off."""
     _fn("lt_gemm_set_tail_split")(1 if enable else 0)
+
+
+def gemm_skinny_set_target(ctas_per_sm: int = 1, min_chunks_per_warp: int = 16):
+    """Tuning of the 9-128-row weight-streaming GEMM on narrow outputs: CTAs per SM that its K split aims for and the
+    fewest 32-element chunks of K a warp keeps (defaults 1 and 16: K is split from 8192 on)."""
+    _fn("lt_gemm_skinny_set_target")(int(ctas_per_sm), int(min_chunks_per_warp))
 
 
 def gemm_set_pair_mode(mode: int):

@@ -243,6 +243,14 @@ def test_skinny_gemm_against_fp32(M, N, Kd):
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     KK.gemm(a, b, out=out, residual=res)
     assert float((out.float() - (ref + res.float())).norm() / (ref + res.float()).norm()) < 6e-3
+    # the same product with K split over several CTAs per column group (off by default for short K)
+    KK.gemm_skinny_set_target(4, 1)
+    try:
+        ys = KK.gemm(a, b)
+        ys2 = KK.gemm(a, b)
+    finally:
+        KK.gemm_skinny_set_target()
+    assert torch.equal(ys, ys2) and float((ys.float() - ref).norm() / ref.norm()) < 6e-3
     # rows of a wider buffer (strided operands)
     wide = torch.randn(M, Kd + 64, device="cuda").bfloat16()
     y3 = KK.gemm(wide[:, :Kd], b)
