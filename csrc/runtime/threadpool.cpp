@@ -1,6 +1,7 @@
 // Small fixed thread pool with a blocking parallel_for, used by host-side data preparation and
 // checkpoint I/O.  Same contract as the reference pool (include/litetorch/thread_pool.h:15-157): ranges
 // shorter than a threshold run inline on the caller, the caller executes the last chunk itself.
+#include <cstdlib>
 #include <algorithm>
 #include <atomic>
 #include <condition_variable>
@@ -46,7 +47,15 @@ struct PoolT {
 };
 
 PoolT& pool() {
-  static PoolT p(std::max(1u, std::thread::hardware_concurrency()));
+  // LITETORCH_NUM_THREADS (documented by the reference, docs-en/2.installation.md:100) caps the pool; default: every core.
+  static PoolT p([] {
+    unsigned n = std::max(1u, std::thread::hardware_concurrency());
+    if (const char* e = std::getenv("LITETORCH_NUM_THREADS")) {
+      const long v = std::strtol(e, nullptr, 10);
+      if (v >= 1 && v <= 1024) n = unsigned(v);
+    }
+    return n;
+  }());
   return p;
 }
 

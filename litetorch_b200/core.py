@@ -10,6 +10,7 @@ reference (Embedding, cross-entropy targets, block tables).
 from __future__ import annotations
 
 import enum
+import os
 from typing import Callable, List, Optional, Sequence, Union
 
 import torch
@@ -259,8 +260,16 @@ class Tensor:
     def __neg__(self): return Tensor(-self._t)
 
 
-def is_gpu_available() -> bool:
+def _gpu_enabled() -> bool:
+    """A CUDA device is present and not switched off by the reference's environment variables (LITETORCH_NO_GPU /
+    LITETORCH_NO_NATIVE_GPU, src/backend/backend.cpp:115)."""
+    if os.environ.get("LITETORCH_NO_GPU") or os.environ.get("LITETORCH_NO_NATIVE_GPU"):
+        return False
     return torch.cuda.is_available()
+
+
+def is_gpu_available() -> bool:
+    return _gpu_enabled()
 
 
 def is_tpu_available() -> bool:
@@ -268,11 +277,18 @@ def is_tpu_available() -> bool:
 
 
 def auto_device() -> Device:
-    return Device(DeviceType.GPU, torch.cuda.current_device()) if torch.cuda.is_available() else Device(DeviceType.CPU, 0)
+    """The GPU when there is one and it is not switched off, else the CPU; LITETORCH_DEVICE_INDEX picks the GPU
+    (src/cl_backend/cl_backend.cpp:192), otherwise the current CUDA device."""
+    if not _gpu_enabled():
+        return Device(DeviceType.CPU, 0)
+    idx = os.environ.get("LITETORCH_DEVICE_INDEX", "")
+    if idx.strip().isdigit() and int(idx) < torch.cuda.device_count():
+        return Device(DeviceType.GPU, int(idx))
+    return Device(DeviceType.GPU, torch.cuda.current_device())
 
 
 def get_backend_name() -> str:
-    return "CUDA sm_100a (tcgen05/TMA kernels)" if torch.cuda.is_available() else "CPU"
+    return "CUDA sm_100a (tcgen05/TMA kernels)" if _gpu_enabled() else "CPU"
 
 
 def checkpoint(fn: Callable, x: Tensor) -> Tensor:

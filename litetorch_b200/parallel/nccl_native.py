@@ -11,6 +11,8 @@ The reference's counterpart is NCCLBridge (src/distributed/distributed.cpp:785-9
 from __future__ import annotations
 
 import ctypes
+import os
+import time
 from ctypes import c_int, c_ulonglong, c_void_p
 
 import torch
@@ -48,21 +50,64 @@ class NcclError(RuntimeError):
     pass
 
 
+def _id_file():
+    for k in ("LITETORCH_RENDEZVOUS_FILE", "NCCL_UNIQUE_ID_FILE"):
+        v = os.environ.get(k, "")
+        if v:
+            return v + ".ncclid"
+    return None
+
+
+def publish_id_file(path: str, raw: bytes) -> None:
+    """Rank 0 of the reference writes the 128-byte communicator id into the rendezvous file and the others poll for it
+    (src/distributed/distributed.cpp:829-860).  Written to a temporary name and renamed, so that a reader never sees a
+    partial id."""
+    tmp = "%s.%d.tmp" % (path, os.getpid())
+    with open(tmp, "wb") as f:
+        f.write(raw)
+        f.flush()
+        os.fsync(f.fileno())
+    os.replace(tmp, path)
+
+
+def read_id_file(path: str, timeout_s: float = 120.0) -> bytes:
+    t_end = time.monotonic() + timeout_s
+    while True:
+        try:
+            with open(path, "rb") as f:
+                raw = f.read()
+            if len(raw) >= 128:
+                return raw[:128]
+        except OSError:
+            pass
+        if time.monotonic() > t_end:
+            raise NcclError("no communicator id in %s after %.0f s" % (path, timeout_s))
+        time.sleep(0.01)
+
+
 class NativeNccl:
     def __init__(self, store, rank: int, world: int, key: str = "lt_nccl_id", timeout_s: float = 120.0):
         self._L = _lib()
         self.rank, self.world = rank, world
         if nccl_version() == 0:
             raise NcclError("libnccl.so.2 could not be opened")
+        id_file = None if store is not None else _id_file()
+        if store is None and id_file is None:
+            raise NcclError("no store given and neither LITETORCH_RENDEZVOUS_FILE nor NCCL_UNIQUE_ID_FILE is set")
         if rank == 0:
             buf = (ctypes.c_char * 128)()
             rc = self._L.lt_nccl_unique_id(buf)
             if rc != 0:
                 raise NcclError("ncclGetUniqueId failed: %d" % rc)
-            store.set(key, bytes(buf.raw))
             raw = bytes(buf.raw)
-        else:
+            if store is not None:
+                store.set(key, raw)
+            else:
+                publish_id_file(id_file, raw)
+        elif store is not None:
             raw = store.get(key, timeout_s=timeout_s)
+        else:
+            raw = read_id_file(id_file, timeout_s)
         if len(raw) != 128:
             raise NcclError("rendezvous returned %d bytes for the communicator id" % len(raw))
         err = c_int(0)

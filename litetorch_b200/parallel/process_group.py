@@ -206,7 +206,12 @@ class ProcessGroup:
                 local = int(os.environ.get("LOCAL_RANK", rank % max(torch.cuda.device_count(), 1)))
                 torch.cuda.set_device(local)
                 kw["device_id"] = torch.device("cuda", local)
-            dist.init_process_group(backend, init_method="tcp://%s:%d" % (master_addr, master_port), rank=rank,
+            # The reference publishes its communicator id through a file named by LITETORCH_RENDEZVOUS_FILE (or
+            # NCCL_UNIQUE_ID_FILE; src/distributed/distributed.cpp:824-850); here the same variable selects
+            # torch.distributed's file rendezvous instead of the TCP one.
+            rend = rendezvous_file()
+            method = ("file://" + os.path.abspath(rend)) if rend else "tcp://%s:%d" % (master_addr, master_port)
+            dist.init_process_group(backend, init_method=method, rank=rank,
                                     world_size=world_size, timeout=timedelta(seconds=timeout_s), **kw)
         if with_store:
             self.store = TCPStore(master_addr, master_port + 1, is_server=(rank == 0))
@@ -311,6 +316,15 @@ class ProcessGroup:
             self.store.barrier("pg_barrier", self.get_world_size(), timeout_s)
         elif self._live():
             dist.barrier()
+
+
+def rendezvous_file() -> Optional[str]:
+    """The path named by LITETORCH_RENDEZVOUS_FILE or NCCL_UNIQUE_ID_FILE, or None."""
+    for k in ("LITETORCH_RENDEZVOUS_FILE", "NCCL_UNIQUE_ID_FILE"):
+        v = os.environ.get(k, "")
+        if v:
+            return v
+    return None
 
 
 def init_process_group(rank: int, world_size: int, master_addr: str = "127.0.0.1", master_port: int = 29500, **kw) -> ProcessGroup:

@@ -318,3 +318,48 @@ def test_rank_that_leaves_is_detected_not_hung(tmp_path):
         os._exit(0)
     ''', tmp_path=tmp_path, port=29861, expect_fail=True, timeout=120)
     assert 'RESULT {"detected": true' in r.stdout and "[1]" in r.stdout and "BARRIER timeout" in r.stdout, r.stdout + r.stderr[-1500:]
+
+
+def test_reference_environment_variables_are_honoured(tmp_path):
+    """LITETORCH_RENDEZVOUS_FILE selects the file rendezvous (the reference publishes its communicator id through that
+    file), the 128-byte id travels through `<file>.ncclid` for the native NCCL bridge, LITETORCH_NO_GPU switches the GPU
+    off and LITETORCH_NUM_THREADS sizes the host thread pool."""
+    rend = os.path.join(str(tmp_path), "rendezvous")
+    script = os.path.join(str(tmp_path), "w.py")
+    with open(script, "w") as f:
+        f.write(textwrap.dedent('''
+            import json, os, sys, torch
+            sys.path.insert(0, %r)
+            import torch.distributed as dist
+            import litetorch_b200 as lt
+            from litetorch_b200.core import _unwrap
+            from litetorch_b200.parallel import nccl_native as NN
+            rank = int(sys.argv[1])
+            # a port nobody listens on: only the file rendezvous can bring the two ranks together
+            pg = lt.distributed.init_process_group(rank, 2, "127.0.0.1", 1, backend="gloo", timeout_s=60)
+            t = lt.Tensor(torch.tensor([1.0 + rank]))
+            pg.all_reduce(t)
+            path = NN._id_file()
+            if rank == 0:
+                NN.publish_id_file(path, bytes(range(128)))
+            raw = NN.read_id_file(path, 30)
+            import ctypes
+            from litetorch_b200._native import host_lib
+            L = host_lib(); L.lt_pool_threads.restype = ctypes.c_int
+            print("RESULT " + json.dumps({"sum": _unwrap(t).item(), "id_ok": raw == bytes(range(128)), "gpu": lt.is_gpu_available(),
+                                          "dev": str(lt.auto_device()), "backend": lt.get_backend_name(), "threads": L.lt_pool_threads()}))
+            dist.barrier(); pg.shutdown()
+        ''' % ROOT))
+    env = dict(os.environ, LITETORCH_RENDEZVOUS_FILE=rend, LITETORCH_NO_GPU="1", LITETORCH_NUM_THREADS="3", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, script, str(r)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+             for r in range(2)]
+    outs = [p.communicate(timeout=240) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, o[-1500:] + e[-3000:]
+    for o, _ in outs:
+        res = json.loads([l for l in o.splitlines() if l.startswith("RESULT ")][-1][7:])
+        assert res["sum"] == 3.0 and res["id_ok"] and res["gpu"] is False and res["backend"] == "CPU" and res["threads"] == 3
+        assert "cpu" in res["dev"].lower()
+    from litetorch_b200.parallel import nccl_native as NN
+    with pytest.raises(NN.NcclError):
+        NN.read_id_file(os.path.join(str(tmp_path), "never_written"), 0.2)
