@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of one kernel each.
 
-    python -m litetorch_b200.utils.profile_cases gemm|gemm_vs_cublas|gemm_wgrad|gemm_fp8|gemm_e4m3|gemm_rs|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
+    python -m litetorch_b200.utils.profile_cases gemm|gemm_vs_cublas|gemm_wgrad|gemm_fp8|gemm_e4m3|gemm_rs|ag_gemm|rs_adamw|flash_fwd|flash_bwd|flash_fwd_d128|flash_bwd_d128|paged_decode|shard_gather|
                                                  rmsnorm|rmsnorm_bwd|swiglu|adamw|ce [reps]
 
 Every case touches more than the 126 MB L2 but only a few hundred MB of device memory, launches the kernel a
@@ -101,6 +101,43 @@ def main():
         shards = [torch.randn(n, device=dev).bfloat16() for _ in range(4)]
         dst = torch.empty(4 * n, device=dev, dtype=torch.bfloat16)
         fn = lambda: K.gather_shards([s.data_ptr() for s in shards], [(0, n)], [dst], max_ctas=64)
+    elif case in ("ag_gemm", "rs_adamw"):
+        # the two ZeRO-3 kernels on a one-rank group: the gather CTAs copy the local shard while the GEMM CTAs wait on its flags
+        # (ag_gemm), the reduce phase reads one "peer" (rs_adamw): everything but the NVLink hop
+        import os
+        import torch.distributed as dist
+        from ..parallel.fsdp import SymmetricBuffer
+        for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29534")):
+            os.environ.setdefault(k, v)
+        torch.cuda.set_device(0)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", 0))
+        if case == "ag_gemm":       # Llama-1.1B gate/up forward, the weight "gathered" by 8 gather CTAs
+            Mt, N, Kd = 8192, 11264, 2048
+            shard = SymmetricBuffer(N * Kd, torch.bfloat16, dev)
+            shard.tensor.copy_((torch.randn(N * Kd, device=dev) * 0.02).bfloat16())
+            full = torch.empty(N, Kd, device=dev, dtype=torch.bfloat16)
+            gflags = torch.zeros(4096, dtype=torch.int32, device=dev)
+            xt = torch.randn(Mt, Kd, device=dev).bfloat16()
+            st = {"e": 0}
+
+            def fn():
+                st["e"] += 1
+                K.ag_gemm(None, full, gather_operand=1, shard_ptrs=shard.ptrs, world=1, rank=0, rows_per_rank=N, flags=gflags,
+                          epoch=st["e"], other=xt, n_comm=8)
+        else:                       # one 64 M-element gradient bucket: bf16 gradients in, fp32 master / moments, bf16 parameters out
+            n = 64 * 1024 * 1024
+            grads = SymmetricBuffer(n, torch.bfloat16, dev)
+            grads.tensor.copy_((torch.randn(n, device=dev) * 0.01).bfloat16())
+            rs_flags = SymmetricBuffer(64 * 8, torch.int32, dev)
+            master = torch.randn(n, device=dev)
+            m1, v1 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+            p16 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+            st = {"e": 0}
+
+            def fn():
+                st["e"] += 1
+                K.rs_adamw(grads.ptrs, None, master, m1, v1, p16, [(0, 0, n)], lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1,
+                           step=st["e"], my_flags=rs_flags.tensor, peer_flag_ptrs=rs_flags.ptrs, slot=1, epoch=st["e"], world=1, rank=0)
     elif case == "gemm_rs":
         # GEMM -> reduce-scatter on a one-rank group: the scatter epilogue and the reduce phase without NVLink
         import os
@@ -108,7 +145,8 @@ def main():
         from ..parallel.tp_fused import TPFusedContext
         for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
             os.environ.setdefault(k, v)
-        dist.init_process_group("nccl", device_id=dev)
+        torch.cuda.set_device(0)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", 0))
         tp = TPFusedContext(8192, 4096, dev)
         h = torch.randn(8192, 1792, device=dev).bfloat16()
         w_row = (torch.randn(4096, 1792, device=dev) * 0.02).bfloat16()
