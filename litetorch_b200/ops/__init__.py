@@ -96,7 +96,15 @@ class Ops:
     def scaled_matmul(a, b, a_scale: float, b_scale: float, bias=None, out_dtype: DataType = DataType.FP32):
         """Low-precision operands with per-tensor scales: (a @ b) * a_scale * b_scale + bias (src/ops/scaled_matmul.cpp:8-43)."""
         from ..quantization import to_float
-        y = torch.matmul(to_float(a), to_float(b)) * (a_scale * b_scale)
+        at, bt = _unwrap(a), _unwrap(b)
+        if (at.is_cuda and at.dtype == torch.float8_e4m3fn and bt.dtype == torch.float8_e4m3fn and at.dim() == 2 and bt.dim() == 2
+                and at.shape[1] % 16 == 0 and at.numel() > 0 and bt.numel() > 0):
+            # e4m3 codes on the tensor cores (tcgen05 kind::f8f6f4, fp32 accumulation over the whole K extent); b is [K, N]:
+            # its codes are laid out K-major first
+            from . import kernels as K
+            y = K.gemm_e4m3(at.contiguous(), None, bt.t().contiguous(), None, out_dtype=torch.float32, alpha=float(a_scale * b_scale))
+        else:
+            y = torch.matmul(to_float(a), to_float(b)) * (a_scale * b_scale)
         if bias is not None:
             y = y + _unwrap(bias).float()
         return _w(y).cast(out_dtype)

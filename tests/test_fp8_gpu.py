@@ -114,3 +114,19 @@ def test_gemm_e4m3_row_scaled_is_exact_on_the_codes(M, N, Kd):
     exact = x.double() @ w.double().t()
     assert float((y32.double() - exact).norm() / exact.norm()) < 0.06
     assert torch.equal(K.gemm_e4m3(xq, xs, wq, ws, out_dtype=torch.float32), y32)
+
+
+def test_scaled_matmul_runs_e4m3_codes_on_the_tensor_cores():
+    """lt.Ops.scaled_matmul on two e4m3 tensors with per-tensor scales: the tcgen05 kind::f8f6f4 GEMM against float64 on the codes."""
+    import litetorch_b200 as lt
+    from litetorch_b200.core import _unwrap
+    from litetorch_b200.ops import kernels as K
+    torch.manual_seed(11)
+    a = (torch.randn(200, 96, device="cuda") * 3).to(torch.float8_e4m3fn)
+    b = (torch.randn(96, 72, device="cuda") * 3).to(torch.float8_e4m3fn)       # [K, N]
+    bias = torch.randn(72, device="cuda")
+    n0 = K.launch_count()
+    y = _unwrap(lt.Ops.scaled_matmul(lt.Tensor(a), lt.Tensor(b), 0.25, 0.5, bias=lt.Tensor(bias)))
+    assert K.launch_count() > n0                                              # the native kernel ran
+    ref = (a.double() @ b.double()) * 0.125 + bias.double()
+    assert y.dtype == torch.float32 and float((y.double() - ref).norm() / ref.norm()) < 1e-5
