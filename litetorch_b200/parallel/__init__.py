@@ -10,6 +10,7 @@ from .cp import (context_parallel_backward, context_parallel_forward, ring_atten
 from .ep import MoEFeedForward
 from .ulysses import head_to_seq, seq_to_head, ulysses_attention
 from .fsdp_api import FSDP, FullyShardedDataParallel
+from .elastic import ElasticLauncher
 from ..core import manual_seed
 
 __all__ = [n for n in dir() if not n.startswith("_")]

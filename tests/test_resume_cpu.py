@@ -5,6 +5,8 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 WORKER = r'''
@@ -196,3 +198,77 @@ def test_zero3_optimizer_sharded_save_and_load_on_two_ranks(tmp_path):
     assert res["first"] == res["full"][:3]
     assert all(abs(a - b) < 1e-6 for a, b in zip(res["rest"], res["full"][3:])), res
     assert res["step"] == 6
+
+
+ELASTIC_WORKER = r'''
+import json, os, sys, time, torch
+sys.path.insert(0, %(root)r)
+import torch.distributed as dist
+from litetorch_b200.models.llama import LlamaConfig
+from litetorch_b200.trainer import Trainer
+from litetorch_b200.parallel import elastic
+info = elastic.worker_info()
+rank, world, attempt = info["rank"], info["world"], info["attempt"]
+ck, mode = sys.argv[1], sys.argv[2]
+torch.set_num_threads(2)
+hb = elastic.start_heartbeat(0.1)
+cfg = LlamaConfig.tiny()
+B, T = 2, 64
+gen = torch.Generator().manual_seed(7)
+data = torch.randint(0, cfg.vocab_size, (6, world * B, T + 1), generator=gen)
+tr = Trainer(cfg, seed=3, device="cpu", param_dtype=torch.float32, parallel="hybrid")
+start = 0
+if os.path.exists(os.path.join(ck, "DONE")):
+    tr.load(ck)
+    start = tr.engine.step_count
+losses = []
+for s in range(start, 6):
+    losses.append(tr.step(data[s, rank * B:(rank + 1) * B, :-1].contiguous(), data[s, rank * B:(rank + 1) * B, 1:].contiguous()))
+    tr.save(ck)
+    dist.barrier()                                  # every rank's files of this step are on disk
+    if rank == 0:
+        open(os.path.join(ck, "DONE"), "w").write(str(s + 1))
+    dist.barrier()
+    if attempt == 0 and rank == 1 and s == 2:
+        if mode == "exit":
+            os._exit(17)                            # dies between steps, nothing in flight
+        if mode == "hang":
+            hb.stop()                               # stops beating and never joins the next collective
+            time.sleep(600)
+if rank == 0:
+    print("RESULT " + json.dumps({"attempt": attempt, "start": start, "losses": losses}), flush=True)
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("mode", ["exit", "hang"])
+def test_elastic_launcher_restarts_the_group_and_the_run_ends_on_the_uninterrupted_curve(tmp_path, mode):
+    """Rank 1 dies (or stops beating and hangs) after the third step of the first attempt; the launcher stops the other rank,
+    restarts both, they resume from the checkpoint and the last three losses equal those of a run nobody interrupted."""
+    from litetorch_b200.parallel.elastic import ElasticLauncher
+    script = os.path.join(str(tmp_path), "w.py")
+    with open(script, "w") as f:
+        f.write(ELASTIC_WORKER % {"root": ROOT})
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+
+    def run(ck, m, port):
+        logs = os.path.join(str(tmp_path), "logs_" + os.path.basename(ck))
+        res = ElasticLauncher([sys.executable, script, ck, m], nproc=2, max_restarts=2, base_port=port, heartbeat_ttl_s=2.0,
+                              start_grace_s=120.0, env=env, log_dir=logs).run()
+        out = []
+        for a in range(len(res["attempts"])):
+            with open(os.path.join(logs, "attempt%d_rank0.log" % a)) as f:
+                out += [json.loads(l[7:]) for l in f.read().splitlines() if l.startswith("RESULT ")]
+        return res, out
+
+    ref, ref_out = run(os.path.join(str(tmp_path), "ck_ref"), "none", 29640 if mode == "exit" else 29680)
+    assert ref["ok"] and ref["restarts"] == 0 and len(ref_out) == 1 and len(ref_out[0]["losses"]) == 6
+    res, out = run(os.path.join(str(tmp_path), "ck"), mode, 29660 if mode == "exit" else 29700)
+    assert res["ok"] and res["restarts"] == 1, res
+    first = res["attempts"][0]
+    assert ("exited with code 17" in first["reason"]) if mode == "exit" else ("heartbeats" in first["reason"]), first
+    assert len(out) == 1 and out[0]["attempt"] == 1 and out[0]["start"] == 3
+    assert all(abs(x - y) < 1e-6 for x, y in zip(out[0]["losses"], ref_out[0]["losses"][3:])), (out, ref_out)
