@@ -107,10 +107,16 @@ class Trainer:
         return {"weights": type(self.engine.w).__name__, "world_size": self.world_size if self.engine.w.__class__.__name__ != "LocalWeights" else 1,
                 "tp": self.tp, "model": asdict(self.cfg)}
 
-    def save(self, directory: str) -> None:
+    def save(self, directory: str, keep: int = 2) -> None:
         """Write everything a restart needs: per rank, its fp32 master weights and AdamW moments (the shard it owns
         under ZeRO-3 / tensor parallelism, the replicated norm gains included) as one LTW1 file, and by rank 0 a
-        manifest with the model, the layout and the optimizer's step count (bias correction depends on it)."""
+        manifest with the model, the layout and the optimizer's step count (bias correction depends on it).
+
+        A checkpoint is a sub-directory `step-<n>`: every rank writes into `.step-<n>.tmp`, and once all files are on disk
+        rank 0 renames it and points the file `LATEST` at it (both atomic), then drops all but the newest `keep`
+        checkpoints.  A job that dies in the middle of a save therefore leaves the previous checkpoint intact and
+        `load` never sees a mix of two steps."""
+        import shutil
         from .serialization import save_sharded
         w = self.engine.w
         state = w.state_tensors()
@@ -118,12 +124,40 @@ class Trainer:
         sharded = lay["world_size"] > 1
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+        name = "step-%08d" % self.engine.step_count
+        tmp, final = os.path.join(directory, "." + name + ".tmp"), os.path.join(directory, name)
         meta = dict(lay, names=list(state), step_count=self.engine.step_count)
-        save_sharded(directory, [t.detach().float().cpu() for t in state.values()], self.rank if sharded else 0,
+        save_sharded(tmp, [t.detach().float().cpu() for t in state.values()], self.rank if sharded else 0,
                      lay["world_size"], tag="trainer", meta=meta)
         if sharded:
             import torch.distributed as dist
+            dist.barrier()                                   # every rank's file is in the temporary directory
+        if not sharded or self.rank == 0:
+            if os.path.isdir(final):
+                shutil.rmtree(final)                         # the same step saved twice
+            os.replace(tmp, final)
+            with open(os.path.join(directory, "LATEST.tmp"), "w") as f:
+                f.write(name)
+            os.replace(os.path.join(directory, "LATEST.tmp"), os.path.join(directory, "LATEST"))
+            done = sorted(d for d in os.listdir(directory) if d.startswith("step-") and os.path.isdir(os.path.join(directory, d)))
+            for d in done[:-keep] if keep > 0 else []:
+                if d != name:
+                    shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
+            for d in os.listdir(directory):                  # leftovers of saves that never finished
+                if d.startswith(".step-") and d.endswith(".tmp") and d != "." + name + ".tmp":
+                    shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
+        if sharded:
             dist.barrier()
+
+    @staticmethod
+    def latest_checkpoint(directory: str):
+        """The sub-directory `LATEST` points at, `directory` itself for a flat checkpoint, None when there is none."""
+        try:
+            with open(os.path.join(directory, "LATEST")) as f:
+                d = os.path.join(directory, f.read().strip())
+            return d if os.path.isdir(d) else None
+        except OSError:
+            return directory if os.path.exists(os.path.join(directory, "trainer.manifest.json")) else None
 
     def load(self, directory: str) -> None:
         """Resume from `save`: the checkpoint must come from the same model on the same layout (world size, tp)."""
@@ -132,6 +166,10 @@ class Trainer:
         w = self.engine.w
         state = w.state_tensors()
         lay = self._layout()
+        root = directory
+        directory = self.latest_checkpoint(root)
+        if directory is None:
+            raise CheckpointError("no finished checkpoint in %s" % root)
         with open(os.path.join(directory, "trainer.manifest.json")) as f:
             meta = json.load(f)["meta"]
         for k in ("weights", "world_size", "tp", "model"):

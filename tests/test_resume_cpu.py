@@ -218,17 +218,13 @@ gen = torch.Generator().manual_seed(7)
 data = torch.randint(0, cfg.vocab_size, (6, world * B, T + 1), generator=gen)
 tr = Trainer(cfg, seed=3, device="cpu", param_dtype=torch.float32, parallel="hybrid")
 start = 0
-if os.path.exists(os.path.join(ck, "DONE")):
+if Trainer.latest_checkpoint(ck) is not None:
     tr.load(ck)
     start = tr.engine.step_count
 losses = []
 for s in range(start, 6):
     losses.append(tr.step(data[s, rank * B:(rank + 1) * B, :-1].contiguous(), data[s, rank * B:(rank + 1) * B, 1:].contiguous()))
-    tr.save(ck)
-    dist.barrier()                                  # every rank's files of this step are on disk
-    if rank == 0:
-        open(os.path.join(ck, "DONE"), "w").write(str(s + 1))
-    dist.barrier()
+    tr.save(ck)                                     # returns once the checkpoint of this step is complete and LATEST points at it
     if attempt == 0 and rank == 1 and s == 2:
         if mode == "exit":
             os._exit(17)                            # dies between steps, nothing in flight
@@ -272,3 +268,36 @@ def test_elastic_launcher_restarts_the_group_and_the_run_ends_on_the_uninterrupt
     assert ("exited with code 17" in first["reason"]) if mode == "exit" else ("heartbeats" in first["reason"]), first
     assert len(out) == 1 and out[0]["attempt"] == 1 and out[0]["start"] == 3
     assert all(abs(x - y) < 1e-6 for x, y in zip(out[0]["losses"], ref_out[0]["losses"][3:])), (out, ref_out)
+
+
+def test_trainer_checkpoints_are_complete_or_absent(tmp_path):
+    """`Trainer.save` builds a checkpoint in a temporary sub-directory and publishes it with two renames: what an interrupted
+    save leaves behind is ignored by `load` and removed by the next save; only the newest `keep` checkpoints stay."""
+    import torch
+    from litetorch_b200.models.llama import LlamaConfig
+    from litetorch_b200.serialization import CheckpointError
+    from litetorch_b200.trainer import Trainer
+    ck = str(tmp_path / "ck")
+    cfg = LlamaConfig.tiny()
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(1))
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    tr = Trainer(cfg, seed=3, device="cpu", param_dtype=torch.float32, parallel="none")
+    assert Trainer.latest_checkpoint(ck) is None
+    with pytest.raises(CheckpointError):
+        tr.load(ck)
+    for _ in range(3):
+        tr.step(x, y)
+    tr.save(ck)
+    assert open(os.path.join(ck, "LATEST")).read() == "step-00000003"
+    # a save of step 4 that died after writing half a file
+    os.makedirs(os.path.join(ck, ".step-00000004.tmp"))
+    with open(os.path.join(ck, ".step-00000004.tmp", "trainer.rank00000.ltw1"), "wb") as f:
+        f.write(b"LTW1\x05\x00")
+    nxt = tr.step(x, y)
+    other = Trainer(cfg, seed=9, device="cpu", param_dtype=torch.float32, parallel="none")
+    other.load(ck)
+    assert other.engine.step_count == 3 and abs(other.step(x, y) - nxt) < 1e-6
+    for _ in range(2):
+        tr.step(x, y)
+        tr.save(ck)
+    assert sorted(d for d in os.listdir(ck)) == ["LATEST", "step-00000005", "step-00000006"]
