@@ -107,7 +107,7 @@ class Trainer:
         return {"weights": type(self.engine.w).__name__, "world_size": self.world_size if self.engine.w.__class__.__name__ != "LocalWeights" else 1,
                 "tp": self.tp, "model": asdict(self.cfg)}
 
-    def save(self, directory: str, keep: int = 2) -> None:
+    def save(self, directory: str, keep: int = 2, loader=None) -> None:
         """Write everything a restart needs: per rank, its fp32 master weights and AdamW moments (the shard it owns
         under ZeRO-3 / tensor parallelism, the replicated norm gains included) as one LTW1 file, and by rank 0 a
         manifest with the model, the layout and the optimizer's step count (bias correction depends on it).
@@ -115,7 +115,8 @@ class Trainer:
         A checkpoint is a sub-directory `step-<n>`: every rank writes into `.step-<n>.tmp`, and once all files are on disk
         rank 0 renames it and points the file `LATEST` at it (both atomic), then drops all but the newest `keep`
         checkpoints.  A job that dies in the middle of a save therefore leaves the previous checkpoint intact and
-        `load` never sees a mix of two steps."""
+        `load` never sees a mix of two steps.  `loader`: an `lt.data.DataLoader` whose position (epoch, permutation, next
+        index: the LTDL record) is stored per rank next to the tensors and restored by `load(..., loader=...)`."""
         import shutil
         from .serialization import save_sharded
         w = self.engine.w
@@ -129,6 +130,8 @@ class Trainer:
         meta = dict(lay, names=list(state), step_count=self.engine.step_count)
         save_sharded(tmp, [t.detach().float().cpu() for t in state.values()], self.rank if sharded else 0,
                      lay["world_size"], tag="trainer", meta=meta)
+        if loader is not None:
+            loader.save_state(os.path.join(tmp, "loader.rank%05d.ltdl" % (self.rank if sharded else 0)))
         if sharded:
             import torch.distributed as dist
             dist.barrier()                                   # every rank's file is in the temporary directory
@@ -159,7 +162,7 @@ class Trainer:
         except OSError:
             return directory if os.path.exists(os.path.join(directory, "trainer.manifest.json")) else None
 
-    def load(self, directory: str) -> None:
+    def load(self, directory: str, loader=None) -> None:
         """Resume from `save`: the checkpoint must come from the same model on the same layout (world size, tp)."""
         import json
         from .serialization import CheckpointError, load_sharded
@@ -185,6 +188,11 @@ class Trainer:
             dst.copy_(src.view_as(dst))
         self.engine.step_count = int(meta["step_count"])
         w.after_load()
+        if loader is not None:
+            path = os.path.join(directory, "loader.rank%05d.ltdl" % (self.rank if sharded else 0))
+            if not os.path.exists(path):
+                raise CheckpointError("the checkpoint holds no data-loader state for rank %d" % self.rank)
+            loader.load_state(path)
 
     def log_metrics(self, path: str) -> None:
         """Append one JSON line per `step` (step, loss, step_ms, tokens_per_s, allocator high-water mark) to `path`."""

@@ -301,3 +301,43 @@ def test_trainer_checkpoints_are_complete_or_absent(tmp_path):
         tr.step(x, y)
         tr.save(ck)
     assert sorted(d for d in os.listdir(ck)) == ["LATEST", "step-00000005", "step-00000006"]
+
+
+def test_trainer_checkpoint_carries_the_data_loader_position(tmp_path):
+    """`Trainer.save(dir, loader=dl)` stores the loader's LTDL record (epoch, permutation, next index) with the tensors: a fresh
+    trainer and a fresh loader built with the job's seed continue with the batches and the losses of the uninterrupted run, across
+    the next reshuffle too."""
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200.core import _unwrap
+    from litetorch_b200.models.llama import LlamaConfig
+    from litetorch_b200.trainer import Trainer
+    cfg = LlamaConfig.tiny()
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (24, 33), generator=g)
+
+    def loader(seed):
+        return lt.data.DataLoader(lt.data.TensorDataset(lt.Tensor(toks[:, :-1].float()), lt.Tensor(toks[:, 1:].float())), 4, True,
+                                  lt.Device("cpu"), 2, seed=seed)
+
+    def run(tr, dl, n):
+        out = []
+        for _ in range(n):
+            b = dl.next()
+            if b is None:
+                dl.reset()
+                b = dl.next()
+            out.append(tr.step(_unwrap(b[0]).long(), _unwrap(b[1]).long()))
+        return out
+
+    make = lambda seed: Trainer(cfg, seed=seed, device="cpu", param_dtype=torch.float32, parallel="none")   # noqa: E731
+    full = run(make(3), loader(1), 8)                       # crosses an epoch boundary (6 batches per epoch)
+    tr, dl = make(3), loader(1)
+    first = run(tr, dl, 4)
+    ck = str(tmp_path / "ck")
+    tr.save(ck, loader=dl)
+    tr2, dl2 = make(9), loader(1)
+    run(make(3), dl2, 2)                                    # the fresh loader is somewhere else before the load
+    tr2.load(ck, loader=dl2)
+    rest = run(tr2, dl2, 4)
+    assert first == full[:4] and all(abs(a - b) < 1e-6 for a, b in zip(rest, full[4:])), (rest, full)
