@@ -88,3 +88,10 @@ def test_shape_mismatch_raises_and_nan_inf_propagate():
     scaler.step(opt)
     scaler.update()
     assert torch.equal(_unwrap(w).detach(), torch.ones(2)) and scaler.get_scale() < 4.0
+
+
+def test_spiral_demo_learns_the_three_arms():
+    """The end-to-end demo of the reference's tests/demo_run.py through this package's public API."""
+    from litetorch_b200.models.spiral import train
+    r = train(epochs=300, device="cpu")
+    assert r["loss"] < 0.2 * r["first_loss"] and r["accuracy"] > 0.95, r
