@@ -46,3 +46,43 @@ def test_reference_python_surface_is_present():
                                               "sync_comm get_rank get_world_size is_initialized").split() if not hasattr(pg, n)]
     assert not missing, missing
     assert hasattr(lt.DataType, "FP4") and hasattr(lt.distributed.FSDP, "fully_shard")
+
+
+def test_a_script_written_for_the_reference_runs_unchanged(tmp_path):
+    """`python -m litetorch_b200.compat script.py` binds the name `litetorch`: the calls the reference's own Python test makes
+    (tests/test_litetorch.py: from_vector / add / sum / backward, Linear + AdamW + mse_loss, the function form of checkpoint)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "user_script.py"
+    script.write_text('''
+import json
+import litetorch as lt
+from litetorch import nn
+dev = lt.Device("cpu")
+x = lt.Tensor.from_vector([1.0, 2.0, 3.0, 4.0], [2, 2], dev, True)
+y = lt.Tensor.from_vector([2.0, 0.5, 1.0, 2.0], [2, 2], dev, True)
+z = lt.Ops.add(x, y)
+loss = lt.Ops.sum(z)
+loss.backward()
+lin = nn.Linear(2, 1, True)
+opt = lt.optim.AdamW(lin.parameters(), lr=0.01)
+out = lin.forward(lt.Tensor.from_vector([1.0, 2.0], [1, 2], dev, False))
+mse = lt.Ops.mse_loss(out, lt.Tensor.from_vector([5.0], [1, 1], dev, False))
+before = [p.to_vector() for p in lin.parameters()]
+opt.zero_grad(); mse.backward(); opt.step()
+after = [p.to_vector() for p in lin.parameters()]
+xc = lt.Tensor.from_vector([1.0, 2.0, 3.0, 4.0], [4], dev, True)
+cp = lt.checkpoint(lambda t: lt.Ops.add(lt.Ops.mul(t, t), t), xc)
+lt.Ops.sum(cp).backward()
+print("RESULT " + json.dumps({"z": z.to_vector(), "sum": loss.item(), "gx": x.grad.to_vector(), "moved": before != after,
+                              "gcp": xc.grad.to_vector(), "mse": mse.item()}))
+''')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "litetorch_b200.compat", str(script)], capture_output=True, text=True, timeout=300,
+                       cwd=root)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-3000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["z"] == [3.0, 2.5, 4.0, 6.0] and res["sum"] == 15.5 and res["gx"] == [1.0, 1.0, 1.0, 1.0]
+    assert res["moved"] and res["gcp"] == [3.0, 5.0, 7.0, 9.0] and res["mse"] > 0
