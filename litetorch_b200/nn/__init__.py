@@ -197,7 +197,7 @@ class Embedding(Module):
 class LayerNorm(Module):
     def __init__(self, normalized_shape: Sequence[int], eps: float = 1e-5):
         super().__init__()
-        self.normalized_shape, self.eps = list(normalized_shape), eps
+        self.normalized_shape, self.eps = ([int(normalized_shape)] if isinstance(normalized_shape, int) else list(normalized_shape)), eps
         self.weight = _param(torch.ones(*self.normalized_shape))
         self.bias = _param(torch.zeros(*self.normalized_shape))
 

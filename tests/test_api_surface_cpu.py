@@ -86,3 +86,118 @@ print("RESULT " + json.dumps({"z": z.to_vector(), "sum": loss.item(), "gx": x.gr
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert res["z"] == [3.0, 2.5, 4.0, 6.0] and res["sum"] == 15.5 and res["gx"] == [1.0, 1.0, 1.0, 1.0]
     assert res["moved"] and res["gcp"] == [3.0, 5.0, 7.0, 9.0] and res["mse"] > 0
+
+
+def test_the_example_applications_call_patterns_work():
+    """The call shapes of the reference's example applications (train_cat_dog_cnn.py / train_cat_dog.py): positional Conv2d /
+    MaxPool2d / Linear arguments, JIT functions called with a list, reshape with a list, `.forward`, parameter lists that are
+    concatenated, `.to(device)`, dropout train / eval, cross-entropy on float class ids, save / load of a module."""
+    import os
+    import tempfile
+    import torch
+    import litetorch_b200 as lt
+
+    class Net(lt.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1, self.p1 = lt.nn.Conv2d(3, 8, 3, 1, 1, True), lt.nn.MaxPool2d(2, 2, 0)
+            self.c2, self.p2 = lt.nn.Conv2d(8, 16, 3, 1, 1, True), lt.nn.MaxPool2d(2, 2, 0)
+            self.drop = lt.nn.Dropout(0.3)
+            self.norm = lt.nn.LayerNorm([16 * 4 * 4])
+            self.fc1, self.fc2 = lt.nn.Linear(16 * 4 * 4, 32, True), lt.nn.Linear(32, 2, True)
+            v1, v2 = lt.jit.JITVar(lt.jit.OpType.INPUT, "a"), lt.jit.JITVar(lt.jit.OpType.INPUT, "b")
+            self.r1 = lt.jit.JITFunction("relu_a", lt.jit.relu(v1), [v1])
+            self.r2 = lt.jit.JITFunction("relu_b", lt.jit.relu(v2), [v2])
+
+        def forward(self, x):
+            b = x.shape[0]
+            h = self.p1.forward(self.r1([self.c1.forward(x)]))
+            h = self.p2.forward(self.r2([self.c2.forward(h)]))
+            h = self.drop.forward(h).reshape([b, 16 * 4 * 4])
+            return self.fc2.forward(lt.Ops.gelu(self.fc1.forward(self.norm.forward(h))))
+
+        def parameters(self):
+            return self.c1.parameters() + self.c2.parameters() + self.norm.parameters() + self.fc1.parameters() + self.fc2.parameters()
+
+        def to(self, device):
+            for m in (self.c1, self.c2, self.norm, self.fc1, self.fc2):
+                m.to(device)
+
+    lt.manual_seed(0)
+    dev = lt.auto_device() if not lt.is_gpu_available() else lt.Device("cpu")
+    net = Net()
+    net.to(dev)
+    net.drop.eval()
+    g = torch.Generator().manual_seed(0)
+    imgs = torch.randn(8, 3, 16, 16, generator=g)
+    labels = (imgs.mean((1, 2, 3)) > 0).float()
+    x = lt.Tensor.from_vector(imgs.flatten().tolist(), [8, 3, 16, 16], dev, False)
+    y = lt.Tensor.from_vector(labels.tolist(), [8], dev, False)
+    opt = lt.optim.AdamW(net.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        loss = lt.Ops.cross_entropy_loss(net.forward(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.5 * losses[0], losses
+    probs = lt.Ops.softmax(net.forward(x), -1).to_vector()
+    assert len(probs) == 16 and abs(sum(probs[:2]) - 1.0) < 1e-5
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "net.ltw")
+        lt.save(net, path)
+        before = [p.to_vector() for p in net.parameters()]
+        for p in net.parameters():
+            p.add_(lt.Tensor.from_vector([1.0] * p.numel(), p.shape, dev, False))
+        lt.load(net, path)
+        assert [p.to_vector() for p in net.parameters()] == before
+    lt.empty_cache()
+    assert isinstance(lt.get_backend_name(), str) and lt.get_gpu_memory_used() >= 0 and lt.cuda.memory_allocated() >= 0
+
+
+def test_the_vit_example_call_patterns_work():
+    """Call shapes of the reference's ViT example (train_cat_dog.py): MultiHeadAttention(embed, heads).forward on [B, N, E],
+    LayerNorm([E]), a learned position tensor added by broadcasting, transpose(1, 2) followed by a Linear over the patch
+    axis, contiguous().view([B, E]), parameter lists that include a bare Tensor."""
+    import torch
+    import litetorch_b200 as lt
+    B, N, P, E, H = 4, 16, 12, 32, 4
+    dev = lt.Device("cpu")
+    lt.manual_seed(1)
+
+    class Block(lt.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn, self.ln1, self.ln2 = lt.nn.MultiHeadAttention(E, H), lt.nn.LayerNorm([E]), lt.nn.LayerNorm([E])
+            self.fc1, self.fc2 = lt.nn.Linear(E, 2 * E, True), lt.nn.Linear(2 * E, E, True)
+
+        def forward(self, x):
+            x = lt.Ops.add(x, self.attn.forward(self.ln1.forward(x)))
+            return lt.Ops.add(x, self.fc2.forward(lt.Ops.gelu(self.fc1.forward(self.ln2.forward(x)))))
+
+        def parameters(self):
+            return self.attn.parameters() + self.ln1.parameters() + self.fc1.parameters() + self.fc2.parameters() + self.ln2.parameters()
+
+    proj, blk, ln_f = lt.nn.Linear(P, E, True), Block(), lt.nn.LayerNorm([E])
+    pool, head = lt.nn.Linear(N, 1, False), lt.nn.Linear(E, 2, True)
+    pos = lt.Tensor.from_vector((torch.randn(N * E) * 0.02).tolist(), [1, N, E], dev, True)
+
+    def forward(x):
+        h = ln_f.forward(blk.forward(lt.Ops.add(proj.forward(x), pos)))
+        return head.forward(pool.forward(h.transpose(1, 2)).contiguous().view([B, E]))
+
+    params = proj.parameters() + [pos] + blk.parameters() + ln_f.parameters() + pool.parameters() + head.parameters()
+    opt = lt.optim.AdamW(params, lr=3e-3)
+    g = torch.Generator().manual_seed(2)
+    xs = torch.randn(B, N, P, generator=g)
+    x = lt.Tensor.from_vector(xs.flatten().tolist(), [B, N, P], dev, False)
+    y = lt.Tensor.from_vector([0.0, 1.0, 1.0, 0.0], [B], dev, False)
+    losses = []
+    for _ in range(40):
+        opt.zero_grad()
+        loss = lt.Ops.cross_entropy_loss(forward(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert pos.grad is not None and losses[-1] < 0.3 * losses[0], losses
