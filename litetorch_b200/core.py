@@ -235,9 +235,9 @@ class Tensor:
     def clone(self) -> "Tensor":
         return Tensor(self._t.clone(), self._dtype_tag)
 
-    def cast(self, dtype: DataType) -> "Tensor":
+    def cast(self, target_dtype: DataType) -> "Tensor":
         from .quantization import cast_tensor
-        return cast_tensor(self, dtype)
+        return cast_tensor(self, target_dtype)
 
     def copy_(self, other: "Tensor") -> "Tensor":
         with torch.no_grad():

@@ -29,8 +29,8 @@ class Dataset:
     def __len__(self):
         return self.size()
 
-    def __getitem__(self, i):
-        return self.get(i)
+    def __getitem__(self, index):
+        return self.get(index)
 
 
 class TensorDataset(Dataset):

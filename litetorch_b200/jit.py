@@ -62,8 +62,12 @@ def _lib():
 class JITVar:
     """Node handle in the native expression arena."""
 
-    def __init__(self, op_or_val=None, name: str = "", _node: Optional[int] = None):
+    def __init__(self, op_or_val=None, name: str = "", _node: Optional[int] = None, op=None, val=None):
+        """`JITVar(OpType.INPUT, "x")` / `JITVar(2.0)`; the reference's keywords `op=` and `val=` are accepted
+        (src/bindings/python_bindings.cpp:814-815)."""
         lib = _lib()
+        if op_or_val is None:
+            op_or_val = op if op is not None else val
         if _node is not None:
             self.node = _node
         elif isinstance(op_or_val, (int, float)) and not isinstance(op_or_val, OpType):
@@ -139,10 +143,71 @@ def neg(a): return _unary(OpType.NEG, a)
 
 class Tracer:
     @staticmethod
-    def trace(inputs: Sequence[str], func: Callable, name: str = "traced_fn") -> "JITFunction":
-        """Call `func` on symbolic inputs named `inputs` and wrap the resulting tree."""
-        vars_ = [JITVar.input(n) for n in inputs]
-        return JITFunction(name, func(*vars_), vars_)
+    def trace(inputs: Sequence, func: Callable, name: str = "traced_fn") -> "JITFunction":
+        """Two forms.  `trace(["x", "w"], lambda x, w: relu(x * w))`: `func` is called on symbolic inputs of those names.
+        `trace([t1, t2], fn, name)`, the reference's form (src/ops/jit.cpp:496-525): `fn` takes the LIST of example
+        tensors, is run once with autograd recording, and the recorded graph of `lt.Ops` element-wise calls (add, sub, mul,
+        div, neg, relu, gelu, sigmoid, tanh, sqrt, exp, log, abs) between those tensors becomes the expression tree."""
+        if all(isinstance(i, str) for i in inputs):
+            vars_ = [JITVar.input(n) for n in inputs]
+            return JITFunction(name, func(*vars_), vars_)
+        leaves = [_unwrap(t).detach().clone().float().requires_grad_(True) for t in inputs]
+        with torch.enable_grad():
+            out = _unwrap(func([Tensor(l) for l in leaves]))
+        vars_ = [JITVar.input("x%d" % i) for i in range(len(leaves))]
+        used, cache = set(), {}
+        unary = {"relu": relu, "gelu": gelu, "sigmoid": sigmoid, "tanh": tanh, "sqrt": sqrt, "exp": exp, "log": log, "abs": abs}
+
+        def const_of(fn, attr):
+            v = getattr(fn, attr, None)
+            if v is None:
+                raise ValueError("the traced function combines an input with a tensor that is not in the input list")
+            v = v if not torch.is_tensor(v) else (v.item() if v.numel() == 1 else None)
+            if v is None:
+                raise ValueError("the traced function combines an input with a tensor that is not in the input list")
+            return JITVar(float(v))
+
+        def walk(fn):
+            if fn is None:
+                raise ValueError("the traced function's result does not depend on its inputs through element-wise lt.Ops calls")
+            if fn in cache:
+                return cache[fn]
+            kind = fn.name().lower().split("::")[-1]
+            if kind.startswith("accumulategrad"):
+                for i, l in enumerate(leaves):
+                    if fn.variable is l:
+                        used.add(i)
+                        return vars_[i]
+                raise ValueError("the traced graph reaches a tensor that is not in the input list")
+            nxt = [f for f, _ in fn.next_functions]
+            if kind.startswith(("addbackward", "subbackward")):
+                alpha = float(getattr(fn, "_saved_alpha", 1) or 1)
+                if len(nxt) < 2 or nxt[1] is None or nxt[0] is None:
+                    raise ValueError("adding a constant cannot be traced: pass it as an input tensor")
+                rhs = walk(nxt[1]) if alpha == 1.0 else walk(nxt[1]) * alpha
+                res = walk(nxt[0]) + rhs if kind.startswith("add") else walk(nxt[0]) - rhs
+            elif kind.startswith("mulbackward"):
+                a = walk(nxt[0]) if nxt[0] is not None else const_of(fn, "_saved_self")
+                b = walk(nxt[1]) if len(nxt) > 1 and nxt[1] is not None else const_of(fn, "_saved_other")
+                res = a * b
+            elif kind.startswith("divbackward"):
+                a = walk(nxt[0]) if nxt[0] is not None else const_of(fn, "_saved_self")
+                b = walk(nxt[1]) if len(nxt) > 1 and nxt[1] is not None else const_of(fn, "_saved_other")
+                res = a / b
+            elif kind.startswith("negbackward"):
+                res = -walk(nxt[0])
+            else:
+                for key, mk in unary.items():
+                    if kind.startswith(key) or kind.startswith("_" + key):
+                        res = mk(walk(nxt[0]))
+                        break
+                else:
+                    raise ValueError("unsupported operation in the traced function: %s" % fn.name())
+            cache[fn] = res
+            return res
+
+        expr = walk(out.grad_fn)
+        return JITFunction(name, expr, [v for i, v in enumerate(vars_) if i in used])
 
     @staticmethod
     def derivative(var: JITVar, wrt) -> JITVar:
@@ -161,7 +226,8 @@ class Tracer:
             cap = -n + 16
 
     @staticmethod
-    def deserialize_var(text: str) -> JITVar:
+    def deserialize_var(str: str = None, text: str = None) -> JITVar:
+        text = str if text is None else text
         n = _lib().lt_jit_deserialize(text.encode())
         if n < 0:
             raise ValueError("cannot parse expression %r" % text[:80])

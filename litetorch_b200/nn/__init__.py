@@ -173,6 +173,11 @@ class QLoRALinear(Module):
         codes = _unwrap(self.base_codes)
         return NF4_CODEBOOK.to(codes.device)[codes.long()] * _unwrap(self.absmax)
 
+    @property
+    def weight(self) -> Tensor:
+        """The frozen base weight: its NF4 codes (the reference binds the quantised tensor under this name)."""
+        return self.base_codes
+
     def forward(self, x: Tensor) -> Tensor:
         xt = _unwrap(x)
         y = torch.nn.functional.linear(xt, self.base_weight().to(xt.dtype))
@@ -188,6 +193,7 @@ class Embedding(Module):
 
     def __init__(self, num_embeddings: int, embedding_dim: int):
         super().__init__()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
         self.weight = _param(torch.randn(num_embeddings, embedding_dim))
 
     def forward(self, idx: Tensor) -> Tensor:
@@ -218,7 +224,7 @@ class RMSNorm(Module):
 class BatchNorm2d(Module):
     def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1):
         super().__init__()
-        self.eps, self.momentum = eps, momentum
+        self.num_features, self.eps, self.momentum = num_features, eps, momentum
         self.weight = _param(torch.ones(num_features))
         self.bias = _param(torch.zeros(num_features))
         self.running_mean = Tensor(torch.zeros(num_features))
@@ -257,28 +263,28 @@ class Conv3d(Module):
 class MaxPool2d(Module):
     def __init__(self, kernel_size, stride=-1, padding=0):
         super().__init__()
-        self.k, self.s, self.p = kernel_size, stride, padding
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
 
     def forward(self, x):
-        return Ops.max_pool2d(x, self.k, self.s, self.p)
+        return Ops.max_pool2d(x, self.kernel_size, self.stride, self.padding)
 
 
 class MaxPool3d(Module):
     def __init__(self, kernel_size, stride=-1, padding=0):
         super().__init__()
-        self.k, self.s, self.p = kernel_size, stride, padding
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
 
     def forward(self, x):
-        return Ops.max_pool3d(x, self.k, self.s, self.p)
+        return Ops.max_pool3d(x, self.kernel_size, self.stride, self.padding)
 
 
 class AdaptiveAvgPool2d(Module):
     def __init__(self, output_height, output_width):
         super().__init__()
-        self.h, self.w = output_height, output_width
+        self.output_height, self.output_width = output_height, output_width
 
     def forward(self, x):
-        return Ops.adaptive_avg_pool2d(x, self.h, self.w)
+        return Ops.adaptive_avg_pool2d(x, self.output_height, self.output_width)
 
 
 class Dropout(Module):

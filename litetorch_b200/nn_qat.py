@@ -8,11 +8,13 @@ from .core import Tensor, _as_device, _unwrap
 
 
 class QATLinear:
-    def __init__(self, linear, w_scale: float = 0.01, w_zp: float = 0.0, a_scale: float = 0.01, a_zp: float = 0.0, bits: int = 8):
+    def __init__(self, linear, w_scale: float = 0.01, w_zp: float = 0.0, a_scale: float = 0.01, a_zp: float = 0.0, b: int = 8,
+                 bits: int = None):
+        """`b` is the bit width under the reference's keyword (src/bindings/python_bindings.cpp:710-711); `bits` is accepted too."""
         self.weight, self.bias = linear.weight, linear.bias
         self.weight_scale, self.weight_zero_point = w_scale, w_zp
         self.act_scale, self.act_zero_point = a_scale, a_zp
-        self.bits = bits
+        self.bits = int(b if bits is None else bits)
         self.qat_enabled = True
         self.training = True
 

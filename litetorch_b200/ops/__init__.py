@@ -77,7 +77,7 @@ class Ops:
     @staticmethod
     def unsqueeze(a, dim: int): return _w(_unwrap(a).unsqueeze(dim))
     @staticmethod
-    def cast(a, dtype: DataType): return a.cast(dtype)
+    def cast(a, target_dtype: DataType): return a.cast(target_dtype)
 
     # ------------------------------------------------------------------ GEMM
     @staticmethod
@@ -144,16 +144,16 @@ class Ops:
 
     # ------------------------------------------------------------------ normalisation
     @staticmethod
-    def layer_norm(x, normalized_shape, weight=None, bias=None, eps: float = 1e-5):
-        t = _unwrap(x)
+    def layer_norm(input, normalized_shape, weight=None, bias=None, eps: float = 1e-5):
+        t = _unwrap(input)
         D = t.shape[-1]
         if len(list(normalized_shape)) == 1 and weight is not None and bias is not None:
             return _w(Fn.layer_norm(t, _unwrap(weight), _unwrap(bias), eps))
         return _w(F.layer_norm(t, list(normalized_shape), _unwrap(weight), _unwrap(bias), eps))
 
     @staticmethod
-    def fused_add_layernorm(x, residual, normalized_shape, weight=None, bias=None, eps: float = 1e-5):
-        t, r = _unwrap(x), _unwrap(residual)
+    def fused_add_layernorm(input, residual, normalized_shape, weight=None, bias=None, eps: float = 1e-5):
+        t, r = _unwrap(input), _unwrap(residual)
         if len(list(normalized_shape)) == 1 and weight is not None and bias is not None:
             return _w(Fn.layer_norm(t, _unwrap(weight), _unwrap(bias), eps, residual=r))
         return _w(F.layer_norm(t + r, list(normalized_shape), _unwrap(weight), _unwrap(bias), eps))
@@ -163,26 +163,26 @@ class Ops:
         return _w(Fn.rms_norm(_unwrap(x), _unwrap(weight), eps, _unwrap(residual)))
 
     @staticmethod
-    def batch_norm2d(x, running_mean, running_var, weight, bias, training: bool, momentum: float = 0.1, eps: float = 1e-5):
-        return _w(F.batch_norm(_unwrap(x), _unwrap(running_mean), _unwrap(running_var), _unwrap(weight), _unwrap(bias),
+    def batch_norm2d(input, running_mean, running_var, weight, bias, training: bool, momentum: float = 0.1, eps: float = 1e-5):
+        return _w(F.batch_norm(_unwrap(input), _unwrap(running_mean), _unwrap(running_var), _unwrap(weight), _unwrap(bias),
                                training, momentum, eps))
 
     # ------------------------------------------------------------------ vision
     @staticmethod
-    def conv2d(x, weight, bias=None, stride: int = 1, padding: int = 0):
-        return _w(F.conv2d(_unwrap(x), _unwrap(weight), _unwrap(bias), stride, padding))
+    def conv2d(input, weight, bias=None, stride: int = 1, padding: int = 0):
+        return _w(F.conv2d(_unwrap(input), _unwrap(weight), _unwrap(bias), stride, padding))
     @staticmethod
-    def conv3d(x, weight, bias=None, stride: int = 1, padding: int = 0):
-        return _w(F.conv3d(_unwrap(x), _unwrap(weight), _unwrap(bias), stride, padding))
+    def conv3d(input, weight, bias=None, stride: int = 1, padding: int = 0):
+        return _w(F.conv3d(_unwrap(input), _unwrap(weight), _unwrap(bias), stride, padding))
     @staticmethod
-    def max_pool2d(x, kernel_size: int, stride: int = -1, padding: int = 0):
-        return _w(F.max_pool2d(_unwrap(x), kernel_size, kernel_size if stride <= 0 else stride, padding))
+    def max_pool2d(input, kernel_size: int, stride: int = -1, padding: int = 0):
+        return _w(F.max_pool2d(_unwrap(input), kernel_size, kernel_size if stride <= 0 else stride, padding))
     @staticmethod
-    def max_pool3d(x, kernel_size: int, stride: int = -1, padding: int = 0):
-        return _w(F.max_pool3d(_unwrap(x), kernel_size, kernel_size if stride <= 0 else stride, padding))
+    def max_pool3d(input, kernel_size: int, stride: int = -1, padding: int = 0):
+        return _w(F.max_pool3d(_unwrap(input), kernel_size, kernel_size if stride <= 0 else stride, padding))
     @staticmethod
-    def adaptive_avg_pool2d(x, output_height: int, output_width: int):
-        return _w(F.adaptive_avg_pool2d(_unwrap(x), (output_height, output_width)))
+    def adaptive_avg_pool2d(input, output_height: int, output_width: int):
+        return _w(F.adaptive_avg_pool2d(_unwrap(input), (output_height, output_width)))
 
     # ------------------------------------------------------------------ losses
     @staticmethod
@@ -195,8 +195,13 @@ class Ops:
         return _w(F.binary_cross_entropy(p, _unwrap(target)).reshape(1))
     @staticmethod
     def cross_entropy_loss(logits, target):
-        """Mean CE of logits [N, C] against class indices [N] stored as floats or integers."""
-        return _w(Fn.cross_entropy(_unwrap(logits), _unwrap(target)).reshape(1))
+        """Mean CE of logits [N, C] against class indices [N] stored as floats or integers.  A floating-point target of the
+        logits' own shape is read as class probabilities per row (the reference's AMP guide passes such a target,
+        docs-en/7.optimizers_and_amp.md, though its own op insists on a 1-D target, src/ops/loss.cpp:373-375)."""
+        lt_, tt = _unwrap(logits), _unwrap(target)
+        if tt.dim() == 2 and tt.shape == lt_.shape and tt.is_floating_point():
+            return _w(F.cross_entropy(lt_.float(), tt.float()).reshape(1))
+        return _w(Fn.cross_entropy(lt_, tt).reshape(1))
 
     @staticmethod
     def fused_linear_cross_entropy(x, weight, target, bias=None, chunk_rows: int = 4096):
@@ -247,8 +252,10 @@ class Ops:
     @staticmethod
     def paged_attention(q, k_cache, v_cache, block_tables, context_lens, block_size: int):
         from ..serving import paged_attention
-        return _w(paged_attention(_unwrap(q), _unwrap(k_cache), _unwrap(v_cache), _unwrap(block_tables), _unwrap(context_lens),
-                                  block_size))
+        qt, kt, vt = _unwrap(q), _unwrap(k_cache), _unwrap(v_cache)
+        if kt.dim() == 3:        # [num_blocks, block_size, head_dim]: one KV head (the layout the reference's serving guide uses)
+            kt, vt = kt.unsqueeze(1), vt.unsqueeze(1)
+        return _w(paged_attention(qt, kt, vt, _unwrap(block_tables), _unwrap(context_lens), block_size))
 
     @staticmethod
     def flash_decoding(q, k, v, num_splits: int = 4):
@@ -307,15 +314,15 @@ class Ops:
         return _w(top_p.reshape(*lead, top_k)), _w(top_i.reshape(*lead, top_k).to(torch.float32))
 
     @staticmethod
-    def fake_quantize(x, scale: float, zero_point: float = 0.0, bits: int = 8):
+    def fake_quantize(input, scale: float, zero_point: float = 0.0, bits: int = 8):
         from ..quantization import fake_quantize
-        return _w(fake_quantize(_unwrap(x), scale, zero_point, bits))
+        return _w(fake_quantize(_unwrap(input), scale, zero_point, bits))
 
     @staticmethod
-    def checkpoint(module, x):
+    def checkpoint(module, input):
         """Activation checkpointing, module form (src/ops/checkpoint.cpp:8-96)."""
         from torch.utils.checkpoint import checkpoint as ckpt
-        xt = _unwrap(x)
+        xt = _unwrap(input)
         if not xt.requires_grad:
             xt = xt.detach().requires_grad_(True)
         return _w(ckpt(lambda t: _unwrap(module.forward(Tensor(t))), xt, use_reentrant=False))

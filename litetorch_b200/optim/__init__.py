@@ -30,6 +30,12 @@ class Optimizer:
     def step(self):
         raise NotImplementedError
 
+    def get_lr(self) -> float:
+        return self.lr
+
+    def set_lr(self, new_lr: float) -> None:
+        self.lr = float(new_lr)
+
     def _tensors(self):
         return [_unwrap(p) for p in self.params]
 
@@ -458,11 +464,15 @@ class ZeRO3Optimizer(_AdamBase):
 class StepLR:
     def __init__(self, optimizer: Optimizer, step_size: int, gamma: float = 0.1):
         self.optimizer, self.step_size, self.gamma = optimizer, step_size, gamma
-        self.base_lr, self.epoch = optimizer.lr, 0
+        self.base_lr, self.last_epoch = optimizer.lr, 0      # `last_epoch`: steps taken, the reference's field (include/litetorch/optim.h:131)
+
+    @property
+    def epoch(self) -> int:
+        return self.last_epoch
 
     def step(self):
-        self.epoch += 1
-        self.optimizer.lr = self.base_lr * (self.gamma ** (self.epoch // self.step_size))
+        self.last_epoch += 1
+        self.optimizer.lr = self.base_lr * (self.gamma ** (self.last_epoch // self.step_size))
 
     def get_lr(self) -> float:
         return self.optimizer.lr
@@ -471,11 +481,15 @@ class StepLR:
 class CosineAnnealingLR:
     def __init__(self, optimizer: Optimizer, T_max: int, eta_min: float = 0.0):
         self.optimizer, self.T_max, self.eta_min = optimizer, T_max, eta_min
-        self.base_lr, self.epoch = optimizer.lr, 0
+        self.base_lr, self.last_epoch = optimizer.lr, 0
+
+    @property
+    def epoch(self) -> int:
+        return self.last_epoch
 
     def step(self):
-        self.epoch += 1
-        t = min(self.epoch, self.T_max)
+        self.last_epoch += 1
+        t = min(self.last_epoch, self.T_max)
         self.optimizer.lr = self.eta_min + (self.base_lr - self.eta_min) * (1 + math.cos(math.pi * t / self.T_max)) / 2
 
     def get_lr(self) -> float:

@@ -61,8 +61,23 @@ class DeviceMesh:
             r = r * s + c
         return r
 
-    def get_rank(self) -> int:
-        return self._rank
+    def get_rank(self, coords: Optional[Sequence[int]] = None) -> int:
+        """This process's rank, or with `coords` the rank at those mesh coordinates (the reference's signature,
+        src/bindings/python_bindings.cpp:743; its implementation returns 0 for every input)."""
+        return self._rank if coords is None else self.rank_of(coords)
+
+    # the reference's field names (include/litetorch/device_mesh.h:12-14)
+    @property
+    def mesh_shape(self) -> List[int]:
+        return self.shape
+
+    @property
+    def mesh_dim_names(self) -> str:
+        return ",".join(self.dim_names)
+
+    @property
+    def mesh_topology(self) -> List[int]:
+        return list(range(self.world))
 
     def get_coordinate(self) -> List[int]:
         return self.coords_of(self._rank)
@@ -124,7 +139,13 @@ class DTensor:
 
     def __init__(self, local_tensor: Tensor, mesh: DeviceMesh, placements: Sequence[Placement]):
         self.local_tensor, self.mesh, self.placements = local_tensor, mesh, list(placements)
+        # fewer placements than mesh axes (the reference's guide builds a DTensor on a 2-D mesh from one): the rest replicate
+        self.placements += [Placement.replicate() for _ in range(len(mesh.shape) - len(self.placements))]
         assert len(self.placements) == len(mesh.shape)
+
+    @property
+    def device_mesh(self) -> DeviceMesh:
+        return self.mesh
 
     def to_local(self) -> Tensor:
         return self.local_tensor
@@ -132,7 +153,18 @@ class DTensor:
     def full_tensor(self) -> Tensor:
         return self.redistribute([Placement.replicate()] * len(self.placements)).local_tensor
 
-    def redistribute(self, placements: Sequence[Placement]) -> "DTensor":
+    def redistribute(self, new_mesh=None, new_placements: Optional[Sequence[Placement]] = None, placements=None) -> "DTensor":
+        """`redistribute(placements)` or, with the reference's arguments, `redistribute(new_mesh, new_placements)`
+        (src/bindings/python_bindings.cpp:762); the mesh must be the tensor's own mesh (same shape)."""
+        if placements is None:
+            if new_placements is not None:
+                placements = new_placements
+            elif new_mesh is not None and not isinstance(new_mesh, DeviceMesh):
+                placements, new_mesh = new_mesh, None
+        if isinstance(new_mesh, DeviceMesh) and list(new_mesh.shape) != list(self.mesh.shape):
+            raise ValueError("redistribute onto a mesh of another shape is not supported: %s vs %s" % (new_mesh.shape, self.mesh.shape))
+        if placements is None:
+            raise TypeError("redistribute needs the new placements")
         t = _unwrap(self.local_tensor)
         cur = list(self.placements)
         for ax, (src, dst) in enumerate(zip(cur, placements)):

@@ -90,8 +90,9 @@ class PipelineParallelModule:
         return t
 
     # ---- forward only
-    def forward(self, x: Optional[Tensor] = None) -> Optional[Tensor]:
+    def forward(self, input: Optional[Tensor] = None) -> Optional[Tensor]:
         """recv (unless first) -> local module -> send (unless last).  Returns the output on the last stage."""
+        x = input
         if not self.is_first and self.world > 1:
             x = Tensor(self._recv_activation(self.rank - 1))
         out = self.local_module(x)

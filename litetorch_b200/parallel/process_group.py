@@ -295,8 +295,19 @@ class ProcessGroup:
         dist.send(hdr.to(t.device) if t.is_cuda else hdr, dst)
         dist.send(t, dst)
 
-    def recv_tensor(self, src: int, device=None) -> Tensor:
+    def recv_tensor(self, tensor=None, src: Optional[int] = None, device=None) -> Tensor:
+        """`recv_tensor(src)` returns the tensor rank `src` sent with `send_tensor` (shape and dtype travel with it);
+        `recv_tensor(tensor, src)`, the reference's form (src/bindings/python_bindings.cpp:735), also copies it into `tensor`."""
         from ..core import _as_device
+        dst = None
+        if isinstance(tensor, Tensor) or torch.is_tensor(tensor):
+            dst = tensor
+        elif tensor is not None and src is None:
+            src = int(tensor)
+        if src is None:
+            raise TypeError("recv_tensor needs the source rank")
+        if dst is not None and device is None:
+            device = _unwrap(dst).device
         dev = _as_device(device) if device is not None else (torch.device("cuda", torch.cuda.current_device())
                                                              if dist.get_backend() == "nccl" else torch.device("cpu"))
         hdr = torch.zeros(10, dtype=torch.int64, device=dev)
@@ -305,6 +316,10 @@ class ProcessGroup:
         dtype = {0: torch.float32, 1: torch.bfloat16, 2: torch.float16, 3: torch.int64}[int(h[1])]
         t = torch.empty([int(x) for x in h[2:2 + int(h[0])]], dtype=dtype, device=dev)
         dist.recv(t, src)
+        if dst is not None:
+            with torch.no_grad():
+                _unwrap(dst).copy_(t.reshape(_unwrap(dst).shape))
+            return dst if isinstance(dst, Tensor) else Tensor(dst)
         return Tensor(t)
 
     def sync_comm(self) -> None:
@@ -401,8 +416,8 @@ class OverlappedAllReducer:
         self._works.clear()
 
 
-def overlapped_all_reduce(t: Tensor) -> None:
-    OverlappedAllReducer.get().push_and_all_reduce(t)
+def overlapped_all_reduce(tensor: Tensor) -> None:
+    OverlappedAllReducer.get().push_and_all_reduce(tensor)
 
 
 def overlapped_reduce_scatter(shard: Tensor, full: Tensor) -> None:

@@ -183,11 +183,12 @@ def _adam_states(opt):
     return ms, vs
 
 
-def save_optimizer_state(opt, filepath: str) -> None:
+def save_optimizer_state(optimizer, filepath: str) -> None:
     """SGD -> LTSG, RMSprop -> LTRP, Adam -> LTAD, AdamW family -> LTAW.  The Adam formats hold step count, m and v
     (the reference's layout, src/serialization/checkpoint.cpp) and, when the optimizer keeps fp32 master copies of
     low-precision parameters, those masters in a trailing record, so that a resumed bf16 run continues from the
     exact fp32 weights instead of their rounded copies."""
+    opt = optimizer
     lib = _lib()
     kind = _opt_kind(opt)
     w = lib.lt_ckpt_writer_open(filepath.encode(), kind)
@@ -215,7 +216,8 @@ def save_optimizer_state(opt, filepath: str) -> None:
         raise CheckpointError("write failure while closing %s" % filepath)
 
 
-def load_optimizer_state(opt, filepath: str) -> None:
+def load_optimizer_state(optimizer, filepath: str) -> None:
+    opt = optimizer
     from . import optim as O
     kind = _opt_kind(opt)
     r = _Reader(filepath, [kind])

@@ -293,8 +293,14 @@ class PrefixCache:
             PrefixCache._inst = PrefixCache()
         return PrefixCache._inst
 
-    def put(self, prefix: Sequence[int], kv_cache: Sequence[Tensor], blocks: Sequence[int] = ()):
+    def put(self, prefix: Sequence[int], kv_cache, blocks: Sequence[int] = (), *more):
+        """`put(prefix, [k, v, ...])` (include/litetorch/llm_serving.h:18); the tensors may also be passed one by one,
+        `put(prefix, k, v)`, as the reference's serving guide writes it.  `blocks`: KV blocks that hold the prefix."""
         key = tuple(int(t) for t in prefix)
+        if isinstance(kv_cache, Tensor) or torch.is_tensor(kv_cache):
+            kv_cache = [kv_cache] + ([blocks] if isinstance(blocks, Tensor) or torch.is_tensor(blocks) else []) + list(more)
+            if len(kv_cache) > 1:
+                blocks = ()
         self._kv[key] = list(kv_cache)
         self._lib.lt_prefix_insert(self._c, _i32(key), len(key), _i32(blocks), len(blocks))
 

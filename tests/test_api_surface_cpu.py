@@ -201,3 +201,85 @@ def test_the_vit_example_call_patterns_work():
         opt.step()
         losses.append(loss.item())
     assert pos.grad is not None and losses[-1] < 0.3 * losses[0], losses
+
+
+def test_keyword_names_and_fields_of_the_reference_bindings():
+    """Keyword names (py::arg) and read-write fields (def_readwrite) of src/bindings/python_bindings.cpp that differ from the
+    obvious Python spelling: each must be accepted / present here too."""
+    import inspect
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200 import data as DT, distributed as D, jit as J, nn, optim, quantization as Q
+
+    def accepts(fn, *names):
+        ps = inspect.signature(fn).parameters
+        return all(n in ps for n in names)
+
+    assert accepts(lt.Tensor.cast, "target_dtype") and accepts(lt.Ops.cast, "a", "target_dtype")
+    for f in ("layer_norm", "fused_add_layernorm", "batch_norm2d", "conv2d", "conv3d", "max_pool2d", "max_pool3d", "adaptive_avg_pool2d",
+              "fake_quantize"):
+        assert accepts(getattr(lt.Ops, f), "input"), f
+    assert accepts(lt.Ops.checkpoint, "module", "input")
+    assert accepts(lt.save_optimizer_state, "optimizer", "filepath") and accepts(lt.load_optimizer_state, "optimizer", "filepath")
+    assert accepts(D.ProcessGroup.recv_tensor, "tensor", "src") and accepts(D.overlapped_all_reduce, "tensor")
+    assert accepts(D.DeviceMesh.get_rank, "coords") and accepts(D.DTensor.redistribute, "new_mesh", "new_placements")
+    assert accepts(D.PipelineParallelModule.forward, "input") and accepts(DT.Dataset.__getitem__, "index")
+    assert accepts(J.JITVar.__init__, "op", "name", "val") and accepts(J.Tracer.deserialize_var, "str")
+    assert accepts(Q.QATLinear.__init__, "linear", "w_scale", "w_zp", "a_scale", "a_zp", "b")
+
+    lin = nn.Linear(4, 4, True)
+    opt = optim.AdamW(lin.parameters(), lr=0.5)
+    opt.set_lr(new_lr=0.25)
+    assert opt.get_lr() == 0.25 and opt.lr == 0.25
+    for cls in (optim.SGD, optim.Adam, optim.AdamW8bit, optim.AdamWFP8, optim.RMSprop):
+        o = cls(lin.parameters())
+        o.set_lr(0.125)
+        assert o.get_lr() == 0.125
+    sch = optim.StepLR(opt, step_size=2, gamma=0.5)
+    for _ in range(2):
+        sch.step()
+    assert sch.last_epoch == 2 and opt.lr == 0.125
+    cos = optim.CosineAnnealingLR(opt, T_max=4, eta_min=0.0)
+    cos.step()
+    assert cos.last_epoch == 1
+    assert Q.QATLinear(lin, b=4).bits == 4 and J.JITVar(val=2.0).val == 2.0 and J.JITVar(op=J.OpType.INPUT, name="q").name == "q"
+    fields = [(nn.QLoRALinear(4, 4), ["weight", "bias", "lora_A", "lora_B", "scaling"]),
+              (nn.BatchNorm2d(2), ["num_features", "eps", "momentum", "running_mean", "running_var"]),
+              (nn.MaxPool2d(2, 2, 0), ["kernel_size", "stride", "padding"]), (nn.MaxPool3d(2), ["kernel_size", "stride", "padding"]),
+              (nn.AdaptiveAvgPool2d(1, 1), ["output_height", "output_width"]), (nn.Embedding(5, 3), ["num_embeddings", "embedding_dim", "weight"]),
+              (nn.LayerNorm([4]), ["weight", "bias", "eps", "normalized_shape"]), (nn.MultiHeadAttention(8, 2), ["embed_dim", "num_heads", "head_dim"])]
+    for obj, names in fields:
+        assert all(hasattr(obj, n) for n in names), (type(obj).__name__, names)
+    mesh = D.DeviceMesh([2, 2], "tp,dp", rank=0, create_groups=False)
+    assert mesh.mesh_shape == [2, 2] and mesh.mesh_dim_names == "tp,dp" and mesh.mesh_topology == [0, 1, 2, 3]
+    assert mesh.get_rank() == 0 and mesh.get_rank(coords=[1, 0]) == 2
+    pl = D.Placement()
+    pl.type, pl.dim = D.PlacementType.SHARD, 0
+    dt = D.DTensor(lt.Tensor(torch.ones(2, 2)), mesh, [pl])                  # one placement on a 2-D mesh: the rest replicate
+    assert dt.device_mesh is mesh and len(dt.placements) == 2
+    same = dt.redistribute(mesh, dt.placements)
+    assert same.placements == dt.placements
+
+
+def test_tracer_follows_the_reference_form():
+    """`Tracer.trace([tensors], fn(list) -> Tensor, name)` records the lt.Ops calls between the example tensors
+    (src/ops/jit.cpp:496-525); the symbolic form with input names keeps working."""
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200.core import _unwrap
+    dev = lt.Device("cpu")
+    a = lt.Tensor.from_vector([1.0, -2.0, 3.0], [3], dev, False)
+    b = lt.Tensor.from_vector([0.5, 1.5, -2.0], [3], dev, False)
+    fn = lt.jit.Tracer.trace([a, b], lambda args: lt.Ops.gelu(lt.Ops.add(lt.Ops.mul(args[0], args[1]), args[0])), "fused")
+    got = _unwrap(fn([a, b]))
+    ref = torch.nn.functional.gelu(_unwrap(a) * _unwrap(b) + _unwrap(a), approximate="tanh")
+    assert torch.allclose(got, ref, atol=1e-5) and fn.input_names == ["x0", "x1"]
+    x2 = lt.Tensor.from_vector([2.0, 0.0, -1.0], [3], dev, True)
+    out = fn([x2, b])
+    lt.Ops.sum(out).backward()
+    assert x2.grad is not None
+    sym = lt.jit.Tracer.trace(["x", "w"], lambda x, w: lt.jit.relu(x * 2.0 + w), "sym")
+    assert _unwrap(sym([a, b])).tolist() == [2.5, 0.0, 4.0]
+    import pytest
+    with pytest.raises(ValueError):
+        lt.jit.Tracer.trace([a], lambda args: lt.Ops.softmax(args[0], -1), "unsupported")
