@@ -59,6 +59,10 @@ def _lib():
     return lib
 
 
+# the reference exports the operator codes into the module too (py::enum_::export_values on OpType)
+globals().update({_m.name: _m for _m in OpType})
+
+
 class JITVar:
     """Node handle in the native expression arena."""
 

@@ -14,3 +14,7 @@ from .elastic import ElasticLauncher
 from ..core import manual_seed
 
 __all__ = [n for n in dir() if not n.startswith("_")]
+
+# the reference's bindings export the enum values into the module as well (py::enum_::export_values,
+# src/bindings/python_bindings.cpp:748-752)
+SHARD, REPLICATE, PARTIAL = PlacementType.SHARD, PlacementType.REPLICATE, PlacementType.PARTIAL

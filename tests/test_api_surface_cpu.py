@@ -283,3 +283,10 @@ def test_tracer_follows_the_reference_form():
     import pytest
     with pytest.raises(ValueError):
         lt.jit.Tracer.trace([a], lambda args: lt.Ops.softmax(args[0], -1), "unsupported")
+
+
+def test_enum_values_are_exported_into_their_modules():
+    import litetorch_b200 as lt
+    assert lt.distributed.SHARD is lt.distributed.PlacementType.SHARD and lt.distributed.PARTIAL is lt.distributed.PlacementType.PARTIAL
+    assert lt.jit.INPUT is lt.jit.OpType.INPUT and lt.jit.GELU is lt.jit.OpType.GELU and callable(lt.jit.gelu)
+    assert lt.CPU is lt.DeviceType.CPU and lt.FP32 is lt.DataType.FP32
