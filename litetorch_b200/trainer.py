@@ -76,6 +76,22 @@ class Trainer:
                    seed=run.seed, activation_checkpointing=run.activation_checkpointing,
                    parallel=("hybrid" if p.tp > 1 else "fsdp") if (p.zero_stage >= 1 or p.tp > 1) else "none", tp=p.tp, **kw)
 
+    # The learning rate lives in the engine and is read at every optimizer step; with these three members a trainer can
+    # stand where the LR schedulers expect an optimizer: `lt.optim.CosineAnnealingLR(trainer, T_max=...)`.
+    @property
+    def lr(self) -> float:
+        return self.engine.lr
+
+    @lr.setter
+    def lr(self, value: float) -> None:
+        self.engine.lr = float(value)
+
+    def get_lr(self) -> float:
+        return self.engine.lr
+
+    def set_lr(self, new_lr: float) -> None:
+        self.engine.lr = float(new_lr)
+
     def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """Batch already on the device; returns the loss as a device scalar (no host sync)."""
         return self.engine.train_step(tokens, targets)

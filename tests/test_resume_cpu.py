@@ -341,3 +341,28 @@ def test_trainer_checkpoint_carries_the_data_loader_position(tmp_path):
     tr2.load(ck, loader=dl2)
     rest = run(tr2, dl2, 4)
     assert first == full[:4] and all(abs(a - b) < 1e-6 for a, b in zip(rest, full[4:])), (rest, full)
+
+
+def test_lr_schedulers_drive_a_trainer():
+    """`StepLR` / `CosineAnnealingLR` set `.lr` on whatever they are given: a Trainer exposes the engine's learning rate under that
+    name, and the step really uses it (a run whose rate is cut to zero stops moving)."""
+    import torch
+    import litetorch_b200 as lt
+    from litetorch_b200.models.llama import LlamaConfig
+    from litetorch_b200.trainer import Trainer
+    cfg = LlamaConfig.tiny()
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(4))
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    tr = Trainer(cfg, seed=3, lr=1e-3, device="cpu", param_dtype=torch.float32, parallel="none")
+    sch = lt.optim.CosineAnnealingLR(tr, T_max=4, eta_min=0.0)
+    rates = []
+    for _ in range(4):
+        tr.step(x, y)
+        sch.step()
+        rates.append(tr.get_lr())
+    assert rates[0] < 1e-3 and rates == sorted(rates, reverse=True) and abs(rates[-1]) < 1e-12 and tr.engine.lr == rates[-1]
+    frozen = [tr.step(x, y) for _ in range(3)]          # rate 0: the weights no longer change (weight decay is scaled by the rate too)
+    assert abs(frozen[1] - frozen[2]) < 1e-7
+    tr.set_lr(1e-3)
+    moving = [tr.step(x, y) for _ in range(3)]
+    assert moving[2] < moving[0] - 1e-4
