@@ -471,6 +471,25 @@ class LlamaEngine:
         return loss
 
 
+    def train_step_accumulated(self, micro_batches) -> torch.Tensor:
+        """One optimizer step over several micro-batches (gradient accumulation): `micro_batches` is a sequence of
+        (tokens, targets) pairs of equal size; every micro-batch's gradient is scaled by 1 / k and added into the flat
+        gradient buffer, the sharded reduce + AdamW of each bucket runs under the LAST micro-batch's backward pass.
+        Returns the mean loss (device scalar).  Equal to `train_step` on the concatenated batch up to rounding."""
+        k = len(micro_batches)
+        if k == 1:
+            return self.train_step(*micro_batches[0])
+        self.w.begin_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
+                          weight_decay=self.weight_decay, step=self.step_count + 1)
+        total = None
+        for i, (tok, tgt) in enumerate(micro_batches):
+            loss = self.forward_backward(tok, tgt, accumulate=i > 0, loss_scale=1.0 / k, fused_update=(i == k - 1))
+            total = loss / k if total is None else total + loss / k
+        self.optimizer_step()
+        self.w.finish_step()
+        return total
+
+
 class TorchLlama(torch.nn.Module):
     """The same architecture in stock PyTorch (fp32 or bf16): oracle for the tests and the cuBLAS/SDPA baseline."""
 

@@ -96,14 +96,22 @@ class Trainer:
         """Batch already on the device; returns the loss as a device scalar (no host sync)."""
         return self.engine.train_step(tokens, targets)
 
-    def step(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor) -> float:
+    def step(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor, micro_batches: int = 1) -> float:
+        """One optimizer step on a host batch: copy in, train, read the loss back.  micro_batches > 1 splits the batch along
+        its first axis and accumulates the gradients (`LlamaEngine.train_step_accumulated`; checked against the one-batch step
+        on CPU and gloo ranks)."""
         if self._tok is None or self._tok.shape != tokens_cpu.shape:
             self._tok = torch.empty(tokens_cpu.shape, dtype=torch.int64, device=self.device)
             self._tgt = torch.empty(targets_cpu.shape, dtype=torch.int64, device=self.device)
         self._tok.copy_(tokens_cpu, non_blocking=True)
         self._tgt.copy_(targets_cpu, non_blocking=True)
         self.h2d_bytes = tokens_cpu.numel() * tokens_cpu.element_size() + targets_cpu.numel() * targets_cpu.element_size()
-        loss = self.engine.train_step(self._tok, self._tgt)
+        if micro_batches > 1:
+            if tokens_cpu.shape[0] % micro_batches:
+                raise ValueError("%d sequences do not split into %d micro-batches" % (tokens_cpu.shape[0], micro_batches))
+            loss = self.engine.train_step_accumulated(list(zip(self._tok.chunk(micro_batches), self._tgt.chunk(micro_batches))))
+        else:
+            loss = self.engine.train_step(self._tok, self._tgt)
         out = loss.float().cpu()
         self.d2h_bytes = out.numel() * out.element_size()
         if self._metrics is not None:

@@ -184,3 +184,53 @@ def test_trainer_from_config_builds_the_fsdp_tp_layout(tmp_path):
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert res["tp"] == 2 and res["dp"] == 2 and res["weights"] == "HybridWeights"
     assert res["losses"][2] < res["losses"][0]
+
+
+ACCUM_WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, %(root)r)
+import torch.distributed as dist
+from litetorch_b200.models.llama import LlamaConfig
+from litetorch_b200.trainer import Trainer
+rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+tp = %(tp)d
+torch.set_num_threads(2)
+cfg = LlamaConfig.tiny()
+dp = world // tp
+data = torch.randint(0, cfg.vocab_size, (3, dp * 4, 65), generator=torch.Generator().manual_seed(7))
+def batch(s):
+    d = rank // tp
+    return data[s, d * 4:(d + 1) * 4, :-1].contiguous(), data[s, d * 4:(d + 1) * 4, 1:].contiguous()
+make = lambda: Trainer(cfg, seed=3, tp=tp, device="cpu", param_dtype=torch.float32, parallel="hybrid" if world > 1 else "none")
+a, b = make(), make()
+la = [a.step(*batch(s)) for s in range(3)]
+lb = [b.step(*batch(s), micro_batches=2) for s in range(3)]
+sa = torch.cat([t.flatten().float() for t in a.engine.w.state_tensors().values()])
+sb = torch.cat([t.flatten().float() for t in b.engine.w.state_tensors().values()])
+if rank == 0:
+    print("RESULT " + json.dumps({"la": la, "lb": lb, "diff": float((sa - sb).abs().max())}))
+if world > 1:
+    dist.barrier()
+    dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("nproc,tp", [(1, 1), (4, 2)])
+def test_gradient_accumulation_equals_the_one_batch_step(tmp_path, nproc, tp):
+    """`Trainer.step(..., micro_batches=2)`: two half batches accumulated into one AdamW step give the losses and the
+    parameters / moments of the whole batch in one pass, on one rank and on dp2 x tp2 gloo ranks."""
+    script = os.path.join(str(tmp_path), "accum_worker.py")
+    with open(script, "w") as f:
+        f.write(ACCUM_WORKER % {"root": ROOT, "tp": tp})
+    if nproc == 1:
+        cmd = [sys.executable, script]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
+               "127.0.0.1", "--master-port", "29883", script]
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert all(abs(x - y) < 1e-5 for x, y in zip(res["la"], res["lb"])) and res["diff"] < 1e-4, res
