@@ -24,7 +24,9 @@ from .models.llama import LlamaConfig, LlamaEngine
 class Trainer:
     def __init__(self, cfg: LlamaConfig, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, seed: int = 0, activation_checkpointing: bool = False,
-                 device: Optional[str] = None, parallel: str = "auto", tp: int = 1, param_dtype=torch.bfloat16):
+                 device: Optional[str] = None, parallel: str = "auto", tp: int = 1, param_dtype=torch.bfloat16,
+                 micro_batches: int = 1):
+        self.micro_batches = max(1, int(micro_batches))     # default split of a `step` batch (gradient accumulation)
         self.rank = int(os.environ.get("RANK", "0"))
         self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -74,7 +76,8 @@ class Trainer:
         o = run.optim
         return cls(run.llama_config(), lr=o.lr, betas=(o.beta1, o.beta2), eps=o.eps, weight_decay=o.weight_decay,
                    seed=run.seed, activation_checkpointing=run.activation_checkpointing,
-                   parallel=("hybrid" if p.tp > 1 else "fsdp") if (p.zero_stage >= 1 or p.tp > 1) else "none", tp=p.tp, **kw)
+                   parallel=("hybrid" if p.tp > 1 else "fsdp") if (p.zero_stage >= 1 or p.tp > 1) else "none", tp=p.tp,
+                   **dict({"micro_batches": getattr(run, "micro_batches", 1)}, **kw))
 
     # The learning rate lives in the engine and is read at every optimizer step; with these three members a trainer can
     # stand where the LR schedulers expect an optimizer: `lt.optim.CosineAnnealingLR(trainer, T_max=...)`.
@@ -96,7 +99,7 @@ class Trainer:
         """Batch already on the device; returns the loss as a device scalar (no host sync)."""
         return self.engine.train_step(tokens, targets)
 
-    def step(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor, micro_batches: int = 1) -> float:
+    def step(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor, micro_batches: Optional[int] = None) -> float:
         """One optimizer step on a host batch: copy in, train, read the loss back.  micro_batches > 1 splits the batch along
         its first axis and accumulates the gradients (`LlamaEngine.train_step_accumulated`; checked against the one-batch step
         on CPU and gloo ranks)."""
@@ -106,6 +109,7 @@ class Trainer:
         self._tok.copy_(tokens_cpu, non_blocking=True)
         self._tgt.copy_(targets_cpu, non_blocking=True)
         self.h2d_bytes = tokens_cpu.numel() * tokens_cpu.element_size() + targets_cpu.numel() * targets_cpu.element_size()
+        micro_batches = self.micro_batches if micro_batches is None else int(micro_batches)
         if micro_batches > 1:
             if tokens_cpu.shape[0] % micro_batches:
                 raise ValueError("%d sequences do not split into %d micro-batches" % (tokens_cpu.shape[0], micro_batches))
