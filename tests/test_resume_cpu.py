@@ -238,36 +238,43 @@ dist.destroy_process_group()
 '''
 
 
-@pytest.mark.parametrize("mode", ["exit", "hang"])
-def test_elastic_launcher_restarts_the_group_and_the_run_ends_on_the_uninterrupted_curve(tmp_path, mode):
-    """Rank 1 dies (or stops beating and hangs) after the third step of the first attempt; the launcher stops the other rank,
-    restarts both, they resume from the checkpoint and the last three losses equal those of a run nobody interrupted."""
+def _elastic_run(tmp, ck_name, mode, port):
     from litetorch_b200.parallel.elastic import ElasticLauncher
-    script = os.path.join(str(tmp_path), "w.py")
-    with open(script, "w") as f:
-        f.write(ELASTIC_WORKER % {"root": ROOT})
+    script = os.path.join(tmp, "w.py")
+    if not os.path.exists(script):
+        with open(script, "w") as f:
+            f.write(ELASTIC_WORKER % {"root": ROOT})
     env = dict(os.environ, OMP_NUM_THREADS="2")
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
+    ck, logs = os.path.join(tmp, ck_name), os.path.join(tmp, "logs_" + ck_name)
+    res = ElasticLauncher([sys.executable, script, ck, mode], nproc=2, max_restarts=2, base_port=port, heartbeat_ttl_s=2.0,
+                          start_grace_s=120.0, env=env, log_dir=logs).run()
+    out = []
+    for a in range(len(res["attempts"])):
+        with open(os.path.join(logs, "attempt%d_rank0.log" % a)) as f:
+            out += [json.loads(l[7:]) for l in f.read().splitlines() if l.startswith("RESULT ")]
+    return res, out
 
-    def run(ck, m, port):
-        logs = os.path.join(str(tmp_path), "logs_" + os.path.basename(ck))
-        res = ElasticLauncher([sys.executable, script, ck, m], nproc=2, max_restarts=2, base_port=port, heartbeat_ttl_s=2.0,
-                              start_grace_s=120.0, env=env, log_dir=logs).run()
-        out = []
-        for a in range(len(res["attempts"])):
-            with open(os.path.join(logs, "attempt%d_rank0.log" % a)) as f:
-                out += [json.loads(l[7:]) for l in f.read().splitlines() if l.startswith("RESULT ")]
-        return res, out
 
-    ref, ref_out = run(os.path.join(str(tmp_path), "ck_ref"), "none", 29640 if mode == "exit" else 29680)
-    assert ref["ok"] and ref["restarts"] == 0 and len(ref_out) == 1 and len(ref_out[0]["losses"]) == 6
-    res, out = run(os.path.join(str(tmp_path), "ck"), mode, 29660 if mode == "exit" else 29700)
+@pytest.fixture(scope="module")
+def uninterrupted_run(tmp_path_factory):
+    tmp = str(tmp_path_factory.mktemp("elastic_ref"))
+    res, out = _elastic_run(tmp, "ck_ref", "none", 29640)
+    assert res["ok"] and res["restarts"] == 0 and len(out) == 1 and len(out[0]["losses"]) == 6
+    return out[0]["losses"]
+
+
+@pytest.mark.parametrize("mode", ["exit", "hang"])
+def test_elastic_launcher_restarts_the_group_and_the_run_ends_on_the_uninterrupted_curve(tmp_path, mode, uninterrupted_run):
+    """Rank 1 dies (or stops beating and hangs) after the third step of the first attempt; the launcher stops the other rank,
+    restarts both, they resume from the checkpoint and the last three losses equal those of a run nobody interrupted."""
+    res, out = _elastic_run(str(tmp_path), "ck", mode, 29660 if mode == "exit" else 29700)
     assert res["ok"] and res["restarts"] == 1, res
     first = res["attempts"][0]
     assert ("exited with code 17" in first["reason"]) if mode == "exit" else ("heartbeats" in first["reason"]), first
     assert len(out) == 1 and out[0]["attempt"] == 1 and out[0]["start"] == 3
-    assert all(abs(x - y) < 1e-6 for x, y in zip(out[0]["losses"], ref_out[0]["losses"][3:])), (out, ref_out)
+    assert all(abs(x - y) < 1e-6 for x, y in zip(out[0]["losses"], uninterrupted_run[3:])), (out, uninterrupted_run)
 
 
 def test_trainer_checkpoints_are_complete_or_absent(tmp_path):
