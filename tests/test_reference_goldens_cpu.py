@@ -1,0 +1,118 @@
+"""Expected values that the reference's own C++ tests assert, replayed through this package's Python API on the CPU
+(tests/stage4_test.cpp: asymmetric calibration + fake quantisation, JIT forward / saved / derivative functions;
+tests/audit_bugs_test.cpp: conv3d on a transposed view, gradient accumulation when a tensor is used twice)."""
+import litetorch_b200 as lt
+
+CPU = lt.Device("cpu")
+
+
+def _t(v, shape, grad=False):
+    return lt.Tensor.from_vector([float(x) for x in v], shape, CPU, grad)
+
+
+def test_asymmetric_calibration_and_fake_quantize():
+    t = _t([-10.0, -5.0, 0.0, 2.0], [4])
+    cal = lt.quantization.Calibrator()
+    cal.collect("test_layer", t)
+    scale, zp = cal.get_asymmetric_params("test_layer", 8)
+    assert scale > 0.0 and -127.0 <= zp <= 127.0
+    q = lt.Ops.fake_quantize(t, scale, zp, 8).to_vector()
+    assert abs(q[0] + 10.0) < 0.1 and abs(q[3] - 2.0) < 0.1
+
+
+def test_jit_forward_saved_and_derivative_functions(tmp_path):
+    J = lt.jit
+    x, y = J.JITVar(J.OpType.INPUT, "x"), J.JITVar(J.OpType.INPUT, "y")
+    expr = J.relu(x * y)
+    fwd = J.JITFunction("fwd", expr, [x, y])
+    bwd = J.JITFunction("bwd", J.Tracer.derivative(expr, x), [x, y])
+    x1, y1 = _t([-2, 3, 4, -5], [4]), _t([2, 2, -2, 2], [4])
+    assert fwd([x1, y1]).to_vector() == [0.0, 6.0, 0.0, 0.0]
+    path = str(tmp_path / "jit_func_test.txt")
+    fwd.save(path)
+    assert J.JITFunction.load(path)([x1, y1]).to_vector() == [0.0, 6.0, 0.0, 0.0]
+    assert bwd([x1, y1]).to_vector() == [0.0, 2.0, 0.0, 0.0]
+    # another length through the same functions (the reference guards its compiled kernels by shape)
+    x2, y2 = _t([-1, 2, 3, 4, 5, -6], [6]), _t([3, 3, 3, 3, -3, 3], [6])
+    assert fwd([x2, y2]).to_vector() == [0.0, 6.0, 9.0, 12.0, 0.0, 0.0]
+    assert bwd([x2, y2]).to_vector() == [0.0, 3.0, 3.0, 3.0, 0.0, 0.0]
+
+
+def test_conv3d_reads_a_transposed_view_correctly():
+    inp = _t([1, 2, 3, 4, 5, 6, 7, 8], [1, 1, 2, 2, 2]).transpose(3, 4)
+    assert not inp.is_contiguous()
+    out = lt.Ops.conv3d(inp, _t([1.0], [1, 1, 1, 1, 1]), None, 1, 0)
+    assert out.to_vector() == [1.0, 3.0, 2.0, 4.0, 5.0, 7.0, 6.0, 8.0]
+
+
+def test_gradients_accumulate_when_a_tensor_is_used_twice():
+    a, b = _t([2.0], [1], True), _t([3.0], [1], True)
+    lt.Ops.add(lt.Ops.add(a, b), a).backward()
+    assert a.grad.item() == 2.0 and b.grad.item() == 1.0
+
+
+# ---- tests/llm_optimization_test.cpp
+class _Mock(lt.nn.Module):
+    """Logits that depend on the position only (the reference test's MockModel)."""
+
+    def __init__(self, rows):
+        super().__init__()
+        self.rows = rows
+
+    def forward(self, x):
+        import torch
+        T = x.shape[1]
+        return lt.Tensor(torch.tensor([[self.rows[min(s, len(self.rows) - 1)] for s in range(T)]], dtype=torch.float32))
+
+
+def test_prefix_cache_hit_and_miss():
+    cache = lt.nn.PrefixCache.get()
+    cache.clear()
+    cache.put([101, 102, 103], [_t([1.0, 2.0], [1, 2])])
+    got = cache.get_cache([101, 102, 103])
+    assert len(got) == 1 and got[0].to_vector()[0] == 1.0
+    assert len(cache.get_cache([101, 102, 104])) == 0
+    cache.clear()
+
+
+def test_speculative_decoding_accepts_agreeing_drafts():
+    rows = [[0.1, 0.8, 0.1], [0.1, 0.1, 0.8], [0.8, 0.1, 0.1], [0.1, 0.8, 0.1], [0.1, 0.1, 0.8]]
+    eng = lt.nn.SpeculativeEngine(_Mock(rows), _Mock(rows))
+    toks = eng.generate([0], 3, 2)
+    assert len(toks) == 4 and toks[1] == 1 and toks[2] == 2
+
+
+def test_flash_decoding_equals_flash_attention():
+    q = _t([0.1, 0.2, 0.3, 0.4], [1, 1, 1, 4])
+    k = _t([0.1, 0.2, 0.3, 0.4, 0.5, 0.6, 0.7, 0.8], [1, 1, 2, 4])
+    v = _t([1, 2, 3, 4, 5, 6, 7, 8], [1, 1, 2, 4])
+    dec, att = lt.Ops.flash_decoding(q, k, v, 2).to_vector(), lt.Ops.flash_attention(q, k, v).to_vector()
+    assert all(abs(a - b) < 1e-4 for a, b in zip(dec, att))
+
+
+def test_nf4_cast_round_trip():
+    x = _t([0.0, -0.6, 0.5, 1.0, -1.0], [1, 5]).cast(lt.DataType.NF4)
+    assert x.dtype == lt.DataType.NF4
+    back = x.cast(lt.DataType.FP32).to_vector()
+    assert back[0] == 0.0 and back[4] == -1.0 and abs(back[1] + 0.6961917) < 0.25
+
+
+def test_qlora_linear_trains_its_adapters():
+    lin = lt.nn.QLoRALinear(4, 2, 2, 16.0, True)
+    out = lin.forward(_t([1, 2, 3, 4], [1, 4], True))
+    assert out.shape == [1, 2]
+    lt.Ops.sum(out).backward()
+    assert lin.lora_A.grad is not None and lin.lora_B.grad is not None
+
+
+def test_fused_linear_cross_entropy_equals_the_two_step_form():
+    x, w = _t([1.0, 2.0, 0.5, -0.5], [2, 2], True), _t([0.1, 0.2, -0.3, 0.4], [2, 2], True)
+    tgt = _t([0.0, 1.0], [2])
+    fused = lt.Ops.fused_linear_cross_entropy(x, w, tgt)
+    fused.backward()
+    gx = x.grad.to_vector()
+    x2, w2 = _t([1.0, 2.0, 0.5, -0.5], [2, 2], True), _t([0.1, 0.2, -0.3, 0.4], [2, 2], True)
+    plain = lt.Ops.cross_entropy_loss(lt.Ops.matmul(x2, w2.transpose(0, 1)), tgt)
+    plain.backward()
+    assert abs(fused.to_vector()[0] - plain.to_vector()[0]) < 1e-5
+    assert all(abs(a - b) < 1e-4 for a, b in zip(gx, x2.grad.to_vector()))
