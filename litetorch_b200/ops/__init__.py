@@ -111,18 +111,23 @@ class Ops:
 
     @staticmethod
     def w8a8_matmul(x, w, x_scale: float, w_scale: float):
-        """int8 x int8 with int32 accumulation and per-tensor scales (src/ops/w8a8_ops.cpp:28-107)."""
+        """int8 x int8 with int32 accumulation and per-tensor scales: x [M, K], w [N, K] (one row per output feature, the
+        layout of a Linear weight), result [M, N] = (q(x) @ q(w)^T) * x_scale * w_scale (src/ops/w8a8_ops.cpp:28-107)."""
         xt, wt = _unwrap(x), _unwrap(w)
-        if (xt.is_cuda and xt.dim() == 2 and wt.dim() == 2 and xt.dtype in (torch.float32, torch.bfloat16) and wt.dtype == xt.dtype
+        if xt.dim() != 2 or wt.dim() != 2:
+            raise ValueError("w8a8_matmul expects 2-D inputs")
+        if wt.shape[1] != xt.shape[1]:
+            raise ValueError("inner dimensions differ in w8a8_matmul: x %s, w %s" % (list(xt.shape), list(wt.shape)))
+        if (xt.is_cuda and xt.dtype in (torch.float32, torch.bfloat16) and wt.dtype == xt.dtype
                 and xt.shape[1] % 16 == 0 and xt.numel() > 0 and wt.numel() > 0):
-            # quantiser kernels + the tcgen05 int8 GEMM (exact int32 sums); w is [K, N]: its codes are laid out K-major first
+            # quantiser kernels + the tcgen05 int8 GEMM (exact int32 sums); both operands are K-major as they stand
             from . import kernels as K
-            xq = K.quant_int8_tensor(xt, x_scale)
-            wq = K.quant_int8_tensor(wt.t().contiguous(), w_scale)
+            xq = K.quant_int8_tensor(xt.contiguous(), x_scale)
+            wq = K.quant_int8_tensor(wt.contiguous(), w_scale)
             return _w(K.gemm_i8(xq, wq, alpha=x_scale * w_scale))
         xq = torch.clamp(torch.round(xt.float() / x_scale), -127, 127)
         wq = torch.clamp(torch.round(wt.float() / w_scale), -127, 127)
-        return _w(torch.matmul(xq, wq) * (x_scale * w_scale))
+        return _w(torch.matmul(xq, wq.t()) * (x_scale * w_scale))
 
     # ------------------------------------------------------------------ activations
     @staticmethod

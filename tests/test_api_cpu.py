@@ -288,8 +288,8 @@ def test_casts_quantization_qat_qlora():
     ql = lt.nn.QLoRALinear(8, 4, r=2)
     assert ql(inp).shape == [3, 4] and len(ql.parameters()) == 3
     assert lt.Ops.scaled_matmul(x.cast(lt.FP8_E4M3).view([2, 4]), T([1.0] * 8, [4, 2]).cast(lt.FP8_E4M3), 0.5, 2.0).shape == [2, 2]
-    w8 = lt.Ops.w8a8_matmul(lt.Tensor(torch.randn(4, 8)), lt.Tensor(torch.randn(8, 4)), 0.02, 0.02)
-    assert w8.shape == [4, 4]
+    w8 = lt.Ops.w8a8_matmul(lt.Tensor(torch.randn(4, 8)), lt.Tensor(torch.randn(6, 8)), 0.02, 0.02)      # w is [N, K]
+    assert w8.shape == [4, 6]
 
 
 def test_moe_layer_grads_and_gate():

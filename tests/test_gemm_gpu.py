@@ -217,9 +217,10 @@ def test_int8_gemm_and_quantisers_are_exact():
     sref = xb.abs().amax(1) / 127.0
     assert float((sc - sref).abs().max()) < 1e-6
     assert int((qr.int() - torch.clamp(torch.round(xb / sref[:, None]), -127, 127).int()).abs().max()) <= 1
-    w = torch.randn(160, 96, device="cuda", generator=g)
+    w = torch.randn(96, 160, device="cuda", generator=g)                   # [N, K], one row per output feature
     y = _unwrap(lt.Ops.w8a8_matmul(Tensor(x), Tensor(w), 0.03, 0.02))
-    yr = torch.clamp(torch.round(x / 0.03), -127, 127) @ torch.clamp(torch.round(w / 0.02), -127, 127) * (0.03 * 0.02)
+    yr = torch.clamp(torch.round(x / 0.03), -127, 127) @ torch.clamp(torch.round(w / 0.02), -127, 127).t() * (0.03 * 0.02)
+    assert y.shape == (300, 96)
     assert float((y - yr).abs().max()) < 1e-3
     KK.check_status()
 

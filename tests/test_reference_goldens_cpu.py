@@ -116,3 +116,22 @@ def test_fused_linear_cross_entropy_equals_the_two_step_form():
     plain.backward()
     assert abs(fused.to_vector()[0] - plain.to_vector()[0]) < 1e-5
     assert all(abs(a - b) < 1e-4 for a, b in zip(gx, x2.grad.to_vector()))
+
+
+# ---- tests/advanced_optimization_stage2_test.cpp
+def test_guided_decoding_masks():
+    dec = lt.nn.GuidedDecoder(["123", "abc", "789", "xyz"])
+    logits = _t([1.0, 2.0, 3.0, 4.0], [4])
+    dec.apply_mask(logits, "", "digits")
+    assert logits.to_vector() == [1.0, -1e9, 3.0, -1e9]
+    logits2 = _t([1.0, 2.0, 3.0, 4.0], [4])
+    dec.apply_mask(logits2, "", "prefix:abc")
+    assert logits2.to_vector() == [-1e9, 2.0, -1e9, -1e9]
+
+
+def test_w8a8_matmul_takes_the_weight_as_out_by_in():
+    x, w = _t([1.5, 2.5, -3.5, 4.5], [2, 2]), _t([0.5, -1.5, 2.0, 1.0], [2, 2])
+    out = lt.Ops.w8a8_matmul(x, w, 0.5, 0.5)
+    assert out.shape == [2, 2]
+    val0 = (round(1.5 / 0.5) * round(0.5 / 0.5) + round(2.5 / 0.5) * round(-1.5 / 0.5)) * 0.25
+    assert abs(out.to_vector()[0] - val0) < 1e-5
