@@ -126,6 +126,11 @@ class Request:
         self.block_ids: List[int] = []
 
 
+class _BlockCount(int):
+    def __len__(self) -> int:
+        return int(self)
+
+
 class ServingScheduler:
     """Continuous batching over a paged KV pool.  `step(model)` admits, prefills in chunks within the token budget,
     decodes one token for every running sequence in ONE batched forward, samples greedily and returns the requests
@@ -162,8 +167,11 @@ class ServingScheduler:
         return [self._reqs[i] for i in self._order if self._reqs[i].block_ids and not self._reqs[i].is_finished]
 
     @property
-    def free_blocks(self) -> int:
-        return self._lib.lt_sched_num_free_blocks(self._s)
+    def free_blocks(self) -> "_BlockCount":
+        """How many KV blocks are free.  The reference exposes the list of free block ids here and its callers take its length
+        (tests/advanced_serving_test.cpp:84); the native scheduler keeps the ids to itself, so this is a count that also
+        answers `len()`."""
+        return _BlockCount(self._lib.lt_sched_num_free_blocks(self._s))
 
     def _sync(self, rid: int):
         r = self._reqs[rid]

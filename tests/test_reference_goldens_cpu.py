@@ -135,3 +135,63 @@ def test_w8a8_matmul_takes_the_weight_as_out_by_in():
     assert out.shape == [2, 2]
     val0 = (round(1.5 / 0.5) * round(0.5 / 0.5) + round(2.5 / 0.5) * round(-1.5 / 0.5)) * 0.25
     assert abs(out.to_vector()[0] - val0) < 1e-5
+
+
+# ---- tests/advanced_serving_test.cpp
+class _NextToken(lt.nn.Module):
+    """logits favour token + 1 (mod vocab) at every position (the reference test's MockModel)."""
+
+    def __init__(self, vocab):
+        super().__init__()
+        self.vocab = vocab
+
+    def forward(self, x):
+        import torch
+        from litetorch_b200.core import _unwrap
+        tok = _unwrap(x).long()
+        return lt.Tensor(torch.nn.functional.one_hot((tok + 1) % self.vocab, self.vocab).float() * 10.0)
+
+
+def test_continuous_batching_generates_the_counting_sequences():
+    model = _NextToken(32)
+    sched = lt.nn.ServingScheduler(10, 4, 2, 8)
+    r1, r2 = lt.nn.Request(1, [1, 2, 3, 4, 5, 6], 4), lt.nn.Request(2, [10, 11], 4)
+    sched.add_request(r1)
+    sched.add_request(r2)
+    steps = 0
+    while (sched.pending_queue or sched.running_queue) and steps < 50:
+        sched.step(model)
+        steps += 1
+    assert r1.is_finished and r2.is_finished
+    assert r1.generated_tokens == [7, 8, 9, 10] and r2.generated_tokens == [12, 13, 14, 15]
+    assert len(sched.free_blocks) == 10 and sched.free_blocks == 10
+
+
+def test_moe_linear_routes_gradients_to_gate_and_experts():
+    moe = lt.nn.MoELinear(4, 4, 3, 2)
+    x = _t([1, 2, 3, 4, 5, 6, 7, 8], [2, 4], True)
+    out = moe.forward(x)
+    assert out.shape == [2, 4]
+    lt.Ops.sum(out).backward()
+    assert x.grad is not None and moe.gate_weight.grad is not None
+    assert any(abs(g) > 1e-5 for g in moe.gate_weight.grad.to_vector())
+    assert len(moe.experts) == 3 and moe.num_experts == 3 and moe.top_k == 2
+
+
+def test_medusa_heads_speed_up_the_counting_model():
+    import torch
+    from litetorch_b200.core import _unwrap
+    base = _NextToken(32)
+    heads = []
+    for h in range(2):
+        head = lt.nn.MedusaHead(32, 32)
+        w = torch.zeros(32, 32)
+        for cur in range(32):
+            w[(cur + h + 2) % 32, cur] = 10.0
+        with torch.no_grad():
+            _unwrap(head.weight).copy_(w)
+            if head.bias is not None:
+                _unwrap(head.bias).zero_()
+        heads.append(head)
+    toks = lt.nn.MedusaEngine(base, heads).generate([1, 2], 6, 2)
+    assert len(toks) >= 8 and toks[2:5] == [3, 4, 5]
