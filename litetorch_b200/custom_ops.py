@@ -45,6 +45,20 @@ class Registry:
     def register(cls, name: str, cpu_forward: Callable, backward: Optional[Callable] = None, gpu_forward: Optional[Callable] = None):
         cls._ops[name] = _Entry(cpu_forward, gpu_forward, backward)
 
+    # the C++ spelling of the reference: custom_ops::Registry::get().register_op(name, cpu_forward, gpu_forward, backward)
+    @classmethod
+    def get(cls) -> "type":
+        return cls
+
+    @classmethod
+    def register_op(cls, name: str, cpu_forward: Callable, gpu_forward: Optional[Callable] = None, backward: Optional[Callable] = None):
+        """The reference's calling conventions (include/litetorch/custom_ops.h): forward(list of tensors) -> tensor,
+        backward(grad_output, list of inputs, output) -> list of gradients."""
+        def fwd(f):
+            return None if f is None else (lambda *ts: f(list(ts)))
+        bwd = None if backward is None else (lambda inputs, out, g: backward(g, list(inputs), out))
+        cls.register(name, fwd(cpu_forward), bwd, fwd(gpu_forward))
+
     @classmethod
     def has(cls, name: str) -> bool:
         return name in cls._ops

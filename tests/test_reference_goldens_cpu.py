@@ -195,3 +195,38 @@ def test_medusa_heads_speed_up_the_counting_model():
         heads.append(head)
     toks = lt.nn.MedusaEngine(base, heads).generate([1, 2], 6, 2)
     assert len(toks) >= 8 and toks[2:5] == [3, 4, 5]
+
+
+# ---- tests/production_optimization_test.cpp
+def test_adamw8bit_tracks_adamw_on_the_first_step():
+    p1, p2 = _t([1, 2, 3], [1, 3], True), _t([1, 2, 3], [1, 3], True)
+    p1.grad, p2.grad = _t([0.1, -0.2, 0.3], [1, 3]), _t([0.1, -0.2, 0.3], [1, 3])
+    lt.optim.AdamW([p1], 0.1, 0.9, 0.999, 1e-8, 0.01).step()
+    lt.optim.AdamW8bit([p2], 0.1, 0.9, 0.999, 1e-8, 0.01).step()
+    assert all(abs(a - b) <= 0.05 for a, b in zip(p1.to_vector(), p2.to_vector()))
+    assert p1.to_vector() != [1.0, 2.0, 3.0]
+
+
+def test_paged_attention_of_constant_values_returns_the_value():
+    import torch
+    S, H, Hkv, D, bs = 2, 4, 2, 8, 4
+    q = lt.Tensor(torch.full((S, H, D), 0.1))
+    kc, vc = lt.Tensor(torch.full((4, Hkv, bs, D), 0.2)), lt.Tensor(torch.full((4, Hkv, bs, D), 0.3))
+    bt = lt.Tensor(torch.tensor([[0, 1], [2, 3]], dtype=torch.float32))
+    cl = lt.Tensor(torch.tensor([6, 8], dtype=torch.float32))
+    out = lt.Ops.paged_attention(q, kc, vc, bt, cl, bs)
+    assert out.shape == [S, H, D] and all(abs(v - 0.3) < 1e-4 for v in out.to_vector())
+
+
+def test_custom_operator_with_the_reference_conventions():
+    import torch
+    from litetorch_b200.core import _unwrap
+    reg = lt.custom_ops.Registry.get()
+    reg.register_op("mul_by_two", lambda args: lt.Tensor(_unwrap(args[0]) * 2.0), None,
+                    lambda grad_out, inputs, output: [lt.Tensor(_unwrap(grad_out) * 2.0)])
+    x = _t([1, 2, 3], [1, 3], True)
+    y = reg.call("mul_by_two", [x])
+    assert y.to_vector() == [2.0, 4.0, 6.0]
+    y.backward(_t([1, 1, 1], [1, 3]))
+    assert x.grad.to_vector() == [2.0, 2.0, 2.0]
+    reg.unregister("mul_by_two")
