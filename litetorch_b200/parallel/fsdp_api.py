@@ -73,7 +73,7 @@ class FullyShardedDataParallel:
 
     def shard_parameters(self) -> None:
         """Keep only this rank's shard: gradients of the full parameter are reduce-scattered into `shard.grad`
-        and the full storage is released."""
+        and the full storage is released (the parameter aliases its flat shard)."""
         for p in self.params:
             t = _unwrap(p)
             if t.grad is not None:
@@ -88,7 +88,9 @@ class FullyShardedDataParallel:
             if not self.sharded:
                 with torch.no_grad():
                     _unwrap(p.shard).data.copy_(_shard_of(t, self.rank, self.world))
-            t.data = torch.empty(0, dtype=t.dtype, device=t.device)
+            # the parameter itself now views this rank's flat shard (reference: fsdp.h:113-120), so its shape is
+            # [shard_size] until the next gather
+            t.data = _unwrap(p.shard).data
         self.sharded = True
 
     def forward(self, x):

@@ -47,11 +47,12 @@ def cast_tensor(t: Tensor, dtype: DataType) -> Tensor:
         return Tensor(_nearest_code(torch.clamp(x, -1.0, 1.0), NF4_CODEBOOK), DataType.NF4)
     if dtype == DataType.FP4_E2M1:
         return Tensor(_nearest_code(torch.clamp(x, -6.0, 6.0), FP4_CODEBOOK), DataType.FP4_E2M1)
+    # integer targets clamp and then drop the fraction, as a C cast does (src/tensor/tensor_core.cpp:1102-1117: 1.5 -> 1, -2.5 -> -2)
     if dtype == DataType.INT4:
-        return Tensor(torch.clamp(torch.round(x), -8, 7).to(torch.int8), DataType.INT4)
+        return Tensor(torch.trunc(torch.clamp(x, -8, 7)).to(torch.int8), DataType.INT4)
     if dtype in (DataType.INT8, DataType.INT16):
         lim = 127 if dtype == DataType.INT8 else 32767
-        return Tensor(torch.clamp(torch.round(x), -lim - 1, lim).to(_TO_TORCH[dtype]))
+        return Tensor(torch.trunc(torch.clamp(x, -lim - 1, lim)).to(_TO_TORCH[dtype]))
     if dtype == DataType.FP8_E4M3:
         return Tensor(torch.clamp(x, -448.0, 448.0).to(torch.float8_e4m3fn))
     if dtype == DataType.FP8_E5M2:

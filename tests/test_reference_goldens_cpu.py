@@ -230,3 +230,73 @@ def test_custom_operator_with_the_reference_conventions():
     y.backward(_t([1, 1, 1], [1, 3]))
     assert x.grad.to_vector() == [2.0, 2.0, 2.0]
     reg.unregister("mul_by_two")
+
+
+# ---- tests/production_features_test.cpp
+def test_casts_round_trip_with_the_expected_values():
+    D = lt.DataType
+    t = _t([1.5, -2.5, 0.0, 10.25], [4])
+    h = t.cast(D.FP16)
+    assert h.dtype == D.FP16
+    back = h.cast(D.FP32)
+    assert back.dtype == D.FP32 and all(abs(a - b) < 1e-3 for a, b in zip(back.to_vector(), [1.5, -2.5, 0.0, 10.25]))
+    i8 = t.cast(D.INT8)
+    assert i8.dtype == D.INT8 and i8.cast(D.FP32).to_vector() == [1.0, -2.0, 0.0, 10.0]
+    f64 = t.cast(D.FP64)
+    assert f64.dtype == D.FP64 and abs(f64.cast(D.FP32).to_vector()[0] - 1.5) < 1e-5
+    i16 = t.cast(D.INT16)
+    assert i16.dtype == D.INT16 and i16.cast(D.FP32).to_vector()[0] == 1.0
+    i4 = t.cast(D.INT4)
+    assert i4.dtype == D.INT4 and i4.cast(D.FP32).to_vector()[0] == 1.0
+    bf = t.cast(D.BF16)
+    assert bf.dtype == D.BF16 and abs(bf.cast(D.FP32).to_vector()[0] - 1.5) < 1e-2
+
+
+def test_half_precision_matmul_with_a_grad_scaler_moves_the_weight():
+    x, w = _t([1.0, 2.0], [1, 2], True), _t([0.5, -0.5, 1.0, 2.0], [2, 2], True)
+    out = lt.Ops.cast(lt.Ops.matmul(lt.Ops.cast(x, lt.DataType.FP16), lt.Ops.cast(w, lt.DataType.FP16).transpose(0, 1)), lt.DataType.FP32)
+    loss = lt.Ops.mse_loss(out, _t([0.5, 4.5], [1, 2]))
+    scaler = lt.amp.GradScaler(1024.0)
+    scaler.scale(loss).backward()
+    opt = lt.optim.SGD([x, w], 0.1)
+    old = w.to_vector()[0]
+    scaler.step(opt)
+    scaler.update()
+    assert w.to_vector()[0] != old
+
+
+def test_fsdp_wrapper_flattens_and_restores_the_weight_shape():
+    lin = lt.nn.Linear(4, 4, False)
+    fsdp = lt.distributed.FullyShardedDataParallel(lin)
+    assert lin.weight.shape[0] == 16
+    fsdp.gather_parameters()
+    assert lin.weight.shape == [4, 4]
+    fsdp.shard_parameters()
+    assert lin.weight.shape[0] == 16
+
+
+def test_quantize_linear_and_calibrator_scale():
+    import torch
+    from litetorch_b200.core import _unwrap
+    W = [0.5, -0.2, 0.8, -0.1, 1.2, 0.0, -0.5, 0.3, -0.9, 0.4, 0.1, -0.2, 0.6, -0.7, 0.3, 0.5]
+    lin = lt.nn.Linear(4, 4, False)
+    with torch.no_grad():
+        _unwrap(lin.weight).copy_(torch.tensor(W).view(4, 4))
+    lt.quantization.quantize_linear(lin)
+    assert lin.weight.dtype == lt.DataType.INT8 and lin.scales is not None and lin.scales.shape[0] == 4
+    assert len(lin.forward(_t([1, 1, 1, 1], [1, 4])).to_vector()) == 4
+    cal = lt.quantization.Calibrator()
+    cal.collect("layer1_act", _t([-2.5, 1.0, 3.2, -0.5], [1, 4]))
+    assert abs(cal.get_scale("layer1_act", 8) - 3.2 / 127.0) < 1e-5
+    lin2 = lt.nn.Linear(4, 4, False)
+    with torch.no_grad():
+        _unwrap(lin2.weight).copy_(torch.tensor(W).view(4, 4))
+    # positional arguments as the reference's C++ test passes them: (linear, w_scale, w_zp, a_scale ...) - here by keyword
+    qat = lt.quantization.QATLinear(lin2, w_scale=0.01, a_scale=0.01, b=8)
+    qat.qat_enabled = True
+    qat.train()
+    x = _t([1, 2, 3, 4], [1, 4], True)
+    out = qat.forward(x)
+    assert out.requires_grad
+    lt.Ops.sum(out).backward()
+    assert x.grad is not None and qat.weight.grad is not None
