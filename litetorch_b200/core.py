@@ -185,6 +185,17 @@ class Tensor:
     def numel(self) -> int:
         return self._t.numel()
 
+    def data_ptr(self) -> int:
+        """Address of the first element; a meta tensor has no storage and raises (reference: Tensor::data_ptr,
+        src/tensor/tensor.cpp)."""
+        if self._t.device.type == "meta":
+            raise RuntimeError("a meta tensor has no data")
+        return self._t.data_ptr()
+
+    def element_size(self) -> int:
+        """Bytes per stored element (reference: StorageImpl::element_size, include/litetorch/tensor.h)."""
+        return self._t.element_size()
+
     def item(self) -> float:
         return float(self._t.detach().float().reshape(-1)[0].item())
 

@@ -388,12 +388,30 @@ class AdamWFP8(_AdamBase):
     HISTORY = 10
 
     def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+        self.m8, self.v8 = [], []
         super().__init__(params, lr, beta1, beta2, eps, weight_decay)
         n = len(self.params)
         self.m8, self.v8 = [None] * n, [None] * n
         self.m_scale, self.v_scale = [1.0] * n, [1.0] * n
         self.m_hist, self.v_hist = [[] for _ in range(n)], [[] for _ in range(n)]
         self._qstate = [None] * n
+
+    # `m` / `v` read as the e4m3 moment tensors, as the reference's public members do (include/litetorch/optim.h)
+    @property
+    def m(self):
+        return [None if t is None else Tensor(t) for t in self.m8]
+
+    @m.setter
+    def m(self, _):
+        pass
+
+    @property
+    def v(self):
+        return [None if t is None else Tensor(t) for t in self.v8]
+
+    @v.setter
+    def v(self, _):
+        pass
 
     def _store(self, x, hist):
         hist.append(float(x.abs().max()))

@@ -300,3 +300,114 @@ def test_quantize_linear_and_calibrator_scale():
     assert out.requires_grad
     lt.Ops.sum(out).backward()
     assert x.grad is not None and qat.weight.grad is not None
+
+
+# ---- tests/scale_upgrade_test.cpp
+def test_fp8_casts_are_one_byte_and_round_trip():
+    D = lt.DataType
+    x = _t([1.0, -0.5, 2.5, 0.0, 15.0], [1, 5])
+    for dt, tol in ((D.FP8_E4M3, 0.2), (D.FP8_E5M2, 0.5)):
+        q = x.cast(dt)
+        assert q.dtype == dt and q.element_size() == 1
+        v = q.cast(D.FP32).to_vector()
+        assert abs(v[0] - 1.0) < 0.1 and abs(v[1] + 0.5) < 0.1 and abs(v[2] - 2.5) < tol and v[3] == 0.0
+
+
+def test_scaled_matmul_applies_both_scales():
+    out = lt.Ops.scaled_matmul(_t([1, 2, 3, 4], [2, 2]), _t([1, 0, 0, 1], [2, 2]), 0.5, 2.0)
+    assert all(abs(a - b) < 1e-5 for a, b in zip(out.to_vector(), [1.0, 2.0, 3.0, 4.0]))
+
+
+def test_ring_attention_of_constant_values_returns_the_value():
+    q, k, v = (_t([c] * 32, [1, 2, 4, 4]) for c in (0.1, 0.2, 0.3))
+    out = lt.Ops.ring_attention(q, k, v, None)
+    assert all(abs(x - 0.3) < 1e-4 for x in out.to_vector())
+
+
+def test_adamw_fp8_steps_against_the_gradient_and_keeps_fp8_moments():
+    p = _t([1.0, 2.0, 3.0], [1, 3], True)
+    p.grad = _t([0.1, -0.2, 0.3], [1, 3])
+    opt = lt.optim.AdamWFP8([p], 0.1, 0.9, 0.999, 1e-8, 0.01)
+    opt.step()
+    v = p.to_vector()
+    assert v[0] < 1.0 and v[1] > 2.0 and v[2] < 3.0
+    assert opt.m[0].dtype == lt.DataType.FP8_E4M3 and opt.v[0].dtype == lt.DataType.FP8_E4M3
+
+
+# ---- tests/advanced_features_test.cpp
+def test_meta_tensor_has_a_shape_and_no_data():
+    import pytest
+    t = lt.Tensor.create([2, 3, 4], lt.Device(lt.DeviceType.META, 0))
+    assert t.shape == [2, 3, 4] and t.device.type == lt.DeviceType.META
+    with pytest.raises(RuntimeError):
+        t.data_ptr()
+
+
+def test_tensor_backward_hook_scales_the_gradient():
+    x = _t([1.0, 2.0], [2], True)
+    y = lt.Ops.mul(x, _t([3.0, 4.0], [2]))
+    x.register_hook(lambda g: lt.Ops.mul(g, _t([2.0, 2.0], [2])))
+    lt.Ops.sum(y).backward()
+    g = x.grad.to_vector()
+    assert abs(g[0] - 6.0) < 1e-4 and abs(g[1] - 8.0) < 1e-4
+
+
+def test_module_forward_hooks_run_around_the_call():
+    class Double(lt.nn.Module):
+        def forward(self, input):
+            return lt.Ops.mul(input, _t([2.0], [1]))
+
+    m, ran = Double(), []
+    m.register_forward_pre_hook(lambda mod, inp: ran.append("pre"))
+    m.register_forward_hook(lambda mod, inp, out: ran.append("post"))
+    y = m(_t([1.0, 2.0], [2])).to_vector()
+    assert ran == ["pre", "post"] and abs(y[0] - 2.0) < 1e-4 and abs(y[1] - 4.0) < 1e-4
+
+
+def test_adamw_step_and_its_offloaded_form_lower_the_weights():
+    for offload in (False, True):
+        p = _t([1.0, 2.0], [2], True)
+        p.grad = _t([0.1, 0.2], [2])
+        lt.optim.AdamW([p], 1e-1, 0.9, 0.999, 1e-8, 0.01, offload).step()
+        v = p.to_vector()
+        assert v[0] < 1.0 and v[1] < 2.0
+
+
+def test_cosine_annealing_reaches_the_floor_after_t_max_steps():
+    p = _t([1.0], [1], True)
+    opt = lt.optim.AdamW([p], 1.0)
+    sched = lt.optim.CosineAnnealingLR(opt, 10, 0.0)
+    sched.step()
+    assert opt.get_lr() < 1.0
+    for _ in range(9):
+        sched.step()
+    assert opt.get_lr() < 1e-5
+
+
+def test_clip_grad_norm_returns_the_old_norm_and_rescales():
+    p1, p2 = _t([1.0], [1], True), _t([1.0], [1], True)
+    p1.grad, p2.grad = _t([10.0], [1]), _t([20.0], [1])
+    assert lt.Ops.clip_grad_norm_([p1, p2], 5.0) > 22.0
+    g1, g2 = p1.grad.to_vector()[0], p2.grad.to_vector()[0]
+    assert abs((g1 * g1 + g2 * g2) ** 0.5 - 5.0) < 1e-2
+
+
+def test_rope_with_unit_rotation_at_position_zero_keeps_the_first_pair():
+    x = _t([1, 2, 3, 4, 5, 6, 7, 8], [1, 1, 2, 4], True)
+    cos, sin = _t([1.0, 0.0, 0.5, 0.87], [2, 2]), _t([0.0, 1.0, 0.87, 0.5], [2, 2])
+    y = lt.Ops.rope(x, cos, sin)
+    v = y.to_vector()
+    assert abs(v[0] - 1.0) < 1e-4 and abs(v[1] - 2.0) < 1e-4
+    lt.Ops.sum(y).backward()
+    assert len(x.grad.to_vector()) == 8
+
+
+def test_grouped_query_attention_shapes_and_kv_head_gradients():
+    q = _t([1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 1, 1, 0, 0, 0, 0, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1],
+           [1, 4, 2, 4], True)
+    eye = [1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1]
+    k, v = _t(eye, [1, 2, 2, 4], True), _t(eye, [1, 2, 2, 4], True)
+    out = lt.Ops.flash_attention(q, k, v)
+    assert out.shape == [1, 4, 2, 4]
+    lt.Ops.sum(out).backward()
+    assert q.grad is not None and k.grad.shape[1] == 2 and v.grad.shape[1] == 2
