@@ -244,7 +244,8 @@ class Tensor:
         return self._t.is_contiguous()
 
     def clone(self) -> "Tensor":
-        return Tensor(self._t.clone(), self._dtype_tag)
+        # a clone is always contiguous in row-major order (reference: Tensor::clone, src/tensor/tensor.cpp)
+        return Tensor(self._t.clone(memory_format=torch.contiguous_format), self._dtype_tag)
 
     def cast(self, target_dtype: DataType) -> "Tensor":
         from .quantization import cast_tensor

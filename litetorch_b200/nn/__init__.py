@@ -425,6 +425,11 @@ class TransformerDecoderLayer(Module):
         self.norm1, self.norm2, self.norm3 = LayerNorm([embed_dim]), LayerNorm([embed_dim]), LayerNorm([embed_dim])
         self.linear1, self.linear2 = Linear(embed_dim, dim_feedforward), Linear(dim_feedforward, embed_dim)
 
+    @property
+    def multihead_attn(self):
+        """The cross-attention block under the reference's member name (include/litetorch/nn.h)."""
+        return self.cross_attn
+
     def forward(self, x: Tensor, memory: Optional[Tensor] = None) -> Tensor:
         a = self.self_attn(x)
         x = Ops.fused_add_layernorm(a, x, self.norm1.normalized_shape, self.norm1.weight, self.norm1.bias, self.norm1.eps)

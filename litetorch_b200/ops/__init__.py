@@ -169,7 +169,22 @@ class Ops:
 
     @staticmethod
     def batch_norm2d(input, running_mean, running_var, weight, bias, training: bool, momentum: float = 0.1, eps: float = 1e-5):
-        return _w(F.batch_norm(_unwrap(input), _unwrap(running_mean), _unwrap(running_var), _unwrap(weight), _unwrap(bias),
+        t = _unwrap(input)
+        if training and t.numel() == t.shape[1]:
+            # one value per channel: the batch variance is 0 and its unbiased factor M / (M - 1) is taken as 1
+            # (reference: src/ops/normalization.cpp:650), where torch refuses the call
+            rm, rv = _unwrap(running_mean), _unwrap(running_var)
+            with torch.no_grad():
+                rm.mul_(1 - momentum).add_(t.detach().reshape(-1).to(rm.dtype), alpha=momentum)
+                rv.mul_(1 - momentum)
+            shape = [1, -1] + [1] * (t.dim() - 2)
+            out = (t - t.detach()) * torch.rsqrt(torch.zeros((), dtype=t.dtype, device=t.device) + eps)
+            if weight is not None:
+                out = out * _unwrap(weight).view(shape)
+            if bias is not None:
+                out = out + _unwrap(bias).view(shape)
+            return _w(out)
+        return _w(F.batch_norm(t, _unwrap(running_mean), _unwrap(running_var), _unwrap(weight), _unwrap(bias),
                                training, momentum, eps))
 
     # ------------------------------------------------------------------ vision

@@ -411,3 +411,202 @@ def test_grouped_query_attention_shapes_and_kv_head_gradients():
     assert out.shape == [1, 4, 2, 4]
     lt.Ops.sum(out).backward()
     assert q.grad is not None and k.grad.shape[1] == 2 and v.grad.shape[1] == 2
+
+
+# ---- tests/attention_test.cpp, checkpoint_test.cpp, double_backward_test.cpp, audit_optimizations_test.cpp
+def test_multi_head_attention_forward_backward_reaches_input_and_q_projection():
+    import math
+    B, T, C = 2, 4, 8
+    x = _t([math.sin(i) for i in range(B * T * C)], [B, T, C], True)
+    mha = lt.nn.MultiHeadAttention(C, 2)
+    mha.to(CPU)
+    out = mha.forward(x)
+    assert out.shape == [B, T, C]
+    lt.Ops.sum(out).backward()
+    assert sum(abs(g) for g in x.grad.to_vector()) > 0.0
+    assert sum(abs(g) for g in mha.q_proj.weight.grad.to_vector()) > 0.0
+
+
+def test_activation_checkpoint_of_a_function_gives_the_gradient():
+    x = _t([1.0] * 16, [4, 4], True)
+    out = lt.checkpoint(lambda inp: lt.Ops.add(lt.Ops.mul(inp, inp), inp), x)
+    assert out is not None and out.requires_grad
+    lt.Ops.sum(out).backward()
+    assert x.grad is not None and abs(lt.Ops.sum(x.grad).item() - 48.0) < 1e-4      # d(x^2 + x)/dx = 3 at x = 1
+
+
+def test_double_backward_gives_first_and_second_derivative():
+    x = _t([3.0], [1], True)
+    y = lt.Ops.mul(x, x)
+    y.backward(None, True)
+    assert abs(x.grad.item() - 6.0) < 1e-5
+    grad = x.grad
+    x.zero_grad()
+    grad.backward(None)
+    assert abs(x.grad.item() - 2.0) < 1e-5
+
+
+def test_from_vector_takes_a_dtype():
+    t8 = lt.Tensor.from_vector([10.0, 20.0, 30.0], [3], CPU, False, lt.DataType.INT8)
+    assert t8.dtype == lt.DataType.INT8 and t8.to_vector() == [10.0, 20.0, 30.0]
+    th = lt.Tensor.from_vector([1.5, 2.5, 3.5], [3], CPU, False, lt.DataType.FP16)
+    assert th.dtype == lt.DataType.FP16 and all(abs(a - b) < 1e-3 for a, b in zip(th.to_vector(), [1.5, 2.5, 3.5]))
+
+
+# ---- tests/transformer_test.cpp, tests/jit_test.cpp
+def test_transformer_decoder_layer_in_both_modes():
+    import math
+    B, Tt, Tm, C = 2, 4, 6, 8
+    tgt = _t([math.sin(i) for i in range(B * Tt * C)], [B, Tt, C], True)
+    mem = _t([math.cos(i) for i in range(B * Tm * C)], [B, Tm, C], True)
+    layer = lt.nn.TransformerDecoderLayer(C, 2, 16)
+    layer.to(CPU)
+    asum = lambda t: sum(abs(g) for g in t.to_vector())
+    out = layer.forward(tgt)
+    assert out.shape == [B, Tt, C]
+    lt.Ops.sum(out).backward()
+    assert asum(tgt.grad) > 0.0 and asum(layer.self_attn.q_proj.weight.grad) > 0.0
+    for p in layer.parameters():
+        p.grad = None
+    tgt.grad = None
+    out = layer.forward(tgt, mem)
+    assert out.shape == [B, Tt, C]
+    lt.Ops.sum(out).backward()
+    assert asum(tgt.grad) > 0.0 and asum(mem.grad) > 0.0 and asum(layer.multihead_attn.q_proj.weight.grad) > 0.0
+
+
+def test_jit_expression_and_traced_function_equal_eager():
+    J = lt.jit
+    a, b, c = (J.JITVar(J.OpType.INPUT, n) for n in "abc")
+    fused = J.JITFunction("fused_gelu_add", J.gelu(a * b + c), [a, b, c])
+    ta, tb, tc = _t([1, 2, -3, 4], [4]), _t([0.5, 1.5, 2.0, -1.0], [4]), _t([1, -1, 0, 2], [4])
+    seq = lt.Ops.gelu(lt.Ops.add(lt.Ops.mul(ta, tb), tc)).to_vector()
+    assert all(abs(x - y) < 1e-5 for x, y in zip(seq, fused([ta, tb, tc]).to_vector()))
+    x0, x1 = _t([1, 2, 3], [3]), _t([0.5, 1.0, 2.0], [3])
+    traced = J.Tracer.trace([x0, x1], lambda ins: lt.Ops.relu(lt.Ops.add(ins[0], ins[1])), "traced_relu_add")
+    eager = lt.Ops.relu(lt.Ops.add(x0, x1)).to_vector()
+    assert all(abs(x - y) < 1e-5 for x, y in zip(eager, traced([x0, x1]).to_vector()))
+
+
+# ---- tests/new_features_test.cpp
+def test_parameter_files_round_trip_and_reject_bad_shapes_magic_and_truncation(tmp_path):
+    import struct
+    import pytest
+    w1, w2 = [1.5, -2.0, 3.1, 0.4], [0.1, 0.2, 0.3, 0.4, 0.5, 0.6]
+    path = str(tmp_path / "test_model_weights.lt")
+    lt.save_parameters([_t(w1, [2, 2]), _t(w2, [2, 3])], path)
+    l1, l2 = lt.Tensor.create([2, 2], CPU), lt.Tensor.create([2, 3], CPU)
+    lt.load_parameters([l1, l2], path)
+    assert all(abs(a - b) < 1e-5 for a, b in zip(l1.to_vector() + l2.to_vector(), w1 + w2))
+    with pytest.raises(RuntimeError):
+        lt.load_parameters([lt.Tensor.create([3, 3], CPU), l2], path)
+    bad = tmp_path / "bad_file.lt"
+    bad.write_bytes(b"BADMAGIC")
+    with pytest.raises(RuntimeError):
+        lt.load_parameters([l1, l2], str(bad))
+    short = tmp_path / "short_file.lt"
+    short.write_bytes(b"LTW1" + struct.pack("<II", 2, 2) + struct.pack("<qq", 2, 2) + struct.pack("<Q", 4)
+                      + struct.pack("<ff", 1.0, 2.0))
+    with pytest.raises(RuntimeError):
+        lt.load_parameters([l1, l2], str(short))
+    # the failed loads left the tensors as they were
+    assert all(abs(a - b) < 1e-5 for a, b in zip(l1.to_vector(), w1))
+
+
+def test_adam_state_round_trips_with_step_count_and_rejects_other_shapes(tmp_path):
+    import pytest
+    p = lt.Tensor.create([2, 2], CPU, True)
+    adam = lt.optim.Adam([p], 1e-3)
+    p.grad = _t([0.0] * 4, [2, 2])
+    adam.step()                                  # allocates the moments
+    adam.step_count = 42
+    md, vd = [0.5, 0.6, 0.7, 0.8], [0.01, 0.02, 0.03, 0.04]
+    lt.Tensor(adam.m[0]).copy_(_t(md, [2, 2]))
+    lt.Tensor(adam.v[0]).copy_(_t(vd, [2, 2]))
+    path = str(tmp_path / "test_opt_state.lt")
+    lt.save_optimizer_state(adam, path)
+    other = lt.optim.Adam([p], 1e-3)
+    lt.load_optimizer_state(other, path)
+    assert other.step_count == 42
+    assert all(abs(a - b) < 1e-5 for a, b in zip(lt.Tensor(other.m[0]).to_vector(), md))
+    assert all(abs(a - b) < 1e-5 for a, b in zip(lt.Tensor(other.v[0]).to_vector(), vd))
+    wrong = lt.optim.Adam([lt.Tensor.create([2, 3], CPU, True)], 1e-3)
+    with pytest.raises(RuntimeError):
+        lt.load_optimizer_state(wrong, path)
+
+
+def test_bmm_forward_and_backward_against_a_float64_oracle():
+    import torch
+    B, M, K, N = 16, 64, 128, 64
+    av = [(i % 100) / 50.0 - 1.0 for i in range(B * M * K)]
+    bv = [(i % 100) / 100.0 - 0.5 for i in range(B * K * N)]
+    a, b = _t(av, [B, M, K], True), _t(bv, [B, K, N], True)
+    c = lt.Ops.bmm(a, b)
+    c.backward(_t([0.1] * (B * M * N), [B, M, N]))
+    ar = torch.tensor(av, dtype=torch.float64).view(B, M, K).requires_grad_()
+    br = torch.tensor(bv, dtype=torch.float64).view(B, K, N).requires_grad_()
+    cr = torch.bmm(ar, br)
+    cr.backward(torch.full_like(cr, 0.1))
+    err = lambda x, r: float((torch.tensor(x.to_vector(), dtype=torch.float64) - r.detach().reshape(-1)).abs().max())
+    assert err(c, cr) < 1e-3 and err(a.grad, ar.grad) < 1e-3 and err(b.grad, br.grad) < 1e-3
+
+
+def test_conv3d_max_pool3d_and_3d_linear_against_a_float64_oracle():
+    import torch
+    import torch.nn.functional as F
+    err = lambda x, r: float((torch.tensor(x.to_vector(), dtype=torch.float64) - r.detach().reshape(-1)).abs().max())
+    iv = [(i % 10) / 10.0 for i in range(2 * 2 * 64)]
+    wv = [(i % 5) / 5.0 - 0.4 for i in range(3 * 2 * 27)]
+    bv = [0.2 * i for i in range(3)]
+    x, w, b = _t(iv, [2, 2, 4, 4, 4], True), _t(wv, [3, 2, 3, 3, 3], True), _t(bv, [3], True)
+    out = lt.Ops.conv3d(x, w, b, 1, 1)
+    out.backward(_t([0.1] * out.numel(), out.shape))
+    xr, wr, br = (torch.tensor(v, dtype=torch.float64).view(s).requires_grad_()
+                  for v, s in ((iv, (2, 2, 4, 4, 4)), (wv, (3, 2, 3, 3, 3)), (bv, (3,))))
+    outr = F.conv3d(xr, wr, br, stride=1, padding=1)
+    outr.backward(torch.full_like(outr, 0.1))
+    assert max(err(out, outr), err(x.grad, xr.grad), err(w.grad, wr.grad), err(b.grad, br.grad)) < 1e-3
+
+    pv = [(i % 20) / 10.0 for i in range(2 * 2 * 64)]
+    x = _t(pv, [2, 2, 4, 4, 4], True)
+    out = lt.Ops.max_pool3d(x, 2, 2, 0)
+    out.backward(_t([0.5] * out.numel(), out.shape))
+    xr = torch.tensor(pv, dtype=torch.float64).view(2, 2, 4, 4, 4).requires_grad_()
+    outr = F.max_pool3d(xr, 2, 2, 0)
+    outr.backward(torch.full_like(outr, 0.5))
+    assert err(out, outr) < 1e-3 and err(x.grad, xr.grad) < 1e-3
+
+    lv = [i / 10.0 for i in range(2 * 3 * 4)]
+    x = _t(lv, [2, 3, 4], True)
+    lin = lt.nn.Linear(4, 5)
+    out = lin.forward(x)
+    assert out.shape == [2, 3, 5]
+    out.backward(_t([0.2] * out.numel(), out.shape))
+    xr = torch.tensor(lv, dtype=torch.float64).view(2, 3, 4).requires_grad_()
+    wr = torch.tensor(lin.weight.to_vector(), dtype=torch.float64).view(5, 4).requires_grad_()
+    br = torch.tensor(lin.bias.to_vector(), dtype=torch.float64).requires_grad_()
+    outr = F.linear(xr, wr, br)
+    outr.backward(torch.full_like(outr, 0.2))
+    assert max(err(out, outr), err(x.grad, xr.grad), err(lin.weight.grad, wr.grad), err(lin.bias.grad, br.grad)) < 1e-3
+
+
+def test_integrity_fixes_batchnorm_of_one_value_views_clones_and_dataset():
+    import math
+    import pytest
+    bn = lt.nn.BatchNorm2d(1)
+    bn.to(CPU)
+    x = _t([3.5], [1, 1, 1, 1], True)
+    out = bn.forward(x)
+    rv = bn.running_var.to_vector()[0]
+    assert not math.isnan(rv) and not math.isinf(rv)
+    out.backward(_t([1.0], [1, 1, 1, 1]))
+    assert x.grad is not None
+    xt = _t([1, 2, 3, 4, 5, 6], [2, 3], True).transpose(0, 1)
+    with pytest.raises(RuntimeError):
+        xt.view([6])
+    xc = _t([0, 1, 2, 3, 4, 5], [2, 3]).transpose(0, 1).clone()
+    assert xc.to_vector() == [0.0, 3.0, 1.0, 4.0, 2.0, 5.0] and xc.is_contiguous()
+    ds = lt.data.TensorDataset(_t([1, 2, 3, 4], [4, 1]), _t([10, 20, 30, 40], [4, 1]))
+    sx, sy = ds.get(2)
+    assert sx.device == CPU and sy.device == CPU
+    assert abs(sx.to_vector()[0] - 3.0) < 1e-5 and abs(sy.to_vector()[0] - 30.0) < 1e-5
