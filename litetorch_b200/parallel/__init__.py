@@ -1,7 +1,9 @@
 """`lt.distributed`: process group, collectives, device mesh, FSDP / TP / SP / PP / CP / EP."""
 from .process_group import (FileStore, OverlappedAllReducer, ProcessGroup, RankFailure, TCPStore, Watchdog,
-                            all_reduce_bucketed, all_reduce_grads, init_process_group, overlapped_all_reduce,
-                            overlapped_reduce_scatter, sync_overlapped_all_reduce)
+                            all_gather, all_reduce, all_reduce_async, all_reduce_bucketed, all_reduce_grads, barrier,
+                            broadcast, get_rank, get_world_size, init_process_group, overlapped_all_reduce,
+                            overlapped_reduce_scatter, recv_tensor, reduce_scatter, send_tensor, shutdown,
+                            sync_overlapped_all_reduce)
 from .mesh import DeviceMesh, DTensor, Placement, PlacementType, distribute_tensor
 from .tp import ColumnParallelLinear, RowParallelLinear, vocab_parallel_cross_entropy
 from .pp import PipelineParallelModule

@@ -268,7 +268,11 @@ class ProcessGroup:
             out.view(-1)[:s.numel()].copy_(s.view(-1))
         return full if full is not None else Tensor(out)
 
-    def reduce_scatter(self, full: Tensor, shard: Optional[Tensor] = None) -> Tensor:
+    def reduce_scatter(self, shard: Tensor, full: Optional[Tensor] = None) -> Tensor:
+        """`reduce_scatter(shard, full)`, the reference's form (src/bindings/python_bindings.cpp:733), sums `full` over the
+        ranks and leaves this rank's slice in `shard`; `reduce_scatter(full)` returns the slice as a new tensor."""
+        if full is None:
+            shard, full = None, shard
         f = _unwrap(full).contiguous()
         W = self.get_world_size()
         out = _unwrap(shard) if shard is not None else torch.empty(f.numel() // W, dtype=f.dtype, device=f.device)
@@ -317,8 +321,12 @@ class ProcessGroup:
         t = torch.empty([int(x) for x in h[2:2 + int(h[0])]], dtype=dtype, device=dev)
         dist.recv(t, src)
         if dst is not None:
+            d = _unwrap(dst)
             with torch.no_grad():
-                _unwrap(dst).copy_(t.reshape(_unwrap(dst).shape))
+                if d.numel() == t.numel() and d.dtype == t.dtype:
+                    d.copy_(t.reshape(d.shape))
+                else:                       # the destination takes the sender's shape, as the reference's does
+                    d.data = t.to(d.dtype)
             return dst if isinstance(dst, Tensor) else Tensor(dst)
         return Tensor(t)
 
@@ -346,6 +354,63 @@ def init_process_group(rank: int, world_size: int, master_addr: str = "127.0.0.1
     pg = ProcessGroup.get()
     pg.init(rank, world_size, master_addr, master_port, **kw)
     return pg
+
+
+# Free functions over the process-wide group, as in the reference's C++ API (include/litetorch/distributed.h:82-92).
+def shutdown() -> None:
+    ProcessGroup.get().shutdown()
+
+
+def get_rank() -> int:
+    return ProcessGroup.get().get_rank()
+
+
+def get_world_size() -> int:
+    return ProcessGroup.get().get_world_size()
+
+
+def barrier(timeout_s: float = 600.0) -> None:
+    ProcessGroup.get().barrier(timeout_s)
+
+
+def all_reduce(tensor: Tensor, average: bool = False) -> Tensor:
+    return ProcessGroup.get().all_reduce(tensor, average)
+
+
+def all_reduce_async(tensor: Tensor):
+    """Starts the sum and returns a handle whose `wait()` (or `get()`) completes it."""
+    class _Done:
+        def __init__(self, work):
+            self.work = work
+
+        def wait(self):
+            if self.work is not None:
+                self.work.wait()
+                self.work = None
+
+        get = wait
+    pg = ProcessGroup.get()
+    return _Done(dist.all_reduce(_unwrap(tensor), async_op=True) if pg._live() else None)
+
+
+def broadcast(tensor: Tensor, src: int = 0) -> Tensor:
+    return ProcessGroup.get().broadcast(tensor, src)
+
+
+def all_gather(shard: Tensor, full: Optional[Tensor] = None) -> Tensor:
+    return ProcessGroup.get().all_gather(shard, full)
+
+
+def reduce_scatter(shard: Tensor, full: Optional[Tensor] = None) -> Tensor:
+    return ProcessGroup.get().reduce_scatter(shard, full)
+
+
+def send_tensor(tensor: Tensor, dst: int) -> None:
+    ProcessGroup.get().send_tensor(tensor, dst)
+
+
+def recv_tensor(tensor=None, src: Optional[int] = None, device=None) -> Tensor:
+    return ProcessGroup.get().recv_tensor(tensor, src, device)
 
 
 def all_reduce_grads(module, average: bool = True) -> None:
@@ -408,7 +473,7 @@ class OverlappedAllReducer:
         if dist.is_initialized() and dist.get_world_size() > 1 and _unwrap(full).is_cuda:
             self._works.append(dist.reduce_scatter_tensor(_unwrap(shard).view(-1), _unwrap(full).contiguous().view(-1), async_op=True))
         else:
-            ProcessGroup.get().reduce_scatter(full, shard)
+            ProcessGroup.get().reduce_scatter(shard, full)
 
     def sync(self) -> None:
         for w in self._works:

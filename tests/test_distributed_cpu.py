@@ -363,3 +363,43 @@ def test_reference_environment_variables_are_honoured(tmp_path):
     from litetorch_b200.parallel import nccl_native as NN
     with pytest.raises(NN.NcclError):
         NN.read_id_file(os.path.join(str(tmp_path), "never_written"), 0.2)
+
+
+def test_reference_distributed_test_replay(tmp_path):
+    """The expectations of the reference's tests/distributed_test.cpp through the module-level functions: its host
+    all-reduce averages (here `average=True`), `recv_tensor` gives the destination the sender's shape, and a two-stage
+    pipeline of doubling modules turns 5 into 20 on the last rank."""
+    res = run_ranks('''
+        D = lt.distributed
+        cpu = lt.Device("cpu")
+        t = lt.Tensor.from_vector([float(rank), float(rank * 2)], [2], cpu, False)
+        D.all_reduce(t, average=True)
+        bc = lt.Tensor.from_vector([42.0 if rank == 0 else 0.0], [1], cpu, False)
+        D.broadcast(bc, 0)
+        got = None
+        if rank == 0:
+            D.send_tensor(lt.Tensor.from_vector([100.0, 200.0, 300.0], [3], cpu, False), 1)
+        else:
+            r = lt.Tensor.create([1], cpu)
+            D.recv_tensor(r, 0)
+            got = [r.shape, r.to_vector()]
+        class TimesTwo(lt.nn.Module):
+            def forward(self, input):
+                return lt.Ops.mul(input, lt.Tensor.from_vector([2.0], [1], cpu, False))
+        pp = D.PipelineParallelModule(TimesTwo())
+        out = pp.forward(lt.Tensor.from_vector([5.0], [1], cpu, False) if rank == 0 else None)
+        last = out.to_vector() if rank == 1 else None
+        sh = lt.Tensor.from_vector([0.0, 0.0], [2], cpu, False)
+        D.reduce_scatter(sh, lt.Tensor.from_vector([1.0, 2.0, 3.0, 4.0], [4], cpu, False))
+        h = D.all_reduce_async(lt.Tensor.from_vector([1.0], [1], cpu, False)); h.wait()
+        objs = [None, None]
+        dist.all_gather_object(objs, (got, last, sh.to_vector()))
+        if rank == 0:
+            print("RESULT " + json.dumps(dict(avg=t.to_vector(), bc=bc.to_vector(), recv=objs[1][0], last=objs[1][1],
+                                              rs=[objs[0][2], objs[1][2]], ids=[D.get_rank(), D.get_world_size()])))
+        D.barrier()
+        D.shutdown()
+    ''', tmp_path=tmp_path, port=29877)
+    assert res["avg"] == [0.5, 1.0] and res["bc"] == [42.0]
+    assert res["recv"] == [[3], [100.0, 200.0, 300.0]] and res["last"] == [20.0]
+    assert res["rs"] == [[2.0, 4.0], [6.0, 8.0]] and res["ids"] == [0, 2]
