@@ -610,3 +610,106 @@ def test_integrity_fixes_batchnorm_of_one_value_views_clones_and_dataset():
     sx, sy = ds.get(2)
     assert sx.device == CPU and sy.device == CPU
     assert abs(sx.to_vector()[0] - 3.0) < 1e-5 and abs(sy.to_vector()[0] - 30.0) < 1e-5
+
+
+# ---- tests/gpt_training_test.cpp, tests/memory_leak_test.cpp
+def test_qat_decoder_under_autocast_jit_round_trip_and_single_rank_group(tmp_path):
+    Q = lt.quantization
+
+    class Decoder(lt.nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            mk = lambda i, o: Q.QATLinear(lt.nn.Linear(i, o, False), w_scale=0.01, a_scale=0.01, b=8)
+            self.c_attn, self.c_proj, self.c_fc, self.c_proj2 = mk(d, 3 * d), mk(d, d), mk(d, 4 * d), mk(4 * d, d)
+            for m in (self.c_attn, self.c_proj, self.c_fc, self.c_proj2):
+                m.qat_enabled = True
+
+        def forward(self, x):
+            self.c_attn.forward(x)
+            return self.c_proj2.forward(self.c_fc.forward(self.c_proj.forward(x)))
+
+    x = _t([1.0, -0.5, 0.2, 0.8, -0.1, 0.4, -0.9, 0.3, -0.2, 0.5, 0.6, -0.7, 0.1, -0.3, 0.8, 0.2], [2, 8], True)
+    with lt.amp.AutocastGuard(True, lt.DataType.FP16):
+        out = Decoder(8).forward(x)
+        assert out.shape == [2, 8]
+        lt.Ops.sum(out).backward()
+    assert x.grad is not None
+    J = lt.jit
+    a, b = J.JITVar(J.OpType.INPUT, "x"), J.JITVar(J.OpType.INPUT, "y")
+    path = str(tmp_path / "gpt_jit_model.txt")
+    J.JITFunction("gpt_fwd", J.gelu(a * b), [a, b]).save(path)
+    assert len(J.JITFunction.load(path)([_t([1, 2, 3, 4], [4]), _t([0.5] * 4, [4])]).to_vector()) == 4
+    pg = lt.distributed.ProcessGroup.get()
+    pg.init(0, 1, "127.0.0.1", 12347)
+    t = _t([2.0, 4.0], [2])
+    pg.all_reduce(t)
+    assert t.to_vector() == [2.0, 4.0]
+    pg.shutdown()
+
+
+def test_decoder_layer_training_loop_does_not_grow_the_process():
+    import gc
+    import resource
+
+    def rss_mb():
+        with open("/proc/self/status") as f:
+            for line in f:
+                if line.startswith("VmRSS:"):
+                    return int(line.split()[1]) / 1024.0
+        return resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 1024.0
+
+    layer = lt.nn.TransformerDecoderLayer(16, 4, 32)
+    layer.to(CPU)
+    tv, mv = [0.5] * (4 * 8 * 16), [-0.5] * (4 * 12 * 16)
+
+    def step():
+        tgt, mem = _t(tv, [4, 8, 16], True), _t(mv, [4, 12, 16], True)
+        lt.Ops.sum(layer.forward(tgt, mem)).backward()
+        for p in layer.parameters():
+            p.grad = None
+    for _ in range(30):
+        step()
+    gc.collect()
+    start = rss_mb()
+    for _ in range(300):
+        step()
+    gc.collect()
+    assert rss_mb() - start < 24.0
+
+
+# ---- tests/stress_test.cpp
+def test_deep_convnet_trains_with_finite_decreasing_loss():
+    import math
+    import torch
+    g = torch.Generator().manual_seed(42)
+    xv = (torch.randn(16 * 3 * 16 * 16, generator=g) * 0.2).tolist()
+    yv = [1.0 if j == i % 10 else 0.0 for i in range(16) for j in range(10)]
+    x, y = _t(xv, [16, 3, 16, 16]), _t(yv, [16, 10])
+    nn = lt.nn
+    model = nn.Sequential()
+    for m in (nn.Conv2d(3, 8, 3, 1, 1), nn.BatchNorm2d(8), nn.ReLU(), nn.MaxPool2d(2, 2),
+              nn.Conv2d(8, 16, 3, 1, 1), nn.BatchNorm2d(16), nn.ReLU(), nn.MaxPool2d(2, 2),
+              nn.AdaptiveAvgPool2d(2, 2), nn.Flatten(), nn.Linear(64, 32), nn.LayerNorm([32]), nn.GELU(),
+              nn.Linear(32, 10), nn.Softmax(-1)):
+        model.add(m)
+    model.to(CPU)
+    opt = lt.optim.Adam(model.parameters(), 0.01)
+    losses = []
+    for _ in range(40):
+        opt.zero_grad()
+        loss = lt.Ops.mse_loss(model.forward(x), y)
+        loss.backward()
+        assert all(p.grad is not None for p in model.parameters())
+        opt.step()
+        losses.append(loss.item())
+        assert not math.isnan(losses[-1]) and not math.isinf(losses[-1])
+    assert losses[-1] < losses[0]
+
+
+def test_matmul_256_matches_a_float64_product():
+    import torch
+    g = torch.Generator().manual_seed(1234)
+    a, b = torch.rand(256, 256, generator=g) - 0.5, torch.rand(256, 256, generator=g) - 0.5
+    c = lt.Ops.matmul(lt.Tensor.from_torch(a), lt.Tensor.from_torch(b))
+    ref = a.double() @ b.double()
+    assert float((torch.tensor(c.to_vector(), dtype=torch.float64).view(256, 256) - ref).abs().max()) < 1e-3
