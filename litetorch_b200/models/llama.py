@@ -299,8 +299,12 @@ class LlamaEngine:
 
     def __init__(self, cfg: LlamaConfig, device="cuda", weights=None, seed: int = 0, lr: float = 3e-4,
                  betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, activation_checkpointing: bool = False,
-                 world_size: int = 1, head_chunk_rows: int = 0):
+                 world_size: int = 1, head_chunk_rows: int = 0, grad_clip: float = 0.0):
         self.cfg = cfg
+        # > 0: the gradient is scaled so that its global L2 norm does not exceed this value (the reference's
+        # Ops::clip_grad_norm_, src/ops/clip_grad.cpp); a non-finite gradient skips the update
+        self.grad_clip = float(grad_clip)
+        self.last_grad_norm = None            # device scalar: norm before clipping, of the latest clipped step
         # > 0: the LM head and the loss go through in chunks of that many token rows, so that only [chunk, vocab]
         # logits exist at a time (whole weights on this rank only)
         self.head_chunk_rows = int(head_chunk_rows)
@@ -308,6 +312,10 @@ class LlamaEngine:
         self.K = kernels_for(self.device)
         self.w = weights if weights is not None else LocalWeights(cfg, self.device, seed)
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        if self.grad_clip > 0 and not isinstance(self.w, LocalWeights):
+            raise NotImplementedError("gradient clipping needs the whole gradient before the first update: it is "
+                                      "available with unsharded weights; the sharded providers update each bucket "
+                                      "under the backward pass")
         # True: every layer is recomputed in the backward pass; an integer k: only the first k layers are
         self.ckpt_layers = cfg.n_layers if activation_checkpointing is True else int(activation_checkpointing or 0)
         self.ckpt = self.ckpt_layers > 0
@@ -461,8 +469,23 @@ class LlamaEngine:
                               weight_decay=self.weight_decay, step=self.step_count, dyn=dyn)
         self.kernel_launches += 2
 
+    def _clip_dyn(self) -> torch.Tensor:
+        """{gradient multiplier, non-finite flag, norm} on the device from one pass over the flat gradient: the AdamW
+        kernel multiplies every gradient by the first and returns at once when the second is set (no host sync)."""
+        stats = torch.zeros(2, dtype=torch.float32, device=self.device)
+        dyn = torch.zeros(3, dtype=torch.float32, device=self.device)
+        self.K.sumsq(self.w.flat_g, stats)
+        self.K.clip_coef(stats, dyn, self.grad_clip)
+        self.last_grad_norm = dyn[2]
+        self.kernel_launches += 2
+        return dyn
+
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """The public one-call training step: forward, backward, AdamW.  Returns the loss (device scalar)."""
+        if self.grad_clip > 0:
+            loss = self.forward_backward(tokens, targets)
+            self.optimizer_step(dyn=self._clip_dyn())
+            return loss
         self.w.begin_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                           weight_decay=self.weight_decay, step=self.step_count + 1)
         loss = self.forward_backward(tokens, targets, fused_update=True)
@@ -479,6 +502,13 @@ class LlamaEngine:
         k = len(micro_batches)
         if k == 1:
             return self.train_step(*micro_batches[0])
+        if self.grad_clip > 0:
+            total = None
+            for i, (tok, tgt) in enumerate(micro_batches):
+                loss = self.forward_backward(tok, tgt, accumulate=i > 0, loss_scale=1.0 / k)
+                total = loss / k if total is None else total + loss / k
+            self.optimizer_step(dyn=self._clip_dyn())
+            return total
         self.w.begin_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                           weight_decay=self.weight_decay, step=self.step_count + 1)
         total = None

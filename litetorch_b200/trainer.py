@@ -25,7 +25,7 @@ class Trainer:
     def __init__(self, cfg: LlamaConfig, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, seed: int = 0, activation_checkpointing: bool = False,
                  device: Optional[str] = None, parallel: str = "auto", tp: int = 1, param_dtype=torch.bfloat16,
-                 micro_batches: int = 1):
+                 micro_batches: int = 1, grad_clip: float = 0.0):
         self.micro_batches = max(1, int(micro_batches))     # default split of a `step` batch (gradient accumulation)
         self.rank = int(os.environ.get("RANK", "0"))
         self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
@@ -55,7 +55,7 @@ class Trainer:
             weights = LocalWeights(cfg, self.device, seed, param_dtype=param_dtype)
         self.engine = LlamaEngine(cfg, self.device, weights=weights, seed=seed, lr=lr, betas=betas, eps=eps,
                                   weight_decay=weight_decay, activation_checkpointing=activation_checkpointing,
-                                  world_size=self.dp)
+                                  world_size=self.dp, grad_clip=grad_clip)
         self._tok = None
         self._tgt = None
         self.h2d_bytes = 0
@@ -77,7 +77,7 @@ class Trainer:
         return cls(run.llama_config(), lr=o.lr, betas=(o.beta1, o.beta2), eps=o.eps, weight_decay=o.weight_decay,
                    seed=run.seed, activation_checkpointing=run.activation_checkpointing,
                    parallel=("hybrid" if p.tp > 1 else "fsdp") if (p.zero_stage >= 1 or p.tp > 1) else "none", tp=p.tp,
-                   **dict({"micro_batches": getattr(run, "micro_batches", 1)}, **kw))
+                   **dict({"micro_batches": getattr(run, "micro_batches", 1), "grad_clip": o.grad_clip}, **kw))
 
     # The learning rate lives in the engine and is read at every optimizer step; with these three members a trainer can
     # stand where the LR schedulers expect an optimizer: `lt.optim.CosineAnnealingLR(trainer, T_max=...)`.

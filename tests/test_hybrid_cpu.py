@@ -234,3 +234,53 @@ def test_gradient_accumulation_equals_the_one_batch_step(tmp_path, nproc, tp):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert all(abs(x - y) < 1e-5 for x, y in zip(res["la"], res["lb"])) and res["diff"] < 1e-4, res
+
+
+def test_gradient_clipping_scales_the_update_and_skips_non_finite_gradients():
+    """`grad_clip` on the unsharded engine: the step equals the one taken with the gradient scaled by hand to the bound,
+    the norm before clipping is reported, a bound above the norm changes nothing, and a NaN gradient leaves the
+    parameters as they were."""
+    import torch
+    from litetorch_b200.models.llama import LlamaConfig, LlamaEngine, LocalWeights
+    from litetorch_b200.trainer import Trainer
+    cfg = LlamaConfig.tiny()
+    gen = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=gen)
+    x, y = tok[:, :-1], tok[:, 1:]
+    mk = lambda clip: LlamaEngine(cfg, "cpu", weights=LocalWeights(cfg, "cpu", seed=3, param_dtype=torch.float32), grad_clip=clip)
+    probe = mk(0.0)
+    probe.forward_backward(x, y)
+    norm = float(probe.w.flat_g.double().norm())
+    bound = norm / 4
+    clipped, manual, loose = mk(bound), mk(0.0), mk(norm * 10)
+    diff = lambda e1, e2: max(float((a - b).abs().max()) for a, b in zip(e1.w.parameters(), e2.w.parameters()))
+    probe.optimizer_step()
+    for step in range(3):        # Adam's first step does not depend on the gradient's scale: compare over several
+        clipped.train_step(x, y)
+        if step == 0:
+            assert abs(float(clipped.last_grad_norm) - norm) < 1e-5 * norm
+        manual.forward_backward(x, y)
+        n = float(manual.w.flat_g.double().norm())
+        manual.w.flat_g.mul_(min(1.0, bound / (n + 1e-6)))
+        manual.optimizer_step()
+        loose.train_step(x, y)
+        if step:
+            probe.train_step(x, y)
+    assert diff(clipped, manual) < 1e-6
+    assert diff(loose, probe) < 1e-7
+    assert diff(clipped, probe) > 1e-5          # the bound did change the trajectory
+    # accumulation goes through the same clipping
+    acc, one = mk(bound), mk(bound)
+    acc.train_step_accumulated([(x[:1], y[:1]), (x[1:], y[1:])])
+    one.train_step(x, y)
+    assert max(float((a - b).abs().max()) for a, b in zip(acc.w.parameters(), one.w.parameters())) < 1e-5
+    # a non-finite gradient: the update is skipped on the device
+    bad = mk(bound)
+    before = [p.clone() for p in bad.w.parameters()]
+    bad.forward_backward(x, y)
+    bad.w.flat_g[7] = float("nan")
+    bad.optimizer_step(dyn=bad._clip_dyn())
+    assert all(torch.equal(a, b) for a, b in zip(before, bad.w.parameters()))
+    t = Trainer(cfg, device="cpu", param_dtype=torch.float32, parallel="none", grad_clip=bound, seed=3)
+    t.step(x, y)
+    assert abs(float(t.engine.last_grad_norm) - norm) < 1e-4 * norm
