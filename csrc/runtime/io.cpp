@@ -6,7 +6,11 @@
 // 0xEDB88320, initial value 0xFFFFFFFF, final xor) of every preceding byte as the last uint32.
 // Tensor record: u32 ndims, i64 dim[ndims], u64 numel, f32 data[numel].
 // The reader loads the whole file and validates the CRC before it hands out a single value, so a caller
-// never mutates its tensors from a corrupt file.
+// never mutates its tensors from a corrupt file.  The writer builds the file under a temporary name beside
+// the target and renames it over the target when every byte and the CRC are on disk: a process that dies in
+// the middle of a save leaves the previous file as it was.
+#include <unistd.h>
+
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -37,6 +41,7 @@ uint32_t crc_update(uint32_t crc, const void* data, size_t n) {
 
 struct Writer {
   FILE* f = nullptr;
+  std::string path, tmp;
   uint32_t crc = 0xFFFFFFFFu;
   bool failed = false;
   void put(const void* d, size_t n) {
@@ -65,10 +70,13 @@ extern "C" {
 uint32_t lt_crc32(const void* data, uint64_t n) { return crc_update(0xFFFFFFFFu, data, n) ^ 0xFFFFFFFFu; }
 
 void* lt_ckpt_writer_open(const char* path, const char* magic4) {
-  FILE* f = fopen(path, "wb");
+  const std::string tmp = std::string(path) + ".tmp." + std::to_string(static_cast<long>(getpid()));
+  FILE* f = fopen(tmp.c_str(), "wb");
   if (!f) return nullptr;
   Writer* w = new Writer();
   w->f = f;
+  w->path = path;
+  w->tmp = tmp;
   w->put(magic4, 4);
   return w;
 }
@@ -86,15 +94,19 @@ int lt_ckpt_write_tensor(void* h, int ndims, const int64_t* dims, const float* d
   w->put(data, sizeof(float) * numel);
   return w->failed ? -1 : 0;
 }
-// Appends the CRC, flushes and closes. Returns 0 on success, -1 on any write failure (disk full...).
+// Appends the CRC, flushes, closes and publishes the file under its final name. Returns 0 on success, -1 on any
+// write failure (disk full...), in which case the target is untouched and the temporary file is removed.
 int lt_ckpt_writer_close(void* h) {
   Writer* w = static_cast<Writer*>(h);
   const uint32_t final_crc = w->crc ^ 0xFFFFFFFFu;
   int rc = 0;
   if (!w->failed && fwrite(&final_crc, 1, 4, w->f) != 4) rc = -1;
   if (fflush(w->f) != 0) rc = -1;
+  if (rc == 0 && fsync(fileno(w->f)) != 0) rc = -1;
   if (fclose(w->f) != 0) rc = -1;
   if (w->failed) rc = -1;
+  if (rc == 0 && rename(w->tmp.c_str(), w->path.c_str()) != 0) rc = -1;
+  if (rc != 0) remove(w->tmp.c_str());
   delete w;
   return rc;
 }

@@ -49,6 +49,31 @@ def test_corrupt_or_mismatched_checkpoint_leaves_model_untouched(tmp_path):
     assert all(torch.equal(_unwrap(p), b) for p, b in zip(victim.parameters(), before))
 
 
+def test_a_save_that_dies_half_way_leaves_the_previous_file_intact(tmp_path):
+    """The writer builds the file under a temporary name and renames it at the end: a process that exits in the middle
+    of `lt.save` does not damage the file that was there, and a finished save leaves no temporary file behind."""
+    import subprocess
+    import sys
+    net = lt.nn.Linear(4, 4)
+    path = str(tmp_path / "m.ltw1")
+    lt.save(net, path)
+    good = open(path, "rb").read()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys, os; sys.path.insert(0, %r)\n"
+            "import ctypes\n"
+            "from litetorch_b200 import serialization as S\n"
+            "lib = S._lib()\n"
+            "w = lib.lt_ckpt_writer_open(%r.encode(), b'LTW1')\n"
+            "lib.lt_ckpt_write_u32(w, 99)\n"
+            "os._exit(0)\n") % (root, path)
+    subprocess.run([sys.executable, "-c", code], check=True, timeout=120)
+    assert open(path, "rb").read() == good
+    lt.load(lt.nn.Linear(4, 4), path)
+    lt.save(net, path)
+    leftovers = [f for f in os.listdir(tmp_path) if f.startswith("m.ltw1.tmp.")]
+    assert len(leftovers) == 1                      # only the dead process's partial file; the finished saves left none
+
+
 @pytest.mark.parametrize("kind,magic", [("adam", b"LTAD"), ("adamw", b"LTAW"), ("sgd", b"LTSG"), ("rmsprop", b"LTRP")])
 def test_optimizer_state_roundtrip_resumes_exactly(tmp_path, kind, magic):
     torch.manual_seed(0)
