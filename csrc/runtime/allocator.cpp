@@ -8,6 +8,8 @@
 // caller: malloc/free for host pools, and cudaMalloc/cudaFree (stream-ordered reuse handled by the CUDA-side
 // wrapper) for device pools.  Unlike the reference (512 MB default), a pool has no default cap: 180 GB of
 // HBM3e per GPU is there to be used, and a cap is opt-in.
+#include "lt_host.h"
+
 #include <cstdint>
 #include <cstdlib>
 #include <list>

@@ -6,6 +6,8 @@
 // from an `LTDL` file: magic, u64 current_index, u64 worker_index, u64 epoch_id, u8 shuffle, u64 n,
 // u64 indices[n], CRC-32 of all preceding bytes.  Batches are assembled straight into buffers the caller
 // provides (pinned host memory, so that the copy to the GPU can be asynchronous).
+#include "lt_host.h"
+
 #include <algorithm>
 #include <atomic>
 #include <condition_variable>
@@ -17,12 +19,6 @@
 #include <random>
 #include <thread>
 #include <vector>
-
-extern "C" uint32_t lt_crc32(const void* data, uint64_t n);
-extern "C" void lt_parallel_for(void* fn_ptr, void* ctx, uint64_t n, uint64_t min_parallel);
-extern "C" void* lt_pool_create(void* ralloc, void* rfree, void* ctx, uint64_t max_cached, uint64_t max_block, uint64_t round_to);
-extern "C" void* lt_pool_alloc(void* pool, uint64_t bytes);
-extern "C" void lt_pool_free(void* pool, void* ptr);
 
 namespace {
 

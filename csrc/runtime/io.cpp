@@ -9,6 +9,8 @@
 // never mutates its tensors from a corrupt file.  The writer builds the file under a temporary name beside
 // the target and renames it over the target when every byte and the CRC are on disk: a process that dies in
 // the middle of a save leaves the previous file as it was.
+#include "lt_host.h"
+
 #include <unistd.h>
 
 #include <cstdint>

@@ -7,6 +7,8 @@
 // saved files is read as well.  The reference generates a fused kernel for OpenCL only and evaluates node by
 // node on CUDA (src/ops/jit.cpp:279-327); here `lt_jit_cuda_source` emits one CUDA kernel for the whole tree,
 // which the CUDA-side runtime compiles with NVRTC and caches.
+#include "lt_host.h"
+
 #include <cmath>
 #include <cstdint>
 #include <cstring>

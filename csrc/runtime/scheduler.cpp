@@ -7,6 +7,8 @@
 // caller, stop on EOS or max_new_tokens, blocks recycled on completion.  The model stays outside: `plan`
 // returns what to run this step, `commit_*` feeds the sampled tokens back.
 // Guided decoding follows src/llm/guided_decoding.cpp:8-65 ("digits", "prefix:<s>", "regex:<re>").
+#include "lt_host.h"
+
 #include <algorithm>
 #include <cctype>
 #include <cstdint>

@@ -10,6 +10,8 @@
 // Wire protocol (one request per message, little-endian): u8 op, u32 key_len, key, u64 val_len, val.
 //   op 1 SET -> u8 ok          op 2 GET -> u8 found, u64 len, bytes       op 3 ADD(i64 delta) -> i64 value
 //   op 4 HEARTBEAT(rank in key) -> u8 ok     op 5 AGES -> u32 n, n x (i32 rank, i64 age_ms)
+#include "lt_host.h"
+
 #include <arpa/inet.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>

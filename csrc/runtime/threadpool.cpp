@@ -1,6 +1,8 @@
 // Small fixed thread pool with a blocking parallel_for, used by host-side data preparation and
 // checkpoint I/O.  Same contract as the reference pool (include/litetorch/thread_pool.h:15-157): ranges
 // shorter than a threshold run inline on the caller, the caller executes the last chunk itself.
+#include "lt_host.h"
+
 #include <cstdlib>
 #include <algorithm>
 #include <atomic>

@@ -1,0 +1,41 @@
+"""The C++ side without Python in the loop: the CMake project builds the host runtime and the demo program of
+examples/native_demo.cpp, the demo passes its own checks, and the public header declares every exported function of the
+runtime."""
+import os
+import re
+import shutil
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(shutil.which("cmake") is None, reason="cmake not installed")
+def test_cmake_builds_the_host_runtime_and_the_demo_runs(tmp_path):
+    build = str(tmp_path / "b")
+    cfg = subprocess.run(["cmake", "-S", ROOT, "-B", build, "-DLT_BUILD_CUDA=OFF", "-DLT_OUTPUT_DIR=" + build + "/lib"],
+                         capture_output=True, text=True, timeout=300)
+    assert cfg.returncode == 0, cfg.stdout[-2000:] + cfg.stderr[-2000:]
+    mk = subprocess.run(["cmake", "--build", build, "-j", "4"], capture_output=True, text=True, timeout=900)
+    assert mk.returncode == 0, mk.stdout[-3000:] + mk.stderr[-3000:]
+    assert os.path.exists(os.path.join(build, "lib", "liblt_host.so"))
+    run = subprocess.run([os.path.join(build, "lt_native_demo"), str(tmp_path)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and "all checks passed" in run.stdout, run.stdout + run.stderr
+
+
+def test_the_public_header_declares_every_exported_function():
+    header = open(os.path.join(ROOT, "csrc", "runtime", "lt_host.h")).read()
+    declared = set(re.findall(r"\b(lt_[a-z0-9_]+)\(", header))
+    defined = set()
+    for name in os.listdir(os.path.join(ROOT, "csrc", "runtime")):
+        if name.endswith(".cpp"):
+            src = open(os.path.join(ROOT, "csrc", "runtime", name)).read()
+            assert '#include "lt_host.h"' in src, name          # a drifting definition then fails to compile
+            defined |= set(re.findall(r"^[A-Za-z_][A-Za-z0-9_ ]*\**\s+(lt_[a-z0-9_]+)\([^;{]*\)\s*\{", src, re.M))
+    assert defined and defined <= declared, sorted(defined - declared)
+    # and the library really exports them
+    from litetorch_b200._native import host_lib
+    lib = host_lib()
+    for fn in sorted(declared):
+        assert hasattr(lib, fn), fn
