@@ -3,6 +3,7 @@
 // CUDA stream.  Counterpart of the reference's NCCLBridge (src/distributed/distributed.cpp:785-905: nine entry points
 // resolved with dlsym, id exchanged through a file or TCP) - with the 128-byte id passed to ncclCommInitRank by value,
 // which is what the library's ABI asks for.
+#include "kernels/lt_cuda.h"
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 

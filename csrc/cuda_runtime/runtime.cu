@@ -5,6 +5,7 @@
 // stream-capture graphs whose replay is followed by an eager re-run (src/backend/gpu_native/entrypoint.cu:162-215;
 // here a replay is only a replay), and the runtime JIT that shells out to `nvcc` and dlopens the result
 // (entrypoint.cu:380-417; here NVRTC in process, no temporary files).
+#include "kernels/lt_cuda.h"
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>

@@ -1,4 +1,5 @@
 // Host-side helpers: status word, SM count, tensor-map encoding via the driver entry point.
+#include "lt_cuda.h"
 #include "host.h"
 
 #include <mutex>

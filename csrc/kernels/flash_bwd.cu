@@ -13,6 +13,7 @@
 //   dQ_i = dS K         -> red.global.add into an fp32 accumulator, converted to bf16 by a last kernel
 //
 // delta = rowsum(O * dO) comes from a small pre-pass.  All waits are bounded (see common/ptx.cuh).
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -12,6 +12,7 @@
 // The running maximum is updated lazily: O in TMEM is rescaled only when a row's maximum grew by more
 // than 2^8, which keeps exp2 arguments bounded and makes the rescale (tcgen05.ld/st of O) rare.
 // Output: O [B, Tq, Hq, D] bf16 and the natural-log LSE [B, Hq, Tq] fp32 for the backward pass.
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -17,6 +17,7 @@
 //    ZeRO3Optimizer::step (src/distributed/fsdp_wrapper.cpp:81-96, src/optim/zero3_optimizer.cpp:11-105).
 // 3. lt_embedding_fwd_sharded: embedding rows fetched from the owning rank.
 // 4. lt_signal_barrier: all-ranks barrier on symmetric flags (bounded wait).
+#include "lt_cuda.h"
 #include "comm_common.cuh"
 #include "gemm_sm100_2cta.cuh"
 
@@ -440,14 +441,7 @@ static void setup_gather(GatherArgs& g, int gather_operand, int M, int N, int K,
 
 extern "C" {
 
-// Description of the next gather-GEMM of the sequence, for prefetching (all fields as in lt_ag_gemm_bf16).
-struct LtNextGather {
-  int gather_operand, M, N, K, rows_per_rank, pad;
-  const void* shard_ptrs[8];
-  void* full;
-  void* flags;
-  unsigned epoch, pad2;
-};
+// LtNextGather (lt_cuda.h): description of the next gather-GEMM of the sequence, for prefetching.
 
 // GEMM whose gathered operand is assembled from `world` row shards while the kernel runs.
 //   gather_operand: 0 = A (stored [M, K], rows sharded, tiles gated by M block),

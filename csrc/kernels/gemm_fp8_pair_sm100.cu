@@ -9,6 +9,7 @@
 // Roles per CTA (576 threads): warp 0 TMA producer (both CTAs; bytes counted on the even CTA's barrier), warp 1 TMEM
 // allocation in both CTAs and MMA issue in the even CTA, warps 2-17 promotion + epilogue of the CTA's own 128 rows.
 // The reference has no fp8 GEMM that its ops use (cublasLtMatmul wrapper, src/backend/gpu_native/math/gemm.cu:122-155).
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -12,6 +12,7 @@
 //   warp 0: TMA producer (128-byte-swizzled 128 x 128-byte tiles of A8 and B8, 6 stages)
 //   warp 1: MMA issuer   (4 instructions per K block, commit -> stage free + partial ready)
 //   warps 2-17: promotion + epilogue (4 warps per TMEM lane quarter, 32 columns each)
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

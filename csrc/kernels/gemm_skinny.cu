@@ -12,6 +12,7 @@
 // that arrives last at the group's counter adds them in a fixed order, so the result does not depend on arrival order
 // and nothing ever waits.  The reference runs every Linear through cublasSgemm whatever the row count
 // (src/ops/linear.cpp:176-192).
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -1,6 +1,7 @@
 // Plain bf16 GEMM entry point on the tcgen05 / TMEM / TMA pipeline of gemm_sm100.cuh.
 // Replaces the cuBLAS calls of the reference (src/backend/gpu_native/math/gemm.cu:3-189) and the
 // backward GEMM pair of src/ops/linear.cpp:30-68, with bias / GELU / residual / accumulate epilogues.
+#include "lt_cuda.h"
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 

@@ -5,6 +5,7 @@
 // the row in 16-byte steps, four loads in flight per lane, and keep one partial dot product per input row; a shuffle
 // reduction finishes the column.  x (a few KB) is read through the read-only path and stays in L1.  The reference runs
 // every Linear through cublasSgemm whatever the row count (src/ops/linear.cpp:176-192).
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -9,6 +9,7 @@
 // exposed so that tensor-parallel ranks can combine them with one tiny collective before the in-place
 // gradient pass; AdamW/Adam/SGD/RMSprop run over flat buffers or over a pointer table in ONE launch,
 // with the gradient unscale and the skip-on-overflow decision read from device memory.
+#include "lt_cuda.h"
 #include <cuda_fp8.h>
 
 #include "common/host.h"

@@ -12,6 +12,7 @@
 //   * full sum / max reductions (reference: cub::DeviceReduce in math/reduction.cu:25-58),
 //   * strided gather to a contiguous tensor (make_contiguous_kernel / cat_forward_kernel,
 //     elementwise/elementwise_ops.cu:133-179, 432-502).
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 #include <cuda_fp8.h>

@@ -14,6 +14,7 @@
 //    adds it straight into the fp32 output accumulator of the rank that owns the token (`red.add` to peer memory),
 //    so the all-to-all "combine" and the weighted sum over the k experts are the GEMM epilogue.
 // The same two kernels serve the backward pass with the roles swapped (gather dY rows for dH; scatter dX rows).
+#include "lt_cuda.h"
 #include "comm_common.cuh"
 
 namespace lt {

@@ -5,6 +5,7 @@
 // reduction), an optional residual add is fused into the forward (the sum is written out for the next
 // residual branch), and the backward produces dx in one pass while each CTA keeps partial dgamma/dbeta
 // sums for the rows it visited; a second tiny kernel folds the partials.
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -8,6 +8,7 @@
 // second kernel merges the per-split (max, sum, partial output) triples.  Decode is bandwidth bound (each
 // K/V byte is used once per query head of its group), so the kernel is plain CUDA-core code.
 // Cache layout: [num_blocks, Hkv, block_size, D] as in the reference.
+#include "lt_cuda.h"
 #include <cuda_fp8.h>
 
 #include "common/host.h"

@@ -6,6 +6,7 @@
 // (src/backend/gpu_native/elementwise/elementwise_ops.cu:3-98), cast kernels (:362-430).
 // The reference has no SiLU/SwiGLU; it is added because the Llama-style configurations need it.
 // Every kernel moves 16 bytes per thread per access and grid-strides.
+#include "lt_cuda.h"
 #include "common/host.h"
 #include "common/ptx.cuh"
 

@@ -10,6 +10,7 @@
 // When its own tiles are done, the same kernel sums the W staged partials of every local row block as soon as
 // the block's counter shows that all ranks delivered it (bounded wait) and writes the bf16 result, optionally
 // adding a bias and a residual.
+#include "lt_cuda.h"
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 

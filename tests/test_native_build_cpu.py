@@ -39,3 +39,25 @@ def test_the_public_header_declares_every_exported_function():
     lib = host_lib()
     for fn in sorted(declared):
         assert hasattr(lib, fn), fn
+
+
+def test_the_device_library_header_covers_every_bound_kernel_and_is_plain_c(tmp_path):
+    header_path = os.path.join(ROOT, "csrc", "kernels", "lt_cuda.h")
+    header = open(header_path).read()
+    declared = set(re.findall(r"\b(lt_[a-z0-9_]+)\(", header))
+    bound = set(re.findall(r'"(lt_[a-z0-9_]+)"', open(os.path.join(ROOT, "litetorch_b200", "ops", "kernels.py")).read()))
+    assert bound and bound <= declared, sorted(bound - declared)
+    for folder, inc in (("kernels", '#include "lt_cuda.h"'), ("kernels/common", '#include "lt_cuda.h"'),
+                        ("cuda_runtime", '#include "kernels/lt_cuda.h"')):
+        for name in os.listdir(os.path.join(ROOT, "csrc", folder)):
+            if name.endswith(".cu"):
+                assert inc in open(os.path.join(ROOT, "csrc", folder, name)).read(), name
+    # usable from a host compiler without the CUDA toolkit's headers, as C and as C++
+    for ext, cc in ((".c", "gcc"), (".cpp", "g++")):
+        if shutil.which(cc) is None:
+            continue
+        src = tmp_path / ("use" + ext)
+        src.write_text('#include "lt_cuda.h"\n#include "lt_host.h"\nint main(void) { return lt_pool_threads() < 0; }\n')
+        r = subprocess.run([cc, "-fsyntax-only", "-I", os.path.join(ROOT, "csrc", "kernels"), "-I",
+                            os.path.join(ROOT, "csrc", "runtime"), str(src)], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-2000:]
