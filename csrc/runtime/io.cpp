@@ -21,23 +21,41 @@
 
 namespace {
 
-uint32_t g_table[256];
-bool g_table_ready = false;
-
-void init_table() {
-  if (g_table_ready) return;
-  for (uint32_t i = 0; i < 256; ++i) {
-    uint32_t c = i;
-    for (int k = 0; k < 8; ++k) c = (c & 1) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
-    g_table[i] = c;
+// Slicing-by-8 CRC-32: eight 256-entry tables, eight input bytes per step (about 2 GB/s per core against 0.4 GB/s for the
+// byte-wise loop; a rank's checkpoint shard of an 8B-parameter job is several GB).
+struct CrcTable {
+  uint32_t v[8][256];
+  CrcTable() {
+    for (uint32_t i = 0; i < 256; ++i) {
+      uint32_t c = i;
+      for (int k = 0; k < 8; ++k) c = (c & 1) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
+      v[0][i] = c;
+    }
+    for (uint32_t i = 0; i < 256; ++i)
+      for (int t = 1; t < 8; ++t) v[t][i] = (v[t - 1][i] >> 8) ^ v[0][v[t - 1][i] & 0xFF];
   }
-  g_table_ready = true;
+};
+
+// built once, by whichever thread gets there first (initialisation of a function-local static is thread-safe)
+const CrcTable& crc_table() {
+  static const CrcTable table;
+  return table;
 }
 
 uint32_t crc_update(uint32_t crc, const void* data, size_t n) {
-  init_table();
+  const CrcTable& t = crc_table();
   const uint8_t* p = static_cast<const uint8_t*>(data);
-  for (size_t i = 0; i < n; ++i) crc = g_table[(crc ^ p[i]) & 0xFF] ^ (crc >> 8);
+  while (n >= 8) {
+    uint32_t lo, hi;
+    memcpy(&lo, p, 4);
+    memcpy(&hi, p + 4, 4);
+    lo ^= crc;                                   // little-endian hosts only (x86-64, aarch64)
+    crc = t.v[7][lo & 0xFF] ^ t.v[6][(lo >> 8) & 0xFF] ^ t.v[5][(lo >> 16) & 0xFF] ^ t.v[4][lo >> 24] ^
+          t.v[3][hi & 0xFF] ^ t.v[2][(hi >> 8) & 0xFF] ^ t.v[1][(hi >> 16) & 0xFF] ^ t.v[0][hi >> 24];
+    p += 8;
+    n -= 8;
+  }
+  for (size_t i = 0; i < n; ++i) crc = t.v[0][(crc ^ p[i]) & 0xFF] ^ (crc >> 8);
   return crc;
 }
 

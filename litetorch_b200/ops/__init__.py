@@ -170,7 +170,7 @@ class Ops:
     @staticmethod
     def batch_norm2d(input, running_mean, running_var, weight, bias, training: bool, momentum: float = 0.1, eps: float = 1e-5):
         t = _unwrap(input)
-        if training and t.numel() == t.shape[1]:
+        if training and t.dim() >= 2 and t.numel() == t.shape[1]:
             # one value per channel: the batch variance is 0 and its unbiased factor M / (M - 1) is taken as 1
             # (reference: src/ops/normalization.cpp:650), where torch refuses the call
             rm, rv = _unwrap(running_mean), _unwrap(running_var)

@@ -29,6 +29,19 @@ def test_ltw1_layout_crc_and_roundtrip(tmp_path):
         assert torch.equal(_unwrap(a), _unwrap(b))
 
 
+def test_crc32_equals_zlib_at_every_alignment_and_tail_length():
+    import ctypes
+    from litetorch_b200._native import host_lib
+    lib = host_lib()
+    lib.lt_crc32.restype = ctypes.c_uint32
+    lib.lt_crc32.argtypes = [ctypes.c_char_p, ctypes.c_uint64]
+    blob = bytes((i * 131 + 7) % 256 for i in range(4099))
+    for n in list(range(0, 40)) + [255, 256, 257, 4096, 4099]:
+        for off in (0, 1, 3):
+            piece = blob[off:off + n]
+            assert lib.lt_crc32(piece, len(piece)) == zlib.crc32(piece), (n, off)
+
+
 def test_corrupt_or_mismatched_checkpoint_leaves_model_untouched(tmp_path):
     net = lt.nn.Linear(4, 4)
     path = str(tmp_path / "m.ltw1")
