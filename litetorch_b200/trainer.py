@@ -135,7 +135,7 @@ class Trainer:
         return {"weights": type(self.engine.w).__name__, "world_size": self.world_size if self.engine.w.__class__.__name__ != "LocalWeights" else 1,
                 "tp": self.tp, "model": asdict(self.cfg)}
 
-    def save(self, directory: str, keep: int = 2, loader=None) -> None:
+    def save(self, directory: str, keep: int = 2, loader=None, background: bool = False) -> None:
         """Write everything a restart needs: per rank, its fp32 master weights and AdamW moments (the shard it owns
         under ZeRO-3 / tensor parallelism, the replicated norm gains included) as one LTW1 file, and by rank 0 a
         manifest with the model, the layout and the optimizer's step count (bias correction depends on it).
@@ -144,9 +144,14 @@ class Trainer:
         rank 0 renames it and points the file `LATEST` at it (both atomic), then drops all but the newest `keep`
         checkpoints.  A job that dies in the middle of a save therefore leaves the previous checkpoint intact and
         `load` never sees a mix of two steps.  `loader`: an `lt.data.DataLoader` whose position (epoch, permutation, next
-        index: the LTDL record) is stored per rank next to the tensors and restored by `load(..., loader=...)`."""
+        index: the LTDL record) is stored per rank next to the tensors and restored by `load(..., loader=...)`.
+
+        `background=True`: the state is copied to host memory now (the checkpoint is of THIS step), the file is written by
+        a thread while training goes on, and the checkpoint is published (barrier of the ranks, renames) by
+        `finish_save()` - called explicitly, or by the next `save` / `load`.  Until then `LATEST` names the previous one."""
         import shutil
         from .serialization import save_sharded
+        self.finish_save()
         w = self.engine.w
         state = w.state_tensors()
         lay = self._layout()
@@ -156,29 +161,65 @@ class Trainer:
         name = "step-%08d" % self.engine.step_count
         tmp, final = os.path.join(directory, "." + name + ".tmp"), os.path.join(directory, name)
         meta = dict(lay, names=list(state), step_count=self.engine.step_count)
-        save_sharded(tmp, [t.detach().float().cpu() for t in state.values()], self.rank if sharded else 0,
-                     lay["world_size"], tag="trainer", meta=meta)
+        rank = self.rank if sharded else 0
+        # private host copies: a CPU fp32 tensor would otherwise be written while later steps change it
+        snapshot = [t.detach().to("cpu", torch.float32, copy=True) for t in state.values()]
+        os.makedirs(tmp, exist_ok=True)
         if loader is not None:
-            loader.save_state(os.path.join(tmp, "loader.rank%05d.ltdl" % (self.rank if sharded else 0)))
-        if sharded:
-            import torch.distributed as dist
-            dist.barrier()                                   # every rank's file is in the temporary directory
-        if not sharded or self.rank == 0:
-            if os.path.isdir(final):
-                shutil.rmtree(final)                         # the same step saved twice
-            os.replace(tmp, final)
-            with open(os.path.join(directory, "LATEST.tmp"), "w") as f:
-                f.write(name)
-            os.replace(os.path.join(directory, "LATEST.tmp"), os.path.join(directory, "LATEST"))
-            done = sorted(d for d in os.listdir(directory) if d.startswith("step-") and os.path.isdir(os.path.join(directory, d)))
-            for d in done[:-keep] if keep > 0 else []:
-                if d != name:
-                    shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
-            for d in os.listdir(directory):                  # leftovers of saves that never finished
-                if d.startswith(".step-") and d.endswith(".tmp") and d != "." + name + ".tmp":
-                    shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
-        if sharded:
-            dist.barrier()
+            loader.save_state(os.path.join(tmp, "loader.rank%05d.ltdl" % rank))
+
+        def write():
+            save_sharded(tmp, snapshot, rank, lay["world_size"], tag="trainer", meta=meta)
+
+        def publish():
+            if sharded:
+                import torch.distributed as dist
+                dist.barrier()                                   # every rank's file is in the temporary directory
+            if not sharded or self.rank == 0:
+                if os.path.isdir(final):
+                    shutil.rmtree(final)                         # the same step saved twice
+                os.replace(tmp, final)
+                with open(os.path.join(directory, "LATEST.tmp"), "w") as f:
+                    f.write(name)
+                os.replace(os.path.join(directory, "LATEST.tmp"), os.path.join(directory, "LATEST"))
+                done = sorted(d for d in os.listdir(directory) if d.startswith("step-") and os.path.isdir(os.path.join(directory, d)))
+                for d in done[:-keep] if keep > 0 else []:
+                    if d != name:
+                        shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
+                for d in os.listdir(directory):                  # leftovers of saves that never finished
+                    if d.startswith(".step-") and d.endswith(".tmp") and d != "." + name + ".tmp":
+                        shutil.rmtree(os.path.join(directory, d), ignore_errors=True)
+            if sharded:
+                import torch.distributed as dist
+                dist.barrier()
+
+        if not background:
+            write()
+            publish()
+            return
+        import threading
+        box = {}
+
+        def run():
+            try:
+                write()
+            except BaseException as e:                           # re-raised on the training thread by finish_save
+                box["error"] = e
+        th = threading.Thread(target=run, name="lt-checkpoint-writer", daemon=False)
+        th.start()
+        self._pending_save = (th, box, publish)
+
+    def finish_save(self) -> None:
+        """Wait for a `save(..., background=True)` that is still writing and publish its checkpoint (all ranks call this at
+        the same step: it contains the barrier).  Raises what the writer thread raised.  A no-op otherwise."""
+        pending, self._pending_save = getattr(self, "_pending_save", None), None
+        if pending is None:
+            return
+        th, box, publish = pending
+        th.join()
+        if "error" in box:
+            raise box["error"]
+        publish()
 
     @staticmethod
     def latest_checkpoint(directory: str):
@@ -194,6 +235,7 @@ class Trainer:
         """Resume from `save`: the checkpoint must come from the same model on the same layout (world size, tp)."""
         import json
         from .serialization import CheckpointError, load_sharded
+        self.finish_save()
         w = self.engine.w
         state = w.state_tensors()
         lay = self._layout()

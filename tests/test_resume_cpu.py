@@ -310,6 +310,52 @@ def test_trainer_checkpoints_are_complete_or_absent(tmp_path):
     assert sorted(d for d in os.listdir(ck)) == ["LATEST", "step-00000005", "step-00000006"]
 
 
+def test_background_save_holds_the_step_it_was_taken_at_and_is_published_later(tmp_path):
+    """`save(..., background=True)` copies the state at once and writes it from a thread: steps taken meanwhile are not in
+    the file, `LATEST` moves only when `finish_save` (or the next save / load) publishes it, and an error of the writer
+    thread surfaces there."""
+    import torch
+    from litetorch_b200.models.llama import LlamaConfig
+    from litetorch_b200.trainer import Trainer
+    ck = str(tmp_path / "ck")
+    cfg = LlamaConfig.tiny()
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(2))
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    tr = Trainer(cfg, seed=3, device="cpu", param_dtype=torch.float32, parallel="none")
+    tr.step(x, y)
+    tr.save(ck)                                             # step 1, published
+    tr.step(x, y)
+    tr.save(ck, background=True)                            # step 2, being written
+    assert open(os.path.join(ck, "LATEST")).read() == "step-00000001"
+    third = tr.step(x, y)                                   # training goes on; the file must not see this step
+    tr.step(x, y)
+    tr.finish_save()
+    tr.finish_save()                                        # a no-op the second time
+    assert open(os.path.join(ck, "LATEST")).read() == "step-00000002"
+    other = Trainer(cfg, seed=9, device="cpu", param_dtype=torch.float32, parallel="none")
+    other.load(ck)
+    assert other.engine.step_count == 2 and abs(other.step(x, y) - third) < 1e-6
+    # the next save publishes a pending one first; so does load
+    tr.save(ck, background=True)                            # step 4
+    tr.step(x, y)
+    tr.save(ck, background=True)                            # step 5: step 4 is published before this one starts
+    assert open(os.path.join(ck, "LATEST")).read() == "step-00000004"
+    tr.load(ck)                                             # publishes step 5 and loads it
+    assert tr.engine.step_count == 5
+    # a writer that fails: the error is raised by finish_save and LATEST stays where it was
+    import litetorch_b200.serialization as S
+    real = S.save_sharded
+    S.save_sharded = lambda *a, **k: (_ for _ in ()).throw(OSError("disk full"))
+    try:
+        tr.step(x, y)
+        tr.save(ck, background=True)
+        with pytest.raises(OSError, match="disk full"):
+            tr.finish_save()
+    finally:
+        S.save_sharded = real
+    assert open(os.path.join(ck, "LATEST")).read() == "step-00000005"
+
+
 def test_trainer_checkpoint_carries_the_data_loader_position(tmp_path):
     """`Trainer.save(dir, loader=dl)` stores the loader's LTDL record (epoch, permutation, next index) with the tensors: a fresh
     trainer and a fresh loader built with the job's seed continue with the batches and the losses of the uninterrupted run, across
