@@ -401,6 +401,21 @@ class ShardedWeights(SingleTPMixin):
     def parameters(self) -> List[torch.Tensor]:
         return [self.gather_full_master(s.name) for s in self.specs]
 
+    def load_parameters(self, tensors: List[torch.Tensor]) -> None:
+        """Take whole parameters (in `specs` order, the same on every rank): each rank keeps its block of rows, as the
+        initialisation does; then the bf16 shards are rebuilt (`after_load`)."""
+        for s, t in zip(self.specs, tensors):
+            n = math.prod(s.shape)
+            if s.kind == "matrix":
+                rows, cols = s.shape
+                rpr = rows // self.world
+                mine = t.view(rows, cols)[self.rank * rpr:(self.rank + 1) * rpr].to(self.device, torch.float32).reshape(-1)
+                so = self.shard_off[s.name]
+                self.master[so:so + mine.numel()].copy_(mine)
+            else:
+                self.vec_master[s.offset:s.offset + n].copy_(t.to(self.device, torch.float32).view(-1))
+        self.after_load()
+
     def state_tensors(self) -> Dict[str, torch.Tensor]:
         """This rank's shard of the fp32 masters and AdamW moments plus the replicated vectors."""
         return {"master": self.master, "m": self.m, "v": self.v, "vec_master": self.vec_master, "vec_m": self.vec_m,
