@@ -29,6 +29,7 @@ class LlamaKVModel:
         self.num_splits = num_splits
         self.graphs = graphs                 # record the decode step per (batch size, table width) and replay it
         self._graphs = {}
+        self.sampler = None                  # None: greedy on the device; else a callable logits [rows, vocab] -> tokens
         self.cache = PagedKVCache(cfg.n_layers, num_blocks, block_size, cfg.n_kv_heads, cfg.head_dim, device=engine.device,
                                   dtype=kv_dtype)
         self.kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * self.cache.k[0].element_size()
@@ -59,6 +60,8 @@ class LlamaKVModel:
         hf, _, _, _ = K.norm_fwd(x_rows, e.w.p("final_norm"), eps=e.cfg.rms_eps)
         logits = K.gemm(hf, e.w.p("lm_head"))
         self.last_logits = logits            # [rows, vocab] of the newest step (kept for inspection and tests)
+        if self.sampler is not None:
+            return self.sampler(logits.float())
         return logits.float().argmax(-1)
 
     def _slots(self, block_ids: Sequence[int], start: int, n: int) -> torch.Tensor:
@@ -174,3 +177,60 @@ class LlamaKVModel:
         """Splits of the key range per (sequence, KV head): about four CTAs per SM, at least 256 keys per split."""
         ctas = S * self.e.cfg.n_kv_heads
         return max(1, min(32, max_ctx // 256, (148 * 4 + ctas - 1) // ctas))
+
+
+class Sampler:
+    """Temperature / top-k / nucleus sampling of next tokens from logits [rows, vocab] with its own random generator, so
+    that a run is reproducible from its seed.  `temperature == 0` (or `top_k == 1`) is greedy."""
+
+    def __init__(self, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0, device="cpu"):
+        self.temperature, self.top_k, self.top_p = float(temperature), int(top_k), float(top_p)
+        self.gen = torch.Generator(device=device).manual_seed(int(seed))
+
+    def __call__(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.temperature <= 0.0 or self.top_k == 1:
+            return logits.argmax(-1)
+        z = logits / self.temperature
+        if self.top_k > 0 and self.top_k < z.shape[-1]:
+            kth = z.topk(self.top_k, -1).values[..., -1:]
+            z = z.masked_fill(z < kth, float("-inf"))
+        if self.top_p < 1.0:
+            order = z.sort(-1, descending=True)
+            p = torch.softmax(order.values, -1)
+            before = p.cumsum(-1) - p                     # probability mass ahead of each token, in sorted order
+            drop = before >= self.top_p                   # the first token always stays
+            z = z.masked_fill(torch.zeros_like(drop).scatter(-1, order.indices, drop), float("-inf"))
+        return torch.multinomial(torch.softmax(z, -1), 1, generator=self.gen).squeeze(-1)
+
+
+@torch.no_grad()
+def generate(engine: LlamaEngine, prompts: Sequence[Sequence[int]], max_new_tokens: int, *, temperature: float = 0.0,
+             top_k: int = 0, top_p: float = 1.0, seed: int = 0, eos_id: int = -1, block_size: int = 16,
+             max_num_seqs: int = 64, max_num_batched_tokens: int = 4096, kv_dtype=None) -> List[List[int]]:
+    """Continue every prompt by up to `max_new_tokens` tokens (stopping at `eos_id`) with continuous batching on a paged KV
+    cache sized for the request, and return the new tokens per prompt.  Greedy by default (the decode step is replayed
+    from CUDA graphs on a GPU); with `temperature > 0` the next tokens are drawn by `Sampler` (eager decode steps)."""
+    from ..serving import Request, ServingScheduler
+    cfg = engine.cfg
+    need = sum((len(p) + max_new_tokens + block_size - 1) // block_size for p in prompts)
+    greedy = temperature <= 0.0 or top_k == 1
+    if kv_dtype is None:
+        kv_dtype = torch.bfloat16 if engine.device.type == "cuda" else torch.float32
+    model = LlamaKVModel(engine, num_blocks=need + 1, block_size=block_size, kv_dtype=kv_dtype, graphs=greedy)
+    if not greedy:
+        model.sampler = Sampler(temperature, top_k, top_p, seed, device=engine.device)
+    sched = ServingScheduler(num_blocks=need + 1, block_size=block_size, max_num_seqs=max_num_seqs,
+                             max_num_batched_tokens=max_num_batched_tokens, eos_id=eos_id)
+    reqs = [Request(i, list(p), max_new_tokens=max_new_tokens) for i, p in enumerate(prompts)]
+    for r in reqs:
+        if len(r.prompt_tokens) + max_new_tokens > cfg.max_seq:
+            raise ValueError("prompt %d: %d tokens + %d new exceed the model's %d positions" %
+                             (r.id, len(r.prompt_tokens), max_new_tokens, cfg.max_seq))
+        sched.add_request(r)
+    finished, guard = 0, 0
+    while finished < len(reqs):
+        finished += len(sched.step(model))
+        guard += 1
+        if guard > 4 * (max_new_tokens + len(reqs)) + 64 + sum(len(p) for p in prompts):
+            raise RuntimeError("the schedule did not finish")
+    return [list(r.generated_tokens) for r in reqs]

@@ -85,3 +85,35 @@ def test_save_pretrained_is_read_by_transformers_and_by_load_pretrained(tmp_path
     assert float((engine.forward_logits(tok[:, :-1]) - ref).abs().max()) < 2e-4
     again = llama_io.load_pretrained(out, device="cpu", weights=LocalWeights(cfg, "cpu", seed=9, param_dtype=torch.float32))
     assert again.cfg.ffn == 128 and float((again.forward_logits(tok[:, :-1]) - ref).abs().max()) < 2e-4
+
+
+def test_generate_equals_transformers_greedy_decoding_and_sampling_is_seeded():
+    from litetorch_b200.models import llama_io
+    from litetorch_b200.models.llama import LlamaEngine, LocalWeights
+    from litetorch_b200.models.llama_serving import Sampler, generate
+    hc, model = _hf_model(seed=2)
+    cfg = llama_io.config_from_hf(hc)
+    engine = LlamaEngine(cfg, "cpu", weights=LocalWeights(cfg, "cpu", seed=1, param_dtype=torch.float32))
+    llama_io.load_into(engine, model.state_dict())
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 19, 11)]
+    ours = generate(engine, prompts, 8, block_size=4, max_num_batched_tokens=16)
+    for p, o in zip(prompts, ours):
+        with torch.no_grad():
+            ref = model.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False, pad_token_id=0, eos_token_id=None)
+        assert ref[0, len(p):].tolist() == o
+    # sampling: top_k = 1 is greedy, a seed reproduces a run, another seed changes it, tokens stay inside the top-k set
+    assert generate(engine, prompts, 8, temperature=0.8, top_k=1) == ours
+    a = generate(engine, prompts, 8, temperature=1.5, top_k=20, top_p=0.9, seed=5)
+    assert a == generate(engine, prompts, 8, temperature=1.5, top_k=20, top_p=0.9, seed=5)
+    assert a != generate(engine, prompts, 8, temperature=1.5, top_k=20, top_p=0.9, seed=6)
+    logits = torch.randn(4, 50, generator=g)
+    s = Sampler(temperature=1.0, top_k=3, top_p=1.0, seed=1)
+    top3 = logits.topk(3, -1).indices
+    for _ in range(20):
+        t = s(logits)
+        assert all(int(t[i]) in top3[i].tolist() for i in range(4))
+    nucleus = Sampler(temperature=1.0, top_p=1e-6, seed=1)          # a vanishing nucleus keeps only the best token
+    assert torch.equal(nucleus(logits), logits.argmax(-1))
+    with pytest.raises(ValueError):
+        generate(engine, [[1] * 125], 8)
