@@ -463,6 +463,19 @@ class LlamaEngine:
         hf, _, _, _ = K.norm_fwd(x, w.p("final_norm"), eps=cfg.rms_eps)
         return w.col_linear(hf, "lm_head")[0].view(B, T, cfg.vocab_size // w.tp)
 
+    def eval_loss(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Mean token loss of a batch (device scalar) from a forward pass only: gradients, moments and the step count are
+        left alone (validation between training steps).  Under tensor parallelism the loss is reduced over the group's
+        vocabulary slices; under data parallelism it is the loss of this rank's batch."""
+        w, K = self.w, self.K
+        B, T = tokens.shape
+        logits = self.forward_logits(tokens).view(B * T, -1)
+        tgt = targets.reshape(-1)
+        stats = w.reduce_ce_stats(K.ce_stats(logits, tgt, w.vocab_start))
+        rows = K.ce_finish(logits, tgt, stats, vocab_start=w.vocab_start, write_grad=False)
+        self.kernel_launches += 2
+        return rows.sum() / (B * T)
+
     def optimizer_step(self, dyn=None):
         self.step_count += 1
         self.w.optimizer_step(lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,

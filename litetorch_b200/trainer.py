@@ -129,6 +129,12 @@ class Trainer:
             self._metrics.write(**rec)
         return float(out)
 
+    def evaluate(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor) -> float:
+        """Loss of a host batch without an update (`LlamaEngine.eval_loss`); this rank's batch under data parallelism."""
+        dev = self.device
+        out = self.engine.eval_loss(tokens_cpu.to(dev, non_blocking=True), targets_cpu.to(dev, non_blocking=True))
+        return float(out)
+
     # ---- checkpoint / resume of the whole training state
     def _layout(self) -> dict:
         from dataclasses import asdict

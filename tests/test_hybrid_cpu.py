@@ -52,6 +52,9 @@ for it in range(3):
     losses.append(float(lt2) / world)
     losses_ref.append(float(ref.train_step(tok_all[:, :-1], tok_all[:, 1:])))
 perr = max(float((a - b).abs().max()) for a, b in zip(w.parameters(), wr.parameters()))
+ev = torch.tensor([float(eng.eval_loss(tok, tgt))]); dist.all_reduce(ev)
+ev_ref = float(ref.eval_loss(tok_all[:, :-1], tok_all[:, 1:]))
+assert abs(float(ev) / world - ev_ref) < 2e-4, (float(ev) / world, ev_ref)
 if rank == 0:
     print("RESULT " + json.dumps(dict(p0=p0, loss=float(lt) / world, loss_ref=loss_ref, gerr=gerr, losses=losses,
                                       losses_ref=losses_ref, perr=perr, trace=w._trace_done)))
@@ -284,3 +287,19 @@ def test_gradient_clipping_scales_the_update_and_skips_non_finite_gradients():
     t = Trainer(cfg, device="cpu", param_dtype=torch.float32, parallel="none", grad_clip=bound, seed=3)
     t.step(x, y)
     assert abs(float(t.engine.last_grad_norm) - norm) < 1e-4 * norm
+
+
+def test_eval_loss_is_the_training_loss_without_side_effects():
+    import torch
+    from litetorch_b200.models.llama import LlamaConfig
+    from litetorch_b200.trainer import Trainer
+    cfg = LlamaConfig.tiny()
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(0))
+    x, y = tok[:, :-1], tok[:, 1:]
+    t = Trainer(cfg, device="cpu", param_dtype=torch.float32, parallel="none", seed=1)
+    t.step(x, y)
+    grads, moments, count = t.engine.w.flat_g.clone(), t.engine.w.m.clone(), t.engine.step_count
+    before = t.evaluate(x, y)
+    assert torch.equal(grads, t.engine.w.flat_g) and torch.equal(moments, t.engine.w.m) and t.engine.step_count == count
+    assert abs(before - t.step(x, y)) < 1e-5          # the step reports the loss before its update
+    assert t.evaluate(x, y) < before
