@@ -133,6 +133,22 @@ int64_t lt_filestore_get(const char* dir, const char* key, void* buf, uint64_t c
 int lt_pool_threads(void);
 void lt_parallel_for(void* fn_ptr, void* ctx, uint64_t n, uint64_t min_parallel);
 
+// ---- tokenstream.cpp
+// Token-stream loader for language-model training over a memory-mapped file of uint16 / uint32 token ids: windows of
+// seq_len + 1 tokens, permuted per epoch from (seed, epoch), dealt to the ranks round-robin, widened to int64 by a
+// prefetch thread.  lt_ts_next returns 1 with a batch ([batch, seq_len] inputs and targets) or 0 at the end of the epoch;
+// the position is (epoch, batch index): lt_ts_seek resumes exactly.
+void* lt_ts_open(const char* path, int token_bytes, uint64_t seq_len, uint64_t batch, int shuffle, uint64_t seed, int rank, int world, int prefetch);
+void lt_ts_close(void* h);
+uint64_t lt_ts_num_tokens(void* h);
+uint64_t lt_ts_num_windows(void* h);
+uint64_t lt_ts_batches_per_epoch(void* h);
+uint64_t lt_ts_epoch(void* h);
+uint64_t lt_ts_position(void* h);
+int lt_ts_next(void* h, int64_t* tokens_out, int64_t* targets_out);
+void lt_ts_next_epoch(void* h);
+void lt_ts_seek(void* h, uint64_t epoch, uint64_t position);
+
 #ifdef __cplusplus
 }  // extern "C"
 #endif

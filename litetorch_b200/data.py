@@ -133,3 +133,108 @@ class DataLoader:
         if rc != 0:
             raise RuntimeError({-1: "cannot open %s", -2: "%s is malformed", -3: "CRC mismatch in %s",
                                 -4: "%s was saved for a dataset of a different size"}.get(rc, "bad state file %s") % filepath)
+
+
+class TokenStream:
+    """Batches of `[batch_size, seq_len]` inputs and next-token targets from a flat binary file of token ids (uint16 or
+    uint32), for language-model training.  The file is memory-mapped by the native runtime (csrc/runtime/tokenstream.cpp):
+    windows of `seq_len + 1` tokens are permuted per epoch from `(seed, epoch)`, dealt to the ranks round-robin (disjoint
+    windows, the same number of batches on every rank) and widened to int64 by a prefetch thread into pinned buffers.
+
+    `next()` returns `(tokens, targets)` as CPU tensors in pinned memory - what `Trainer.step` takes - or None at the end of
+    an epoch (`next_epoch()` goes on; iterating the object does so by itself).  The buffers rotate over `prefetch_limit + 1`
+    slots: a batch stays valid until that many further batches have been taken.  The position is `(epoch, position)` and
+    nothing else: `save_state / load_state` (or `state_dict / load_state_dict`) resume with exactly the batches the
+    interrupted job would have seen, so a `TokenStream` can be the `loader=` of `Trainer.save / load`."""
+
+    def __init__(self, path: str, seq_len: int, batch_size: int, dtype: str = "uint16", shuffle: bool = True, seed: int = 0,
+                 rank: Optional[int] = None, world: Optional[int] = None, prefetch_limit: int = 2):
+        import os
+        self._lib = _ts_lib()
+        self.path, self.seq_len, self.batch_size = path, int(seq_len), int(batch_size)
+        self.rank = int(os.environ.get("RANK", "0")) if rank is None else int(rank)
+        self.world = int(os.environ.get("WORLD_SIZE", "1")) if world is None else int(world)
+        nbytes = {"uint16": 2, "uint32": 4}[dtype]
+        self._h = self._lib.lt_ts_open(path.encode(), nbytes, self.seq_len, self.batch_size, 1 if shuffle else 0, int(seed),
+                                       self.rank, self.world, int(prefetch_limit))
+        if not self._h:
+            raise RuntimeError("cannot open %s as a token stream of %s (a batch needs %d windows of %d + 1 tokens)"
+                               % (path, dtype, self.batch_size * self.world, self.seq_len))
+        pin = torch.cuda.is_available()
+        self._slots = [(torch.empty(batch_size, seq_len, dtype=torch.int64, pin_memory=pin),
+                        torch.empty(batch_size, seq_len, dtype=torch.int64, pin_memory=pin)) for _ in range(prefetch_limit + 1)]
+        self._turn = 0
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                self._lib.lt_ts_close(h)
+            except Exception:
+                pass
+
+    num_tokens = property(lambda self: int(self._lib.lt_ts_num_tokens(self._h)))
+    num_windows = property(lambda self: int(self._lib.lt_ts_num_windows(self._h)))
+    batches_per_epoch = property(lambda self: int(self._lib.lt_ts_batches_per_epoch(self._h)))
+    epoch = property(lambda self: int(self._lib.lt_ts_epoch(self._h)))
+    position = property(lambda self: int(self._lib.lt_ts_position(self._h)))
+
+    def next(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        tok, tgt = self._slots[self._turn]
+        if not self._lib.lt_ts_next(self._h, tok.data_ptr(), tgt.data_ptr()):
+            return None
+        self._turn = (self._turn + 1) % len(self._slots)
+        return tok, tgt
+
+    def next_epoch(self) -> None:
+        self._lib.lt_ts_next_epoch(self._h)
+
+    reset = next_epoch          # the DataLoader's name for "start the next epoch"
+
+    def __iter__(self):
+        """Endless: batches of this epoch, then of the next ones."""
+        while True:
+            b = self.next()
+            if b is None:
+                self.next_epoch()
+                continue
+            yield b
+
+    def state_dict(self) -> dict:
+        return {"epoch": self.epoch, "position": self.position, "seq_len": self.seq_len, "batch_size": self.batch_size,
+                "world": self.world, "num_tokens": self.num_tokens}
+
+    def load_state_dict(self, state: dict) -> None:
+        for k in ("seq_len", "batch_size", "world", "num_tokens"):
+            if int(state[k]) != getattr(self, k):
+                raise RuntimeError("token stream state was saved with %s = %s, this stream has %s" % (k, state[k], getattr(self, k)))
+        self._lib.lt_ts_seek(self._h, int(state["epoch"]), int(state["position"]))
+
+    def save_state(self, filepath: str) -> None:
+        import json
+        import os
+        with open(filepath + ".tmp", "w") as f:
+            json.dump(self.state_dict(), f)
+        os.replace(filepath + ".tmp", filepath)
+
+    def load_state(self, filepath: str) -> None:
+        import json
+        with open(filepath) as f:
+            self.load_state_dict(json.load(f))
+
+
+def _ts_lib():
+    lib = host_lib()
+    if not getattr(lib, "_lt_ts_bound", False):
+        from ctypes import c_int64
+        lib.lt_ts_open.restype = c_void_p
+        lib.lt_ts_open.argtypes = [c_char_p, c_int, c_uint64, c_uint64, c_int, c_uint64, c_int, c_int, c_int]
+        lib.lt_ts_close.argtypes = [c_void_p]
+        for fn in ("lt_ts_num_tokens", "lt_ts_num_windows", "lt_ts_batches_per_epoch", "lt_ts_epoch", "lt_ts_position"):
+            getattr(lib, fn).restype = c_uint64
+            getattr(lib, fn).argtypes = [c_void_p]
+        lib.lt_ts_next.argtypes = [c_void_p, c_void_p, c_void_p]
+        lib.lt_ts_next_epoch.argtypes = [c_void_p]
+        lib.lt_ts_seek.argtypes = [c_void_p, c_uint64, c_uint64]
+        lib._lt_ts_bound = True
+    return lib

@@ -1,4 +1,4 @@
-// Serving scheduler, prefix cache, data loader, checkpoint reader / writer and the JIT expression tree of the host
+// Serving scheduler, prefix cache, data loader, token stream, checkpoint reader / writer and the JIT expression tree of the host
 // runtime under sanitizers (built by tests/test_sanitizers_cpu.py with the runtime's sources).  The scheduler and the
 // prefix cache are driven from several threads, as a serving front end with one engine thread would; the data loader
 // has its own prefetch thread; checkpoints are written, read back, corrupted and truncated.
@@ -45,6 +45,15 @@ int lt_ckpt_read_u32(void* h, uint32_t* v);
 int lt_ckpt_read_tensor_header(void* h, int* ndims, int64_t* dims, uint64_t* numel);
 int lt_ckpt_read_tensor_data(void* h, float* out, uint64_t numel);
 void lt_ckpt_reader_close(void* h);
+void* lt_ts_open(const char* path, int token_bytes, uint64_t seq_len, uint64_t batch, int shuffle, uint64_t seed, int rank,
+                 int world, int prefetch);
+void lt_ts_close(void* h);
+uint64_t lt_ts_batches_per_epoch(void* h);
+uint64_t lt_ts_epoch(void* h);
+uint64_t lt_ts_position(void* h);
+int lt_ts_next(void* h, int64_t* tokens_out, int64_t* targets_out);
+void lt_ts_next_epoch(void* h);
+void lt_ts_seek(void* h, uint64_t epoch, uint64_t position);
 int lt_jit_input(const char* name);
 int lt_jit_const(float v);
 int lt_jit_binary(int op, int a, int b);
@@ -181,6 +190,53 @@ int main(int argc, char** argv) {
     consume(8);
     other.join();
     CHECK(bad.load() == 0);
+  }
+  // ---- token stream: two ranks read an epoch concurrently, seeks and epoch changes race with the prefetch thread
+  {
+    const std::string path = dir + "/tokens.bin";
+    const uint32_t n = 6000;
+    {
+      std::vector<uint32_t> toks(n);
+      for (uint32_t i = 0; i < n; ++i) toks[i] = i;
+      FILE* f = fopen(path.c_str(), "wb");
+      CHECK(f != nullptr);
+      CHECK(fwrite(toks.data(), 4, n, f) == n);
+      fclose(f);
+    }
+    const uint64_t T = 16, B = 4;
+    std::atomic<uint64_t> windows{0};
+    auto reader = [&](int rank) {
+      void* ts = lt_ts_open(path.c_str(), 4, T, B, 1, 9, rank, 2, 3);
+      CHECK(ts != nullptr);
+      std::vector<int64_t> tok(B * T), tgt(B * T);
+      for (int epoch = 0; epoch < 3; ++epoch) {
+        uint64_t got = 0;
+        while (lt_ts_next(ts, tok.data(), tgt.data()) == 1) {
+          for (uint64_t i = 0; i < B * T; ++i) CHECK(tgt[i] == tok[i] + 1);
+          ++got;
+        }
+        CHECK(got == lt_ts_batches_per_epoch(ts));
+        windows += got * B;
+        lt_ts_next_epoch(ts);
+      }
+      // seeks while the worker is filling its queue: the batch after a seek is the one at that position
+      std::vector<int64_t> ref(B * T);
+      lt_ts_seek(ts, 1, 5);
+      CHECK(lt_ts_next(ts, ref.data(), tgt.data()) == 1);
+      for (int i = 0; i < 20; ++i) {
+        lt_ts_seek(ts, uint64_t(i % 3), uint64_t(i));
+        lt_ts_seek(ts, 1, 5);
+        CHECK(lt_ts_next(ts, tok.data(), tgt.data()) == 1);
+        CHECK(tok == ref && lt_ts_epoch(ts) == 1 && lt_ts_position(ts) == 6);
+      }
+      lt_ts_close(ts);
+    };
+    std::thread a(reader, 0), b(reader, 1);
+    a.join();
+    b.join();
+    CHECK(windows.load() == 2 * 3 * (((n - 1) / T / 2) / B) * B);
+    CHECK(lt_ts_open((dir + "/missing.bin").c_str(), 4, T, B, 1, 0, 0, 1, 2) == nullptr);
+    CHECK(lt_ts_open(path.c_str(), 4, T, B, 1, 0, 2, 2, 2) == nullptr);     // rank outside the world
   }
   // ---- checkpoint: round trip, one flipped byte, truncation
   {

@@ -1,0 +1,59 @@
+"""examples/train_llama.py end to end on the CPU: a toy model learns a periodic token file, an interrupted run that is
+started again with the same checkpoint directory ends on the curve of the uninterrupted one, and the same script runs
+as two data-parallel gloo ranks."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPT = os.path.join(ROOT, "examples", "train_llama.py")
+
+
+def _tokens(path, n=40000, period=37, vocab=512):
+    rng = np.random.default_rng(0)
+    base = rng.integers(3, vocab, size=period)
+    np.tile(base, n // period + 1)[:n].astype(np.uint16).tofile(path)
+
+
+def _run(args, nproc=1, port=29931, timeout=900):
+    cmd = [sys.executable, SCRIPT] if nproc == 1 else [
+        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr", "127.0.0.1",
+        "--master-port", str(port), SCRIPT]
+    r = subprocess.run(cmd + args, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+
+
+def test_example_trains_evaluates_and_resumes_on_the_same_curve(tmp_path):
+    data = str(tmp_path / "tokens.bin")
+    _tokens(data)
+    common = ["--data", data, "--tiny", "--device", "cpu", "--config", "llama-1.1b-fsdp", "--seq-len", "32", "--batch", "4",
+              "--lr", "3e-3", "--warmup", "4", "--eval-every", "10", "--grad-clip", "1.0"]
+    whole = _run(common + ["--steps", "30", "--ckpt", str(tmp_path / "a"), "--ckpt-every", "10",
+                           "--metrics", str(tmp_path / "m.jsonl")])
+    assert whole["steps"] == 30 and whole["losses"][-1] < 0.6 * whole["losses"][0]
+    assert [s for s, _ in whole["evals"]] == [10, 20, 30] and whole["evals"][-1][1] < whole["evals"][0][1]
+    assert len(open(tmp_path / "m.jsonl").read().splitlines()) == 30
+    # an interrupted job: the same 30-step job whose newest finished checkpoint is the one of step 20
+    part = _run(common + ["--steps", "30", "--ckpt", str(tmp_path / "c"), "--ckpt-every", "20"])
+    assert part["losses"] == whole["losses"]                      # same seed, same data order: deterministic on the CPU
+    os.remove(os.path.join(str(tmp_path / "c"), "LATEST"))        # forget the final checkpoint: step 20 is the newest left
+    with open(os.path.join(str(tmp_path / "c"), "LATEST"), "w") as f:
+        f.write("step-00000020")
+    rest = _run(common + ["--steps", "30", "--ckpt", str(tmp_path / "c"), "--ckpt-every", "20"])
+    assert rest["steps"] == 30 and len(rest["losses"]) == 10
+    assert all(abs(a - b) < 1e-5 for a, b in zip(rest["losses"], whole["losses"][20:]))
+    assert (rest["epoch"], rest["position"]) == (whole["epoch"], whole["position"])
+
+
+def test_example_runs_as_two_data_parallel_ranks(tmp_path):
+    data = str(tmp_path / "tokens.bin")
+    _tokens(data)
+    out = _run(["--data", data, "--tiny", "--device", "cpu", "--config", "llama-1.1b-fsdp", "--seq-len", "32", "--batch", "2",
+                "--lr", "3e-3", "--warmup", "2", "--steps", "8", "--ckpt", str(tmp_path / "ck"), "--ckpt-every", "4"], nproc=2)
+    assert out["steps"] == 8 and out["losses"][-1] < out["losses"][0]
+    assert sorted(os.listdir(tmp_path / "ck")) == ["LATEST", "step-00000004", "step-00000008"]
+    assert "trainer.rank00001.ltw1" in os.listdir(tmp_path / "ck" / "step-00000008")

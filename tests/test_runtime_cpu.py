@@ -181,6 +181,70 @@ def test_dataloader_state_file_layout_and_deterministic_resume(tmp_path):
         dl2.load_state(path)
 
 
+def test_token_stream_windows_ranks_epochs_and_exact_resume(tmp_path):
+    import numpy as np
+    path = str(tmp_path / "tokens.bin")
+    n = 5000
+    np.arange(n, dtype=np.uint32).tofile(path)                      # token i has the value i: windows are recognisable
+    T, B, W = 16, 3, 2
+    streams = [lt.data.TokenStream(path, T, B, dtype="uint32", shuffle=True, seed=5, rank=r, world=W) for r in range(W)]
+    assert streams[0].num_tokens == n and streams[0].num_windows == (n - 1) // T
+    per_epoch = streams[0].batches_per_epoch
+    assert per_epoch == (streams[0].num_windows // W) // B
+    seen = []
+    for s in streams:
+        mine = []
+        while (b := s.next()) is not None:
+            tok, tgt = b
+            assert tok.shape == (B, T) and tok.dtype == torch.int64
+            assert torch.equal(tgt, tok + 1) and bool((tok[:, 1:] == tok[:, :-1] + 1).all())
+            assert bool((tok[:, 0] % T == 0).all())                  # window i starts at token i * T
+            mine += (tok[:, 0] // T).tolist()
+        assert s.next() is None and len(mine) == per_epoch * B       # the end of the epoch is sticky
+        seen.append(mine)
+    assert not set(seen[0]) & set(seen[1]) and len(set(seen[0])) == len(seen[0])   # ranks see disjoint windows, once
+    first_epoch = list(seen[0])
+    streams[0].next_epoch()
+    second = []
+    while (b := streams[0].next()) is not None:
+        second += (b[0][:, 0] // T).tolist()
+    assert streams[0].epoch == 1 and second != first_epoch           # a new permutation
+    # exact resume: take some batches, save, read the rest; a fresh stream that loads the state reads the same rest
+    a = lt.data.TokenStream(path, T, B, dtype="uint32", shuffle=True, seed=5, rank=1, world=W)
+    a.next_epoch()
+    for _ in range(7):
+        a.next()
+    a.save_state(str(tmp_path / "ts.json"))
+    rest = []
+    for _ in range(per_epoch + 5):                                   # across the epoch boundary
+        b = a.next()
+        if b is None:
+            a.next_epoch()
+            continue
+        rest.append(b[0].clone())
+    c = lt.data.TokenStream(path, T, B, dtype="uint32", shuffle=True, seed=5, rank=1, world=W)
+    c.load_state(str(tmp_path / "ts.json"))
+    assert (c.epoch, c.position) == (1, 7)
+    again = []
+    for _ in range(per_epoch + 5):
+        b = c.next()
+        if b is None:
+            c.next_epoch()
+            continue
+        again.append(b[0].clone())
+    assert len(again) == len(rest) and all(torch.equal(x, y) for x, y in zip(again, rest))
+    with pytest.raises(RuntimeError):
+        lt.data.TokenStream(path, T, B + 1, dtype="uint32", rank=1, world=W).load_state(str(tmp_path / "ts.json"))
+    with pytest.raises(RuntimeError):
+        lt.data.TokenStream(path, 4000, 4, dtype="uint32")           # not enough windows for one batch
+    # sequential order without shuffling, 16-bit tokens, the endless iterator
+    np.arange(300, dtype=np.uint16).tofile(str(tmp_path / "small.bin"))
+    seq = lt.data.TokenStream(str(tmp_path / "small.bin"), 10, 2, shuffle=False)
+    it = iter(seq)
+    firsts = [next(it)[0][:, 0].tolist() for _ in range(seq.batches_per_epoch + 1)]
+    assert firsts[0] == [0, 10] and firsts[1] == [20, 30] and firsts[-1] == [0, 10] and seq.epoch == 1
+
+
 def test_python_dataset_subclass():
     class Sq(lt.data.Dataset):
         def size(self): return 10

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 RUNTIME = os.path.join(ROOT, "csrc", "runtime")
 DRIVERS = {
     "runtime_stress": ["threadpool.cpp", "allocator.cpp", "store.cpp"],
-    "services_stress": ["scheduler.cpp", "dataloader.cpp", "io.cpp", "jit.cpp", "threadpool.cpp", "allocator.cpp"],
+    "services_stress": ["scheduler.cpp", "dataloader.cpp", "tokenstream.cpp", "io.cpp", "jit.cpp", "threadpool.cpp", "allocator.cpp"],
 }
 
 
