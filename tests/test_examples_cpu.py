@@ -57,3 +57,35 @@ def test_example_runs_as_two_data_parallel_ranks(tmp_path):
     assert out["steps"] == 8 and out["losses"][-1] < out["losses"][0]
     assert sorted(os.listdir(tmp_path / "ck")) == ["LATEST", "step-00000004", "step-00000008"]
     assert "trainer.rank00001.ltw1" in os.listdir(tmp_path / "ck" / "step-00000008")
+
+
+def test_prepare_data_then_train_then_export_then_generate(tmp_path):
+    """The whole path a user walks: text -> token file -> a few training steps -> Hugging Face export -> generation."""
+    import torch
+    sys.path.insert(0, ROOT)
+    from litetorch_b200.models import llama_io
+    from litetorch_b200.models.llama import LlamaConfig, LlamaEngine, LocalWeights
+    text = tmp_path / "corpus.txt"
+    text.write_text(("the quick brown fox jumps over the lazy dog\n" * 40 + "\n") * 30)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "prepare_data.py"), "--input", str(text), "--out",
+                        str(tmp_path / "tokens.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    meta = json.loads(r.stdout.splitlines()[-1])
+    assert meta["documents"] == 30 and meta["vocab_size"] == 257 and meta["tokens"] == 30 * (40 * 44 + 1)
+    toks = np.fromfile(str(tmp_path / "tokens.bin"), dtype=np.uint16)
+    assert len(toks) == meta["tokens"] and int(toks.max()) == 256 and bytes(toks[:9].astype(np.uint8)) == b"the quick"
+    # a small byte-level model, trained a little in-process on that file
+    import litetorch_b200 as lt
+    cfg = LlamaConfig(vocab_size=264, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=128, max_seq=128, name="bytes")
+    engine = LlamaEngine(cfg, "cpu", weights=LocalWeights(cfg, "cpu", seed=0, param_dtype=torch.float32), lr=3e-3, weight_decay=0.0)
+    stream = lt.data.TokenStream(str(tmp_path / "tokens.bin"), 64, 8, seed=0, rank=0, world=1)
+    it = iter(stream)
+    losses = [float(engine.train_step(*next(it))) for _ in range(60)]
+    assert losses[-1] < 0.5 * losses[0]
+    llama_io.save_pretrained(engine, str(tmp_path / "export"), dtype=torch.float32)
+    g = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "generate_llama.py"), "--model", str(tmp_path / "export"),
+                        "--bytes", "--device", "cpu", "--prompt", "the quick brown fox jumps over the lazy dog\nthe quick ",
+                        "--max-new-tokens", "10"], capture_output=True, text=True, timeout=600)
+    assert g.returncode == 0, g.stdout[-2000:] + g.stderr[-3000:]
+    res = json.loads([l for l in g.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["new_tokens"] == 10 and len(res["texts"][0]) > 0
