@@ -13,7 +13,6 @@ process also beats in the launcher's store, so a hung rank is noticed and the gr
 """
 import argparse
 import json
-import math
 import os
 import sys
 import time
@@ -84,21 +83,17 @@ def main(argv=None) -> dict:
         trainer.load(args.ckpt, loader=stream)
         say("resumed from %s at step %d" % (Trainer.latest_checkpoint(args.ckpt), trainer.engine.step_count))
 
-    def lr_at(step: int) -> float:
-        if step < args.warmup:
-            return peak * (step + 1) / args.warmup
-        t = (step - args.warmup) / max(1, args.steps - args.warmup)
-        return peak * (args.min_lr_ratio + (1 - args.min_lr_ratio) * 0.5 * (1 + math.cos(math.pi * min(t, 1.0))))
+    # the rate depends on the step count alone: a resumed job continues on the same curve
+    sched = lt.optim.WarmupCosineLR(trainer, args.warmup, args.steps, args.min_lr_ratio, last_epoch=trainer.engine.step_count)
 
     losses, evals = [], []
     batches = iter(stream)
     t0 = time.time()
     while trainer.engine.step_count < args.steps:
-        step = trainer.engine.step_count
-        trainer.set_lr(lr_at(step))
         tokens, targets = next(batches)
         losses.append(trainer.step(tokens, targets))
-        step += 1
+        sched.step()
+        step = trainer.engine.step_count
         if args.eval_every and step % args.eval_every == 0:
             tk, tg = next(iter(held_out))
             evals.append((step, trainer.evaluate(tk, tg)))

@@ -514,6 +514,36 @@ class CosineAnnealingLR:
         return self.optimizer.lr
 
 
+class WarmupCosineLR:
+    """Linear warm-up from 0 to the optimizer's rate over `warmup_steps`, then half a cosine down to `min_lr_ratio` times
+    that rate at `total_steps` (constant afterwards): the usual schedule of LLM pre-training.  The rate is a function of
+    `last_epoch` alone, so a resumed job sets `last_epoch` to its step count and continues on the same curve.  Unlike the
+    two schedulers of the reference it also sets the rate of step 0 at construction (a warm-up starts below the base rate)."""
+
+    def __init__(self, optimizer, warmup_steps: int, total_steps: int, min_lr_ratio: float = 0.1, last_epoch: int = 0):
+        self.optimizer, self.warmup_steps, self.total_steps = optimizer, int(warmup_steps), int(total_steps)
+        self.min_lr_ratio, self.base_lr = float(min_lr_ratio), optimizer.lr
+        self.last_epoch = int(last_epoch)
+        self.optimizer.lr = self.lr_at(self.last_epoch)
+
+    def lr_at(self, step: int) -> float:
+        if step < self.warmup_steps:
+            return self.base_lr * (step + 1) / self.warmup_steps
+        t = (step - self.warmup_steps) / max(1, self.total_steps - self.warmup_steps)
+        return self.base_lr * (self.min_lr_ratio + (1.0 - self.min_lr_ratio) * 0.5 * (1.0 + math.cos(math.pi * min(t, 1.0))))
+
+    @property
+    def epoch(self) -> int:
+        return self.last_epoch
+
+    def step(self):
+        self.last_epoch += 1
+        self.optimizer.lr = self.lr_at(self.last_epoch)
+
+    def get_lr(self) -> float:
+        return self.optimizer.lr
+
+
 class GradScaler(_AmpGradScaler):
     """`lt.optim.GradScaler`: `scale_loss / step / update` and the `.scale` value (src/optim/grad_scaler.cpp:8-79)."""
 
@@ -524,4 +554,4 @@ class GradScaler(_AmpGradScaler):
 
 
 __all__ = ["Optimizer", "SGD", "Adam", "AdamW", "AdamW8bit", "AdamWFP8", "RMSprop", "ZeRO3Optimizer", "StepLR",
-           "CosineAnnealingLR", "GradScaler"]
+           "CosineAnnealingLR", "WarmupCosineLR", "GradScaler"]
