@@ -235,7 +235,18 @@ class ServingScheduler:
             r.is_finished = True
             r.block_ids = []
             out.append(r)
+            self._retire(r.id)
         return out
+
+    def _retire(self, rid: int) -> None:
+        """A finished request leaves the books (here and in the native scheduler): a server that runs for days holds
+        state for the requests in flight only.  The caller keeps the `Request` object it was handed."""
+        self._lib.lt_sched_release(self._s, rid)
+        self._reqs.pop(rid, None)
+        try:
+            self._order.remove(rid)
+        except ValueError:
+            pass
 
     def _step_kv(self, model) -> List[Request]:
         cap = max(self.max_num_seqs, 1)
@@ -270,6 +281,7 @@ class ServingScheduler:
             r.is_finished = True
             r.block_ids = []
             out.append(r)
+            self._retire(r.id)
         return out
 
     def get_block_table_tensor(self) -> Tensor:
