@@ -11,6 +11,7 @@ prompt chunk).  The reference's counterparts: ContinuousBatchingScheduler::step 
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import List, Sequence
 
 import torch
@@ -21,7 +22,7 @@ from .llama import LlamaEngine
 
 class LlamaKVModel:
     def __init__(self, engine: LlamaEngine, num_blocks: int, block_size: int = 16, kv_dtype=torch.bfloat16, num_splits: int = 0,
-                 graphs: bool = True):
+                 graphs: bool = True, prefix_cache_bytes: int = 0):
         assert engine.w.tp == 1 and hasattr(engine.w, "flat_p"), "serving runs on whole (unsharded) weights"
         self.e = engine
         cfg = engine.cfg
@@ -33,6 +34,20 @@ class LlamaKVModel:
         self.cache = PagedKVCache(cfg.n_layers, num_blocks, block_size, cfg.n_kv_heads, cfg.head_dim, device=engine.device,
                                   dtype=kv_dtype)
         self.kv_bytes_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * self.cache.k[0].element_size()
+        # ---- prefix reuse: K / V of finished prompts' whole blocks are kept as snapshots (up to `prefix_cache_bytes`,
+        # least recently used first out); a later prompt that starts with the same tokens gets those blocks by a copy
+        # and only its remaining tokens are computed.  The reference has the prefix map (src/llm/prefix_cache.cpp) but
+        # never consults it while serving.
+        self.prefix_cache_bytes = int(prefix_cache_bytes)
+        self.prefill_tokens_computed = 0
+        self.prefill_tokens_reused = 0
+        self._snap = OrderedDict()           # handle -> (k [layers, nb, Hkv, bs, hd], v, bytes)
+        self._snap_bytes = 0
+        self._next_handle = 1
+        self._seq_tokens = {}                # first block of a sequence in prefill -> its prompt tokens so far
+        if self.prefix_cache_bytes > 0:
+            from ..serving import PrefixCache
+            self._index = PrefixCache()
 
     # ------------------------------------------------------------------ shared layer body
     def _layers(self, x, positions, attend):
@@ -74,9 +89,78 @@ class LlamaKVModel:
         """Run prompt positions [start, start + len(tokens)) of one sequence: their K / V go into the sequence's blocks,
         their queries attend to everything cached so far.  Returns the greedy next token when `want_token` (the chunk
         completes the prompt), else -1."""
+        if self.prefix_cache_bytes > 0:
+            return self._prefill_with_reuse(list(tokens), start, block_ids, want_token)
+        return self._prefill_compute(tokens, start, block_ids, want_token)
+
+    # ---- prefix reuse around the computation
+    def _prefill_with_reuse(self, tokens: List[int], start: int, block_ids: Sequence[int], want_token: bool) -> int:
+        bs = self.block_size
+        key = block_ids[0]
+        sofar = (self._seq_tokens.get(key, []) if start > 0 else []) + tokens
+        end = start + len(tokens)
+        matched, handles = self._index.longest_prefix(sofar, bs)
+        snap = self._snap.get(handles[0]) if handles else None
+        covered = start
+        if snap is not None and matched > start:
+            self._snap.move_to_end(handles[0])
+            m = min(matched, snap[0].shape[1] * bs)
+            if m >= end and want_token:                           # the last token's logits are needed: compute it
+                m = (end - 1) // bs * bs
+            if m > start:
+                b0, b1 = start // bs, m // bs
+                dst = torch.tensor(list(block_ids[b0:b1]), dtype=torch.int64, device=self.e.device)
+                for i in range(self.e.cfg.n_layers):
+                    self.cache.k[i][dst] = snap[0][i, b0:b1]
+                    self.cache.v[i][dst] = snap[1][i, b0:b1]
+                self.prefill_tokens_reused += m - start
+                covered = m
+        out = self._prefill_compute(sofar[covered:end], covered, block_ids, want_token) if covered < end else -1
+        if want_token:
+            self._seq_tokens.pop(key, None)
+            self._remember(sofar, block_ids)
+        else:
+            self._seq_tokens[key] = sofar
+        return out
+
+    def _remember(self, prompt: List[int], block_ids: Sequence[int]) -> None:
+        bs = self.block_size
+        nb = len(prompt) // bs
+        if nb == 0:
+            return
+        L = nb * bs
+        got, handles = self._index.longest_prefix(prompt[:L], bs)
+        if got == L and handles and handles[0] in self._snap:
+            return                                                # this prefix is cached already
+        blocks = torch.tensor(list(block_ids[:nb]), dtype=torch.int64, device=self.e.device)
+        k = torch.stack([self.cache.k[i][blocks] for i in range(self.e.cfg.n_layers)])
+        v = torch.stack([self.cache.v[i][blocks] for i in range(self.e.cfg.n_layers)])
+        nbytes = 2 * k.numel() * k.element_size()
+        if nbytes > self.prefix_cache_bytes:
+            return
+        while self._snap and self._snap_bytes + nbytes > self.prefix_cache_bytes:
+            _, (_, _, old) = self._snap.popitem(last=False)
+            self._snap_bytes -= old
+        h = self._next_handle
+        self._next_handle += 1
+        self._snap[h] = (k, v, nbytes)
+        self._snap_bytes += nbytes
+        # findable by prompts that share the whole thing or a power-of-two number of its blocks: a later prompt reuses at
+        # least half of the whole blocks it shares, for a logarithmic number of index entries per prompt
+        lengths, j = {L}, 1
+        while j * bs < L:
+            lengths.add(j * bs)
+            j *= 2
+        from ..serving import _i32
+        for n in sorted(lengths):                                 # the native index alone (it evicts by itself)
+            self._index._lib.lt_prefix_insert(self._index._c, _i32(prompt[:n]), n, _i32([h]), 1)
+
+    @torch.no_grad()
+    def _prefill_compute(self, tokens: Sequence[int], start: int, block_ids: Sequence[int], want_token: bool) -> int:
         e, K = self.e, self.e.K
         dev = e.device
         n = len(tokens)
+        self.prefill_tokens_computed += n
         host = torch.empty(3, n, dtype=torch.int64)
         host[0] = torch.tensor(tokens, dtype=torch.int64)
         host[1] = torch.arange(start, start + n)

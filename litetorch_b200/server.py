@@ -165,6 +165,7 @@ def main(argv=None):
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--max-batched-tokens", type=int, default=4096)
+    ap.add_argument("--prefix-cache-mb", type=int, default=0, help="keep K / V of finished prompts for reuse by prompts that share a prefix")
     args = ap.parse_args(argv)
     kw = {}
     if args.device == "cpu":
@@ -175,7 +176,8 @@ def main(argv=None):
         kw["weights"] = LocalWeights(cfg, "cpu", seed=0, param_dtype=torch.float32)
     engine = llama_io.load_pretrained(args.model, device=args.device, **kw)
     model = LlamaKVModel(engine, num_blocks=args.kv_blocks, block_size=args.block_size,
-                         kv_dtype=torch.float32 if args.device == "cpu" else torch.bfloat16)
+                         kv_dtype=torch.float32 if args.device == "cpu" else torch.bfloat16,
+                         prefix_cache_bytes=args.prefix_cache_mb << 20)
     encode, decode, eos = tokenizer(args.sentencepiece, args.bytes)
     loop = EngineLoop(model, args.kv_blocks, args.block_size, args.max_num_seqs, args.max_batched_tokens, eos_id=eos,
                       max_context=engine.cfg.max_seq)
