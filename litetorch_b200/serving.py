@@ -188,10 +188,21 @@ class ServingScheduler:
         r = self._reqs[rid]
         return r.prompt_tokens + r.generated_tokens
 
-    def step(self, model) -> List[Request]:
+    def step(self, model=None) -> List[Request]:
         """One scheduling step.  A model with `prefill_chunk` / `decode_batch` (e.g. `models.llama_serving.LlamaKVModel`)
         owns a paged KV cache and is driven with the scheduler's block tables: every token is computed once.  Any other
-        callable `model(tokens) -> logits` is served by recomputing each context (the reference's behaviour)."""
+        callable `model(tokens) -> logits` is served by recomputing each context (the reference's behaviour).
+
+        Without a model (the form the reference's serving guide shows) nothing is computed: pending requests are admitted
+        while blocks are free and the requests that would run in this step are returned, so that the caller can read
+        `get_block_table_tensor()` / `get_context_lens_tensor()` and drive its own kernels."""
+        if model is None:
+            cap = max(self.max_num_seqs, 1)
+            ids, starts, lens = (c_int64 * cap)(), (c_int32 * cap)(), (c_int32 * cap)()
+            n = self._lib.lt_sched_plan(self._s, ids, starts, lens, cap)      # planning alone changes no position
+            for i in range(n):
+                self._sync(int(ids[i]))
+            return [self._reqs[int(ids[i])] for i in range(n)]
         if hasattr(model, "prefill_chunk") and hasattr(model, "decode_batch"):
             return self._step_kv(model)
         cap = max(self.max_num_seqs, 1)

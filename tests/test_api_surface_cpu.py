@@ -290,3 +290,22 @@ def test_enum_values_are_exported_into_their_modules():
     assert lt.distributed.SHARD is lt.distributed.PlacementType.SHARD and lt.distributed.PARTIAL is lt.distributed.PlacementType.PARTIAL
     assert lt.jit.INPUT is lt.jit.OpType.INPUT and lt.jit.GELU is lt.jit.OpType.GELU and callable(lt.jit.gelu)
     assert lt.CPU is lt.DeviceType.CPU and lt.FP32 is lt.DataType.FP32
+
+
+def test_scheduler_step_without_a_model_plans_only():
+    """The reference's serving guide calls `scheduler.step()` and then reads the block tables: admission and planning
+    happen, no position moves, and a later `step(model)` serves the request as usual."""
+    import torch
+    s = lt.nn.ServingScheduler(num_blocks=8, block_size=4, max_num_seqs=2, max_num_batched_tokens=16)
+    r = lt.nn.Request(id=1, prompt=[1, 2, 3, 4, 5], max_new_tokens=2)
+    s.add_request(r)
+    first, second = s.step(), s.step()
+    assert [q.id for q in first] == [1] == [q.id for q in second] and len(r.block_ids) == 2 and s.free_blocks == 6
+    assert s.get_block_table_tensor().shape == [1, 2] and s.get_context_lens_tensor().to_vector() == [0.0]
+
+    class Next(lt.nn.Module):
+        def forward(self, x):
+            return lt.Tensor(torch.nn.functional.one_hot((x.torch().long() + 1) % 16, 16).float())
+    while not r.is_finished:
+        s.step(Next())
+    assert r.generated_tokens == [6, 7] and s.free_blocks == 8
