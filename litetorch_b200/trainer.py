@@ -253,7 +253,9 @@ class Trainer:
             meta = json.load(f)["meta"]
         for k in ("weights", "world_size", "tp", "model"):
             if meta.get(k) != lay[k]:
-                raise CheckpointError("checkpoint %s differs: written with %r, this trainer has %r" % (k, meta.get(k), lay[k]))
+                raise CheckpointError("checkpoint %s differs: written with %r, this trainer has %r (another world size or "
+                                      "tensor-parallel width: `python -m litetorch_b200.checkpoint_tools reshard`)"
+                                      % (k, meta.get(k), lay[k]))
         if meta["names"] != list(state):
             raise CheckpointError("checkpoint holds %r, this trainer expects %r" % (meta["names"], list(state)))
         sharded = lay["world_size"] > 1
