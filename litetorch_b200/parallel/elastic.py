@@ -48,7 +48,13 @@ def start_heartbeat(interval_s: float = 0.25) -> Optional[Watchdog]:
 class ElasticLauncher:
     def __init__(self, argv: Sequence[str], nproc: int, max_restarts: int = 3, master_addr: str = "127.0.0.1", base_port: int = 29600,
                  heartbeat_ttl_s: float = 10.0, start_grace_s: float = 120.0, poll_s: float = 0.1, stop_grace_s: float = 5.0,
-                 env: Optional[Dict[str, str]] = None, log_dir: Optional[str] = None):
+                 env: Optional[Dict[str, str]] = None, log_dir: Optional[str] = None, shrink_after: int = 0, min_nproc: int = 1,
+                 ckpt_dir: Optional[str] = None, tp: int = 1):
+        """shrink_after = k > 0: after k failed attempts in a row at the current size the group restarts with half the
+        ranks (not below `min_nproc`, and a multiple of `tp`): a job that lost a GPU for good continues on the rest.  With
+        `ckpt_dir` the newest trainer checkpoint there is first re-cut for the new world size
+        (`checkpoint_tools.reshard`), so the script resumes as usual."""
+        self.shrink_after, self.min_nproc, self.ckpt_dir, self.tp = int(shrink_after), max(1, int(min_nproc)), ckpt_dir, max(1, int(tp))
         self.argv, self.nproc, self.max_restarts = list(argv), nproc, max_restarts
         self.addr, self.base_port = master_addr, base_port
         self.ttl, self.start_grace, self.poll, self.stop_grace = heartbeat_ttl_s, start_grace_s, poll_s, stop_grace_s
@@ -128,18 +134,42 @@ class ElasticLauncher:
             store.close()
             for f in logs:
                 f.close()
-        rec = {"attempt": attempt, "returncodes": [p.returncode for p in procs], "reason": reason,
+        rec = {"attempt": attempt, "nproc": self.nproc, "returncodes": [p.returncode for p in procs], "reason": reason,
                "seconds": round(time.monotonic() - t0, 3)}
         self.attempts.append(rec)
         return rec
 
     # ------------------------------------------------------------------ the job
+    def _shrink(self) -> bool:
+        """Halve the group (a multiple of tp, at least min_nproc) and re-cut the newest checkpoint for it."""
+        new = max(self.min_nproc, (self.nproc // 2) // self.tp * self.tp, self.tp)
+        if new >= self.nproc:
+            return False
+        if self.ckpt_dir:
+            from .. import checkpoint_tools as tools
+            from ..trainer import Trainer
+            if Trainer.latest_checkpoint(self.ckpt_dir):
+                import shutil
+                staged = self.ckpt_dir.rstrip("/") + ".resharded"
+                shutil.rmtree(staged, ignore_errors=True)
+                tools.reshard(self.ckpt_dir, staged, world=new, tp=self.tp)
+                kept = self.ckpt_dir.rstrip("/") + ".world%d" % self.nproc      # the old cut stays beside it
+                shutil.rmtree(kept, ignore_errors=True)
+                os.replace(self.ckpt_dir, kept)
+                os.replace(staged, self.ckpt_dir)
+        self.nproc = new
+        return True
+
     def run(self) -> Dict:
+        failed_here = 0
         for attempt in range(self.max_restarts + 1):
             rec = self._attempt(attempt)
             if rec["reason"] is None:
-                return {"ok": True, "restarts": attempt, "attempts": self.attempts}
-        return {"ok": False, "restarts": self.max_restarts, "attempts": self.attempts}
+                return {"ok": True, "restarts": attempt, "nproc": self.nproc, "attempts": self.attempts}
+            failed_here += 1
+            if self.shrink_after and failed_here >= self.shrink_after and attempt < self.max_restarts and self._shrink():
+                failed_here = 0
+        return {"ok": False, "restarts": self.max_restarts, "nproc": self.nproc, "attempts": self.attempts}
 
 
 def main(argv=None) -> int:
@@ -150,11 +180,15 @@ def main(argv=None) -> int:
     ap.add_argument("--base-port", type=int, default=29600)
     ap.add_argument("--heartbeat-ttl", type=float, default=10.0)
     ap.add_argument("--log-dir", default=None)
+    ap.add_argument("--shrink-after", type=int, default=0, help="failed attempts at one size before the group is halved (0: never)")
+    ap.add_argument("--min-nproc", type=int, default=1)
+    ap.add_argument("--ckpt", default=None, help="trainer checkpoint directory to re-cut when the group shrinks")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel width of the job (group sizes stay multiples of it)")
     ap.add_argument("script")
     ap.add_argument("args", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     res = ElasticLauncher([sys.executable, a.script] + a.args, a.nproc, a.max_restarts, a.master_addr, a.base_port, a.heartbeat_ttl,
-                          log_dir=a.log_dir).run()
+                          log_dir=a.log_dir, shrink_after=a.shrink_after, min_nproc=a.min_nproc, ckpt_dir=a.ckpt, tp=a.tp).run()
     print(json.dumps(res))
     return 0 if res["ok"] else 1
 

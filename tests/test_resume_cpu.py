@@ -233,8 +233,9 @@ for s in range(start, 6):
             time.sleep(600)
 if rank == 0:
     print("RESULT " + json.dumps({"attempt": attempt, "start": start, "losses": losses}), flush=True)
-dist.barrier()
-dist.destroy_process_group()
+if dist.is_initialized():                           # a group that shrank to one rank has no process group
+    dist.barrier()
+    dist.destroy_process_group()
 '''
 
 
@@ -275,6 +276,30 @@ def test_elastic_launcher_restarts_the_group_and_the_run_ends_on_the_uninterrupt
     assert ("exited with code 17" in first["reason"]) if mode == "exit" else ("heartbeats" in first["reason"]), first
     assert len(out) == 1 and out[0]["attempt"] == 1 and out[0]["start"] == 3
     assert all(abs(x - y) < 1e-6 for x, y in zip(out[0]["losses"], uninterrupted_run[3:])), (out, uninterrupted_run)
+
+
+def test_elastic_launcher_shrinks_the_group_and_recuts_the_checkpoint(tmp_path):
+    """A rank that fails every time at two ranks (a GPU lost for good): after one failed attempt the launcher halves the
+    group, re-cuts the newest checkpoint for one rank, and the job resumes from step 3 and finishes there."""
+    from litetorch_b200.parallel.elastic import ElasticLauncher
+    script = tmp_path / "w.py"
+    script.write_text((ELASTIC_WORKER % {"root": ROOT}).replace("if attempt == 0 and rank == 1 and s == 2:",
+                                                                "if world == 2 and rank == 1 and s == 2:"))
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    ck, logs = str(tmp_path / "ck"), str(tmp_path / "logs")
+    res = ElasticLauncher([sys.executable, str(script), ck, "exit"], nproc=2, max_restarts=2, base_port=29760, heartbeat_ttl_s=2.0,
+                          start_grace_s=120.0, env=env, log_dir=logs, shrink_after=1, ckpt_dir=ck, tp=1).run()
+    assert res["ok"] and res["restarts"] == 1 and res["nproc"] == 1, res
+    assert [a["nproc"] for a in res["attempts"]] == [2, 1] and "code 17" in res["attempts"][0]["reason"]
+    with open(os.path.join(logs, "attempt1_rank0.log")) as f:
+        out = [json.loads(l[7:]) for l in f.read().splitlines() if l.startswith("RESULT ")]
+    assert len(out) == 1 and out[0]["start"] == 3 and len(out[0]["losses"]) == 3
+    assert os.path.isdir(ck + ".world2")                               # the two-rank cut is kept beside the new one
+    with open(os.path.join(ck, open(os.path.join(ck, "LATEST")).read(), "trainer.manifest.json")) as f:
+        meta = json.load(f)["meta"]
+    assert meta["world_size"] == 1 and meta["weights"] == "LocalWeights" and meta["step_count"] == 6
 
 
 def test_trainer_checkpoints_are_complete_or_absent(tmp_path):
