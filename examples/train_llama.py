@@ -80,7 +80,17 @@ def main(argv=None) -> dict:
     if args.metrics:
         trainer.log_metrics(args.metrics)
     if args.ckpt and Trainer.latest_checkpoint(args.ckpt):
-        trainer.load(args.ckpt, loader=stream)
+        try:
+            trainer.load(args.ckpt, loader=stream)
+        except RuntimeError as e:
+            # a checkpoint that was re-cut for another world size carries no loader position: the weights and the
+            # optimizer resume, the data starts from the beginning of an epoch chosen by the step count
+            if "loader" not in str(e) and "token stream" not in str(e):
+                raise
+            trainer.load(args.ckpt)
+            stream.load_state_dict(dict(stream.state_dict(), epoch=trainer.engine.step_count // max(1, stream.batches_per_epoch) + 1,
+                                        position=0))
+            say("the checkpoint has no loader position for this layout: data restarts at epoch %d" % stream.epoch)
         say("resumed from %s at step %d" % (Trainer.latest_checkpoint(args.ckpt), trainer.engine.step_count))
 
     # the rate depends on the step count alone: a resumed job continues on the same curve

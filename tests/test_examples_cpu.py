@@ -89,3 +89,19 @@ def test_prepare_data_then_train_then_export_then_generate(tmp_path):
     assert g.returncode == 0, g.stdout[-2000:] + g.stderr[-3000:]
     res = json.loads([l for l in g.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert res["new_tokens"] == 10 and len(res["texts"][0]) > 0
+
+
+def test_example_continues_from_a_checkpoint_recut_for_fewer_ranks(tmp_path):
+    """Two data-parallel ranks train and checkpoint; the checkpoint is re-cut for one rank and the same script goes on
+    from its step count (weights and optimizer resume, the data position does not carry over)."""
+    sys.path.insert(0, ROOT)
+    from litetorch_b200 import checkpoint_tools
+    data = str(tmp_path / "tokens.bin")
+    _tokens(data)
+    common = ["--data", data, "--tiny", "--device", "cpu", "--config", "llama-1.1b-fsdp", "--seq-len", "32", "--batch", "2",
+              "--lr", "3e-3", "--warmup", "2", "--ckpt-every", "6"]
+    two = _run(common + ["--steps", "6", "--ckpt", str(tmp_path / "ck2")], nproc=2, port=29951)
+    assert two["steps"] == 6
+    checkpoint_tools.reshard(str(tmp_path / "ck2"), str(tmp_path / "ck1"), world=1)
+    one = _run(common + ["--steps", "12", "--ckpt", str(tmp_path / "ck1")])
+    assert one["steps"] == 12 and len(one["losses"]) == 6 and one["losses"][0] < two["losses"][0]
