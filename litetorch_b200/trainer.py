@@ -21,6 +21,11 @@ import torch
 from .models.llama import LlamaConfig, LlamaEngine
 
 
+def _local_weights():
+    from .models.llama import LocalWeights
+    return LocalWeights
+
+
 class Trainer:
     def __init__(self, cfg: LlamaConfig, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, seed: int = 0, activation_checkpointing: bool = False,
@@ -129,10 +134,17 @@ class Trainer:
             self._metrics.write(**rec)
         return float(out)
 
-    def evaluate(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor) -> float:
-        """Loss of a host batch without an update (`LlamaEngine.eval_loss`); this rank's batch under data parallelism."""
+    def evaluate(self, tokens_cpu: torch.Tensor, targets_cpu: torch.Tensor, reduce: bool = True) -> float:
+        """Loss of a host batch without an update (`LlamaEngine.eval_loss`).  Under data parallelism every replica
+        evaluates its own batch; `reduce` (default) averages the result over all ranks (the ranks of a tensor-parallel
+        group hold the same value, so this is the mean over the replicas) - every rank must then call it."""
         dev = self.device
         out = self.engine.eval_loss(tokens_cpu.to(dev, non_blocking=True), targets_cpu.to(dev, non_blocking=True))
+        if reduce and self.world_size > 1 and not isinstance(self.engine.w, _local_weights()):
+            import torch.distributed as dist
+            out = out.detach().clone().reshape(1)
+            dist.all_reduce(out)
+            out = out / self.world_size
         return float(out)
 
     # ---- checkpoint / resume of the whole training state

@@ -53,8 +53,10 @@ def test_example_runs_as_two_data_parallel_ranks(tmp_path):
     data = str(tmp_path / "tokens.bin")
     _tokens(data)
     out = _run(["--data", data, "--tiny", "--device", "cpu", "--config", "llama-1.1b-fsdp", "--seq-len", "32", "--batch", "2",
-                "--lr", "3e-3", "--warmup", "2", "--steps", "8", "--ckpt", str(tmp_path / "ck"), "--ckpt-every", "4"], nproc=2)
+                "--lr", "3e-3", "--warmup", "2", "--steps", "8", "--ckpt", str(tmp_path / "ck"), "--ckpt-every", "4",
+                "--eval-every", "4"], nproc=2)
     assert out["steps"] == 8 and out["losses"][-1] < out["losses"][0]
+    assert [s for s, _ in out["evals"]] == [4, 8] and out["evals"][1][1] < out["evals"][0][1]      # averaged over the two ranks
     assert sorted(os.listdir(tmp_path / "ck")) == ["LATEST", "step-00000004", "step-00000008"]
     assert "trainer.rank00001.ltw1" in os.listdir(tmp_path / "ck" / "step-00000008")
 
