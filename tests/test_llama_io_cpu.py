@@ -4,10 +4,8 @@ engine gives the same logits and the same loss, the conversion back reproduces t
 import pytest
 import torch
 
-transformers = pytest.importorskip("transformers")
-
-
 def _hf_model(seed=0, **kw):
+    pytest.importorskip("transformers")            # imported by the tests that need it, not at collection time
     from transformers import LlamaConfig as HC, LlamaForCausalLM
     torch.manual_seed(seed)
     args = dict(vocab_size=384, hidden_size=128, intermediate_size=320, num_hidden_layers=2, num_attention_heads=4,
@@ -69,6 +67,7 @@ def test_conversion_round_trip_and_tied_embeddings():
 
 def test_save_pretrained_is_read_by_transformers_and_by_load_pretrained(tmp_path):
     pytest.importorskip("safetensors")
+    pytest.importorskip("transformers")
     from transformers import LlamaForCausalLM
     from litetorch_b200.models import llama_io
     from litetorch_b200.models.llama import LlamaConfig, LlamaEngine, LocalWeights
