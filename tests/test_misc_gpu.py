@@ -194,17 +194,3 @@ def test_optimizer_kernels_follow_the_torch_path(name):
             assert torch.is_tensor(opt.m_scale[0]) and opt.m_scale[0].is_cuda        # scales never left the device
     tol = 1e-5 if name in ("SGD", "RMSprop") else 2e-2      # a code may round the other way when fp32 sums are fused differently
     assert float((res[0] - res[1]).abs().max()) < tol * max(1.0, float(res[0].abs().max()))
-
-
-@pytest.mark.parametrize("name", ["FP16", "BF16", "NF4", "INT8", "INT4", "FP8_E4M3", "FP8_E5M2"])
-def test_casts_give_the_same_values_on_the_gpu_and_on_the_cpu(name):
-    """The reference's tests/gpu_cast_test.cpp: 2 sin(i) cast to each storage type and back agrees between devices."""
-    import math
-    import litetorch_b200 as lt
-    data = [math.sin(i) * 2.0 for i in range(128)]
-    dt = getattr(lt.DataType, name)
-    back = []
-    for dev in (lt.Device("cpu"), lt.Device("cuda", 0)):
-        t = lt.Tensor.from_vector(data, [128], dev, False)
-        back.append(t.cast(dt).cast(lt.DataType.FP32).to_vector())
-    assert max(abs(a - b) for a, b in zip(*back)) <= 1e-4
