@@ -61,3 +61,32 @@ def test_the_device_library_header_covers_every_bound_kernel_and_is_plain_c(tmp_
         r = subprocess.run([cc, "-fsyntax-only", "-I", os.path.join(ROOT, "csrc", "kernels"), "-I",
                             os.path.join(ROOT, "csrc", "runtime"), str(src)], capture_output=True, text=True, timeout=120)
         assert r.returncode == 0, r.stderr[-2000:]
+
+
+def _build_libtorch_example(tmp_path):
+    import torch
+    from torch.utils.cpp_extension import include_paths
+    from litetorch_b200 import _native
+    lib_dir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    lt_dir = os.path.join(ROOT, "litetorch_b200", "_lib")
+    if not os.path.exists(os.path.join(lt_dir, "liblt_cuda.so")):
+        _native.build_cuda()
+    exe = str(tmp_path / "lt_libtorch_linear")
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    cmd = (["g++", "-std=c++17", "-O1"] + ["-I" + p for p in include_paths("cuda")] + ["-I" + cuda_inc,
+           "-I" + os.path.join(ROOT, "csrc", "kernels"), os.path.join(ROOT, "examples", "libtorch_linear.cpp"),
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), "-L" + lib_dir, "-L" + lt_dir,
+           "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-llt_cuda",
+           "-Wl,-rpath," + lib_dir, "-Wl,-rpath," + lt_dir, "-o", exe])
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    return exe
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not os.path.isdir("/usr/local/cuda/include"), reason="needs g++ and the CUDA headers")
+def test_libtorch_example_compiles_and_links_against_the_device_library(tmp_path):
+    """examples/libtorch_linear.cpp: libtorch as the tensor layer, `lt_gemm_bf16` for the math.  Without a GPU the program
+    says so and exits 0; tests/test_zzz_libtorch_example_gpu.py runs it on a device."""
+    exe = _build_libtorch_example(tmp_path)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
