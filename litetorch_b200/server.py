@@ -45,6 +45,10 @@ class EngineLoop:
 
     def _run(self):
         try:
+            dev = getattr(getattr(self.model, "e", None), "device", None)
+            if dev is not None and dev.type == "cuda":
+                import torch
+                torch.cuda.set_device(dev)                      # the current device is per thread
             while True:
                 with self._wake:
                     while not self._stop and not self._done:
