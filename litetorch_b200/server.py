@@ -46,7 +46,7 @@ class EngineLoop:
     def _run(self):
         try:
             dev = getattr(getattr(self.model, "e", None), "device", None)
-            if dev is not None and dev.type == "cuda":
+            if dev is not None and dev.type == "cuda" and dev.index is not None:
                 import torch
                 torch.cuda.set_device(dev)                      # the current device is per thread
             while True:
