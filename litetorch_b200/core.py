@@ -270,6 +270,13 @@ class Tensor:
     def __mul__(self, o): return Tensor(self._t * _unwrap(o))
     def __truediv__(self, o): return Tensor(self._t / _unwrap(o))
     def __neg__(self): return Tensor(-self._t)
+    def __radd__(self, o): return Tensor(_unwrap(o) + self._t)
+    def __rsub__(self, o): return Tensor(_unwrap(o) - self._t)
+    def __rmul__(self, o): return Tensor(_unwrap(o) * self._t)
+
+    def __matmul__(self, o):
+        from .ops import Ops                     # the kernel path of Ops.matmul, not a plain torch product
+        return Ops.matmul(self, o)
 
 
 def _gpu_enabled() -> bool:
