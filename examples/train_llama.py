@@ -47,11 +47,18 @@ def main(argv=None) -> dict:
     ap.add_argument("--ckpt-every", type=int, default=50)
     ap.add_argument("--metrics", default="", help="JSON-lines file for per-step metrics")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--init-hf", default="", help="start from a Hugging Face Llama directory (fine-tuning): its config.json "
+                    "replaces the configuration's model, its weights are loaded unless --ckpt already holds a checkpoint")
+    ap.add_argument("--export-hf", default="", help="write the final weights as a Hugging Face directory")
     args = ap.parse_args(argv)
 
     elastic.start_heartbeat()                               # a no-op unless the elastic launcher started this process
     run = lt.config.load(args.config)
     cfg = LlamaConfig.tiny() if args.tiny else run.llama_config()
+    if args.init_hf:
+        from litetorch_b200.models import llama_io
+        with open(os.path.join(args.init_hf, "config.json")) as f:
+            cfg = llama_io.config_from_hf(json.load(f))
     seq_len = args.seq_len or min(run.seq_len, cfg.max_seq)
     batch = args.batch or run.micro_batch
     peak = args.lr or run.optim.lr
@@ -79,6 +86,9 @@ def main(argv=None) -> dict:
                                    rank=trainer.dp_rank, world=max(trainer.dp, 1)) if args.eval_every else None
     if args.metrics:
         trainer.log_metrics(args.metrics)
+    if args.init_hf and not (args.ckpt and Trainer.latest_checkpoint(args.ckpt)):
+        llama_io.load_into(trainer.engine, llama_io.read_state_dict(args.init_hf))     # every rank keeps its part
+        say("initialised from %s" % args.init_hf)
     if args.ckpt and Trainer.latest_checkpoint(args.ckpt):
         try:
             trainer.load(args.ckpt, loader=stream)
@@ -111,6 +121,9 @@ def main(argv=None) -> dict:
         if args.ckpt and (step % args.ckpt_every == 0 or step == args.steps):
             trainer.save(args.ckpt, keep=2, loader=stream, background=step != args.steps)
     trainer.finish_save()
+    if args.export_hf:
+        from litetorch_b200.models import llama_io
+        llama_io.save_pretrained(trainer.engine, args.export_hf, dtype=torch.float32 if args.device == "cpu" else torch.bfloat16)
     out = {"steps": trainer.engine.step_count, "losses": losses, "evals": evals, "seconds": round(time.time() - t0, 3),
            "epoch": stream.epoch, "position": stream.position}
     if trainer.rank == 0:

@@ -107,3 +107,24 @@ def test_example_continues_from_a_checkpoint_recut_for_fewer_ranks(tmp_path):
     checkpoint_tools.reshard(str(tmp_path / "ck2"), str(tmp_path / "ck1"), world=1)
     one = _run(common + ["--steps", "12", "--ckpt", str(tmp_path / "ck1")])
     assert one["steps"] == 12 and len(one["losses"]) == 6 and one["losses"][0] < two["losses"][0]
+
+
+def test_example_fine_tunes_from_a_hugging_face_directory_and_exports(tmp_path):
+    import torch
+    sys.path.insert(0, ROOT)
+    from litetorch_b200.models import llama_io
+    from litetorch_b200.models.llama import LlamaConfig, LlamaEngine, LocalWeights
+    data = str(tmp_path / "tokens.bin")
+    _tokens(data, vocab=256)
+    cfg = LlamaConfig(vocab_size=256, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=128, max_seq=64, name="base")
+    base = LlamaEngine(cfg, "cpu", weights=LocalWeights(cfg, "cpu", seed=11, param_dtype=torch.float32))
+    llama_io.save_pretrained(base, str(tmp_path / "base"), dtype=torch.float32)
+    out = _run(["--data", data, "--device", "cpu", "--init-hf", str(tmp_path / "base"), "--seq-len", "32", "--batch", "4",
+                "--lr", "2e-3", "--warmup", "2", "--steps", "12", "--export-hf", str(tmp_path / "tuned")])
+    # the first loss is the base model's loss on the first batch: the weights came from the directory, not from a seed
+    import litetorch_b200 as lt
+    stream = lt.data.TokenStream(data, 32, 4, shuffle=True, seed=0, rank=0, world=1)
+    tok, tgt = stream.next()
+    assert abs(out["losses"][0] - float(base.eval_loss(tok, tgt))) < 1e-4 and out["losses"][-1] < out["losses"][0]
+    tuned = llama_io.load_pretrained(str(tmp_path / "tuned"), device="cpu", weights=LocalWeights(cfg, "cpu", seed=0, param_dtype=torch.float32))
+    assert float(tuned.eval_loss(tok, tgt)) < float(base.eval_loss(tok, tgt))
