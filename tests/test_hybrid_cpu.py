@@ -303,3 +303,22 @@ def test_eval_loss_is_the_training_loss_without_side_effects():
     assert torch.equal(grads, t.engine.w.flat_g) and torch.equal(moments, t.engine.w.m) and t.engine.step_count == count
     assert abs(before - t.step(x, y)) < 1e-5          # the step reports the loss before its update
     assert t.evaluate(x, y) < before
+
+
+def test_targets_of_minus_100_are_ignored_in_loss_and_gradient():
+    """Masked positions (prompt tokens in supervised fine-tuning) contribute neither loss nor gradient; the mean is over
+    all positions, as in the unmasked case."""
+    import torch
+    from litetorch_b200.models.llama import LlamaConfig, LlamaEngine, LocalWeights, TorchLlama
+    cfg = LlamaConfig.tiny()
+    e = LlamaEngine(cfg, "cpu", weights=LocalWeights(cfg, "cpu", seed=1, param_dtype=torch.float32))
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(0))
+    x, y = tok[:, :-1], tok[:, 1:].clone()
+    y[:, :10] = -100
+    loss = float(e.forward_backward(x, y))
+    ref = TorchLlama(cfg)
+    ref.load_from([e.w.p(s.name).float() for s in e.w.specs])
+    want = torch.nn.functional.cross_entropy(ref(x).view(-1, cfg.vocab_size), y.reshape(-1), ignore_index=-100, reduction="sum") / y.numel()
+    want.backward()
+    assert abs(loss - float(want.detach())) < 1e-5 and abs(float(e.eval_loss(x, y)) - loss) < 1e-6
+    assert max(float((e.w.g(s.name) - ref.P(s.name).grad).abs().max()) for s in e.w.specs) < 1e-5
