@@ -4,8 +4,9 @@ for theirs to finish.  Standard library only.
 
     python -m litetorch_b200.server --model /models/llama --port 8000 [--sentencepiece tok.model | --bytes]
 
-    POST /generate   {"prompt": "text" | "prompt_ids": [1, 2, 3], "max_new_tokens": 32}
+    POST /generate   {"prompt": "text" | "prompt_ids": [1, 2, 3], "max_new_tokens": 32, "stream": false}
                   -> {"ids": [...], "text": "...", "prompt_tokens": n, "new_tokens": m, "seconds": s}
+                     with "stream": true, one JSON line per piece as the tokens arrive, then {"done": true, ...}
     GET  /health     {"running": r, "pending": p, "free_blocks": f, "served": n}
 
 Decoding is greedy (the decode step is replayed from CUDA graphs on a GPU).  The reference has the scheduler and no
@@ -37,6 +38,7 @@ class EngineLoop:
         self._lock = threading.Lock()              # the Python side of the scheduler (its request table) is not re-entrant
         self._wake = threading.Condition(self._lock)
         self._done = {}                            # request id -> Event
+        self._live = {}                            # request id -> (Request, tokens already handed out, queue or None)
         self._stop = False
         self.served = 0
         self.error: Optional[BaseException] = None
@@ -56,8 +58,15 @@ class EngineLoop:
                     if self._stop:
                         return
                     finished = self.sched.step(self.model)     # one step under the lock: submissions wait at most a step
+                    for rid, (req, seen, q) in list(self._live.items()):
+                        if q is not None and len(req.generated_tokens) > seen:        # streaming: hand out the new tokens
+                            q.put(list(req.generated_tokens[seen:]))
+                            self._live[rid] = (req, len(req.generated_tokens), q)
                     for r in finished:
                         ev = self._done.pop(r.id, None)
+                        _, _, q = self._live.pop(r.id, (None, 0, None))
+                        if q is not None:
+                            q.put(None)                        # end of stream
                         self.served += 1
                         if ev is not None:
                             ev.set()
@@ -66,9 +75,13 @@ class EngineLoop:
             with self._wake:
                 for ev in self._done.values():
                     ev.set()
+                for _, _, q in self._live.values():
+                    if q is not None:
+                        q.put(None)
                 self._done.clear()
+                self._live.clear()
 
-    def submit(self, prompt_ids: Sequence[int], max_new_tokens: int, timeout_s: float = 600.0) -> Request:
+    def _check(self, prompt_ids, max_new_tokens):
         need = (len(prompt_ids) + max_new_tokens + self.block_size - 1) // self.block_size
         if not prompt_ids or max_new_tokens < 1:
             raise ValueError("a request needs a prompt and at least one new token")
@@ -76,12 +89,38 @@ class EngineLoop:
             raise ValueError("the request does not fit: %d prompt + %d new tokens" % (len(prompt_ids), max_new_tokens))
         if self.error is not None:
             raise RuntimeError("the engine loop stopped: %r" % (self.error,))
+
+    def _enqueue(self, prompt_ids, max_new_tokens, q):
         ev = threading.Event()
         with self._wake:
             req = Request(next(self._ids), list(prompt_ids), max_new_tokens=max_new_tokens)
             self.sched.add_request(req)
             self._done[req.id] = ev
+            self._live[req.id] = (req, 0, q)
             self._wake.notify_all()
+        return req, ev
+
+    def stream(self, prompt_ids: Sequence[int], max_new_tokens: int, timeout_s: float = 600.0):
+        """Yields lists of new token ids as the engine produces them (one list per scheduling step that advanced the
+        request), then returns."""
+        import queue
+        self._check(prompt_ids, max_new_tokens)
+        q = queue.Queue()
+        self._enqueue(prompt_ids, max_new_tokens, q)
+        while True:
+            try:
+                item = q.get(timeout=timeout_s)
+            except queue.Empty:
+                raise TimeoutError("the stream stalled for %.0f s" % timeout_s)
+            if item is None:
+                break
+            yield item
+        if self.error is not None:
+            raise RuntimeError("the engine loop stopped: %r" % (self.error,))
+
+    def submit(self, prompt_ids: Sequence[int], max_new_tokens: int, timeout_s: float = 600.0) -> Request:
+        self._check(prompt_ids, max_new_tokens)
+        req, ev = self._enqueue(prompt_ids, max_new_tokens, None)
         if not ev.wait(timeout_s):
             raise TimeoutError("request %d did not finish in %.0f s" % (req.id, timeout_s))
         if self.error is not None:
@@ -113,6 +152,23 @@ def make_handler(loop: EngineLoop, encode, decode, default_new: int = 32):
         def log_message(self, *a):                              # quiet: one line per request is the caller's business
             pass
 
+        def _stream(self, ids, max_new, t0):
+            """One JSON object per line as tokens arrive ({"ids", "text"}), a closing line with the totals."""
+            pieces = loop.stream(ids, max_new)
+            first = next(pieces, None)                          # validation errors surface before the headers are sent
+            self.send_response(200)
+            self.send_header("Content-Type", "application/x-ndjson")
+            self.send_header("Connection", "close")
+            self.end_headers()
+            total = 0
+            while first is not None:
+                total += len(first)
+                self.wfile.write((json.dumps({"ids": first, "text": decode(first)}) + "\n").encode())
+                self.wfile.flush()
+                first = next(pieces, None)
+            self.wfile.write((json.dumps({"done": True, "prompt_tokens": len(ids), "new_tokens": total,
+                                          "seconds": round(time.time() - t0, 4)}) + "\n").encode())
+
         def do_GET(self):
             if self.path == "/health":
                 return self._send(200, loop.stats())
@@ -125,6 +181,8 @@ def make_handler(loop: EngineLoop, encode, decode, default_new: int = 32):
                 req = json.loads(self.rfile.read(int(self.headers.get("Content-Length", "0"))) or b"{}")
                 ids = [int(t) for t in req["prompt_ids"]] if "prompt_ids" in req else encode(str(req["prompt"]))
                 t0 = time.time()
+                if req.get("stream"):
+                    return self._stream(ids, int(req.get("max_new_tokens", default_new)), t0)
                 done = loop.submit(ids, int(req.get("max_new_tokens", default_new)))
                 out = list(done.generated_tokens)
                 self._send(200, {"ids": out, "text": decode(out), "prompt_tokens": len(ids), "new_tokens": len(out),

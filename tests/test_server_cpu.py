@@ -45,8 +45,17 @@ def test_concurrent_http_clients_get_the_greedy_continuations():
                 assert int(engine.forward_logits(torch.tensor([ctx]))[0, -1].argmax()) == tok
                 ctx.append(tok)
         assert _post(port, {"prompt": "5,6,7", "max_new_tokens": 2})["text"].count(",") == 1      # the text form of ids
+        # streaming: pieces arrive as JSON lines and concatenate to the non-streamed answer
+        req = urllib.request.Request("http://127.0.0.1:%d/generate" % port, headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"prompt_ids": prompts[1], "max_new_tokens": 5, "stream": True}).encode())
+        with urllib.request.urlopen(req, timeout=120) as r:
+            lines = [json.loads(l) for l in r.read().decode().splitlines()]
+        assert lines[-1]["done"] and lines[-1]["new_tokens"] == 5 and len(lines) >= 3
+        streamed = [t for l in lines[:-1] for t in l["ids"]]
+        assert streamed == _post(port, {"prompt_ids": prompts[1], "max_new_tokens": 5})["ids"]
+        assert [t for piece in loop.stream(prompts[0], 3) for t in piece] == answers[0]["ids"]
         health = json.loads(urllib.request.urlopen("http://127.0.0.1:%d/health" % port, timeout=30).read())
-        assert health == {"running": 0, "pending": 0, "free_blocks": 96, "served": 7}
+        assert health == {"running": 0, "pending": 0, "free_blocks": 96, "served": 10}
         assert not loop.sched._reqs and not loop.sched._order                      # nothing is kept for finished requests
         for bad in ({"max_new_tokens": 4}, {"prompt_ids": [], "max_new_tokens": 4}, {"prompt_ids": [1] * 250, "max_new_tokens": 50}):
             try:
