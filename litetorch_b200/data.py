@@ -238,3 +238,38 @@ def _ts_lib():
         lib.lt_ts_seek.argtypes = [c_void_p, c_uint64, c_uint64]
         lib._lt_ts_bound = True
     return lib
+
+
+def pack_examples(examples, seq_len: int, pad_id: int = 0, mask_prompt: bool = True):
+    """Supervised fine-tuning batches from `(prompt_ids, response_ids)` pairs: examples are laid end to end into rows of
+    `seq_len + 1` tokens (a new row starts when the next example does not fit; an example longer than a row is cut), and
+    the targets are -100 - ignored by the engine's loss - on prompt tokens (unless `mask_prompt=False`), on padding, and
+    where a row's next token belongs to another example.  Returns `(tokens [rows, seq_len], targets [rows, seq_len])` as
+    int64 CPU tensors, ready for `Trainer.step`."""
+    rows_t, rows_m = [], []
+    cur_t, cur_m = [], []
+
+    def flush():
+        if cur_t:
+            pad = seq_len + 1 - len(cur_t)
+            rows_t.append(cur_t + [pad_id] * pad)
+            rows_m.append(cur_m + [False] * pad)
+
+    for prompt, response in examples:
+        toks = [int(t) for t in prompt] + [int(t) for t in response]
+        keep = [not mask_prompt] * len(prompt) + [True] * len(response)
+        toks, keep = toks[:seq_len + 1], keep[:seq_len + 1]
+        if len(cur_t) + len(toks) > seq_len + 1:
+            flush()
+            cur_t, cur_m = [], []
+        if cur_t:
+            keep = [False] + keep[1:]            # the first token of an example is never predicted from the previous one
+        cur_t, cur_m = cur_t + toks, cur_m + keep
+    flush()
+    if not rows_t:
+        raise ValueError("no examples")
+    t = torch.tensor(rows_t, dtype=torch.int64)
+    m = torch.tensor(rows_m, dtype=torch.bool)
+    tokens, targets = t[:, :-1].contiguous(), t[:, 1:].clone()
+    targets[~m[:, 1:]] = -100                    # position j predicts token j + 1: masked when that token is not kept
+    return tokens, targets

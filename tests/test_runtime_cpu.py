@@ -245,6 +245,18 @@ def test_token_stream_windows_ranks_epochs_and_exact_resume(tmp_path):
     assert firsts[0] == [0, 10] and firsts[1] == [20, 30] and firsts[-1] == [0, 10] and seq.epoch == 1
 
 
+def test_pack_examples_masks_prompts_padding_and_example_boundaries():
+    tok, tgt = lt.data.pack_examples([([1, 2, 3], [4, 5]), ([6], [7, 8, 9]), ([10, 11], [12])], seq_len=8, pad_id=0)
+    assert tok.tolist() == [[1, 2, 3, 4, 5, 6, 7, 8], [10, 11, 12, 0, 0, 0, 0, 0]]
+    assert tgt.tolist() == [[-100, -100, 4, 5, -100, 7, 8, 9], [-100, 12, -100, -100, -100, -100, -100, -100]]
+    tok, tgt = lt.data.pack_examples([([1, 2], [3])], seq_len=4, mask_prompt=False)
+    assert tgt.tolist() == [[2, 3, -100, -100]]
+    tok, tgt = lt.data.pack_examples([(list(range(1, 8)), [8, 9, 10])], seq_len=4)          # longer than a row: cut
+    assert tok.tolist() == [[1, 2, 3, 4]] and tgt.tolist() == [[-100] * 4]
+    with pytest.raises(ValueError):
+        lt.data.pack_examples([], seq_len=4)
+
+
 def test_python_dataset_subclass():
     class Sq(lt.data.Dataset):
         def size(self): return 10
