@@ -8,6 +8,7 @@ for theirs to finish.  Standard library only.
                   -> {"ids": [...], "text": "...", "prompt_tokens": n, "new_tokens": m, "seconds": s}
                      with "stream": true, one JSON line per piece as the tokens arrive, then {"done": true, ...}
     GET  /health     {"running": r, "pending": p, "free_blocks": f, "served": n}
+    GET  /metrics    the same counters and the prefill token counts in the Prometheus text format
 
 Decoding is greedy (the decode step is replayed from CUDA graphs on a GPU).  The reference has the scheduler and no
 server around it (src/llm/continuous_batching.cpp); `EngineLoop` is that missing piece and is usable without HTTP:
@@ -172,6 +173,20 @@ def make_handler(loop: EngineLoop, encode, decode, default_new: int = 32):
         def do_GET(self):
             if self.path == "/health":
                 return self._send(200, loop.stats())
+            if self.path == "/metrics":                         # Prometheus text exposition format
+                st = loop.stats()
+                model = loop.model
+                st["prefill_tokens_computed"] = getattr(model, "prefill_tokens_computed", 0)
+                st["prefill_tokens_reused"] = getattr(model, "prefill_tokens_reused", 0)
+                kinds = {"served": "counter", "prefill_tokens_computed": "counter", "prefill_tokens_reused": "counter"}
+                body = "".join("# TYPE litetorch_%s %s\nlitetorch_%s %d\n" % (k, kinds.get(k, "gauge"), k, int(v))
+                               for k, v in sorted(st.items())).encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+                return
             self._send(404, {"error": "unknown path"})
 
         def do_POST(self):

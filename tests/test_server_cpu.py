@@ -56,6 +56,9 @@ def test_concurrent_http_clients_get_the_greedy_continuations():
         assert [t for piece in loop.stream(prompts[0], 3) for t in piece] == answers[0]["ids"]
         health = json.loads(urllib.request.urlopen("http://127.0.0.1:%d/health" % port, timeout=30).read())
         assert health == {"running": 0, "pending": 0, "free_blocks": 96, "served": 10}
+        metrics = urllib.request.urlopen("http://127.0.0.1:%d/metrics" % port, timeout=30).read().decode()
+        assert "litetorch_served 10" in metrics and "# TYPE litetorch_free_blocks gauge" in metrics
+        assert "litetorch_prefill_tokens_computed" in metrics
         assert not loop.sched._reqs and not loop.sched._order                      # nothing is kept for finished requests
         for bad in ({"max_new_tokens": 4}, {"prompt_ids": [], "max_new_tokens": 4}, {"prompt_ids": [1] * 250, "max_new_tokens": 50}):
             try:
