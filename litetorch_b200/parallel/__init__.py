@@ -12,7 +12,17 @@ from .cp import (context_parallel_backward, context_parallel_forward, ring_atten
 from .ep import MoEFeedForward
 from .ulysses import head_to_seq, seq_to_head, ulysses_attention
 from .fsdp_api import FSDP, FullyShardedDataParallel
-from .elastic import ElasticLauncher
+
+
+def __getattr__(name):
+    # imported on first use, so that `python -m litetorch_b200.parallel.elastic` does not find its module half-loaded
+    if name == "ElasticLauncher":
+        from .elastic import ElasticLauncher
+        return ElasticLauncher
+    if name == "elastic":
+        import importlib
+        return importlib.import_module(".elastic", __name__)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))
 from ..core import manual_seed
 
 __all__ = [n for n in dir() if not n.startswith("_")]
