@@ -25,7 +25,7 @@ def __getattr__(name):
     raise AttributeError("module %r has no attribute %r" % (__name__, name))
 from ..core import manual_seed
 
-__all__ = [n for n in dir() if not n.startswith("_")]
+__all__ = [n for n in dir() if not n.startswith("_")] + ["ElasticLauncher"]
 
 # the reference's bindings export the enum values into the module as well (py::enum_::export_values,
 # src/bindings/python_bindings.cpp:748-752)
