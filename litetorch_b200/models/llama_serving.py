@@ -290,7 +290,8 @@ class Sampler:
 @torch.no_grad()
 def generate(engine: LlamaEngine, prompts: Sequence[Sequence[int]], max_new_tokens: int, *, temperature: float = 0.0,
              top_k: int = 0, top_p: float = 1.0, seed: int = 0, eos_id: int = -1, block_size: int = 16,
-             max_num_seqs: int = 64, max_num_batched_tokens: int = 4096, kv_dtype=None) -> List[List[int]]:
+             max_num_seqs: int = 64, max_num_batched_tokens: int = 4096, kv_dtype=None,
+             prefix_cache_bytes: int = 0) -> List[List[int]]:
     """Continue every prompt by up to `max_new_tokens` tokens (stopping at `eos_id`) with continuous batching on a paged KV
     cache sized for the request, and return the new tokens per prompt.  Greedy by default (the decode step is replayed
     from CUDA graphs on a GPU); with `temperature > 0` the next tokens are drawn by `Sampler` (eager decode steps)."""
@@ -300,7 +301,8 @@ def generate(engine: LlamaEngine, prompts: Sequence[Sequence[int]], max_new_toke
     greedy = temperature <= 0.0 or top_k == 1
     if kv_dtype is None:
         kv_dtype = torch.bfloat16 if engine.device.type == "cuda" else torch.float32
-    model = LlamaKVModel(engine, num_blocks=need + 1, block_size=block_size, kv_dtype=kv_dtype, graphs=greedy)
+    model = LlamaKVModel(engine, num_blocks=need + 1, block_size=block_size, kv_dtype=kv_dtype, graphs=greedy,
+                         prefix_cache_bytes=prefix_cache_bytes)   # prompts of one call that share a prefix reuse its blocks
     if not greedy:
         model.sampler = Sampler(temperature, top_k, top_p, seed, device=engine.device)
     sched = ServingScheduler(num_blocks=need + 1, block_size=block_size, max_num_seqs=max_num_seqs,

@@ -101,6 +101,8 @@ def test_generate_equals_transformers_greedy_decoding_and_sampling_is_seeded():
         with torch.no_grad():
             ref = model.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False, pad_token_id=0, eos_token_id=None)
         assert ref[0, len(p):].tolist() == o
+    shared = [prompts[1] + [7, 8, 9], prompts[1] + [11, 12]]                    # a common 19-token prefix
+    assert generate(engine, shared, 4, block_size=4, max_num_seqs=1, prefix_cache_bytes=1 << 20) == generate(engine, shared, 4, block_size=4)
     # sampling: top_k = 1 is greedy, a seed reproduces a run, another seed changes it, tokens stay inside the top-k set
     assert generate(engine, prompts, 8, temperature=0.8, top_k=1) == ours
     a = generate(engine, prompts, 8, temperature=1.5, top_k=20, top_p=0.9, seed=5)
